@@ -1,0 +1,163 @@
+/* zippel_b200 -- C ABI of the B200 (sm_100a) kernels for the eSEN SO(2) edge-convolution
+ * block: gather, per-edge Wigner-D rotation, per-m SO(2) linear mixing, gate, inverse
+ * rotation, deterministic segmented scatter, and the matching first-order VJP.
+ *
+ * The reference project has no native boundary: its GPU back end is a Python API
+ * (codegen/compose.py:113-239 compile_program / allocate / run_program) that launches
+ * run-time generated kernels.  Each entry point below names the reference code whose work
+ * it takes over.
+ *
+ * Conventions
+ *   - every function returns a zp_status (0 = ok); nothing throws across the boundary
+ *   - unless said otherwise every pointer is DEVICE memory owned by the caller, fp32 values,
+ *     int32 indices, row-major, 16-byte aligned
+ *   - every launch goes to the cudaStream_t given as `stream` (an opaque pointer here)
+ *   - edges are expected in destination-sorted order (see zp_csr_build); `row_ptr[n]` ..
+ *     `row_ptr[n+1]` are the edges whose destination is node n
+ *   - a zp_plan owns static tables only (layout indices, the J matrices); it may be shared
+ *     by threads that use different streams and different workspaces
+ */
+#ifndef ZIPPEL_B200_H
+#define ZIPPEL_B200_H
+
+#include <stddef.h>
+#include <stdint.h>
+
+#ifdef __cplusplus
+extern "C" {
+#endif
+
+typedef enum zp_status {
+  ZP_OK = 0,
+  ZP_ERR_INVALID_ARG = 1,      /* null pointer, negative size, misaligned pointer          */
+  ZP_ERR_UNSUPPORTED = 2,      /* lmax/mmax/channel combination outside the built kernels  */
+  ZP_ERR_WORKSPACE = 3,        /* workspace smaller than zp_workspace_bytes()              */
+  ZP_ERR_CUDA = 4,             /* a CUDA runtime call failed; see zp_last_cuda_error()     */
+  ZP_ERR_DEVICE_TIMEOUT = 5,   /* a bounded device-side wait gave up (status word set)     */
+  ZP_ERR_NO_DEVICE_CODE = 6    /* the library holds no code for this GPU (needs sm_100a)   */
+} zp_status;
+
+/* Mirrors the fields of the reference's BlockConfig (blocks/eso2_ref.py:51-76) that the
+ * kernel path reads.  precision: 0 = fp32 storage, fp32-accurate contraction (3xTF32 on
+ * the tensor cores); 1 = bf16 operands for the SO(2) contraction, fp32 accumulate.        */
+typedef struct zp_config {
+  int32_t lmax;
+  int32_t mmax;
+  int32_t sphere_channels;   /* C  */
+  int32_t hidden_channels;   /* H  */
+  int32_t precision;
+} zp_config;
+
+/* Derived sizes, filled by zp_plan_sizes(). */
+typedef struct zp_sizes {
+  int32_t K;         /* (lmax+1)^2, rows of x_node / node_out                               */
+  int32_t Km;        /* m'-major rows with |m| <= mmax                                      */
+  int32_t nnz;       /* nonzeros of one edge's [Km, K] rotation (block diagonal in l)       */
+  int32_t nnz_pad;   /* row stride of the packed rotation array (nnz rounded up to 4)       */
+  int32_t R;         /* radial width: 2C * sum_m m_size[m]                                  */
+  int32_t n_gate;    /* lmax * H gate scalars emitted by conv1's m = 0 head                 */
+  int32_t w1_cols;   /* n_gate + Km*H: row width of conv1's output                          */
+} zp_sizes;
+
+typedef struct zp_plan zp_plan;
+
+const char *zp_status_string(int status);
+/* Text of the last CUDA error seen by this thread inside the library. */
+const char *zp_last_cuda_error(void);
+/* 1 if the current device can run the kernels in this library (compute capability 10.x). */
+int zp_device_supported(void);
+
+/* Layout tables (replaces Layout.make / to_m / gate_expand_index, blocks/eso2_ref.py:98-146,
+ * with the rectangular [Km, K] selection for mmax < lmax).  `jd_host` is HOST memory: the
+ * J_l matrices for l = 0..lmax, each (2l+1)^2 doubles row-major, concatenated.             */
+int zp_plan_create(const zp_config *cfg, const double *jd_host, zp_plan **plan_out);
+int zp_plan_destroy(zp_plan *plan);
+int zp_plan_sizes(const zp_plan *plan, zp_sizes *out);
+/* Host copies of the index tables, for callers and tests: row_l/row_m [Km] give (l, signed m)
+ * of each m' row, rot_off [Km] the offset of that row's 2l+1 entries in a packed rotation,
+ * gate_idx [Km] the gate scalar block (l-1) used by the row (-1 for row 0).                */
+int zp_plan_tables(const zp_plan *plan, int32_t *row_l, int32_t *row_m, int32_t *rot_off,
+                   int32_t *gate_idx);
+
+/* Destination-sorted edge order and CSR offsets (the reference scatters with index_add_,
+ * blocks/eso2_ref.py:346-349, and has no sorted form).  Stable sort of the E edges by
+ * (dst, src, original position); `perm[i]` is the original position of sorted edge i.
+ * Also builds the source-sorted view used by the backward scatter: `perm_src[i]` is the
+ * SORTED-edge id of the i-th edge in (src, sorted id) order and `row_ptr_src` its offsets.
+ * `work` needs zp_csr_work_bytes(E, N) bytes.                                              */
+size_t zp_csr_work_bytes(int64_t n_edges, int64_t n_nodes);
+int zp_csr_build(const int64_t *edge_index /* [2,E] int64: row 0 src, row 1 dst */,
+                 int64_t n_edges, int64_t n_nodes,
+                 int32_t *perm, int32_t *src_sorted, int32_t *dst_sorted, int32_t *row_ptr,
+                 int32_t *perm_src, int32_t *row_ptr_src, void *work, size_t work_bytes,
+                 void *stream);
+
+/* Packed rotation rot[e, rot_off[r] + j] = D_l(e)[row of (l, m_r), j], the nonzeros of
+ * to_m @ wigner (replaces wigner_from_edge_vec, blocks/wigner.py:115-160, and the einsum at
+ * blocks/eso2_ref.py:330-331).  edge_vec [E,3], cos_g/sin_g [E, lmax+1], rot [E, nnz_pad].  */
+int zp_wigner_forward(const zp_plan *plan, int64_t n_edges, const float *edge_vec,
+                      const float *cos_g, const float *sin_g, float *rot, void *stream);
+/* VJP of the above w.r.t. edge_vec (autograd through blocks/wigner.py:60-160, including the
+ * clamp_min masks).  grad_rot [E, nnz_pad] -> grad_edge_vec [E,3] (overwritten).            */
+int zp_wigner_backward(const zp_plan *plan, int64_t n_edges, const float *edge_vec,
+                       const float *cos_g, const float *sin_g, const float *grad_rot,
+                       float *grad_edge_vec, void *stream);
+
+/* SO(2) weights in the reference module's own layout (blocks/eso2_ref.py:184-202):
+ * c1_w0 [n_gate + (lmax+1)H, (lmax+1)*2C] + bias, c1_wm[m-1] [2*km*H, km*2C],
+ * c2_w0 [(lmax+1)C, (lmax+1)H] + bias, c2_wm[m-1] [2*km*C, km*H]; km = lmax+1-m.
+ * The pointer arrays c1_wm / c2_wm are HOST arrays of mmax device pointers.                */
+typedef struct zp_weights {
+  const float *c1_w0;
+  const float *c1_b0;
+  const float *const *c1_wm;
+  const float *c2_w0;
+  const float *c2_b0;
+  const float *const *c2_wm;
+} zp_weights;
+
+typedef struct zp_weight_grads {
+  float *c1_w0;
+  float *c1_b0;
+  float *const *c1_wm;
+  float *c2_w0;
+  float *c2_b0;
+  float *const *c2_wm;
+} zp_weight_grads;
+
+/* Bytes of scratch + saved activations for E edges / N nodes.  The same workspace must be
+ * passed to zp_eso2_forward and to the zp_eso2_backward that follows it.                   */
+size_t zp_workspace_bytes(const zp_plan *plan, int64_t n_nodes, int64_t n_edges,
+                          int with_backward);
+
+/* node_out[n] = sum over edges e into n of  rot_e^T * env_e * conv2(gate(conv1(radial_e .
+ * (rot_e [x_src ; x_dst])))).  Replaces blocks/eso2_ref.py:334-349 and the 55-kernel program
+ * run by codegen/compose.py:218-239.  x_node, node_out [N, K, C]; edge_vec [E,3];
+ * cos_g, sin_g [E, lmax+1]; radial [E, R]; env [E]; src, dst [E]; row_ptr [N+1].
+ * node_out is overwritten (rows without incoming edges become zero).                       */
+int zp_eso2_forward(const zp_plan *plan, int64_t n_nodes, int64_t n_edges,
+                    const float *x_node, const float *edge_vec, const float *cos_g,
+                    const float *sin_g, const float *radial, const float *env,
+                    const int32_t *src, const int32_t *dst, const int32_t *row_ptr,
+                    const zp_weights *w, float *node_out, void *workspace,
+                    size_t workspace_bytes, void *stream);
+
+/* First-order VJP of zp_eso2_forward (what torch.autograd.grad computes through
+ * blocks/eso2_ref.py:334-349; IR rule zippel/vjp.py:88-153).  Needs the workspace of the
+ * matching forward call.  Outputs (all overwritten): grad_x_node [N,K,C]; grad_edge_vec
+ * [E,3] (through the rotation only); grad_radial [E,R]; grad_env [E]; weight gradients in
+ * the reference layout.  perm_src / row_ptr_src: the source-sorted view from zp_csr_build.  */
+int zp_eso2_backward(const zp_plan *plan, int64_t n_nodes, int64_t n_edges,
+                     const float *grad_node_out, const float *x_node, const float *edge_vec,
+                     const float *cos_g, const float *sin_g, const float *radial,
+                     const float *env, const int32_t *src, const int32_t *dst,
+                     const int32_t *row_ptr, const int32_t *perm_src,
+                     const int32_t *row_ptr_src, const zp_weights *w, float *grad_x_node,
+                     float *grad_edge_vec, float *grad_radial, float *grad_env,
+                     const zp_weight_grads *gw, void *workspace, size_t workspace_bytes,
+                     void *stream);
+
+#ifdef __cplusplus
+}
+#endif
+#endif /* ZIPPEL_B200_H */

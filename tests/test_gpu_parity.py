@@ -1,0 +1,177 @@
+"""GPU parity: the CUDA path (through the C ABI) against the golden vectors of the reference
+and against the CPU oracle on seeded inputs.  Tolerance: 1e-5 relative L2 for fp32 outputs and
+gradients; sort order, CSR offsets and index maps bit-exact."""
+
+from __future__ import annotations
+
+import ctypes
+
+import numpy as np
+import pytest
+import torch
+
+from oracle import eso2_oracle as orc
+from tests.conftest import golden_names, load_golden
+from tests.helpers import (gpu_node_out_and_vjp, make_block, oracle_node_out_and_vjp,
+                           random_case, rel_l2)
+
+pytestmark = pytest.mark.gpu
+TOL = 1e-5
+
+
+def check_against(node_out, gx, gpos, pg, want_out, want_gx, want_gpos, want_pg, tol=TOL):
+    assert rel_l2(node_out, want_out) < tol
+    assert rel_l2(gx, want_gx) < tol
+    assert rel_l2(gpos, want_gpos) < tol
+    for name, want in want_pg.items():
+        got = pg[name]
+        if want is None or want.abs().max().item() == 0.0:
+            assert got is None or got.abs().max().item() == 0.0, name
+            continue
+        assert rel_l2(got, want) < tol, name
+
+
+@pytest.mark.parametrize("name", golden_names())
+def test_golden_reference_vectors(name):
+    c = load_golden(name)
+    block = make_block(c["cfg"], c["params"])
+    out = gpu_node_out_and_vjp(block, c, c["upstream"])
+    check_against(*out, c["node_out"], c["vjp_x_node"], c["vjp_pos"], c["vjp_params"])
+    # and the scalar E with its force through the reference call signature
+    pos = c["pos"].cuda().float().requires_grad_(True)
+    e = block(pos, c["atomic_numbers"].cuda(), c["x_node"].cuda().float(), c["edge_index"].cuda(),
+              c["shifts"].cuda().float(), c["cos_gamma_k"].cuda().float(),
+              c["sin_gamma_k"].cuda().float(), None)
+    (f,) = torch.autograd.grad(e, pos)
+    assert abs(e.item() - c["energy"].item()) < 1e-5 * max(1.0, abs(c["energy"].item()))
+    assert rel_l2(f, c["de_dpos"]) < TOL
+
+
+ORACLE_CASES = [
+    # lmax, mmax, C, H, EC, NB, nodes, edges
+    (4, 2, 8, 8, 8, 6, 12, 60),
+    (6, 2, 4, 8, 4, 5, 9, 40),
+    (3, 1, 12, 4, 8, 4, 7, 33),
+    (2, 2, 32, 32, 32, 32, 20, 150),
+    (5, 3, 8, 4, 4, 4, 6, 25),
+    (1, 0, 4, 4, 4, 4, 5, 12),
+]
+
+
+@pytest.mark.parametrize("lmax,mmax,c,h,ec,nb,n,e", ORACLE_CASES)
+def test_oracle_parity_small(lmax, mmax, c, h, ec, nb, n, e, jd64):
+    cfg = dict(lmax=lmax, mmax=mmax, sphere_channels=c, hidden_channels=h, edge_channels=ec,
+               num_distance_basis=nb, cutoff=5.0)
+    params = orc.init_params(cfg, seed=lmax * 10 + mmax)
+    case = random_case(cfg, n, e, seed=100 + lmax)
+    want = oracle_node_out_and_vjp(cfg, params, case, case["upstream"], jd64)
+    got = gpu_node_out_and_vjp(make_block(cfg, params), case, case["upstream"])
+    check_against(*got, *want)
+
+
+def test_nodes_without_edges_and_empty_graph(jd64):
+    cfg = dict(lmax=2, mmax=1, sphere_channels=8, hidden_channels=8, edge_channels=4,
+               num_distance_basis=4, cutoff=5.0)
+    params = orc.init_params(cfg, seed=3)
+    block = make_block(cfg, params)
+    case = random_case(cfg, 10, 6, seed=5)
+    case["edge_index"][1] = torch.tensor([2, 2, 2, 7, 7, 2])     # ragged: most nodes empty
+    case["edge_index"][0] = torch.tensor([0, 1, 3, 0, 9, 5])
+    want = oracle_node_out_and_vjp(cfg, params, case, case["upstream"], jd64)
+    got = gpu_node_out_and_vjp(block, case, case["upstream"])
+    check_against(*got, *want)
+    assert got[0][[0, 1, 3, 4, 5, 6, 8, 9]].abs().max().item() == 0.0
+    # no edges at all: zero output, zero gradients
+    empty = dict(case, edge_index=torch.zeros(2, 0, dtype=torch.long),
+                 shifts=torch.zeros(0, 3, dtype=torch.float64),
+                 cos_gamma_k=torch.zeros(0, 3, dtype=torch.float64),
+                 sin_gamma_k=torch.zeros(0, 3, dtype=torch.float64))
+    node_out, gx, gpos, pg = gpu_node_out_and_vjp(block, empty, case["upstream"])
+    assert node_out.abs().max().item() == 0.0 and gx.abs().max().item() == 0.0
+    assert pg["c1_m0.weight"].abs().max().item() == 0.0
+
+
+def test_high_degree_node(jd64):
+    """One destination with far more than 30 incoming edges (the reference applies no cap)."""
+    cfg = dict(lmax=2, mmax=2, sphere_channels=8, hidden_channels=8, edge_channels=4,
+               num_distance_basis=4, cutoff=6.0)
+    params = orc.init_params(cfg, seed=8)
+    case = random_case(cfg, 40, 300, seed=9)
+    case["edge_index"][1, :200] = 17
+    case["edge_index"][0, :200] = torch.arange(200) % 39
+    case["edge_index"][0, :200][case["edge_index"][0, :200] >= 17] += 1
+    want = oracle_node_out_and_vjp(cfg, params, case, case["upstream"], jd64)
+    got = gpu_node_out_and_vjp(make_block(cfg, params), case, case["upstream"])
+    check_against(*got, *want)
+
+
+@pytest.mark.parametrize("lmax,mmax", [(2, 2), (4, 2), (6, 2), (3, 3)])
+def test_wigner_kernel_forward_backward(lmax, mmax, jd64):
+    from zippel_b200 import _lib
+    from zippel_b200.blocks.eso2 import Plan
+    plan = Plan.get(lmax, mmax, 8, 8, "cuda")
+    lib, s = _lib.load(), plan.sizes
+    g = torch.Generator("cpu").manual_seed(lmax)
+    e = 257
+    ev = torch.randn(e, 3, generator=g, dtype=torch.float64)
+    ev[0] = torch.tensor([0.0, 1.3, 0.0])            # on the pole: clamp path
+    ev[1] = torch.tensor([1e-4, -2.0, 1e-4])
+    gamma = torch.rand(e, generator=g, dtype=torch.float64) * 6.28
+    cg, sg = orc.gamma_harmonics(gamma, lmax)
+    ev32 = ev.float()
+    evd = ev32.double().requires_grad_(True)          # oracle sees the same rounded inputs
+    rot = orc.edge_rotation(evd, cg.float().double(), sg.float().double(), lmax, mmax, jd64)
+    tabs = plan.tables()
+    d_ev, d_cg, d_sg = ev32.cuda(), cg.float().cuda(), sg.float().cuda()
+    out = torch.zeros(e, s.nnz_pad, device="cuda")
+    st = torch.cuda.current_stream().cuda_stream
+    _lib.check(lib.zp_wigner_forward(plan.handle, e, d_ev.data_ptr(), d_cg.data_ptr(),
+                                     d_sg.data_ptr(), out.data_ptr(), st), "fwd")
+    dense = torch.zeros(e, s.Km, s.K, dtype=torch.float64)
+    up = torch.randn(e, s.Km, s.K, generator=g, dtype=torch.float64)
+    gpacked = torch.zeros(e, s.nnz_pad)
+    mask = torch.zeros(s.Km, s.K, dtype=torch.float64)
+    for r in range(s.Km):
+        l, off = int(tabs["row_l"][r]), int(tabs["rot_off"][r])
+        dense[:, r, l * l:(l + 1) ** 2] = out[:, off:off + 2 * l + 1].double().cpu()
+        gpacked[:, off:off + 2 * l + 1] = up[:, r, l * l:(l + 1) ** 2].float()
+        mask[r, l * l:(l + 1) ** 2] = 1.0
+    assert (dense - rot.detach()).abs().max().item() < 2e-7
+    (want,) = torch.autograd.grad((rot * up.float().double() * mask).sum(), evd)
+    gev = torch.zeros(e, 3, device="cuda")
+    d_g = gpacked.cuda()
+    _lib.check(lib.zp_wigner_backward(plan.handle, e, d_ev.data_ptr(), d_cg.data_ptr(),
+                                      d_sg.data_ptr(), d_g.data_ptr(), gev.data_ptr(), st), "bwd")
+    # the two near-pole edges have huge, ill-conditioned derivatives; compare them separately
+    assert rel_l2(gev[2:], want[2:]) < 1e-6
+    assert rel_l2(gev[:2], want[:2]) < 1e-3
+
+
+@pytest.mark.parametrize("n,e,seed", [(1, 0, 0), (5, 1, 1), (50, 1000, 2), (3000, 50000, 3),
+                                      (7, 400, 4)])
+def test_csr_build_bit_exact(n, e, seed):
+    from zippel_b200.graph import EdgeGraph, csr_reference
+    g = torch.Generator("cpu").manual_seed(seed)
+    ei = torch.randint(0, n, (2, e), generator=g)
+    want = csr_reference(ei.numpy(), n)
+    got = EdgeGraph.build(ei.cuda(), n)
+    for key in ("perm", "src", "dst", "row_ptr", "perm_src", "row_ptr_src"):
+        assert np.array_equal(getattr(got, key).cpu().numpy(), want[key]), key
+
+
+def test_abi_rejects_bad_arguments():
+    from zippel_b200 import _lib
+    from zippel_b200.blocks.eso2 import Plan
+    lib = _lib.load()
+    cfg = _lib.ZpConfig(7, 2, 8, 8, 0)
+    h = ctypes.c_void_p()
+    jd = (ctypes.c_double * 4)()
+    assert lib.zp_plan_create(ctypes.byref(cfg), jd, ctypes.byref(h)) == 2      # lmax too large
+    cfg = _lib.ZpConfig(2, 3, 8, 8, 0)
+    assert lib.zp_plan_create(ctypes.byref(cfg), jd, ctypes.byref(h)) == 2      # mmax > lmax
+    cfg = _lib.ZpConfig(2, 2, 6, 8, 0)
+    assert lib.zp_plan_create(ctypes.byref(cfg), jd, ctypes.byref(h)) == 2      # C % 4
+    assert lib.zp_plan_create(None, jd, ctypes.byref(h)) == 1
+    plan = Plan.get(2, 2, 8, 8, "cuda")
+    assert lib.zp_workspace_bytes(plan.handle, 4, -1, 0) == 0
+    assert lib.zp_wigner_forward(plan.handle, 5, None, None, None, None, None) == 1

@@ -1,0 +1,334 @@
+"""The eSEN SO(2) interaction block on the B200 kernels.
+
+Drop-in for the reference's ``blocks/eso2_ref.py``: ``BlockConfig`` and ``Layout`` carry the
+same fields (``eso2_ref.py:51-146``), ``ESO2Block`` has the parameter names, ``state_dict`` and
+``forward`` signature of ``ESO2RefBlock`` (``eso2_ref.py:154-351``), and
+``conservative_training_step`` is *not* offered (it needs a double backward, which the kernels
+do not provide).  Unlike the reference, ``mmax < lmax`` works: the l-major -> m'-major selection
+is the rectangular ``[Km, K]`` matrix.
+
+What runs where
+    * edge geometry, Gaussian basis, element embedding, the radial MLP, the envelope and the
+      readout head are small torch ops on the GPU;
+    * everything per edge and per (l, m, channel) -- gather, Wigner-D rotation, both SO(2)
+      convolutions, the gate, rotation back and the scatter onto destination nodes, forward and
+      VJP -- is one call into the C ABI (``zp_eso2_forward`` / ``zp_eso2_backward``) through
+      ``EdgeConvFunction``.
+There is no fallback: without the built library and a supported GPU every call raises.
+"""
+
+from __future__ import annotations
+
+import ctypes
+import math
+from dataclasses import dataclass
+
+import numpy as np
+import torch
+import torch.nn as nn
+
+from .. import _lib
+from ..graph import EdgeGraph
+
+_JD_PATH = __import__("pathlib").Path(__file__).resolve().parent.parent / "data" / "jd.npz"
+
+
+def load_jd(lmax: int = 6) -> list[torch.Tensor]:
+    """The J_l matrices (l = 0..lmax, FP64) shipped with the package; same values as the
+    reference's ``blocks/Jd.pt``."""
+    z = np.load(_JD_PATH)
+    return [torch.from_numpy(z[f"J{l}"]) for l in range(lmax + 1)]
+
+
+@dataclass(frozen=True)
+class BlockConfig:
+    lmax: int = 2
+    mmax: int = 2
+    sphere_channels: int = 128
+    hidden_channels: int = 128
+    edge_channels: int = 128
+    num_distance_basis: int = 64
+    cutoff: float = 6.0
+    max_num_elements: int = 100
+    envelope_exponent: int = 5
+
+    @property
+    def num_coeffs(self) -> int:
+        return (self.lmax + 1) ** 2
+
+    @property
+    def edge_channels_list(self) -> list[int]:
+        return [self.num_distance_basis + 2 * self.edge_channels, self.edge_channels,
+                self.edge_channels]
+
+
+@dataclass(frozen=True)
+class Layout:
+    """Index tables of an (lmax, mmax) pair."""
+
+    lmax: int
+    mmax: int
+    m_size: tuple[int, ...]
+    m_split: tuple[int, ...]
+
+    @staticmethod
+    def make(lmax: int, mmax: int) -> "Layout":
+        m_size = tuple(lmax + 1 - m for m in range(mmax + 1))
+        return Layout(lmax, mmax, m_size, (m_size[0],) + tuple(2 * s for s in m_size[1:]))
+
+    @property
+    def rows(self) -> list[tuple[int, int]]:
+        """(l, signed m) per m'-major row."""
+        out = [(l, 0) for l in range(self.lmax + 1)]
+        for m in range(1, self.mmax + 1):
+            out += [(l, m) for l in range(m, self.lmax + 1)]
+            out += [(l, -m) for l in range(m, self.lmax + 1)]
+        return out
+
+    def to_m(self, device, dtype) -> torch.Tensor:
+        """[Km, K] selection from l-major (l, m = -l..l) to m'-major rows."""
+        rows = self.rows
+        mat = torch.zeros(len(rows), (self.lmax + 1) ** 2, device=device, dtype=dtype)
+        for r, (l, m) in enumerate(rows):
+            mat[r, l * l + l + m] = 1.0
+        return mat
+
+    def gate_expand_index(self, device) -> torch.Tensor:
+        return torch.tensor([l - 1 for l, _ in self.rows[1:]], dtype=torch.long, device=device)
+
+
+# --------------------------------------------------------------------------------------------
+# plan cache and the autograd function over the C ABI
+# --------------------------------------------------------------------------------------------
+
+
+class Plan:
+    """Owns one ``zp_plan`` (static tables on one device)."""
+
+    _cache: dict = {}
+
+    def __init__(self, lmax: int, mmax: int, c: int, h: int, device: torch.device):
+        lib = _lib.load()
+        self.device = device
+        jd = np.concatenate([j.numpy().astype(np.float64).ravel() for j in load_jd(lmax)])
+        cfg = _lib.ZpConfig(lmax, mmax, c, h, 0)
+        handle = ctypes.c_void_p()
+        with torch.cuda.device(device):
+            _lib.check(lib.zp_plan_create(ctypes.byref(cfg),
+                                          jd.ctypes.data_as(ctypes.POINTER(ctypes.c_double)),
+                                          ctypes.byref(handle)), "zp_plan_create")
+        self.handle = handle
+        sizes = _lib.ZpSizes()
+        _lib.check(lib.zp_plan_sizes(handle, ctypes.byref(sizes)), "zp_plan_sizes")
+        self.sizes = sizes
+        self.lmax, self.mmax, self.c, self.h = lmax, mmax, c, h
+
+    @classmethod
+    def get(cls, lmax, mmax, c, h, device) -> "Plan":
+        device = torch.device(device)
+        if device.type != "cuda":
+            raise RuntimeError("zippel_b200 runs on CUDA devices only; there is no CPU path")
+        if device.index is None:
+            device = torch.device("cuda", torch.cuda.current_device())
+        key = (lmax, mmax, c, h, device.index)
+        if key not in cls._cache:
+            cls._cache[key] = cls(lmax, mmax, c, h, device)
+        return cls._cache[key]
+
+    def tables(self) -> dict[str, np.ndarray]:
+        km = self.sizes.Km
+        arrs = [np.zeros(km, np.int32) for _ in range(4)]
+        ptrs = [a.ctypes.data_as(ctypes.POINTER(ctypes.c_int32)) for a in arrs]
+        _lib.check(_lib.load().zp_plan_tables(self.handle, *ptrs), "zp_plan_tables")
+        return dict(zip(("row_l", "row_m", "rot_off", "gate_idx"), arrs))
+
+    def workspace(self, n: int, e: int, with_backward: bool) -> torch.Tensor:
+        nbytes = _lib.load().zp_workspace_bytes(self.handle, n, e, int(with_backward))
+        return torch.empty(max(nbytes, 16), dtype=torch.uint8, device=self.device)
+
+
+def _weights_struct(mmax, c1_w0, c1_b0, c1_wm, c2_w0, c2_b0, c2_wm):
+    arr_t = ctypes.c_void_p * max(mmax, 1)
+    a1 = arr_t(*[t.data_ptr() for t in c1_wm]) if mmax else arr_t(0)
+    a2 = arr_t(*[t.data_ptr() for t in c2_wm]) if mmax else arr_t(0)
+    w = _lib.ZpWeights(c1_w0.data_ptr(), c1_b0.data_ptr(), a1, c2_w0.data_ptr(), c2_b0.data_ptr(), a2)
+    return w, (a1, a2)
+
+
+def _f32(t: torch.Tensor) -> torch.Tensor:
+    return t.detach().to(torch.float32).contiguous()
+
+
+class EdgeConvFunction(torch.autograd.Function):
+    """node_out = edge_conv(x_node, edge_vec, cos_g, sin_g, radial, env; SO(2) weights).
+
+    Per-edge inputs are in the graph's destination-sorted order.  Differentiable w.r.t. x_node,
+    edge_vec (through the rotation), radial, env and the SO(2) weights; first order only.
+    """
+
+    @staticmethod
+    def forward(ctx, plan: Plan, graph: EdgeGraph, x_node, edge_vec, cos_g, sin_g, radial, env,
+                c1_w0, c1_b0, c2_w0, c2_b0, *wm):
+        lib = _lib.load()
+        mmax = plan.mmax
+        c1_wm, c2_wm = wm[:mmax], wm[mmax:]
+        n, e = graph.n_nodes, graph.n_edges
+        tens = [_f32(t) for t in (x_node, edge_vec, cos_g, sin_g, radial, env, c1_w0, c1_b0,
+                                  c2_w0, c2_b0, *wm)]
+        x, ev, cg, sg, rad, en, w10, b10, w20, b20 = tens[:10]
+        wms = tens[10:]
+        s = plan.sizes
+        assert x.shape == (n, s.K, plan.c), (x.shape, (n, s.K, plan.c))
+        assert rad.shape == (e, s.R) and ev.shape == (e, 3) and en.shape == (e,)
+        assert cg.shape == (e, plan.lmax + 1) and sg.shape == cg.shape
+        needs_bwd = any(ctx.needs_input_grad)
+        ws = plan.workspace(n, e, needs_bwd)
+        out = torch.empty(n, s.K, plan.c, dtype=torch.float32, device=x.device)
+        wstruct, keep = _weights_struct(mmax, w10, b10, wms[:mmax], w20, b20, wms[mmax:])
+        with torch.cuda.device(x.device):
+            st = torch.cuda.current_stream().cuda_stream
+            _lib.check(lib.zp_eso2_forward(
+                plan.handle, n, e, x.data_ptr(), ev.data_ptr(), cg.data_ptr(), sg.data_ptr(),
+                rad.data_ptr(), en.data_ptr(), graph.src.data_ptr(), graph.dst.data_ptr(),
+                graph.row_ptr.data_ptr(), ctypes.byref(wstruct), out.data_ptr(), ws.data_ptr(),
+                ws.numel(), st), "zp_eso2_forward")
+        del keep
+        if needs_bwd:
+            ctx.plan, ctx.graph, ctx.ws = plan, graph, ws
+            ctx.save_for_backward(*tens)
+            ctx.in_dtypes = [t.dtype for t in (x_node, edge_vec, cos_g, sin_g, radial, env, c1_w0,
+                                               c1_b0, c2_w0, c2_b0, *wm)]
+        return out.to(x_node.dtype)
+
+    @staticmethod
+    @torch.autograd.function.once_differentiable
+    def backward(ctx, grad_out):
+        lib = _lib.load()
+        plan, graph, ws = ctx.plan, ctx.graph, ctx.ws
+        tens = ctx.saved_tensors
+        x, ev, cg, sg, rad, en, w10, b10, w20, b20 = tens[:10]
+        wms = tens[10:]
+        mmax = plan.mmax
+        n, e = graph.n_nodes, graph.n_edges
+        g = _f32(grad_out)
+        gx, gev, grad, gen = (torch.empty_like(t) for t in (x, ev, rad, en))
+        gws = [torch.empty_like(t) for t in (w10, b10, w20, b20, *wms)]
+        wstruct, keep = _weights_struct(mmax, w10, b10, wms[:mmax], w20, b20, wms[mmax:])
+        gstruct, keep2 = _weights_struct(mmax, gws[0], gws[1], gws[4:4 + mmax], gws[2], gws[3],
+                                         gws[4 + mmax:])
+        with torch.cuda.device(x.device):
+            st = torch.cuda.current_stream().cuda_stream
+            _lib.check(lib.zp_eso2_backward(
+                plan.handle, n, e, g.data_ptr(), x.data_ptr(), ev.data_ptr(), cg.data_ptr(),
+                sg.data_ptr(), rad.data_ptr(), en.data_ptr(), graph.src.data_ptr(),
+                graph.dst.data_ptr(), graph.row_ptr.data_ptr(), graph.perm_src.data_ptr(),
+                graph.row_ptr_src.data_ptr(), ctypes.byref(wstruct), gx.data_ptr(),
+                gev.data_ptr(), grad.data_ptr(), gen.data_ptr(), ctypes.byref(gstruct),
+                ws.data_ptr(), ws.numel(), st), "zp_eso2_backward")
+        del keep, keep2
+        ctx.ws = None
+        grads = [gx, gev, None, None, grad, gen, *gws]
+        dts = ctx.in_dtypes
+        outs = []
+        for i, gr in enumerate(grads):
+            outs.append(None if gr is None or not ctx.needs_input_grad[i + 2] else gr.to(dts[i]))
+        return (None, None, *outs)
+
+
+def edge_conv(plan: Plan, graph: EdgeGraph, x_node, edge_vec, cos_g, sin_g, radial, env,
+              c1_m0: nn.Linear, c1_m, c2_m0: nn.Linear, c2_m) -> torch.Tensor:
+    return EdgeConvFunction.apply(plan, graph, x_node, edge_vec, cos_g, sin_g, radial, env,
+                                  c1_m0.weight, c1_m0.bias, c2_m0.weight, c2_m0.bias,
+                                  *[l.weight for l in c1_m], *[l.weight for l in c2_m])
+
+
+# --------------------------------------------------------------------------------------------
+# the module
+# --------------------------------------------------------------------------------------------
+
+
+class ESO2Block(nn.Module):
+    """One SO(2) interaction block + per-atom energy head, reference call signature."""
+
+    def __init__(self, cfg: BlockConfig = BlockConfig()):
+        super().__init__()
+        self.cfg = cfg
+        self.layout = Layout.make(cfg.lmax, cfg.mmax)
+        L, C, H = cfg.lmax, cfg.sphere_channels, cfg.hidden_channels
+        ms = self.layout.m_size
+
+        self.elem_emb = nn.Embedding(cfg.max_num_elements, cfg.edge_channels)
+        offset = torch.linspace(0.0, cfg.cutoff, cfg.num_distance_basis)     # fp32, as the reference
+        self.register_buffer("gauss_offset", offset, persistent=False)
+        self.gauss_coeff = -0.5 / (offset[1] - offset[0]).item() ** 2
+
+        self.edge_split = [k * 2 * C for k in ms]
+        self.num_channels_rad = sum(self.edge_split)
+        widths = [*cfg.edge_channels_list, self.num_channels_rad]
+        layers: list[nn.Module] = []
+        for i in range(1, len(widths)):
+            layers.append(nn.Linear(widths[i - 1], widths[i]))
+            if i < len(widths) - 1:
+                layers += [nn.LayerNorm(widths[i]), nn.SiLU()]
+        self.rad_func = nn.Sequential(*layers)
+
+        self.extra_m0 = L * H
+        self.c1_m0 = nn.Linear(ms[0] * 2 * C, H * (L + 1) + self.extra_m0)
+        self.c1_m = nn.ModuleList(nn.Linear(ms[m] * 2 * C, 2 * H * ms[m], bias=False)
+                                  for m in range(1, cfg.mmax + 1))
+        self.c2_m0 = nn.Linear(ms[0] * H, C * (L + 1))
+        self.c2_m = nn.ModuleList(nn.Linear(ms[m] * H, 2 * C * ms[m], bias=False)
+                                  for m in range(1, cfg.mmax + 1))
+        with torch.no_grad():
+            for lin in (*self.c1_m, *self.c2_m):
+                lin.weight.mul_(1.0 / math.sqrt(2.0))
+        self.readout = nn.Sequential(nn.Linear(C * (L + 1), C), nn.SiLU(), nn.Linear(C, 1))
+        p = float(cfg.envelope_exponent)
+        self.env_p, self.env_a = p, -(p + 1) * (p + 2) / 2
+        self.env_b, self.env_c = p * (p + 2), -p * (p + 1) / 2
+
+    # -- small torch pieces ---------------------------------------------------------------
+    def envelope(self, d_scaled: torch.Tensor) -> torch.Tensor:
+        val = 1 + d_scaled ** self.env_p * (self.env_a + d_scaled * (self.env_b + self.env_c * d_scaled))
+        return torch.where(d_scaled < 1, val, torch.zeros_like(val))
+
+    def gaussian_basis(self, dist: torch.Tensor) -> torch.Tensor:
+        d = dist.unsqueeze(1) - self.gauss_offset.to(dist.dtype).unsqueeze(0)
+        return torch.exp(self.gauss_coeff * d * d)
+
+    def node_invariants(self, node_out: torch.Tensor) -> torch.Tensor:
+        feats = [node_out[:, 0, :]]
+        for l in range(1, self.cfg.lmax + 1):
+            feats.append(node_out[:, l * l:(l + 1) ** 2, :].pow(2).sum(dim=1))
+        return torch.cat(feats, dim=-1)
+
+    def plan(self, device) -> Plan:
+        c = self.cfg
+        return Plan.get(c.lmax, c.mmax, c.sphere_channels, c.hidden_channels, device)
+
+    # -- forward --------------------------------------------------------------------------
+    def node_output(self, pos, atomic_numbers, x_node, edge_index, shifts, cos_gamma_k,
+                    sin_gamma_k, graph: EdgeGraph | None = None) -> torch.Tensor:
+        """pos -> node_out [N, K, C] (what the reference scatters at eso2_ref.py:346-349)."""
+        cfg = self.cfg
+        if graph is None:
+            graph = EdgeGraph.build(edge_index, pos.shape[0])
+        perm = graph.perm64
+        src, dst = graph.src.long(), graph.dst.long()
+        edge_vec = pos[dst] - pos[src] + shifts[perm]
+        dist = edge_vec.pow(2).sum(-1).clamp_min(1e-24).sqrt()
+        x_edge = torch.cat([self.gaussian_basis(dist), self.elem_emb(atomic_numbers[src]),
+                            self.elem_emb(atomic_numbers[dst])], dim=-1)
+        radial = self.rad_func(x_edge)
+        env = self.envelope(dist / cfg.cutoff)
+        return edge_conv(self.plan(pos.device), graph, x_node, edge_vec, cos_gamma_k[perm],
+                         sin_gamma_k[perm], radial, env, self.c1_m0, self.c1_m, self.c2_m0,
+                         self.c2_m)
+
+    def forward(self, pos, atomic_numbers, x_node, edge_index, shifts, cos_gamma_k, sin_gamma_k,
+                jd=None, graph: EdgeGraph | None = None) -> torch.Tensor:
+        """Scalar E.  ``jd`` is accepted for signature compatibility; the kernels use the J
+        matrices shipped with the package."""
+        node_out = self.node_output(pos, atomic_numbers, x_node, edge_index, shifts,
+                                    cos_gamma_k, sin_gamma_k, graph)
+        return self.readout(self.node_invariants(node_out)).sum()

@@ -1,0 +1,354 @@
+// C ABI of zippel_b200: plan/tables, workspace carving, and the forward / backward drivers
+// that sequence the kernels on the caller's stream.
+#include <cstdio>
+#include <cstring>
+#include <new>
+
+#include "zp_common.cuh"
+
+namespace {
+
+thread_local char g_cuda_error[512] = "";
+
+bool aligned16(const void *p) { return (reinterpret_cast<uintptr_t>(p) & 15u) == 0; }
+
+// Workspace carving; every region starts 256-byte aligned.
+struct Workspace {
+  float *rot, *a1, *h1, *ht, *y, *wfold;
+  float *dy, *dht, *dh1, *da1, *du_src, *grot, *wgrad, *scratch;
+  size_t scratch_elems;
+  size_t bytes;
+};
+
+int wgrad_splits(int64_t E) {
+  int64_t s = E / 2048;
+  if (s < 1) s = 1;
+  if (s > 32) s = 32;
+  return (int)s;
+}
+
+Workspace carve(const zp_plan *p, int64_t N, int64_t E, int with_backward, void *base) {
+  (void)N;
+  const ZpTables &t = p->t;
+  Workspace w;
+  std::memset(&w, 0, sizeof(w));
+  size_t off = 0;
+  auto take = [&](size_t elems) {
+    float *ptr = base ? reinterpret_cast<float *>(static_cast<char *>(base) + off) : nullptr;
+    off += zp_align_up(elems * sizeof(float), 256);
+    return ptr;
+  };
+  const size_t e = (size_t)E;
+  w.rot = take(e * t.nnz_pad);
+  w.a1 = take(e * t.Km * 2 * t.C);
+  w.h1 = take(e * t.w1_cols);
+  w.ht = take(e * t.Km * t.H);
+  w.y = take(e * t.Km * t.C);
+  w.wfold = take((size_t)p->w_elems);
+  if (with_backward) {
+    w.dy = take(e * t.Km * t.C);
+    w.dht = take(e * t.Km * t.H);
+    w.dh1 = take(e * t.w1_cols);
+    w.da1 = take(e * t.Km * 2 * t.C);
+    w.du_src = take(e * t.K * t.C);
+    w.grot = take(e * t.nnz_pad);
+    w.wgrad = take((size_t)p->w_elems);
+    size_t max_block = 0;
+    for (int m = 0; m < p->n_blocks; ++m) {
+      max_block = max_block > (size_t)p->c1_out[m] * p->c1_in[m] ? max_block
+                                                                 : (size_t)p->c1_out[m] * p->c1_in[m];
+      max_block = max_block > (size_t)p->c2_out[m] * p->c2_in[m] ? max_block
+                                                                 : (size_t)p->c2_out[m] * p->c2_in[m];
+    }
+    const size_t colsum = (size_t)zp_ceil_div(E > 0 ? E : 1, 256) * (size_t)t.w1_cols;
+    const size_t gemm = (size_t)wgrad_splits(E) * max_block;
+    w.scratch_elems = colsum > gemm ? colsum : gemm;
+    w.scratch = take(w.scratch_elems);
+  }
+  w.bytes = off;
+  return w;
+}
+
+}  // namespace
+
+void zp_set_cuda_error(cudaError_t e, const char *where) {
+  std::snprintf(g_cuda_error, sizeof(g_cuda_error), "%s: %s (%s)", where, cudaGetErrorName(e),
+                cudaGetErrorString(e));
+}
+
+extern "C" {
+
+const char *zp_status_string(int status) {
+  switch (status) {
+    case ZP_OK: return "ok";
+    case ZP_ERR_INVALID_ARG: return "invalid argument";
+    case ZP_ERR_UNSUPPORTED: return "unsupported configuration";
+    case ZP_ERR_WORKSPACE: return "workspace too small";
+    case ZP_ERR_CUDA: return "CUDA runtime error";
+    case ZP_ERR_DEVICE_TIMEOUT: return "device-side wait timed out";
+    case ZP_ERR_NO_DEVICE_CODE: return "no device code for this GPU (library is built for sm_100a)";
+    default: return "unknown status";
+  }
+}
+
+const char *zp_last_cuda_error(void) { return g_cuda_error; }
+
+int zp_device_supported(void) {
+  int dev = 0, major = 0;
+  if (cudaGetDevice(&dev) != cudaSuccess) return 0;
+  if (cudaDeviceGetAttribute(&major, cudaDevAttrComputeCapabilityMajor, dev) != cudaSuccess)
+    return 0;
+  return major == 10;
+}
+
+int zp_plan_create(const zp_config *cfg, const double *jd_host, zp_plan **plan_out) {
+  if (!cfg || !jd_host || !plan_out) return ZP_ERR_INVALID_ARG;
+  const int L = cfg->lmax, MM = cfg->mmax, C = cfg->sphere_channels, H = cfg->hidden_channels;
+  if (L < 0 || L > ZP_MAX_L || MM < 0 || MM > L) return ZP_ERR_UNSUPPORTED;
+  if (C <= 0 || H <= 0 || C % 4 || H % 4 || C > 512) return ZP_ERR_UNSUPPORTED;
+  if (cfg->precision != 0) return ZP_ERR_UNSUPPORTED;
+  if (!zp_device_supported()) return ZP_ERR_NO_DEVICE_CODE;
+
+  zp_plan *p = new (std::nothrow) zp_plan;
+  if (!p) return ZP_ERR_INVALID_ARG;
+  std::memset(p, 0, sizeof(*p));
+  p->cfg = *cfg;
+  ZpTables &t = p->t;
+  t.lmax = L; t.mmax = MM; t.C = C; t.H = H;
+  t.K = (L + 1) * (L + 1);
+  std::memset(t.row_of, -1, sizeof(t.row_of));
+  int r = 0, off = 0, rad = 0, jo = 0;
+  for (int m = 0; m <= MM; ++m) {
+    t.m_row0[m] = (int16_t)r;
+    t.rad_off[m] = rad;
+    const int km = L + 1 - m;
+    rad += km * 2 * C;
+    for (int sgn = 1; sgn >= (m == 0 ? 1 : -1); sgn -= 2) {
+      for (int l = m; l <= L; ++l) {
+        t.row_l[r] = (int8_t)l;
+        t.row_m[r] = (int8_t)(sgn * m);
+        t.rot_off[r] = (int16_t)off;
+        t.row_of[l][l + sgn * m] = (int8_t)r;
+        off += 2 * l + 1;
+        ++r;
+      }
+    }
+    t.m_rows[m] = (int16_t)(r - t.m_row0[m]);
+  }
+  t.Km = r;
+  t.nnz = off;
+  t.nnz_pad = (off + 3) / 4 * 4;
+  t.R = rad;
+  t.n_gate = L * H;
+  t.w1_cols = t.n_gate + t.Km * H;
+  for (int l = 0; l <= L; ++l) {
+    t.jd_off[l] = (int16_t)jo;
+    jo += (2 * l + 1) * (2 * l + 1);
+  }
+
+  p->n_blocks = MM + 1;
+  int64_t woff = 0;
+  for (int conv = 0; conv < 2; ++conv) {
+    for (int m = 0; m <= MM; ++m) {
+      const int km = L + 1 - m;
+      const int cin = conv ? H : 2 * C, cout = conv ? C : H;
+      const int in = (m == 0 ? 1 : 2) * km * cin;
+      const int out = (m == 0 ? 1 : 2) * km * cout + ((m == 0 && conv == 0) ? t.n_gate : 0);
+      (conv ? p->c2_in : p->c1_in)[m] = in;
+      (conv ? p->c2_out : p->c1_out)[m] = out;
+      (conv ? p->c2_woff : p->c1_woff)[m] = woff;
+      woff += (int64_t)zp_align_up((size_t)in * out, 64);
+    }
+  }
+  p->w_elems = woff;
+
+  if (cudaGetDevice(&p->device) != cudaSuccess ||
+      cudaMalloc(&p->jd_dev, sizeof(double) * jo) != cudaSuccess ||
+      cudaMemcpy(p->jd_dev, jd_host, sizeof(double) * jo, cudaMemcpyHostToDevice) !=
+          cudaSuccess) {
+    zp_set_cuda_error(cudaGetLastError(), "zp_plan_create");
+    delete p;
+    return ZP_ERR_CUDA;
+  }
+  *plan_out = p;
+  return ZP_OK;
+}
+
+int zp_plan_destroy(zp_plan *plan) {
+  if (!plan) return ZP_OK;
+  if (plan->jd_dev) cudaFree(plan->jd_dev);
+  delete plan;
+  return ZP_OK;
+}
+
+int zp_plan_sizes(const zp_plan *plan, zp_sizes *out) {
+  if (!plan || !out) return ZP_ERR_INVALID_ARG;
+  const ZpTables &t = plan->t;
+  out->K = t.K; out->Km = t.Km; out->nnz = t.nnz; out->nnz_pad = t.nnz_pad;
+  out->R = t.R; out->n_gate = t.n_gate; out->w1_cols = t.w1_cols;
+  return ZP_OK;
+}
+
+int zp_plan_tables(const zp_plan *plan, int32_t *row_l, int32_t *row_m, int32_t *rot_off,
+                   int32_t *gate_idx) {
+  if (!plan) return ZP_ERR_INVALID_ARG;
+  const ZpTables &t = plan->t;
+  for (int r = 0; r < t.Km; ++r) {
+    if (row_l) row_l[r] = t.row_l[r];
+    if (row_m) row_m[r] = t.row_m[r];
+    if (rot_off) rot_off[r] = t.rot_off[r];
+    if (gate_idx) gate_idx[r] = r == 0 ? -1 : t.row_l[r] - 1;
+  }
+  return ZP_OK;
+}
+
+int zp_wigner_forward(const zp_plan *plan, int64_t n_edges, const float *edge_vec,
+                      const float *cos_g, const float *sin_g, float *rot, void *stream) {
+  if (!plan || n_edges < 0) return ZP_ERR_INVALID_ARG;
+  if (n_edges && (!edge_vec || !cos_g || !sin_g || !rot)) return ZP_ERR_INVALID_ARG;
+  return zp_launch_wigner_fwd(plan, n_edges, edge_vec, cos_g, sin_g, rot, (cudaStream_t)stream);
+}
+
+int zp_wigner_backward(const zp_plan *plan, int64_t n_edges, const float *edge_vec,
+                       const float *cos_g, const float *sin_g, const float *grad_rot,
+                       float *grad_edge_vec, void *stream) {
+  if (!plan || n_edges < 0) return ZP_ERR_INVALID_ARG;
+  if (n_edges && (!edge_vec || !cos_g || !sin_g || !grad_rot || !grad_edge_vec))
+    return ZP_ERR_INVALID_ARG;
+  return zp_launch_wigner_bwd(plan, n_edges, edge_vec, cos_g, sin_g, grad_rot, grad_edge_vec,
+                              (cudaStream_t)stream);
+}
+
+size_t zp_workspace_bytes(const zp_plan *plan, int64_t n_nodes, int64_t n_edges,
+                          int with_backward) {
+  if (!plan || n_nodes < 0 || n_edges < 0) return 0;
+  return carve(plan, n_nodes, n_edges, with_backward, nullptr).bytes;
+}
+
+static int check_weights(const zp_plan *p, const zp_weights *w) {
+  if (!w || !w->c1_w0 || !w->c1_b0 || !w->c2_w0 || !w->c2_b0) return ZP_ERR_INVALID_ARG;
+  if (p->n_blocks > 1 && (!w->c1_wm || !w->c2_wm)) return ZP_ERR_INVALID_ARG;
+  for (int m = 1; m < p->n_blocks; ++m)
+    if (!w->c1_wm[m - 1] || !w->c2_wm[m - 1]) return ZP_ERR_INVALID_ARG;
+  return ZP_OK;
+}
+
+int zp_eso2_forward(const zp_plan *plan, int64_t N, int64_t E, const float *x_node,
+                    const float *edge_vec, const float *cos_g, const float *sin_g,
+                    const float *radial, const float *env, const int32_t *src,
+                    const int32_t *dst, const int32_t *row_ptr, const zp_weights *w,
+                    float *node_out, void *workspace, size_t workspace_bytes, void *stream) {
+  if (!plan || N < 0 || E < 0) return ZP_ERR_INVALID_ARG;
+  if (N == 0) return E == 0 ? ZP_OK : ZP_ERR_INVALID_ARG;
+  if (!x_node || !row_ptr || !node_out || !workspace) return ZP_ERR_INVALID_ARG;
+  if (E && (!edge_vec || !cos_g || !sin_g || !radial || !env || !src || !dst))
+    return ZP_ERR_INVALID_ARG;
+  if (!aligned16(x_node) || !aligned16(node_out) || !aligned16(radial) || !aligned16(workspace))
+    return ZP_ERR_INVALID_ARG;
+  int rc = check_weights(plan, w);
+  if (rc) return rc;
+  const Workspace ws = carve(plan, N, E, 0, workspace);
+  if (workspace_bytes < ws.bytes) return ZP_ERR_WORKSPACE;
+  cudaStream_t st = (cudaStream_t)stream;
+  const ZpTables &t = plan->t;
+
+  if ((rc = zp_launch_fold_weights(plan, w, ws.wfold, st))) return rc;
+  if ((rc = zp_launch_wigner_fwd(plan, E, edge_vec, cos_g, sin_g, ws.rot, st))) return rc;
+  if ((rc = zp_launch_rotate_in(plan, E, x_node, src, dst, ws.rot, radial, ws.a1, st))) return rc;
+  const int64_t lda = (int64_t)t.Km * 2 * t.C, ldh = (int64_t)t.Km * t.H, ldy = (int64_t)t.Km * t.C;
+  for (int m = 0; m < plan->n_blocks; ++m) {
+    const int in = plan->c1_in[m], out = plan->c1_out[m];
+    const float *A = ws.a1 + (size_t)t.m_row0[m] * 2 * t.C;
+    float *Cc = ws.h1 + (m == 0 ? 0 : t.n_gate + (size_t)t.m_row0[m] * t.H);
+    if ((rc = zp_launch_gemm(E, out, in, A, lda, 1, ws.wfold + plan->c1_woff[m], 1, in,
+                             m == 0 ? w->c1_b0 : nullptr, Cc, t.w1_cols, 1, nullptr, st)))
+      return rc;
+  }
+  if ((rc = zp_launch_gate_fwd(plan, E, ws.h1, ws.ht, st))) return rc;
+  for (int m = 0; m < plan->n_blocks; ++m) {
+    const int in = plan->c2_in[m], out = plan->c2_out[m];
+    const float *A = ws.ht + (size_t)t.m_row0[m] * t.H;
+    float *Cc = ws.y + (size_t)t.m_row0[m] * t.C;
+    if ((rc = zp_launch_gemm(E, out, in, A, ldh, 1, ws.wfold + plan->c2_woff[m], 1, in,
+                             m == 0 ? w->c2_b0 : nullptr, Cc, ldy, 1, nullptr, st)))
+      return rc;
+  }
+  return zp_launch_rotate_back_scatter(plan, N, ws.y, env, ws.rot, row_ptr, node_out, st);
+}
+
+int zp_eso2_backward(const zp_plan *plan, int64_t N, int64_t E, const float *grad_node_out,
+                     const float *x_node, const float *edge_vec, const float *cos_g,
+                     const float *sin_g, const float *radial, const float *env,
+                     const int32_t *src, const int32_t *dst, const int32_t *row_ptr,
+                     const int32_t *perm_src, const int32_t *row_ptr_src, const zp_weights *w,
+                     float *grad_x_node, float *grad_edge_vec, float *grad_radial,
+                     float *grad_env, const zp_weight_grads *gw, void *workspace,
+                     size_t workspace_bytes, void *stream) {
+  (void)dst;
+  if (!plan || N < 0 || E < 0) return ZP_ERR_INVALID_ARG;
+  if (N == 0) return E == 0 ? ZP_OK : ZP_ERR_INVALID_ARG;
+  if (!grad_node_out || !x_node || !row_ptr || !row_ptr_src || !grad_x_node || !workspace || !gw)
+    return ZP_ERR_INVALID_ARG;
+  if (E && (!edge_vec || !cos_g || !sin_g || !radial || !env || !src || !perm_src ||
+            !grad_edge_vec || !grad_radial || !grad_env))
+    return ZP_ERR_INVALID_ARG;
+  if (!gw->c1_w0 || !gw->c1_b0 || !gw->c2_w0 || !gw->c2_b0) return ZP_ERR_INVALID_ARG;
+  for (int m = 1; m < plan->n_blocks; ++m)
+    if (!gw->c1_wm || !gw->c2_wm || !gw->c1_wm[m - 1] || !gw->c2_wm[m - 1])
+      return ZP_ERR_INVALID_ARG;
+  if (!aligned16(grad_node_out) || !aligned16(grad_x_node) || !aligned16(grad_radial) ||
+      !aligned16(workspace))
+    return ZP_ERR_INVALID_ARG;
+  int rc = check_weights(plan, w);
+  if (rc) return rc;
+  const Workspace ws = carve(plan, N, E, 1, workspace);
+  if (workspace_bytes < ws.bytes) return ZP_ERR_WORKSPACE;
+  cudaStream_t st = (cudaStream_t)stream;
+  const ZpTables &t = plan->t;
+  const int64_t lda = (int64_t)t.Km * 2 * t.C, ldh = (int64_t)t.Km * t.H, ldy = (int64_t)t.Km * t.C;
+  const int splits = wgrad_splits(E);
+
+  if ((rc = zp_launch_rotate_grad_out(plan, N, grad_node_out, ws.y, env, ws.rot, row_ptr, ws.dy,
+                                      grad_env, ws.grot, st)))
+    return rc;
+  // conv2: input gradient, weight gradient (reduced over edges), bias gradient
+  for (int m = 0; m < plan->n_blocks; ++m) {
+    const int in = plan->c2_in[m], out = plan->c2_out[m];
+    const float *dYm = ws.dy + (size_t)t.m_row0[m] * t.C;
+    const float *Xm = ws.ht + (size_t)t.m_row0[m] * t.H;
+    float *dXm = ws.dht + (size_t)t.m_row0[m] * t.H;
+    const float *Wm = ws.wfold + plan->c2_woff[m];
+    if ((rc = zp_launch_gemm(E, in, out, dYm, ldy, 1, Wm, in, 1, nullptr, dXm, ldh, 1, nullptr, st)))
+      return rc;
+    if ((rc = zp_launch_gemm(out, in, E, dYm, 1, ldy, Xm, ldh, 1, nullptr,
+                             ws.wgrad + plan->c2_woff[m], in, splits, ws.scratch, st)))
+      return rc;
+  }
+  if ((rc = zp_launch_colsum(E, plan->c2_out[0], ws.dy, ldy, gw->c2_b0, ws.scratch, st))) return rc;
+  if ((rc = zp_launch_gate_bwd(plan, E, ws.h1, ws.dht, ws.dh1, st))) return rc;
+  for (int m = 0; m < plan->n_blocks; ++m) {
+    const int in = plan->c1_in[m], out = plan->c1_out[m];
+    const float *dYm = ws.dh1 + (m == 0 ? 0 : t.n_gate + (size_t)t.m_row0[m] * t.H);
+    const float *Xm = ws.a1 + (size_t)t.m_row0[m] * 2 * t.C;
+    float *dXm = ws.da1 + (size_t)t.m_row0[m] * 2 * t.C;
+    const float *Wm = ws.wfold + plan->c1_woff[m];
+    if ((rc = zp_launch_gemm(E, in, out, dYm, t.w1_cols, 1, Wm, in, 1, nullptr, dXm, lda, 1,
+                             nullptr, st)))
+      return rc;
+    if ((rc = zp_launch_gemm(out, in, E, dYm, 1, t.w1_cols, Xm, lda, 1, nullptr,
+                             ws.wgrad + plan->c1_woff[m], in, splits, ws.scratch, st)))
+      return rc;
+  }
+  if ((rc = zp_launch_colsum(E, plan->c1_out[0], ws.dh1, t.w1_cols, gw->c1_b0, ws.scratch, st)))
+    return rc;
+  if ((rc = zp_launch_rotate_in_bwd(plan, N, ws.da1, radial, x_node, src, ws.rot, row_ptr,
+                                    grad_radial, ws.du_src, grad_x_node, ws.grot, st)))
+    return rc;
+  if ((rc = zp_launch_src_reduce(plan, N, ws.du_src, perm_src, row_ptr_src, grad_x_node, st)))
+    return rc;
+  if ((rc = zp_launch_wigner_bwd(plan, E, edge_vec, cos_g, sin_g, ws.grot, grad_edge_vec, st)))
+    return rc;
+  return zp_launch_unfold_wgrad(plan, ws.wgrad, gw, st);
+}
+
+}  // extern "C"

@@ -1,0 +1,119 @@
+// Shared declarations of the zippel_b200 kernels: layout tables, the plan, launch helpers.
+#pragma once
+
+#include <cuda_runtime.h>
+#include <stdint.h>
+
+#include "zippel_b200.h"
+
+#define ZP_MAX_L 6                              // largest supported lmax
+#define ZP_MAX_KM ((ZP_MAX_L + 1) * (ZP_MAX_L + 1))
+#define ZP_MAX_N (2 * ZP_MAX_L + 1)
+
+// Index tables of one (lmax, mmax) layout, passed to kernels by value.
+//   m'-major rows: m = 0 for l = 0..lmax, then for |m| = 1..mmax the +m rows (l = m..lmax)
+//   followed by the -m rows.  Row r belongs to degree row_l[r]; its 2l+1 rotation entries sit
+//   at rot_off[r] in the packed per-edge rotation.
+struct ZpTables {
+  int lmax, mmax, K, Km, nnz, nnz_pad;
+  int C, H;
+  int n_gate;                                   // lmax * H
+  int w1_cols;                                  // n_gate + Km * H
+  int R;                                        // 2C * sum_m km
+  int8_t row_l[ZP_MAX_KM];
+  int8_t row_m[ZP_MAX_KM];                      // signed m
+  int16_t rot_off[ZP_MAX_KM];
+  int8_t row_of[ZP_MAX_L + 1][ZP_MAX_N];        // m' row of (l, i = m + l), or -1
+  int16_t m_row0[ZP_MAX_L + 1];                 // first m' row of m-block m
+  int16_t m_rows[ZP_MAX_L + 1];                 // rows in m-block m (km or 2 km)
+  int32_t rad_off[ZP_MAX_L + 1];                // first radial column of m-block m
+  int16_t jd_off[ZP_MAX_L + 1];                 // offset of J_l in the packed J array
+};
+
+struct zp_plan {
+  zp_config cfg;
+  ZpTables t;
+  int device;
+  double *jd_dev;                               // packed J_l, fp64
+  // per-m GEMM shapes of the folded SO(2) weights
+  int n_blocks;                                 // mmax + 1
+  int c1_in[ZP_MAX_L + 1], c1_out[ZP_MAX_L + 1], c2_in[ZP_MAX_L + 1], c2_out[ZP_MAX_L + 1];
+  int64_t c1_woff[ZP_MAX_L + 1], c2_woff[ZP_MAX_L + 1];   // element offsets in the packed buffer
+  int64_t w_elems;                              // total packed (folded) weight elements
+};
+
+// thread-local text of the last CUDA error
+void zp_set_cuda_error(cudaError_t e, const char *where);
+
+#define ZP_CUDA(call)                                   \
+  do {                                                  \
+    cudaError_t e_ = (call);                            \
+    if (e_ != cudaSuccess) {                            \
+      zp_set_cuda_error(e_, #call);                     \
+      return ZP_ERR_CUDA;                               \
+    }                                                   \
+  } while (0)
+
+#define ZP_LAUNCH_CHECK(name)                           \
+  do {                                                  \
+    cudaError_t e_ = cudaGetLastError();                \
+    if (e_ != cudaSuccess) {                            \
+      zp_set_cuda_error(e_, name);                      \
+      return ZP_ERR_CUDA;                               \
+    }                                                   \
+  } while (0)
+
+static inline int64_t zp_ceil_div(int64_t a, int64_t b) { return (a + b - 1) / b; }
+static inline size_t zp_align_up(size_t x, size_t a) { return (x + a - 1) / a * a; }
+
+#define ZP_DISPATCH_LMAX(lmax, CALL)          \
+  switch (lmax) {                             \
+    case 0: { CALL(0); break; }               \
+    case 1: { CALL(1); break; }               \
+    case 2: { CALL(2); break; }               \
+    case 3: { CALL(3); break; }               \
+    case 4: { CALL(4); break; }               \
+    case 5: { CALL(5); break; }               \
+    case 6: { CALL(6); break; }               \
+    default: return ZP_ERR_UNSUPPORTED;       \
+  }
+
+// ---- kernels (each in its own translation unit) --------------------------------------------
+int zp_launch_wigner_fwd(const zp_plan *p, int64_t E, const float *ev, const float *cg,
+                         const float *sg, float *rot, cudaStream_t st);
+int zp_launch_wigner_bwd(const zp_plan *p, int64_t E, const float *ev, const float *cg,
+                         const float *sg, const float *grot, float *gev, cudaStream_t st);
+
+int zp_launch_rotate_in(const zp_plan *p, int64_t E, const float *x, const int32_t *src,
+                        const int32_t *dst, const float *rot, const float *radial, float *a1,
+                        cudaStream_t st);
+int zp_launch_rotate_back_scatter(const zp_plan *p, int64_t N, const float *y, const float *env,
+                                  const float *rot, const int32_t *row_ptr, float *node_out,
+                                  cudaStream_t st);
+int zp_launch_rotate_grad_out(const zp_plan *p, int64_t N, const float *g, const float *y,
+                              const float *env, const float *rot, const int32_t *row_ptr,
+                              float *dy, float *grad_env, float *grad_rot, cudaStream_t st);
+int zp_launch_rotate_in_bwd(const zp_plan *p, int64_t N, const float *da1, const float *radial,
+                            const float *x, const int32_t *src, const float *rot,
+                            const int32_t *row_ptr, float *grad_radial, float *du_src,
+                            float *grad_x, float *grad_rot, cudaStream_t st);
+int zp_launch_src_reduce(const zp_plan *p, int64_t N, const float *du_src,
+                         const int32_t *perm_src, const int32_t *row_ptr_src, float *grad_x,
+                         cudaStream_t st);
+
+int zp_launch_gate_fwd(const zp_plan *p, int64_t E, const float *h1, float *ht, cudaStream_t st);
+int zp_launch_gate_bwd(const zp_plan *p, int64_t E, const float *h1, const float *dht, float *dh1,
+                       cudaStream_t st);
+
+// C[M,N] = A * B (+ bias[n]) with arbitrary element strides: A(m,k) = A[m*am + k*ak],
+// B(k,n) = B[k*bk + n*bn].  Exactly one of (am, ak) and one of (bk, bn) must be 1.
+// splits > 1 partitions K and sums the partials in a fixed order (scratch: splits*M*N floats).
+int zp_launch_gemm(int64_t M, int64_t N, int64_t K, const float *A, int64_t am, int64_t ak,
+                   const float *B, int64_t bk, int64_t bn, const float *bias, float *C,
+                   int64_t ldc, int splits, float *scratch, cudaStream_t st);
+
+int zp_launch_fold_weights(const zp_plan *p, const zp_weights *w, float *packed, cudaStream_t st);
+int zp_launch_unfold_wgrad(const zp_plan *p, const float *packed_grad, const zp_weight_grads *gw,
+                           cudaStream_t st);
+int zp_launch_colsum(int64_t rows, int64_t cols, const float *a, int64_t lda, float *out,
+                     float *scratch, cudaStream_t st);

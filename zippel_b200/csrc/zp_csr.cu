@@ -1,0 +1,191 @@
+// Destination-sorted edge order, CSR offsets and the source-sorted view, built on the device.
+//
+// The required order is the total order (dst, src, original position); the source view orders
+// sorted-edge ids by (src, sorted id).  Both are total orders without ties, so any algorithm
+// gives the same arrays bit for bit: bucket the edges by node with atomics (arbitrary order
+// inside a bucket), then rank every element inside its bucket by counting the keys below it.
+// Buckets are the in-/out-neighbourhoods (tens of edges), so the quadratic rank is cheap.
+#include "zp_common.cuh"
+
+namespace {
+
+constexpr int kScanBlock = 1024;
+
+__global__ void count_kernel(int64_t E, const int64_t *__restrict__ key, int32_t *counts) {
+  const int64_t i = (int64_t)blockIdx.x * blockDim.x + threadIdx.x;
+  if (i < E) atomicAdd(&counts[key[i]], 1);
+}
+__global__ void count32_kernel(int64_t E, const int32_t *__restrict__ key, int32_t *counts) {
+  const int64_t i = (int64_t)blockIdx.x * blockDim.x + threadIdx.x;
+  if (i < E) atomicAdd(&counts[key[i]], 1);
+}
+
+// exclusive scan of n ints in three steps: per-block scan, scan of block totals, add back
+__global__ void scan_block_kernel(int64_t n, const int32_t *__restrict__ in, int32_t *out,
+                                  int32_t *block_sums) {
+  __shared__ int32_t s[kScanBlock];
+  const int64_t i = (int64_t)blockIdx.x * kScanBlock + threadIdx.x;
+  s[threadIdx.x] = i < n ? in[i] : 0;
+  __syncthreads();
+  for (int off = 1; off < kScanBlock; off <<= 1) {
+    const int32_t v = threadIdx.x >= off ? s[threadIdx.x - off] : 0;
+    __syncthreads();
+    s[threadIdx.x] += v;
+    __syncthreads();
+  }
+  if (i < n) out[i] = s[threadIdx.x] - in[i];          // exclusive
+  if (threadIdx.x == kScanBlock - 1) block_sums[blockIdx.x] = s[threadIdx.x];
+}
+__global__ void scan_sums_kernel(int64_t nb, int32_t *block_sums) {
+  if (threadIdx.x == 0 && blockIdx.x == 0) {
+    int32_t run = 0;
+    for (int64_t b = 0; b < nb; ++b) {
+      const int32_t v = block_sums[b];
+      block_sums[b] = run;
+      run += v;
+    }
+  }
+}
+__global__ void scan_add_kernel(int64_t n, int32_t *out, const int32_t *__restrict__ block_sums,
+                                int32_t total_slot_value_is_E) {
+  const int64_t i = (int64_t)blockIdx.x * kScanBlock + threadIdx.x;
+  if (i < n) out[i] += block_sums[blockIdx.x];
+  if (i == n) out[n] = total_slot_value_is_E;
+}
+
+__global__ void bucket_kernel(int64_t E, const int64_t *__restrict__ key,
+                              const int32_t *__restrict__ row_ptr, int32_t *cursor,
+                              int32_t *tmp) {
+  const int64_t i = (int64_t)blockIdx.x * blockDim.x + threadIdx.x;
+  if (i >= E) return;
+  const int64_t k = key[i];
+  tmp[row_ptr[k] + atomicAdd(&cursor[k], 1)] = (int32_t)i;
+}
+__global__ void bucket32_kernel(int64_t E, const int32_t *__restrict__ key,
+                                const int32_t *__restrict__ row_ptr, int32_t *cursor,
+                                int32_t *tmp) {
+  const int64_t i = (int64_t)blockIdx.x * blockDim.x + threadIdx.x;
+  if (i >= E) return;
+  const int32_t k = key[i];
+  tmp[row_ptr[k] + atomicAdd(&cursor[k], 1)] = (int32_t)i;
+}
+
+// One warp per destination node: order its edges by (src, original position).
+__global__ void rank_dst_kernel(int64_t N, const int64_t *__restrict__ src64,
+                                const int32_t *__restrict__ row_ptr,
+                                const int32_t *__restrict__ tmp, int32_t *perm,
+                                int32_t *src_sorted, int32_t *dst_sorted) {
+  const int64_t n = ((int64_t)blockIdx.x * blockDim.x + threadIdx.x) / 32;
+  const int lane = threadIdx.x % 32;
+  if (n >= N) return;
+  const int beg = row_ptr[n], end = row_ptr[n + 1];
+  for (int i = beg + lane; i < end; i += 32) {
+    const int32_t id = tmp[i];
+    const int64_t s = src64[id];
+    int rank = 0;
+    for (int j = beg; j < end; ++j) {
+      const int32_t jd = tmp[j];
+      const int64_t sj = src64[jd];
+      rank += (sj < s) || (sj == s && jd < id);
+    }
+    perm[beg + rank] = id;
+    src_sorted[beg + rank] = (int32_t)s;
+    dst_sorted[beg + rank] = (int32_t)n;
+  }
+}
+
+// One warp per source node: order the sorted-edge ids of its outgoing edges increasingly.
+__global__ void rank_src_kernel(int64_t N, const int32_t *__restrict__ row_ptr_src,
+                                const int32_t *__restrict__ tmp, int32_t *perm_src) {
+  const int64_t n = ((int64_t)blockIdx.x * blockDim.x + threadIdx.x) / 32;
+  const int lane = threadIdx.x % 32;
+  if (n >= N) return;
+  const int beg = row_ptr_src[n], end = row_ptr_src[n + 1];
+  for (int i = beg + lane; i < end; i += 32) {
+    const int32_t id = tmp[i];
+    int rank = 0;
+    for (int j = beg; j < end; ++j) rank += tmp[j] < id;
+    perm_src[beg + rank] = id;
+  }
+}
+
+struct CsrWork {
+  int32_t *counts, *cursor, *tmp, *block_sums;
+  size_t bytes;
+};
+
+CsrWork carve_csr(int64_t E, int64_t N, void *base) {
+  CsrWork w;
+  size_t off = 0;
+  auto take = [&](size_t n) {
+    int32_t *p = base ? reinterpret_cast<int32_t *>(static_cast<char *>(base) + off) : nullptr;
+    off += zp_align_up(n * sizeof(int32_t), 256);
+    return p;
+  };
+  w.counts = take((size_t)N + 1);
+  w.cursor = take((size_t)N + 1);
+  w.tmp = take((size_t)(E > 0 ? E : 1));
+  w.block_sums = take((size_t)zp_ceil_div(N + 1, kScanBlock) + 1);
+  w.bytes = off;
+  return w;
+}
+
+int exclusive_scan(int64_t n, const int32_t *in, int32_t *out, int32_t *block_sums, int64_t E,
+                   cudaStream_t st) {
+  const int64_t nb = zp_ceil_div(n + 1, kScanBlock);
+  scan_block_kernel<<<(unsigned)nb, kScanBlock, 0, st>>>(n, in, out, block_sums);
+  scan_sums_kernel<<<1, 32, 0, st>>>(nb, block_sums);
+  scan_add_kernel<<<(unsigned)nb, kScanBlock, 0, st>>>(n, out, block_sums, (int32_t)E);
+  ZP_LAUNCH_CHECK("exclusive_scan");
+  return ZP_OK;
+}
+
+}  // namespace
+
+extern "C" {
+
+size_t zp_csr_work_bytes(int64_t n_edges, int64_t n_nodes) {
+  if (n_edges < 0 || n_nodes < 0) return 0;
+  return carve_csr(n_edges, n_nodes, nullptr).bytes;
+}
+
+int zp_csr_build(const int64_t *edge_index, int64_t E, int64_t N, int32_t *perm,
+                 int32_t *src_sorted, int32_t *dst_sorted, int32_t *row_ptr, int32_t *perm_src,
+                 int32_t *row_ptr_src, void *work, size_t work_bytes, void *stream) {
+  if (E < 0 || N < 0 || E > INT32_MAX || N >= INT32_MAX) return ZP_ERR_INVALID_ARG;
+  if (!row_ptr || !row_ptr_src || !work) return ZP_ERR_INVALID_ARG;
+  if (E && (!edge_index || !perm || !src_sorted || !dst_sorted || !perm_src))
+    return ZP_ERR_INVALID_ARG;
+  const CsrWork w = carve_csr(E, N, work);
+  if (work_bytes < w.bytes) return ZP_ERR_WORKSPACE;
+  cudaStream_t st = (cudaStream_t)stream;
+  const int64_t *src64 = edge_index, *dst64 = edge_index + E;
+  const unsigned eb = (unsigned)zp_ceil_div(E > 0 ? E : 1, 256);
+  const unsigned nbw = (unsigned)zp_ceil_div((N > 0 ? N : 1) * 32, 256);
+  int rc;
+
+  // destination view
+  ZP_CUDA(cudaMemsetAsync(w.counts, 0, sizeof(int32_t) * (N + 1), st));
+  ZP_CUDA(cudaMemsetAsync(w.cursor, 0, sizeof(int32_t) * (N + 1), st));
+  if (E) count_kernel<<<eb, 256, 0, st>>>(E, dst64, w.counts);
+  if ((rc = exclusive_scan(N, w.counts, row_ptr, w.block_sums, E, st))) return rc;
+  if (E) {
+    bucket_kernel<<<eb, 256, 0, st>>>(E, dst64, row_ptr, w.cursor, w.tmp);
+    rank_dst_kernel<<<nbw, 256, 0, st>>>(N, src64, row_ptr, w.tmp, perm, src_sorted, dst_sorted);
+  }
+  ZP_LAUNCH_CHECK("csr destination view");
+
+  // source view over sorted-edge ids
+  ZP_CUDA(cudaMemsetAsync(w.counts, 0, sizeof(int32_t) * (N + 1), st));
+  ZP_CUDA(cudaMemsetAsync(w.cursor, 0, sizeof(int32_t) * (N + 1), st));
+  if (E) count32_kernel<<<eb, 256, 0, st>>>(E, src_sorted, w.counts);
+  if ((rc = exclusive_scan(N, w.counts, row_ptr_src, w.block_sums, E, st))) return rc;
+  if (E) {
+    bucket32_kernel<<<eb, 256, 0, st>>>(E, src_sorted, row_ptr_src, w.cursor, w.tmp);
+    rank_src_kernel<<<nbw, 256, 0, st>>>(N, row_ptr_src, w.tmp, perm_src);
+  }
+  ZP_LAUNCH_CHECK("csr source view");
+  return ZP_OK;
+}
+
+}  // extern "C"

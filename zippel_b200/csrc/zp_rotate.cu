@@ -1,0 +1,592 @@
+// Gather / rotate / scatter kernels around the SO(2) contraction.
+//
+//   rotate_in            a[e, r, c2] = radial[e, .] * sum_j rot[e, r, j] * [x_src ; x_dst][l_r^2 + j, c2]
+//   rotate_back_scatter  node_out[n, l^2 + j, c] = sum_{e -> n} env_e * sum_r rot[e, r, j] * y[e, r, c]
+//   rotate_grad_out      the VJP of rotate_back_scatter (needs y), per destination node
+//   rotate_in_bwd        the VJP of rotate_in, per destination node
+//   src_reduce           fixed-order sum of the per-edge source contributions
+//
+// They take over blocks/eso2_ref.py:334-335 (gather + rotate in, with the radial gain of
+// :269-271, :284-285 applied while the row is in registers) and :343-349 (envelope, rotate
+// back, index_add_).  The rotation is block diagonal in the degree l, so each thread keeps
+// one degree's 2l+1 input rows of its channel group in registers and forms only the rows with
+// |m| <= mmax.  Channels are the fastest axis everywhere: a thread owns VEC consecutive
+// channels and moves them with one vector load/store.  No atomics: every output element is
+// produced by exactly one thread, in an order fixed by the CSR offsets.
+#include "zp_common.cuh"
+
+namespace {
+
+template <int VEC> struct Vec;
+template <> struct Vec<4> { using type = float4; };
+template <> struct Vec<2> { using type = float2; };
+template <> struct Vec<1> { using type = float; };
+
+template <int VEC>
+__device__ __forceinline__ void vload(float (&r)[VEC], const float *p) {
+  using V = typename Vec<VEC>::type;
+  const V v = *reinterpret_cast<const V *>(p);
+  const float *s = reinterpret_cast<const float *>(&v);
+#pragma unroll
+  for (int i = 0; i < VEC; ++i) r[i] = s[i];
+}
+template <int VEC>
+__device__ __forceinline__ void vstore(float *p, const float (&r)[VEC]) {
+  using V = typename Vec<VEC>::type;
+  V v;
+  float *s = reinterpret_cast<float *>(&v);
+#pragma unroll
+  for (int i = 0; i < VEC; ++i) s[i] = r[i];
+  *reinterpret_cast<V *>(p) = v;
+}
+
+__device__ __forceinline__ float warp_sum(float v) {
+#pragma unroll
+  for (int o = 16; o > 0; o >>= 1) v += __shfl_xor_sync(0xffffffffu, v, o);
+  return v;
+}
+
+// ------------------------------------------------------------------------------------------
+// rotate_in: one (edge, channel quad) per thread
+// ------------------------------------------------------------------------------------------
+
+constexpr int kRotInThreads = 256;
+constexpr int kRotInMaxEdges = 32;
+
+template <int L, int LMAX>
+struct RotIn {
+  static __device__ __forceinline__ void run(const ZpTables &t, const float *xrow,
+                                             const float *rot_s, const float *rad_e, float *a_e,
+                                             int c2) {
+    RotIn<L - 1, LMAX>::run(t, xrow, rot_s, rad_e, a_e, c2);
+    constexpr int n = 2 * L + 1;
+    const int C2 = 2 * t.C;
+    float u[n][4];
+#pragma unroll
+    for (int j = 0; j < n; ++j) vload<4>(u[j], xrow + (size_t)(L * L + j) * t.C);
+    const int mm = t.mmax < L ? t.mmax : L;
+#pragma unroll
+    for (int i = 0; i < n; ++i) {
+      const int am = i > L ? i - L : L - i;
+      if (am <= mm) {
+        const int r = t.row_of[L][i];
+        const float *rr = rot_s + t.rot_off[r];
+        float acc[4] = {0.f, 0.f, 0.f, 0.f};
+#pragma unroll
+        for (int j = 0; j < n; ++j) {
+          const float w = rr[j];
+#pragma unroll
+          for (int v = 0; v < 4; ++v) acc[v] = fmaf(w, u[j][v], acc[v]);
+        }
+        float g[4];
+        vload<4>(g, rad_e + t.rad_off[am] + (L - am) * C2 + c2);
+#pragma unroll
+        for (int v = 0; v < 4; ++v) acc[v] *= g[v];
+        vstore<4>(a_e + (size_t)r * C2 + c2, acc);
+      }
+    }
+  }
+};
+template <int LMAX>
+struct RotIn<-1, LMAX> {
+  static __device__ __forceinline__ void run(const ZpTables &, const float *, const float *,
+                                             const float *, float *, int) {}
+};
+
+template <int LMAX>
+__global__ void __launch_bounds__(kRotInThreads)
+rotate_in_kernel(const __grid_constant__ ZpTables t, int64_t E, int epb,
+                 const float *__restrict__ x, const int32_t *__restrict__ src,
+                 const int32_t *__restrict__ dst, const float *__restrict__ rot,
+                 const float *__restrict__ radial, float *__restrict__ a1) {
+  extern __shared__ float rot_s[];                       // [epb][nnz_pad]
+  const int Q = t.C / 2;                                 // channel quads of the 2C-wide message
+  const int64_t e0 = (int64_t)blockIdx.x * epb;
+  const int n_e = (int)min((int64_t)epb, E - e0);
+  for (int i = threadIdx.x; i < n_e * t.nnz_pad; i += blockDim.x)
+    rot_s[i] = rot[e0 * t.nnz_pad + i];
+  __syncthreads();
+  const int le = threadIdx.x / Q, q = threadIdx.x % Q;
+  if (le >= n_e) return;
+  const int64_t e = e0 + le;
+  const int c2 = 4 * q;
+  const bool second = c2 >= t.C;
+  const int64_t node = second ? dst[e] : src[e];
+  const float *xrow = x + (size_t)node * t.K * t.C + (second ? c2 - t.C : c2);
+  RotIn<LMAX, LMAX>::run(t, xrow, rot_s + le * t.nnz_pad, radial + (size_t)e * t.R,
+                         a1 + (size_t)e * t.Km * 2 * t.C, c2);
+}
+
+// ------------------------------------------------------------------------------------------
+// per-destination-node kernels: blockDim = (32 * W, NPB); W warps cover one node's channels
+// ------------------------------------------------------------------------------------------
+
+template <int LMAX> struct VecFor { static constexpr int value = LMAX <= 4 ? 4 : 2; };
+
+// stage one edge's packed rotation in this node slot's shared buffer
+__device__ __forceinline__ void stage_rot(const ZpTables &t, const float *rot_e, float *buf,
+                                          int tid, int nthreads) {
+  for (int i = tid; i < t.nnz_pad; i += nthreads) buf[i] = rot_e[i];
+}
+
+// named barrier over the threads of one node slot (W warps); slot ids start at 1
+__device__ __forceinline__ void slot_sync(int slot, int nthreads) {
+  if (nthreads == 32) __syncwarp();
+  else asm volatile("bar.sync %0, %1;" ::"r"(slot + 1), "r"(nthreads) : "memory");
+}
+
+template <int L, int LMAX, int VEC>
+struct RotBack {
+  static __device__ __forceinline__ void run(const ZpTables &t, const float *y_e,
+                                             const float *rot_s, float env,
+                                             float (&acc)[(LMAX + 1) * (LMAX + 1)][VEC], int c) {
+    RotBack<L - 1, LMAX, VEC>::run(t, y_e, rot_s, env, acc, c);
+    constexpr int n = 2 * L + 1;
+    const int mm = t.mmax < L ? t.mmax : L;
+#pragma unroll
+    for (int i = 0; i < n; ++i) {
+      const int am = i > L ? i - L : L - i;
+      if (am <= mm) {
+        const int r = t.row_of[L][i];
+        const float *rr = rot_s + t.rot_off[r];
+        float yv[VEC];
+        vload<VEC>(yv, y_e + (size_t)r * t.C + c);
+#pragma unroll
+        for (int v = 0; v < VEC; ++v) yv[v] *= env;
+#pragma unroll
+        for (int j = 0; j < n; ++j) {
+          const float w = rr[j];
+#pragma unroll
+          for (int v = 0; v < VEC; ++v) acc[L * L + j][v] = fmaf(w, yv[v], acc[L * L + j][v]);
+        }
+      }
+    }
+  }
+};
+template <int LMAX, int VEC>
+struct RotBack<-1, LMAX, VEC> {
+  static __device__ __forceinline__ void run(const ZpTables &, const float *, const float *,
+                                             float, float (&)[(LMAX + 1) * (LMAX + 1)][VEC],
+                                             int) {}
+};
+
+template <int LMAX>
+__global__ void __launch_bounds__(128)
+rotate_back_scatter_kernel(const __grid_constant__ ZpTables t, int64_t N,
+                           const float *__restrict__ y, const float *__restrict__ env,
+                           const float *__restrict__ rot, const int32_t *__restrict__ row_ptr,
+                           float *__restrict__ node_out) {
+  constexpr int VEC = VecFor<LMAX>::value;
+  constexpr int K = (LMAX + 1) * (LMAX + 1);
+  extern __shared__ float smem[];                        // [NPB][nnz_pad]
+  const int slot = threadIdx.y, nthr = blockDim.x;
+  float *rot_s = smem + slot * t.nnz_pad;
+  const int64_t n = (int64_t)blockIdx.x * blockDim.y + slot;
+  if (n >= N) return;                                    // whole slot leaves together
+  const int c = threadIdx.x * VEC;
+  const bool active = c < t.C;
+  float acc[K][VEC];
+#pragma unroll
+  for (int k = 0; k < K; ++k)
+#pragma unroll
+    for (int v = 0; v < VEC; ++v) acc[k][v] = 0.f;
+  const int e_beg = row_ptr[n], e_end = row_ptr[n + 1];
+  for (int e = e_beg; e < e_end; ++e) {
+    slot_sync(slot, nthr);
+    stage_rot(t, rot + (size_t)e * t.nnz_pad, rot_s, threadIdx.x, nthr);
+    slot_sync(slot, nthr);
+    if (active)
+      RotBack<LMAX, LMAX, VEC>::run(t, y + (size_t)e * t.Km * t.C, rot_s, env[e], acc, c);
+  }
+  if (active) {
+    float *o = node_out + (size_t)n * K * t.C + c;
+#pragma unroll
+    for (int k = 0; k < K; ++k) vstore<VEC>(o + (size_t)k * t.C, acc[k]);
+  }
+}
+
+// ---- VJP of rotate_back_scatter -------------------------------------------------------------
+//   t[r]        = sum_j rot[r, j] g[n, l^2 + j]          (g = grad of node_out, row n = dst)
+//   dy[e, r]    = env_e * t[r]
+//   grad_env[e] = sum_{r, c} y[e, r, c] t[r, c]
+//   grad_rot[e, r, j] = env_e * sum_c y[e, r, c] g[n, l^2 + j, c]
+template <int L, int LMAX, int VEC>
+struct GradOut {
+  static __device__ __forceinline__ void run(const ZpTables &t, const float *y_e, float *dy_e,
+                                             const float *rot_s, float *grot_s, float env,
+                                             const float (&g)[(LMAX + 1) * (LMAX + 1)][VEC],
+                                             float &genv, int c, bool active, bool lane0) {
+    GradOut<L - 1, LMAX, VEC>::run(t, y_e, dy_e, rot_s, grot_s, env, g, genv, c, active, lane0);
+    constexpr int n = 2 * L + 1;
+    const int mm = t.mmax < L ? t.mmax : L;
+#pragma unroll
+    for (int i = 0; i < n; ++i) {
+      const int am = i > L ? i - L : L - i;
+      if (am <= mm) {
+        const int r = t.row_of[L][i];
+        const float *rr = rot_s + t.rot_off[r];
+        float yv[VEC], tv[VEC];
+#pragma unroll
+        for (int v = 0; v < VEC; ++v) { yv[v] = 0.f; tv[v] = 0.f; }
+        if (active) vload<VEC>(yv, y_e + (size_t)r * t.C + c);
+#pragma unroll
+        for (int j = 0; j < n; ++j) {
+          const float w = rr[j];
+          float part = 0.f;
+#pragma unroll
+          for (int v = 0; v < VEC; ++v) {
+            tv[v] = fmaf(w, g[L * L + j][v], tv[v]);
+            part = fmaf(yv[v], g[L * L + j][v], part);
+          }
+          part = warp_sum(part);
+          if (lane0) grot_s[t.rot_off[r] + j] = env * part;
+        }
+#pragma unroll
+        for (int v = 0; v < VEC; ++v) {
+          genv = fmaf(yv[v], tv[v], genv);
+          tv[v] *= env;
+        }
+        if (active) vstore<VEC>(dy_e + (size_t)r * t.C + c, tv);
+      }
+    }
+  }
+};
+template <int LMAX, int VEC>
+struct GradOut<-1, LMAX, VEC> {
+  static __device__ __forceinline__ void run(const ZpTables &, const float *, float *,
+                                             const float *, float *, float,
+                                             const float (&)[(LMAX + 1) * (LMAX + 1)][VEC],
+                                             float &, int, bool, bool) {}
+};
+
+// Shared memory per node slot: rot [nnz_pad] | per-warp partial grad_rot [W][nnz_pad] | genv [W]
+template <int LMAX>
+__global__ void __launch_bounds__(128)
+rotate_grad_out_kernel(const __grid_constant__ ZpTables t, int64_t N,
+                       const float *__restrict__ g_out, const float *__restrict__ y,
+                       const float *__restrict__ env, const float *__restrict__ rot,
+                       const int32_t *__restrict__ row_ptr, float *__restrict__ dy,
+                       float *__restrict__ grad_env, float *__restrict__ grad_rot) {
+  constexpr int VEC = VecFor<LMAX>::value;
+  constexpr int K = (LMAX + 1) * (LMAX + 1);
+  extern __shared__ float smem[];
+  const int slot = threadIdx.y, nthr = blockDim.x, W = nthr / 32;
+  const int warp = threadIdx.x / 32, lane = threadIdx.x % 32;
+  const int per_slot = t.nnz_pad * (1 + W) + W;
+  float *rot_s = smem + slot * per_slot;
+  float *grot_s = rot_s + t.nnz_pad + warp * t.nnz_pad;
+  float *genv_s = rot_s + t.nnz_pad * (1 + W);
+  const int64_t n = (int64_t)blockIdx.x * blockDim.y + slot;
+  if (n >= N) return;
+  const int c = threadIdx.x * VEC;
+  const bool active = c < t.C;
+  float g[K][VEC];
+#pragma unroll
+  for (int k = 0; k < K; ++k) {
+#pragma unroll
+    for (int v = 0; v < VEC; ++v) g[k][v] = 0.f;
+    if (active) vload<VEC>(g[k], g_out + ((size_t)n * K + k) * t.C + c);
+  }
+  const int e_beg = row_ptr[n], e_end = row_ptr[n + 1];
+  for (int e = e_beg; e < e_end; ++e) {
+    slot_sync(slot, nthr);
+    stage_rot(t, rot + (size_t)e * t.nnz_pad, rot_s, threadIdx.x, nthr);
+    slot_sync(slot, nthr);
+    float genv = 0.f;
+    GradOut<LMAX, LMAX, VEC>::run(t, y + (size_t)e * t.Km * t.C, dy + (size_t)e * t.Km * t.C,
+                                  rot_s, grot_s, env[e], g, genv, c, active, lane == 0);
+    genv = warp_sum(genv);
+    if (lane == 0) genv_s[warp] = genv;
+    slot_sync(slot, nthr);
+    // fixed-order sum over the W warps
+    for (int i = threadIdx.x; i < t.nnz_pad; i += nthr) {
+      float s = 0.f;
+      if (i < t.nnz)
+        for (int w = 0; w < W; ++w) s += rot_s[t.nnz_pad * (1 + w) + i];
+      grad_rot[(size_t)e * t.nnz_pad + i] = s;
+    }
+    if (threadIdx.x == 0) {
+      float s = 0.f;
+      for (int w = 0; w < W; ++w) s += genv_s[w];
+      grad_env[e] = s;
+    }
+  }
+}
+
+// ---- VJP of rotate_in -----------------------------------------------------------------------
+//   a[r]   = sum_j rot[r, j] u[l^2 + j]            (recomputed; u = x_src | x_dst half)
+//   ga[r]  = da[e, r] * radial
+//   grad_radial[e, col] = sum over the +m / -m rows sharing the column of  da[r] * a[r]
+//   du[l^2 + j] = sum_r rot[r, j] ga[r]   -> du_src[e] (source half) or the node's own sum
+//   grad_rot[e, r, j] += sum_c2 ga[r, c2] u[l^2 + j, c2]
+template <int L, int LMAX, int VEC>
+struct RotInBwd {
+  static __device__ __forceinline__ void run(const ZpTables &t, const float *xrow,
+                                             const float *da_e, const float *rad_e,
+                                             float *grad_e, const float *rot_s, float *grot_s,
+                                             float *du_e,
+                                             float (&gx)[(LMAX + 1) * (LMAX + 1)][VEC], int c,
+                                             int half, bool active, bool lane0) {
+    RotInBwd<L - 1, LMAX, VEC>::run(t, xrow, da_e, rad_e, grad_e, rot_s, grot_s, du_e, gx, c,
+                                    half, active, lane0);
+    constexpr int n = 2 * L + 1;
+    const int C2 = 2 * t.C;
+    const int c2 = half * t.C + c;
+    const int mm = t.mmax < L ? t.mmax : L;
+    float u[n][VEC], du[n][VEC];
+#pragma unroll
+    for (int j = 0; j < n; ++j) {
+#pragma unroll
+      for (int v = 0; v < VEC; ++v) { u[j][v] = 0.f; du[j][v] = 0.f; }
+      if (active) vload<VEC>(u[j], xrow + (size_t)(L * L + j) * t.C);
+    }
+    // rows i = L + m and L - m share one radial column; walk m = 0..mm and both signs
+#pragma unroll
+    for (int am = 0; am <= L; ++am) {
+      if (am <= mm) {
+        float gr[VEC], rad[VEC];
+#pragma unroll
+        for (int v = 0; v < VEC; ++v) { gr[v] = 0.f; rad[v] = 0.f; }
+        const int col = t.rad_off[am] + (L - am) * C2 + c2;
+        if (active) vload<VEC>(rad, rad_e + col);
+#pragma unroll
+        for (int sgn = 0; sgn < 2; ++sgn) {
+          if (sgn == 1 && am == 0) continue;
+          const int i = sgn == 0 ? L + am : L - am;
+          const int r = t.row_of[L][i];
+          const float *rr = rot_s + t.rot_off[r];
+          float a[VEC], da[VEC];
+#pragma unroll
+          for (int v = 0; v < VEC; ++v) { a[v] = 0.f; da[v] = 0.f; }
+          if (active) vload<VEC>(da, da_e + (size_t)r * C2 + c2);
+#pragma unroll
+          for (int j = 0; j < n; ++j)
+#pragma unroll
+            for (int v = 0; v < VEC; ++v) a[v] = fmaf(rr[j], u[j][v], a[v]);
+          float ga[VEC];
+#pragma unroll
+          for (int v = 0; v < VEC; ++v) {
+            gr[v] = fmaf(da[v], a[v], gr[v]);
+            ga[v] = da[v] * rad[v];
+          }
+#pragma unroll
+          for (int j = 0; j < n; ++j) {
+            float part = 0.f;
+#pragma unroll
+            for (int v = 0; v < VEC; ++v) {
+              du[j][v] = fmaf(rr[j], ga[v], du[j][v]);
+              part = fmaf(ga[v], u[j][v], part);
+            }
+            part = warp_sum(part);
+            if (lane0) grot_s[t.rot_off[r] + j] += part;
+          }
+        }
+        if (active) vstore<VEC>(grad_e + col, gr);
+      }
+    }
+    if (half == 0) {
+      if (active) {
+#pragma unroll
+        for (int j = 0; j < n; ++j) vstore<VEC>(du_e + (size_t)(L * L + j) * t.C + c, du[j]);
+      }
+    } else {
+#pragma unroll
+      for (int j = 0; j < n; ++j)
+#pragma unroll
+        for (int v = 0; v < VEC; ++v) gx[L * L + j][v] += du[j][v];
+    }
+  }
+};
+template <int LMAX, int VEC>
+struct RotInBwd<-1, LMAX, VEC> {
+  static __device__ __forceinline__ void run(const ZpTables &, const float *, const float *,
+                                             const float *, float *, const float *, float *,
+                                             float *, float (&)[(LMAX + 1) * (LMAX + 1)][VEC],
+                                             int, int, bool, bool) {}
+};
+
+template <int LMAX>
+__global__ void __launch_bounds__(128)
+rotate_in_bwd_kernel(const __grid_constant__ ZpTables t, int64_t N,
+                     const float *__restrict__ da1, const float *__restrict__ radial,
+                     const float *__restrict__ x, const int32_t *__restrict__ src,
+                     const float *__restrict__ rot, const int32_t *__restrict__ row_ptr,
+                     float *__restrict__ grad_radial, float *__restrict__ du_src,
+                     float *__restrict__ grad_x, float *__restrict__ grad_rot) {
+  constexpr int VEC = VecFor<LMAX>::value;
+  constexpr int K = (LMAX + 1) * (LMAX + 1);
+  extern __shared__ float smem[];
+  const int slot = threadIdx.y, nthr = blockDim.x, W = nthr / 32;
+  const int warp = threadIdx.x / 32, lane = threadIdx.x % 32;
+  const int per_slot = t.nnz_pad * (1 + W);
+  float *rot_s = smem + slot * per_slot;
+  float *grot_s = rot_s + t.nnz_pad + warp * t.nnz_pad;
+  const int64_t n = (int64_t)blockIdx.x * blockDim.y + slot;
+  if (n >= N) return;
+  const int c = threadIdx.x * VEC;
+  const bool active = c < t.C;
+  float gx[K][VEC];
+#pragma unroll
+  for (int k = 0; k < K; ++k)
+#pragma unroll
+    for (int v = 0; v < VEC; ++v) gx[k][v] = 0.f;
+  const int e_beg = row_ptr[n], e_end = row_ptr[n + 1];
+  for (int e = e_beg; e < e_end; ++e) {
+    slot_sync(slot, nthr);
+    stage_rot(t, rot + (size_t)e * t.nnz_pad, rot_s, threadIdx.x, nthr);
+    if (lane == 0)
+      for (int i = 0; i < t.nnz_pad; ++i) grot_s[i] = 0.f;
+    slot_sync(slot, nthr);
+    const float *da_e = da1 + (size_t)e * t.Km * 2 * t.C;
+    const float *rad_e = radial + (size_t)e * t.R;
+    float *grad_e = grad_radial + (size_t)e * t.R;
+    float *du_e = du_src + (size_t)e * K * t.C;
+    const float *x_s = x + (size_t)src[e] * K * t.C + c;
+    const float *x_d = x + (size_t)n * K * t.C + c;
+    RotInBwd<LMAX, LMAX, VEC>::run(t, x_s, da_e, rad_e, grad_e, rot_s, grot_s, du_e, gx, c, 0,
+                                   active, lane == 0);
+    RotInBwd<LMAX, LMAX, VEC>::run(t, x_d, da_e, rad_e, grad_e, rot_s, grot_s, du_e, gx, c, 1,
+                                   active, lane == 0);
+    slot_sync(slot, nthr);
+    for (int i = threadIdx.x; i < t.nnz; i += nthr) {
+      float s = 0.f;
+      for (int w = 0; w < W; ++w) s += rot_s[t.nnz_pad * (1 + w) + i];
+      grad_rot[(size_t)e * t.nnz_pad + i] += s;
+    }
+  }
+  if (active) {
+    float *o = grad_x + (size_t)n * K * t.C + c;
+#pragma unroll
+    for (int k = 0; k < K; ++k) vstore<VEC>(o + (size_t)k * t.C, gx[k]);
+  }
+}
+
+// grad_x[n] += sum of du_src over the edges whose SOURCE is n, in source-sorted order
+__global__ void __launch_bounds__(128)
+src_reduce_kernel(int64_t N, int KC4, const float4 *__restrict__ du_src,
+                  const int32_t *__restrict__ perm_src, const int32_t *__restrict__ row_ptr_src,
+                  float4 *__restrict__ grad_x) {
+  const int64_t n = blockIdx.x;
+  if (n >= N) return;
+  const int beg = row_ptr_src[n], end = row_ptr_src[n + 1];
+  if (beg == end) return;
+  for (int i = threadIdx.x; i < KC4; i += blockDim.x) {
+    float4 acc = grad_x[(size_t)n * KC4 + i];
+    for (int k = beg; k < end; ++k) {
+      const float4 v = du_src[(size_t)perm_src[k] * KC4 + i];
+      acc.x += v.x; acc.y += v.y; acc.z += v.z; acc.w += v.w;
+    }
+    grad_x[(size_t)n * KC4 + i] = acc;
+  }
+}
+
+struct NodeLaunch {
+  dim3 grid, block;
+  int W;
+};
+
+template <int LMAX>
+NodeLaunch node_launch(const ZpTables &t, int64_t N) {
+  constexpr int VEC = VecFor<LMAX>::value;
+  const int groups = (t.C + VEC - 1) / VEC;
+  const int W = (groups + 31) / 32;
+  int npb = 4 / W;
+  if (npb < 1) npb = 1;
+  NodeLaunch nl;
+  nl.W = W;
+  nl.block = dim3(32 * W, npb);
+  nl.grid = dim3((unsigned)zp_ceil_div(N, npb));
+  return nl;
+}
+
+}  // namespace
+
+int zp_launch_rotate_in(const zp_plan *p, int64_t E, const float *x, const int32_t *src,
+                        const int32_t *dst, const float *rot, const float *radial, float *a1,
+                        cudaStream_t st) {
+  if (E == 0) return ZP_OK;
+  const ZpTables &t = p->t;
+  const int Q = t.C / 2;
+  if (Q < 1 || Q > kRotInThreads) return ZP_ERR_UNSUPPORTED;
+  int epb = kRotInThreads / Q;
+  if (epb > kRotInMaxEdges) epb = kRotInMaxEdges;
+  const dim3 grid((unsigned)zp_ceil_div(E, epb)), block(epb * Q);
+  const size_t smem = (size_t)epb * t.nnz_pad * sizeof(float);
+#define CALL(LM) \
+  rotate_in_kernel<LM><<<grid, block, smem, st>>>(t, E, epb, x, src, dst, rot, radial, a1)
+  ZP_DISPATCH_LMAX(t.lmax, CALL)
+#undef CALL
+  ZP_LAUNCH_CHECK("rotate_in_kernel");
+  return ZP_OK;
+}
+
+int zp_launch_rotate_back_scatter(const zp_plan *p, int64_t N, const float *y, const float *env,
+                                  const float *rot, const int32_t *row_ptr, float *node_out,
+                                  cudaStream_t st) {
+  if (N == 0) return ZP_OK;
+  const ZpTables &t = p->t;
+#define CALL(LM)                                                                       \
+  {                                                                                    \
+    const NodeLaunch nl = node_launch<LM>(t, N);                                       \
+    if (nl.W > 4) return ZP_ERR_UNSUPPORTED;                                           \
+    const size_t smem = (size_t)nl.block.y * t.nnz_pad * sizeof(float);                \
+    rotate_back_scatter_kernel<LM><<<nl.grid, nl.block, smem, st>>>(t, N, y, env, rot, \
+                                                                    row_ptr, node_out); \
+  }
+  ZP_DISPATCH_LMAX(t.lmax, CALL)
+#undef CALL
+  ZP_LAUNCH_CHECK("rotate_back_scatter_kernel");
+  return ZP_OK;
+}
+
+int zp_launch_rotate_grad_out(const zp_plan *p, int64_t N, const float *g, const float *y,
+                              const float *env, const float *rot, const int32_t *row_ptr,
+                              float *dy, float *grad_env, float *grad_rot, cudaStream_t st) {
+  if (N == 0) return ZP_OK;
+  const ZpTables &t = p->t;
+#define CALL(LM)                                                                            \
+  {                                                                                         \
+    const NodeLaunch nl = node_launch<LM>(t, N);                                            \
+    if (nl.W > 4) return ZP_ERR_UNSUPPORTED;                                                \
+    const size_t smem =                                                                     \
+        (size_t)nl.block.y * (t.nnz_pad * (1 + nl.W) + nl.W) * sizeof(float);               \
+    rotate_grad_out_kernel<LM><<<nl.grid, nl.block, smem, st>>>(t, N, g, y, env, rot,       \
+                                                                row_ptr, dy, grad_env,     \
+                                                                grad_rot);                  \
+  }
+  ZP_DISPATCH_LMAX(t.lmax, CALL)
+#undef CALL
+  ZP_LAUNCH_CHECK("rotate_grad_out_kernel");
+  return ZP_OK;
+}
+
+int zp_launch_rotate_in_bwd(const zp_plan *p, int64_t N, const float *da1, const float *radial,
+                            const float *x, const int32_t *src, const float *rot,
+                            const int32_t *row_ptr, float *grad_radial, float *du_src,
+                            float *grad_x, float *grad_rot, cudaStream_t st) {
+  if (N == 0) return ZP_OK;
+  const ZpTables &t = p->t;
+#define CALL(LM)                                                                          \
+  {                                                                                       \
+    const NodeLaunch nl = node_launch<LM>(t, N);                                          \
+    if (nl.W > 4) return ZP_ERR_UNSUPPORTED;                                              \
+    const size_t smem = (size_t)nl.block.y * t.nnz_pad * (1 + nl.W) * sizeof(float);      \
+    rotate_in_bwd_kernel<LM><<<nl.grid, nl.block, smem, st>>>(                            \
+        t, N, da1, radial, x, src, rot, row_ptr, grad_radial, du_src, grad_x, grad_rot);  \
+  }
+  ZP_DISPATCH_LMAX(t.lmax, CALL)
+#undef CALL
+  ZP_LAUNCH_CHECK("rotate_in_bwd_kernel");
+  return ZP_OK;
+}
+
+int zp_launch_src_reduce(const zp_plan *p, int64_t N, const float *du_src,
+                         const int32_t *perm_src, const int32_t *row_ptr_src, float *grad_x,
+                         cudaStream_t st) {
+  if (N == 0) return ZP_OK;
+  const int KC4 = p->t.K * p->t.C / 4;
+  src_reduce_kernel<<<(unsigned)N, 128, 0, st>>>(N, KC4, (const float4 *)du_src, perm_src,
+                                                 row_ptr_src, (float4 *)grad_x);
+  ZP_LAUNCH_CHECK("src_reduce_kernel");
+  return ZP_OK;
+}

@@ -1,0 +1,429 @@
+"""Benchmark of the eSEN SO(2) edge-convolution block (forward + first-order VJP).
+
+    python bench.py [--gpus N] [--steps K] [--warmup W] [--impl ours|reference]
+
+Workload (one "step" = one forward + VJP pass of the block over one batch): a periodic cube
+of 2 000 atoms at 0.1 atoms/A^3, 6 A cutoff, 30 nearest incoming neighbours per atom
+(60 000 directed edges), lmax 4 / mmax 2 / C = H = EC = 128, 64 Gaussian RBFs, fp32,
+gradients w.r.t. node embeddings, positions (through the Wigner-D derivative, the radial MLP
+and the envelope) and the SO(2) weights, upstream gradient ~ N(0,1).  Data are seeded
+synthetic tensors of those shapes; weights are Xavier-uniform.  With N > 1 every rank runs its
+own independent structure of that size (weak scaling, no data-path exchange) and the SO(2)
+weight gradients are all-reduced once per step.
+
+The line printed by rank 0 carries
+    value      edges/s of the kernel path with everything resident in HBM (C ABI forward +
+               backward; radial features and envelope precomputed, CSR built beforehand)
+    e2e        edges/s through the public module API from pinned HOST buffers: host->device
+               copies, CSR build, radial MLP, forward, autograd backward, device->host read
+    roofline   the dominant kernel class, timed live with CUDA events inside the library
+    cpu_baseline  the CPU oracle timed on this machine's host cores on a bounded sample
+`--impl reference` times the reference algorithm's CPU restatement (the oracle) instead.
+"""
+
+from __future__ import annotations
+
+import argparse
+import json
+import os
+import pathlib
+import statistics
+import subprocess
+import sys
+import tempfile
+import time
+
+import torch
+
+ROOT = pathlib.Path(__file__).resolve().parent
+if str(ROOT) not in sys.path:
+    sys.path.insert(0, str(ROOT))
+
+CFG = dict(lmax=4, mmax=2, sphere_channels=128, hidden_channels=128, edge_channels=128,
+           num_distance_basis=64, cutoff=6.0)
+N_ATOMS, MAX_NEIGHBORS, DENSITY = 2000, 30, 0.1
+METRIC = "edges/s per eSEN SO(2) block fwd+bwd (lmax4,C128)"
+FALLBACK_PEAKS = {"hbm_gbs": 6650.0, "bf16_tflops": 1590.0, "bf16_tflops_sustained": 1400.0}
+
+
+def peaks() -> tuple[dict, str]:
+    p = ROOT / "MEASURED_PEAKS.json"
+    if p.exists():
+        try:
+            return json.loads(p.read_text()), "measured"
+        except Exception:
+            pass
+    return dict(FALLBACK_PEAKS), "fallback"
+
+
+def gemm_macs_per_edge(cfg) -> int:
+    """Multiply-adds of the six SO(2) contractions for one edge (folded form = reference form)."""
+    L, M, C, H = cfg["lmax"], cfg["mmax"], cfg["sphere_channels"], cfg["hidden_channels"]
+    total = (L + 1) * 2 * C * (H * (L + 1) + L * H) + (L + 1) * H * C * (L + 1)
+    for m in range(1, M + 1):
+        km = L + 1 - m
+        total += (2 * km * 2 * C) * (2 * km * H) + (2 * km * H) * (2 * km * C)
+    return total
+
+
+def xavier_(block, seed: int) -> None:
+    g = torch.Generator("cpu").manual_seed(seed)
+    with torch.no_grad():
+        for name, p in block.named_parameters():
+            if p.dim() == 2 and not name.startswith("elem_emb"):
+                bound = (6.0 / (p.shape[0] + p.shape[1])) ** 0.5
+                p.copy_((torch.rand(p.shape, generator=g) * 2 - 1) * bound)
+                if name.startswith(("c1_m.", "c2_m.")):
+                    p.mul_(2 ** -0.5)
+
+
+class ClockSampler:
+    """Samples SM clock and throttle reasons of one GPU with nvidia-smi while a region runs."""
+
+    FIELDS = ("clocks.sm,clocks.max.sm,power.draw,clocks_event_reasons.hw_slowdown,"
+              "clocks_event_reasons.hw_thermal_slowdown,clocks_event_reasons.sw_thermal_slowdown,"
+              "clocks_event_reasons.sw_power_cap")
+
+    def __init__(self, index: int):
+        self.index, self.proc, self.path = index, None, None
+
+    def __enter__(self):
+        try:
+            fd, self.path = tempfile.mkstemp(suffix=".csv")
+            os.close(fd)
+            self.proc = subprocess.Popen(
+                ["nvidia-smi", f"--query-gpu={self.FIELDS}", "--format=csv,noheader,nounits",
+                 "-lms", "100", "-i", str(self.index)],
+                stdout=open(self.path, "w"), stderr=subprocess.DEVNULL)
+        except Exception:
+            self.proc = None
+        return self
+
+    def __exit__(self, *exc):
+        if self.proc is not None:
+            self.proc.terminate()
+            try:
+                self.proc.wait(timeout=5)
+            except Exception:
+                self.proc.kill()
+
+    def summary(self) -> dict:
+        out = {"sm_mhz": None, "sm_max_mhz": None, "reasons": [], "samples": 0}
+        try:
+            rows = [r.split(",") for r in open(self.path).read().strip().splitlines() if r]
+            os.unlink(self.path)
+        except Exception:
+            return out
+        sm, reasons = [], set()
+        names = ("hw_slowdown", "hw_thermal_slowdown", "sw_thermal_slowdown", "sw_power_cap")
+        for r in rows:
+            try:
+                sm.append(float(r[0])); out["sm_max_mhz"] = float(r[1])
+            except Exception:
+                continue
+            for nm, v in zip(names, r[3:7]):
+                if v.strip().lower() == "active":
+                    reasons.add(nm)
+        if sm:
+            out["sm_mhz"] = statistics.median(sm)
+        out["reasons"], out["samples"] = sorted(reasons), len(sm)
+        return out
+
+
+def make_workload(seed: int):
+    from zippel_b200.graph import synthetic_batch
+    batch = synthetic_batch(N_ATOMS, CFG["lmax"], CFG["sphere_channels"], CFG["cutoff"],
+                            density=DENSITY, max_neighbors=MAX_NEIGHBORS, seed=seed)
+    g = torch.Generator("cpu").manual_seed(seed + 7)
+    batch["upstream"] = torch.randn(batch["x_node"].shape, generator=g)
+    return batch
+
+
+# ------------------------------------------------------------------------------------------
+# CPU leg (oracle): used for cpu_baseline and for --impl reference
+# ------------------------------------------------------------------------------------------
+
+def cpu_step_factory(batch, sample_nodes: int, threads: int):
+    """Forward + VJP of the oracle on the edges into the first `sample_nodes` atoms."""
+    from oracle import eso2_oracle as orc
+    torch.set_num_threads(threads)
+    params = orc.init_params(CFG, seed=0, dtype=torch.float32)
+    jd = orc.load_jd(ROOT / "zippel_b200" / "data" / "jd.npz", CFG["lmax"])
+    ei = batch["edge_index"]
+    keep = ei[1] < sample_nodes
+    ei_s = ei[:, keep]
+    shifts, cg, sg = batch["shifts"][keep], batch["cos_gamma_k"][keep], batch["sin_gamma_k"][keep]
+    so2 = [k for k in params if k.startswith(("c1_", "c2_"))]
+
+    def step():
+        pos = batch["pos"].clone().requires_grad_(True)
+        x = batch["x_node"].clone().requires_grad_(True)
+        p = {k: (v.clone().requires_grad_(True) if k in so2 else v) for k, v in params.items()}
+        out = orc.block_node_out(p, CFG, pos, batch["atomic_numbers"], x, ei_s, shifts, cg, sg, jd)
+        torch.autograd.grad((out * batch["upstream"]).sum(), [x, pos, *[p[k] for k in so2]])
+
+    return step, int(keep.sum())
+
+
+def run_reference(args) -> dict:
+    threads = os.cpu_count() or 1
+    batch = make_workload(0)
+    step, n_edges = cpu_step_factory(batch, args.cpu_sample_nodes, threads)
+    for _ in range(args.warmup):
+        step()
+    t0 = time.perf_counter()
+    for _ in range(args.steps):
+        step()
+    dt = (time.perf_counter() - t0) / args.steps
+    val = n_edges / dt
+    sample = (f"edges into the first {args.cpu_sample_nodes} of {N_ATOMS} atoms "
+              f"({n_edges} of {batch['meta']['n_edges']} edges) per step, fp32 torch CPU")
+    return {
+        "impl": "reference", "metric": METRIC, "value": val, "unit": "edges/s",
+        "n_gpus": args.gpus, "steps": args.steps, "warmup": args.warmup,
+        "ms_per_step": dt * 1e3, "higher_is_better": True, "scaling": "weak",
+        "vs_baseline": None, "dtype": "f32", "data": "synthetic",
+        "config": workload_config(batch, "host cores only"),
+        "cpu_baseline": {"value": val, "unit": "edges/s", "cores": threads, "kind": "port",
+                         "sample": sample},
+        "e2e": {"value": val, "unit": "edges/s", "h2d_bytes_per_step": 0,
+                "d2h_bytes_per_step": 0},
+        "gpu_launches": 0,
+    }
+
+
+def workload_config(batch, l2: str) -> dict:
+    m = batch["meta"]
+    return {"workload": "eSEN SO(2) block fwd+VJP, 2000 atoms periodic cube 0.1/A^3, 6 A cutoff, "
+                        "30 neighbours, lmax4 mmax2 C128 H128 EC128 64 RBF, fp32",
+            "atoms_per_gpu": m["n_atoms"], "edges_per_gpu": m["n_edges"], "lmax": CFG["lmax"],
+            "mmax": CFG["mmax"], "channels": CFG["sphere_channels"], "l2": l2}
+
+
+# ------------------------------------------------------------------------------------------
+# GPU arm
+# ------------------------------------------------------------------------------------------
+
+def run_ours(args) -> dict | None:
+    import torch.distributed as dist
+
+    from zippel_b200 import _lib
+    from zippel_b200.blocks.eso2 import BlockConfig, ESO2Block
+    from zippel_b200.graph import EdgeGraph
+    from zippel_b200.runner import EdgeConvRunner
+
+    world = int(os.environ.get("WORLD_SIZE", "1"))
+    rank = int(os.environ.get("RANK", "0"))
+    local = int(os.environ.get("LOCAL_RANK", "0"))
+    if not torch.cuda.is_available():
+        raise RuntimeError("bench.py needs a CUDA device: the kernels have no CPU path")
+    torch.cuda.set_device(local)
+    dev = torch.device("cuda", local)
+    if world > 1:
+        dist.init_process_group("nccl", device_id=dev)
+    _lib.load()
+
+    batch = make_workload(rank)
+    n, e = batch["meta"]["n_atoms"], batch["meta"]["n_edges"]
+    block = ESO2Block(BlockConfig(**CFG))
+    xavier_(block, 0)
+    block = block.to(dev)
+    so2_params = [block.c1_m0.weight, block.c1_m0.bias, *[l.weight for l in block.c1_m],
+                  block.c2_m0.weight, block.c2_m0.bias, *[l.weight for l in block.c2_m]]
+
+    # ---- resident inputs for the kernel-path timing ----------------------------------------
+    d = {k: v.to(dev) for k, v in batch.items() if torch.is_tensor(v)}
+    graph = EdgeGraph.build(d["edge_index"], n)
+    with torch.no_grad():
+        perm, src, dst = graph.perm64, graph.src.long(), graph.dst.long()
+        edge_vec = (d["pos"][dst] - d["pos"][src] + d["shifts"][perm]).contiguous()
+        dist_e = edge_vec.pow(2).sum(-1).clamp_min(1e-24).sqrt()
+        x_edge = torch.cat([block.gaussian_basis(dist_e), block.elem_emb(d["atomic_numbers"][src]),
+                            block.elem_emb(d["atomic_numbers"][dst])], dim=-1)
+        radial = block.rad_func(x_edge).contiguous()
+        env = block.envelope(dist_e / CFG["cutoff"]).contiguous()
+        cg, sg = d["cos_gamma_k"][perm].contiguous(), d["sin_gamma_k"][perm].contiguous()
+    runner = EdgeConvRunner(block.plan(dev), graph, with_backward=True)
+    runner.bind(d["x_node"].contiguous(), edge_vec, cg, sg, radial, env,
+                block.c1_m0.weight.detach(), block.c1_m0.bias.detach(),
+                [l.weight.detach() for l in block.c1_m], block.c2_m0.weight.detach(),
+                block.c2_m0.bias.detach(), [l.weight.detach() for l in block.c2_m])
+    upstream = d["upstream"].contiguous()
+    flush = torch.empty(256 << 20, dtype=torch.uint8, device=dev)
+    grad_bucket = None
+
+    def kernel_step():
+        runner.forward()
+        gw = runner.backward(upstream)[4]
+        if world > 1:
+            nonlocal grad_bucket
+            flat = [gw[0], gw[1], *gw[2], gw[3], gw[4], *gw[5]]
+            grad_bucket = torch.cat([t.reshape(-1) for t in flat])
+            dist.all_reduce(grad_bucket)
+
+    def barrier():
+        if world > 1:
+            dist.barrier()
+        torch.cuda.synchronize()
+
+    for _ in range(max(args.warmup, 3)):
+        kernel_step()
+    barrier()
+    runner.timing(True)
+    runner.read_timing()
+    ev = [(torch.cuda.Event(True), torch.cuda.Event(True)) for _ in range(args.steps)]
+    fwd_ev = [torch.cuda.Event(True) for _ in range(args.steps)]
+    with ClockSampler(local) as clocks:
+        barrier()
+        t_wall = time.perf_counter()
+        for a, b in ev:
+            flush.zero_()                       # evict L2 between steps (not inside the events)
+            a.record()
+            kernel_step()
+            b.record()
+        barrier()
+        t_wall = time.perf_counter() - t_wall
+    step_ms = [a.elapsed_time(b) for a, b in ev]
+    total_ms = torch.tensor([sum(step_ms)], dtype=torch.float64, device=dev)
+    if world > 1:
+        dist.all_reduce(total_ms, op=dist.ReduceOp.MAX)
+    ms_per_step = total_ms.item() / args.steps
+    timing = runner.read_timing()
+    runner.timing(False)
+    clk = clocks.summary()
+
+    # forward-only timing (same resident inputs)
+    for a in fwd_ev:
+        pass
+    fa, fb = torch.cuda.Event(True), torch.cuda.Event(True)
+    barrier()
+    fwd_ms = 0.0
+    for _ in range(args.steps):
+        flush.zero_()
+        fa.record(); runner.forward(); fb.record()
+        fb.synchronize()
+        fwd_ms += fa.elapsed_time(fb)
+    fwd_ms /= args.steps
+
+    # ---- end to end through the module API from pinned host memory -------------------------
+    host = {k: batch[k].pin_memory() for k in ("pos", "x_node", "edge_index", "shifts",
+                                               "cos_gamma_k", "sin_gamma_k", "atomic_numbers",
+                                               "upstream")}
+    h2d = sum(t.numel() * t.element_size() for t in host.values())
+    out_host = torch.empty(n, 3, pin_memory=True)
+    loss_host = torch.empty((), pin_memory=True)
+    d2h = out_host.numel() * 4 + 4
+
+    def e2e_step():
+        t = {k: v.to(dev, non_blocking=True) for k, v in host.items()}
+        pos = t["pos"].requires_grad_(True)
+        x = t["x_node"].requires_grad_(True)
+        node_out = block.node_output(pos, t["atomic_numbers"], x, t["edge_index"], t["shifts"],
+                                     t["cos_gamma_k"], t["sin_gamma_k"])
+        loss = (node_out * t["upstream"]).sum()
+        grads = torch.autograd.grad(loss, [x, pos, *block.parameters()], allow_unused=True)
+        if world > 1:
+            flat = torch.cat([g.reshape(-1) for g, p in zip(grads[2:], block.parameters())
+                              if g is not None and any(p is q for q in so2_params)])
+            dist.all_reduce(flat)
+        out_host.copy_(grads[1], non_blocking=True)
+        loss_host.copy_(loss.detach(), non_blocking=True)
+        torch.cuda.current_stream().synchronize()
+
+    for _ in range(3):
+        e2e_step()
+    barrier()
+    t0 = time.perf_counter()
+    for _ in range(args.steps):
+        e2e_step()
+    barrier()
+    e2e_s = torch.tensor([(time.perf_counter() - t0) / args.steps], dtype=torch.float64, device=dev)
+    if world > 1:
+        dist.all_reduce(e2e_s, op=dist.ReduceOp.MAX)
+    total_edges = torch.tensor([e], dtype=torch.float64, device=dev)
+    if world > 1:
+        dist.all_reduce(total_edges)
+    total_edges = total_edges.item()
+
+    # ---- roofline of the dominant kernel class ---------------------------------------------
+    pk, pk_src = peaks()
+    macs = gemm_macs_per_edge(CFG)
+    total_kernel_ms = sum(v[0] for v in timing.values())
+    kernels = {k: {"ms_per_step": v[0] / args.steps, "launches_per_step": v[1] / args.steps,
+                   "share": v[0] / total_kernel_ms if total_kernel_ms else 0.0}
+               for k, v in timing.items() if v[1]}
+    top = max(kernels, key=lambda k: kernels[k]["share"])
+    launches = sum(v[1] for v in timing.values()) / args.steps
+    roof = None
+    if top.startswith("gemm"):
+        per_launch = kernels[top]["ms_per_step"] / max(kernels[top]["launches_per_step"], 1)
+        flops_step = 2.0 * macs * e            # each of fwd / dgrad / wgrad does the same MACs
+        ach = flops_step / (kernels[top]["ms_per_step"] * 1e-3) / 1e12
+        peak = pk["bf16_tflops_sustained"]
+        roof = {"bound": "tensor", "kernel": top, "achieved": ach, "peak": peak,
+                "unit": "TFLOP/s", "frac": ach / peak, "traffic": None,
+                "peak_source": f"{pk_src} bf16 dense sustained (no fp32/tf32 peak is measured)",
+                "ms_per_launch": per_launch,
+                "note": "algorithmic FLOPs = 2*MAC of the six per-m SO(2) products, counted "
+                        "once whatever the tensor-core pass count"}
+    else:
+        roof = {"bound": "hbm", "kernel": top, "achieved": None, "peak": pk["hbm_gbs"],
+                "unit": "GB/s", "frac": None, "traffic": None, "peak_source": pk_src}
+
+    line = None
+    if rank == 0:
+        line = {
+            "metric": METRIC, "value": total_edges / (ms_per_step * 1e-3), "unit": "edges/s",
+            "n_gpus": world, "steps": args.steps, "warmup": max(args.warmup, 3),
+            "ms_per_step": ms_per_step, "higher_is_better": True, "scaling": "weak",
+            "vs_baseline": None, "dtype": "f32", "data": "synthetic",
+            "config": workload_config(batch, "256 MiB L2 flush between steps, outside the "
+                                             "per-step events; per-step activations are >5 GB"),
+            "fwd_only": {"value": e / (fwd_ms * 1e-3), "unit": "edges/s (this rank)",
+                         "ms_per_step": fwd_ms},
+            "wall_ms_per_step_incl_flush": t_wall * 1e3 / args.steps,
+            "roofline": roof, "kernels": kernels, "gpu_launches": launches,
+            "e2e": {"value": total_edges / e2e_s.item(), "unit": "edges/s",
+                    "ms_per_step": e2e_s.item() * 1e3, "h2d_bytes_per_step": h2d,
+                    "d2h_bytes_per_step": d2h},
+            "clocks": clk,
+        }
+        if world == 1 and not args.no_cpu_baseline:
+            threads = os.cpu_count() or 1
+            step, n_s = cpu_step_factory(batch, args.cpu_sample_nodes, threads)
+            step()
+            t0 = time.perf_counter()
+            reps = 2
+            for _ in range(reps):
+                step()
+            dt = (time.perf_counter() - t0) / reps
+            line["cpu_baseline"] = {
+                "value": n_s / dt, "unit": "edges/s", "cores": threads, "kind": "port",
+                "sample": f"oracle fwd+VJP on the {n_s} edges into the first "
+                          f"{args.cpu_sample_nodes} atoms, {reps} repetitions after 1 warm-up"}
+    if world > 1:
+        dist.barrier()
+        dist.destroy_process_group()
+    return line
+
+
+def main() -> None:
+    ap = argparse.ArgumentParser()
+    ap.add_argument("--gpus", type=int, default=1)
+    ap.add_argument("--steps", type=int, default=10)
+    ap.add_argument("--warmup", type=int, default=3)
+    ap.add_argument("--impl", default="ours", choices=["ours", "reference"])
+    ap.add_argument("--cpu-sample-nodes", type=int, default=100)
+    ap.add_argument("--no-cpu-baseline", action="store_true")
+    args = ap.parse_args()
+    if args.impl == "reference":
+        if int(os.environ.get("RANK", "0")) == 0:
+            print(json.dumps(run_reference(args)), flush=True)
+        return
+    line = run_ours(args)
+    if line is not None:
+        print(json.dumps(line), flush=True)
+
+
+if __name__ == "__main__":
+    main()

@@ -157,6 +157,33 @@ int zp_eso2_backward(const zp_plan *plan, int64_t n_nodes, int64_t n_edges,
                      const zp_weight_grads *gw, void *workspace, size_t workspace_bytes,
                      void *stream);
 
+/* Per-kernel-class device timing for benchmarks (the reference times whole steps with CUDA
+ * events, bench/harness.py:88-149; there is no per-kernel counterpart).  While enabled, the
+ * forward/backward drivers bracket each kernel class with CUDA events on the caller's stream.
+ * zp_timing_read synchronises those events, ADDS the elapsed milliseconds and launch counts
+ * since the previous read into ms[cls] / launches[cls] (arrays of ZP_N_KERNEL_CLASSES) and
+ * resets.  Not thread-safe: use one thread per plan while timing is on.                     */
+typedef enum zp_kernel_class {
+  ZP_K_FOLD = 0,          /* weight folding / unfolding                                     */
+  ZP_K_WIGNER_FWD = 1,
+  ZP_K_ROTATE_IN = 2,
+  ZP_K_GEMM_FWD = 3,      /* SO(2) contractions, forward                                    */
+  ZP_K_GATE_FWD = 4,
+  ZP_K_ROTATE_BACK = 5,   /* envelope + rotate back + segmented scatter                      */
+  ZP_K_ROTATE_GRAD_OUT = 6,
+  ZP_K_GEMM_DGRAD = 7,
+  ZP_K_GEMM_WGRAD = 8,
+  ZP_K_BIAS_GRAD = 9,
+  ZP_K_GATE_BWD = 10,
+  ZP_K_ROTATE_IN_BWD = 11,
+  ZP_K_SRC_REDUCE = 12,
+  ZP_K_WIGNER_BWD = 13,
+  ZP_N_KERNEL_CLASSES = 14
+} zp_kernel_class;
+const char *zp_kernel_class_name(int cls);
+int zp_timing_enable(zp_plan *plan, int on);
+int zp_timing_read(zp_plan *plan, float *ms, int64_t *launches);
+
 #ifdef __cplusplus
 }
 #endif

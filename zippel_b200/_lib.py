@@ -56,7 +56,11 @@ SIGNATURES = {
                                                                 _SZ, _P]),
     "zp_eso2_backward": (C.c_int, [_P, _I64, _I64] + [_P] * 12 + [C.POINTER(ZpWeights)]
                          + [_P] * 4 + [C.POINTER(ZpWeights), _P, _SZ, _P]),
+    "zp_kernel_class_name": (C.c_char_p, [C.c_int]),
+    "zp_timing_enable": (C.c_int, [_P, C.c_int]),
+    "zp_timing_read": (C.c_int, [_P, C.POINTER(C.c_float), C.POINTER(C.c_int64)]),
 }
+N_KERNEL_CLASSES = 14
 
 
 def lib_path() -> pathlib.Path:

@@ -3,12 +3,47 @@
 #include <cstdio>
 #include <cstring>
 #include <new>
+#include <vector>
 
 #include "zp_common.cuh"
+
+// Event pairs recorded around kernel classes while timing is on.
+struct ZpTimer {
+  struct Span { int cls; cudaEvent_t a, b; int64_t launches; };
+  std::vector<Span> spans;      // pool; `used` of them hold live records
+  size_t used = 0;
+  Span *open(int cls, cudaStream_t st) {
+    if (used == spans.size()) {
+      Span s{cls, nullptr, nullptr, 0};
+      if (cudaEventCreate(&s.a) != cudaSuccess || cudaEventCreate(&s.b) != cudaSuccess) return nullptr;
+      spans.push_back(s);
+    }
+    Span *s = &spans[used++];
+    s->cls = cls;
+    s->launches = zp_launch_counter();
+    cudaEventRecord(s->a, st);
+    return s;
+  }
+  static void close(Span *s, cudaStream_t st) {
+    if (!s) return;
+    cudaEventRecord(s->b, st);
+    s->launches = zp_launch_counter() - s->launches;
+  }
+};
 
 namespace {
 
 thread_local char g_cuda_error[512] = "";
+thread_local int64_t g_launches = 0;
+
+// brackets one expression with a timing span when the plan has a timer
+#define ZP_TIMED(cls, expr)                                                      \
+  do {                                                                           \
+    ZpTimer::Span *span_ = plan->timer ? plan->timer->open(cls, st) : nullptr;   \
+    rc = (expr);                                                                 \
+    ZpTimer::close(span_, st);                                                   \
+    if (rc) return rc;                                                           \
+  } while (0)
 
 bool aligned16(const void *p) { return (reinterpret_cast<uintptr_t>(p) & 15u) == 0; }
 
@@ -70,6 +105,8 @@ Workspace carve(const zp_plan *p, int64_t N, int64_t E, int with_backward, void 
 }
 
 }  // namespace
+
+int64_t &zp_launch_counter() { return g_launches; }
 
 void zp_set_cuda_error(cudaError_t e, const char *where) {
   std::snprintf(g_cuda_error, sizeof(g_cuda_error), "%s: %s (%s)", where, cudaGetErrorName(e),
@@ -174,8 +211,43 @@ int zp_plan_create(const zp_config *cfg, const double *jd_host, zp_plan **plan_o
   return ZP_OK;
 }
 
+const char *zp_kernel_class_name(int cls) {
+  static const char *names[ZP_N_KERNEL_CLASSES] = {
+      "fold_weights", "wigner_fwd", "rotate_in", "gemm_fwd", "gate_fwd", "rotate_back_scatter",
+      "rotate_grad_out", "gemm_dgrad", "gemm_wgrad", "bias_grad", "gate_bwd", "rotate_in_bwd",
+      "src_reduce", "wigner_bwd"};
+  return cls >= 0 && cls < ZP_N_KERNEL_CLASSES ? names[cls] : "?";
+}
+
+int zp_timing_enable(zp_plan *plan, int on) {
+  if (!plan) return ZP_ERR_INVALID_ARG;
+  if (on && !plan->timer) plan->timer = new (std::nothrow) ZpTimer;
+  if (!on && plan->timer) {
+    for (auto &s : plan->timer->spans) { cudaEventDestroy(s.a); cudaEventDestroy(s.b); }
+    delete plan->timer;
+    plan->timer = nullptr;
+  }
+  return ZP_OK;
+}
+
+int zp_timing_read(zp_plan *plan, float *ms, int64_t *launches) {
+  if (!plan || !plan->timer || !ms || !launches) return ZP_ERR_INVALID_ARG;
+  ZpTimer *t = plan->timer;
+  for (size_t i = 0; i < t->used; ++i) {
+    ZpTimer::Span &s = t->spans[i];
+    ZP_CUDA(cudaEventSynchronize(s.b));
+    float v = 0.f;
+    ZP_CUDA(cudaEventElapsedTime(&v, s.a, s.b));
+    ms[s.cls] += v;
+    launches[s.cls] += s.launches;
+  }
+  t->used = 0;
+  return ZP_OK;
+}
+
 int zp_plan_destroy(zp_plan *plan) {
   if (!plan) return ZP_OK;
+  zp_timing_enable(plan, 0);
   if (plan->jd_dev) cudaFree(plan->jd_dev);
   delete plan;
   return ZP_OK;
@@ -252,28 +324,31 @@ int zp_eso2_forward(const zp_plan *plan, int64_t N, int64_t E, const float *x_no
   cudaStream_t st = (cudaStream_t)stream;
   const ZpTables &t = plan->t;
 
-  if ((rc = zp_launch_fold_weights(plan, w, ws.wfold, st))) return rc;
-  if ((rc = zp_launch_wigner_fwd(plan, E, edge_vec, cos_g, sin_g, ws.rot, st))) return rc;
-  if ((rc = zp_launch_rotate_in(plan, E, x_node, src, dst, ws.rot, radial, ws.a1, st))) return rc;
+  ZP_TIMED(ZP_K_FOLD, zp_launch_fold_weights(plan, w, ws.wfold, st));
+  ZP_TIMED(ZP_K_WIGNER_FWD, zp_launch_wigner_fwd(plan, E, edge_vec, cos_g, sin_g, ws.rot, st));
+  ZP_TIMED(ZP_K_ROTATE_IN,
+           zp_launch_rotate_in(plan, E, x_node, src, dst, ws.rot, radial, ws.a1, st));
   const int64_t lda = (int64_t)t.Km * 2 * t.C, ldh = (int64_t)t.Km * t.H, ldy = (int64_t)t.Km * t.C;
   for (int m = 0; m < plan->n_blocks; ++m) {
     const int in = plan->c1_in[m], out = plan->c1_out[m];
     const float *A = ws.a1 + (size_t)t.m_row0[m] * 2 * t.C;
     float *Cc = ws.h1 + (m == 0 ? 0 : t.n_gate + (size_t)t.m_row0[m] * t.H);
-    if ((rc = zp_launch_gemm(E, out, in, A, lda, 1, ws.wfold + plan->c1_woff[m], 1, in,
-                             m == 0 ? w->c1_b0 : nullptr, Cc, t.w1_cols, 1, nullptr, st)))
-      return rc;
+    ZP_TIMED(ZP_K_GEMM_FWD,
+             zp_launch_gemm(E, out, in, A, lda, 1, ws.wfold + plan->c1_woff[m], 1, in,
+                            m == 0 ? w->c1_b0 : nullptr, Cc, t.w1_cols, 1, nullptr, st));
   }
-  if ((rc = zp_launch_gate_fwd(plan, E, ws.h1, ws.ht, st))) return rc;
+  ZP_TIMED(ZP_K_GATE_FWD, zp_launch_gate_fwd(plan, E, ws.h1, ws.ht, st));
   for (int m = 0; m < plan->n_blocks; ++m) {
     const int in = plan->c2_in[m], out = plan->c2_out[m];
     const float *A = ws.ht + (size_t)t.m_row0[m] * t.H;
     float *Cc = ws.y + (size_t)t.m_row0[m] * t.C;
-    if ((rc = zp_launch_gemm(E, out, in, A, ldh, 1, ws.wfold + plan->c2_woff[m], 1, in,
-                             m == 0 ? w->c2_b0 : nullptr, Cc, ldy, 1, nullptr, st)))
-      return rc;
+    ZP_TIMED(ZP_K_GEMM_FWD,
+             zp_launch_gemm(E, out, in, A, ldh, 1, ws.wfold + plan->c2_woff[m], 1, in,
+                            m == 0 ? w->c2_b0 : nullptr, Cc, ldy, 1, nullptr, st));
   }
-  return zp_launch_rotate_back_scatter(plan, N, ws.y, env, ws.rot, row_ptr, node_out, st);
+  ZP_TIMED(ZP_K_ROTATE_BACK,
+           zp_launch_rotate_back_scatter(plan, N, ws.y, env, ws.rot, row_ptr, node_out, st));
+  return ZP_OK;
 }
 
 int zp_eso2_backward(const zp_plan *plan, int64_t N, int64_t E, const float *grad_node_out,
@@ -308,9 +383,9 @@ int zp_eso2_backward(const zp_plan *plan, int64_t N, int64_t E, const float *gra
   const int64_t lda = (int64_t)t.Km * 2 * t.C, ldh = (int64_t)t.Km * t.H, ldy = (int64_t)t.Km * t.C;
   const int splits = wgrad_splits(E);
 
-  if ((rc = zp_launch_rotate_grad_out(plan, N, grad_node_out, ws.y, env, ws.rot, row_ptr, ws.dy,
-                                      grad_env, ws.grot, st)))
-    return rc;
+  ZP_TIMED(ZP_K_ROTATE_GRAD_OUT,
+           zp_launch_rotate_grad_out(plan, N, grad_node_out, ws.y, env, ws.rot, row_ptr, ws.dy,
+                                     grad_env, ws.grot, st));
   // conv2: input gradient, weight gradient (reduced over edges), bias gradient
   for (int m = 0; m < plan->n_blocks; ++m) {
     const int in = plan->c2_in[m], out = plan->c2_out[m];
@@ -318,37 +393,38 @@ int zp_eso2_backward(const zp_plan *plan, int64_t N, int64_t E, const float *gra
     const float *Xm = ws.ht + (size_t)t.m_row0[m] * t.H;
     float *dXm = ws.dht + (size_t)t.m_row0[m] * t.H;
     const float *Wm = ws.wfold + plan->c2_woff[m];
-    if ((rc = zp_launch_gemm(E, in, out, dYm, ldy, 1, Wm, in, 1, nullptr, dXm, ldh, 1, nullptr, st)))
-      return rc;
-    if ((rc = zp_launch_gemm(out, in, E, dYm, 1, ldy, Xm, ldh, 1, nullptr,
-                             ws.wgrad + plan->c2_woff[m], in, splits, ws.scratch, st)))
-      return rc;
+    ZP_TIMED(ZP_K_GEMM_DGRAD,
+             zp_launch_gemm(E, in, out, dYm, ldy, 1, Wm, in, 1, nullptr, dXm, ldh, 1, nullptr, st));
+    ZP_TIMED(ZP_K_GEMM_WGRAD,
+             zp_launch_gemm(out, in, E, dYm, 1, ldy, Xm, ldh, 1, nullptr,
+                            ws.wgrad + plan->c2_woff[m], in, splits, ws.scratch, st));
   }
-  if ((rc = zp_launch_colsum(E, plan->c2_out[0], ws.dy, ldy, gw->c2_b0, ws.scratch, st))) return rc;
-  if ((rc = zp_launch_gate_bwd(plan, E, ws.h1, ws.dht, ws.dh1, st))) return rc;
+  ZP_TIMED(ZP_K_BIAS_GRAD,
+           zp_launch_colsum(E, plan->c2_out[0], ws.dy, ldy, gw->c2_b0, ws.scratch, st));
+  ZP_TIMED(ZP_K_GATE_BWD, zp_launch_gate_bwd(plan, E, ws.h1, ws.dht, ws.dh1, st));
   for (int m = 0; m < plan->n_blocks; ++m) {
     const int in = plan->c1_in[m], out = plan->c1_out[m];
     const float *dYm = ws.dh1 + (m == 0 ? 0 : t.n_gate + (size_t)t.m_row0[m] * t.H);
     const float *Xm = ws.a1 + (size_t)t.m_row0[m] * 2 * t.C;
     float *dXm = ws.da1 + (size_t)t.m_row0[m] * 2 * t.C;
     const float *Wm = ws.wfold + plan->c1_woff[m];
-    if ((rc = zp_launch_gemm(E, in, out, dYm, t.w1_cols, 1, Wm, in, 1, nullptr, dXm, lda, 1,
-                             nullptr, st)))
-      return rc;
-    if ((rc = zp_launch_gemm(out, in, E, dYm, 1, t.w1_cols, Xm, lda, 1, nullptr,
-                             ws.wgrad + plan->c1_woff[m], in, splits, ws.scratch, st)))
-      return rc;
+    ZP_TIMED(ZP_K_GEMM_DGRAD, zp_launch_gemm(E, in, out, dYm, t.w1_cols, 1, Wm, in, 1, nullptr,
+                                             dXm, lda, 1, nullptr, st));
+    ZP_TIMED(ZP_K_GEMM_WGRAD,
+             zp_launch_gemm(out, in, E, dYm, 1, t.w1_cols, Xm, lda, 1, nullptr,
+                            ws.wgrad + plan->c1_woff[m], in, splits, ws.scratch, st));
   }
-  if ((rc = zp_launch_colsum(E, plan->c1_out[0], ws.dh1, t.w1_cols, gw->c1_b0, ws.scratch, st)))
-    return rc;
-  if ((rc = zp_launch_rotate_in_bwd(plan, N, ws.da1, radial, x_node, src, ws.rot, row_ptr,
-                                    grad_radial, ws.du_src, grad_x_node, ws.grot, st)))
-    return rc;
-  if ((rc = zp_launch_src_reduce(plan, N, ws.du_src, perm_src, row_ptr_src, grad_x_node, st)))
-    return rc;
-  if ((rc = zp_launch_wigner_bwd(plan, E, edge_vec, cos_g, sin_g, ws.grot, grad_edge_vec, st)))
-    return rc;
-  return zp_launch_unfold_wgrad(plan, ws.wgrad, gw, st);
+  ZP_TIMED(ZP_K_BIAS_GRAD,
+           zp_launch_colsum(E, plan->c1_out[0], ws.dh1, t.w1_cols, gw->c1_b0, ws.scratch, st));
+  ZP_TIMED(ZP_K_ROTATE_IN_BWD,
+           zp_launch_rotate_in_bwd(plan, N, ws.da1, radial, x_node, src, ws.rot, row_ptr,
+                                   grad_radial, ws.du_src, grad_x_node, ws.grot, st));
+  ZP_TIMED(ZP_K_SRC_REDUCE,
+           zp_launch_src_reduce(plan, N, ws.du_src, perm_src, row_ptr_src, grad_x_node, st));
+  ZP_TIMED(ZP_K_WIGNER_BWD,
+           zp_launch_wigner_bwd(plan, E, edge_vec, cos_g, sin_g, ws.grot, grad_edge_vec, st));
+  ZP_TIMED(ZP_K_FOLD, zp_launch_unfold_wgrad(plan, ws.wgrad, gw, st));
+  return ZP_OK;
 }
 
 }  // extern "C"

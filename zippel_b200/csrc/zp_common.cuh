@@ -30,7 +30,10 @@ struct ZpTables {
   int16_t jd_off[ZP_MAX_L + 1];                 // offset of J_l in the packed J array
 };
 
+struct ZpTimer;
+
 struct zp_plan {
+  ZpTimer *timer;                               // null unless timing is enabled
   zp_config cfg;
   ZpTables t;
   int device;
@@ -54,8 +57,12 @@ void zp_set_cuda_error(cudaError_t e, const char *where);
     }                                                   \
   } while (0)
 
+// kernel launches issued by this thread (each launch is followed by one ZP_LAUNCH_CHECK)
+int64_t &zp_launch_counter();
+
 #define ZP_LAUNCH_CHECK(name)                           \
   do {                                                  \
+    ++zp_launch_counter();                              \
     cudaError_t e_ = cudaGetLastError();                \
     if (e_ != cudaSuccess) {                            \
       zp_set_cuda_error(e_, name);                      \

@@ -134,9 +134,11 @@ int exclusive_scan(int64_t n, const int32_t *in, int32_t *out, int32_t *block_su
                    cudaStream_t st) {
   const int64_t nb = zp_ceil_div(n + 1, kScanBlock);
   scan_block_kernel<<<(unsigned)nb, kScanBlock, 0, st>>>(n, in, out, block_sums);
+  ZP_LAUNCH_CHECK("scan_block_kernel");
   scan_sums_kernel<<<1, 32, 0, st>>>(nb, block_sums);
+  ZP_LAUNCH_CHECK("scan_sums_kernel");
   scan_add_kernel<<<(unsigned)nb, kScanBlock, 0, st>>>(n, out, block_sums, (int32_t)E);
-  ZP_LAUNCH_CHECK("exclusive_scan");
+  ZP_LAUNCH_CHECK("scan_add_kernel");
   return ZP_OK;
 }
 
@@ -167,24 +169,32 @@ int zp_csr_build(const int64_t *edge_index, int64_t E, int64_t N, int32_t *perm,
   // destination view
   ZP_CUDA(cudaMemsetAsync(w.counts, 0, sizeof(int32_t) * (N + 1), st));
   ZP_CUDA(cudaMemsetAsync(w.cursor, 0, sizeof(int32_t) * (N + 1), st));
-  if (E) count_kernel<<<eb, 256, 0, st>>>(E, dst64, w.counts);
+  if (E) {
+    count_kernel<<<eb, 256, 0, st>>>(E, dst64, w.counts);
+    ZP_LAUNCH_CHECK("count_kernel");
+  }
   if ((rc = exclusive_scan(N, w.counts, row_ptr, w.block_sums, E, st))) return rc;
   if (E) {
     bucket_kernel<<<eb, 256, 0, st>>>(E, dst64, row_ptr, w.cursor, w.tmp);
+    ZP_LAUNCH_CHECK("bucket_kernel");
     rank_dst_kernel<<<nbw, 256, 0, st>>>(N, src64, row_ptr, w.tmp, perm, src_sorted, dst_sorted);
+    ZP_LAUNCH_CHECK("rank_dst_kernel");
   }
-  ZP_LAUNCH_CHECK("csr destination view");
 
   // source view over sorted-edge ids
   ZP_CUDA(cudaMemsetAsync(w.counts, 0, sizeof(int32_t) * (N + 1), st));
   ZP_CUDA(cudaMemsetAsync(w.cursor, 0, sizeof(int32_t) * (N + 1), st));
-  if (E) count32_kernel<<<eb, 256, 0, st>>>(E, src_sorted, w.counts);
+  if (E) {
+    count32_kernel<<<eb, 256, 0, st>>>(E, src_sorted, w.counts);
+    ZP_LAUNCH_CHECK("count32_kernel");
+  }
   if ((rc = exclusive_scan(N, w.counts, row_ptr_src, w.block_sums, E, st))) return rc;
   if (E) {
     bucket32_kernel<<<eb, 256, 0, st>>>(E, src_sorted, row_ptr_src, w.cursor, w.tmp);
+    ZP_LAUNCH_CHECK("bucket32_kernel");
     rank_src_kernel<<<nbw, 256, 0, st>>>(N, row_ptr_src, w.tmp, perm_src);
+    ZP_LAUNCH_CHECK("rank_src_kernel");
   }
-  ZP_LAUNCH_CHECK("csr source view");
   return ZP_OK;
 }
 

@@ -1,0 +1,88 @@
+"""Pre-allocated, autograd-free driver of the edge-convolution kernels.
+
+``EdgeConvRunner`` plays the role of the reference back end's ``compile_program`` /
+``allocate`` / ``run_program`` trio (codegen/compose.py:113-239) for the one program this
+package runs: it sizes and allocates every device buffer once, then ``forward()`` /
+``backward()`` only enqueue kernels on the current stream through the C ABI.
+"""
+
+from __future__ import annotations
+
+import ctypes
+
+import torch
+
+from . import _lib
+from .blocks.eso2 import Plan, _weights_struct
+from .graph import EdgeGraph
+
+
+class EdgeConvRunner:
+    def __init__(self, plan: Plan, graph: EdgeGraph, with_backward: bool = True):
+        self.plan, self.graph, self.with_backward = plan, graph, with_backward
+        self.lib = _lib.load()
+        n, e, s, dev = graph.n_nodes, graph.n_edges, plan.sizes, plan.device
+        f32 = dict(dtype=torch.float32, device=dev)
+        self.ws = plan.workspace(n, e, with_backward)
+        self.node_out = torch.empty(n, s.K, plan.c, **f32)
+        if with_backward:
+            self.grad_x = torch.empty(n, s.K, plan.c, **f32)
+            self.grad_edge_vec = torch.empty(e, 3, **f32)
+            self.grad_radial = torch.empty(e, s.R, **f32)
+            self.grad_env = torch.empty(e, **f32)
+            self.grad_w = None
+        self._w = self._gw = None
+        self._keep = []
+
+    def bind(self, x_node, edge_vec, cos_g, sin_g, radial, env, c1_w0, c1_b0, c1_wm, c2_w0,
+             c2_b0, c2_wm):
+        """Fixes the input tensors (fp32, contiguous, sorted-edge order); no copies are made."""
+        tens = [x_node, edge_vec, cos_g, sin_g, radial, env, c1_w0, c1_b0, c2_w0, c2_b0,
+                *c1_wm, *c2_wm]
+        for t in tens:
+            if t.dtype != torch.float32 or not t.is_contiguous() or not t.is_cuda:
+                raise ValueError("EdgeConvRunner.bind needs contiguous fp32 CUDA tensors")
+        self.inputs = (x_node, edge_vec, cos_g, sin_g, radial, env)
+        self.weights = (c1_w0, c1_b0, list(c1_wm), c2_w0, c2_b0, list(c2_wm))
+        self._w, k1 = _weights_struct(self.plan.mmax, *self.weights)
+        self._keep = [k1]
+        if self.with_backward:
+            g = [torch.empty_like(t) for t in (c1_w0, c1_b0, c2_w0, c2_b0)]
+            g1, g2 = [torch.empty_like(t) for t in c1_wm], [torch.empty_like(t) for t in c2_wm]
+            self.grad_w = (g[0], g[1], g1, g[2], g[3], g2)
+            self._gw, k2 = _weights_struct(self.plan.mmax, *self.grad_w)
+            self._keep.append(k2)
+
+    def forward(self) -> torch.Tensor:
+        x, ev, cg, sg, rad, en = self.inputs
+        g = self.graph
+        st = torch.cuda.current_stream().cuda_stream
+        _lib.check(self.lib.zp_eso2_forward(
+            self.plan.handle, g.n_nodes, g.n_edges, x.data_ptr(), ev.data_ptr(), cg.data_ptr(),
+            sg.data_ptr(), rad.data_ptr(), en.data_ptr(), g.src.data_ptr(), g.dst.data_ptr(),
+            g.row_ptr.data_ptr(), ctypes.byref(self._w), self.node_out.data_ptr(),
+            self.ws.data_ptr(), self.ws.numel(), st), "zp_eso2_forward")
+        return self.node_out
+
+    def backward(self, grad_node_out: torch.Tensor):
+        x, ev, cg, sg, rad, en = self.inputs
+        g = self.graph
+        st = torch.cuda.current_stream().cuda_stream
+        _lib.check(self.lib.zp_eso2_backward(
+            self.plan.handle, g.n_nodes, g.n_edges, grad_node_out.data_ptr(), x.data_ptr(),
+            ev.data_ptr(), cg.data_ptr(), sg.data_ptr(), rad.data_ptr(), en.data_ptr(),
+            g.src.data_ptr(), g.dst.data_ptr(), g.row_ptr.data_ptr(), g.perm_src.data_ptr(),
+            g.row_ptr_src.data_ptr(), ctypes.byref(self._w), self.grad_x.data_ptr(),
+            self.grad_edge_vec.data_ptr(), self.grad_radial.data_ptr(), self.grad_env.data_ptr(),
+            ctypes.byref(self._gw), self.ws.data_ptr(), self.ws.numel(), st), "zp_eso2_backward")
+        return self.grad_x, self.grad_edge_vec, self.grad_radial, self.grad_env, self.grad_w
+
+    # -- per-kernel-class timing ---------------------------------------------------------
+    def timing(self, on: bool) -> None:
+        _lib.check(self.lib.zp_timing_enable(self.plan.handle, int(on)), "zp_timing_enable")
+
+    def read_timing(self) -> dict[str, tuple[float, int]]:
+        n = _lib.N_KERNEL_CLASSES
+        ms, cnt = (ctypes.c_float * n)(), (ctypes.c_int64 * n)()
+        _lib.check(self.lib.zp_timing_read(self.plan.handle, ms, cnt), "zp_timing_read")
+        return {self.lib.zp_kernel_class_name(i).decode(): (ms[i], cnt[i]) for i in range(n)}

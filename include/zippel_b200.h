@@ -157,6 +157,24 @@ int zp_eso2_backward(const zp_plan *plan, int64_t n_nodes, int64_t n_edges,
                      const zp_weight_grads *gw, void *workspace, size_t workspace_bytes,
                      void *stream);
 
+/* The contraction engine on its own (no reference counterpart: the reference calls
+ * torch.nn.functional.linear, blocks/eso2_ref.py:272,286).  Exposed for tests and benchmarks.
+ * zp_split_planes writes an fp32 matrix [rows, cols] (row stride ld_in) as `planes` (1 or 3)
+ * bf16 matrices [rows, ld_out] that sum to it, plane p starting plane_stride elements after
+ * plane p-1; columns cols..ld_out-1 are zero.  zp_gemm_planes computes, on the tensor cores,
+ *   C[M, N] = sum over plane pairs  A_pa  B_pb^T  (+ bias[n]),   fp32 output, row stride ldc,
+ * for K-major operands X[p*plane + r*ld + k] or, with a_mn / b_mn = 1, MN-major operands
+ * X[p*plane + k*ld + r].  ld, plane strides: multiples of 8; ldc: multiple of 4.            */
+int zp_split_planes(int64_t rows, int64_t cols, const float *in, int64_t ld_in, void *out,
+                    int64_t ld_out, int64_t plane_stride, int planes, void *stream);
+int zp_gemm_planes(zp_plan *plan, int64_t M, int64_t N, int64_t K, int planes, const void *A,
+                   int64_t lda, int64_t a_plane, int a_mn, const void *B, int64_t ldb,
+                   int64_t b_plane, int b_mn, const float *bias, float *C, int64_t ldc,
+                   int variant, void *stream);
+/* Reads (synchronously) and clears the plan's device status word: ZP_OK, or
+ * ZP_ERR_DEVICE_TIMEOUT if a bounded device-side wait gave up since the last read.          */
+int zp_plan_device_status(zp_plan *plan, int *status_out);
+
 /* Per-kernel-class device timing for benchmarks (the reference times whole steps with CUDA
  * events, bench/harness.py:88-149; there is no per-kernel counterpart).  While enabled, the
  * forward/backward drivers bracket each kernel class with CUDA events on the caller's stream.

@@ -200,6 +200,8 @@ int zp_plan_create(const zp_config *cfg, const double *jd_host, zp_plan **plan_o
   p->w_elems = woff;
 
   if (cudaGetDevice(&p->device) != cudaSuccess ||
+      cudaMalloc(&p->status_dev, sizeof(int)) != cudaSuccess ||
+      cudaMemset(p->status_dev, 0, sizeof(int)) != cudaSuccess ||
       cudaMalloc(&p->jd_dev, sizeof(double) * jo) != cudaSuccess ||
       cudaMemcpy(p->jd_dev, jd_host, sizeof(double) * jo, cudaMemcpyHostToDevice) !=
           cudaSuccess) {
@@ -249,6 +251,7 @@ int zp_plan_destroy(zp_plan *plan) {
   if (!plan) return ZP_OK;
   zp_timing_enable(plan, 0);
   if (plan->jd_dev) cudaFree(plan->jd_dev);
+  if (plan->status_dev) cudaFree(plan->status_dev);
   delete plan;
   return ZP_OK;
 }
@@ -272,6 +275,31 @@ int zp_plan_tables(const zp_plan *plan, int32_t *row_l, int32_t *row_m, int32_t 
     if (gate_idx) gate_idx[r] = r == 0 ? -1 : t.row_l[r] - 1;
   }
   return ZP_OK;
+}
+
+int zp_plan_device_status(zp_plan *plan, int *status_out) {
+  if (!plan || !status_out) return ZP_ERR_INVALID_ARG;
+  ZP_CUDA(cudaMemcpy(status_out, plan->status_dev, sizeof(int), cudaMemcpyDeviceToHost));
+  if (*status_out) ZP_CUDA(cudaMemset(plan->status_dev, 0, sizeof(int)));
+  return ZP_OK;
+}
+
+int zp_split_planes(int64_t rows, int64_t cols, const float *in, int64_t ld_in, void *out,
+                    int64_t ld_out, int64_t plane_stride, int planes, void *stream) {
+  if (rows < 0 || cols < 0 || cols > ld_out || planes < 1 || planes > 3 || !in || !out)
+    return ZP_ERR_INVALID_ARG;
+  return zp_launch_split_planes(rows, cols, in, ld_in, out, ld_out, plane_stride, planes,
+                                (cudaStream_t)stream);
+}
+
+int zp_gemm_planes(zp_plan *plan, int64_t M, int64_t N, int64_t K, int planes, const void *A,
+                   int64_t lda, int64_t a_plane, int a_mn, const void *B, int64_t ldb,
+                   int64_t b_plane, int b_mn, const float *bias, float *C, int64_t ldc,
+                   int variant, void *stream) {
+  if (!plan || !A || !B || !C || M < 0 || N < 0 || K <= 0) return ZP_ERR_INVALID_ARG;
+  ZpGemmTc g{M, N, K, planes, A, lda, a_plane, a_mn, B, ldb, b_plane, b_mn, bias, C, ldc,
+             plan->status_dev, variant};
+  return zp_launch_gemm_tc(g, (cudaStream_t)stream);
 }
 
 int zp_wigner_forward(const zp_plan *plan, int64_t n_edges, const float *edge_vec,

@@ -38,6 +38,7 @@ struct zp_plan {
   ZpTables t;
   int device;
   double *jd_dev;                               // packed J_l, fp64
+  int *status_dev;                              // device status word (0 = ok)
   // per-m GEMM shapes of the folded SO(2) weights
   int n_blocks;                                 // mmax + 1
   int c1_in[ZP_MAX_L + 1], c1_out[ZP_MAX_L + 1], c2_in[ZP_MAX_L + 1], c2_out[ZP_MAX_L + 1];
@@ -118,6 +119,23 @@ int zp_launch_gate_bwd(const zp_plan *p, int64_t E, const float *h1, const float
 int zp_launch_gemm(int64_t M, int64_t N, int64_t K, const float *A, int64_t am, int64_t ak,
                    const float *B, int64_t bk, int64_t bn, const float *bias, float *C,
                    int64_t ldc, int splits, float *scratch, cudaStream_t st);
+
+// Tensor-core product over bf16 planes: C[M,N] = sum_pairs A_pa * B_pb^T (+ bias), fp32 out.
+// K-major operand: X[p*plane + r*ld + k]; MN-major (x_mn = 1): X[p*plane + k*ld + r].
+struct ZpGemmTc {
+  int64_t M, N, K;
+  int planes;                                   // 1 (bf16) or 3 (fp32 carried as three bf16)
+  const void *A; int64_t lda, a_plane; int a_mn;
+  const void *B; int64_t ldb, b_plane; int b_mn;
+  const float *bias;
+  float *C; int64_t ldc;
+  int *status;                                  // device word, set on a device-side timeout
+  int variant;                                  // tile-shape choice for the 3-plane K-major case
+};
+int zp_launch_gemm_tc(const ZpGemmTc &g, cudaStream_t st);
+// fp32 [rows, cols] (row stride ld_in) -> `planes` bf16 planes [rows, ld_out]
+int zp_launch_split_planes(int64_t rows, int64_t cols, const float *in, int64_t ld_in, void *out,
+                           int64_t ld_out, int64_t plane_stride, int planes, cudaStream_t st);
 
 int zp_launch_fold_weights(const zp_plan *p, const zp_weights *w, float *packed, cudaStream_t st);
 int zp_launch_unfold_wgrad(const zp_plan *p, const float *packed_grad, const zp_weight_grads *gw,

@@ -9,9 +9,26 @@
 //              [ Wb   Wa ]            of shape [2 km Cout, 2 km Cin],
 // the same number of multiply-adds as the reference's two-row form, and no recombination.
 // Every m-block of conv1 and conv2 is therefore a plain  Y[E, out] = X[E, in] W_fold^T.
+#include <cuda_bf16.h>
+
 #include "zp_common.cuh"
 
 namespace {
+
+// fp32 -> up to three bf16 terms whose sum reproduces the value to ~2^-24
+__global__ void split_planes_kernel(int64_t rows, int64_t cols, const float *__restrict__ in,
+                                    int64_t ld_in, __nv_bfloat16 *__restrict__ out, int64_t ld_out,
+                                    int64_t plane_stride, int planes) {
+  const int64_t idx = (int64_t)blockIdx.x * blockDim.x + threadIdx.x;
+  if (idx >= rows * ld_out) return;
+  const int64_t r = idx / ld_out, c = idx % ld_out;
+  float x = c < cols ? in[r * ld_in + c] : 0.f;
+  for (int p = 0; p < planes; ++p) {
+    const __nv_bfloat16 h = __float2bfloat16_rn(x);
+    out[(size_t)p * plane_stride + idx] = h;
+    x -= __bfloat162float(h);
+  }
+}
 
 // ------------------------------------------------------------------------------------------
 // strided SIMT GEMM, 128x128x16 tiles, 8x8 outputs per thread
@@ -268,6 +285,15 @@ int zp_launch_gemm(int64_t M, int64_t N, int64_t K, const float *A, int64_t am, 
                                                                            bias, C, ldc);
     ZP_LAUNCH_CHECK("split_reduce_kernel");
   }
+  return ZP_OK;
+}
+
+int zp_launch_split_planes(int64_t rows, int64_t cols, const float *in, int64_t ld_in, void *out,
+                           int64_t ld_out, int64_t plane_stride, int planes, cudaStream_t st) {
+  if (rows == 0 || ld_out == 0) return ZP_OK;
+  split_planes_kernel<<<(unsigned)zp_ceil_div(rows * ld_out, 256), 256, 0, st>>>(
+      rows, cols, in, ld_in, (__nv_bfloat16 *)out, ld_out, plane_stride, planes);
+  ZP_LAUNCH_CHECK("split_planes_kernel");
   return ZP_OK;
 }
 

@@ -1,0 +1,482 @@
+// The SO(2) contraction on the Blackwell tensor cores (tcgen05 + TMEM + TMA), sm_100a only.
+//
+//     C[M, N] (fp32) = sum over plane pairs (pa, pb) of  A_pa[M, K] * B_pb[N, K]^T   (+ bias[n])
+//
+// Operands are bf16 "planes".  With one plane per operand this is a plain bf16 GEMM with fp32
+// accumulation.  With three planes an fp32 value x is carried as x = x0 + x1 + x2 (each a
+// bf16, x0 = rn(x), x1 = rn(x - x0), x2 = rn(x - x0 - x1)), and the six products
+//     A0B0, A0B1, A1B0, A1B1, A0B2, A2B0
+// (everything down to 2^-16 of the leading term) accumulate into the same TMEM tile, which
+// reproduces the fp32 product to ~2^-22 while staying on the bf16 pipe and keeping fp32's
+// exponent range.  All planes of a k-block are loaded once and reused by the six MMAs.
+//
+// Structure: persistent CTAs (one per SM), 192 threads.
+//   warp 0      TMA producer: one elected lane streams A/B plane tiles into a ring of stages
+//   warp 1      allocates TMEM, then one elected lane issues tcgen05.mma and commits
+//   warps 2..5  epilogue: tcgen05.ld the 128 x BN accumulator, add bias, store fp32 rows
+// Two TMEM accumulators (2 x 256 columns) let the epilogue of tile i overlap the main loop of
+// tile i+1.  Tiles are ordered n-fastest so CTAs running side by side share one A row block
+// (read from HBM once, then L2) while the weights stay L2 resident.
+//
+// Operand layouts in global memory (element strides, all multiples of 8 so TMA rows are 16-byte
+// aligned):  K-major   X[p*plane + r*ld + k]   (rows r = m or n, contraction index fastest)
+//            MN-major  X[p*plane + k*ld + r]   (used by the weight-gradient products, whose
+//                                               contraction runs over edges)
+// Shared-memory tiles use the 128-byte (BK = 64) or 64-byte (BK = 32) swizzle that TMA writes
+// and the matrix descriptors name.  Every mbarrier wait is bounded: after ~2 s it records
+// ZP_ERR_DEVICE_TIMEOUT in the status word, raises the CTA's abort flag and the CTA drains.
+#include <cuda.h>
+#include <cuda_bf16.h>
+
+#include "zp_common.cuh"
+
+namespace {
+
+constexpr int BM = 128;
+constexpr int kTmemBuf = 256;          // TMEM columns per accumulator buffer
+constexpr int kThreads = 192;
+constexpr uint64_t kWaitLimitNs = 2000000000ull;
+
+__device__ __forceinline__ uint32_t smem_u32(const void *p) {
+  return (uint32_t)__cvta_generic_to_shared(p);
+}
+__device__ __forceinline__ uint64_t globaltimer_ns() {
+  uint64_t t;
+  asm volatile("mov.u64 %0, %%globaltimer;" : "=l"(t));
+  return t;
+}
+__device__ __forceinline__ bool elect_one() {
+  uint32_t pred = 0;
+  asm volatile(
+      "{\n"
+      ".reg .pred px;\n"
+      "elect.sync _|px, 0xFFFFFFFF;\n"
+      "@px mov.s32 %0, 1;\n"
+      "}\n"
+      : "+r"(pred));
+  return pred != 0;
+}
+
+__device__ __forceinline__ void mbar_init(uint64_t *bar, uint32_t count) {
+  asm volatile("mbarrier.init.shared::cta.b64 [%0], %1;" ::"r"(smem_u32(bar)), "r"(count));
+}
+__device__ __forceinline__ void mbar_expect_tx(uint64_t *bar, uint32_t bytes) {
+  asm volatile("mbarrier.arrive.expect_tx.shared::cta.b64 _, [%0], %1;" ::"r"(smem_u32(bar)),
+               "r"(bytes)
+               : "memory");
+}
+__device__ __forceinline__ void mbar_arrive(uint64_t *bar) {
+  asm volatile("mbarrier.arrive.shared::cta.b64 _, [%0];" ::"r"(smem_u32(bar)) : "memory");
+}
+__device__ __forceinline__ bool mbar_try_wait(uint64_t *bar, uint32_t parity) {
+  uint32_t ok;
+  asm volatile(
+      "{\n"
+      ".reg .pred p;\n"
+      "mbarrier.try_wait.parity.shared::cta.b64 p, [%1], %2;\n"
+      "selp.u32 %0, 1, 0, p;\n"
+      "}\n"
+      : "=r"(ok)
+      : "r"(smem_u32(bar)), "r"(parity)
+      : "memory");
+  return ok != 0;
+}
+
+// Bounded wait.  Returns false when the CTA is aborting (this wait or another one timed out).
+__device__ __forceinline__ bool mbar_wait(uint64_t *bar, uint32_t parity, volatile int *abort_flag,
+                                          int *status) {
+  if (mbar_try_wait(bar, parity)) return true;
+  const uint64_t t0 = globaltimer_ns();
+  uint32_t spins = 0;
+  while (!mbar_try_wait(bar, parity)) {
+    if ((++spins & 0x3ff) == 0) {
+      if (*abort_flag) return false;
+      if (globaltimer_ns() - t0 > kWaitLimitNs) {
+        *abort_flag = 1;
+        atomicExch(status, (int)ZP_ERR_DEVICE_TIMEOUT);
+        return false;
+      }
+    }
+  }
+  return true;
+}
+
+__device__ __forceinline__ void tma_load_3d(void *dst, const CUtensorMap *map, uint64_t *bar, int c0,
+                                            int c1, int c2) {
+  asm volatile(
+      "cp.async.bulk.tensor.3d.shared::cluster.global.mbarrier::complete_tx::bytes"
+      " [%0], [%1, {%3, %4, %5}], [%2];"
+      :
+      : "r"(smem_u32(dst)), "l"(reinterpret_cast<uint64_t>(map)), "r"(smem_u32(bar)), "r"(c0),
+        "r"(c1), "r"(c2)
+      : "memory");
+}
+
+__device__ __forceinline__ void tcgen05_fence_before() {
+  asm volatile("tcgen05.fence::before_thread_sync;" ::: "memory");
+}
+__device__ __forceinline__ void tcgen05_fence_after() {
+  asm volatile("tcgen05.fence::after_thread_sync;" ::: "memory");
+}
+__device__ __forceinline__ void tcgen05_commit(uint64_t *bar) {
+  asm volatile("tcgen05.commit.cta_group::1.mbarrier::arrive::one.shared::cluster.b64 [%0];" ::"r"(
+                   smem_u32(bar))
+               : "memory");
+}
+__device__ __forceinline__ void umma_bf16(uint32_t tmem_d, uint64_t desc_a, uint64_t desc_b,
+                                          uint32_t idesc, uint32_t accumulate) {
+  asm volatile(
+      "{\n"
+      ".reg .pred p;\n"
+      "setp.ne.b32 p, %4, 0;\n"
+      "tcgen05.mma.cta_group::1.kind::f16 [%0], %1, %2, %3, p;\n"
+      "}\n"
+      :
+      : "r"(tmem_d), "l"(desc_a), "l"(desc_b), "r"(idesc), "r"(accumulate)
+      : "memory");
+}
+__device__ __forceinline__ void tmem_ld32(uint32_t taddr, uint32_t (&r)[32]) {
+  asm volatile(
+      "tcgen05.ld.sync.aligned.32x32b.x32.b32 "
+      "{%0, %1, %2, %3, %4, %5, %6, %7, %8, %9, %10, %11, %12, %13, %14, %15, "
+      "%16, %17, %18, %19, %20, %21, %22, %23, %24, %25, %26, %27, %28, %29, %30, %31}, [%32];"
+      : "=r"(r[0]), "=r"(r[1]), "=r"(r[2]), "=r"(r[3]), "=r"(r[4]), "=r"(r[5]), "=r"(r[6]),
+        "=r"(r[7]), "=r"(r[8]), "=r"(r[9]), "=r"(r[10]), "=r"(r[11]), "=r"(r[12]), "=r"(r[13]),
+        "=r"(r[14]), "=r"(r[15]), "=r"(r[16]), "=r"(r[17]), "=r"(r[18]), "=r"(r[19]), "=r"(r[20]),
+        "=r"(r[21]), "=r"(r[22]), "=r"(r[23]), "=r"(r[24]), "=r"(r[25]), "=r"(r[26]), "=r"(r[27]),
+        "=r"(r[28]), "=r"(r[29]), "=r"(r[30]), "=r"(r[31])
+      : "r"(taddr));
+}
+__device__ __forceinline__ void tmem_ld_wait() {
+  asm volatile("tcgen05.wait::ld.sync.aligned;" ::: "memory");
+}
+
+// Shared-memory matrix descriptor.
+//   K-major tile  [rows][BK] with a BK*2-byte swizzle: 8-row groups are 8*BK*2 bytes apart (SBO).
+//   MN-major tile [BK][64] with the 128-byte swizzle: 8 k-rows are 1024 bytes apart (SBO) and the
+//   next 64 elements along M/N start `lbo_bytes` later (LBO).
+__device__ __forceinline__ uint64_t make_desc(uint32_t saddr, uint32_t lbo_bytes, uint32_t sbo_bytes,
+                                              uint32_t layout_type) {
+  uint64_t d = 0;
+  d |= (uint64_t)((saddr >> 4) & 0x3fff);
+  d |= (uint64_t)((lbo_bytes >> 4) & 0x3fff) << 16;
+  d |= (uint64_t)((sbo_bytes >> 4) & 0x3fff) << 32;
+  d |= (uint64_t)1 << 46;                       // descriptor version of this architecture
+  d |= (uint64_t)layout_type << 61;             // 2 = 128-byte swizzle, 4 = 64-byte swizzle
+  return d;
+}
+
+struct GemmParams {
+  int M, N, K;
+  int BN;                 // tile width, multiple of 16, <= 256
+  int num_m, num_n, num_k;
+  int a_mn, b_mn;         // operand is MN-major
+  const float *bias;
+  float *C;
+  int64_t ldc;
+  int *status;
+};
+
+template <int P>
+struct Pairs;
+template <>
+struct Pairs<1> {
+  static constexpr int n = 1;
+  __device__ static constexpr int a(int) { return 0; }
+  __device__ static constexpr int b(int) { return 0; }
+};
+template <>
+struct Pairs<3> {
+  static constexpr int n = 6;
+  // smallest terms first, the leading product last
+  __device__ static constexpr int a(int i) { return i == 0 ? 2 : i == 1 ? 0 : i == 2 ? 1 : i == 3 ? 1 : i == 4 ? 0 : 0; }
+  __device__ static constexpr int b(int i) { return i == 0 ? 0 : i == 1 ? 2 : i == 2 ? 1 : i == 3 ? 0 : i == 4 ? 1 : 0; }
+};
+
+template <int P, int BK, int STAGES, int BN_CAP>
+struct SmemLayout {
+  static constexpr int kATile = BM * BK * 2;
+  static constexpr int kBTile = BN_CAP * BK * 2;
+  static constexpr int kStage = P * (kATile + kBTile);
+  static constexpr int kTiles = STAGES * kStage;
+  static constexpr int kBars = 8 * (2 * STAGES + 4);
+  static constexpr int kTotal = kTiles + kBars + 16 + 1024;   // + tmem slot/abort + alignment slack
+};
+
+template <int P, int BK, int STAGES, int BN_CAP>
+__global__ void __launch_bounds__(kThreads, 1)
+gemm_tc_kernel(const __grid_constant__ CUtensorMap map_a, const __grid_constant__ CUtensorMap map_b,
+               const GemmParams p) {
+  using L = SmemLayout<P, BK, STAGES, BN_CAP>;
+  extern __shared__ uint8_t smem_raw[];
+  uint8_t *smem = reinterpret_cast<uint8_t *>((reinterpret_cast<uintptr_t>(smem_raw) + 1023) &
+                                              ~(uintptr_t)1023);
+  uint64_t *full = reinterpret_cast<uint64_t *>(smem + L::kTiles);
+  uint64_t *empty = full + STAGES;
+  uint64_t *tmem_full = empty + STAGES;
+  uint64_t *tmem_empty = tmem_full + 2;
+  uint32_t *tmem_slot = reinterpret_cast<uint32_t *>(tmem_empty + 2);
+  volatile int *abort_flag = reinterpret_cast<volatile int *>(tmem_slot + 1);
+
+  const int warp = threadIdx.x / 32, lane = threadIdx.x % 32;
+  const int num_tiles = p.num_m * p.num_n;
+
+  if (threadIdx.x == 0) {
+    for (int s = 0; s < STAGES; ++s) { mbar_init(&full[s], 1); mbar_init(&empty[s], 1); }
+    for (int b = 0; b < 2; ++b) { mbar_init(&tmem_full[b], 1); mbar_init(&tmem_empty[b], 4); }
+    *abort_flag = 0;
+    asm volatile("fence.mbarrier_init.release.cluster;" ::: "memory");
+    asm volatile("fence.proxy.async.shared::cta;" ::: "memory");
+  }
+  if (warp == 1) {
+    asm volatile("tcgen05.alloc.cta_group::1.sync.aligned.shared::cta.b32 [%0], %1;" ::"r"(
+                     smem_u32(tmem_slot)),
+                 "r"(512u)
+                 : "memory");
+    asm volatile("tcgen05.relinquish_alloc_permit.cta_group::1.sync.aligned;" ::: "memory");
+  }
+  tcgen05_fence_before();
+  __syncthreads();
+  tcgen05_fence_after();
+  const uint32_t tmem_base = *tmem_slot;
+
+  // byte extents of the operand tiles actually loaded for this launch
+  const uint32_t a_bytes = BM * BK * 2;
+  const uint32_t b_bytes = (uint32_t)p.BN * BK * 2;
+
+  if (warp == 0) {
+    // ---------------------------------------------------------------- TMA producer
+    if (elect_one()) {
+      uint32_t it = 0;
+      bool ok = true;
+      for (int tile = blockIdx.x; tile < num_tiles && ok; tile += gridDim.x) {
+        const int m0 = (tile / p.num_n) * BM, n0 = (tile % p.num_n) * p.BN;
+        for (int kb = 0; kb < p.num_k && ok; ++kb, ++it) {
+          const int s = it % STAGES;
+          const uint32_t ph = (it / STAGES) & 1;
+          ok = mbar_wait(&empty[s], ph ^ 1, abort_flag, p.status);
+          if (!ok) break;
+          uint8_t *st = smem + (size_t)s * L::kStage;
+          mbar_expect_tx(&full[s], P * (a_bytes + b_bytes));
+          const int k0 = kb * BK;
+#pragma unroll
+          for (int pl = 0; pl < P; ++pl) {
+            uint8_t *ta = st + pl * L::kATile, *tb = st + P * L::kATile + pl * L::kBTile;
+            if (!p.a_mn) {
+              tma_load_3d(ta, &map_a, &full[s], k0, m0, pl);
+            } else {                      // two 64-wide column blocks of [BK][64]
+              tma_load_3d(ta, &map_a, &full[s], m0, k0, pl);
+              tma_load_3d(ta + BK * 128, &map_a, &full[s], m0 + 64, k0, pl);
+            }
+            if (!p.b_mn) {
+              tma_load_3d(tb, &map_b, &full[s], k0, n0, pl);
+            } else {
+              for (int nb = 0; nb < p.BN; nb += 64)
+                tma_load_3d(tb + (nb / 64) * BK * 128, &map_b, &full[s], n0 + nb, k0, pl);
+            }
+          }
+        }
+      }
+    }
+  } else if (warp == 1) {
+    // ---------------------------------------------------------------- MMA issuer
+    if (elect_one()) {
+      const uint32_t idesc = (1u << 4) | (1u << 7) | (1u << 10) | ((uint32_t)(p.a_mn ? 1 : 0) << 15) |
+                             ((uint32_t)(p.b_mn ? 1 : 0) << 16) | ((uint32_t)(p.BN >> 3) << 17) |
+                             ((uint32_t)(BM >> 4) << 24);
+      constexpr uint32_t kLayout = BK == 64 ? 2u : 4u;
+      uint32_t it = 0, local = 0;
+      bool ok = true;
+      for (int tile = blockIdx.x; tile < num_tiles && ok; tile += gridDim.x, ++local) {
+        const int buf = local & 1;
+        ok = mbar_wait(&tmem_empty[buf], ((local >> 1) & 1) ^ 1, abort_flag, p.status);
+        if (!ok) break;
+        tcgen05_fence_after();
+        const uint32_t d_tmem = tmem_base + (uint32_t)buf * kTmemBuf;
+        for (int kb = 0; kb < p.num_k && ok; ++kb, ++it) {
+          const int s = it % STAGES;
+          ok = mbar_wait(&full[s], (it / STAGES) & 1, abort_flag, p.status);
+          if (!ok) break;
+          tcgen05_fence_after();
+          const uint32_t sa = smem_u32(smem + (size_t)s * L::kStage);
+          const uint32_t sb = sa + P * L::kATile;
+#pragma unroll
+          for (int ks = 0; ks < BK / 16; ++ks) {
+#pragma unroll
+            for (int q = 0; q < Pairs<P>::n; ++q) {
+              const uint32_t ta = sa + Pairs<P>::a(q) * L::kATile;
+              const uint32_t tb = sb + Pairs<P>::b(q) * L::kBTile;
+              // K-major: 32 bytes along the swizzled row per k-step of 16
+              // MN-major: 16 k-rows of 128 bytes per k-step
+              const uint64_t da = p.a_mn ? make_desc(ta + ks * 2048, BK * 128, 1024, 2u)
+                                         : make_desc(ta + ks * 32, 16, 8 * BK * 2, kLayout);
+              const uint64_t db = p.b_mn ? make_desc(tb + ks * 2048, BK * 128, 1024, 2u)
+                                         : make_desc(tb + ks * 32, 16, 8 * BK * 2, kLayout);
+              umma_bf16(d_tmem, da, db, idesc, (kb | ks | q) != 0 ? 1u : 0u);
+            }
+          }
+          tcgen05_commit(&empty[s]);            // stage reusable once these MMAs have read it
+        }
+        if (ok) tcgen05_commit(&tmem_full[buf]);
+      }
+    }
+  } else {
+    // ---------------------------------------------------------------- epilogue (warps 2..5)
+    const int q = warp & 3;                     // TMEM lane quarter this warp may read
+    uint32_t local = 0;
+    bool ok = true;
+    for (int tile = blockIdx.x; tile < num_tiles && ok; tile += gridDim.x, ++local) {
+      const int buf = local & 1;
+      const int m0 = (tile / p.num_n) * BM, n0 = (tile % p.num_n) * p.BN;
+      ok = mbar_wait(&tmem_full[buf], (local >> 1) & 1, abort_flag, p.status);
+      ok = __all_sync(0xffffffffu, ok);
+      if (!ok) break;
+      tcgen05_fence_after();
+      const int row = m0 + q * 32 + lane;
+      float *crow = p.C + (size_t)row * p.ldc;
+      const uint32_t t_row = tmem_base + ((uint32_t)(q * 32) << 16) + (uint32_t)buf * kTmemBuf;
+      for (int c0 = 0; c0 < p.BN; c0 += 32) {
+        uint32_t r[32];
+        tmem_ld32(t_row + c0, r);
+        tmem_ld_wait();
+        if (row < p.M) {
+#pragma unroll
+          for (int j = 0; j < 32; j += 4) {
+            const int n = n0 + c0 + j;
+            if (c0 + j < p.BN && n + 3 < p.N) {
+              float4 v = make_float4(__uint_as_float(r[j]), __uint_as_float(r[j + 1]),
+                                     __uint_as_float(r[j + 2]), __uint_as_float(r[j + 3]));
+              if (p.bias) {
+                const float4 bv = *reinterpret_cast<const float4 *>(p.bias + n);
+                v.x += bv.x; v.y += bv.y; v.z += bv.z; v.w += bv.w;
+              }
+              *reinterpret_cast<float4 *>(crow + n) = v;
+            } else if (c0 + j < p.BN) {
+#pragma unroll
+              for (int u = 0; u < 4; ++u)
+                if (n + u < p.N) crow[n + u] = __uint_as_float(r[j + u]) + (p.bias ? p.bias[n + u] : 0.f);
+            }
+          }
+        }
+      }
+      tcgen05_fence_before();
+      __syncwarp();
+      if (lane == 0) mbar_arrive(&tmem_empty[buf]);
+    }
+  }
+
+  tcgen05_fence_before();
+  __syncthreads();
+  if (warp == 1) {
+    tcgen05_fence_after();
+    asm volatile("tcgen05.dealloc.cta_group::1.sync.aligned.b32 %0, %1;" ::"r"(tmem_base), "r"(512u)
+                 : "memory");
+  }
+}
+
+// ---- host side ---------------------------------------------------------------------------
+
+typedef CUresult (*EncodeTiledFn)(CUtensorMap *, CUtensorMapDataType, cuuint32_t, void *,
+                                  const cuuint64_t *, const cuuint64_t *, const cuuint32_t *,
+                                  const cuuint32_t *, CUtensorMapInterleave, CUtensorMapSwizzle,
+                                  CUtensorMapL2promotion, CUtensorMapFloatOOBfill);
+
+EncodeTiledFn encode_fn() {
+  static EncodeTiledFn fn = nullptr;
+  if (!fn) {
+    void *ptr = nullptr;
+    cudaDriverEntryPointQueryResult qres;
+    if (cudaGetDriverEntryPoint("cuTensorMapEncodeTiled", &ptr, cudaEnableDefault, &qres) ==
+            cudaSuccess &&
+        qres == cudaDriverEntryPointSuccess)
+      fn = reinterpret_cast<EncodeTiledFn>(ptr);
+  }
+  return fn;
+}
+
+// 3-d map over (inner, outer, plane) of a bf16 operand
+int make_map(CUtensorMap *map, const void *base, uint64_t inner, uint64_t outer, uint64_t planes,
+             uint64_t ld, uint64_t plane_stride, uint32_t box_inner, uint32_t box_outer,
+             CUtensorMapSwizzle swz) {
+  EncodeTiledFn fn = encode_fn();
+  if (!fn) return ZP_ERR_CUDA;
+  const cuuint64_t dims[3] = {inner, outer, planes};
+  const cuuint64_t strides[2] = {ld * 2, plane_stride * 2};
+  const cuuint32_t box[3] = {box_inner, box_outer, 1};
+  const cuuint32_t estr[3] = {1, 1, 1};
+  const CUresult r = fn(map, CU_TENSOR_MAP_DATA_TYPE_BFLOAT16, 3, const_cast<void *>(base), dims,
+                        strides, box, estr, CU_TENSOR_MAP_INTERLEAVE_NONE, swz,
+                        CU_TENSOR_MAP_L2_PROMOTION_L2_256B, CU_TENSOR_MAP_FLOAT_OOB_FILL_NONE);
+  if (r != CUDA_SUCCESS) {
+    zp_set_cuda_error(cudaErrorInvalidValue, "cuTensorMapEncodeTiled");
+    return ZP_ERR_CUDA;
+  }
+  return ZP_OK;
+}
+
+int pick_bn(int64_t N, int cap) {
+  const int64_t tiles = zp_ceil_div(N, cap);
+  int64_t bn = zp_ceil_div(zp_ceil_div(N, tiles), 16) * 16;
+  if (bn < 16) bn = 16;
+  return (int)bn;
+}
+
+template <int P, int BK, int STAGES, int BN_CAP>
+int launch(const ZpGemmTc &g, cudaStream_t st) {
+  using L = SmemLayout<P, BK, STAGES, BN_CAP>;
+  static_assert(L::kTotal <= 232448, "shared memory budget of one CTA");
+  static bool configured = false;
+  if (!configured) {
+    ZP_CUDA(cudaFuncSetAttribute(gemm_tc_kernel<P, BK, STAGES, BN_CAP>,
+                                 cudaFuncAttributeMaxDynamicSharedMemorySize, L::kTotal));
+    configured = true;
+  }
+  GemmParams p;
+  p.M = (int)g.M; p.N = (int)g.N; p.K = (int)g.K;
+  p.BN = pick_bn(g.N, BN_CAP);
+  if (g.b_mn) p.BN = (p.BN + 63) / 64 * 64;       // MN-major B tiles come in 64-wide blocks
+  p.num_m = (int)zp_ceil_div(g.M, BM);
+  p.num_n = (int)zp_ceil_div(g.N, p.BN);
+  p.num_k = (int)zp_ceil_div(g.K, BK);
+  p.a_mn = g.a_mn; p.b_mn = g.b_mn;
+  p.bias = g.bias; p.C = g.C; p.ldc = g.ldc; p.status = g.status;
+  const CUtensorMapSwizzle kswz = BK == 64 ? CU_TENSOR_MAP_SWIZZLE_128B : CU_TENSOR_MAP_SWIZZLE_64B;
+  CUtensorMap ma, mb;
+  int rc;
+  if (!g.a_mn) rc = make_map(&ma, g.A, g.K, g.M, P, g.lda, g.a_plane, BK, BM, kswz);
+  else rc = make_map(&ma, g.A, g.M, g.K, P, g.lda, g.a_plane, 64, BK, CU_TENSOR_MAP_SWIZZLE_128B);
+  if (rc) return rc;
+  if (!g.b_mn) rc = make_map(&mb, g.B, g.K, g.N, P, g.ldb, g.b_plane, BK, p.BN, kswz);
+  else rc = make_map(&mb, g.B, g.N, g.K, P, g.ldb, g.b_plane, 64, BK, CU_TENSOR_MAP_SWIZZLE_128B);
+  if (rc) return rc;
+  int dev = 0, sms = 148;
+  cudaGetDevice(&dev);
+  cudaDeviceGetAttribute(&sms, cudaDevAttrMultiProcessorCount, dev);
+  const int tiles = p.num_m * p.num_n;
+  const int grid = tiles < sms ? tiles : sms;
+  gemm_tc_kernel<P, BK, STAGES, BN_CAP><<<grid, kThreads, L::kTotal, st>>>(ma, mb, p);
+  ZP_LAUNCH_CHECK("gemm_tc_kernel");
+  return ZP_OK;
+}
+
+}  // namespace
+
+int zp_launch_gemm_tc(const ZpGemmTc &g, cudaStream_t st) {
+  if (g.M <= 0 || g.N <= 0) return ZP_OK;
+  if (g.K <= 0) return ZP_ERR_INVALID_ARG;
+  if ((g.lda % 8) || (g.ldb % 8) || (g.a_plane % 8) || (g.b_plane % 8) || (g.ldc % 4))
+    return ZP_ERR_INVALID_ARG;
+  if ((reinterpret_cast<uintptr_t>(g.A) | reinterpret_cast<uintptr_t>(g.B) |
+       reinterpret_cast<uintptr_t>(g.C)) & 15)
+    return ZP_ERR_INVALID_ARG;
+  if (g.a_mn || g.b_mn) {
+    // MN-major tiles are [BK = 64][64] blocks under the 128-byte swizzle
+    if (g.planes == 3) return launch<3, 64, 2, 128>(g, st);
+    if (g.planes == 1) return launch<1, 64, 4, 256>(g, st);
+    return ZP_ERR_UNSUPPORTED;
+  }
+  if (g.planes == 3)
+    return g.variant == 1 ? launch<3, 64, 2, 128>(g, st) : launch<3, 32, 3, 256>(g, st);
+  if (g.planes == 1) return launch<1, 64, 4, 256>(g, st);
+  return ZP_ERR_UNSUPPORTED;
+}

@@ -164,13 +164,18 @@ int zp_eso2_backward(const zp_plan *plan, int64_t n_nodes, int64_t n_edges,
  * plane p-1; columns cols..ld_out-1 are zero.  zp_gemm_planes computes, on the tensor cores,
  *   C[M, N] = sum over plane pairs  A_pa  B_pb^T  (+ bias[n]),   fp32 output, row stride ldc,
  * for K-major operands X[p*plane + r*ld + k] or, with a_mn / b_mn = 1, MN-major operands
- * X[p*plane + k*ld + r].  ld, plane strides: multiples of 8; ldc: multiple of 4.            */
+ * X[p*plane + k*ld + r].  ld, plane strides: multiples of 8; ldc: multiple of 4.
+ * The contraction is accumulated in TMEM in chunks of kc_elems (0 = 2048) and the chunks are
+ * summed in fp32; ksplit > 1 additionally splits it over CTAs, split s writing its partial
+ * matrix at C + s*split_stride (the number actually written is returned in *splits_out and
+ * never exceeds ksplit; the caller sums them).  variant selects a tile shape (0 = default).  */
 int zp_split_planes(int64_t rows, int64_t cols, const float *in, int64_t ld_in, void *out,
                     int64_t ld_out, int64_t plane_stride, int planes, void *stream);
 int zp_gemm_planes(zp_plan *plan, int64_t M, int64_t N, int64_t K, int planes, const void *A,
                    int64_t lda, int64_t a_plane, int a_mn, const void *B, int64_t ldb,
                    int64_t b_plane, int b_mn, const float *bias, float *C, int64_t ldc,
-                   int variant, void *stream);
+                   int variant, int ksplit, int64_t split_stride, int kc_elems, int *splits_out,
+                   void *stream);
 /* Reads (synchronously) and clears the plan's device status word: ZP_OK, or
  * ZP_ERR_DEVICE_TIMEOUT if a bounded device-side wait gave up since the last read.          */
 int zp_plan_device_status(zp_plan *plan, int *status_out);

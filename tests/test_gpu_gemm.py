@@ -1,0 +1,96 @@
+"""The tensor-core contraction engine on its own (zp_gemm_planes through the C ABI) against
+fp64 products of the same inputs.  Tolerances: with three planes the result must match the
+fp32 x fp32 product to 4e-6 relative L2 (the engine's own budget inside the 1e-5 block
+tolerance); with one plane it must match the product of the bf16-rounded operands to 4e-6."""
+
+from __future__ import annotations
+
+import ctypes
+
+import pytest
+import torch
+
+pytestmark = pytest.mark.gpu
+
+
+def run_gemm(M, N, K, planes, a_mn, b_mn, variant=0, ksplit=1, kc=0, bias=True, seed=0):
+    from zippel_b200 import _lib
+    from zippel_b200.blocks.eso2 import Plan
+    lib, plan = _lib.load(), Plan.get(2, 2, 8, 8, "cuda")
+    g = torch.Generator("cpu").manual_seed(seed)
+    A = torch.randn(M, K, generator=g)
+    B = torch.randn(N, K, generator=g) * 0.1
+    bvec = torch.randn(N, generator=g) if bias else None
+
+    def planes_of(X, mn):
+        Xs = (X.t() if mn else X).contiguous().cuda()
+        rows, cols = Xs.shape
+        ld = (cols + 7) // 8 * 8
+        out = torch.zeros(planes, rows, ld, dtype=torch.bfloat16, device="cuda")
+        _lib.check(lib.zp_split_planes(rows, cols, Xs.data_ptr(), cols, out.data_ptr(), ld,
+                                       rows * ld, planes, None), "zp_split_planes")
+        return out, ld, rows * ld
+
+    Ap, lda, aps = planes_of(A, a_mn)
+    Bp, ldb, bps = planes_of(B, b_mn)
+    ldc = (N + 3) // 4 * 4
+    C = torch.full((max(ksplit, 1), M, ldc), float("nan"), device="cuda")
+    bd = bvec.cuda() if bias else None
+    used = ctypes.c_int(0)
+    st = torch.cuda.current_stream().cuda_stream
+    _lib.check(lib.zp_gemm_planes(plan.handle, M, N, K, planes, Ap.data_ptr(), lda, aps, int(a_mn),
+                                  Bp.data_ptr(), ldb, bps, int(b_mn),
+                                  bd.data_ptr() if bias else None, C.data_ptr(), ldc, variant,
+                                  ksplit, M * ldc, kc, ctypes.byref(used), st), "zp_gemm_planes")
+    torch.cuda.synchronize()
+    stat = ctypes.c_int(0)
+    _lib.check(lib.zp_plan_device_status(plan.handle, ctypes.byref(stat)), "status")
+    assert stat.value == 0
+    assert 1 <= used.value <= max(ksplit, 1)
+    got = C[:used.value, :, :N].double().sum(0).cpu()
+    Ar = Ap.double().sum(0).cpu()
+    Br = Bp.double().sum(0).cpu()
+    Ar = Ar[:, :M].t() if a_mn else Ar[:, :K]
+    Br = Br[:, :N].t() if b_mn else Br[:, :K]
+    ref_planes = Ar[:M, :K] @ Br[:N, :K].t() + (bvec.double() if bias else 0)
+    ref_fp32 = A.double() @ B.double().t() + (bvec.double() if bias else 0)
+    rel = lambda x, y: ((x - y).norm() / y.norm()).item()  # noqa: E731
+    return rel(got, ref_planes), rel(got, ref_fp32)
+
+
+SHAPES = [(128, 128, 64), (300, 200, 100), (1000, 1152, 1280), (129, 20, 24), (77, 640, 2048)]
+
+
+@pytest.mark.parametrize("M,N,K", SHAPES)
+@pytest.mark.parametrize("variant", [0, 1])
+def test_three_planes_k_major(M, N, K, variant):
+    _, err = run_gemm(M, N, K, 3, False, False, variant=variant)
+    assert err < 4e-6
+
+
+@pytest.mark.parametrize("M,N,K", SHAPES)
+def test_one_plane_k_major(M, N, K):
+    err, _ = run_gemm(M, N, K, 1, False, False)
+    assert err < 4e-6
+
+
+@pytest.mark.parametrize("planes", [1, 3])
+@pytest.mark.parametrize("M,N,K", [(128, 128, 64), (256, 192, 200), (1152, 1280, 5000), (24, 40, 333)])
+def test_mn_major_operands(M, N, K, planes):
+    err_p, err_f = run_gemm(M, N, K, planes, True, True)
+    assert (err_f if planes == 3 else err_p) < 4e-6
+
+
+def test_mixed_majors():
+    assert run_gemm(300, 256, 512, 3, True, False, variant=1)[1] < 4e-6
+    assert run_gemm(300, 256, 512, 3, False, True, variant=1)[1] < 4e-6
+
+
+@pytest.mark.parametrize("planes", [1, 3])
+def test_long_contraction_chunks_and_splits(planes):
+    """Contraction over 60 000 'edges' as in the weight gradients: chunked TMEM accumulation plus
+    a split over CTAs must hold the tolerance that a single running accumulator cannot."""
+    err_p, err_f = run_gemm(640, 512, 60000, planes, True, True, ksplit=4, bias=False)
+    assert (err_f if planes == 3 else err_p) < 4e-6
+    err_p, err_f = run_gemm(256, 256, 9000, planes, False, False, ksplit=3, kc=512, bias=True)
+    assert (err_f if planes == 3 else err_p) < 4e-6

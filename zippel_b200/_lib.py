@@ -58,7 +58,8 @@ SIGNATURES = {
                          + [_P] * 4 + [C.POINTER(ZpWeights), _P, _SZ, _P]),
     "zp_split_planes": (C.c_int, [_I64, _I64, _P, _I64, _P, _I64, _I64, C.c_int, _P]),
     "zp_gemm_planes": (C.c_int, [_P, _I64, _I64, _I64, C.c_int, _P, _I64, _I64, C.c_int, _P, _I64,
-                                 _I64, C.c_int, _P, _P, _I64, C.c_int, _P]),
+                                 _I64, C.c_int, _P, _P, _I64, C.c_int, C.c_int, _I64, C.c_int,
+                                 C.POINTER(C.c_int), _P]),
     "zp_plan_device_status": (C.c_int, [_P, C.POINTER(C.c_int)]),
     "zp_kernel_class_name": (C.c_char_p, [C.c_int]),
     "zp_timing_enable": (C.c_int, [_P, C.c_int]),

@@ -295,10 +295,12 @@ int zp_split_planes(int64_t rows, int64_t cols, const float *in, int64_t ld_in, 
 int zp_gemm_planes(zp_plan *plan, int64_t M, int64_t N, int64_t K, int planes, const void *A,
                    int64_t lda, int64_t a_plane, int a_mn, const void *B, int64_t ldb,
                    int64_t b_plane, int b_mn, const float *bias, float *C, int64_t ldc,
-                   int variant, void *stream) {
+                   int variant, int ksplit, int64_t split_stride, int kc_elems, int *splits_out,
+                   void *stream) {
   if (!plan || !A || !B || !C || M < 0 || N < 0 || K <= 0) return ZP_ERR_INVALID_ARG;
   ZpGemmTc g{M, N, K, planes, A, lda, a_plane, a_mn, B, ldb, b_plane, b_mn, bias, C, ldc,
-             plan->status_dev, variant};
+             plan->status_dev, variant, ksplit, split_stride, kc_elems};
+  if (splits_out) *splits_out = zp_gemm_tc_splits(g);
   return zp_launch_gemm_tc(g, (cudaStream_t)stream);
 }
 

@@ -131,8 +131,13 @@ struct ZpGemmTc {
   float *C; int64_t ldc;
   int *status;                                  // device word, set on a device-side timeout
   int variant;                                  // tile-shape choice for the 3-plane K-major case
+  int ksplit;                                   // requested split of K over CTAs (>= 1)
+  int64_t split_stride;                         // elements between the partial outputs of splits
+  int kc_elems;                                 // K per TMEM accumulation chunk (0 = 2048)
 };
 int zp_launch_gemm_tc(const ZpGemmTc &g, cudaStream_t st);
+// number of partial outputs the launch above will write for this problem (<= g.ksplit)
+int zp_gemm_tc_splits(const ZpGemmTc &g);
 // fp32 [rows, cols] (row stride ld_in) -> `planes` bf16 planes [rows, ld_out]
 int zp_launch_split_planes(int64_t rows, int64_t cols, const float *in, int64_t ld_in, void *out,
                            int64_t ld_out, int64_t plane_stride, int planes, cudaStream_t st);

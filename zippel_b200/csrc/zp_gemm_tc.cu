@@ -6,16 +6,28 @@
 // accumulation.  With three planes an fp32 value x is carried as x = x0 + x1 + x2 (each a
 // bf16, x0 = rn(x), x1 = rn(x - x0), x2 = rn(x - x0 - x1)), and the six products
 //     A0B0, A0B1, A1B0, A1B1, A0B2, A2B0
-// (everything down to 2^-16 of the leading term) accumulate into the same TMEM tile, which
-// reproduces the fp32 product to ~2^-22 while staying on the bf16 pipe and keeping fp32's
-// exponent range.  All planes of a k-block are loaded once and reused by the six MMAs.
+// (everything down to 2^-16 of the leading term) reproduce the fp32 product to ~2^-22 while
+// staying on the bf16 pipe and keeping fp32's exponent range.  All planes of a k-block are
+// loaded once and reused by the six MMAs.
+//
+// Accumulation accuracy.  The tensor core adds each k = 16 step into the fp32 accumulator with
+// truncation, a bias of about 3e-8 of the accumulator per step (measured: relative error
+// ~1e-9 * K for one product, 6.5e-9 * K when all six share an accumulator).  Two measures keep
+// that below the fp32 budget: (1) the leading product A0B0 has its own TMEM accumulator and the
+// five small products share a second one, whose truncation is 2^-8 smaller in absolute terms;
+// (2) the contraction is cut into chunks of at most `kc` k-blocks, each accumulated in TMEM
+// from zero and then added to C in fp32 by the epilogue (first chunk stores, later chunks
+// add), so the bias never grows beyond one chunk's length.  Long contractions (the weight
+// gradients, which run over all edges) can also be split over CTAs: split s writes its own
+// partial matrix C + s * split_stride, reduced afterwards in a fixed order.
 //
 // Structure: persistent CTAs (one per SM), 192 threads.
 //   warp 0      TMA producer: one elected lane streams A/B plane tiles into a ring of stages
 //   warp 1      allocates TMEM, then one elected lane issues tcgen05.mma and commits
 //   warps 2..5  epilogue: tcgen05.ld the 128 x BN accumulator, add bias, store fp32 rows
-// Two TMEM accumulators (2 x 256 columns) let the epilogue of tile i overlap the main loop of
-// tile i+1.  Tiles are ordered n-fastest so CTAs running side by side share one A row block
+// With one plane two TMEM accumulators (2 x 256 columns) let the epilogue of one tile overlap
+// the main loop of the next; with three planes the 512 columns hold the leading and the small
+// accumulator of one tile.  Tiles are ordered n-fastest so CTAs running side by side share one A row block
 // (read from HBM once, then L2) while the weights stay L2 resident.
 //
 // Operand layouts in global memory (element strides, all multiples of 8 so TMA rows are 16-byte
@@ -170,27 +182,25 @@ struct GemmParams {
   int M, N, K;
   int BN;                 // tile width, multiple of 16, <= 256
   int num_m, num_n, num_k;
+  int ksplit, kb_per_split, kc;   // CTAs-level split of K; k-blocks per TMEM accumulation chunk
   int a_mn, b_mn;         // operand is MN-major
   const float *bias;
   float *C;
-  int64_t ldc;
+  int64_t ldc, split_stride;
   int *status;
 };
 
-template <int P>
-struct Pairs;
-template <>
-struct Pairs<1> {
+// plane pairs; for three planes pair 0 is the leading product, pairs 1..5 the small ones
+template <int P> struct Pairs;
+template <> struct Pairs<1> {
   static constexpr int n = 1;
   __device__ static constexpr int a(int) { return 0; }
   __device__ static constexpr int b(int) { return 0; }
 };
-template <>
-struct Pairs<3> {
+template <> struct Pairs<3> {
   static constexpr int n = 6;
-  // smallest terms first, the leading product last
-  __device__ static constexpr int a(int i) { return i == 0 ? 2 : i == 1 ? 0 : i == 2 ? 1 : i == 3 ? 1 : i == 4 ? 0 : 0; }
-  __device__ static constexpr int b(int i) { return i == 0 ? 0 : i == 1 ? 2 : i == 2 ? 1 : i == 3 ? 0 : i == 4 ? 1 : 0; }
+  __device__ static constexpr int a(int i) { return i == 0 ? 0 : i == 1 ? 2 : i == 2 ? 0 : i == 3 ? 1 : i == 4 ? 1 : 0; }
+  __device__ static constexpr int b(int i) { return i == 0 ? 0 : i == 1 ? 0 : i == 2 ? 2 : i == 3 ? 1 : i == 4 ? 0 : 1; }
 };
 
 template <int P, int BK, int STAGES, int BN_CAP>
@@ -203,11 +213,27 @@ struct SmemLayout {
   static constexpr int kTotal = kTiles + kBars + 16 + 1024;   // + tmem slot/abort + alignment slack
 };
 
+// One unit of work of a CTA: an output tile, a K split, and its k-block range.
+struct Work {
+  int m0, n0, split, kb0, kb1;
+};
+__device__ __forceinline__ Work decode_work(const GemmParams &p, int w) {
+  Work x;
+  x.split = w % p.ksplit;
+  const int tile = w / p.ksplit;
+  x.m0 = (tile / p.num_n) * BM;
+  x.n0 = (tile % p.num_n) * p.BN;
+  x.kb0 = x.split * p.kb_per_split;
+  x.kb1 = min(p.num_k, x.kb0 + p.kb_per_split);
+  return x;
+}
+
 template <int P, int BK, int STAGES, int BN_CAP>
 __global__ void __launch_bounds__(kThreads, 1)
 gemm_tc_kernel(const __grid_constant__ CUtensorMap map_a, const __grid_constant__ CUtensorMap map_b,
                const GemmParams p) {
   using L = SmemLayout<P, BK, STAGES, BN_CAP>;
+  constexpr int kAccBufs = P == 1 ? 2 : 1;      // accumulation units in flight in TMEM
   extern __shared__ uint8_t smem_raw[];
   uint8_t *smem = reinterpret_cast<uint8_t *>((reinterpret_cast<uintptr_t>(smem_raw) + 1023) &
                                               ~(uintptr_t)1023);
@@ -219,7 +245,7 @@ gemm_tc_kernel(const __grid_constant__ CUtensorMap map_a, const __grid_constant_
   volatile int *abort_flag = reinterpret_cast<volatile int *>(tmem_slot + 1);
 
   const int warp = threadIdx.x / 32, lane = threadIdx.x % 32;
-  const int num_tiles = p.num_m * p.num_n;
+  const int num_work = p.num_m * p.num_n * p.ksplit;
 
   if (threadIdx.x == 0) {
     for (int s = 0; s < STAGES; ++s) { mbar_init(&full[s], 1); mbar_init(&empty[s], 1); }
@@ -240,7 +266,6 @@ gemm_tc_kernel(const __grid_constant__ CUtensorMap map_a, const __grid_constant_
   tcgen05_fence_after();
   const uint32_t tmem_base = *tmem_slot;
 
-  // byte extents of the operand tiles actually loaded for this launch
   const uint32_t a_bytes = BM * BK * 2;
   const uint32_t b_bytes = (uint32_t)p.BN * BK * 2;
 
@@ -249,12 +274,11 @@ gemm_tc_kernel(const __grid_constant__ CUtensorMap map_a, const __grid_constant_
     if (elect_one()) {
       uint32_t it = 0;
       bool ok = true;
-      for (int tile = blockIdx.x; tile < num_tiles && ok; tile += gridDim.x) {
-        const int m0 = (tile / p.num_n) * BM, n0 = (tile % p.num_n) * p.BN;
-        for (int kb = 0; kb < p.num_k && ok; ++kb, ++it) {
+      for (int w = blockIdx.x; w < num_work && ok; w += gridDim.x) {
+        const Work x = decode_work(p, w);
+        for (int kb = x.kb0; kb < x.kb1 && ok; ++kb, ++it) {
           const int s = it % STAGES;
-          const uint32_t ph = (it / STAGES) & 1;
-          ok = mbar_wait(&empty[s], ph ^ 1, abort_flag, p.status);
+          ok = mbar_wait(&empty[s], ((it / STAGES) & 1) ^ 1, abort_flag, p.status);
           if (!ok) break;
           uint8_t *st = smem + (size_t)s * L::kStage;
           mbar_expect_tx(&full[s], P * (a_bytes + b_bytes));
@@ -263,16 +287,16 @@ gemm_tc_kernel(const __grid_constant__ CUtensorMap map_a, const __grid_constant_
           for (int pl = 0; pl < P; ++pl) {
             uint8_t *ta = st + pl * L::kATile, *tb = st + P * L::kATile + pl * L::kBTile;
             if (!p.a_mn) {
-              tma_load_3d(ta, &map_a, &full[s], k0, m0, pl);
+              tma_load_3d(ta, &map_a, &full[s], k0, x.m0, pl);
             } else {                      // two 64-wide column blocks of [BK][64]
-              tma_load_3d(ta, &map_a, &full[s], m0, k0, pl);
-              tma_load_3d(ta + BK * 128, &map_a, &full[s], m0 + 64, k0, pl);
+              tma_load_3d(ta, &map_a, &full[s], x.m0, k0, pl);
+              tma_load_3d(ta + BK * 128, &map_a, &full[s], x.m0 + 64, k0, pl);
             }
             if (!p.b_mn) {
-              tma_load_3d(tb, &map_b, &full[s], k0, n0, pl);
+              tma_load_3d(tb, &map_b, &full[s], k0, x.n0, pl);
             } else {
               for (int nb = 0; nb < p.BN; nb += 64)
-                tma_load_3d(tb + (nb / 64) * BK * 128, &map_b, &full[s], n0 + nb, k0, pl);
+                tma_load_3d(tb + (nb / 64) * BK * 128, &map_b, &full[s], x.n0 + nb, k0, pl);
             }
           }
         }
@@ -285,83 +309,113 @@ gemm_tc_kernel(const __grid_constant__ CUtensorMap map_a, const __grid_constant_
                              ((uint32_t)(p.b_mn ? 1 : 0) << 16) | ((uint32_t)(p.BN >> 3) << 17) |
                              ((uint32_t)(BM >> 4) << 24);
       constexpr uint32_t kLayout = BK == 64 ? 2u : 4u;
-      uint32_t it = 0, local = 0;
+      uint32_t it = 0, unit = 0;
       bool ok = true;
-      for (int tile = blockIdx.x; tile < num_tiles && ok; tile += gridDim.x, ++local) {
-        const int buf = local & 1;
-        ok = mbar_wait(&tmem_empty[buf], ((local >> 1) & 1) ^ 1, abort_flag, p.status);
-        if (!ok) break;
-        tcgen05_fence_after();
-        const uint32_t d_tmem = tmem_base + (uint32_t)buf * kTmemBuf;
-        for (int kb = 0; kb < p.num_k && ok; ++kb, ++it) {
-          const int s = it % STAGES;
-          ok = mbar_wait(&full[s], (it / STAGES) & 1, abort_flag, p.status);
+      for (int w = blockIdx.x; w < num_work && ok; w += gridDim.x) {
+        const Work x = decode_work(p, w);
+        for (int c0 = x.kb0; c0 < x.kb1 && ok; c0 += p.kc, ++unit) {
+          const int c1 = min(x.kb1, c0 + p.kc);
+          const int buf = unit % kAccBufs;
+          ok = mbar_wait(&tmem_empty[buf], ((unit / kAccBufs) & 1) ^ 1, abort_flag, p.status);
           if (!ok) break;
           tcgen05_fence_after();
-          const uint32_t sa = smem_u32(smem + (size_t)s * L::kStage);
-          const uint32_t sb = sa + P * L::kATile;
+          // one plane: accumulator `buf`; three planes: leading product at column 0, small at 256
+          const uint32_t d_main = tmem_base + (P == 1 ? (uint32_t)buf * kTmemBuf : 0u);
+          const uint32_t d_small = tmem_base + kTmemBuf;
+          for (int kb = c0; kb < c1 && ok; ++kb, ++it) {
+            const int s = it % STAGES;
+            ok = mbar_wait(&full[s], (it / STAGES) & 1, abort_flag, p.status);
+            if (!ok) break;
+            tcgen05_fence_after();
+            const uint32_t sa = smem_u32(smem + (size_t)s * L::kStage);
+            const uint32_t sb = sa + P * L::kATile;
 #pragma unroll
-          for (int ks = 0; ks < BK / 16; ++ks) {
+            for (int ks = 0; ks < BK / 16; ++ks) {
 #pragma unroll
-            for (int q = 0; q < Pairs<P>::n; ++q) {
-              const uint32_t ta = sa + Pairs<P>::a(q) * L::kATile;
-              const uint32_t tb = sb + Pairs<P>::b(q) * L::kBTile;
-              // K-major: 32 bytes along the swizzled row per k-step of 16
-              // MN-major: 16 k-rows of 128 bytes per k-step
-              const uint64_t da = p.a_mn ? make_desc(ta + ks * 2048, BK * 128, 1024, 2u)
-                                         : make_desc(ta + ks * 32, 16, 8 * BK * 2, kLayout);
-              const uint64_t db = p.b_mn ? make_desc(tb + ks * 2048, BK * 128, 1024, 2u)
-                                         : make_desc(tb + ks * 32, 16, 8 * BK * 2, kLayout);
-              umma_bf16(d_tmem, da, db, idesc, (kb | ks | q) != 0 ? 1u : 0u);
+              for (int q = 0; q < Pairs<P>::n; ++q) {
+                const uint32_t ta = sa + Pairs<P>::a(q) * L::kATile;
+                const uint32_t tb = sb + Pairs<P>::b(q) * L::kBTile;
+                // K-major: 32 bytes along the swizzled row per k-step of 16
+                // MN-major: 16 k-rows of 128 bytes per k-step
+                const uint64_t da = p.a_mn ? make_desc(ta + ks * 2048, BK * 128, 1024, 2u)
+                                           : make_desc(ta + ks * 32, 16, 8 * BK * 2, kLayout);
+                const uint64_t db = p.b_mn ? make_desc(tb + ks * 2048, BK * 128, 1024, 2u)
+                                           : make_desc(tb + ks * 32, 16, 8 * BK * 2, kLayout);
+                const bool first_step = kb == c0 && ks == 0;
+                if (q == 0) umma_bf16(d_main, da, db, idesc, first_step ? 0u : 1u);
+                else umma_bf16(d_small, da, db, idesc, (first_step && q == 1) ? 0u : 1u);
+              }
             }
+            tcgen05_commit(&empty[s]);          // stage reusable once these MMAs have read it
           }
-          tcgen05_commit(&empty[s]);            // stage reusable once these MMAs have read it
+          if (ok) tcgen05_commit(&tmem_full[buf]);
         }
-        if (ok) tcgen05_commit(&tmem_full[buf]);
       }
     }
   } else {
     // ---------------------------------------------------------------- epilogue (warps 2..5)
     const int q = warp & 3;                     // TMEM lane quarter this warp may read
-    uint32_t local = 0;
+    uint32_t unit = 0;
     bool ok = true;
-    for (int tile = blockIdx.x; tile < num_tiles && ok; tile += gridDim.x, ++local) {
-      const int buf = local & 1;
-      const int m0 = (tile / p.num_n) * BM, n0 = (tile % p.num_n) * p.BN;
-      ok = mbar_wait(&tmem_full[buf], (local >> 1) & 1, abort_flag, p.status);
-      ok = __all_sync(0xffffffffu, ok);
-      if (!ok) break;
-      tcgen05_fence_after();
-      const int row = m0 + q * 32 + lane;
-      float *crow = p.C + (size_t)row * p.ldc;
-      const uint32_t t_row = tmem_base + ((uint32_t)(q * 32) << 16) + (uint32_t)buf * kTmemBuf;
-      for (int c0 = 0; c0 < p.BN; c0 += 32) {
-        uint32_t r[32];
-        tmem_ld32(t_row + c0, r);
-        tmem_ld_wait();
-        if (row < p.M) {
+    for (int w = blockIdx.x; w < num_work && ok; w += gridDim.x) {
+      const Work x = decode_work(p, w);
+      const int row = x.m0 + q * 32 + lane;
+      float *crow = p.C + (size_t)x.split * p.split_stride + (size_t)row * p.ldc;
+      const float *bias = x.split == 0 ? p.bias : nullptr;
+      for (int c0 = x.kb0; c0 < x.kb1 && ok; c0 += p.kc, ++unit) {
+        const int buf = unit % kAccBufs;
+        const bool first = c0 == x.kb0;         // first chunk stores, later chunks add
+        ok = mbar_wait(&tmem_full[buf], (unit / kAccBufs) & 1, abort_flag, p.status);
+        ok = __all_sync(0xffffffffu, ok);
+        if (!ok) break;
+        tcgen05_fence_after();
+        const uint32_t t_row = tmem_base + ((uint32_t)(q * 32) << 16) +
+                               (P == 1 ? (uint32_t)buf * kTmemBuf : 0u);
+        for (int cc = 0; cc < p.BN; cc += 32) {
+          uint32_t r[32];
+          tmem_ld32(t_row + cc, r);
+          if (P == 3) {
+            uint32_t r2[32];
+            tmem_ld32(t_row + kTmemBuf + cc, r2);
+            tmem_ld_wait();
 #pragma unroll
-          for (int j = 0; j < 32; j += 4) {
-            const int n = n0 + c0 + j;
-            if (c0 + j < p.BN && n + 3 < p.N) {
-              float4 v = make_float4(__uint_as_float(r[j]), __uint_as_float(r[j + 1]),
-                                     __uint_as_float(r[j + 2]), __uint_as_float(r[j + 3]));
-              if (p.bias) {
-                const float4 bv = *reinterpret_cast<const float4 *>(p.bias + n);
-                v.x += bv.x; v.y += bv.y; v.z += bv.z; v.w += bv.w;
+            for (int j = 0; j < 32; ++j)
+              r[j] = __float_as_uint(__uint_as_float(r[j]) + __uint_as_float(r2[j]));
+          } else {
+            tmem_ld_wait();
+          }
+          if (row < p.M) {
+#pragma unroll
+            for (int j = 0; j < 32; j += 4) {
+              const int n = x.n0 + cc + j;
+              if (cc + j < p.BN && n + 3 < p.N) {
+                float4 v = make_float4(__uint_as_float(r[j]), __uint_as_float(r[j + 1]),
+                                       __uint_as_float(r[j + 2]), __uint_as_float(r[j + 3]));
+                if (first) {
+                  if (bias) {
+                    const float4 bv = *reinterpret_cast<const float4 *>(bias + n);
+                    v.x += bv.x; v.y += bv.y; v.z += bv.z; v.w += bv.w;
+                  }
+                } else {
+                  const float4 o = *reinterpret_cast<const float4 *>(crow + n);
+                  v.x += o.x; v.y += o.y; v.z += o.z; v.w += o.w;
+                }
+                *reinterpret_cast<float4 *>(crow + n) = v;
+              } else if (cc + j < p.BN) {
+#pragma unroll
+                for (int u = 0; u < 4; ++u)
+                  if (n + u < p.N) {
+                    const float base = first ? (bias ? bias[n + u] : 0.f) : crow[n + u];
+                    crow[n + u] = __uint_as_float(r[j + u]) + base;
+                  }
               }
-              *reinterpret_cast<float4 *>(crow + n) = v;
-            } else if (c0 + j < p.BN) {
-#pragma unroll
-              for (int u = 0; u < 4; ++u)
-                if (n + u < p.N) crow[n + u] = __uint_as_float(r[j + u]) + (p.bias ? p.bias[n + u] : 0.f);
             }
           }
         }
+        tcgen05_fence_before();
+        __syncwarp();
+        if (lane == 0) mbar_arrive(&tmem_empty[buf]);
       }
-      tcgen05_fence_before();
-      __syncwarp();
-      if (lane == 0) mbar_arrive(&tmem_empty[buf]);
     }
   }
 
@@ -421,6 +475,18 @@ int pick_bn(int64_t N, int cap) {
   return (int)bn;
 }
 
+int block_k(const ZpGemmTc &g) {
+  return (g.planes == 3 && !g.a_mn && !g.b_mn && g.variant != 1) ? 32 : 64;
+}
+
+void split_plan(const ZpGemmTc &g, int bk, int *ksplit, int *kbs, int *num_k) {
+  *num_k = (int)zp_ceil_div(g.K, bk);
+  int req = g.ksplit < 1 ? 1 : g.ksplit;
+  if (req > *num_k) req = *num_k;
+  *kbs = (int)zp_ceil_div(*num_k, req);
+  *ksplit = (int)zp_ceil_div(*num_k, *kbs);
+}
+
 template <int P, int BK, int STAGES, int BN_CAP>
 int launch(const ZpGemmTc &g, cudaStream_t st) {
   using L = SmemLayout<P, BK, STAGES, BN_CAP>;
@@ -437,9 +503,11 @@ int launch(const ZpGemmTc &g, cudaStream_t st) {
   if (g.b_mn) p.BN = (p.BN + 63) / 64 * 64;       // MN-major B tiles come in 64-wide blocks
   p.num_m = (int)zp_ceil_div(g.M, BM);
   p.num_n = (int)zp_ceil_div(g.N, p.BN);
-  p.num_k = (int)zp_ceil_div(g.K, BK);
+  split_plan(g, BK, &p.ksplit, &p.kb_per_split, &p.num_k);
+  const int kc_elems = g.kc_elems > 0 ? g.kc_elems : 2048;
+  p.kc = kc_elems / BK < 1 ? 1 : kc_elems / BK;
   p.a_mn = g.a_mn; p.b_mn = g.b_mn;
-  p.bias = g.bias; p.C = g.C; p.ldc = g.ldc; p.status = g.status;
+  p.bias = g.bias; p.C = g.C; p.ldc = g.ldc; p.split_stride = g.split_stride; p.status = g.status;
   const CUtensorMapSwizzle kswz = BK == 64 ? CU_TENSOR_MAP_SWIZZLE_128B : CU_TENSOR_MAP_SWIZZLE_64B;
   CUtensorMap ma, mb;
   int rc;
@@ -452,8 +520,8 @@ int launch(const ZpGemmTc &g, cudaStream_t st) {
   int dev = 0, sms = 148;
   cudaGetDevice(&dev);
   cudaDeviceGetAttribute(&sms, cudaDevAttrMultiProcessorCount, dev);
-  const int tiles = p.num_m * p.num_n;
-  const int grid = tiles < sms ? tiles : sms;
+  const int work = p.num_m * p.num_n * p.ksplit;
+  const int grid = work < sms ? work : sms;
   gemm_tc_kernel<P, BK, STAGES, BN_CAP><<<grid, kThreads, L::kTotal, st>>>(ma, mb, p);
   ZP_LAUNCH_CHECK("gemm_tc_kernel");
   return ZP_OK;
@@ -461,10 +529,18 @@ int launch(const ZpGemmTc &g, cudaStream_t st) {
 
 }  // namespace
 
+int zp_gemm_tc_splits(const ZpGemmTc &g) {
+  if (g.K <= 0) return 1;
+  int ksplit, kbs, num_k;
+  split_plan(g, block_k(g), &ksplit, &kbs, &num_k);
+  return ksplit;
+}
+
 int zp_launch_gemm_tc(const ZpGemmTc &g, cudaStream_t st) {
   if (g.M <= 0 || g.N <= 0) return ZP_OK;
   if (g.K <= 0) return ZP_ERR_INVALID_ARG;
-  if ((g.lda % 8) || (g.ldb % 8) || (g.a_plane % 8) || (g.b_plane % 8) || (g.ldc % 4))
+  if ((g.lda % 8) || (g.ldb % 8) || (g.a_plane % 8) || (g.b_plane % 8) || (g.ldc % 4) ||
+      (g.split_stride % 4))
     return ZP_ERR_INVALID_ARG;
   if ((reinterpret_cast<uintptr_t>(g.A) | reinterpret_cast<uintptr_t>(g.B) |
        reinterpret_cast<uintptr_t>(g.C)) & 15)

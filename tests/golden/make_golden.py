@@ -29,9 +29,9 @@ CASES = {
                          num_distance_basis=8, cutoff=5.0), 10, 48, 11),
     "ref_l2m2_c16h8": (dict(lmax=2, mmax=2, sphere_channels=16, hidden_channels=8,
                             edge_channels=12, num_distance_basis=10, cutoff=6.0), 9, 40, 12),
-    "ref_l4m4_c4": (dict(lmax=4, mmax=4, sphere_channels=4, hidden_channels=4, edge_channels=4,
+    "ref_l4m4_c8": (dict(lmax=4, mmax=4, sphere_channels=8, hidden_channels=8, edge_channels=4,
                          num_distance_basis=6, cutoff=6.0), 8, 24, 13),
-    "ref_l3m3_c4": (dict(lmax=3, mmax=3, sphere_channels=4, hidden_channels=8, edge_channels=4,
+    "ref_l3m3_c8h16": (dict(lmax=3, mmax=3, sphere_channels=8, hidden_channels=16, edge_channels=4,
                          num_distance_basis=5, cutoff=4.0), 7, 30, 14),
 }
 

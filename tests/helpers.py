@@ -13,8 +13,9 @@ def rel_l2(a: torch.Tensor, b: torch.Tensor) -> float:
     return ((a - b).norm() / b.norm().clamp_min(1e-300)).item()
 
 
-def make_block(cfg: dict, params: dict, device="cuda", dtype=torch.float32) -> ESO2Block:
-    block = ESO2Block(BlockConfig(**cfg))
+def make_block(cfg: dict, params: dict, device="cuda", dtype=torch.float32,
+               precision: str = "fp32") -> ESO2Block:
+    block = ESO2Block(BlockConfig(**cfg), precision=precision)
     block.load_state_dict({k: v.clone() for k, v in params.items()})
     return block.to(device=device, dtype=dtype)
 

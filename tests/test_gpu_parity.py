@@ -50,11 +50,12 @@ def test_golden_reference_vectors(name):
 ORACLE_CASES = [
     # lmax, mmax, C, H, EC, NB, nodes, edges
     (4, 2, 8, 8, 8, 6, 12, 60),
-    (6, 2, 4, 8, 4, 5, 9, 40),
-    (3, 1, 12, 4, 8, 4, 7, 33),
+    (6, 2, 8, 16, 4, 5, 9, 40),
+    (3, 1, 24, 8, 8, 4, 7, 33),
     (2, 2, 32, 32, 32, 32, 20, 150),
-    (5, 3, 8, 4, 4, 4, 6, 25),
-    (1, 0, 4, 4, 4, 4, 5, 12),
+    (5, 3, 16, 8, 4, 4, 6, 25),
+    (1, 0, 8, 8, 4, 4, 5, 12),
+    (4, 2, 128, 128, 32, 16, 40, 300),
 ]
 
 
@@ -67,6 +68,20 @@ def test_oracle_parity_small(lmax, mmax, c, h, ec, nb, n, e, jd64):
     want = oracle_node_out_and_vjp(cfg, params, case, case["upstream"], jd64)
     got = gpu_node_out_and_vjp(make_block(cfg, params), case, case["upstream"])
     check_against(*got, *want)
+
+
+@pytest.mark.parametrize("lmax,mmax,c,h,n,e", [(4, 2, 32, 32, 16, 120), (2, 2, 64, 32, 12, 80)])
+def test_bf16_operands_fp32_accumulate(lmax, mmax, c, h, n, e, jd64):
+    """bf16 embeddings/weights in the SO(2) contraction, fp32 accumulation: 2e-2 relative L2."""
+    cfg = dict(lmax=lmax, mmax=mmax, sphere_channels=c, hidden_channels=h, edge_channels=8,
+               num_distance_basis=6, cutoff=5.0)
+    params = orc.init_params(cfg, seed=21)
+    case = random_case(cfg, n, e, seed=22)
+    want = oracle_node_out_and_vjp(cfg, params, case, case["upstream"], jd64)
+    block = make_block(cfg, params, precision="bf16")
+    got = gpu_node_out_and_vjp(block, case, case["upstream"])
+    check_against(*got, *want, tol=2e-2)
+    assert block.plan("cuda").device_status() == 0
 
 
 def test_nodes_without_edges_and_empty_graph(jd64):
@@ -169,8 +184,8 @@ def test_abi_rejects_bad_arguments():
     assert lib.zp_plan_create(ctypes.byref(cfg), jd, ctypes.byref(h)) == 2      # lmax too large
     cfg = _lib.ZpConfig(2, 3, 8, 8, 0)
     assert lib.zp_plan_create(ctypes.byref(cfg), jd, ctypes.byref(h)) == 2      # mmax > lmax
-    cfg = _lib.ZpConfig(2, 2, 6, 8, 0)
-    assert lib.zp_plan_create(ctypes.byref(cfg), jd, ctypes.byref(h)) == 2      # C % 4
+    cfg = _lib.ZpConfig(2, 2, 12, 8, 0)
+    assert lib.zp_plan_create(ctypes.byref(cfg), jd, ctypes.byref(h)) == 2      # C % 8
     assert lib.zp_plan_create(None, jd, ctypes.byref(h)) == 1
     plan = Plan.get(2, 2, 8, 8, "cuda")
     assert lib.zp_workspace_bytes(plan.handle, 4, -1, 0) == 0

@@ -107,11 +107,13 @@ class Plan:
 
     _cache: dict = {}
 
-    def __init__(self, lmax: int, mmax: int, c: int, h: int, device: torch.device):
+    def __init__(self, lmax: int, mmax: int, c: int, h: int, device: torch.device,
+                 precision: int = 0):
         lib = _lib.load()
+        self.precision = precision
         self.device = device
         jd = np.concatenate([j.numpy().astype(np.float64).ravel() for j in load_jd(lmax)])
-        cfg = _lib.ZpConfig(lmax, mmax, c, h, 0)
+        cfg = _lib.ZpConfig(lmax, mmax, c, h, precision)
         handle = ctypes.c_void_p()
         with torch.cuda.device(device):
             _lib.check(lib.zp_plan_create(ctypes.byref(cfg),
@@ -124,15 +126,15 @@ class Plan:
         self.lmax, self.mmax, self.c, self.h = lmax, mmax, c, h
 
     @classmethod
-    def get(cls, lmax, mmax, c, h, device) -> "Plan":
+    def get(cls, lmax, mmax, c, h, device, precision: int = 0) -> "Plan":
         device = torch.device(device)
         if device.type != "cuda":
             raise RuntimeError("zippel_b200 runs on CUDA devices only; there is no CPU path")
         if device.index is None:
             device = torch.device("cuda", torch.cuda.current_device())
-        key = (lmax, mmax, c, h, device.index)
+        key = (lmax, mmax, c, h, device.index, precision)
         if key not in cls._cache:
-            cls._cache[key] = cls(lmax, mmax, c, h, device)
+            cls._cache[key] = cls(lmax, mmax, c, h, device, precision)
         return cls._cache[key]
 
     def tables(self) -> dict[str, np.ndarray]:
@@ -141,6 +143,13 @@ class Plan:
         ptrs = [a.ctypes.data_as(ctypes.POINTER(ctypes.c_int32)) for a in arrs]
         _lib.check(_lib.load().zp_plan_tables(self.handle, *ptrs), "zp_plan_tables")
         return dict(zip(("row_l", "row_m", "rot_off", "gate_idx"), arrs))
+
+    def device_status(self) -> int:
+        """Reads and clears the device status word (synchronises the device)."""
+        st = ctypes.c_int(0)
+        _lib.check(_lib.load().zp_plan_device_status(self.handle, ctypes.byref(st)),
+                   "zp_plan_device_status")
+        return st.value
 
     def workspace(self, n: int, e: int, with_backward: bool) -> torch.Tensor:
         nbytes = _lib.load().zp_workspace_bytes(self.handle, n, e, int(with_backward))
@@ -250,9 +259,14 @@ def edge_conv(plan: Plan, graph: EdgeGraph, x_node, edge_vec, cos_g, sin_g, radi
 class ESO2Block(nn.Module):
     """One SO(2) interaction block + per-atom energy head, reference call signature."""
 
-    def __init__(self, cfg: BlockConfig = BlockConfig()):
+    PRECISIONS = {"fp32": 0, "bf16": 1}
+
+    def __init__(self, cfg: BlockConfig = BlockConfig(), precision: str = "fp32"):
+        """``precision``: "fp32" carries every operand of the SO(2) contraction as three bf16
+        terms (fp32-accurate results); "bf16" rounds operands to bf16 and accumulates in fp32."""
         super().__init__()
         self.cfg = cfg
+        self.precision = self.PRECISIONS[precision]
         self.layout = Layout.make(cfg.lmax, cfg.mmax)
         L, C, H = cfg.lmax, cfg.sphere_channels, cfg.hidden_channels
         ms = self.layout.m_size
@@ -304,7 +318,8 @@ class ESO2Block(nn.Module):
 
     def plan(self, device) -> Plan:
         c = self.cfg
-        return Plan.get(c.lmax, c.mmax, c.sphere_channels, c.hidden_channels, device)
+        return Plan.get(c.lmax, c.mmax, c.sphere_channels, c.hidden_channels, device,
+                        self.precision)
 
     # -- forward --------------------------------------------------------------------------
     def node_output(self, pos, atomic_numbers, x_node, edge_index, shifts, cos_gamma_k,

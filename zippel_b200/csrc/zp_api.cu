@@ -5,6 +5,8 @@
 #include <new>
 #include <vector>
 
+#include <cuda_bf16.h>
+
 #include "zp_common.cuh"
 
 // Event pairs recorded around kernel classes while timing is on.
@@ -48,19 +50,18 @@ thread_local int64_t g_launches = 0;
 bool aligned16(const void *p) { return (reinterpret_cast<uintptr_t>(p) & 15u) == 0; }
 
 // Workspace carving; every region starts 256-byte aligned.
+//   forward:  rot | a1 planes | h1 | ht planes | y | folded weight planes
+//   backward: dy planes | dht | dh1 planes | da1 | du_src | grot | wgrad partials | scratch
 struct Workspace {
-  float *rot, *a1, *h1, *ht, *y, *wfold;
-  float *dy, *dht, *dh1, *da1, *du_src, *grot, *wgrad, *scratch;
-  size_t scratch_elems;
+  float *rot, *h1, *y, *dht, *da1, *du_src, *grot, *wgrad, *scratch;
+  ZpPlanes a1, ht, dy, dh1;
+  __nv_bfloat16 *wfold;
   size_t bytes;
 };
 
-int wgrad_splits(int64_t E) {
-  int64_t s = E / 2048;
-  if (s < 1) s = 1;
-  if (s > 32) s = 32;
-  return (int)s;
-}
+constexpr int kMaxWgradSplits = 8;
+
+int64_t round8(int64_t x) { return (x + 7) / 8 * 8; }
 
 Workspace carve(const zp_plan *p, int64_t N, int64_t E, int with_backward, void *base) {
   (void)N;
@@ -68,40 +69,46 @@ Workspace carve(const zp_plan *p, int64_t N, int64_t E, int with_backward, void 
   Workspace w;
   std::memset(&w, 0, sizeof(w));
   size_t off = 0;
-  auto take = [&](size_t elems) {
-    float *ptr = base ? reinterpret_cast<float *>(static_cast<char *>(base) + off) : nullptr;
-    off += zp_align_up(elems * sizeof(float), 256);
+  auto take = [&](size_t nbytes) {
+    char *ptr = base ? static_cast<char *>(base) + off : nullptr;
+    off += zp_align_up(nbytes, 256);
     return ptr;
   };
+  auto takef = [&](size_t elems) { return reinterpret_cast<float *>(take(elems * sizeof(float))); };
+  auto takep = [&](int64_t cols) {
+    ZpPlanes pl;
+    pl.ld = round8(cols);
+    pl.planes = p->planes;
+    pl.plane_stride = (int64_t)zp_align_up((size_t)E * pl.ld, 128);
+    pl.base = reinterpret_cast<__nv_bfloat16 *>(take((size_t)pl.planes * pl.plane_stride * 2));
+    return pl;
+  };
   const size_t e = (size_t)E;
-  w.rot = take(e * t.nnz_pad);
-  w.a1 = take(e * t.Km * 2 * t.C);
-  w.h1 = take(e * t.w1_cols);
-  w.ht = take(e * t.Km * t.H);
-  w.y = take(e * t.Km * t.C);
-  w.wfold = take((size_t)p->w_elems);
+  w.rot = takef(e * t.nnz_pad);
+  w.a1 = takep((int64_t)t.Km * 2 * t.C);
+  w.h1 = takef(e * t.w1_cols);
+  w.ht = takep((int64_t)t.Km * t.H);
+  w.y = takef(e * t.Km * t.C);
+  w.wfold = reinterpret_cast<__nv_bfloat16 *>(take((size_t)p->w_elems * 2));
   if (with_backward) {
-    w.dy = take(e * t.Km * t.C);
-    w.dht = take(e * t.Km * t.H);
-    w.dh1 = take(e * t.w1_cols);
-    w.da1 = take(e * t.Km * 2 * t.C);
-    w.du_src = take(e * t.K * t.C);
-    w.grot = take(e * t.nnz_pad);
-    w.wgrad = take((size_t)p->w_elems);
-    size_t max_block = 0;
-    for (int m = 0; m < p->n_blocks; ++m) {
-      max_block = max_block > (size_t)p->c1_out[m] * p->c1_in[m] ? max_block
-                                                                 : (size_t)p->c1_out[m] * p->c1_in[m];
-      max_block = max_block > (size_t)p->c2_out[m] * p->c2_in[m] ? max_block
-                                                                 : (size_t)p->c2_out[m] * p->c2_in[m];
-    }
-    const size_t colsum = (size_t)zp_ceil_div(E > 0 ? E : 1, 256) * (size_t)t.w1_cols;
-    const size_t gemm = (size_t)wgrad_splits(E) * max_block;
-    w.scratch_elems = colsum > gemm ? colsum : gemm;
-    w.scratch = take(w.scratch_elems);
+    w.dy = takep((int64_t)t.Km * t.C);
+    w.dht = takef(e * t.Km * t.H);
+    w.dh1 = takep(t.w1_cols);
+    w.da1 = takef(e * t.Km * 2 * t.C);
+    w.du_src = takef(e * t.K * t.C);
+    w.grot = takef(e * t.nnz_pad);
+    w.wgrad = takef((size_t)kMaxWgradSplits * p->g_elems);
+    w.scratch = takef((size_t)zp_ceil_div(E > 0 ? E : 1, 256) * (size_t)t.w1_cols);
   }
   w.bytes = off;
   return w;
+}
+
+// operand views of one m-block inside a plane buffer (column offset `col`)
+ZpPlanes sub(const ZpPlanes &p, int64_t col) {
+  ZpPlanes q = p;
+  q.base = p.base + col;
+  return q;
 }
 
 }  // namespace
@@ -142,8 +149,8 @@ int zp_plan_create(const zp_config *cfg, const double *jd_host, zp_plan **plan_o
   if (!cfg || !jd_host || !plan_out) return ZP_ERR_INVALID_ARG;
   const int L = cfg->lmax, MM = cfg->mmax, C = cfg->sphere_channels, H = cfg->hidden_channels;
   if (L < 0 || L > ZP_MAX_L || MM < 0 || MM > L) return ZP_ERR_UNSUPPORTED;
-  if (C <= 0 || H <= 0 || C % 4 || H % 4 || C > 512) return ZP_ERR_UNSUPPORTED;
-  if (cfg->precision != 0) return ZP_ERR_UNSUPPORTED;
+  if (C <= 0 || H <= 0 || C % 8 || H % 8 || C > 512) return ZP_ERR_UNSUPPORTED;
+  if (cfg->precision != 0 && cfg->precision != 1) return ZP_ERR_UNSUPPORTED;
   if (!zp_device_supported()) return ZP_ERR_NO_DEVICE_CODE;
 
   zp_plan *p = new (std::nothrow) zp_plan;
@@ -184,7 +191,8 @@ int zp_plan_create(const zp_config *cfg, const double *jd_host, zp_plan **plan_o
   }
 
   p->n_blocks = MM + 1;
-  int64_t woff = 0;
+  p->planes = cfg->precision == 0 ? 3 : 1;
+  int64_t woff = 0, goff = 0;
   for (int conv = 0; conv < 2; ++conv) {
     for (int m = 0; m <= MM; ++m) {
       const int km = L + 1 - m;
@@ -194,10 +202,13 @@ int zp_plan_create(const zp_config *cfg, const double *jd_host, zp_plan **plan_o
       (conv ? p->c2_in : p->c1_in)[m] = in;
       (conv ? p->c2_out : p->c1_out)[m] = out;
       (conv ? p->c2_woff : p->c1_woff)[m] = woff;
-      woff += (int64_t)zp_align_up((size_t)in * out, 64);
+      (conv ? p->c2_goff : p->c1_goff)[m] = goff;
+      woff += (int64_t)zp_align_up((size_t)2 * p->planes * in * out, 64);
+      goff += (int64_t)zp_align_up((size_t)in * out, 64);
     }
   }
   p->w_elems = woff;
+  p->g_elems = goff;
 
   if (cudaGetDevice(&p->device) != cudaSuccess ||
       cudaMalloc(&p->status_dev, sizeof(int)) != cudaSuccess ||
@@ -358,23 +369,26 @@ int zp_eso2_forward(const zp_plan *plan, int64_t N, int64_t E, const float *x_no
   ZP_TIMED(ZP_K_WIGNER_FWD, zp_launch_wigner_fwd(plan, E, edge_vec, cos_g, sin_g, ws.rot, st));
   ZP_TIMED(ZP_K_ROTATE_IN,
            zp_launch_rotate_in(plan, E, x_node, src, dst, ws.rot, radial, ws.a1, st));
-  const int64_t lda = (int64_t)t.Km * 2 * t.C, ldh = (int64_t)t.Km * t.H, ldy = (int64_t)t.Km * t.C;
-  for (int m = 0; m < plan->n_blocks; ++m) {
+  const int P = plan->planes;
+  const int64_t ldy = (int64_t)t.Km * t.C;
+  for (int m = 0; m < plan->n_blocks && E > 0; ++m) {
     const int in = plan->c1_in[m], out = plan->c1_out[m];
-    const float *A = ws.a1 + (size_t)t.m_row0[m] * 2 * t.C;
+    const ZpPlanes A = sub(ws.a1, (int64_t)t.m_row0[m] * 2 * t.C);
     float *Cc = ws.h1 + (m == 0 ? 0 : t.n_gate + (size_t)t.m_row0[m] * t.H);
-    ZP_TIMED(ZP_K_GEMM_FWD,
-             zp_launch_gemm(E, out, in, A, lda, 1, ws.wfold + plan->c1_woff[m], 1, in,
-                            m == 0 ? w->c1_b0 : nullptr, Cc, t.w1_cols, 1, nullptr, st));
+    const ZpGemmTc g{E, out, in, P, A.base, A.ld, A.plane_stride, 0,
+                     ws.wfold + plan->c1_woff[m], in, (int64_t)out * in, 0,
+                     m == 0 ? w->c1_b0 : nullptr, Cc, t.w1_cols, plan->status_dev, 0, 1, 0, 0};
+    ZP_TIMED(ZP_K_GEMM_FWD, zp_launch_gemm_tc(g, st));
   }
   ZP_TIMED(ZP_K_GATE_FWD, zp_launch_gate_fwd(plan, E, ws.h1, ws.ht, st));
-  for (int m = 0; m < plan->n_blocks; ++m) {
+  for (int m = 0; m < plan->n_blocks && E > 0; ++m) {
     const int in = plan->c2_in[m], out = plan->c2_out[m];
-    const float *A = ws.ht + (size_t)t.m_row0[m] * t.H;
+    const ZpPlanes A = sub(ws.ht, (int64_t)t.m_row0[m] * t.H);
     float *Cc = ws.y + (size_t)t.m_row0[m] * t.C;
-    ZP_TIMED(ZP_K_GEMM_FWD,
-             zp_launch_gemm(E, out, in, A, ldh, 1, ws.wfold + plan->c2_woff[m], 1, in,
-                            m == 0 ? w->c2_b0 : nullptr, Cc, ldy, 1, nullptr, st));
+    const ZpGemmTc g{E, out, in, P, A.base, A.ld, A.plane_stride, 0,
+                     ws.wfold + plan->c2_woff[m], in, (int64_t)out * in, 0,
+                     m == 0 ? w->c2_b0 : nullptr, Cc, ldy, plan->status_dev, 0, 1, 0, 0};
+    ZP_TIMED(ZP_K_GEMM_FWD, zp_launch_gemm_tc(g, st));
   }
   ZP_TIMED(ZP_K_ROTATE_BACK,
            zp_launch_rotate_back_scatter(plan, N, ws.y, env, ws.rot, row_ptr, node_out, st));
@@ -410,42 +424,57 @@ int zp_eso2_backward(const zp_plan *plan, int64_t N, int64_t E, const float *gra
   if (workspace_bytes < ws.bytes) return ZP_ERR_WORKSPACE;
   cudaStream_t st = (cudaStream_t)stream;
   const ZpTables &t = plan->t;
-  const int64_t lda = (int64_t)t.Km * 2 * t.C, ldh = (int64_t)t.Km * t.H, ldy = (int64_t)t.Km * t.C;
-  const int splits = wgrad_splits(E);
+  const int P = plan->planes;
+  const int64_t lda = (int64_t)t.Km * 2 * t.C, ldh = (int64_t)t.Km * t.H;
+  int splits_c1[ZP_MAX_L + 1], splits_c2[ZP_MAX_L + 1];
+  int sms = 148;
+  cudaDeviceGetAttribute(&sms, cudaDevAttrMultiProcessorCount, plan->device);
 
   ZP_TIMED(ZP_K_ROTATE_GRAD_OUT,
            zp_launch_rotate_grad_out(plan, N, grad_node_out, ws.y, env, ws.rot, row_ptr, ws.dy,
                                      grad_env, ws.grot, st));
-  // conv2: input gradient, weight gradient (reduced over edges), bias gradient
-  for (int m = 0; m < plan->n_blocks; ++m) {
-    const int in = plan->c2_in[m], out = plan->c2_out[m];
-    const float *dYm = ws.dy + (size_t)t.m_row0[m] * t.C;
-    const float *Xm = ws.ht + (size_t)t.m_row0[m] * t.H;
-    float *dXm = ws.dht + (size_t)t.m_row0[m] * t.H;
-    const float *Wm = ws.wfold + plan->c2_woff[m];
-    ZP_TIMED(ZP_K_GEMM_DGRAD,
-             zp_launch_gemm(E, in, out, dYm, ldy, 1, Wm, in, 1, nullptr, dXm, ldh, 1, nullptr, st));
-    ZP_TIMED(ZP_K_GEMM_WGRAD,
-             zp_launch_gemm(out, in, E, dYm, 1, ldy, Xm, ldh, 1, nullptr,
-                            ws.wgrad + plan->c2_woff[m], in, splits, ws.scratch, st));
+  // One conv at a time: input gradient dX = dY W_fold (K-major against the transposed planes),
+  // weight gradient dW_fold = dY^T X with both operands MN-major (the contraction runs over
+  // edges), bias gradient = column sums of dY.
+  for (int conv = 1; conv >= 0; --conv) {
+    const ZpPlanes &dYp = conv ? ws.dy : ws.dh1;
+    const ZpPlanes &Xp = conv ? ws.ht : ws.a1;
+    float *dX = conv ? ws.dht : ws.da1;
+    const int64_t ldx = conv ? ldh : lda;
+    const int cin = conv ? t.H : 2 * t.C, cout = conv ? t.C : t.H;
+    if (conv == 0) ZP_TIMED(ZP_K_GATE_BWD, zp_launch_gate_bwd(plan, E, ws.h1, ws.dht, ws.dh1, st));
+    for (int m = 0; m < plan->n_blocks; ++m) {
+      const int in = conv ? plan->c2_in[m] : plan->c1_in[m];
+      const int out = conv ? plan->c2_out[m] : plan->c1_out[m];
+      const int64_t ycol = (conv == 0 && m > 0 ? t.n_gate : 0) + (m == 0 ? 0 : (int64_t)t.m_row0[m] * cout);
+      const int64_t xcol = (int64_t)t.m_row0[m] * cin;
+      const ZpPlanes dYm = sub(dYp, ycol), Xm = sub(Xp, xcol);
+      const __nv_bfloat16 *Wt = ws.wfold + (conv ? plan->c2_woff[m] : plan->c1_woff[m]) +
+                                (int64_t)P * out * in;
+      float *G = ws.wgrad + (conv ? plan->c2_goff[m] : plan->c1_goff[m]);
+      int &nsplit = (conv ? splits_c2 : splits_c1)[m];
+      nsplit = 1;
+      if (E == 0) {
+        ZP_CUDA(cudaMemsetAsync(G, 0, sizeof(float) * (size_t)out * in, st));
+        continue;
+      }
+      const ZpGemmTc gd{E, in, out, P, dYm.base, dYm.ld, dYm.plane_stride, 0,
+                        Wt, out, (int64_t)out * in, 0, nullptr, dX + xcol, ldx,
+                        plan->status_dev, 0, 1, 0, 0};
+      ZP_TIMED(ZP_K_GEMM_DGRAD, zp_launch_gemm_tc(gd, st));
+      const int64_t tiles = zp_ceil_div(out, 128) * zp_ceil_div(in, P == 3 ? 128 : 256);
+      int want = (int)zp_ceil_div(sms, tiles);
+      if (want > kMaxWgradSplits) want = kMaxWgradSplits;
+      ZpGemmTc gw_{out, in, E, P, dYm.base, dYm.ld, dYm.plane_stride, 1,
+                   Xm.base, Xm.ld, Xm.plane_stride, 1, nullptr, G, in,
+                   plan->status_dev, 0, want, plan->g_elems, 0};
+      nsplit = zp_gemm_tc_splits(gw_);
+      ZP_TIMED(ZP_K_GEMM_WGRAD, zp_launch_gemm_tc(gw_, st));
+    }
+    ZP_TIMED(ZP_K_BIAS_GRAD,
+             zp_launch_colsum(E, conv ? plan->c2_out[0] : plan->c1_out[0], dYp,
+                              conv ? gw->c2_b0 : gw->c1_b0, ws.scratch, st));
   }
-  ZP_TIMED(ZP_K_BIAS_GRAD,
-           zp_launch_colsum(E, plan->c2_out[0], ws.dy, ldy, gw->c2_b0, ws.scratch, st));
-  ZP_TIMED(ZP_K_GATE_BWD, zp_launch_gate_bwd(plan, E, ws.h1, ws.dht, ws.dh1, st));
-  for (int m = 0; m < plan->n_blocks; ++m) {
-    const int in = plan->c1_in[m], out = plan->c1_out[m];
-    const float *dYm = ws.dh1 + (m == 0 ? 0 : t.n_gate + (size_t)t.m_row0[m] * t.H);
-    const float *Xm = ws.a1 + (size_t)t.m_row0[m] * 2 * t.C;
-    float *dXm = ws.da1 + (size_t)t.m_row0[m] * 2 * t.C;
-    const float *Wm = ws.wfold + plan->c1_woff[m];
-    ZP_TIMED(ZP_K_GEMM_DGRAD, zp_launch_gemm(E, in, out, dYm, t.w1_cols, 1, Wm, in, 1, nullptr,
-                                             dXm, lda, 1, nullptr, st));
-    ZP_TIMED(ZP_K_GEMM_WGRAD,
-             zp_launch_gemm(out, in, E, dYm, 1, t.w1_cols, Xm, lda, 1, nullptr,
-                            ws.wgrad + plan->c1_woff[m], in, splits, ws.scratch, st));
-  }
-  ZP_TIMED(ZP_K_BIAS_GRAD,
-           zp_launch_colsum(E, plan->c1_out[0], ws.dh1, t.w1_cols, gw->c1_b0, ws.scratch, st));
   ZP_TIMED(ZP_K_ROTATE_IN_BWD,
            zp_launch_rotate_in_bwd(plan, N, ws.da1, radial, x_node, src, ws.rot, row_ptr,
                                    grad_radial, ws.du_src, grad_x_node, ws.grot, st));
@@ -453,7 +482,8 @@ int zp_eso2_backward(const zp_plan *plan, int64_t N, int64_t E, const float *gra
            zp_launch_src_reduce(plan, N, ws.du_src, perm_src, row_ptr_src, grad_x_node, st));
   ZP_TIMED(ZP_K_WIGNER_BWD,
            zp_launch_wigner_bwd(plan, E, edge_vec, cos_g, sin_g, ws.grot, grad_edge_vec, st));
-  ZP_TIMED(ZP_K_FOLD, zp_launch_unfold_wgrad(plan, ws.wgrad, gw, st));
+  ZP_TIMED(ZP_K_FOLD, zp_launch_unfold_wgrad(plan, ws.wgrad, plan->g_elems, splits_c1, splits_c2,
+                                             gw, st));
   return ZP_OK;
 }
 

@@ -5,6 +5,7 @@
 #include <stdint.h>
 
 #include "zippel_b200.h"
+#include "zp_planes.cuh"
 
 #define ZP_MAX_L 6                              // largest supported lmax
 #define ZP_MAX_KM ((ZP_MAX_L + 1) * (ZP_MAX_L + 1))
@@ -42,8 +43,11 @@ struct zp_plan {
   // per-m GEMM shapes of the folded SO(2) weights
   int n_blocks;                                 // mmax + 1
   int c1_in[ZP_MAX_L + 1], c1_out[ZP_MAX_L + 1], c2_in[ZP_MAX_L + 1], c2_out[ZP_MAX_L + 1];
-  int64_t c1_woff[ZP_MAX_L + 1], c2_woff[ZP_MAX_L + 1];   // element offsets in the packed buffer
-  int64_t w_elems;                              // total packed (folded) weight elements
+  int planes;                                   // bf16 planes per fp32 operand: 3 (fp32) or 1 (bf16)
+  int64_t c1_woff[ZP_MAX_L + 1], c2_woff[ZP_MAX_L + 1];   // bf16 offsets of the folded planes
+  int64_t w_elems;                              // bf16 elements of all folded planes
+  int64_t c1_goff[ZP_MAX_L + 1], c2_goff[ZP_MAX_L + 1];   // fp32 offsets of the folded gradients
+  int64_t g_elems;                              // fp32 elements of one set of folded gradients
 };
 
 // thread-local text of the last CUDA error
@@ -93,14 +97,15 @@ int zp_launch_wigner_bwd(const zp_plan *p, int64_t E, const float *ev, const flo
                          const float *sg, const float *grot, float *gev, cudaStream_t st);
 
 int zp_launch_rotate_in(const zp_plan *p, int64_t E, const float *x, const int32_t *src,
-                        const int32_t *dst, const float *rot, const float *radial, float *a1,
-                        cudaStream_t st);
+                        const int32_t *dst, const float *rot, const float *radial,
+                        const ZpPlanes &a1, cudaStream_t st);
 int zp_launch_rotate_back_scatter(const zp_plan *p, int64_t N, const float *y, const float *env,
                                   const float *rot, const int32_t *row_ptr, float *node_out,
                                   cudaStream_t st);
 int zp_launch_rotate_grad_out(const zp_plan *p, int64_t N, const float *g, const float *y,
                               const float *env, const float *rot, const int32_t *row_ptr,
-                              float *dy, float *grad_env, float *grad_rot, cudaStream_t st);
+                              const ZpPlanes &dy, float *grad_env, float *grad_rot,
+                              cudaStream_t st);
 int zp_launch_rotate_in_bwd(const zp_plan *p, int64_t N, const float *da1, const float *radial,
                             const float *x, const int32_t *src, const float *rot,
                             const int32_t *row_ptr, float *grad_radial, float *du_src,
@@ -109,16 +114,10 @@ int zp_launch_src_reduce(const zp_plan *p, int64_t N, const float *du_src,
                          const int32_t *perm_src, const int32_t *row_ptr_src, float *grad_x,
                          cudaStream_t st);
 
-int zp_launch_gate_fwd(const zp_plan *p, int64_t E, const float *h1, float *ht, cudaStream_t st);
-int zp_launch_gate_bwd(const zp_plan *p, int64_t E, const float *h1, const float *dht, float *dh1,
+int zp_launch_gate_fwd(const zp_plan *p, int64_t E, const float *h1, const ZpPlanes &ht,
                        cudaStream_t st);
-
-// C[M,N] = A * B (+ bias[n]) with arbitrary element strides: A(m,k) = A[m*am + k*ak],
-// B(k,n) = B[k*bk + n*bn].  Exactly one of (am, ak) and one of (bk, bn) must be 1.
-// splits > 1 partitions K and sums the partials in a fixed order (scratch: splits*M*N floats).
-int zp_launch_gemm(int64_t M, int64_t N, int64_t K, const float *A, int64_t am, int64_t ak,
-                   const float *B, int64_t bk, int64_t bn, const float *bias, float *C,
-                   int64_t ldc, int splits, float *scratch, cudaStream_t st);
+int zp_launch_gate_bwd(const zp_plan *p, int64_t E, const float *h1, const float *dht,
+                       const ZpPlanes &dh1, cudaStream_t st);
 
 // Tensor-core product over bf16 planes: C[M,N] = sum_pairs A_pa * B_pb^T (+ bias), fp32 out.
 // K-major operand: X[p*plane + r*ld + k]; MN-major (x_mn = 1): X[p*plane + k*ld + r].
@@ -142,8 +141,12 @@ int zp_gemm_tc_splits(const ZpGemmTc &g);
 int zp_launch_split_planes(int64_t rows, int64_t cols, const float *in, int64_t ld_in, void *out,
                            int64_t ld_out, int64_t plane_stride, int planes, cudaStream_t st);
 
-int zp_launch_fold_weights(const zp_plan *p, const zp_weights *w, float *packed, cudaStream_t st);
-int zp_launch_unfold_wgrad(const zp_plan *p, const float *packed_grad, const zp_weight_grads *gw,
+// Folded SO(2) weights as bf16 planes: per block W_fold [P][out][in] followed by its transpose
+// [P][in][out], at element offset c{1,2}_woff[m] of `packed`.
+int zp_launch_fold_weights(const zp_plan *p, const zp_weights *w, void *packed, cudaStream_t st);
+// partials: per split s the folded fp32 gradients at partials + s*split_stride + c{1,2}_goff[m]
+int zp_launch_unfold_wgrad(const zp_plan *p, const float *partials, int64_t split_stride,
+                           const int *splits_c1, const int *splits_c2, const zp_weight_grads *gw,
                            cudaStream_t st);
-int zp_launch_colsum(int64_t rows, int64_t cols, const float *a, int64_t lda, float *out,
-                     float *scratch, cudaStream_t st);
+int zp_launch_colsum(int64_t rows, int64_t cols, const ZpPlanes &a, float *out, float *scratch,
+                     cudaStream_t st);

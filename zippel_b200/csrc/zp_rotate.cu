@@ -14,6 +14,7 @@
 // channels and moves them with one vector load/store.  No atomics: every output element is
 // produced by exactly one thread, in an order fixed by the CSR offsets.
 #include "zp_common.cuh"
+#include "zp_planes.cuh"
 
 namespace {
 
@@ -56,9 +57,9 @@ constexpr int kRotInMaxEdges = 32;
 template <int L, int LMAX>
 struct RotIn {
   static __device__ __forceinline__ void run(const ZpTables &t, const float *xrow,
-                                             const float *rot_s, const float *rad_e, float *a_e,
-                                             int c2) {
-    RotIn<L - 1, LMAX>::run(t, xrow, rot_s, rad_e, a_e, c2);
+                                             const float *rot_s, const float *rad_e,
+                                             const ZpPlanes &a1, int64_t a_row, int c2) {
+    RotIn<L - 1, LMAX>::run(t, xrow, rot_s, rad_e, a1, a_row, c2);
     constexpr int n = 2 * L + 1;
     const int C2 = 2 * t.C;
     float u[n][4];
@@ -82,7 +83,7 @@ struct RotIn {
         vload<4>(g, rad_e + t.rad_off[am] + (L - am) * C2 + c2);
 #pragma unroll
         for (int v = 0; v < 4; ++v) acc[v] *= g[v];
-        vstore<4>(a_e + (size_t)r * C2 + c2, acc);
+        zp_store_planes<4>(a1, a_row + (int64_t)r * C2 + c2, acc);
       }
     }
   }
@@ -90,7 +91,7 @@ struct RotIn {
 template <int LMAX>
 struct RotIn<-1, LMAX> {
   static __device__ __forceinline__ void run(const ZpTables &, const float *, const float *,
-                                             const float *, float *, int) {}
+                                             const float *, const ZpPlanes &, int64_t, int) {}
 };
 
 template <int LMAX>
@@ -98,7 +99,7 @@ __global__ void __launch_bounds__(kRotInThreads)
 rotate_in_kernel(const __grid_constant__ ZpTables t, int64_t E, int epb,
                  const float *__restrict__ x, const int32_t *__restrict__ src,
                  const int32_t *__restrict__ dst, const float *__restrict__ rot,
-                 const float *__restrict__ radial, float *__restrict__ a1) {
+                 const float *__restrict__ radial, const ZpPlanes a1) {
   extern __shared__ float rot_s[];                       // [epb][nnz_pad]
   const int Q = t.C / 2;                                 // channel quads of the 2C-wide message
   const int64_t e0 = (int64_t)blockIdx.x * epb;
@@ -114,7 +115,7 @@ rotate_in_kernel(const __grid_constant__ ZpTables t, int64_t E, int epb,
   const int64_t node = second ? dst[e] : src[e];
   const float *xrow = x + (size_t)node * t.K * t.C + (second ? c2 - t.C : c2);
   RotIn<LMAX, LMAX>::run(t, xrow, rot_s + le * t.nnz_pad, radial + (size_t)e * t.R,
-                         a1 + (size_t)e * t.Km * 2 * t.C, c2);
+                         a1, e * a1.ld, c2);
 }
 
 // ------------------------------------------------------------------------------------------
@@ -212,11 +213,12 @@ rotate_back_scatter_kernel(const __grid_constant__ ZpTables t, int64_t N,
 //   grad_rot[e, r, j] = env_e * sum_c y[e, r, c] g[n, l^2 + j, c]
 template <int L, int LMAX, int VEC>
 struct GradOut {
-  static __device__ __forceinline__ void run(const ZpTables &t, const float *y_e, float *dy_e,
+  static __device__ __forceinline__ void run(const ZpTables &t, const float *y_e,
+                                             const ZpPlanes &dy, int64_t dy_row,
                                              const float *rot_s, float *grot_s, float env,
                                              const float (&g)[(LMAX + 1) * (LMAX + 1)][VEC],
                                              float &genv, int c, bool active, bool lane0) {
-    GradOut<L - 1, LMAX, VEC>::run(t, y_e, dy_e, rot_s, grot_s, env, g, genv, c, active, lane0);
+    GradOut<L - 1, LMAX, VEC>::run(t, y_e, dy, dy_row, rot_s, grot_s, env, g, genv, c, active, lane0);
     constexpr int n = 2 * L + 1;
     const int mm = t.mmax < L ? t.mmax : L;
 #pragma unroll
@@ -246,15 +248,15 @@ struct GradOut {
           genv = fmaf(yv[v], tv[v], genv);
           tv[v] *= env;
         }
-        if (active) vstore<VEC>(dy_e + (size_t)r * t.C + c, tv);
+        if (active) zp_store_planes<VEC>(dy, dy_row + (int64_t)r * t.C + c, tv);
       }
     }
   }
 };
 template <int LMAX, int VEC>
 struct GradOut<-1, LMAX, VEC> {
-  static __device__ __forceinline__ void run(const ZpTables &, const float *, float *,
-                                             const float *, float *, float,
+  static __device__ __forceinline__ void run(const ZpTables &, const float *, const ZpPlanes &,
+                                             int64_t, const float *, float *, float,
                                              const float (&)[(LMAX + 1) * (LMAX + 1)][VEC],
                                              float &, int, bool, bool) {}
 };
@@ -265,7 +267,7 @@ __global__ void __launch_bounds__(128)
 rotate_grad_out_kernel(const __grid_constant__ ZpTables t, int64_t N,
                        const float *__restrict__ g_out, const float *__restrict__ y,
                        const float *__restrict__ env, const float *__restrict__ rot,
-                       const int32_t *__restrict__ row_ptr, float *__restrict__ dy,
+                       const int32_t *__restrict__ row_ptr, const ZpPlanes dy,
                        float *__restrict__ grad_env, float *__restrict__ grad_rot) {
   constexpr int VEC = VecFor<LMAX>::value;
   constexpr int K = (LMAX + 1) * (LMAX + 1);
@@ -293,7 +295,7 @@ rotate_grad_out_kernel(const __grid_constant__ ZpTables t, int64_t N,
     stage_rot(t, rot + (size_t)e * t.nnz_pad, rot_s, threadIdx.x, nthr);
     slot_sync(slot, nthr);
     float genv = 0.f;
-    GradOut<LMAX, LMAX, VEC>::run(t, y + (size_t)e * t.Km * t.C, dy + (size_t)e * t.Km * t.C,
+    GradOut<LMAX, LMAX, VEC>::run(t, y + (size_t)e * t.Km * t.C, dy, (int64_t)e * dy.ld,
                                   rot_s, grot_s, env[e], g, genv, c, active, lane == 0);
     genv = warp_sum(genv);
     if (lane == 0) genv_s[warp] = genv;
@@ -502,8 +504,8 @@ NodeLaunch node_launch(const ZpTables &t, int64_t N) {
 }  // namespace
 
 int zp_launch_rotate_in(const zp_plan *p, int64_t E, const float *x, const int32_t *src,
-                        const int32_t *dst, const float *rot, const float *radial, float *a1,
-                        cudaStream_t st) {
+                        const int32_t *dst, const float *rot, const float *radial,
+                        const ZpPlanes &a1, cudaStream_t st) {
   if (E == 0) return ZP_OK;
   const ZpTables &t = p->t;
   const int Q = t.C / 2;
@@ -541,7 +543,8 @@ int zp_launch_rotate_back_scatter(const zp_plan *p, int64_t N, const float *y, c
 
 int zp_launch_rotate_grad_out(const zp_plan *p, int64_t N, const float *g, const float *y,
                               const float *env, const float *rot, const int32_t *row_ptr,
-                              float *dy, float *grad_env, float *grad_rot, cudaStream_t st) {
+                              const ZpPlanes &dy, float *grad_env, float *grad_rot,
+                              cudaStream_t st) {
   if (N == 0) return ZP_OK;
   const ZpTables &t = p->t;
 #define CALL(LM)                                                                            \

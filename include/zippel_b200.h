@@ -34,7 +34,8 @@ typedef enum zp_status {
   ZP_ERR_WORKSPACE = 3,        /* workspace smaller than zp_workspace_bytes()              */
   ZP_ERR_CUDA = 4,             /* a CUDA runtime call failed; see zp_last_cuda_error()     */
   ZP_ERR_DEVICE_TIMEOUT = 5,   /* a bounded device-side wait gave up (status word set)     */
-  ZP_ERR_NO_DEVICE_CODE = 6    /* the library holds no code for this GPU (needs sm_100a)   */
+  ZP_ERR_NO_DEVICE_CODE = 6,   /* the library holds no code for this GPU (needs sm_100a)   */
+  ZP_ERR_TOO_LARGE = 7         /* sizes exceed the fixed capacity of a non-allocating call  */
 } zp_status;
 
 /* Mirrors the fields of the reference's BlockConfig (blocks/eso2_ref.py:51-76) that the
@@ -91,6 +92,30 @@ int zp_csr_build(const int64_t *edge_index /* [2,E] int64: row 0 src, row 1 dst 
                  int32_t *perm, int32_t *src_sorted, int32_t *dst_sorted, int32_t *row_ptr,
                  int32_t *perm_src, int32_t *row_ptr_src, void *work, size_t work_bytes,
                  void *stream);
+
+/* zp_csr_build for callers that must not allocate device memory.  This entry point has no
+ * counterpart in the reference.  A molecular-dynamics driver typically reserves all device
+ * memory when it starts and then rebuilds its neighbour list every few steps from inside the
+ * stepping loop; at that point it has no spare buffer to lend as `work`, and it does not want a
+ * runtime allocation either, because an allocation stalls the whole device and can fail long
+ * after start-up.  For such callers the scratch of the sort lives in a fixed array inside the
+ * library: ZP_CSR_STATIC_BYTES of device memory on every GPU that loads the library, held
+ * until the process exits.  Inputs and outputs are the caller's, exactly as for zp_csr_build,
+ * and the results are identical.
+ *   - Limits: n_edges <= ZP_CSR_STATIC_MAX_EDGES and n_nodes <= ZP_CSR_STATIC_MAX_NODES,
+ *     otherwise ZP_ERR_TOO_LARGE and nothing is launched.
+ *   - The first call on a device looks up the array's device address (no allocation); make
+ *     that first call before starting any stream capture on that device.
+ *   - All calls on a device share the one array.  Its counters are cleared at the start of
+ *     every call, so stale contents never matter, but two calls that can run on the GPU at the
+ *     same time (different streams, different host threads) race on it: serialise them.
+ *   - Calls no cudaMalloc / cudaFree and no allocating library routine.                        */
+#define ZP_CSR_STATIC_MAX_EDGES 262144
+#define ZP_CSR_STATIC_MAX_NODES 65536
+#define ZP_CSR_STATIC_BYTES 1573888
+int zp_csr_build_static(const int64_t *edge_index, int64_t n_edges, int64_t n_nodes,
+                        int32_t *perm, int32_t *src_sorted, int32_t *dst_sorted,
+                        int32_t *row_ptr, int32_t *perm_src, int32_t *row_ptr_src, void *stream);
 
 /* Packed rotation rot[e, rot_off[r] + j] = D_l(e)[row of (l, m_r), j], the nonzeros of
  * to_m @ wigner (replaces wigner_from_edge_vec, blocks/wigner.py:115-160, and the einsum at

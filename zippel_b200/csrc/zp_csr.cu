@@ -5,7 +5,13 @@
 // gives the same arrays bit for bit: bucket the edges by node with atomics (arbitrary order
 // inside a bucket), then rank every element inside its bucket by counting the keys below it.
 // Buckets are the in-/out-neighbourhoods (tens of edges), so the quadratic rank is cheap.
+#include <mutex>
+
 #include "zp_common.cuh"
+
+// Scratch of zp_csr_build_static: one fixed array per GPU that loads the library.  In host code
+// this name is only a handle for cudaGetSymbolAddress, never a pointer a kernel can be given.
+static __device__ __align__(256) unsigned char g_csr_static_scratch[ZP_CSR_STATIC_BYTES];
 
 namespace {
 
@@ -196,6 +202,37 @@ int zp_csr_build(const int64_t *edge_index, int64_t E, int64_t N, int32_t *perm,
     ZP_LAUNCH_CHECK("rank_src_kernel");
   }
   return ZP_OK;
+}
+
+// The sort without a caller-provided work buffer and without any allocation: the scratch is the
+// file-scope device array above.  Its device address is looked up once per device (first call on
+// that device, with that device current) and cached; the sort itself is zp_csr_build unchanged,
+// which clears the counters it needs at the start of every call.
+int zp_csr_build_static(const int64_t *edge_index, int64_t E, int64_t N, int32_t *perm,
+                        int32_t *src_sorted, int32_t *dst_sorted, int32_t *row_ptr,
+                        int32_t *perm_src, int32_t *row_ptr_src, void *stream) {
+  if (E < 0 || N < 0) return ZP_ERR_INVALID_ARG;
+  if (E > ZP_CSR_STATIC_MAX_EDGES || N > ZP_CSR_STATIC_MAX_NODES ||
+      carve_csr(E, N, nullptr).bytes > (size_t)ZP_CSR_STATIC_BYTES)
+    return ZP_ERR_TOO_LARGE;
+  constexpr int kMaxDevices = 64;
+  static std::mutex mu;
+  static void *scratch_of_device[kMaxDevices] = {nullptr};
+  int dev = -1;
+  ZP_CUDA(cudaGetDevice(&dev));
+  if (dev < 0 || dev >= kMaxDevices) return ZP_ERR_UNSUPPORTED;
+  void *scratch = nullptr;
+  {
+    std::lock_guard<std::mutex> lock(mu);
+    if (!scratch_of_device[dev]) {
+      void *ptr = nullptr;
+      ZP_CUDA(cudaGetSymbolAddress(&ptr, g_csr_static_scratch));
+      scratch_of_device[dev] = ptr;
+    }
+    scratch = scratch_of_device[dev];
+  }
+  return zp_csr_build(edge_index, E, N, perm, src_sorted, dst_sorted, row_ptr, perm_src,
+                      row_ptr_src, scratch, (size_t)ZP_CSR_STATIC_BYTES, stream);
 }
 
 }  // extern "C"

@@ -74,10 +74,10 @@ def test_one_plane_k_major(M, N, K):
     assert err < 4e-6
 
 
-@pytest.mark.parametrize("planes", [1, 3])
+@pytest.mark.parametrize("planes,variant", [(1, 0), (3, 0), (3, 1)])
 @pytest.mark.parametrize("M,N,K", [(128, 128, 64), (256, 192, 200), (1152, 1280, 5000), (24, 40, 333)])
-def test_mn_major_operands(M, N, K, planes):
-    err_p, err_f = run_gemm(M, N, K, planes, True, True)
+def test_mn_major_operands(M, N, K, planes, variant):
+    err_p, err_f = run_gemm(M, N, K, planes, True, True, variant=variant)
     assert (err_f if planes == 3 else err_p) < 4e-6
 
 

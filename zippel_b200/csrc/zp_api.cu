@@ -463,8 +463,10 @@ int zp_eso2_backward(const zp_plan *plan, int64_t N, int64_t E, const float *gra
                         Wt, out, (int64_t)out * in, 0, nullptr, dX + xcol, ldx,
                         plan->status_dev, 0, 1, 0, 0};
       ZP_TIMED(ZP_K_GEMM_DGRAD, zp_launch_gemm_tc(gd, st));
-      const int64_t tiles = zp_ceil_div(out, 128) * zp_ceil_div(in, P == 3 ? 128 : 256);
-      int want = (int)zp_ceil_div(sms, tiles);
+      // enough K splits to fill the SMs once, never more work items than SMs
+      const int64_t tiles = zp_ceil_div(out, 128) * zp_ceil_div(in, 256);
+      int want = (int)(sms / tiles);
+      if (want < 1) want = 1;
       if (want > kMaxWgradSplits) want = kMaxWgradSplits;
       ZpGemmTc gw_{out, in, E, P, dYm.base, dYm.ld, dYm.plane_stride, 1,
                    Xm.base, Xm.ld, Xm.plane_stride, 1, nullptr, G, in,

@@ -475,9 +475,7 @@ int pick_bn(int64_t N, int cap) {
   return (int)bn;
 }
 
-int block_k(const ZpGemmTc &g) {
-  return (g.planes == 3 && !g.a_mn && !g.b_mn && g.variant != 1) ? 32 : 64;
-}
+int block_k(const ZpGemmTc &g) { return (g.planes == 3 && g.variant != 1) ? 32 : 64; }
 
 void split_plan(const ZpGemmTc &g, int bk, int *ksplit, int *kbs, int *num_k) {
   *num_k = (int)zp_ceil_div(g.K, bk);
@@ -546,8 +544,9 @@ int zp_launch_gemm_tc(const ZpGemmTc &g, cudaStream_t st) {
        reinterpret_cast<uintptr_t>(g.C)) & 15)
     return ZP_ERR_INVALID_ARG;
   if (g.a_mn || g.b_mn) {
-    // MN-major tiles are [BK = 64][64] blocks under the 128-byte swizzle
-    if (g.planes == 3) return launch<3, 64, 2, 128>(g, st);
+    // MN-major tiles are [BK][64] blocks under the 128-byte swizzle
+    if (g.planes == 3)
+      return g.variant == 1 ? launch<3, 64, 2, 128>(g, st) : launch<3, 32, 3, 256>(g, st);
     if (g.planes == 1) return launch<1, 64, 4, 256>(g, st);
     return ZP_ERR_UNSUPPORTED;
   }

@@ -95,7 +95,7 @@ Workspace carve(const zp_plan *p, int64_t N, int64_t E, int with_backward, void 
     w.dht = takef(e * t.Km * t.H);
     w.dh1 = takep(t.w1_cols);
     w.da1 = takef(e * t.Km * 2 * t.C);
-    w.du_src = takef(e * t.K * t.C);
+    w.du_src = takef(e * 2 * t.K * t.C);
     w.grot = takef(e * t.nnz_pad);
     w.wgrad = takef((size_t)kMaxWgradSplits * p->g_elems);
     w.scratch = takef((size_t)zp_ceil_div(E > 0 ? E : 1, 256) * (size_t)t.w1_cols);
@@ -404,12 +404,11 @@ int zp_eso2_backward(const zp_plan *plan, int64_t N, int64_t E, const float *gra
                      float *grad_x_node, float *grad_edge_vec, float *grad_radial,
                      float *grad_env, const zp_weight_grads *gw, void *workspace,
                      size_t workspace_bytes, void *stream) {
-  (void)dst;
   if (!plan || N < 0 || E < 0) return ZP_ERR_INVALID_ARG;
   if (N == 0) return E == 0 ? ZP_OK : ZP_ERR_INVALID_ARG;
   if (!grad_node_out || !x_node || !row_ptr || !row_ptr_src || !grad_x_node || !workspace || !gw)
     return ZP_ERR_INVALID_ARG;
-  if (E && (!edge_vec || !cos_g || !sin_g || !radial || !env || !src || !perm_src ||
+  if (E && (!edge_vec || !cos_g || !sin_g || !radial || !env || !src || !dst || !perm_src ||
             !grad_edge_vec || !grad_radial || !grad_env))
     return ZP_ERR_INVALID_ARG;
   if (!gw->c1_w0 || !gw->c1_b0 || !gw->c2_w0 || !gw->c2_b0) return ZP_ERR_INVALID_ARG;
@@ -432,7 +431,7 @@ int zp_eso2_backward(const zp_plan *plan, int64_t N, int64_t E, const float *gra
   cudaDeviceGetAttribute(&sms, cudaDevAttrMultiProcessorCount, plan->device);
 
   ZP_TIMED(ZP_K_ROTATE_GRAD_OUT,
-           zp_launch_rotate_grad_out(plan, N, grad_node_out, ws.y, env, ws.rot, row_ptr, ws.dy,
+           zp_launch_rotate_grad_out(plan, E, grad_node_out, ws.y, env, ws.rot, dst, ws.dy,
                                      grad_env, ws.grot, st));
   // One conv at a time: input gradient dX = dY W_fold (K-major against the transposed planes),
   // weight gradient dW_fold = dY^T X with both operands MN-major (the contraction runs over
@@ -479,10 +478,11 @@ int zp_eso2_backward(const zp_plan *plan, int64_t N, int64_t E, const float *gra
                               conv ? gw->c2_b0 : gw->c1_b0, ws.scratch, st));
   }
   ZP_TIMED(ZP_K_ROTATE_IN_BWD,
-           zp_launch_rotate_in_bwd(plan, N, ws.da1, radial, x_node, src, ws.rot, row_ptr,
-                                   grad_radial, ws.du_src, grad_x_node, ws.grot, st));
+           zp_launch_rotate_in_bwd(plan, E, ws.da1, radial, x_node, src, dst, ws.rot,
+                                   grad_radial, ws.du_src, ws.grot, st));
   ZP_TIMED(ZP_K_SRC_REDUCE,
-           zp_launch_src_reduce(plan, N, ws.du_src, perm_src, row_ptr_src, grad_x_node, st));
+           zp_launch_node_reduce(plan, N, ws.du_src, row_ptr, perm_src, row_ptr_src,
+                                 grad_x_node, st));
   ZP_TIMED(ZP_K_WIGNER_BWD,
            zp_launch_wigner_bwd(plan, E, edge_vec, cos_g, sin_g, ws.grot, grad_edge_vec, st));
   ZP_TIMED(ZP_K_FOLD, zp_launch_unfold_wgrad(plan, ws.wgrad, plan->g_elems, splits_c1, splits_c2,

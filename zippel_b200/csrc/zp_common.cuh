@@ -102,17 +102,18 @@ int zp_launch_rotate_in(const zp_plan *p, int64_t E, const float *x, const int32
 int zp_launch_rotate_back_scatter(const zp_plan *p, int64_t N, const float *y, const float *env,
                                   const float *rot, const int32_t *row_ptr, float *node_out,
                                   cudaStream_t st);
-int zp_launch_rotate_grad_out(const zp_plan *p, int64_t N, const float *g, const float *y,
-                              const float *env, const float *rot, const int32_t *row_ptr,
+int zp_launch_rotate_grad_out(const zp_plan *p, int64_t E, const float *g, const float *y,
+                              const float *env, const float *rot, const int32_t *dst,
                               const ZpPlanes &dy, float *grad_env, float *grad_rot,
                               cudaStream_t st);
-int zp_launch_rotate_in_bwd(const zp_plan *p, int64_t N, const float *da1, const float *radial,
-                            const float *x, const int32_t *src, const float *rot,
-                            const int32_t *row_ptr, float *grad_radial, float *du_src,
-                            float *grad_x, float *grad_rot, cudaStream_t st);
-int zp_launch_src_reduce(const zp_plan *p, int64_t N, const float *du_src,
-                         const int32_t *perm_src, const int32_t *row_ptr_src, float *grad_x,
-                         cudaStream_t st);
+// du_both [E][2][K][C]: per-edge contributions to grad_x of the source (0) and destination (1)
+int zp_launch_rotate_in_bwd(const zp_plan *p, int64_t E, const float *da1, const float *radial,
+                            const float *x, const int32_t *src, const int32_t *dst,
+                            const float *rot, float *grad_radial, float *du_both, float *grad_rot,
+                            cudaStream_t st);
+int zp_launch_node_reduce(const zp_plan *p, int64_t N, const float *du_both,
+                          const int32_t *row_ptr, const int32_t *perm_src,
+                          const int32_t *row_ptr_src, float *grad_x, cudaStream_t st);
 
 int zp_launch_gate_fwd(const zp_plan *p, int64_t E, const float *h1, const ZpPlanes &ht,
                        cudaStream_t st);

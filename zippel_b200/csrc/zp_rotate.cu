@@ -2,9 +2,9 @@
 //
 //   rotate_in            a[e, r, c2] = radial[e, .] * sum_j rot[e, r, j] * [x_src ; x_dst][l_r^2 + j, c2]
 //   rotate_back_scatter  node_out[n, l^2 + j, c] = sum_{e -> n} env_e * sum_r rot[e, r, j] * y[e, r, c]
-//   rotate_grad_out      the VJP of rotate_back_scatter (needs y), per destination node
-//   rotate_in_bwd        the VJP of rotate_in, per destination node
-//   src_reduce           fixed-order sum of the per-edge source contributions
+//   rotate_grad_out      the VJP of rotate_back_scatter (needs y), one edge per warp group
+//   rotate_in_bwd        the VJP of rotate_in, one edge per warp group, per-edge node contributions
+//   node_reduce          fixed-order sums of those contributions per destination / source node
 //
 // They take over blocks/eso2_ref.py:334-335 (gather + rotate in, with the radial gain of
 // :269-271, :284-285 applied while the row is in registers) and :343-349 (envelope, rotate
@@ -206,276 +206,270 @@ rotate_back_scatter_kernel(const __grid_constant__ ZpTables t, int64_t N,
   }
 }
 
-// ---- VJP of rotate_back_scatter -------------------------------------------------------------
-//   t[r]        = sum_j rot[r, j] g[n, l^2 + j]          (g = grad of node_out, row n = dst)
-//   dy[e, r]    = env_e * t[r]
+// ------------------------------------------------------------------------------------------
+// per-edge backward kernels: blockDim = 256; W warps cover one edge's channel groups, 8 / W
+// edges per block.  Channel reductions (the 2l+1 rotation-gradient entries of a row) are done
+// as batches of independent warp sums so the shuffles pipeline.
+// ------------------------------------------------------------------------------------------
+constexpr int kEdgeThreads = 256;
+
+template <int N>
+__device__ __forceinline__ void warp_sum_n(float (&p)[N]) {
+#pragma unroll
+  for (int o = 16; o > 0; o >>= 1)
+#pragma unroll
+    for (int j = 0; j < N; ++j) p[j] += __shfl_xor_sync(0xffffffffu, p[j], o);
+}
+
+// ---- VJP of rotate_back_scatter, one edge per warp group ----------------------------------
+//   t[r]        = sum_j rot[r, j] g[dst, l^2 + j]        (g = grad of node_out)
+//   dy[e, r]    = env_e * t[r]                            (written as bf16 planes)
 //   grad_env[e] = sum_{r, c} y[e, r, c] t[r, c]
-//   grad_rot[e, r, j] = env_e * sum_c y[e, r, c] g[n, l^2 + j, c]
-template <int L, int LMAX, int VEC>
-struct GradOut {
-  static __device__ __forceinline__ void run(const ZpTables &t, const float *y_e,
-                                             const ZpPlanes &dy, int64_t dy_row,
-                                             const float *rot_s, float *grot_s, float env,
-                                             const float (&g)[(LMAX + 1) * (LMAX + 1)][VEC],
-                                             float &genv, int c, bool active, bool lane0) {
-    GradOut<L - 1, LMAX, VEC>::run(t, y_e, dy, dy_row, rot_s, grot_s, env, g, genv, c, active, lane0);
+//   grad_rot[e, r, j] = env_e * sum_c y[e, r, c] g[dst, l^2 + j, c]
+template <int L, int LMAX>
+struct GradOutE {
+  static __device__ __forceinline__ void run(const ZpTables &t, const float *g_row, const float *y_e,
+                                             const ZpPlanes &dy, int64_t dy_row, const float *rot_s,
+                                             float *part_s, float env, float &genv, int c,
+                                             bool active, int lane) {
+    GradOutE<L - 1, LMAX>::run(t, g_row, y_e, dy, dy_row, rot_s, part_s, env, genv, c, active, lane);
     constexpr int n = 2 * L + 1;
     const int mm = t.mmax < L ? t.mmax : L;
+    float g[n][4];
+#pragma unroll
+    for (int j = 0; j < n; ++j) {
+#pragma unroll
+      for (int v = 0; v < 4; ++v) g[j][v] = 0.f;
+      if (active) vload<4>(g[j], g_row + (size_t)(L * L + j) * t.C);
+    }
 #pragma unroll
     for (int i = 0; i < n; ++i) {
       const int am = i > L ? i - L : L - i;
       if (am <= mm) {
         const int r = t.row_of[L][i];
         const float *rr = rot_s + t.rot_off[r];
-        float yv[VEC], tv[VEC];
-#pragma unroll
-        for (int v = 0; v < VEC; ++v) { yv[v] = 0.f; tv[v] = 0.f; }
-        if (active) vload<VEC>(yv, y_e + (size_t)r * t.C + c);
+        float yv[4] = {0.f, 0.f, 0.f, 0.f}, tv[4] = {0.f, 0.f, 0.f, 0.f}, part[n];
+        if (active) vload<4>(yv, y_e + (size_t)r * t.C + c);
 #pragma unroll
         for (int j = 0; j < n; ++j) {
           const float w = rr[j];
-          float part = 0.f;
+          float s = 0.f;
 #pragma unroll
-          for (int v = 0; v < VEC; ++v) {
-            tv[v] = fmaf(w, g[L * L + j][v], tv[v]);
-            part = fmaf(yv[v], g[L * L + j][v], part);
+          for (int v = 0; v < 4; ++v) {
+            tv[v] = fmaf(w, g[j][v], tv[v]);
+            s = fmaf(yv[v], g[j][v], s);
           }
-          part = warp_sum(part);
-          if (lane0) grot_s[t.rot_off[r] + j] = env * part;
+          part[j] = s;
+        }
+        warp_sum_n<n>(part);
+        if (lane == 0) {
+#pragma unroll
+          for (int j = 0; j < n; ++j) part_s[t.rot_off[r] + j] = part[j];
         }
 #pragma unroll
-        for (int v = 0; v < VEC; ++v) {
+        for (int v = 0; v < 4; ++v) {
           genv = fmaf(yv[v], tv[v], genv);
           tv[v] *= env;
         }
-        if (active) zp_store_planes<VEC>(dy, dy_row + (int64_t)r * t.C + c, tv);
+        if (active) zp_store_planes<4>(dy, dy_row + (int64_t)r * t.C + c, tv);
       }
     }
   }
 };
-template <int LMAX, int VEC>
-struct GradOut<-1, LMAX, VEC> {
-  static __device__ __forceinline__ void run(const ZpTables &, const float *, const ZpPlanes &,
-                                             int64_t, const float *, float *, float,
-                                             const float (&)[(LMAX + 1) * (LMAX + 1)][VEC],
-                                             float &, int, bool, bool) {}
+template <int LMAX>
+struct GradOutE<-1, LMAX> {
+  static __device__ __forceinline__ void run(const ZpTables &, const float *, const float *,
+                                             const ZpPlanes &, int64_t, const float *, float *,
+                                             float, float &, int, bool, int) {}
 };
 
-// Shared memory per node slot: rot [nnz_pad] | per-warp partial grad_rot [W][nnz_pad] | genv [W]
+// shared memory: rot [epb][nnz_pad] | partial [8 warps][nnz_pad] | genv [8]
 template <int LMAX>
-__global__ void __launch_bounds__(128)
-rotate_grad_out_kernel(const __grid_constant__ ZpTables t, int64_t N,
+__global__ void __launch_bounds__(kEdgeThreads)
+rotate_grad_out_kernel(const __grid_constant__ ZpTables t, int64_t E, int W,
                        const float *__restrict__ g_out, const float *__restrict__ y,
                        const float *__restrict__ env, const float *__restrict__ rot,
-                       const int32_t *__restrict__ row_ptr, const ZpPlanes dy,
+                       const int32_t *__restrict__ dst, const ZpPlanes dy,
                        float *__restrict__ grad_env, float *__restrict__ grad_rot) {
-  constexpr int VEC = VecFor<LMAX>::value;
-  constexpr int K = (LMAX + 1) * (LMAX + 1);
   extern __shared__ float smem[];
-  const int slot = threadIdx.y, nthr = blockDim.x, W = nthr / 32;
+  const int epb = 8 / W;
+  float *rot_s = smem;
+  float *part_all = smem + epb * t.nnz_pad;
+  float *genv_s = part_all + 8 * t.nnz_pad;
   const int warp = threadIdx.x / 32, lane = threadIdx.x % 32;
-  const int per_slot = t.nnz_pad * (1 + W) + W;
-  float *rot_s = smem + slot * per_slot;
-  float *grot_s = rot_s + t.nnz_pad + warp * t.nnz_pad;
-  float *genv_s = rot_s + t.nnz_pad * (1 + W);
-  const int64_t n = (int64_t)blockIdx.x * blockDim.y + slot;
-  if (n >= N) return;
-  const int c = threadIdx.x * VEC;
-  const bool active = c < t.C;
-  float g[K][VEC];
-#pragma unroll
-  for (int k = 0; k < K; ++k) {
-#pragma unroll
-    for (int v = 0; v < VEC; ++v) g[k][v] = 0.f;
-    if (active) vload<VEC>(g[k], g_out + ((size_t)n * K + k) * t.C + c);
-  }
-  const int e_beg = row_ptr[n], e_end = row_ptr[n + 1];
-  for (int e = e_beg; e < e_end; ++e) {
-    slot_sync(slot, nthr);
-    stage_rot(t, rot + (size_t)e * t.nnz_pad, rot_s, threadIdx.x, nthr);
-    slot_sync(slot, nthr);
-    float genv = 0.f;
-    GradOut<LMAX, LMAX, VEC>::run(t, y + (size_t)e * t.Km * t.C, dy, (int64_t)e * dy.ld,
-                                  rot_s, grot_s, env[e], g, genv, c, active, lane == 0);
+  const int slot = warp / W, wsub = warp % W;
+  const int64_t e0 = (int64_t)blockIdx.x * epb;
+  const int n_e = (int)min((int64_t)epb, E - e0);
+  for (int i = threadIdx.x; i < n_e * t.nnz_pad; i += blockDim.x) rot_s[i] = rot[e0 * t.nnz_pad + i];
+  __syncthreads();
+  const bool edge_ok = slot < n_e;
+  const int64_t e = e0 + (edge_ok ? slot : 0);
+  const int c = (wsub * 32 + lane) * 4;
+  const bool active = edge_ok && c < t.C;
+  float genv = 0.f;
+  if (edge_ok) {
+    const float *g_row = g_out + (size_t)dst[e] * t.K * t.C + c;
+    GradOutE<LMAX, LMAX>::run(t, g_row, y + (size_t)e * t.Km * t.C, dy, e * dy.ld,
+                              rot_s + slot * t.nnz_pad, part_all + warp * t.nnz_pad, env[e], genv,
+                              c, active, lane);
     genv = warp_sum(genv);
     if (lane == 0) genv_s[warp] = genv;
-    slot_sync(slot, nthr);
-    // fixed-order sum over the W warps
-    for (int i = threadIdx.x; i < t.nnz_pad; i += nthr) {
-      float s = 0.f;
-      if (i < t.nnz)
-        for (int w = 0; w < W; ++w) s += rot_s[t.nnz_pad * (1 + w) + i];
-      grad_rot[(size_t)e * t.nnz_pad + i] = s;
-    }
-    if (threadIdx.x == 0) {
-      float s = 0.f;
-      for (int w = 0; w < W; ++w) s += genv_s[w];
-      grad_env[e] = s;
-    }
+  }
+  __syncthreads();
+  // fixed-order sum over the W warps of each edge
+  for (int i = threadIdx.x; i < n_e * t.nnz_pad; i += blockDim.x) {
+    const int s = i / t.nnz_pad, k = i % t.nnz_pad;
+    float acc = 0.f;
+    if (k < t.nnz)
+      for (int w = 0; w < W; ++w) acc += part_all[(s * W + w) * t.nnz_pad + k];
+    grad_rot[(e0 + s) * t.nnz_pad + k] = acc * env[e0 + s];
+  }
+  if (threadIdx.x < n_e) {
+    float acc = 0.f;
+    for (int w = 0; w < W; ++w) acc += genv_s[threadIdx.x * W + w];
+    grad_env[e0 + threadIdx.x] = acc;
   }
 }
 
-// ---- VJP of rotate_in -----------------------------------------------------------------------
+// ---- VJP of rotate_in, one edge per warp group over the 2C message channels --------------------
 //   a[r]   = sum_j rot[r, j] u[l^2 + j]            (recomputed; u = x_src | x_dst half)
 //   ga[r]  = da[e, r] * radial
 //   grad_radial[e, col] = sum over the +m / -m rows sharing the column of  da[r] * a[r]
-//   du[l^2 + j] = sum_r rot[r, j] ga[r]   -> du_src[e] (source half) or the node's own sum
+//   du[e, half, l^2 + j] = sum_r rot[r, j] ga[r]   (summed per node afterwards)
 //   grad_rot[e, r, j] += sum_c2 ga[r, c2] u[l^2 + j, c2]
-template <int L, int LMAX, int VEC>
-struct RotInBwd {
+template <int L, int LMAX>
+struct RotInBwdE {
   static __device__ __forceinline__ void run(const ZpTables &t, const float *xrow,
                                              const float *da_e, const float *rad_e,
-                                             float *grad_e, const float *rot_s, float *grot_s,
-                                             float *du_e,
-                                             float (&gx)[(LMAX + 1) * (LMAX + 1)][VEC], int c,
-                                             int half, bool active, bool lane0) {
-    RotInBwd<L - 1, LMAX, VEC>::run(t, xrow, da_e, rad_e, grad_e, rot_s, grot_s, du_e, gx, c,
-                                    half, active, lane0);
+                                             float *grad_e, const float *rot_s, float *part_s,
+                                             float *du_row, int c2, bool active, int lane) {
+    RotInBwdE<L - 1, LMAX>::run(t, xrow, da_e, rad_e, grad_e, rot_s, part_s, du_row, c2, active, lane);
     constexpr int n = 2 * L + 1;
     const int C2 = 2 * t.C;
-    const int c2 = half * t.C + c;
     const int mm = t.mmax < L ? t.mmax : L;
-    float u[n][VEC], du[n][VEC];
+    float u[n][4], du[n][4];
 #pragma unroll
     for (int j = 0; j < n; ++j) {
 #pragma unroll
-      for (int v = 0; v < VEC; ++v) { u[j][v] = 0.f; du[j][v] = 0.f; }
-      if (active) vload<VEC>(u[j], xrow + (size_t)(L * L + j) * t.C);
+      for (int v = 0; v < 4; ++v) { u[j][v] = 0.f; du[j][v] = 0.f; }
+      if (active) vload<4>(u[j], xrow + (size_t)(L * L + j) * t.C);
     }
-    // rows i = L + m and L - m share one radial column; walk m = 0..mm and both signs
 #pragma unroll
     for (int am = 0; am <= L; ++am) {
       if (am <= mm) {
-        float gr[VEC], rad[VEC];
-#pragma unroll
-        for (int v = 0; v < VEC; ++v) { gr[v] = 0.f; rad[v] = 0.f; }
+        float gr[4] = {0.f, 0.f, 0.f, 0.f}, rad[4] = {0.f, 0.f, 0.f, 0.f};
         const int col = t.rad_off[am] + (L - am) * C2 + c2;
-        if (active) vload<VEC>(rad, rad_e + col);
+        if (active) vload<4>(rad, rad_e + col);
 #pragma unroll
         for (int sgn = 0; sgn < 2; ++sgn) {
           if (sgn == 1 && am == 0) continue;
           const int i = sgn == 0 ? L + am : L - am;
           const int r = t.row_of[L][i];
           const float *rr = rot_s + t.rot_off[r];
-          float a[VEC], da[VEC];
-#pragma unroll
-          for (int v = 0; v < VEC; ++v) { a[v] = 0.f; da[v] = 0.f; }
-          if (active) vload<VEC>(da, da_e + (size_t)r * C2 + c2);
+          float a[4] = {0.f, 0.f, 0.f, 0.f}, da[4] = {0.f, 0.f, 0.f, 0.f}, ga[4], part[n];
+          if (active) vload<4>(da, da_e + (size_t)r * C2 + c2);
 #pragma unroll
           for (int j = 0; j < n; ++j)
 #pragma unroll
-            for (int v = 0; v < VEC; ++v) a[v] = fmaf(rr[j], u[j][v], a[v]);
-          float ga[VEC];
+            for (int v = 0; v < 4; ++v) a[v] = fmaf(rr[j], u[j][v], a[v]);
 #pragma unroll
-          for (int v = 0; v < VEC; ++v) {
+          for (int v = 0; v < 4; ++v) {
             gr[v] = fmaf(da[v], a[v], gr[v]);
             ga[v] = da[v] * rad[v];
           }
 #pragma unroll
           for (int j = 0; j < n; ++j) {
-            float part = 0.f;
+            float s = 0.f;
 #pragma unroll
-            for (int v = 0; v < VEC; ++v) {
+            for (int v = 0; v < 4; ++v) {
               du[j][v] = fmaf(rr[j], ga[v], du[j][v]);
-              part = fmaf(ga[v], u[j][v], part);
+              s = fmaf(ga[v], u[j][v], s);
             }
-            part = warp_sum(part);
-            if (lane0) grot_s[t.rot_off[r] + j] += part;
+            part[j] = s;
+          }
+          warp_sum_n<n>(part);
+          if (lane == 0) {
+#pragma unroll
+            for (int j = 0; j < n; ++j) part_s[t.rot_off[r] + j] = part[j];
           }
         }
-        if (active) vstore<VEC>(grad_e + col, gr);
+        if (active) vstore<4>(grad_e + col, gr);
       }
     }
-    if (half == 0) {
-      if (active) {
+    if (active) {
 #pragma unroll
-        for (int j = 0; j < n; ++j) vstore<VEC>(du_e + (size_t)(L * L + j) * t.C + c, du[j]);
-      }
-    } else {
-#pragma unroll
-      for (int j = 0; j < n; ++j)
-#pragma unroll
-        for (int v = 0; v < VEC; ++v) gx[L * L + j][v] += du[j][v];
+      for (int j = 0; j < n; ++j) vstore<4>(du_row + (size_t)(L * L + j) * t.C, du[j]);
     }
   }
 };
-template <int LMAX, int VEC>
-struct RotInBwd<-1, LMAX, VEC> {
+template <int LMAX>
+struct RotInBwdE<-1, LMAX> {
   static __device__ __forceinline__ void run(const ZpTables &, const float *, const float *,
                                              const float *, float *, const float *, float *,
-                                             float *, float (&)[(LMAX + 1) * (LMAX + 1)][VEC],
-                                             int, int, bool, bool) {}
+                                             float *, int, bool, int) {}
 };
 
+// du_both [E][2][K][C]: half 0 = contribution to the source node, half 1 = to the destination
 template <int LMAX>
-__global__ void __launch_bounds__(128)
-rotate_in_bwd_kernel(const __grid_constant__ ZpTables t, int64_t N,
+__global__ void __launch_bounds__(kEdgeThreads)
+rotate_in_bwd_kernel(const __grid_constant__ ZpTables t, int64_t E, int W,
                      const float *__restrict__ da1, const float *__restrict__ radial,
                      const float *__restrict__ x, const int32_t *__restrict__ src,
-                     const float *__restrict__ rot, const int32_t *__restrict__ row_ptr,
-                     float *__restrict__ grad_radial, float *__restrict__ du_src,
-                     float *__restrict__ grad_x, float *__restrict__ grad_rot) {
-  constexpr int VEC = VecFor<LMAX>::value;
-  constexpr int K = (LMAX + 1) * (LMAX + 1);
+                     const int32_t *__restrict__ dst, const float *__restrict__ rot,
+                     float *__restrict__ grad_radial, float *__restrict__ du_both,
+                     float *__restrict__ grad_rot) {
   extern __shared__ float smem[];
-  const int slot = threadIdx.y, nthr = blockDim.x, W = nthr / 32;
+  const int epb = 8 / W;
+  float *rot_s = smem;
+  float *part_all = smem + epb * t.nnz_pad;
   const int warp = threadIdx.x / 32, lane = threadIdx.x % 32;
-  const int per_slot = t.nnz_pad * (1 + W);
-  float *rot_s = smem + slot * per_slot;
-  float *grot_s = rot_s + t.nnz_pad + warp * t.nnz_pad;
-  const int64_t n = (int64_t)blockIdx.x * blockDim.y + slot;
-  if (n >= N) return;
-  const int c = threadIdx.x * VEC;
-  const bool active = c < t.C;
-  float gx[K][VEC];
-#pragma unroll
-  for (int k = 0; k < K; ++k)
-#pragma unroll
-    for (int v = 0; v < VEC; ++v) gx[k][v] = 0.f;
-  const int e_beg = row_ptr[n], e_end = row_ptr[n + 1];
-  for (int e = e_beg; e < e_end; ++e) {
-    slot_sync(slot, nthr);
-    stage_rot(t, rot + (size_t)e * t.nnz_pad, rot_s, threadIdx.x, nthr);
-    if (lane == 0)
-      for (int i = 0; i < t.nnz_pad; ++i) grot_s[i] = 0.f;
-    slot_sync(slot, nthr);
-    const float *da_e = da1 + (size_t)e * t.Km * 2 * t.C;
-    const float *rad_e = radial + (size_t)e * t.R;
-    float *grad_e = grad_radial + (size_t)e * t.R;
-    float *du_e = du_src + (size_t)e * K * t.C;
-    const float *x_s = x + (size_t)src[e] * K * t.C + c;
-    const float *x_d = x + (size_t)n * K * t.C + c;
-    RotInBwd<LMAX, LMAX, VEC>::run(t, x_s, da_e, rad_e, grad_e, rot_s, grot_s, du_e, gx, c, 0,
-                                   active, lane == 0);
-    RotInBwd<LMAX, LMAX, VEC>::run(t, x_d, da_e, rad_e, grad_e, rot_s, grot_s, du_e, gx, c, 1,
-                                   active, lane == 0);
-    slot_sync(slot, nthr);
-    for (int i = threadIdx.x; i < t.nnz; i += nthr) {
-      float s = 0.f;
-      for (int w = 0; w < W; ++w) s += rot_s[t.nnz_pad * (1 + w) + i];
-      grad_rot[(size_t)e * t.nnz_pad + i] += s;
-    }
+  const int slot = warp / W, wsub = warp % W;
+  const int64_t e0 = (int64_t)blockIdx.x * epb;
+  const int n_e = (int)min((int64_t)epb, E - e0);
+  for (int i = threadIdx.x; i < n_e * t.nnz_pad; i += blockDim.x) rot_s[i] = rot[e0 * t.nnz_pad + i];
+  __syncthreads();
+  const bool edge_ok = slot < n_e;
+  const int64_t e = e0 + (edge_ok ? slot : 0);
+  const int c2 = (wsub * 32 + lane) * 4;
+  const bool active = edge_ok && c2 < 2 * t.C;
+  if (edge_ok) {
+    const int half = c2 >= t.C ? 1 : 0;
+    const int c = c2 - half * t.C;
+    const int64_t node = half ? dst[e] : src[e];
+    const float *xrow = x + (size_t)node * t.K * t.C + c;
+    float *du_row = du_both + ((size_t)e * 2 + half) * t.K * t.C + c;
+    RotInBwdE<LMAX, LMAX>::run(t, xrow, da1 + (size_t)e * t.Km * 2 * t.C, radial + (size_t)e * t.R,
+                               grad_radial + (size_t)e * t.R, rot_s + slot * t.nnz_pad,
+                               part_all + warp * t.nnz_pad, du_row, c2, active, lane);
   }
-  if (active) {
-    float *o = grad_x + (size_t)n * K * t.C + c;
-#pragma unroll
-    for (int k = 0; k < K; ++k) vstore<VEC>(o + (size_t)k * t.C, gx[k]);
+  __syncthreads();
+  for (int i = threadIdx.x; i < n_e * t.nnz_pad; i += blockDim.x) {
+    const int s = i / t.nnz_pad, k = i % t.nnz_pad;
+    if (k >= t.nnz) continue;
+    float acc = 0.f;
+    for (int w = 0; w < W; ++w) acc += part_all[(s * W + w) * t.nnz_pad + k];
+    grad_rot[(e0 + s) * t.nnz_pad + k] += acc;
   }
 }
 
-// grad_x[n] += sum of du_src over the edges whose SOURCE is n, in source-sorted order
+// grad_x[n] = sum over edges INTO n of du_both[e][1]  +  sum over edges OUT OF n of du_both[e][0],
+// both in fixed (sorted) order.
 __global__ void __launch_bounds__(128)
-src_reduce_kernel(int64_t N, int KC4, const float4 *__restrict__ du_src,
-                  const int32_t *__restrict__ perm_src, const int32_t *__restrict__ row_ptr_src,
-                  float4 *__restrict__ grad_x) {
+node_reduce_kernel(int64_t N, int KC4, const float4 *__restrict__ du_both,
+                   const int32_t *__restrict__ row_ptr, const int32_t *__restrict__ perm_src,
+                   const int32_t *__restrict__ row_ptr_src, float4 *__restrict__ grad_x) {
   const int64_t n = blockIdx.x;
   if (n >= N) return;
-  const int beg = row_ptr_src[n], end = row_ptr_src[n + 1];
-  if (beg == end) return;
+  const int beg = row_ptr[n], end = row_ptr[n + 1];
+  const int sbeg = row_ptr_src[n], send = row_ptr_src[n + 1];
   for (int i = threadIdx.x; i < KC4; i += blockDim.x) {
-    float4 acc = grad_x[(size_t)n * KC4 + i];
-    for (int k = beg; k < end; ++k) {
-      const float4 v = du_src[(size_t)perm_src[k] * KC4 + i];
+    float4 acc = make_float4(0.f, 0.f, 0.f, 0.f);
+    for (int e = beg; e < end; ++e) {
+      const float4 v = du_both[((size_t)e * 2 + 1) * KC4 + i];
+      acc.x += v.x; acc.y += v.y; acc.z += v.z; acc.w += v.w;
+    }
+    for (int k = sbeg; k < send; ++k) {
+      const float4 v = du_both[((size_t)perm_src[k] * 2) * KC4 + i];
       acc.x += v.x; acc.y += v.y; acc.z += v.z; acc.w += v.w;
     }
     grad_x[(size_t)n * KC4 + i] = acc;
@@ -541,55 +535,59 @@ int zp_launch_rotate_back_scatter(const zp_plan *p, int64_t N, const float *y, c
   return ZP_OK;
 }
 
-int zp_launch_rotate_grad_out(const zp_plan *p, int64_t N, const float *g, const float *y,
-                              const float *env, const float *rot, const int32_t *row_ptr,
+// warps per edge for `quads` channel quads (1, 2 or 4), or 0 if unsupported
+static int warps_per_edge(int quads) {
+  const int w = (quads + 31) / 32;
+  return w <= 1 ? 1 : w == 2 ? 2 : w <= 4 ? 4 : 0;
+}
+
+int zp_launch_rotate_grad_out(const zp_plan *p, int64_t E, const float *g, const float *y,
+                              const float *env, const float *rot, const int32_t *dst,
                               const ZpPlanes &dy, float *grad_env, float *grad_rot,
                               cudaStream_t st) {
-  if (N == 0) return ZP_OK;
+  if (E == 0) return ZP_OK;
   const ZpTables &t = p->t;
-#define CALL(LM)                                                                            \
-  {                                                                                         \
-    const NodeLaunch nl = node_launch<LM>(t, N);                                            \
-    if (nl.W > 4) return ZP_ERR_UNSUPPORTED;                                                \
-    const size_t smem =                                                                     \
-        (size_t)nl.block.y * (t.nnz_pad * (1 + nl.W) + nl.W) * sizeof(float);               \
-    rotate_grad_out_kernel<LM><<<nl.grid, nl.block, smem, st>>>(t, N, g, y, env, rot,       \
-                                                                row_ptr, dy, grad_env,     \
-                                                                grad_rot);                  \
-  }
+  const int W = warps_per_edge(t.C / 4);
+  if (!W) return ZP_ERR_UNSUPPORTED;
+  const int epb = 8 / W;
+  const dim3 grid((unsigned)zp_ceil_div(E, epb));
+  const size_t smem = ((size_t)(epb + 8) * t.nnz_pad + 8) * sizeof(float);
+#define CALL(LM)                                                                              \
+  rotate_grad_out_kernel<LM><<<grid, kEdgeThreads, smem, st>>>(t, E, W, g, y, env, rot, dst, dy, \
+                                                               grad_env, grad_rot)
   ZP_DISPATCH_LMAX(t.lmax, CALL)
 #undef CALL
   ZP_LAUNCH_CHECK("rotate_grad_out_kernel");
   return ZP_OK;
 }
 
-int zp_launch_rotate_in_bwd(const zp_plan *p, int64_t N, const float *da1, const float *radial,
-                            const float *x, const int32_t *src, const float *rot,
-                            const int32_t *row_ptr, float *grad_radial, float *du_src,
-                            float *grad_x, float *grad_rot, cudaStream_t st) {
-  if (N == 0) return ZP_OK;
+int zp_launch_rotate_in_bwd(const zp_plan *p, int64_t E, const float *da1, const float *radial,
+                            const float *x, const int32_t *src, const int32_t *dst,
+                            const float *rot, float *grad_radial, float *du_both, float *grad_rot,
+                            cudaStream_t st) {
+  if (E == 0) return ZP_OK;
   const ZpTables &t = p->t;
-#define CALL(LM)                                                                          \
-  {                                                                                       \
-    const NodeLaunch nl = node_launch<LM>(t, N);                                          \
-    if (nl.W > 4) return ZP_ERR_UNSUPPORTED;                                              \
-    const size_t smem = (size_t)nl.block.y * t.nnz_pad * (1 + nl.W) * sizeof(float);      \
-    rotate_in_bwd_kernel<LM><<<nl.grid, nl.block, smem, st>>>(                            \
-        t, N, da1, radial, x, src, rot, row_ptr, grad_radial, du_src, grad_x, grad_rot);  \
-  }
+  const int W = warps_per_edge(t.C / 2);
+  if (!W) return ZP_ERR_UNSUPPORTED;
+  const int epb = 8 / W;
+  const dim3 grid((unsigned)zp_ceil_div(E, epb));
+  const size_t smem = (size_t)(epb + 8) * t.nnz_pad * sizeof(float);
+#define CALL(LM)                                                                               \
+  rotate_in_bwd_kernel<LM><<<grid, kEdgeThreads, smem, st>>>(t, E, W, da1, radial, x, src, dst, \
+                                                             rot, grad_radial, du_both, grad_rot)
   ZP_DISPATCH_LMAX(t.lmax, CALL)
 #undef CALL
   ZP_LAUNCH_CHECK("rotate_in_bwd_kernel");
   return ZP_OK;
 }
 
-int zp_launch_src_reduce(const zp_plan *p, int64_t N, const float *du_src,
-                         const int32_t *perm_src, const int32_t *row_ptr_src, float *grad_x,
-                         cudaStream_t st) {
+int zp_launch_node_reduce(const zp_plan *p, int64_t N, const float *du_both,
+                          const int32_t *row_ptr, const int32_t *perm_src,
+                          const int32_t *row_ptr_src, float *grad_x, cudaStream_t st) {
   if (N == 0) return ZP_OK;
   const int KC4 = p->t.K * p->t.C / 4;
-  src_reduce_kernel<<<(unsigned)N, 128, 0, st>>>(N, KC4, (const float4 *)du_src, perm_src,
-                                                 row_ptr_src, (float4 *)grad_x);
-  ZP_LAUNCH_CHECK("src_reduce_kernel");
+  node_reduce_kernel<<<(unsigned)N, 128, 0, st>>>(N, KC4, (const float4 *)du_both, row_ptr,
+                                                  perm_src, row_ptr_src, (float4 *)grad_x);
+  ZP_LAUNCH_CHECK("node_reduce_kernel");
   return ZP_OK;
 }

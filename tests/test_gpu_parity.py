@@ -84,6 +84,28 @@ def test_bf16_operands_fp32_accumulate(lmax, mmax, c, h, n, e, jd64):
     assert block.plan("cuda").device_status() == 0
 
 
+def test_chunked_execution_matches(jd64, monkeypatch):
+    """Graphs larger than the per-call edge budget run as destination-node chunks with the
+    forward recomputed in the backward; results must not change beyond summation order."""
+    from zippel_b200.blocks import eso2
+    cfg = dict(lmax=4, mmax=2, sphere_channels=16, hidden_channels=8, edge_channels=8,
+               num_distance_basis=6, cutoff=5.0)
+    params = orc.init_params(cfg, seed=31)
+    case = random_case(cfg, 30, 400, seed=32)
+    case["edge_index"][1, :90] = 11                      # one node above the budget on its own
+    case["edge_index"][0, :90] = (torch.arange(90) % 29 + 12) % 30
+    want = oracle_node_out_and_vjp(cfg, params, case, case["upstream"], jd64)
+    block = make_block(cfg, params)
+    monkeypatch.setattr(eso2, "MAX_EDGES_PER_CALL", 64)
+    from zippel_b200.graph import EdgeGraph
+    graph = EdgeGraph.build(case["edge_index"].cuda(), 30)
+    pieces = graph.chunks(64)
+    assert len(pieces) > 4 and pieces[0].n0 == 0 and pieces[-1].n1 == 30
+    assert all(a.n1 == b.n0 and a.e1 == b.e0 for a, b in zip(pieces, pieces[1:]))
+    got = gpu_node_out_and_vjp(block, case, case["upstream"])
+    check_against(*got, *want)
+
+
 def test_nodes_without_edges_and_empty_graph(jd64):
     cfg = dict(lmax=2, mmax=1, sphere_channels=8, hidden_channels=8, edge_channels=4,
                num_distance_basis=4, cutoff=5.0)

@@ -168,6 +168,43 @@ def _f32(t: torch.Tensor) -> torch.Tensor:
     return t.detach().to(torch.float32).contiguous()
 
 
+#: Upper bound on the edges handed to one forward/backward call of the C ABI.  ``None`` sizes it
+#: from the device's free memory (the per-call workspace is ~140 KB per edge at lmax 4 / C 128).
+#: Larger graphs are processed as destination-node chunks; the backward then recomputes each
+#: chunk's forward instead of keeping every chunk's activations.
+MAX_EDGES_PER_CALL: int | None = None
+
+
+def _edge_budget(plan: Plan, n: int, e: int) -> int:
+    if MAX_EDGES_PER_CALL is not None:
+        return max(1, MAX_EDGES_PER_CALL)
+    lib = _lib.load()
+    probe = 4096
+    per_edge = (lib.zp_workspace_bytes(plan.handle, n, probe, 1)
+                - lib.zp_workspace_bytes(plan.handle, n, 0, 1)) / probe
+    free, _total = torch.cuda.mem_get_info(plan.device)
+    return max(1024, int(0.6 * free / max(per_edge, 1.0)))
+
+
+def _abi_forward(plan, n_rows, e, x, ev, cg, sg, rad, en, src, dst, row_ptr, wstruct, out, ws):
+    st = torch.cuda.current_stream().cuda_stream
+    _lib.check(_lib.load().zp_eso2_forward(
+        plan.handle, n_rows, e, x.data_ptr(), ev.data_ptr(), cg.data_ptr(), sg.data_ptr(),
+        rad.data_ptr(), en.data_ptr(), src.data_ptr(), dst.data_ptr(), row_ptr.data_ptr(),
+        ctypes.byref(wstruct), out.data_ptr(), ws.data_ptr(), ws.numel(), st), "zp_eso2_forward")
+
+
+def _abi_backward(plan, n, e, g, x, ev, cg, sg, rad, en, sub: EdgeGraph, wstruct, gx, gev, grad,
+                  gen, gstruct, ws):
+    st = torch.cuda.current_stream().cuda_stream
+    _lib.check(_lib.load().zp_eso2_backward(
+        plan.handle, n, e, g.data_ptr(), x.data_ptr(), ev.data_ptr(), cg.data_ptr(),
+        sg.data_ptr(), rad.data_ptr(), en.data_ptr(), sub.src.data_ptr(), sub.dst.data_ptr(),
+        sub.row_ptr.data_ptr(), sub.perm_src.data_ptr(), sub.row_ptr_src.data_ptr(),
+        ctypes.byref(wstruct), gx.data_ptr(), gev.data_ptr(), grad.data_ptr(), gen.data_ptr(),
+        ctypes.byref(gstruct), ws.data_ptr(), ws.numel(), st), "zp_eso2_backward")
+
+
 class EdgeConvFunction(torch.autograd.Function):
     """node_out = edge_conv(x_node, edge_vec, cos_g, sin_g, radial, env; SO(2) weights).
 
@@ -178,12 +215,10 @@ class EdgeConvFunction(torch.autograd.Function):
     @staticmethod
     def forward(ctx, plan: Plan, graph: EdgeGraph, x_node, edge_vec, cos_g, sin_g, radial, env,
                 c1_w0, c1_b0, c2_w0, c2_b0, *wm):
-        lib = _lib.load()
         mmax = plan.mmax
-        c1_wm, c2_wm = wm[:mmax], wm[mmax:]
         n, e = graph.n_nodes, graph.n_edges
-        tens = [_f32(t) for t in (x_node, edge_vec, cos_g, sin_g, radial, env, c1_w0, c1_b0,
-                                  c2_w0, c2_b0, *wm)]
+        ins = (x_node, edge_vec, cos_g, sin_g, radial, env, c1_w0, c1_b0, c2_w0, c2_b0, *wm)
+        tens = [_f32(t) for t in ins]
         x, ev, cg, sg, rad, en, w10, b10, w20, b20 = tens[:10]
         wms = tens[10:]
         s = plan.sizes
@@ -191,29 +226,33 @@ class EdgeConvFunction(torch.autograd.Function):
         assert rad.shape == (e, s.R) and ev.shape == (e, 3) and en.shape == (e,)
         assert cg.shape == (e, plan.lmax + 1) and sg.shape == cg.shape
         needs_bwd = any(ctx.needs_input_grad)
-        ws = plan.workspace(n, e, needs_bwd)
         out = torch.empty(n, s.K, plan.c, dtype=torch.float32, device=x.device)
         wstruct, keep = _weights_struct(mmax, w10, b10, wms[:mmax], w20, b20, wms[mmax:])
         with torch.cuda.device(x.device):
-            st = torch.cuda.current_stream().cuda_stream
-            _lib.check(lib.zp_eso2_forward(
-                plan.handle, n, e, x.data_ptr(), ev.data_ptr(), cg.data_ptr(), sg.data_ptr(),
-                rad.data_ptr(), en.data_ptr(), graph.src.data_ptr(), graph.dst.data_ptr(),
-                graph.row_ptr.data_ptr(), ctypes.byref(wstruct), out.data_ptr(), ws.data_ptr(),
-                ws.numel(), st), "zp_eso2_forward")
+            chunks = graph.chunks(_edge_budget(plan, n, e))
+            if len(chunks) == 1:
+                ws = plan.workspace(n, e, needs_bwd)
+                _abi_forward(plan, n, e, x, ev, cg, sg, rad, en, graph.src, graph.dst,
+                             graph.row_ptr, wstruct, out, ws)
+            else:
+                ws = plan.workspace(n, max(c.n_edges for c in chunks), False)
+                for c in chunks:
+                    sl = slice(c.e0, c.e1)
+                    _abi_forward(plan, c.n1 - c.n0, c.n_edges, x, ev[sl], cg[sl], sg[sl], rad[sl],
+                                 en[sl], c.sub.src, c.sub.dst, c.sub.row_ptr[c.n0:],
+                                 wstruct, out[c.n0:c.n1], ws)
+                ws = None
         del keep
         if needs_bwd:
-            ctx.plan, ctx.graph, ctx.ws = plan, graph, ws
+            ctx.plan, ctx.graph, ctx.ws, ctx.chunks = plan, graph, ws, chunks
             ctx.save_for_backward(*tens)
-            ctx.in_dtypes = [t.dtype for t in (x_node, edge_vec, cos_g, sin_g, radial, env, c1_w0,
-                                               c1_b0, c2_w0, c2_b0, *wm)]
+            ctx.in_dtypes = [t.dtype for t in ins]
         return out.to(x_node.dtype)
 
     @staticmethod
     @torch.autograd.function.once_differentiable
     def backward(ctx, grad_out):
-        lib = _lib.load()
-        plan, graph, ws = ctx.plan, ctx.graph, ctx.ws
+        plan, graph, ws, chunks = ctx.plan, ctx.graph, ctx.ws, ctx.chunks
         tens = ctx.saved_tensors
         x, ev, cg, sg, rad, en, w10, b10, w20, b20 = tens[:10]
         wms = tens[10:]
@@ -226,14 +265,33 @@ class EdgeConvFunction(torch.autograd.Function):
         gstruct, keep2 = _weights_struct(mmax, gws[0], gws[1], gws[4:4 + mmax], gws[2], gws[3],
                                          gws[4 + mmax:])
         with torch.cuda.device(x.device):
-            st = torch.cuda.current_stream().cuda_stream
-            _lib.check(lib.zp_eso2_backward(
-                plan.handle, n, e, g.data_ptr(), x.data_ptr(), ev.data_ptr(), cg.data_ptr(),
-                sg.data_ptr(), rad.data_ptr(), en.data_ptr(), graph.src.data_ptr(),
-                graph.dst.data_ptr(), graph.row_ptr.data_ptr(), graph.perm_src.data_ptr(),
-                graph.row_ptr_src.data_ptr(), ctypes.byref(wstruct), gx.data_ptr(),
-                gev.data_ptr(), grad.data_ptr(), gen.data_ptr(), ctypes.byref(gstruct),
-                ws.data_ptr(), ws.numel(), st), "zp_eso2_backward")
+            if len(chunks) == 1:
+                _abi_backward(plan, n, e, g, x, ev, cg, sg, rad, en, graph, wstruct, gx, gev, grad,
+                              gen, gstruct, ws)
+            else:
+                # per chunk: recompute its forward into the shared workspace, then its backward;
+                # node and weight gradients add up over chunks, per-edge gradients are slices
+                ws = plan.workspace(n, max(c.n_edges for c in chunks), True)
+                gx_c = torch.empty_like(gx)
+                gws_c = [torch.empty_like(t) for t in gws]
+                cstruct, keep3 = _weights_struct(mmax, gws_c[0], gws_c[1], gws_c[4:4 + mmax],
+                                                 gws_c[2], gws_c[3], gws_c[4 + mmax:])
+                scratch_out = torch.empty(max(c.n1 - c.n0 for c in chunks), plan.sizes.K, plan.c,
+                                          dtype=torch.float32, device=x.device)
+                for i, c in enumerate(chunks):
+                    sl = slice(c.e0, c.e1)
+                    _abi_forward(plan, c.n1 - c.n0, c.n_edges, x, ev[sl], cg[sl], sg[sl], rad[sl],
+                                 en[sl], c.sub.src, c.sub.dst, c.sub.row_ptr[c.n0:], wstruct,
+                                 scratch_out, ws)
+                    first = i == 0
+                    _abi_backward(plan, n, c.n_edges, g, x, ev[sl], cg[sl], sg[sl], rad[sl], en[sl],
+                                  c.sub, wstruct, gx if first else gx_c, gev[sl], grad[sl], gen[sl],
+                                  gstruct if first else cstruct, ws)
+                    if not first:
+                        gx.add_(gx_c)
+                        for a_, b_ in zip(gws, gws_c):
+                            a_.add_(b_)
+                del keep3
         del keep, keep2
         ctx.ws = None
         grads = [gx, gev, None, None, grad, gen, *gws]

@@ -98,7 +98,7 @@ Workspace carve(const zp_plan *p, int64_t N, int64_t E, int with_backward, void 
     w.du_src = takef(e * 2 * t.K * t.C);
     w.grot = takef(e * t.nnz_pad);
     w.wgrad = takef((size_t)kMaxWgradSplits * p->g_elems);
-    w.scratch = takef((size_t)zp_ceil_div(E > 0 ? E : 1, 256) * (size_t)t.w1_cols);
+    w.scratch = takef((size_t)zp_ceil_div(E > 0 ? E : 1, 128) * (size_t)t.w1_cols);   // column-sum partials
   }
   w.bytes = off;
   return w;

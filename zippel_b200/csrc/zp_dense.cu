@@ -168,17 +168,43 @@ __global__ void unfold_kernel(int out, int in, int folded, int splits, int64_t s
   gw[idx] = acc;
 }
 
-// column sums in two fixed-order stages
-constexpr int kColRowsPerBlock = 256;
-__global__ void colsum_part_kernel(int64_t rows, int64_t cols, const ZpPlanes a,
-                                   float *__restrict__ part) {
-  const int64_t c = (int64_t)blockIdx.x * blockDim.x + threadIdx.x;
-  if (c >= cols) return;
+// column sums in two fixed-order stages.  Stage one: a block of 32 x 8 threads sums 128 rows of
+// 256 columns; a thread owns 8 consecutive columns (one 16-byte load per row and plane) and every
+// eighth row, the eight row groups are then added in order through shared memory.
+constexpr int kColRowsPerBlock = 128;
+__global__ void __launch_bounds__(256)
+colsum_part_kernel(int64_t rows, int64_t cols, const ZpPlanes a, float *__restrict__ part) {
+  __shared__ float red[8][32][9];
+  const int tx = threadIdx.x, ty = threadIdx.y;
+  const int64_t c0 = ((int64_t)blockIdx.x * 32 + tx) * 8;
   const int64_t r0 = (int64_t)blockIdx.y * kColRowsPerBlock;
   const int64_t r1 = min(rows, r0 + kColRowsPerBlock);
-  float s = 0.f;
-  for (int64_t r = r0; r < r1; ++r) s += zp_load_planes(a, r * a.ld + c);
-  part[(size_t)blockIdx.y * cols + c] = s;
+  float s[8] = {0.f, 0.f, 0.f, 0.f, 0.f, 0.f, 0.f, 0.f};
+  if (c0 < cols) {
+    for (int64_t r = r0 + ty; r < r1; r += 8) {
+      for (int pl = a.planes - 1; pl >= 0; --pl) {
+        const uint4 v = *reinterpret_cast<const uint4 *>(a.base + (size_t)pl * a.plane_stride +
+                                                         r * a.ld + c0);
+        const uint32_t w[4] = {v.x, v.y, v.z, v.w};
+#pragma unroll
+        for (int k = 0; k < 4; ++k) {
+          s[2 * k] += __uint_as_float(w[k] << 16);
+          s[2 * k + 1] += __uint_as_float(w[k] & 0xffff0000u);
+        }
+      }
+    }
+  }
+#pragma unroll
+  for (int k = 0; k < 8; ++k) red[ty][tx][k] = s[k];
+  __syncthreads();
+  if (ty == 0 && c0 < cols) {
+#pragma unroll
+    for (int k = 0; k < 8; ++k) {
+      float acc = 0.f;
+      for (int g = 0; g < 8; ++g) acc += red[g][tx][k];
+      if (c0 + k < cols) part[(size_t)blockIdx.y * cols + c0 + k] = acc;
+    }
+  }
 }
 __global__ void colsum_final_kernel(int64_t nparts, int64_t cols, const float *__restrict__ part,
                                     float *__restrict__ out) {
@@ -261,8 +287,8 @@ int zp_launch_colsum(int64_t rows, int64_t cols, const ZpPlanes &a, float *out, 
   if (cols == 0) return ZP_OK;
   const int64_t nparts = rows > 0 ? zp_ceil_div(rows, kColRowsPerBlock) : 0;
   if (nparts > 0) {
-    const dim3 grid((unsigned)zp_ceil_div(cols, 128), (unsigned)nparts);
-    colsum_part_kernel<<<grid, 128, 0, st>>>(rows, cols, a, scratch);
+    const dim3 grid((unsigned)zp_ceil_div(cols, 256), (unsigned)nparts), block(32, 8);
+    colsum_part_kernel<<<grid, block, 0, st>>>(rows, cols, a, scratch);
     ZP_LAUNCH_CHECK("colsum_part_kernel");
   }
   colsum_final_kernel<<<(unsigned)zp_ceil_div(cols, 128), 128, 0, st>>>(nparts, cols, scratch, out);

@@ -53,6 +53,37 @@ class EdgeGraph:
     def perm64(self) -> torch.Tensor:
         return self.perm.long()
 
+    def chunks(self, max_edges: int) -> list["EdgeChunk"]:
+        """Splits the sorted edge list at destination-node boundaries into pieces of at most
+        ``max_edges`` edges (a single node with more incoming edges than that gets a piece of
+        its own).  Each piece carries its own sub-graph: the same node numbering, only its edges.
+        Cached per ``max_edges``."""
+        cache = self.__dict__.setdefault("_chunk_cache", {})
+        if max_edges in cache:
+            return cache[max_edges]
+        if self.n_edges <= max_edges:
+            out = [EdgeChunk(0, self.n_edges, 0, self.n_nodes, self)]
+        else:
+            rp = self.row_ptr.cpu().numpy().astype(np.int64)
+            out, n0 = [], 0
+            while n0 < self.n_nodes:
+                # furthest node boundary n1 > n0 with rp[n1] - rp[n0] <= max_edges
+                n1 = int(np.searchsorted(rp, rp[n0] + max_edges, side="right")) - 1
+                n1 = min(max(n1, n0 + 1), self.n_nodes)
+                if n1 == self.n_nodes or rp[n1] > rp[n0]:
+                    out.append((n0, n1))
+                elif out:
+                    out[-1] = (out[-1][0], n1)
+                n0 = n1
+            pieces = []
+            for n0, n1 in out:
+                e0, e1 = int(rp[n0]), int(rp[n1])
+                ei = torch.stack([self.src[e0:e1].long(), self.dst[e0:e1].long()])
+                pieces.append(EdgeChunk(e0, e1, n0, n1, EdgeGraph.build(ei, self.n_nodes)))
+            out = pieces
+        cache[max_edges] = out
+        return out
+
     @staticmethod
     def build(edge_index: torch.Tensor, n_nodes: int) -> "EdgeGraph":
         """Runs ``zp_csr_build`` on ``edge_index`` ([2, E] int64, CUDA)."""
@@ -73,6 +104,21 @@ class EdgeGraph:
                                         row_ptr_src.data_ptr(), work.data_ptr(), nbytes, st),
                        "zp_csr_build")
         return EdgeGraph(n_nodes, e, perm[:e], src[:e], dst[:e], row_ptr, perm_src[:e], row_ptr_src)
+
+
+@dataclasses.dataclass
+class EdgeChunk:
+    """Edges ``e0:e1`` (all edges into nodes ``n0:n1``) with their own sorted sub-graph."""
+
+    e0: int
+    e1: int
+    n0: int
+    n1: int
+    sub: EdgeGraph
+
+    @property
+    def n_edges(self) -> int:
+        return self.e1 - self.e0
 
 
 # --------------------------------------------------------------------------------------------

@@ -210,6 +210,7 @@ def run_ours(args) -> dict | None:
     from zippel_b200 import _lib
     from zippel_b200.blocks.eso2 import BlockConfig, ESO2Block
     from zippel_b200.graph import EdgeGraph
+    from zippel_b200.partition import all_reduce_grads
     from zippel_b200.runner import EdgeConvRunner
 
     world = int(os.environ.get("WORLD_SIZE", "1"))
@@ -250,16 +251,12 @@ def run_ours(args) -> dict | None:
                 block.c2_m0.bias.detach(), [l.weight.detach() for l in block.c2_m])
     upstream = d["upstream"].contiguous()
     flush = torch.empty(256 << 20, dtype=torch.uint8, device=dev)
-    grad_bucket = None
 
     def kernel_step():
         runner.forward()
         gw = runner.backward(upstream)[4]
         if world > 1:
-            nonlocal grad_bucket
-            flat = [gw[0], gw[1], *gw[2], gw[3], gw[4], *gw[5]]
-            grad_bucket = torch.cat([t.reshape(-1) for t in flat])
-            dist.all_reduce(grad_bucket)
+            all_reduce_grads([gw[0], gw[1], *gw[2], gw[3], gw[4], *gw[5]])
 
     def barrier():
         if world > 1:
@@ -323,9 +320,8 @@ def run_ours(args) -> dict | None:
         loss = (node_out * t["upstream"]).sum()
         grads = torch.autograd.grad(loss, [x, pos, *block.parameters()], allow_unused=True)
         if world > 1:
-            flat = torch.cat([g.reshape(-1) for g, p in zip(grads[2:], block.parameters())
+            all_reduce_grads([g for g, p in zip(grads[2:], block.parameters())
                               if g is not None and any(p is q for q in so2_params)])
-            dist.all_reduce(flat)
         out_host.copy_(grads[1], non_blocking=True)
         loss_host.copy_(loss.detach(), non_blocking=True)
         torch.cuda.current_stream().synchronize()

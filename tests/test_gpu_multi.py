@@ -1,0 +1,79 @@
+"""Two ranks on two GPUs over NCCL with the real kernels: the destination-range partition of one
+graph must reproduce the single-process oracle (1e-5 relative L2).  Skipped with fewer GPUs."""
+
+from __future__ import annotations
+
+import os
+import pathlib
+import sys
+
+import pytest
+import torch
+import torch.distributed as dist
+import torch.multiprocessing as mp
+
+pytestmark = pytest.mark.gpu
+ROOT = pathlib.Path(__file__).resolve().parent.parent
+WORLD = 2
+
+
+def _case():
+    from oracle import eso2_oracle as orc
+    from tests.helpers import random_case
+    cfg = dict(lmax=4, mmax=2, sphere_channels=16, hidden_channels=16, edge_channels=8,
+               num_distance_basis=6, cutoff=5.0)
+    return cfg, orc.init_params(cfg, seed=41), random_case(cfg, 40, 500, seed=42)
+
+
+def _worker(rank: int, port: int, out_dir: str):
+    sys.path.insert(0, str(ROOT))
+    os.environ.update(MASTER_ADDR="127.0.0.1", MASTER_PORT=str(port))
+    torch.cuda.set_device(rank)
+    dev = torch.device("cuda", rank)
+    dist.init_process_group("nccl", rank=rank, world_size=WORLD, device_id=dev)
+    from tests.helpers import make_block
+    from zippel_b200 import partition as part
+    cfg, params, case = _case()
+    block = make_block(cfg, params, device=dev)
+    n = case["pos"].shape[0]
+    ranges = part.node_ranges(n, WORLD)
+    a, b = ranges[rank]
+    keep = part.local_edges(case["edge_index"], ranges[rank])
+    f = lambda t: t.to(dev, torch.float32)  # noqa: E731
+    pos = f(case["pos"]).requires_grad_(True)
+    x_shard = f(case["x_node"][a:b]).requires_grad_(True)
+    out = part.partitioned_node_output(
+        block.node_output, pos, case["atomic_numbers"].to(dev), x_shard,
+        case["edge_index"][:, keep].to(dev), f(case["shifts"][keep]), f(case["cos_gamma_k"][keep]),
+        f(case["sin_gamma_k"][keep]), ranges, rank)
+    names = [k for k, _ in block.named_parameters()]
+    grads = torch.autograd.grad((out * f(case["upstream"][a:b])).sum(),
+                                [x_shard, pos, *block.parameters()], allow_unused=True)
+    shared = [g.clone() if g is not None else None for g in grads[1:]]
+    part.all_reduce_grads(shared)
+    torch.cuda.synchronize()
+    torch.save({"out": out.detach().cpu(), "gx": grads[0].cpu(), "gpos": shared[0].cpu(),
+                "gw": {k: (g.cpu() if g is not None else None) for k, g in zip(names, shared[1:])},
+                "range": (a, b), "status": block.plan(dev).device_status()},
+               os.path.join(out_dir, f"rank{rank}.pt"))
+    dist.barrier()
+    dist.destroy_process_group()
+
+
+@pytest.mark.skipif(torch.cuda.device_count() < 2, reason="needs two GPUs")
+def test_two_gpu_destination_partition(tmp_path, jd64):
+    from tests.helpers import oracle_node_out_and_vjp, rel_l2
+    port = 29600 + os.getpid() % 2000
+    mp.spawn(_worker, args=(port, str(tmp_path)), nprocs=WORLD, join=True)
+    cfg, params, case = _case()
+    want_out, want_gx, want_gpos, want_pg = oracle_node_out_and_vjp(cfg, params, case,
+                                                                    case["upstream"], jd64)
+    for r in range(WORLD):
+        got = torch.load(tmp_path / f"rank{r}.pt")
+        a, b = got["range"]
+        assert got["status"] == 0
+        assert rel_l2(got["out"], want_out[a:b]) < 1e-5
+        assert rel_l2(got["gx"], want_gx[a:b]) < 1e-5
+        assert rel_l2(got["gpos"], want_gpos) < 1e-5
+        for k in ("c1_m0.weight", "c1_m.0.weight", "c2_m.1.weight", "c2_m0.bias", "rad_func.0.weight"):
+            assert rel_l2(got["gw"][k], want_pg[k]) < 1e-5, k

@@ -418,13 +418,23 @@ def main() -> None:
                     help="atoms per GPU; anything but the default is a profiling-size run, "
                          "not the benchmark workload")
     args = ap.parse_args()
+    # Library chatter (e.g. NCCL's version banner) must not share stdout with the JSON line:
+    # everything else written to fd 1 during the run goes to stderr.
+    sys.stdout.flush()
+    json_out = os.fdopen(os.dup(1), "w")
+    os.dup2(2, 1)
+
+    def emit(line):
+        json_out.write(json.dumps(line) + "\n")
+        json_out.flush()
+
     if args.impl == "reference":
         if int(os.environ.get("RANK", "0")) == 0:
-            print(json.dumps(run_reference(args)), flush=True)
+            emit(run_reference(args))
         return
     line = run_ours(args)
     if line is not None:
-        print(json.dumps(line), flush=True)
+        emit(line)
 
 
 if __name__ == "__main__":

@@ -212,3 +212,34 @@ def test_abi_rejects_bad_arguments():
     plan = Plan.get(2, 2, 8, 8, "cuda")
     assert lib.zp_workspace_bytes(plan.handle, 4, -1, 0) == 0
     assert lib.zp_wigner_forward(plan.handle, 5, None, None, None, None, None) == 1
+
+
+def test_ir_program_dispatch(jd64):
+    """compile_program / allocate / run_program on the force program: kernels vs FP64 interpreter."""
+    from oracle import ir_interp as interp
+    from zippel_b200.blocks.eso2 import BlockConfig, ESO2Block
+    from zippel_b200.blocks.eso2_ir import build_force
+    from zippel_b200.blocks.ir_bind import bind
+    from zippel_b200.codegen.compose import UnsupportedProgram, allocate, compile_program, run_program
+    cfg = dict(lmax=4, mmax=2, sphere_channels=16, hidden_channels=8, edge_channels=8,
+               num_distance_basis=6, cutoff=5.0)
+    params = orc.init_params(cfg, seed=51)
+    block = ESO2Block(BlockConfig(**cfg)).double()
+    block.load_state_dict(params)
+    case = random_case(cfg, 14, 90, seed=52)
+    prog, meta = build_force(BlockConfig(**cfg), block.gauss_coeff)
+    inputs, sizes = bind(block, case, jd64)
+    inputs["seed_E"] = torch.ones(1, dtype=torch.float64)
+    want = interp.run(prog, inputs, sizes)
+    cp = compile_program(prog, sizes, label="force")
+    assert cp.kind == "force" and cp.cfg.lmax == 4 and cp.cfg.mmax == 2 and cp.cfg.cutoff == 5.0
+    env = run_program(cp, allocate(cp, inputs))
+    e_want = want[meta["energy"]].item()
+    assert abs(env[meta["energy"]].item() - e_want) < 1e-5 * max(1.0, abs(e_want))
+    assert rel_l2(env[meta["force"]], want[meta["force"]]) < TOL
+    assert rel_l2(env[meta["node_out"]], want[meta["node_out"]]) < TOL
+    # anything that is not the block program is refused
+    other, _ = build_force(BlockConfig(**cfg), block.gauss_coeff)
+    other.scale(meta["energy"], 2.0)
+    with pytest.raises(UnsupportedProgram):
+        compile_program(other, sizes)

@@ -67,3 +67,19 @@ def random_case(cfg: dict, n: int, e: int, seed: int, box: float = 4.0) -> dict:
         "upstream": torch.randn(n, (lmax + 1) ** 2, cfg["sphere_channels"], generator=g,
                                 dtype=torch.float64),
     }
+
+
+def check_against(node_out, gx, gpos, pg, want_out, want_gx, want_gpos, want_pg, tol=1e-5, rows=None):
+    """Relative-L2 comparison of outputs and all gradients; unused parameters must have zero/None."""
+    if rows is None:
+        assert rel_l2(node_out, want_out) < tol
+    else:
+        assert rel_l2(node_out[rows], want_out[rows]) < tol
+    assert rel_l2(gx, want_gx) < tol
+    assert rel_l2(gpos, want_gpos) < tol
+    for name, want in want_pg.items():
+        got = pg[name]
+        if want is None or want.abs().max().item() == 0.0:
+            assert got is None or got.abs().max().item() == 0.0, name
+            continue
+        assert rel_l2(got, want) < tol, name

@@ -12,23 +12,11 @@ import torch
 
 from oracle import eso2_oracle as orc
 from tests.conftest import golden_names, load_golden
-from tests.helpers import (gpu_node_out_and_vjp, make_block, oracle_node_out_and_vjp,
-                           random_case, rel_l2)
+from tests.helpers import (check_against, gpu_node_out_and_vjp, make_block,
+                           oracle_node_out_and_vjp, random_case, rel_l2)
 
 pytestmark = pytest.mark.gpu
 TOL = 1e-5
-
-
-def check_against(node_out, gx, gpos, pg, want_out, want_gx, want_gpos, want_pg, tol=TOL):
-    assert rel_l2(node_out, want_out) < tol
-    assert rel_l2(gx, want_gx) < tol
-    assert rel_l2(gpos, want_gpos) < tol
-    for name, want in want_pg.items():
-        got = pg[name]
-        if want is None or want.abs().max().item() == 0.0:
-            assert got is None or got.abs().max().item() == 0.0, name
-            continue
-        assert rel_l2(got, want) < tol, name
 
 
 @pytest.mark.parametrize("name", golden_names())

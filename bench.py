@@ -226,7 +226,7 @@ def run_ours(args) -> dict | None:
 
     batch = make_workload(rank, args.atoms)
     n, e = batch["meta"]["n_atoms"], batch["meta"]["n_edges"]
-    block = ESO2Block(BlockConfig(**CFG))
+    block = ESO2Block(BlockConfig(**CFG), precision=args.precision)
     xavier_(block, 0)
     block = block.to(dev)
     so2_params = [block.c1_m0.weight, block.c1_m0.bias, *[l.weight for l in block.c1_m],
@@ -356,15 +356,16 @@ def run_ours(args) -> dict | None:
         flops_step = 2.0 * macs * e            # each of fwd / dgrad / wgrad does the same MACs
         ach = flops_step / (kernels[top]["ms_per_step"] * 1e-3) / 1e12
         peak = pk["bf16_tflops_sustained"]
-        passes = 6          # bf16 plane products per fp32-accurate product (1 in bf16 precision)
+        passes = {"fp32": 3, "fp32_bf16x3": 6, "bf16": 1}[args.precision]   # tensor-core passes per product
         roof = {"bound": "tensor", "kernel": top, "achieved": ach, "peak": peak,
                 "unit": "TFLOP/s", "frac": ach / peak, "traffic": None,
                 "peak_source": f"{pk_src} bf16 dense sustained (no fp32/tf32 peak is measured)",
                 "ms_per_launch": per_launch, "mma_passes": passes,
                 "mma_tflops": ach * passes, "mma_frac": ach * passes / peak,
                 "note": "achieved counts algorithmic FLOPs (2*MAC of the six per-m SO(2) "
-                        "products) once; fp32 accuracy costs 6 bf16 tensor-core passes per "
-                        "product, so mma_tflops = 6 x achieved is what the tensor pipe executes"}
+                        "products) once; the operand format costs mma_passes 16-bit tensor-core "
+                        "passes per product, so mma_tflops = mma_passes x achieved is what the "
+                        "tensor pipe executes"}
     else:
         roof = {"bound": "hbm", "kernel": top, "achieved": None, "peak": pk["hbm_gbs"],
                 "unit": "GB/s", "frac": None, "traffic": None, "peak_source": pk_src}
@@ -375,7 +376,8 @@ def run_ours(args) -> dict | None:
             "metric": METRIC, "value": total_edges / (ms_per_step * 1e-3), "unit": "edges/s",
             "n_gpus": world, "steps": args.steps, "warmup": max(args.warmup, 3),
             "ms_per_step": ms_per_step, "higher_is_better": True, "scaling": "weak",
-            "vs_baseline": None, "dtype": "f32", "data": "synthetic",
+            "vs_baseline": None, "dtype": "bf16" if args.precision == "bf16" else "f32",
+            "precision": args.precision, "data": "synthetic",
             "config": workload_config(batch, "256 MiB L2 flush between steps, outside the "
                                              "per-step events; per-step activations are >5 GB"),
             "fwd_only": {"value": e / (fwd_ms * 1e-3), "unit": "edges/s (this rank)",
@@ -414,6 +416,8 @@ def main() -> None:
     ap.add_argument("--impl", default="ours", choices=["ours", "reference"])
     ap.add_argument("--cpu-sample-nodes", type=int, default=100)
     ap.add_argument("--no-cpu-baseline", action="store_true")
+    ap.add_argument("--precision", default="fp32", choices=["fp32", "fp32_bf16x3", "bf16"],
+                    help="operand format of the SO(2) contraction (see ESO2Block)")
     ap.add_argument("--atoms", type=int, default=N_ATOMS,
                     help="atoms per GPU; anything but the default is a profiling-size run, "
                          "not the benchmark workload")

@@ -39,8 +39,11 @@ typedef enum zp_status {
 } zp_status;
 
 /* Mirrors the fields of the reference's BlockConfig (blocks/eso2_ref.py:51-76) that the
- * kernel path reads.  precision: 0 = fp32 storage, fp32-accurate contraction (3xTF32 on
- * the tensor cores); 1 = bf16 operands for the SO(2) contraction, fp32 accumulate.        */
+ * kernel path reads.  precision selects how the operands of the SO(2) contraction are carried:
+ *   0  three bf16 terms per fp32 value (six tensor-core passes, ~24 bits, no range limits);
+ *   1  one bf16 term (bf16 operands, fp32 accumulation);
+ *   2  two fp16 terms and a per-tensor power-of-two scale derived on the device from
+ *      magnitude bounds (three passes, 22 bits relative to each tensor's largest entries).  */
 typedef struct zp_config {
   int32_t lmax;
   int32_t mmax;
@@ -184,8 +187,8 @@ int zp_eso2_backward(const zp_plan *plan, int64_t n_nodes, int64_t n_edges,
 
 /* The contraction engine on its own (no reference counterpart: the reference calls
  * torch.nn.functional.linear, blocks/eso2_ref.py:272,286).  Exposed for tests and benchmarks.
- * zp_split_planes writes an fp32 matrix [rows, cols] (row stride ld_in) as `planes` (1 or 3)
- * bf16 matrices [rows, ld_out] that sum to it, plane p starting plane_stride elements after
+ * zp_split_planes writes an fp32 matrix [rows, cols] (row stride ld_in) as `planes` 16-bit
+ * matrices [rows, ld_out] that sum to it (1 or 3: bf16 terms; 2: fp16 terms, unscaled), plane p starting plane_stride elements after
  * plane p-1; columns cols..ld_out-1 are zero.  zp_gemm_planes computes, on the tensor cores,
  *   C[M, N] = sum over plane pairs  A_pa  B_pb^T  (+ bias[n]),   fp32 output, row stride ldc,
  * for K-major operands X[p*plane + r*ld + k] or, with a_mn / b_mn = 1, MN-major operands

@@ -47,6 +47,26 @@ ORACLE_CASES = [
 ]
 
 
+@pytest.mark.parametrize("scale", [1.0, 1e-4, 30.0])
+@pytest.mark.parametrize("lmax,mmax,c,h,ec,nb,n,e", ORACLE_CASES[:4] + ORACLE_CASES[-1:])
+def test_oracle_parity_bf16x3_and_scaled_inputs(lmax, mmax, c, h, ec, nb, n, e, scale, jd64):
+    """Both fp32-accurate operand formats (two scaled fp16 terms = the default, three bf16 terms)
+    hold the fp32 tolerance, also when embeddings and upstream gradient are far from unit
+    magnitude (the fp16 scales are derived from device-side magnitude bounds)."""
+    cfg = dict(lmax=lmax, mmax=mmax, sphere_channels=c, hidden_channels=h, edge_channels=ec,
+               num_distance_basis=nb, cutoff=5.0)
+    params = orc.init_params(cfg, seed=lmax * 10 + mmax)
+    case = random_case(cfg, n, e, seed=100 + lmax)
+    case["x_node"] = case["x_node"] * scale
+    case["upstream"] = case["upstream"] / scale
+    want = oracle_node_out_and_vjp(cfg, params, case, case["upstream"], jd64)
+    for precision in ("fp32", "fp32_bf16x3"):
+        block = make_block(cfg, params, precision=precision)
+        got = gpu_node_out_and_vjp(block, case, case["upstream"])
+        check_against(*got, *want)
+        assert block.plan("cuda").device_status() == 0
+
+
 @pytest.mark.parametrize("lmax,mmax,c,h,ec,nb,n,e", ORACLE_CASES)
 def test_oracle_parity_small(lmax, mmax, c, h, ec, nb, n, e, jd64):
     cfg = dict(lmax=lmax, mmax=mmax, sphere_channels=c, hidden_channels=h, edge_channels=ec,

@@ -108,7 +108,7 @@ class Plan:
     _cache: dict = {}
 
     def __init__(self, lmax: int, mmax: int, c: int, h: int, device: torch.device,
-                 precision: int = 0):
+                 precision: int = 2):
         lib = _lib.load()
         self.precision = precision
         self.device = device
@@ -126,7 +126,7 @@ class Plan:
         self.lmax, self.mmax, self.c, self.h = lmax, mmax, c, h
 
     @classmethod
-    def get(cls, lmax, mmax, c, h, device, precision: int = 0) -> "Plan":
+    def get(cls, lmax, mmax, c, h, device, precision: int = 2) -> "Plan":
         device = torch.device(device)
         if device.type != "cuda":
             raise RuntimeError("zippel_b200 runs on CUDA devices only; there is no CPU path")
@@ -317,11 +317,13 @@ def edge_conv(plan: Plan, graph: EdgeGraph, x_node, edge_vec, cos_g, sin_g, radi
 class ESO2Block(nn.Module):
     """One SO(2) interaction block + per-atom energy head, reference call signature."""
 
-    PRECISIONS = {"fp32": 0, "bf16": 1}
+    PRECISIONS = {"fp32": 2, "fp32_bf16x3": 0, "bf16": 1}
 
     def __init__(self, cfg: BlockConfig = BlockConfig(), precision: str = "fp32"):
-        """``precision``: "fp32" carries every operand of the SO(2) contraction as three bf16
-        terms (fp32-accurate results); "bf16" rounds operands to bf16 and accumulates in fp32."""
+        """``precision`` of the SO(2) contraction's operands: "fp32" carries each value as two
+        fp16 terms with per-tensor power-of-two scales derived on the device (22 bits, three
+        tensor-core passes); "fp32_bf16x3" as three bf16 terms (24 bits, six passes, no scales);
+        "bf16" rounds operands to bf16.  Accumulation is fp32 in all three."""
         super().__init__()
         self.cfg = cfg
         self.precision = self.PRECISIONS[precision]

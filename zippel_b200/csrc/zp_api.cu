@@ -53,11 +53,16 @@ bool aligned16(const void *p) { return (reinterpret_cast<uintptr_t>(p) & 15u) ==
 //   forward:  rot | a1 planes | h1 | ht planes | y | folded weight planes
 //   backward: dy planes | dht | dh1 planes | da1 | du_src | grot | wgrad partials | scratch
 struct Workspace {
-  float *rot, *h1, *y, *dht, *da1, *du_src, *grot, *wgrad, *scratch;
+  float *rot, *h1, *y, *dht, *da1, *du_src, *grot, *wgrad, *scratch, *scales;
   ZpPlanes a1, ht, dy, dh1;
-  __nv_bfloat16 *wfold;
+  uint16_t *wfold;
   size_t bytes;
 };
+
+// slots of the device-side scale array (fp16-plane precision): raw maxima, derived scales, and
+// per weight block {max |W|, scale} from kScWeights on
+enum { kScX = 0, kScRad, kScG, kScH1, kScDht, kScA1, kScHt, kScDy, kScDh1, kScWeights = 16,
+       kScCount = kScWeights + 4 * (ZP_MAX_L + 1) };
 
 constexpr int kMaxWgradSplits = 8;
 
@@ -79,8 +84,10 @@ Workspace carve(const zp_plan *p, int64_t N, int64_t E, int with_backward, void 
     ZpPlanes pl;
     pl.ld = round8(cols);
     pl.planes = p->planes;
+    pl.fp16 = p->fp16;
+    pl.scale = nullptr;
     pl.plane_stride = (int64_t)zp_align_up((size_t)E * pl.ld, 128);
-    pl.base = reinterpret_cast<__nv_bfloat16 *>(take((size_t)pl.planes * pl.plane_stride * 2));
+    pl.base = take((size_t)pl.planes * pl.plane_stride * 2);
     return pl;
   };
   const size_t e = (size_t)E;
@@ -89,7 +96,8 @@ Workspace carve(const zp_plan *p, int64_t N, int64_t E, int with_backward, void 
   w.h1 = takef(e * t.w1_cols);
   w.ht = takep((int64_t)t.Km * t.H);
   w.y = takef(e * t.Km * t.C);
-  w.wfold = reinterpret_cast<__nv_bfloat16 *>(take((size_t)p->w_elems * 2));
+  w.wfold = reinterpret_cast<uint16_t *>(take((size_t)p->w_elems * 2));
+  w.scales = takef(kScCount);
   if (with_backward) {
     w.dy = takep((int64_t)t.Km * t.C);
     w.dht = takef(e * t.Km * t.H);
@@ -100,14 +108,24 @@ Workspace carve(const zp_plan *p, int64_t N, int64_t E, int with_backward, void 
     w.wgrad = takef((size_t)kMaxWgradSplits * p->g_elems);
     w.scratch = takef((size_t)zp_ceil_div(E > 0 ? E : 1, 128) * (size_t)t.w1_cols);   // column-sum partials
   }
+  if (p->fp16 && base) {
+    w.a1.scale = w.scales + kScA1;
+    w.ht.scale = w.scales + kScHt;
+    w.dy.scale = w.scales + kScDy;
+    w.dh1.scale = w.scales + kScDh1;
+  }
   w.bytes = off;
   return w;
+}
+
+const float *wscale(const zp_plan *p, const Workspace &w, int conv, int m) {
+  return p->fp16 ? w.scales + kScWeights + (conv * (ZP_MAX_L + 1) + m) * 2 + 1 : nullptr;
 }
 
 // operand views of one m-block inside a plane buffer (column offset `col`)
 ZpPlanes sub(const ZpPlanes &p, int64_t col) {
   ZpPlanes q = p;
-  q.base = p.base + col;
+  q.base = static_cast<uint16_t *>(p.base) + col;
   return q;
 }
 
@@ -151,7 +169,7 @@ int zp_plan_create(const zp_config *cfg, const double *jd_host, zp_plan **plan_o
   const int L = cfg->lmax, MM = cfg->mmax, C = cfg->sphere_channels, H = cfg->hidden_channels;
   if (L < 0 || L > ZP_MAX_L || MM < 0 || MM > L) return ZP_ERR_UNSUPPORTED;
   if (C <= 0 || H <= 0 || C % 8 || H % 8 || C > 512) return ZP_ERR_UNSUPPORTED;
-  if (cfg->precision != 0 && cfg->precision != 1) return ZP_ERR_UNSUPPORTED;
+  if (cfg->precision < 0 || cfg->precision > 2) return ZP_ERR_UNSUPPORTED;
   if (!zp_device_supported()) return ZP_ERR_NO_DEVICE_CODE;
 
   zp_plan *p = new (std::nothrow) zp_plan;
@@ -192,7 +210,8 @@ int zp_plan_create(const zp_config *cfg, const double *jd_host, zp_plan **plan_o
   }
 
   p->n_blocks = MM + 1;
-  p->planes = cfg->precision == 0 ? 3 : 1;
+  p->planes = cfg->precision == 0 ? 3 : cfg->precision == 2 ? 2 : 1;
+  p->fp16 = cfg->precision == 2;
   int64_t woff = 0, goff = 0;
   for (int conv = 0; conv < 2; ++conv) {
     for (int m = 0; m <= MM; ++m) {
@@ -298,10 +317,10 @@ int zp_plan_device_status(zp_plan *plan, int *status_out) {
 
 int zp_split_planes(int64_t rows, int64_t cols, const float *in, int64_t ld_in, void *out,
                     int64_t ld_out, int64_t plane_stride, int planes, void *stream) {
-  if (rows < 0 || cols < 0 || cols > ld_out || planes < 1 || planes > 3 || !in || !out)
+  if (rows < 0 || cols < 0 || cols > ld_out || planes < 1 || planes > 3 || !in || !out || ld_out % 2)
     return ZP_ERR_INVALID_ARG;
-  return zp_launch_split_planes(rows, cols, in, ld_in, out, ld_out, plane_stride, planes,
-                                (cudaStream_t)stream);
+  const ZpPlanes pl{out, plane_stride, ld_out, planes, planes == 2, nullptr};
+  return zp_launch_split_planes(rows, cols, in, ld_in, pl, (cudaStream_t)stream);
 }
 
 int zp_gemm_planes(zp_plan *plan, int64_t M, int64_t N, int64_t K, int planes, const void *A,
@@ -310,8 +329,10 @@ int zp_gemm_planes(zp_plan *plan, int64_t M, int64_t N, int64_t K, int planes, c
                    int variant, int ksplit, int64_t split_stride, int kc_elems, int *splits_out,
                    void *stream) {
   if (!plan || !A || !B || !C || M < 0 || N < 0 || K <= 0) return ZP_ERR_INVALID_ARG;
+  const int fp16 = planes == 2;
   ZpGemmTc g{M, N, K, planes, A, lda, a_plane, a_mn, B, ldb, b_plane, b_mn, bias, C, ldc,
-             plan->status_dev, variant, ksplit, split_stride, kc_elems};
+             plan->status_dev, variant, ksplit, split_stride, kc_elems, fp16, nullptr, nullptr,
+             nullptr};
   if (splits_out) *splits_out = zp_gemm_tc_splits(g);
   return zp_launch_gemm_tc(g, (cudaStream_t)stream);
 }
@@ -366,7 +387,16 @@ int zp_eso2_forward(const zp_plan *plan, int64_t N, int64_t E, const float *x_no
   cudaStream_t st = (cudaStream_t)stream;
   const ZpTables &t = plan->t;
 
-  ZP_TIMED(ZP_K_FOLD, zp_launch_fold_weights(plan, w, ws.wfold, st));
+  if (plan->fp16) {
+    // magnitude bounds -> power-of-two scales, all on the device:  |rot row . x| <= sqrt(2l+1) max|x|
+    ZP_TIMED(ZP_K_FOLD, zp_launch_absmax(N, (int64_t)t.K * t.C, x_node, (int64_t)t.K * t.C,
+                                         ws.scales + kScX, st));
+    ZP_TIMED(ZP_K_FOLD, zp_launch_absmax(E, t.R, radial, t.R, ws.scales + kScRad, st));
+    ZP_TIMED(ZP_K_FOLD, zp_launch_scale(3.7f, ws.scales + kScX, ws.scales + kScRad, nullptr, 0.f,
+                                        ws.scales + kScA1, st));
+    ZP_CUDA(cudaMemsetAsync(ws.scales + kScH1, 0, sizeof(float), st));
+  }
+  ZP_TIMED(ZP_K_FOLD, zp_launch_fold_weights(plan, w, ws.wfold, ws.scales + kScWeights, st));
   ZP_TIMED(ZP_K_WIGNER_FWD, zp_launch_wigner_fwd(plan, E, edge_vec, cos_g, sin_g, ws.rot, st));
   ZP_TIMED(ZP_K_ROTATE_IN,
            zp_launch_rotate_in(plan, E, x_node, src, dst, ws.rot, radial, ws.a1, st));
@@ -378,9 +408,14 @@ int zp_eso2_forward(const zp_plan *plan, int64_t N, int64_t E, const float *x_no
     float *Cc = ws.h1 + (m == 0 ? 0 : t.n_gate + (size_t)t.m_row0[m] * t.H);
     const ZpGemmTc g{E, out, in, P, A.base, A.ld, A.plane_stride, 0,
                      ws.wfold + plan->c1_woff[m], in, (int64_t)out * in, 0,
-                     m == 0 ? w->c1_b0 : nullptr, Cc, t.w1_cols, plan->status_dev, 0, 1, 0, 0};
+                     m == 0 ? w->c1_b0 : nullptr, Cc, t.w1_cols, plan->status_dev, 0, 1, 0, 0,
+                     plan->fp16, A.scale, wscale(plan, ws, 0, m),
+                     plan->fp16 ? ws.scales + kScH1 : nullptr};
     ZP_TIMED(ZP_K_GEMM_FWD, zp_launch_gemm_tc(g, st));
   }
+  if (plan->fp16)      // |gate(h1)| <= |h1|
+    ZP_TIMED(ZP_K_GATE_FWD, zp_launch_scale(1.f, ws.scales + kScH1, nullptr, nullptr, 0.f,
+                                            ws.scales + kScHt, st));
   ZP_TIMED(ZP_K_GATE_FWD, zp_launch_gate_fwd(plan, E, ws.h1, ws.ht, st));
   for (int m = 0; m < plan->n_blocks && E > 0; ++m) {
     const int in = plan->c2_in[m], out = plan->c2_out[m];
@@ -388,7 +423,8 @@ int zp_eso2_forward(const zp_plan *plan, int64_t N, int64_t E, const float *x_no
     float *Cc = ws.y + (size_t)t.m_row0[m] * t.C;
     const ZpGemmTc g{E, out, in, P, A.base, A.ld, A.plane_stride, 0,
                      ws.wfold + plan->c2_woff[m], in, (int64_t)out * in, 0,
-                     m == 0 ? w->c2_b0 : nullptr, Cc, ldy, plan->status_dev, 0, 1, 0, 0};
+                     m == 0 ? w->c2_b0 : nullptr, Cc, ldy, plan->status_dev, 0, 1, 0, 0,
+                     plan->fp16, A.scale, wscale(plan, ws, 1, m), nullptr};
     ZP_TIMED(ZP_K_GEMM_FWD, zp_launch_gemm_tc(g, st));
   }
   ZP_TIMED(ZP_K_ROTATE_BACK,
@@ -430,6 +466,12 @@ int zp_eso2_backward(const zp_plan *plan, int64_t N, int64_t E, const float *gra
   int sms = 148;
   cudaDeviceGetAttribute(&sms, cudaDevAttrMultiProcessorCount, plan->device);
 
+  if (plan->fp16) {
+    ZP_TIMED(ZP_K_ROTATE_GRAD_OUT, zp_launch_absmax(N, (int64_t)t.K * t.C, grad_node_out,
+                                                    (int64_t)t.K * t.C, ws.scales + kScG, st));
+    ZP_TIMED(ZP_K_ROTATE_GRAD_OUT, zp_launch_scale(3.7f, ws.scales + kScG, nullptr, nullptr, 0.f,
+                                                   ws.scales + kScDy, st));
+  }
   ZP_TIMED(ZP_K_ROTATE_GRAD_OUT,
            zp_launch_rotate_grad_out(plan, E, grad_node_out, ws.y, env, ws.rot, dst, ws.dy,
                                      grad_env, ws.grot, st));
@@ -442,14 +484,22 @@ int zp_eso2_backward(const zp_plan *plan, int64_t N, int64_t E, const float *gra
     float *dX = conv ? ws.dht : ws.da1;
     const int64_t ldx = conv ? ldh : lda;
     const int cin = conv ? t.H : 2 * t.C, cout = conv ? t.C : t.H;
-    if (conv == 0) ZP_TIMED(ZP_K_GATE_BWD, zp_launch_gate_bwd(plan, E, ws.h1, ws.dht, ws.dh1, st));
+    if (conv == 0) {
+      if (plan->fp16) {      // true max |dh1| from a store-free pass, then its scale
+        ZP_TIMED(ZP_K_GATE_BWD,
+                 zp_launch_gate_bwd(plan, E, ws.h1, ws.dht, ws.dh1, ws.scales + kScDht, st));
+        ZP_TIMED(ZP_K_GATE_BWD, zp_launch_scale(1.f, ws.scales + kScDht, nullptr, nullptr, 0.f,
+                                                ws.scales + kScDh1, st));
+      }
+      ZP_TIMED(ZP_K_GATE_BWD, zp_launch_gate_bwd(plan, E, ws.h1, ws.dht, ws.dh1, nullptr, st));
+    }
     for (int m = 0; m < plan->n_blocks; ++m) {
       const int in = conv ? plan->c2_in[m] : plan->c1_in[m];
       const int out = conv ? plan->c2_out[m] : plan->c1_out[m];
       const int64_t ycol = (conv == 0 && m > 0 ? t.n_gate : 0) + (m == 0 ? 0 : (int64_t)t.m_row0[m] * cout);
       const int64_t xcol = (int64_t)t.m_row0[m] * cin;
       const ZpPlanes dYm = sub(dYp, ycol), Xm = sub(Xp, xcol);
-      const __nv_bfloat16 *Wt = ws.wfold + (conv ? plan->c2_woff[m] : plan->c1_woff[m]) +
+      const uint16_t *Wt = ws.wfold + (conv ? plan->c2_woff[m] : plan->c1_woff[m]) +
                                 (int64_t)P * out * in;
       float *G = ws.wgrad + (conv ? plan->c2_goff[m] : plan->c1_goff[m]);
       int &nsplit = (conv ? splits_c2 : splits_c1)[m];
@@ -460,7 +510,9 @@ int zp_eso2_backward(const zp_plan *plan, int64_t N, int64_t E, const float *gra
       }
       const ZpGemmTc gd{E, in, out, P, dYm.base, dYm.ld, dYm.plane_stride, 0,
                         Wt, out, (int64_t)out * in, 0, nullptr, dX + xcol, ldx,
-                        plan->status_dev, 0, 1, 0, 0};
+                        plan->status_dev, 0, 1, 0, 0, plan->fp16, dYm.scale,
+                        wscale(plan, ws, conv, m),
+                        nullptr};
       ZP_TIMED(ZP_K_GEMM_DGRAD, zp_launch_gemm_tc(gd, st));
       // enough K splits to fill the SMs once, never more work items than SMs
       const int64_t tiles = zp_ceil_div(out, 128) * zp_ceil_div(in, 256);
@@ -469,7 +521,8 @@ int zp_eso2_backward(const zp_plan *plan, int64_t N, int64_t E, const float *gra
       if (want > kMaxWgradSplits) want = kMaxWgradSplits;
       ZpGemmTc gw_{out, in, E, P, dYm.base, dYm.ld, dYm.plane_stride, 1,
                    Xm.base, Xm.ld, Xm.plane_stride, 1, nullptr, G, in,
-                   plan->status_dev, 0, want, plan->g_elems, 0};
+                   plan->status_dev, 0, want, plan->g_elems, 0, plan->fp16, dYm.scale, Xm.scale,
+                   nullptr};
       nsplit = zp_gemm_tc_splits(gw_);
       ZP_TIMED(ZP_K_GEMM_WGRAD, zp_launch_gemm_tc(gw_, st));
     }

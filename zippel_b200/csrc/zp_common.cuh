@@ -43,7 +43,8 @@ struct zp_plan {
   // per-m GEMM shapes of the folded SO(2) weights
   int n_blocks;                                 // mmax + 1
   int c1_in[ZP_MAX_L + 1], c1_out[ZP_MAX_L + 1], c2_in[ZP_MAX_L + 1], c2_out[ZP_MAX_L + 1];
-  int planes;                                   // bf16 planes per fp32 operand: 3 (fp32) or 1 (bf16)
+  int planes;                                   // 16-bit planes per operand: 3 bf16, 2 fp16 or 1 bf16
+  int fp16;                                     // planes are fp16 with per-tensor scales
   int64_t c1_woff[ZP_MAX_L + 1], c2_woff[ZP_MAX_L + 1];   // bf16 offsets of the folded planes
   int64_t w_elems;                              // bf16 elements of all folded planes
   int64_t c1_goff[ZP_MAX_L + 1], c2_goff[ZP_MAX_L + 1];   // fp32 offsets of the folded gradients
@@ -117,8 +118,9 @@ int zp_launch_node_reduce(const zp_plan *p, int64_t N, const float *du_both,
 
 int zp_launch_gate_fwd(const zp_plan *p, int64_t E, const float *h1, const ZpPlanes &ht,
                        cudaStream_t st);
+// max_out != null: store nothing, only record max |dh1| in *max_out (device scalar)
 int zp_launch_gate_bwd(const zp_plan *p, int64_t E, const float *h1, const float *dht,
-                       const ZpPlanes &dh1, cudaStream_t st);
+                       const ZpPlanes &dh1, float *max_out, cudaStream_t st);
 
 // Tensor-core product over bf16 planes: C[M,N] = sum_pairs A_pa * B_pb^T (+ bias), fp32 out.
 // K-major operand: X[p*plane + r*ld + k]; MN-major (x_mn = 1): X[p*plane + k*ld + r].
@@ -134,17 +136,27 @@ struct ZpGemmTc {
   int ksplit;                                   // requested split of K over CTAs (>= 1)
   int64_t split_stride;                         // elements between the partial outputs of splits
   int kc_elems;                                 // K per TMEM accumulation chunk (0 = 2048)
+  int fp16;                                     // planes are fp16 (planes must be 2), else bf16
+  const float *scale_a, *scale_b;               // device scalars multiplied into the result
+  float *absmax_out;                            // device scalar updated with max |C| (or null)
 };
 int zp_launch_gemm_tc(const ZpGemmTc &g, cudaStream_t st);
 // number of partial outputs the launch above will write for this problem (<= g.ksplit)
 int zp_gemm_tc_splits(const ZpGemmTc &g);
-// fp32 [rows, cols] (row stride ld_in) -> `planes` bf16 planes [rows, ld_out]
-int zp_launch_split_planes(int64_t rows, int64_t cols, const float *in, int64_t ld_in, void *out,
-                           int64_t ld_out, int64_t plane_stride, int planes, cudaStream_t st);
+// fp32 [rows, cols] (row stride ld_in) -> planes [rows, out.ld], zero padded
+int zp_launch_split_planes(int64_t rows, int64_t cols, const float *in, int64_t ld_in,
+                           const ZpPlanes &out, cudaStream_t st);
+// *out = max |in| (device scalar);  *scale = power of two mapping factor*a*b*max(offset_c, c) to 2^15
+int zp_launch_absmax(int64_t rows, int64_t cols, const float *in, int64_t ld, float *out,
+                     cudaStream_t st);
+int zp_launch_scale(float factor, const float *a, const float *b, const float *c, float offset_c,
+                    float *scale, cudaStream_t st);
 
 // Folded SO(2) weights as bf16 planes: per block W_fold [P][out][in] followed by its transpose
 // [P][in][out], at element offset c{1,2}_woff[m] of `packed`.
-int zp_launch_fold_weights(const zp_plan *p, const zp_weights *w, void *packed, cudaStream_t st);
+// `scales`: per block (conv * (ZP_MAX_L+1) + m) two floats {max |W|, scale}; used for fp16 planes
+int zp_launch_fold_weights(const zp_plan *p, const zp_weights *w, void *packed, float *scales,
+                           cudaStream_t st);
 // partials: per split s the folded fp32 gradients at partials + s*split_stride + c{1,2}_goff[m]
 int zp_launch_unfold_wgrad(const zp_plan *p, const float *partials, int64_t split_stride,
                            const int *splits_c1, const int *splits_c2, const zp_weight_grads *gw,

@@ -16,19 +16,47 @@
 
 namespace {
 
-// fp32 -> up to three bf16 terms whose sum reproduces the value to ~2^-24
+// fp32 matrix -> planes (bf16, or fp16 with the tensor's scale), zero padding up to ld_out
 __global__ void split_planes_kernel(int64_t rows, int64_t cols, const float *__restrict__ in,
-                                    int64_t ld_in, __nv_bfloat16 *__restrict__ out, int64_t ld_out,
-                                    int64_t plane_stride, int planes) {
+                                    int64_t ld_in, const ZpPlanes out) {
   const int64_t idx = (int64_t)blockIdx.x * blockDim.x + threadIdx.x;
-  if (idx >= rows * ld_out) return;
-  const int64_t r = idx / ld_out, c = idx % ld_out;
-  float x = c < cols ? in[r * ld_in + c] : 0.f;
-  for (int p = 0; p < planes; ++p) {
-    const __nv_bfloat16 h = __float2bfloat16_rn(x);
-    out[(size_t)p * plane_stride + idx] = h;
-    x -= __bfloat162float(h);
+  if (idx >= rows * (out.ld / 2)) return;
+  const int64_t r = idx / (out.ld / 2), c = (idx % (out.ld / 2)) * 2;
+  float v[2];
+  v[0] = c < cols ? in[r * ld_in + c] : 0.f;
+  v[1] = c + 1 < cols ? in[r * ld_in + c + 1] : 0.f;
+  zp_store_planes<2>(out, r * out.ld + c, v, zp_inv_scale(out));
+}
+
+// max |x| over a strided matrix into *out (which the caller zeroed), and the scale derived from
+// products of such maxima
+__global__ void absmax_kernel(int64_t rows, int64_t cols, const float *__restrict__ in, int64_t ld,
+                              float *out) {
+  float m = 0.f;
+  const int64_t n = rows * cols;
+  if (ld == cols && (n & 3) == 0 && (reinterpret_cast<uintptr_t>(in) & 15) == 0) {
+    const float4 *in4 = reinterpret_cast<const float4 *>(in);     // contiguous: 16-byte loads
+    for (int64_t i = (int64_t)blockIdx.x * blockDim.x + threadIdx.x; i < n / 4;
+         i += (int64_t)gridDim.x * blockDim.x) {
+      const float4 v = in4[i];
+      m = fmaxf(fmaxf(m, fmaxf(fabsf(v.x), fabsf(v.y))), fmaxf(fabsf(v.z), fabsf(v.w)));
+    }
+  } else {
+    for (int64_t i = (int64_t)blockIdx.x * blockDim.x + threadIdx.x; i < n;
+         i += (int64_t)gridDim.x * blockDim.x)
+      m = fmaxf(m, fabsf(in[(i / cols) * ld + i % cols]));
   }
+#pragma unroll
+  for (int o = 16; o > 0; o >>= 1) m = fmaxf(m, __shfl_xor_sync(0xffffffffu, m, o));
+  if ((threadIdx.x & 31) == 0 && m > 0.f) zp_atomic_absmax(out, m);
+}
+
+// scale[0] = power of two mapping  factor * a * b (* c)  to 2^15; null pointers count as 1
+__global__ void scale_kernel(float factor, const float *a, const float *b, const float *c,
+                             float offset_c, float *scale) {
+  float bound = factor * (a ? *a : 1.f) * (b ? *b : 1.f);
+  if (c) bound *= fmaxf(offset_c, *c);
+  *scale = zp_scale_for_bound(bound);
 }
 
 // ------------------------------------------------------------------------------------------
@@ -56,20 +84,26 @@ __global__ void gate_fwd_kernel(const __grid_constant__ ZpTables t, int64_t E,
     o[0] = x.x * sigmoidf(g.x); o[1] = x.y * sigmoidf(g.y);
     o[2] = x.z * sigmoidf(g.z); o[3] = x.w * sigmoidf(g.w);
   }
-  zp_store_planes<4>(ht, e * ht.ld + (int64_t)r * t.H + h, o);
+  zp_store_planes<4>(ht, e * ht.ld + (int64_t)r * t.H + h, o, zp_inv_scale(ht));
 }
 
-// one thread per (edge, hidden-channel quad): walks the Km rows, accumulates the lmax gate grads
+// one thread per (edge, hidden-channel quad): walks the Km rows, accumulates the lmax gate grads.
+// With `max_out` set nothing is stored: the kernel only records max |dh1| there (the scale of
+// the fp16 planes needs the true maximum; a product of bounds is far too loose once the gates
+// saturate).
 __global__ void gate_bwd_kernel(const __grid_constant__ ZpTables t, int64_t E,
                                 const float *__restrict__ h1, const float *__restrict__ dht,
-                                const ZpPlanes dh1) {
+                                const ZpPlanes dh1, float *max_out) {
   const int H4 = t.H / 4;
-  const int64_t idx = (int64_t)blockIdx.x * blockDim.x + threadIdx.x;
-  if (idx >= E * H4) return;
+  const int64_t idx0 = (int64_t)blockIdx.x * blockDim.x + threadIdx.x;
+  const bool in_range = idx0 < E * H4;
+  const int64_t idx = in_range ? idx0 : 0;        // out-of-range threads recompute item 0
+  float seen = 0.f;
   const int h = (int)(idx % H4) * 4;
   const int64_t e = idx / H4;
   const float *row = h1 + (size_t)e * t.w1_cols;
   const int64_t drow = e * dh1.ld;
+  const float inv = zp_inv_scale(dh1);
   const float *dt = dht + (size_t)e * t.Km * t.H;
   float sg[ZP_MAX_L][4], dg[ZP_MAX_L][4];
 #pragma unroll
@@ -106,7 +140,12 @@ __global__ void gate_bwd_kernel(const __grid_constant__ ZpTables t, int64_t E,
         }
       }
     }
-    zp_store_planes<4>(dh1, drow + t.n_gate + r * t.H + h, o);
+    if (max_out) {
+#pragma unroll
+      for (int v = 0; v < 4; ++v) seen = fmaxf(seen, fabsf(o[v]));
+    } else if (in_range) {
+      zp_store_planes<4>(dh1, drow + t.n_gate + r * t.H + h, o, inv);
+    }
   }
 #pragma unroll
   for (int l = 0; l < ZP_MAX_L; ++l) {
@@ -114,38 +153,87 @@ __global__ void gate_bwd_kernel(const __grid_constant__ ZpTables t, int64_t E,
       float o[4];
 #pragma unroll
       for (int v = 0; v < 4; ++v) o[v] = dg[l][v] * sg[l][v] * (1.f - sg[l][v]);
-      zp_store_planes<4>(dh1, drow + l * t.H + h, o);
+      if (max_out) {
+#pragma unroll
+        for (int v = 0; v < 4; ++v) seen = fmaxf(seen, fabsf(o[v]));
+      } else if (in_range) {
+        zp_store_planes<4>(dh1, drow + l * t.H + h, o, inv);
+      }
     }
+  }
+  if (max_out) {
+#pragma unroll
+    for (int o = 16; o > 0; o >>= 1) seen = fmaxf(seen, __shfl_xor_sync(0xffffffffu, seen, o));
+    if ((threadIdx.x & 31) == 0 && seen > 0.f) zp_atomic_absmax(max_out, seen);
   }
 }
 
 // ------------------------------------------------------------------------------------------
 // weight folding and its transpose
 // ------------------------------------------------------------------------------------------
-// fold: writes W_fold [out, in] and its transpose [in, out] as bf16 planes.
+// All weight blocks of both convolutions in one launch each (blockIdx.y = block).
+struct FoldDesc {
+  int n;
+  int out[2 * (ZP_MAX_L + 1)], in[2 * (ZP_MAX_L + 1)], folded[2 * (ZP_MAX_L + 1)];
+  int slot[2 * (ZP_MAX_L + 1)];                 // index of the block's {max, scale} pair
+  const float *w[2 * (ZP_MAX_L + 1)];
+  int64_t woff[2 * (ZP_MAX_L + 1)];
+};
+
+__global__ void weight_absmax_kernel(const FoldDesc d, float *scales) {
+  const int b = blockIdx.y;
+  const int64_t total = (int64_t)d.out[b] * (d.folded[b] ? d.in[b] / 2 : d.in[b]);
+  float m = 0.f;
+  for (int64_t i = (int64_t)blockIdx.x * blockDim.x + threadIdx.x; i < total;
+       i += (int64_t)gridDim.x * blockDim.x)
+    m = fmaxf(m, fabsf(d.w[b][i]));
+#pragma unroll
+  for (int o = 16; o > 0; o >>= 1) m = fmaxf(m, __shfl_xor_sync(0xffffffffu, m, o));
+  if ((threadIdx.x & 31) == 0 && m > 0.f) zp_atomic_absmax(scales + 2 * d.slot[b], m);
+}
+
+__global__ void weight_scale_kernel(const FoldDesc d, float *scales) {
+  const int b = threadIdx.x;
+  if (b < d.n) scales[2 * d.slot[b] + 1] = zp_scale_for_bound(scales[2 * d.slot[b]]);
+}
+
+// fold: writes W_fold [out, in] and its transpose [in, out] as 16-bit planes.
 //   m = 0 (folded == 0): W_fold = W.   m > 0: W = [Wa ; Wb] (rows), W_fold = [Wa -Wb ; Wb Wa].
-__global__ void fold_planes_kernel(int out, int in, int folded, const float *__restrict__ w,
-                                   __nv_bfloat16 *__restrict__ wp, __nv_bfloat16 *__restrict__ wtp,
-                                   int planes) {
-  const int64_t idx = (int64_t)blockIdx.x * blockDim.x + threadIdx.x;
+__global__ void fold_planes_kernel(const FoldDesc d, uint16_t *__restrict__ packed, int planes,
+                                   int fp16, const float *__restrict__ scales) {
+  const int b = blockIdx.y;
+  const int out = d.out[b], in = d.in[b];
   const int64_t total = (int64_t)out * in;
-  if (idx >= total) return;
-  const int col = (int)(idx % in), row = (int)(idx / in);
-  float v;
-  if (!folded) {
-    v = w[idx];
-  } else {
-    const int half = out / 2, kin = in / 2;
-    const bool lower = row >= half, right = col >= kin;
-    const int o = lower ? row - half : row, c = right ? col - kin : col;
-    v = w[(size_t)((lower != right) ? half + o : o) * kin + c];
-    if (!lower && right) v = -v;
-  }
-  for (int p = 0; p < planes; ++p) {
-    const __nv_bfloat16 h = __float2bfloat16_rn(v);
-    wp[(size_t)p * total + idx] = h;
-    wtp[(size_t)p * total + (size_t)col * out + row] = h;
-    v -= __bfloat162float(h);
+  uint16_t *wp = packed + d.woff[b], *wtp = wp + (size_t)planes * total;
+  const float inv = fp16 ? 1.f / scales[2 * d.slot[b] + 1] : 1.f;
+  for (int64_t idx = (int64_t)blockIdx.x * blockDim.x + threadIdx.x; idx < total;
+       idx += (int64_t)gridDim.x * blockDim.x) {
+    const int col = (int)(idx % in), row = (int)(idx / in);
+    float v;
+    if (!d.folded[b]) {
+      v = d.w[b][idx];
+    } else {
+      const int half = out / 2, kin = in / 2;
+      const bool lower = row >= half, right = col >= kin;
+      const int o = lower ? row - half : row, c = right ? col - kin : col;
+      v = d.w[b][(size_t)((lower != right) ? half + o : o) * kin + c];
+      if (!lower && right) v = -v;
+    }
+    v *= inv;
+    for (int p = 0; p < planes; ++p) {
+      uint16_t h;
+      if (fp16) {
+        const __half q = __float2half_rn(v);
+        h = __half_as_ushort(q);
+        v -= __half2float(q);
+      } else {
+        const __nv_bfloat16 q = __float2bfloat16_rn(v);
+        h = __bfloat16_as_ushort(q);
+        v -= __bfloat162float(q);
+      }
+      wp[(size_t)p * total + idx] = h;
+      wtp[(size_t)p * total + (size_t)col * out + row] = h;
+    }
   }
 }
 
@@ -183,13 +271,13 @@ colsum_part_kernel(int64_t rows, int64_t cols, const ZpPlanes a, float *__restri
   if (c0 < cols) {
     for (int64_t r = r0 + ty; r < r1; r += 8) {
       for (int pl = a.planes - 1; pl >= 0; --pl) {
-        const uint4 v = *reinterpret_cast<const uint4 *>(a.base + (size_t)pl * a.plane_stride +
-                                                         r * a.ld + c0);
+        const uint4 v = *reinterpret_cast<const uint4 *>(
+            static_cast<const uint16_t *>(a.base) + (size_t)pl * a.plane_stride + r * a.ld + c0);
         const uint32_t w[4] = {v.x, v.y, v.z, v.w};
 #pragma unroll
         for (int k = 0; k < 4; ++k) {
-          s[2 * k] += __uint_as_float(w[k] << 16);
-          s[2 * k + 1] += __uint_as_float(w[k] & 0xffff0000u);
+          s[2 * k] += zp_plane_value(a, (uint16_t)(w[k] & 0xffffu));
+          s[2 * k + 1] += zp_plane_value(a, (uint16_t)(w[k] >> 16));
         }
       }
     }
@@ -202,7 +290,7 @@ colsum_part_kernel(int64_t rows, int64_t cols, const ZpPlanes a, float *__restri
     for (int k = 0; k < 8; ++k) {
       float acc = 0.f;
       for (int g = 0; g < 8; ++g) acc += red[g][tx][k];
-      if (c0 + k < cols) part[(size_t)blockIdx.y * cols + c0 + k] = acc;
+      if (c0 + k < cols) part[(size_t)blockIdx.y * cols + c0 + k] = acc * zp_scale(a);
     }
   }
 }
@@ -217,12 +305,30 @@ __global__ void colsum_final_kernel(int64_t nparts, int64_t cols, const float *_
 
 }  // namespace
 
-int zp_launch_split_planes(int64_t rows, int64_t cols, const float *in, int64_t ld_in, void *out,
-                           int64_t ld_out, int64_t plane_stride, int planes, cudaStream_t st) {
-  if (rows == 0 || ld_out == 0) return ZP_OK;
-  split_planes_kernel<<<(unsigned)zp_ceil_div(rows * ld_out, 256), 256, 0, st>>>(
-      rows, cols, in, ld_in, (__nv_bfloat16 *)out, ld_out, plane_stride, planes);
+int zp_launch_split_planes(int64_t rows, int64_t cols, const float *in, int64_t ld_in,
+                           const ZpPlanes &out, cudaStream_t st) {
+  if (rows == 0 || out.ld == 0) return ZP_OK;
+  split_planes_kernel<<<(unsigned)zp_ceil_div(rows * (out.ld / 2), 256), 256, 0, st>>>(
+      rows, cols, in, ld_in, out);
   ZP_LAUNCH_CHECK("split_planes_kernel");
+  return ZP_OK;
+}
+
+int zp_launch_absmax(int64_t rows, int64_t cols, const float *in, int64_t ld, float *out,
+                     cudaStream_t st) {
+  ZP_CUDA(cudaMemsetAsync(out, 0, sizeof(float), st));
+  if (rows * cols == 0) return ZP_OK;
+  int64_t blocks = zp_ceil_div(rows * cols, 256 * 8);
+  if (blocks > 1184) blocks = 1184;
+  absmax_kernel<<<(unsigned)blocks, 256, 0, st>>>(rows, cols, in, ld, out);
+  ZP_LAUNCH_CHECK("absmax_kernel");
+  return ZP_OK;
+}
+
+int zp_launch_scale(float factor, const float *a, const float *b, const float *c, float offset_c,
+                    float *scale, cudaStream_t st) {
+  scale_kernel<<<1, 1, 0, st>>>(factor, a, b, c, offset_c, scale);
+  ZP_LAUNCH_CHECK("scale_kernel");
   return ZP_OK;
 }
 
@@ -236,10 +342,12 @@ int zp_launch_gate_fwd(const zp_plan *p, int64_t E, const float *h1, const ZpPla
 }
 
 int zp_launch_gate_bwd(const zp_plan *p, int64_t E, const float *h1, const float *dht,
-                       const ZpPlanes &dh1, cudaStream_t st) {
+                       const ZpPlanes &dh1, float *max_out, cudaStream_t st) {
+  if (max_out) ZP_CUDA(cudaMemsetAsync(max_out, 0, sizeof(float), st));
   if (E == 0) return ZP_OK;
   const int64_t total = E * (p->t.H / 4);
-  gate_bwd_kernel<<<(unsigned)zp_ceil_div(total, 128), 128, 0, st>>>(p->t, E, h1, dht, dh1);
+  gate_bwd_kernel<<<(unsigned)zp_ceil_div(total, 128), 128, 0, st>>>(p->t, E, h1, dht, dh1,
+                                                                      max_out);
   ZP_LAUNCH_CHECK("gate_bwd_kernel");
   return ZP_OK;
 }
@@ -249,18 +357,30 @@ static const float *block_weight(const zp_weights *w, int conv, int m) {
   return conv ? w->c2_wm[m - 1] : w->c1_wm[m - 1];
 }
 
-int zp_launch_fold_weights(const zp_plan *p, const zp_weights *w, void *packed, cudaStream_t st) {
-  __nv_bfloat16 *base = static_cast<__nv_bfloat16 *>(packed);
-  for (int conv = 0; conv < 2; ++conv) {
+int zp_launch_fold_weights(const zp_plan *p, const zp_weights *w, void *packed, float *scales,
+                           cudaStream_t st) {
+  FoldDesc d;
+  d.n = 0;
+  for (int conv = 0; conv < 2; ++conv)
     for (int m = 0; m < p->n_blocks; ++m) {
-      const int out = conv ? p->c2_out[m] : p->c1_out[m], in = conv ? p->c2_in[m] : p->c1_in[m];
-      const int64_t total = (int64_t)out * in;
-      __nv_bfloat16 *wp = base + (conv ? p->c2_woff[m] : p->c1_woff[m]);
-      fold_planes_kernel<<<(unsigned)zp_ceil_div(total, 256), 256, 0, st>>>(
-          out, in, m > 0, block_weight(w, conv, m), wp, wp + (size_t)p->planes * total, p->planes);
-      ZP_LAUNCH_CHECK("fold_planes_kernel");
+      const int b = d.n++;
+      d.out[b] = conv ? p->c2_out[m] : p->c1_out[m];
+      d.in[b] = conv ? p->c2_in[m] : p->c1_in[m];
+      d.folded[b] = m > 0;
+      d.slot[b] = conv * (ZP_MAX_L + 1) + m;
+      d.w[b] = block_weight(w, conv, m);
+      d.woff[b] = conv ? p->c2_woff[m] : p->c1_woff[m];
     }
+  if (p->fp16) {       // one power-of-two scale per weight block from its largest magnitude
+    ZP_CUDA(cudaMemsetAsync(scales, 0, sizeof(float) * 4 * (ZP_MAX_L + 1), st));
+    weight_absmax_kernel<<<dim3(32, d.n), 256, 0, st>>>(d, scales);
+    ZP_LAUNCH_CHECK("weight_absmax_kernel");
+    weight_scale_kernel<<<1, 32, 0, st>>>(d, scales);
+    ZP_LAUNCH_CHECK("weight_scale_kernel");
   }
+  fold_planes_kernel<<<dim3(148, d.n), 256, 0, st>>>(d, static_cast<uint16_t *>(packed), p->planes,
+                                                     p->fp16, scales);
+  ZP_LAUNCH_CHECK("fold_planes_kernel");
   return ZP_OK;
 }
 

@@ -184,6 +184,9 @@ struct GemmParams {
   int num_m, num_n, num_k;
   int ksplit, kb_per_split, kc;   // CTAs-level split of K; k-blocks per TMEM accumulation chunk
   int a_mn, b_mn;         // operand is MN-major
+  int fp16;               // operand planes are fp16 (else bf16)
+  const float *scale_a, *scale_b;   // device scalars multiplying the result (null = 1)
+  float *absmax_out;      // device scalar: running max |C| of what this launch stores (or null)
   const float *bias;
   float *C;
   int64_t ldc, split_stride;
@@ -196,6 +199,11 @@ template <> struct Pairs<1> {
   static constexpr int n = 1;
   __device__ static constexpr int a(int) { return 0; }
   __device__ static constexpr int b(int) { return 0; }
+};
+template <> struct Pairs<2> {
+  static constexpr int n = 3;          // fp16 pair: h0 h0 | h0 h1, h1 h0
+  __device__ static constexpr int a(int i) { return i == 2 ? 1 : 0; }
+  __device__ static constexpr int b(int i) { return i == 1 ? 1 : 0; }
 };
 template <> struct Pairs<3> {
   static constexpr int n = 6;
@@ -305,7 +313,8 @@ gemm_tc_kernel(const __grid_constant__ CUtensorMap map_a, const __grid_constant_
   } else if (warp == 1) {
     // ---------------------------------------------------------------- MMA issuer
     if (elect_one()) {
-      const uint32_t idesc = (1u << 4) | (1u << 7) | (1u << 10) | ((uint32_t)(p.a_mn ? 1 : 0) << 15) |
+      const uint32_t fmt = p.fp16 ? 0u : 1u;    // operand format field: 0 = f16, 1 = bf16
+      const uint32_t idesc = (1u << 4) | (fmt << 7) | (fmt << 10) | ((uint32_t)(p.a_mn ? 1 : 0) << 15) |
                              ((uint32_t)(p.b_mn ? 1 : 0) << 16) | ((uint32_t)(p.BN >> 3) << 17) |
                              ((uint32_t)(BM >> 4) << 24);
       constexpr uint32_t kLayout = BK == 64 ? 2u : 4u;
@@ -357,6 +366,8 @@ gemm_tc_kernel(const __grid_constant__ CUtensorMap map_a, const __grid_constant_
     const int q = warp & 3;                     // TMEM lane quarter this warp may read
     uint32_t unit = 0;
     bool ok = true;
+    const float out_scale = (p.scale_a ? *p.scale_a : 1.f) * (p.scale_b ? *p.scale_b : 1.f);
+    float seen_max = 0.f;
     for (int w = blockIdx.x; w < num_work && ok; w += gridDim.x) {
       const Work x = decode_work(p, w);
       const int row = x.m0 + q * 32 + lane;
@@ -374,15 +385,17 @@ gemm_tc_kernel(const __grid_constant__ CUtensorMap map_a, const __grid_constant_
         for (int cc = 0; cc < p.BN; cc += 32) {
           uint32_t r[32];
           tmem_ld32(t_row + cc, r);
-          if (P == 3) {
+          if (P != 1) {
             uint32_t r2[32];
             tmem_ld32(t_row + kTmemBuf + cc, r2);
             tmem_ld_wait();
 #pragma unroll
             for (int j = 0; j < 32; ++j)
-              r[j] = __float_as_uint(__uint_as_float(r[j]) + __uint_as_float(r2[j]));
+              r[j] = __float_as_uint((__uint_as_float(r[j]) + __uint_as_float(r2[j])) * out_scale);
           } else {
             tmem_ld_wait();
+#pragma unroll
+            for (int j = 0; j < 32; ++j) r[j] = __float_as_uint(__uint_as_float(r[j]) * out_scale);
           }
           if (row < p.M) {
 #pragma unroll
@@ -401,12 +414,15 @@ gemm_tc_kernel(const __grid_constant__ CUtensorMap map_a, const __grid_constant_
                   v.x += o.x; v.y += o.y; v.z += o.z; v.w += o.w;
                 }
                 *reinterpret_cast<float4 *>(crow + n) = v;
+                seen_max = fmaxf(seen_max, fmaxf(fmaxf(fabsf(v.x), fabsf(v.y)),
+                                                 fmaxf(fabsf(v.z), fabsf(v.w))));
               } else if (cc + j < p.BN) {
 #pragma unroll
                 for (int u = 0; u < 4; ++u)
                   if (n + u < p.N) {
                     const float base = first ? (bias ? bias[n + u] : 0.f) : crow[n + u];
                     crow[n + u] = __uint_as_float(r[j + u]) + base;
+                    seen_max = fmaxf(seen_max, fabsf(crow[n + u]));
                   }
               }
             }
@@ -416,6 +432,11 @@ gemm_tc_kernel(const __grid_constant__ CUtensorMap map_a, const __grid_constant_
         __syncwarp();
         if (lane == 0) mbar_arrive(&tmem_empty[buf]);
       }
+    }
+    if (p.absmax_out) {
+#pragma unroll
+      for (int o = 16; o > 0; o >>= 1) seen_max = fmaxf(seen_max, __shfl_xor_sync(0xffffffffu, seen_max, o));
+      if (lane == 0 && seen_max > 0.f) zp_atomic_absmax(p.absmax_out, seen_max);
     }
   }
 
@@ -451,14 +472,14 @@ EncodeTiledFn encode_fn() {
 // 3-d map over (inner, outer, plane) of a bf16 operand
 int make_map(CUtensorMap *map, const void *base, uint64_t inner, uint64_t outer, uint64_t planes,
              uint64_t ld, uint64_t plane_stride, uint32_t box_inner, uint32_t box_outer,
-             CUtensorMapSwizzle swz) {
+             CUtensorMapSwizzle swz, int fp16) {
   EncodeTiledFn fn = encode_fn();
   if (!fn) return ZP_ERR_CUDA;
   const cuuint64_t dims[3] = {inner, outer, planes};
   const cuuint64_t strides[2] = {ld * 2, plane_stride * 2};
   const cuuint32_t box[3] = {box_inner, box_outer, 1};
   const cuuint32_t estr[3] = {1, 1, 1};
-  const CUresult r = fn(map, CU_TENSOR_MAP_DATA_TYPE_BFLOAT16, 3, const_cast<void *>(base), dims,
+  const CUresult r = fn(map, fp16 ? CU_TENSOR_MAP_DATA_TYPE_FLOAT16 : CU_TENSOR_MAP_DATA_TYPE_BFLOAT16, 3, const_cast<void *>(base), dims,
                         strides, box, estr, CU_TENSOR_MAP_INTERLEAVE_NONE, swz,
                         CU_TENSOR_MAP_L2_PROMOTION_L2_256B, CU_TENSOR_MAP_FLOAT_OOB_FILL_NONE);
   if (r != CUDA_SUCCESS) {
@@ -475,7 +496,9 @@ int pick_bn(int64_t N, int cap) {
   return (int)bn;
 }
 
-int block_k(const ZpGemmTc &g) { return (g.planes == 3 && g.variant != 1) ? 32 : 64; }
+int block_k(const ZpGemmTc &g) {
+  return ((g.planes == 3 && g.variant != 1) || g.planes == 2) ? 32 : 64;
+}
 
 void split_plan(const ZpGemmTc &g, int bk, int *ksplit, int *kbs, int *num_k) {
   *num_k = (int)zp_ceil_div(g.K, bk);
@@ -505,15 +528,16 @@ int launch(const ZpGemmTc &g, cudaStream_t st) {
   const int kc_elems = g.kc_elems > 0 ? g.kc_elems : 2048;
   p.kc = kc_elems / BK < 1 ? 1 : kc_elems / BK;
   p.a_mn = g.a_mn; p.b_mn = g.b_mn;
+  p.fp16 = g.fp16; p.scale_a = g.scale_a; p.scale_b = g.scale_b; p.absmax_out = g.absmax_out;
   p.bias = g.bias; p.C = g.C; p.ldc = g.ldc; p.split_stride = g.split_stride; p.status = g.status;
   const CUtensorMapSwizzle kswz = BK == 64 ? CU_TENSOR_MAP_SWIZZLE_128B : CU_TENSOR_MAP_SWIZZLE_64B;
   CUtensorMap ma, mb;
   int rc;
-  if (!g.a_mn) rc = make_map(&ma, g.A, g.K, g.M, P, g.lda, g.a_plane, BK, BM, kswz);
-  else rc = make_map(&ma, g.A, g.M, g.K, P, g.lda, g.a_plane, 64, BK, CU_TENSOR_MAP_SWIZZLE_128B);
+  if (!g.a_mn) rc = make_map(&ma, g.A, g.K, g.M, P, g.lda, g.a_plane, BK, BM, kswz, g.fp16);
+  else rc = make_map(&ma, g.A, g.M, g.K, P, g.lda, g.a_plane, 64, BK, CU_TENSOR_MAP_SWIZZLE_128B, g.fp16);
   if (rc) return rc;
-  if (!g.b_mn) rc = make_map(&mb, g.B, g.K, g.N, P, g.ldb, g.b_plane, BK, p.BN, kswz);
-  else rc = make_map(&mb, g.B, g.N, g.K, P, g.ldb, g.b_plane, 64, BK, CU_TENSOR_MAP_SWIZZLE_128B);
+  if (!g.b_mn) rc = make_map(&mb, g.B, g.K, g.N, P, g.ldb, g.b_plane, BK, p.BN, kswz, g.fp16);
+  else rc = make_map(&mb, g.B, g.N, g.K, P, g.ldb, g.b_plane, 64, BK, CU_TENSOR_MAP_SWIZZLE_128B, g.fp16);
   if (rc) return rc;
   int dev = 0, sms = 148;
   cudaGetDevice(&dev);
@@ -537,6 +561,7 @@ int zp_gemm_tc_splits(const ZpGemmTc &g) {
 int zp_launch_gemm_tc(const ZpGemmTc &g, cudaStream_t st) {
   if (g.M <= 0 || g.N <= 0) return ZP_OK;
   if (g.K <= 0) return ZP_ERR_INVALID_ARG;
+  if (g.fp16 != (g.planes == 2)) return ZP_ERR_UNSUPPORTED;   // fp16 planes come in pairs
   if ((g.lda % 8) || (g.ldb % 8) || (g.a_plane % 8) || (g.b_plane % 8) || (g.ldc % 4) ||
       (g.split_stride % 4))
     return ZP_ERR_INVALID_ARG;
@@ -547,9 +572,11 @@ int zp_launch_gemm_tc(const ZpGemmTc &g, cudaStream_t st) {
     // MN-major tiles are [BK][64] blocks under the 128-byte swizzle
     if (g.planes == 3)
       return g.variant == 1 ? launch<3, 64, 2, 128>(g, st) : launch<3, 32, 3, 256>(g, st);
+    if (g.planes == 2) return launch<2, 32, 4, 256>(g, st);
     if (g.planes == 1) return launch<1, 64, 4, 256>(g, st);
     return ZP_ERR_UNSUPPORTED;
   }
+  if (g.planes == 2) return launch<2, 32, 4, 256>(g, st);
   if (g.planes == 3)
     return g.variant == 1 ? launch<3, 64, 2, 128>(g, st) : launch<3, 32, 3, 256>(g, st);
   if (g.planes == 1) return launch<1, 64, 4, 256>(g, st);

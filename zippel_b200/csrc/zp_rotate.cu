@@ -58,8 +58,8 @@ template <int L, int LMAX>
 struct RotIn {
   static __device__ __forceinline__ void run(const ZpTables &t, const float *xrow,
                                              const float *rot_s, const float *rad_e,
-                                             const ZpPlanes &a1, int64_t a_row, int c2) {
-    RotIn<L - 1, LMAX>::run(t, xrow, rot_s, rad_e, a1, a_row, c2);
+                                             const ZpPlanes &a1, int64_t a_row, int c2, float inv) {
+    RotIn<L - 1, LMAX>::run(t, xrow, rot_s, rad_e, a1, a_row, c2, inv);
     constexpr int n = 2 * L + 1;
     const int C2 = 2 * t.C;
     float u[n][4];
@@ -83,7 +83,7 @@ struct RotIn {
         vload<4>(g, rad_e + t.rad_off[am] + (L - am) * C2 + c2);
 #pragma unroll
         for (int v = 0; v < 4; ++v) acc[v] *= g[v];
-        zp_store_planes<4>(a1, a_row + (int64_t)r * C2 + c2, acc);
+        zp_store_planes<4>(a1, a_row + (int64_t)r * C2 + c2, acc, inv);
       }
     }
   }
@@ -91,7 +91,7 @@ struct RotIn {
 template <int LMAX>
 struct RotIn<-1, LMAX> {
   static __device__ __forceinline__ void run(const ZpTables &, const float *, const float *,
-                                             const float *, const ZpPlanes &, int64_t, int) {}
+                                             const float *, const ZpPlanes &, int64_t, int, float) {}
 };
 
 template <int LMAX>
@@ -115,14 +115,13 @@ rotate_in_kernel(const __grid_constant__ ZpTables t, int64_t E, int epb,
   const int64_t node = second ? dst[e] : src[e];
   const float *xrow = x + (size_t)node * t.K * t.C + (second ? c2 - t.C : c2);
   RotIn<LMAX, LMAX>::run(t, xrow, rot_s + le * t.nnz_pad, radial + (size_t)e * t.R,
-                         a1, e * a1.ld, c2);
+                         a1, e * a1.ld, c2, zp_inv_scale(a1));
 }
 
 // ------------------------------------------------------------------------------------------
 // per-destination-node kernels: blockDim = (32 * W, NPB); W warps cover one node's channels
 // ------------------------------------------------------------------------------------------
 
-template <int LMAX> struct VecFor { static constexpr int value = LMAX <= 4 ? 4 : 2; };
 
 // stage one edge's packed rotation in this node slot's shared buffer
 __device__ __forceinline__ void stage_rot(const ZpTables &t, const float *rot_e, float *buf,
@@ -171,13 +170,16 @@ struct RotBack<-1, LMAX, VEC> {
                                              int) {}
 };
 
-template <int LMAX>
+// VEC channels per lane: 4 (one 16-byte access) while the K x VEC accumulators fit in registers
+// (lmax <= 4), else 2.  One warp per 32 x VEC channels of a node; measured on B200, spreading a
+// node over more warps (VEC = 1) doubles the time: the per-edge barrier and rotation staging
+// dominate, not the loads.
+template <int LMAX, int VEC>
 __global__ void __launch_bounds__(128)
 rotate_back_scatter_kernel(const __grid_constant__ ZpTables t, int64_t N,
                            const float *__restrict__ y, const float *__restrict__ env,
                            const float *__restrict__ rot, const int32_t *__restrict__ row_ptr,
                            float *__restrict__ node_out) {
-  constexpr int VEC = VecFor<LMAX>::value;
   constexpr int K = (LMAX + 1) * (LMAX + 1);
   extern __shared__ float smem[];                        // [NPB][nnz_pad]
   const int slot = threadIdx.y, nthr = blockDim.x;
@@ -231,8 +233,9 @@ struct GradOutE {
   static __device__ __forceinline__ void run(const ZpTables &t, const float *g_row, const float *y_e,
                                              const ZpPlanes &dy, int64_t dy_row, const float *rot_s,
                                              float *part_s, float env, float &genv, int c,
-                                             bool active, int lane) {
-    GradOutE<L - 1, LMAX>::run(t, g_row, y_e, dy, dy_row, rot_s, part_s, env, genv, c, active, lane);
+                                             bool active, int lane, float inv) {
+    GradOutE<L - 1, LMAX>::run(t, g_row, y_e, dy, dy_row, rot_s, part_s, env, genv, c, active, lane,
+                               inv);
     constexpr int n = 2 * L + 1;
     const int mm = t.mmax < L ? t.mmax : L;
     float g[n][4];
@@ -271,7 +274,7 @@ struct GradOutE {
           genv = fmaf(yv[v], tv[v], genv);
           tv[v] *= env;
         }
-        if (active) zp_store_planes<4>(dy, dy_row + (int64_t)r * t.C + c, tv);
+        if (active) zp_store_planes<4>(dy, dy_row + (int64_t)r * t.C + c, tv, inv);
       }
     }
   }
@@ -280,7 +283,7 @@ template <int LMAX>
 struct GradOutE<-1, LMAX> {
   static __device__ __forceinline__ void run(const ZpTables &, const float *, const float *,
                                              const ZpPlanes &, int64_t, const float *, float *,
-                                             float, float &, int, bool, int) {}
+                                             float, float &, int, bool, int, float) {}
 };
 
 // shared memory: rot [epb][nnz_pad] | partial [8 warps][nnz_pad] | genv [8]
@@ -311,7 +314,7 @@ rotate_grad_out_kernel(const __grid_constant__ ZpTables t, int64_t E, int W,
     const float *g_row = g_out + (size_t)dst[e] * t.K * t.C + c;
     GradOutE<LMAX, LMAX>::run(t, g_row, y + (size_t)e * t.Km * t.C, dy, e * dy.ld,
                               rot_s + slot * t.nnz_pad, part_all + warp * t.nnz_pad, env[e], genv,
-                              c, active, lane);
+                              c, active, lane, zp_inv_scale(dy));
     genv = warp_sum(genv);
     if (lane == 0) genv_s[warp] = genv;
   }
@@ -481,9 +484,7 @@ struct NodeLaunch {
   int W;
 };
 
-template <int LMAX>
-NodeLaunch node_launch(const ZpTables &t, int64_t N) {
-  constexpr int VEC = VecFor<LMAX>::value;
+NodeLaunch node_launch(const ZpTables &t, int64_t N, int VEC) {
   const int groups = (t.C + VEC - 1) / VEC;
   const int W = (groups + 31) / 32;
   int npb = 4 / W;
@@ -521,13 +522,21 @@ int zp_launch_rotate_back_scatter(const zp_plan *p, int64_t N, const float *y, c
                                   cudaStream_t st) {
   if (N == 0) return ZP_OK;
   const ZpTables &t = p->t;
-#define CALL(LM)                                                                       \
-  {                                                                                    \
-    const NodeLaunch nl = node_launch<LM>(t, N);                                       \
-    if (nl.W > 4) return ZP_ERR_UNSUPPORTED;                                           \
-    const size_t smem = (size_t)nl.block.y * t.nnz_pad * sizeof(float);                \
-    rotate_back_scatter_kernel<LM><<<nl.grid, nl.block, smem, st>>>(t, N, y, env, rot, \
-                                                                    row_ptr, node_out); \
+  const int vec = t.lmax <= 4 ? 4 : 2;
+  const NodeLaunch nl = node_launch(t, N, vec);
+  if (nl.W > 4) return ZP_ERR_UNSUPPORTED;
+  const size_t smem = (size_t)nl.block.y * t.nnz_pad * sizeof(float);
+#define CALL(LM)                                                                              \
+  {                                                                                           \
+    if (vec == 1)                                                                             \
+      rotate_back_scatter_kernel<LM, 1><<<nl.grid, nl.block, smem, st>>>(t, N, y, env, rot,   \
+                                                                         row_ptr, node_out); \
+    else if (vec == 2)                                                                        \
+      rotate_back_scatter_kernel<LM, 2><<<nl.grid, nl.block, smem, st>>>(t, N, y, env, rot,   \
+                                                                         row_ptr, node_out); \
+    else                                                                                      \
+      rotate_back_scatter_kernel<LM, 4><<<nl.grid, nl.block, smem, st>>>(t, N, y, env, rot,   \
+                                                                         row_ptr, node_out); \
   }
   ZP_DISPATCH_LMAX(t.lmax, CALL)
 #undef CALL

@@ -21,10 +21,11 @@
 // gradients, which run over all edges) can also be split over CTAs: split s writes its own
 // partial matrix C + s * split_stride, reduced afterwards in a fixed order.
 //
-// Structure: persistent CTAs (one per SM), 192 threads.
+// Structure: persistent CTAs (one per SM), 320 threads.
 //   warp 0      TMA producer: one elected lane streams A/B plane tiles into a ring of stages
 //   warp 1      allocates TMEM, then one elected lane issues tcgen05.mma and commits
-//   warps 2..5  epilogue: tcgen05.ld the 128 x BN accumulator, add bias, store fp32 rows
+//   warps 2..9  epilogue: tcgen05.ld the 128 x BN accumulator into registers, release TMEM,
+//               then scale, add bias and store fp32 rows
 // With one plane two TMEM accumulators (2 x 256 columns) let the epilogue of one tile overlap
 // the main loop of the next; with three planes the 512 columns hold the leading and the small
 // accumulator of one tile.  Tiles are ordered n-fastest so CTAs running side by side share one A row block
@@ -46,7 +47,7 @@ namespace {
 
 constexpr int BM = 128;
 constexpr int kTmemBuf = 256;          // TMEM columns per accumulator buffer
-constexpr int kThreads = 192;
+constexpr int kThreads = 320;            // producer warp, MMA warp, eight epilogue warps
 constexpr uint64_t kWaitLimitNs = 2000000000ull;
 
 __device__ __forceinline__ uint32_t smem_u32(const void *p) {
@@ -257,7 +258,7 @@ gemm_tc_kernel(const __grid_constant__ CUtensorMap map_a, const __grid_constant_
 
   if (threadIdx.x == 0) {
     for (int s = 0; s < STAGES; ++s) { mbar_init(&full[s], 1); mbar_init(&empty[s], 1); }
-    for (int b = 0; b < 2; ++b) { mbar_init(&tmem_full[b], 1); mbar_init(&tmem_empty[b], 4); }
+    for (int b = 0; b < 2; ++b) { mbar_init(&tmem_full[b], 1); mbar_init(&tmem_empty[b], 8); }
     *abort_flag = 0;
     asm volatile("fence.mbarrier_init.release.cluster;" ::: "memory");
     asm volatile("fence.proxy.async.shared::cta;" ::: "memory");
@@ -362,12 +363,17 @@ gemm_tc_kernel(const __grid_constant__ CUtensorMap map_a, const __grid_constant_
       }
     }
   } else {
-    // ---------------------------------------------------------------- epilogue (warps 2..5)
-    const int q = warp & 3;                     // TMEM lane quarter this warp may read
+    // ---------------------------------------------------------------- epilogue (warps 2..9)
+    // Eight warps: warp w reads TMEM lane quarter w % 4 (the only one it may access) and column
+    // half (w - 2) / 4.  A warp first pulls its whole 32 x 128 slice of the accumulator(s) into
+    // registers and releases TMEM, so the next tile's MMAs start while it scales and stores.
+    const int q = warp & 3;
+    const int half = (warp - 2) >> 2;
     uint32_t unit = 0;
     bool ok = true;
     const float out_scale = (p.scale_a ? *p.scale_a : 1.f) * (p.scale_b ? *p.scale_b : 1.f);
     float seen_max = 0.f;
+    const int col_lo = half * 128, col_hi = min(p.BN, col_lo + 128);
     for (int w = blockIdx.x; w < num_work && ok; w += gridDim.x) {
       const Work x = decode_work(p, w);
       const int row = x.m0 + q * 32 + lane;
@@ -382,55 +388,66 @@ gemm_tc_kernel(const __grid_constant__ CUtensorMap map_a, const __grid_constant_
         tcgen05_fence_after();
         const uint32_t t_row = tmem_base + ((uint32_t)(q * 32) << 16) +
                                (P == 1 ? (uint32_t)buf * kTmemBuf : 0u);
-        for (int cc = 0; cc < p.BN; cc += 32) {
-          uint32_t r[32];
-          tmem_ld32(t_row + cc, r);
-          if (P != 1) {
-            uint32_t r2[32];
-            tmem_ld32(t_row + kTmemBuf + cc, r2);
-            tmem_ld_wait();
+        float v[4][32];
 #pragma unroll
-            for (int j = 0; j < 32; ++j)
-              r[j] = __float_as_uint((__uint_as_float(r[j]) + __uint_as_float(r2[j])) * out_scale);
-          } else {
-            tmem_ld_wait();
+        for (int b = 0; b < 4; ++b) {
+          const int cc = col_lo + 32 * b;
+          if (cc < col_hi) {                    // warp-uniform
+            uint32_t r[32];
+            tmem_ld32(t_row + cc, r);
+            if (P != 1) {
+              uint32_t r2[32];
+              tmem_ld32(t_row + kTmemBuf + cc, r2);
+              tmem_ld_wait();
 #pragma unroll
-            for (int j = 0; j < 32; ++j) r[j] = __float_as_uint(__uint_as_float(r[j]) * out_scale);
-          }
-          if (row < p.M) {
+              for (int j = 0; j < 32; ++j)
+                v[b][j] = (__uint_as_float(r[j]) + __uint_as_float(r2[j])) * out_scale;
+            } else {
+              tmem_ld_wait();
 #pragma unroll
-            for (int j = 0; j < 32; j += 4) {
-              const int n = x.n0 + cc + j;
-              if (cc + j < p.BN && n + 3 < p.N) {
-                float4 v = make_float4(__uint_as_float(r[j]), __uint_as_float(r[j + 1]),
-                                       __uint_as_float(r[j + 2]), __uint_as_float(r[j + 3]));
-                if (first) {
-                  if (bias) {
-                    const float4 bv = *reinterpret_cast<const float4 *>(bias + n);
-                    v.x += bv.x; v.y += bv.y; v.z += bv.z; v.w += bv.w;
-                  }
-                } else {
-                  const float4 o = *reinterpret_cast<const float4 *>(crow + n);
-                  v.x += o.x; v.y += o.y; v.z += o.z; v.w += o.w;
-                }
-                *reinterpret_cast<float4 *>(crow + n) = v;
-                seen_max = fmaxf(seen_max, fmaxf(fmaxf(fabsf(v.x), fabsf(v.y)),
-                                                 fmaxf(fabsf(v.z), fabsf(v.w))));
-              } else if (cc + j < p.BN) {
-#pragma unroll
-                for (int u = 0; u < 4; ++u)
-                  if (n + u < p.N) {
-                    const float base = first ? (bias ? bias[n + u] : 0.f) : crow[n + u];
-                    crow[n + u] = __uint_as_float(r[j + u]) + base;
-                    seen_max = fmaxf(seen_max, fabsf(crow[n + u]));
-                  }
-              }
+              for (int j = 0; j < 32; ++j) v[b][j] = __uint_as_float(r[j]) * out_scale;
             }
           }
         }
         tcgen05_fence_before();
         __syncwarp();
-        if (lane == 0) mbar_arrive(&tmem_empty[buf]);
+        if (lane == 0) mbar_arrive(&tmem_empty[buf]);      // TMEM slice is in registers now
+
+        if (row < p.M) {
+#pragma unroll
+          for (int b = 0; b < 4; ++b) {
+            const int cc = col_lo + 32 * b;
+            if (cc >= col_hi) continue;
+#pragma unroll
+            for (int j = 0; j < 32; j += 4) {
+              const int n = x.n0 + cc + j;
+              if (cc + j < p.BN && n + 3 < p.N) {
+                float4 o = make_float4(v[b][j], v[b][j + 1], v[b][j + 2], v[b][j + 3]);
+                if (first) {
+                  if (bias) {
+                    const float4 bv = *reinterpret_cast<const float4 *>(bias + n);
+                    o.x += bv.x; o.y += bv.y; o.z += bv.z; o.w += bv.w;
+                  }
+                } else {
+                  const float4 old = *reinterpret_cast<const float4 *>(crow + n);
+                  o.x += old.x; o.y += old.y; o.z += old.z; o.w += old.w;
+                }
+                *reinterpret_cast<float4 *>(crow + n) = o;
+                seen_max = fmaxf(seen_max, fmaxf(fmaxf(fabsf(o.x), fabsf(o.y)),
+                                                 fmaxf(fabsf(o.z), fabsf(o.w))));
+              } else if (cc + j < p.BN) {
+#pragma unroll
+                for (int u = 0; u < 4; ++u)
+                  if (n + u < p.N) {
+                    const float base = first ? (bias ? bias[n + u] : 0.f) : crow[n + u];
+                    const float o = v[b][j + u] + base;
+                    crow[n + u] = o;
+                    seen_max = fmaxf(seen_max, fabsf(o));
+                  }
+              }
+            }
+          }
+        }
       }
     }
     if (p.absmax_out) {

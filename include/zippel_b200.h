@@ -204,6 +204,18 @@ int zp_gemm_planes(zp_plan *plan, int64_t M, int64_t N, int64_t K, int planes, c
                    int64_t b_plane, int b_mn, const float *bias, float *C, int64_t ldc,
                    int variant, int ksplit, int64_t split_stride, int kc_elems, int *splits_out,
                    void *stream);
+/* A dense layer on the same engine, in the plan's operand format: y[M,N] = x[M,K] w[N,K]^T + bias,
+ * and its VJP (dx may be null; db may be null).  Takes over the fp32 library GEMMs of the widest
+ * radial-MLP layer (rad_func[6], blocks/eso2_ref.py:169-182, 327).  K and N multiples of 8.
+ * `work`: zp_linear_work_bytes(plan, M, K, N) bytes of device scratch, caller-owned.           */
+size_t zp_linear_work_bytes(const zp_plan *plan, int64_t M, int64_t K, int64_t N);
+int zp_linear_forward(const zp_plan *plan, int64_t M, int64_t K, int64_t N, const float *x,
+                      const float *w, const float *bias, float *y, void *work, size_t work_bytes,
+                      void *stream);
+int zp_linear_backward(const zp_plan *plan, int64_t M, int64_t K, int64_t N, const float *x,
+                       const float *w, const float *dy, float *dx, float *dw, float *db,
+                       void *work, size_t work_bytes, void *stream);
+
 /* Reads (synchronously) and clears the plan's device status word: ZP_OK, or
  * ZP_ERR_DEVICE_TIMEOUT if a bounded device-side wait gave up since the last read.          */
 int zp_plan_device_status(zp_plan *plan, int *status_out);

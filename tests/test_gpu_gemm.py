@@ -101,3 +101,30 @@ def test_long_contraction_chunks_and_splits(planes):
     assert (err_p if planes == 1 else err_f) < 4e-6
     err_p, err_f = run_gemm(256, 256, 9000, planes, False, False, ksplit=3, kc=512, bias=True)
     assert (err_p if planes == 1 else err_f) < 4e-6
+
+
+@pytest.mark.parametrize("precision", [0, 1, 2])
+@pytest.mark.parametrize("M,K,N", [(1000, 128, 3072), (77, 40, 24), (0, 16, 8)])
+def test_tensor_core_linear_and_vjp(M, K, N, precision):
+    """zp_linear_forward/backward against fp64 torch (bf16 operands: 2e-2, else 4e-6)."""
+    from zippel_b200.blocks.eso2 import Plan, TensorCoreLinear
+    plan = Plan.get(2, 2, 8, 8, "cuda", precision)
+    g = torch.Generator("cpu").manual_seed(M + N)
+    x = torch.randn(M, K, generator=g, dtype=torch.float64)
+    w = torch.randn(N, K, generator=g, dtype=torch.float64) * 0.1
+    b = torch.randn(N, generator=g, dtype=torch.float64)
+    up = torch.randn(M, N, generator=g, dtype=torch.float64)
+    xr, wr, br = (t.clone().requires_grad_(True) for t in (x, w, b))
+    want = torch.nn.functional.linear(xr, wr, br)
+    gx, gw, gb = torch.autograd.grad((want * up).sum(), [xr, wr, br])
+    xc, wc, bc = (t.float().cuda().requires_grad_(True) for t in (x, w, b))
+    got = TensorCoreLinear.apply(plan, xc, wc, bc)
+    hx, hw, hb = torch.autograd.grad((got * up.float().cuda()).sum(), [xc, wc, bc])
+    tol = 2e-2 if precision == 1 else 4e-6
+    rel = lambda a, r: ((a.double().cpu() - r).norm() / r.norm().clamp_min(1e-300)).item()  # noqa: E731
+    if M:
+        assert rel(got, want.detach()) < tol and rel(hx, gx) < tol and rel(hw, gw) < tol
+        assert rel(hb, gb) < tol
+    else:
+        assert got.shape == (0, N) and hw.abs().max().item() == 0.0
+    assert plan.device_status() == 0

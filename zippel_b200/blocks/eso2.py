@@ -302,6 +302,53 @@ class EdgeConvFunction(torch.autograd.Function):
         return (None, None, *outs)
 
 
+class TensorCoreLinear(torch.autograd.Function):
+    """y = x W^T + b on the contraction engine (``zp_linear_forward/backward``), in the plan's
+    operand format.  Used for the widest radial layer; first order only."""
+
+    @staticmethod
+    def forward(ctx, plan: Plan, x, weight, bias):
+        lib = _lib.load()
+        xf, wf, bf = _f32(x), _f32(weight), _f32(bias)
+        m, k = xf.shape
+        n = wf.shape[0]
+        y = torch.empty(m, n, dtype=torch.float32, device=xf.device)
+        nbytes = lib.zp_linear_work_bytes(plan.handle, m, k, n)
+        if nbytes == 0:
+            raise _lib.ZpError(2, "zp_linear_work_bytes")
+        work = torch.empty(nbytes, dtype=torch.uint8, device=xf.device)
+        with torch.cuda.device(xf.device):
+            st = torch.cuda.current_stream().cuda_stream
+            _lib.check(lib.zp_linear_forward(plan.handle, m, k, n, xf.data_ptr(), wf.data_ptr(),
+                                             bf.data_ptr(), y.data_ptr(), work.data_ptr(), nbytes,
+                                             st), "zp_linear_forward")
+        ctx.plan, ctx.dtypes = plan, (x.dtype, weight.dtype, bias.dtype)
+        ctx.save_for_backward(xf, wf)
+        return y.to(x.dtype)
+
+    @staticmethod
+    @torch.autograd.function.once_differentiable
+    def backward(ctx, grad_y):
+        lib = _lib.load()
+        xf, wf = ctx.saved_tensors
+        plan = ctx.plan
+        m, k = xf.shape
+        n = wf.shape[0]
+        dy = _f32(grad_y)
+        dx, dw = torch.empty_like(xf), torch.empty_like(wf)
+        db = torch.empty(n, dtype=torch.float32, device=xf.device)
+        nbytes = lib.zp_linear_work_bytes(plan.handle, m, k, n)
+        work = torch.empty(nbytes, dtype=torch.uint8, device=xf.device)
+        with torch.cuda.device(xf.device):
+            st = torch.cuda.current_stream().cuda_stream
+            _lib.check(lib.zp_linear_backward(plan.handle, m, k, n, xf.data_ptr(), wf.data_ptr(),
+                                              dy.data_ptr(), dx.data_ptr(), dw.data_ptr(),
+                                              db.data_ptr(), work.data_ptr(), nbytes, st),
+                       "zp_linear_backward")
+        dt = ctx.dtypes
+        return None, dx.to(dt[0]), dw.to(dt[1]), db.to(dt[2])
+
+
 def edge_conv(plan: Plan, graph: EdgeGraph, x_node, edge_vec, cos_g, sin_g, radial, env,
               c1_m0: nn.Linear, c1_m, c2_m0: nn.Linear, c2_m) -> torch.Tensor:
     return EdgeConvFunction.apply(plan, graph, x_node, edge_vec, cos_g, sin_g, radial, env,
@@ -394,9 +441,15 @@ class ESO2Block(nn.Module):
         dist = edge_vec.pow(2).sum(-1).clamp_min(1e-24).sqrt()
         x_edge = torch.cat([self.gaussian_basis(dist), self.elem_emb(atomic_numbers[src]),
                             self.elem_emb(atomic_numbers[dst])], dim=-1)
-        radial = self.rad_func(x_edge)
+        plan = self.plan(pos.device)
+        hidden = self.rad_func[:-1](x_edge)
+        last = self.rad_func[-1]
+        if last.in_features % 8 == 0 and last.out_features % 8 == 0 and hidden.shape[0] > 0:
+            radial = TensorCoreLinear.apply(plan, hidden, last.weight, last.bias)
+        else:
+            radial = last(hidden)
         env = self.envelope(dist / cfg.cutoff)
-        return edge_conv(self.plan(pos.device), graph, x_node, edge_vec, cos_gamma_k[perm],
+        return edge_conv(plan, graph, x_node, edge_vec, cos_gamma_k[perm],
                          sin_gamma_k[perm], radial, env, self.c1_m0, self.c1_m, self.c2_m0,
                          self.c2_m)
 

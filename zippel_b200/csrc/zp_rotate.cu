@@ -119,7 +119,7 @@ rotate_in_kernel(const __grid_constant__ ZpTables t, int64_t E, int epb,
 }
 
 // ------------------------------------------------------------------------------------------
-// per-destination-node kernels: blockDim = (32 * W, NPB); W warps cover one node's channels
+// per-destination-node kernel (forward scatter)
 // ------------------------------------------------------------------------------------------
 
 
@@ -127,12 +127,6 @@ rotate_in_kernel(const __grid_constant__ ZpTables t, int64_t E, int epb,
 __device__ __forceinline__ void stage_rot(const ZpTables &t, const float *rot_e, float *buf,
                                           int tid, int nthreads) {
   for (int i = tid; i < t.nnz_pad; i += nthreads) buf[i] = rot_e[i];
-}
-
-// named barrier over the threads of one node slot (W warps); slot ids start at 1
-__device__ __forceinline__ void slot_sync(int slot, int nthreads) {
-  if (nthreads == 32) __syncwarp();
-  else asm volatile("bar.sync %0, %1;" ::"r"(slot + 1), "r"(nthreads) : "memory");
 }
 
 template <int L, int LMAX, int VEC>
@@ -170,23 +164,25 @@ struct RotBack<-1, LMAX, VEC> {
                                              int) {}
 };
 
-// VEC channels per lane: 4 (one 16-byte access) while the K x VEC accumulators fit in registers
-// (lmax <= 4), else 2.  One warp per 32 x VEC channels of a node; measured on B200, spreading a
-// node over more warps (VEC = 1) doubles the time: the per-edge barrier and rotation staging
-// dominate, not the loads.
+// One block (four warps) owns 32 x VEC channels of one destination node.  The node's edges are
+// dealt round-robin to the warps (warp w takes edges w, w + 4, ... of the CSR segment), which cuts
+// the serial load->rotate chain per node by four; the four partial sums are then added in warp
+// order through shared memory, so the result does not depend on timing.
+constexpr int kBackWarps = 4;
 template <int LMAX, int VEC>
-__global__ void __launch_bounds__(128)
+__global__ void __launch_bounds__(32 * kBackWarps)
 rotate_back_scatter_kernel(const __grid_constant__ ZpTables t, int64_t N,
                            const float *__restrict__ y, const float *__restrict__ env,
                            const float *__restrict__ rot, const int32_t *__restrict__ row_ptr,
                            float *__restrict__ node_out) {
   constexpr int K = (LMAX + 1) * (LMAX + 1);
-  extern __shared__ float smem[];                        // [NPB][nnz_pad]
-  const int slot = threadIdx.y, nthr = blockDim.x;
-  float *rot_s = smem + slot * t.nnz_pad;
-  const int64_t n = (int64_t)blockIdx.x * blockDim.y + slot;
-  if (n >= N) return;                                    // whole slot leaves together
-  const int c = threadIdx.x * VEC;
+  extern __shared__ float smem[];          // rot [4][nnz_pad] | partial [4][K][32 * VEC]
+  const int warp = threadIdx.x / 32, lane = threadIdx.x % 32;
+  float *rot_s = smem + warp * t.nnz_pad;
+  float *part = smem + kBackWarps * t.nnz_pad;
+  const int64_t n = blockIdx.x;
+  const int c0 = blockIdx.y * 32 * VEC;
+  const int c = c0 + lane * VEC;
   const bool active = c < t.C;
   float acc[K][VEC];
 #pragma unroll
@@ -194,17 +190,43 @@ rotate_back_scatter_kernel(const __grid_constant__ ZpTables t, int64_t N,
 #pragma unroll
     for (int v = 0; v < VEC; ++v) acc[k][v] = 0.f;
   const int e_beg = row_ptr[n], e_end = row_ptr[n + 1];
-  for (int e = e_beg; e < e_end; ++e) {
-    slot_sync(slot, nthr);
-    stage_rot(t, rot + (size_t)e * t.nnz_pad, rot_s, threadIdx.x, nthr);
-    slot_sync(slot, nthr);
-    if (active)
-      RotBack<LMAX, LMAX, VEC>::run(t, y + (size_t)e * t.Km * t.C, rot_s, env[e], acc, c);
-  }
-  if (active) {
-    float *o = node_out + (size_t)n * K * t.C + c;
+  // the next edge's packed rotation is fetched into registers while the current one is used
+  constexpr int kRotRegs = (ZP_MAX_KM * ZP_MAX_N + 31) / 32;     // generous upper bound, unrolled
+  float nxt[8];
+  static_assert(kRotRegs >= 1, "");
+  auto fetch = [&](int e) {
 #pragma unroll
-    for (int k = 0; k < K; ++k) vstore<VEC>(o + (size_t)k * t.C, acc[k]);
+    for (int i = 0; i < 8; ++i) {
+      const int k = lane + 32 * i;
+      nxt[i] = (e < e_end && k < t.nnz_pad) ? rot[(size_t)e * t.nnz_pad + k] : 0.f;
+    }
+  };
+  fetch(e_beg + warp);
+  for (int e = e_beg + warp; e < e_end; e += kBackWarps) {
+    __syncwarp();
+#pragma unroll
+    for (int i = 0; i < 8; ++i)
+      if (lane + 32 * i < t.nnz_pad) rot_s[lane + 32 * i] = nxt[i];
+    const float env_e = env[e];
+    fetch(e + kBackWarps);
+    __syncwarp();
+    if (active)
+      RotBack<LMAX, LMAX, VEC>::run(t, y + (size_t)e * t.Km * t.C, rot_s, env_e, acc, c);
+  }
+  constexpr int W = 32 * VEC;              // channels of this block
+#pragma unroll
+  for (int k = 0; k < K; ++k)
+#pragma unroll
+    for (int v = 0; v < VEC; ++v) part[(warp * K + k) * W + lane * VEC + v] = acc[k][v];
+  __syncthreads();
+  for (int i = threadIdx.x; i < K * W; i += blockDim.x) {
+    const int k = i / W, cc = i % W;
+    if (c0 + cc < t.C) {
+      float s = 0.f;
+#pragma unroll
+      for (int w = 0; w < kBackWarps; ++w) s += part[(w * K + k) * W + cc];
+      node_out[((size_t)n * K + k) * t.C + c0 + cc] = s;
+    }
   }
 }
 
@@ -479,23 +501,6 @@ node_reduce_kernel(int64_t N, int KC4, const float4 *__restrict__ du_both,
   }
 }
 
-struct NodeLaunch {
-  dim3 grid, block;
-  int W;
-};
-
-NodeLaunch node_launch(const ZpTables &t, int64_t N, int VEC) {
-  const int groups = (t.C + VEC - 1) / VEC;
-  const int W = (groups + 31) / 32;
-  int npb = 4 / W;
-  if (npb < 1) npb = 1;
-  NodeLaunch nl;
-  nl.W = W;
-  nl.block = dim3(32 * W, npb);
-  nl.grid = dim3((unsigned)zp_ceil_div(N, npb));
-  return nl;
-}
-
 }  // namespace
 
 int zp_launch_rotate_in(const zp_plan *p, int64_t E, const float *x, const int32_t *src,
@@ -522,21 +527,18 @@ int zp_launch_rotate_back_scatter(const zp_plan *p, int64_t N, const float *y, c
                                   cudaStream_t st) {
   if (N == 0) return ZP_OK;
   const ZpTables &t = p->t;
-  const int vec = t.lmax <= 4 ? 4 : 2;
-  const NodeLaunch nl = node_launch(t, N, vec);
-  if (nl.W > 4) return ZP_ERR_UNSUPPORTED;
-  const size_t smem = (size_t)nl.block.y * t.nnz_pad * sizeof(float);
-#define CALL(LM)                                                                              \
-  {                                                                                           \
-    if (vec == 1)                                                                             \
-      rotate_back_scatter_kernel<LM, 1><<<nl.grid, nl.block, smem, st>>>(t, N, y, env, rot,   \
-                                                                         row_ptr, node_out); \
-    else if (vec == 2)                                                                        \
-      rotate_back_scatter_kernel<LM, 2><<<nl.grid, nl.block, smem, st>>>(t, N, y, env, rot,   \
-                                                                         row_ptr, node_out); \
-    else                                                                                      \
-      rotate_back_scatter_kernel<LM, 4><<<nl.grid, nl.block, smem, st>>>(t, N, y, env, rot,   \
-                                                                         row_ptr, node_out); \
+  const int vec = t.lmax <= 4 ? 4 : 2;     // K x VEC accumulators must fit in registers
+  const dim3 grid((unsigned)N, (unsigned)zp_ceil_div(t.C, 32 * vec));
+  const size_t smem = (size_t)kBackWarps * (t.nnz_pad + (size_t)t.K * 32 * vec) * sizeof(float);
+#define CALL(LM)                                                                               \
+  {                                                                                            \
+    auto kern = vec == 4 ? rotate_back_scatter_kernel<LM, 4> : rotate_back_scatter_kernel<LM, 2>; \
+    static size_t allowed = 48 * 1024;     /* per instantiation: raise the limit once */         \
+    if (smem > allowed) {                                                                      \
+      ZP_CUDA(cudaFuncSetAttribute(kern, cudaFuncAttributeMaxDynamicSharedMemorySize, (int)smem)); \
+      allowed = smem;                                                                          \
+    }                                                                                          \
+    kern<<<grid, 32 * kBackWarps, smem, st>>>(t, N, y, env, rot, row_ptr, node_out);           \
   }
   ZP_DISPATCH_LMAX(t.lmax, CALL)
 #undef CALL

@@ -413,6 +413,110 @@ def run_ours(args) -> dict | None:
     return line
 
 
+# ------------------------------------------------------------------------------------------
+# the larger BASELINE configurations (not the headline line): batched structures, single graph
+# ------------------------------------------------------------------------------------------
+
+def run_large(args) -> dict | None:
+    """`--workload cfg3`: `--structures` independent 200-atom structures (bf16 precision unless
+    --precision is given), sharded over the ranks with no data-path exchange.  `--workload cfg4`:
+    one graph of `--atoms` atoms at lmax 6, partitioned by destination-node range over the ranks
+    (all-gather of embedding shards forward, reduce-scatter backward).  Inputs are resident on the
+    device; the step is the module API's forward + VJP, chunked over destination ranges when the
+    activations exceed memory (the backward then recomputes each chunk's forward)."""
+    import torch.distributed as dist
+
+    from zippel_b200 import partition as part
+    from zippel_b200.blocks.eso2 import BlockConfig, ESO2Block
+    from zippel_b200.graph import EdgeGraph, synthetic_batch
+
+    world = int(os.environ.get("WORLD_SIZE", "1"))
+    rank = int(os.environ.get("RANK", "0"))
+    local = int(os.environ.get("LOCAL_RANK", "0"))
+    torch.cuda.set_device(local)
+    dev = torch.device("cuda", local)
+    if world > 1:
+        dist.init_process_group("nccl", device_id=dev)
+    cfg = dict(CFG)
+    if args.workload == "cfg3":
+        ranges = part.structure_ranges(args.structures, world)
+        n_struct = ranges[rank][1] - ranges[rank][0]
+        batch = synthetic_batch(200, cfg["lmax"], cfg["sphere_channels"], cfg["cutoff"],
+                                density=DENSITY, max_neighbors=MAX_NEIGHBORS,
+                                n_structures=n_struct, seed=100 + rank)
+        precision = args.precision if args.precision_given else "bf16"
+    else:
+        cfg["lmax"] = 6
+        batch = synthetic_batch(args.atoms, 6, cfg["sphere_channels"], cfg["cutoff"],
+                                density=DENSITY, max_neighbors=MAX_NEIGHBORS, seed=5)
+        precision = args.precision
+    block = ESO2Block(BlockConfig(**cfg), precision=precision)
+    xavier_(block, 0)
+    block = block.to(dev)
+    n = batch["pos"].shape[0]
+    g = torch.Generator("cpu").manual_seed(9)
+    up_full = torch.randn(batch["x_node"].shape, generator=g)
+    d = {k: v.to(dev) for k, v in batch.items() if torch.is_tensor(v)}
+    if args.workload == "cfg4" and world > 1:
+        nranges = part.node_ranges(n, world)
+        a, b = nranges[rank]
+        keep = part.local_edges(d["edge_index"], nranges[rank])
+        ei, sh, cg, sg = d["edge_index"][:, keep], d["shifts"][keep], d["cos_gamma_k"][keep], d["sin_gamma_k"][keep]
+        x_in, up = d["x_node"][a:b].clone(), up_full[a:b].to(dev)
+    else:
+        ei, sh, cg, sg = d["edge_index"], d["shifts"], d["cos_gamma_k"], d["sin_gamma_k"]
+        x_in, up = d["x_node"], up_full.to(dev)
+    graph = EdgeGraph.build(ei, n)
+    e_local = ei.shape[1]
+
+    def step():
+        pos = d["pos"].detach().requires_grad_(True)
+        x = x_in.detach().requires_grad_(True)
+        if args.workload == "cfg4" and world > 1:
+            fn = lambda p_, z_, xf, e_, s_, c_, g_: block.node_output(p_, z_, xf, e_, s_, c_, g_, graph=graph)  # noqa: E731
+            out = part.partitioned_node_output(fn, pos, d["atomic_numbers"], x, ei, sh, cg, sg, nranges, rank)
+        else:
+            out = block.node_output(pos, d["atomic_numbers"], x, ei, sh, cg, sg, graph=graph)
+        grads = torch.autograd.grad((out * up).sum(), [x, pos, *block.parameters()], allow_unused=True)
+        if world > 1:
+            part.all_reduce_grads([grads[1], *[g_ for g_ in grads[2:] if g_ is not None]])
+        return grads
+
+    for _ in range(max(args.warmup, 1)):
+        step()
+    torch.cuda.synchronize()
+    if world > 1:
+        dist.barrier()
+    a_ev, b_ev = torch.cuda.Event(True), torch.cuda.Event(True)
+    a_ev.record()
+    for _ in range(args.steps):
+        step()
+    b_ev.record()
+    torch.cuda.synchronize()
+    ms = torch.tensor([a_ev.elapsed_time(b_ev) / args.steps], dtype=torch.float64, device=dev)
+    edges = torch.tensor([float(e_local)], dtype=torch.float64, device=dev)
+    if world > 1:
+        dist.all_reduce(ms, op=dist.ReduceOp.MAX)
+        dist.all_reduce(edges)
+    chunks = max((len(v) for v in graph.__dict__.get("_chunk_cache", {}).values()), default=1)
+    status = block.plan(dev).device_status()
+    line = None
+    if rank == 0:
+        line = {"metric": METRIC, "workload": args.workload, "value": edges.item() / (ms.item() * 1e-3),
+                "unit": "edges/s", "n_gpus": world, "steps": args.steps, "ms_per_step": ms.item(),
+                "precision": precision, "data": "synthetic", "scaling": "strong",
+                "config": {"atoms_total": n if args.workload == "cfg4" else 200 * args.structures,
+                           "edges_total": edges.item(), "lmax": cfg["lmax"], "mmax": cfg["mmax"],
+                           "channels": cfg["sphere_channels"], "chunks_per_rank": chunks,
+                           "note": "module API forward+VJP, inputs resident; chunked runs "
+                                   "recompute the forward in the backward"},
+                "device_status": status, "peak_mem_gb": torch.cuda.max_memory_allocated(dev) / 1e9}
+    if world > 1:
+        dist.barrier()
+        dist.destroy_process_group()
+    return line
+
+
 def main() -> None:
     ap = argparse.ArgumentParser()
     ap.add_argument("--gpus", type=int, default=1)
@@ -424,10 +528,14 @@ def main() -> None:
     ap.add_argument("--no-cpu-baseline", action="store_true")
     ap.add_argument("--precision", default="fp32", choices=["fp32", "fp32_bf16x3", "bf16"],
                     help="operand format of the SO(2) contraction (see ESO2Block)")
+    ap.add_argument("--workload", default="cfg2", choices=["cfg2", "cfg3", "cfg4"],
+                    help="cfg2 = the benchmark line; cfg3 / cfg4 = the larger BASELINE configurations")
+    ap.add_argument("--structures", type=int, default=512, help="cfg3: number of 200-atom structures")
     ap.add_argument("--atoms", type=int, default=N_ATOMS,
                     help="atoms per GPU; anything but the default is a profiling-size run, "
                          "not the benchmark workload")
     args = ap.parse_args()
+    args.precision_given = any(a.startswith("--precision") for a in sys.argv[1:])
     # Library chatter (e.g. NCCL's version banner) must not share stdout with the JSON line:
     # everything else written to fd 1 during the run goes to stderr.
     sys.stdout.flush()
@@ -442,7 +550,7 @@ def main() -> None:
         if int(os.environ.get("RANK", "0")) == 0:
             emit(run_reference(args))
         return
-    line = run_ours(args)
+    line = run_ours(args) if args.workload == "cfg2" else run_large(args)
     if line is not None:
         emit(line)
 

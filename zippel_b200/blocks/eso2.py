@@ -28,7 +28,7 @@ import torch
 import torch.nn as nn
 
 from .. import _lib
-from ..graph import EdgeGraph
+from ..graph import EdgeChunk, EdgeGraph
 
 _JD_PATH = __import__("pathlib").Path(__file__).resolve().parent.parent / "data" / "jd.npz"
 
@@ -183,7 +183,9 @@ def _edge_budget(plan: Plan, n: int, e: int) -> int:
     per_edge = (lib.zp_workspace_bytes(plan.handle, n, probe, 1)
                 - lib.zp_workspace_bytes(plan.handle, n, 0, 1)) / probe
     free, _total = torch.cuda.mem_get_info(plan.device)
-    return max(1024, int(0.6 * free / max(per_edge, 1.0)))
+    # memory the caching allocator holds but is not using can be re-used for the workspace
+    free += torch.cuda.memory_reserved(plan.device) - torch.cuda.memory_allocated(plan.device)
+    return max(1024, int(0.5 * free / max(per_edge, 1.0)))
 
 
 def _abi_forward(plan, n_rows, e, x, ev, cg, sg, rad, en, src, dst, row_ptr, wstruct, out, ws):
@@ -194,11 +196,13 @@ def _abi_forward(plan, n_rows, e, x, ev, cg, sg, rad, en, src, dst, row_ptr, wst
         ctypes.byref(wstruct), out.data_ptr(), ws.data_ptr(), ws.numel(), st), "zp_eso2_forward")
 
 
-def _abi_backward(plan, n, e, g, x, ev, cg, sg, rad, en, sub: EdgeGraph, wstruct, gx, gev, grad,
-                  gen, gstruct, ws):
+def _abi_backward(plan, n, e, g_ptr: int, x, ev, cg, sg, rad, en, sub: EdgeGraph, wstruct, gx, gev,
+                  grad, gen, gstruct, ws):
+    """``g_ptr``: address of row 0 of grad_node_out.  The kernels read it only at the rows of the
+    edges' destinations, so a caller holding rows n0:n1 alone passes its base minus n0 rows."""
     st = torch.cuda.current_stream().cuda_stream
     _lib.check(_lib.load().zp_eso2_backward(
-        plan.handle, n, e, g.data_ptr(), x.data_ptr(), ev.data_ptr(), cg.data_ptr(),
+        plan.handle, n, e, g_ptr, x.data_ptr(), ev.data_ptr(), cg.data_ptr(),
         sg.data_ptr(), rad.data_ptr(), en.data_ptr(), sub.src.data_ptr(), sub.dst.data_ptr(),
         sub.row_ptr.data_ptr(), sub.perm_src.data_ptr(), sub.row_ptr_src.data_ptr(),
         ctypes.byref(wstruct), gx.data_ptr(), gev.data_ptr(), grad.data_ptr(), gen.data_ptr(),
@@ -226,14 +230,20 @@ class EdgeConvFunction(torch.autograd.Function):
         assert rad.shape == (e, s.R) and ev.shape == (e, 3) and en.shape == (e,)
         assert cg.shape == (e, plan.lmax + 1) and sg.shape == cg.shape
         needs_bwd = any(ctx.needs_input_grad)
-        out = torch.empty(n, s.K, plan.c, dtype=torch.float32, device=x.device)
+        # a graph may carry `node_range = (n0, n1)`: all its edges end in those nodes and only
+        # those rows of node_out are wanted (used by the chunked module path)
+        rng = getattr(graph, "node_range", None)
+        n0, n1 = rng if rng is not None else (0, n)
+        out = torch.empty(n1 - n0, s.K, plan.c, dtype=torch.float32, device=x.device)
         wstruct, keep = _weights_struct(mmax, w10, b10, wms[:mmax], w20, b20, wms[mmax:])
         with torch.cuda.device(x.device):
-            chunks = graph.chunks(_edge_budget(plan, n, e))
+            # a node-range graph is already one piece of a chunked run: never split it again
+            chunks = ([EdgeChunk(0, e, 0, n, graph)] if rng is not None
+                      else graph.chunks(_edge_budget(plan, n, e)))
             if len(chunks) == 1:
                 ws = plan.workspace(n, e, needs_bwd)
-                _abi_forward(plan, n, e, x, ev, cg, sg, rad, en, graph.src, graph.dst,
-                             graph.row_ptr, wstruct, out, ws)
+                _abi_forward(plan, n1 - n0, e, x, ev, cg, sg, rad, en, graph.src, graph.dst,
+                             graph.row_ptr[n0:], wstruct, out, ws)
             else:
                 ws = plan.workspace(n, max(c.n_edges for c in chunks), False)
                 for c in chunks:
@@ -244,16 +254,21 @@ class EdgeConvFunction(torch.autograd.Function):
                 ws = None
         del keep
         if needs_bwd:
-            ctx.plan, ctx.graph, ctx.ws, ctx.chunks = plan, graph, ws, chunks
-            ctx.save_for_backward(*tens)
+            # the workspace goes through save_for_backward like any activation, so that
+            # activation checkpointing can drop it and recompute
+            ctx.plan, ctx.graph, ctx.chunks, ctx.has_ws = plan, graph, chunks, ws is not None
+            ctx.save_for_backward(*tens, *([ws] if ws is not None else []))
             ctx.in_dtypes = [t.dtype for t in ins]
         return out.to(x_node.dtype)
 
     @staticmethod
     @torch.autograd.function.once_differentiable
     def backward(ctx, grad_out):
-        plan, graph, ws, chunks = ctx.plan, ctx.graph, ctx.ws, ctx.chunks
+        plan, graph, chunks = ctx.plan, ctx.graph, ctx.chunks
         tens = ctx.saved_tensors
+        ws = tens[-1] if ctx.has_ws else None
+        if ctx.has_ws:
+            tens = tens[:-1]
         x, ev, cg, sg, rad, en, w10, b10, w20, b20 = tens[:10]
         wms = tens[10:]
         mmax = plan.mmax
@@ -264,10 +279,13 @@ class EdgeConvFunction(torch.autograd.Function):
         wstruct, keep = _weights_struct(mmax, w10, b10, wms[:mmax], w20, b20, wms[mmax:])
         gstruct, keep2 = _weights_struct(mmax, gws[0], gws[1], gws[4:4 + mmax], gws[2], gws[3],
                                          gws[4 + mmax:])
+        rng = getattr(graph, "node_range", None)
+        row_bytes = plan.sizes.K * plan.c * 4
+        g_ptr = g.data_ptr() - (rng[0] * row_bytes if rng is not None else 0)
         with torch.cuda.device(x.device):
             if len(chunks) == 1:
-                _abi_backward(plan, n, e, g, x, ev, cg, sg, rad, en, graph, wstruct, gx, gev, grad,
-                              gen, gstruct, ws)
+                _abi_backward(plan, n, e, g_ptr, x, ev, cg, sg, rad, en, graph, wstruct, gx, gev,
+                              grad, gen, gstruct, ws)
             else:
                 # per chunk: recompute its forward into the shared workspace, then its backward;
                 # node and weight gradients add up over chunks, per-edge gradients are slices
@@ -284,7 +302,7 @@ class EdgeConvFunction(torch.autograd.Function):
                                  en[sl], c.sub.src, c.sub.dst, c.sub.row_ptr[c.n0:], wstruct,
                                  scratch_out, ws)
                     first = i == 0
-                    _abi_backward(plan, n, c.n_edges, g, x, ev[sl], cg[sl], sg[sl], rad[sl], en[sl],
+                    _abi_backward(plan, n, c.n_edges, g_ptr, x, ev[sl], cg[sl], sg[sl], rad[sl], en[sl],
                                   c.sub, wstruct, gx if first else gx_c, gev[sl], grad[sl], gen[sl],
                                   gstruct if first else cstruct, ws)
                     if not first:
@@ -293,7 +311,6 @@ class EdgeConvFunction(torch.autograd.Function):
                             a_.add_(b_)
                 del keep3
         del keep, keep2
-        ctx.ws = None
         grads = [gx, gev, None, None, grad, gen, *gws]
         dts = ctx.in_dtypes
         outs = []
@@ -429,19 +446,16 @@ class ESO2Block(nn.Module):
                         self.precision)
 
     # -- forward --------------------------------------------------------------------------
-    def node_output(self, pos, atomic_numbers, x_node, edge_index, shifts, cos_gamma_k,
-                    sin_gamma_k, graph: EdgeGraph | None = None) -> torch.Tensor:
-        """pos -> node_out [N, K, C] (what the reference scatters at eso2_ref.py:346-349)."""
+    def _edges_to_nodes(self, plan, graph, perm, pos, atomic_numbers, x_node, shifts, cos_gamma_k,
+                        sin_gamma_k) -> torch.Tensor:
+        """Geometry, radial features, envelope and the edge convolution for the edges of `graph`
+        (whose original positions in the caller's arrays are `perm`)."""
         cfg = self.cfg
-        if graph is None:
-            graph = EdgeGraph.build(edge_index, pos.shape[0])
-        perm = graph.perm64
         src, dst = graph.src.long(), graph.dst.long()
         edge_vec = pos[dst] - pos[src] + shifts[perm]
         dist = edge_vec.pow(2).sum(-1).clamp_min(1e-24).sqrt()
         x_edge = torch.cat([self.gaussian_basis(dist), self.elem_emb(atomic_numbers[src]),
                             self.elem_emb(atomic_numbers[dst])], dim=-1)
-        plan = self.plan(pos.device)
         hidden = self.rad_func[:-1](x_edge)
         last = self.rad_func[-1]
         if last.in_features % 8 == 0 and last.out_features % 8 == 0 and hidden.shape[0] > 0:
@@ -449,9 +463,42 @@ class ESO2Block(nn.Module):
         else:
             radial = last(hidden)
         env = self.envelope(dist / cfg.cutoff)
-        return edge_conv(plan, graph, x_node, edge_vec, cos_gamma_k[perm],
-                         sin_gamma_k[perm], radial, env, self.c1_m0, self.c1_m, self.c2_m0,
-                         self.c2_m)
+        return edge_conv(plan, graph, x_node, edge_vec, cos_gamma_k[perm], sin_gamma_k[perm],
+                         radial, env, self.c1_m0, self.c1_m, self.c2_m0, self.c2_m)
+
+    def node_output(self, pos, atomic_numbers, x_node, edge_index, shifts, cos_gamma_k,
+                    sin_gamma_k, graph: EdgeGraph | None = None) -> torch.Tensor:
+        """pos -> node_out [N, K, C] (what the reference scatters at eso2_ref.py:346-349).
+
+        Graphs whose per-edge activations (radial features included) exceed the memory budget
+        are processed as destination-node chunks under activation checkpointing: each chunk's
+        forward is recomputed in the backward, so memory stays bounded by one chunk."""
+        n = pos.shape[0]
+        if graph is None:
+            graph = EdgeGraph.build(edge_index, n)
+        plan = self.plan(pos.device)
+        # radial features and their gradients roughly double the per-edge footprint
+        budget = max(1024, _edge_budget(plan, n, graph.n_edges) // 2)
+        chunks = graph.chunks(budget)
+        perm = graph.perm64
+        if len(chunks) == 1:
+            return self._edges_to_nodes(plan, graph, perm, pos, atomic_numbers, x_node, shifts,
+                                        cos_gamma_k, sin_gamma_k)
+        from torch.utils.checkpoint import checkpoint
+        outs = []
+        for c in chunks:
+            c.sub.node_range = (c.n0, c.n1)
+            sub_perm = perm[c.e0:c.e1]
+
+            def run(pos_, x_, c=c, sub_perm=sub_perm):
+                return self._edges_to_nodes(plan, c.sub, sub_perm, pos_, atomic_numbers, x_, shifts,
+                                            cos_gamma_k, sin_gamma_k)
+
+            if torch.is_grad_enabled():
+                outs.append(checkpoint(run, pos, x_node, use_reentrant=False))
+            else:
+                outs.append(run(pos, x_node))
+        return torch.cat(outs, dim=0)
 
     def forward(self, pos, atomic_numbers, x_node, edge_index, shifts, cos_gamma_k, sin_gamma_k,
                 jd=None, graph: EdgeGraph | None = None) -> torch.Tensor:

@@ -69,9 +69,10 @@ def test_three_planes_k_major(M, N, K, variant):
     assert err < 4e-6
 
 
-@pytest.mark.parametrize("M,N,K", SHAPES)
-def test_two_fp16_planes_k_major(M, N, K):
-    _, err = run_gemm(M, N, K, 2, False, False)
+@pytest.mark.parametrize("M,N,K", SHAPES + [(700, 1152, 1280), (513, 48, 72)])
+@pytest.mark.parametrize("variant", [2, 3])          # 2 = single-CTA kernel, 3 = CTA-pair kernel
+def test_two_fp16_planes_k_major(M, N, K, variant):
+    _, err = run_gemm(M, N, K, 2, False, False, variant=variant)
     assert err < 4e-6
 
 
@@ -81,7 +82,7 @@ def test_one_plane_k_major(M, N, K):
     assert err < 4e-6
 
 
-@pytest.mark.parametrize("planes,variant", [(1, 0), (2, 0), (3, 0), (3, 1)])
+@pytest.mark.parametrize("planes,variant", [(1, 0), (2, 2), (2, 3), (3, 0), (3, 1)])
 @pytest.mark.parametrize("M,N,K", [(128, 128, 64), (256, 192, 200), (1152, 1280, 5000), (24, 40, 333)])
 def test_mn_major_operands(M, N, K, planes, variant):
     err_p, err_f = run_gemm(M, N, K, planes, True, True, variant=variant)
@@ -93,14 +94,20 @@ def test_mixed_majors():
     assert run_gemm(300, 256, 512, 3, False, True, variant=1)[1] < 4e-6
 
 
-@pytest.mark.parametrize("planes", [1, 2, 3])
-def test_long_contraction_chunks_and_splits(planes):
+@pytest.mark.parametrize("planes,variant", [(1, 0), (2, 2), (2, 3), (3, 0)])
+def test_long_contraction_chunks_and_splits(planes, variant):
     """Contraction over 60 000 'edges' as in the weight gradients: chunked TMEM accumulation plus
     a split over CTAs must hold the tolerance that a single running accumulator cannot."""
-    err_p, err_f = run_gemm(640, 512, 60000, planes, True, True, ksplit=4, bias=False)
+    err_p, err_f = run_gemm(640, 512, 60000, planes, True, True, variant=variant, ksplit=4, bias=False)
     assert (err_p if planes == 1 else err_f) < 4e-6
-    err_p, err_f = run_gemm(256, 256, 9000, planes, False, False, ksplit=3, kc=512, bias=True)
+    err_p, err_f = run_gemm(256, 256, 9000, planes, False, False, variant=variant, ksplit=3, kc=512,
+                            bias=True)
     assert (err_p if planes == 1 else err_f) < 4e-6
+
+
+def test_mixed_majors_pair():
+    assert run_gemm(300, 256, 512, 2, True, False, variant=3)[1] < 4e-6
+    assert run_gemm(300, 128, 512, 2, False, True, variant=3)[1] < 4e-6
 
 
 @pytest.mark.parametrize("precision", [0, 1, 2])

@@ -514,15 +514,11 @@ int zp_eso2_backward(const zp_plan *plan, int64_t N, int64_t E, const float *gra
                         wscale(plan, ws, conv, m),
                         nullptr};
       ZP_TIMED(ZP_K_GEMM_DGRAD, zp_launch_gemm_tc(gd, st));
-      // enough K splits to fill the SMs once, never more work items than SMs
-      const int64_t tiles = zp_ceil_div(out, 128) * zp_ceil_div(in, 256);
-      int want = (int)(sms / tiles);
-      if (want < 1) want = 1;
-      if (want > kMaxWgradSplits) want = kMaxWgradSplits;
       ZpGemmTc gw_{out, in, E, P, dYm.base, dYm.ld, dYm.plane_stride, 1,
                    Xm.base, Xm.ld, Xm.plane_stride, 1, nullptr, G, in,
-                   plan->status_dev, 0, want, plan->g_elems, 0, plan->fp16, dYm.scale, Xm.scale,
+                   plan->status_dev, 0, 1, plan->g_elems, 0, plan->fp16, dYm.scale, Xm.scale,
                    nullptr};
+      gw_.ksplit = zp_gemm_tc_pick_splits(gw_, kMaxWgradSplits);
       nsplit = zp_gemm_tc_splits(gw_);
       ZP_TIMED(ZP_K_GEMM_WGRAD, zp_launch_gemm_tc(gw_, st));
     }

@@ -143,6 +143,8 @@ struct ZpGemmTc {
 int zp_launch_gemm_tc(const ZpGemmTc &g, cudaStream_t st);
 // number of partial outputs the launch above will write for this problem (<= g.ksplit)
 int zp_gemm_tc_splits(const ZpGemmTc &g);
+// K split (<= max_splits) that fills the device's CTAs (or CTA pairs) most evenly for this problem
+int zp_gemm_tc_pick_splits(const ZpGemmTc &g, int max_splits);
 // fp32 [rows, cols] (row stride ld_in) -> planes [rows, out.ld], zero padded
 int zp_launch_split_planes(int64_t rows, int64_t cols, const float *in, int64_t ld_in,
                            const ZpPlanes &out, cudaStream_t st);

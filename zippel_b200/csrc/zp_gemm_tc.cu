@@ -38,6 +38,8 @@
 // Shared-memory tiles use the 128-byte (BK = 64) or 64-byte (BK = 32) swizzle that TMA writes
 // and the matrix descriptors name.  Every mbarrier wait is bounded: after ~2 s it records
 // ZP_ERR_DEVICE_TIMEOUT in the status word, raises the CTA's abort flag and the CTA drains.
+#include <cstdlib>
+
 #include <cuda.h>
 #include <cuda_bf16.h>
 
@@ -466,6 +468,332 @@ gemm_tc_kernel(const __grid_constant__ CUtensorMap map_a, const __grid_constant_
   }
 }
 
+// ---- CTA-pair variant ---------------------------------------------------------------------
+//
+// Two CTAs of a cluster (an SM pair) work on one 256 x BN tile with tcgen05.mma.cta_group::2:
+// each CTA stages its own 128 rows of A and HALF of the B tile, and the pair's tensor cores read
+// both halves, so a CTA pulls (128 + BN/2) operand rows per k-block from L2 instead of
+// (128 + BN).  With two fp16 planes and three MMA passes per k-block the single-CTA kernel is
+// limited by that operand feed; the pair is not.
+//
+// Roles per CTA are as above, except that only the even CTA of the pair (the leader) issues MMAs.
+//   full[s]       leader's barrier; the leader's producer announces the bytes of BOTH CTAs and
+//                 both producers' TMA loads complete on it (cta_group::2 loads)
+//   empty[s]      one per CTA; the leader's tcgen05.commit releases the stage in both CTAs
+//   tmem_full     one per CTA, signalled by the same kind of commit
+//   tmem_empty    leader's barrier, 16 arrivals: the eight epilogue warps of each CTA
+// TMEM holds rows 0..127 of the tile in the leader and rows 128..255 in its peer; each CTA's
+// epilogue reads its own half.
+__device__ __forceinline__ uint32_t cluster_ctarank() {
+  uint32_t r;
+  asm volatile("mov.u32 %0, %%cluster_ctarank;" : "=r"(r));
+  return r;
+}
+__device__ __forceinline__ uint32_t map_to_cta(uint32_t smem_addr, uint32_t rank) {
+  uint32_t r;
+  asm volatile("mapa.shared::cluster.u32 %0, %1, %2;" : "=r"(r) : "r"(smem_addr), "r"(rank));
+  return r;
+}
+__device__ __forceinline__ void cluster_sync_all() {
+  __syncwarp();
+  asm volatile("barrier.cluster.arrive.release;\n"
+               "barrier.cluster.wait.acquire;" ::: "memory");
+}
+__device__ __forceinline__ void mbar_arrive_cluster(uint32_t cluster_addr) {
+  asm volatile("mbarrier.arrive.release.cluster.shared::cluster.b64 _, [%0];" ::"r"(cluster_addr)
+               : "memory");
+}
+// load into this CTA's shared memory, completing on a barrier of the pair's leader
+__device__ __forceinline__ void tma_load_3d_pair(void *dst, const CUtensorMap *map,
+                                                 uint32_t bar_cluster_addr, int c0, int c1, int c2) {
+  asm volatile(
+      "cp.async.bulk.tensor.3d.cta_group::2.shared::cluster.global.mbarrier::complete_tx::bytes"
+      " [%0], [%1, {%3, %4, %5}], [%2];"
+      :
+      : "r"(smem_u32(dst)), "l"(reinterpret_cast<uint64_t>(map)), "r"(bar_cluster_addr), "r"(c0),
+        "r"(c1), "r"(c2)
+      : "memory");
+}
+// arrive on the barrier at this offset in both CTAs of the pair once the MMAs issued so far finish
+__device__ __forceinline__ void tcgen05_commit_pair(uint64_t *bar) {
+  const uint16_t both = 3;
+  asm volatile(
+      "tcgen05.commit.cta_group::2.mbarrier::arrive::one.shared::cluster.multicast::cluster.b64"
+      " [%0], %1;" ::"r"(smem_u32(bar)),
+      "h"(both)
+      : "memory");
+}
+__device__ __forceinline__ void umma_pair(uint32_t tmem_d, uint64_t desc_a, uint64_t desc_b,
+                                          uint32_t idesc, uint32_t accumulate) {
+  asm volatile(
+      "{\n"
+      ".reg .pred p;\n"
+      "setp.ne.b32 p, %4, 0;\n"
+      "tcgen05.mma.cta_group::2.kind::f16 [%0], %1, %2, %3, p;\n"
+      "}\n"
+      :
+      : "r"(tmem_d), "l"(desc_a), "l"(desc_b), "r"(idesc), "r"(accumulate)
+      : "memory");
+}
+
+constexpr int BM2 = 256;               // rows of a pair's tile
+
+template <int P, int BK, int STAGES>
+struct SmemLayoutPair {
+  static constexpr int kATile = BM * BK * 2;          // this CTA's 128 rows
+  static constexpr int kBTile = 128 * BK * 2;         // this CTA's half of a <= 256-wide B tile
+  static constexpr int kStage = P * (kATile + kBTile);
+  static constexpr int kTiles = STAGES * kStage;
+  static constexpr int kBars = 8 * (2 * STAGES + 4);
+  static constexpr int kTotal = kTiles + kBars + 16 + 1024;
+};
+
+__device__ __forceinline__ Work decode_work_pair(const GemmParams &p, int w) {
+  Work x;
+  x.split = w % p.ksplit;
+  const int tile = w / p.ksplit;
+  x.m0 = (tile / p.num_n) * BM2;
+  x.n0 = (tile % p.num_n) * p.BN;
+  x.kb0 = x.split * p.kb_per_split;
+  x.kb1 = min(p.num_k, x.kb0 + p.kb_per_split);
+  return x;
+}
+
+template <int P, int BK, int STAGES>
+__global__ void __launch_bounds__(kThreads, 1)
+gemm_tc_pair_kernel(const __grid_constant__ CUtensorMap map_a,
+                    const __grid_constant__ CUtensorMap map_b, const GemmParams p) {
+  using L = SmemLayoutPair<P, BK, STAGES>;
+  extern __shared__ uint8_t smem_raw[];
+  // the dynamic shared window starts at the same offset in both CTAs, so does everything below
+  uint8_t *smem = reinterpret_cast<uint8_t *>((reinterpret_cast<uintptr_t>(smem_raw) + 1023) &
+                                              ~(uintptr_t)1023);
+  uint64_t *full = reinterpret_cast<uint64_t *>(smem + L::kTiles);
+  uint64_t *empty = full + STAGES;
+  uint64_t *tmem_full = empty + STAGES;
+  uint64_t *tmem_empty = tmem_full + 2;
+  uint32_t *tmem_slot = reinterpret_cast<uint32_t *>(tmem_empty + 2);
+  volatile int *abort_flag = reinterpret_cast<volatile int *>(tmem_slot + 1);
+
+  const int warp = threadIdx.x / 32, lane = threadIdx.x % 32;
+  const uint32_t rank = cluster_ctarank();          // 0 = leader
+  const int pair = blockIdx.x >> 1, num_pairs = gridDim.x >> 1;
+  const int num_work = p.num_m * p.num_n * p.ksplit;
+  const int half_n = p.BN >> 1;
+
+  if (threadIdx.x == 0) {
+    for (int s = 0; s < STAGES; ++s) { mbar_init(&full[s], 1); mbar_init(&empty[s], 1); }
+    mbar_init(&tmem_full[0], 1);
+    mbar_init(&tmem_empty[0], 16);
+    *abort_flag = 0;
+    asm volatile("fence.mbarrier_init.release.cluster;" ::: "memory");
+    asm volatile("fence.proxy.async.shared::cta;" ::: "memory");
+  }
+  __syncthreads();
+  cluster_sync_all();                   // both CTAs' barriers exist before anything signals them
+  if (warp == 1) {
+    asm volatile("tcgen05.alloc.cta_group::2.sync.aligned.shared::cta.b32 [%0], %1;" ::"r"(
+                     smem_u32(tmem_slot)),
+                 "r"(512u)
+                 : "memory");
+    asm volatile("tcgen05.relinquish_alloc_permit.cta_group::2.sync.aligned;" ::: "memory");
+  }
+  tcgen05_fence_before();
+  __syncthreads();
+  cluster_sync_all();                   // both allocations exist before the leader's first MMA
+  tcgen05_fence_after();
+  const uint32_t tmem_base = *tmem_slot;
+
+  const uint32_t a_bytes = BM * BK * 2;
+  const uint32_t b_bytes = (uint32_t)half_n * BK * 2;
+
+  if (warp == 0) {
+    // ---------------------------------------------------------------- TMA producer (both CTAs)
+    if (elect_one()) {
+      uint32_t it = 0;
+      bool ok = true;
+      for (int w = pair; w < num_work && ok; w += num_pairs) {
+        const Work x = decode_work_pair(p, w);
+        const int m0 = x.m0 + (int)rank * BM, n0 = x.n0 + (int)rank * half_n;
+        for (int kb = x.kb0; kb < x.kb1 && ok; ++kb, ++it) {
+          const int s = it % STAGES;
+          ok = mbar_wait(&empty[s], ((it / STAGES) & 1) ^ 1, abort_flag, p.status);
+          if (!ok) break;
+          uint8_t *st = smem + (size_t)s * L::kStage;
+          if (rank == 0) mbar_expect_tx(&full[s], 2 * P * (a_bytes + b_bytes));
+          const uint32_t bar = map_to_cta(smem_u32(&full[s]), 0);
+          const int k0 = kb * BK;
+#pragma unroll
+          for (int pl = 0; pl < P; ++pl) {
+            uint8_t *ta = st + pl * L::kATile, *tb = st + P * L::kATile + pl * L::kBTile;
+            if (!p.a_mn) {
+              tma_load_3d_pair(ta, &map_a, bar, k0, m0, pl);
+            } else {
+              tma_load_3d_pair(ta, &map_a, bar, m0, k0, pl);
+              tma_load_3d_pair(ta + BK * 128, &map_a, bar, m0 + 64, k0, pl);
+            }
+            if (!p.b_mn) {
+              tma_load_3d_pair(tb, &map_b, bar, k0, n0, pl);
+            } else {
+              for (int nb = 0; nb < half_n; nb += 64)
+                tma_load_3d_pair(tb + (nb / 64) * BK * 128, &map_b, bar, n0 + nb, k0, pl);
+            }
+          }
+        }
+      }
+      // the leader's last stage releases must have landed here before this CTA may exit
+      for (int j = 0; j < STAGES && ok; ++j, ++it)
+        ok = mbar_wait(&empty[it % STAGES], ((it / STAGES) & 1) ^ 1, abort_flag, p.status);
+    }
+  } else if (warp == 1) {
+    // ---------------------------------------------------------------- MMA issuer (leader only)
+    if (rank == 0 && elect_one()) {
+      const uint32_t fmt = p.fp16 ? 0u : 1u;
+      const uint32_t idesc = (1u << 4) | (fmt << 7) | (fmt << 10) | ((uint32_t)(p.a_mn ? 1 : 0) << 15) |
+                             ((uint32_t)(p.b_mn ? 1 : 0) << 16) | ((uint32_t)(p.BN >> 3) << 17) |
+                             ((uint32_t)(BM2 >> 4) << 24);
+      constexpr uint32_t kLayout = BK == 64 ? 2u : 4u;
+      uint32_t it = 0, unit = 0;
+      bool ok = true;
+      for (int w = pair; w < num_work && ok; w += num_pairs) {
+        const Work x = decode_work_pair(p, w);
+        for (int c0 = x.kb0; c0 < x.kb1 && ok; c0 += p.kc, ++unit) {
+          const int c1 = min(x.kb1, c0 + p.kc);
+          ok = mbar_wait(&tmem_empty[0], (unit & 1) ^ 1, abort_flag, p.status);
+          if (!ok) break;
+          tcgen05_fence_after();
+          const uint32_t d_main = tmem_base;
+          const uint32_t d_small = tmem_base + kTmemBuf;
+          for (int kb = c0; kb < c1 && ok; ++kb, ++it) {
+            const int s = it % STAGES;
+            ok = mbar_wait(&full[s], (it / STAGES) & 1, abort_flag, p.status);
+            if (!ok) break;
+            tcgen05_fence_after();
+            const uint32_t sa = smem_u32(smem + (size_t)s * L::kStage);
+            const uint32_t sb = sa + P * L::kATile;
+#pragma unroll
+            for (int ks = 0; ks < BK / 16; ++ks) {
+#pragma unroll
+              for (int q = 0; q < Pairs<P>::n; ++q) {
+                const uint32_t ta = sa + Pairs<P>::a(q) * L::kATile;
+                const uint32_t tb = sb + Pairs<P>::b(q) * L::kBTile;
+                const uint64_t da = p.a_mn ? make_desc(ta + ks * 2048, BK * 128, 1024, 2u)
+                                           : make_desc(ta + ks * 32, 16, 8 * BK * 2, kLayout);
+                const uint64_t db = p.b_mn ? make_desc(tb + ks * 2048, BK * 128, 1024, 2u)
+                                           : make_desc(tb + ks * 32, 16, 8 * BK * 2, kLayout);
+                const bool first_step = kb == c0 && ks == 0;
+                if (q == 0 || P == 1) umma_pair(d_main, da, db, idesc, first_step ? 0u : 1u);
+                else umma_pair(d_small, da, db, idesc, (first_step && q == 1) ? 0u : 1u);
+              }
+            }
+            tcgen05_commit_pair(&empty[s]);
+          }
+          if (ok) tcgen05_commit_pair(&tmem_full[0]);
+        }
+      }
+    }
+  } else {
+    // ---------------------------------------------------------------- epilogue (both CTAs)
+    const int q = warp & 3;
+    const int half = (warp - 2) >> 2;
+    uint32_t unit = 0;
+    bool ok = true;
+    const float out_scale = (p.scale_a ? *p.scale_a : 1.f) * (p.scale_b ? *p.scale_b : 1.f);
+    float seen_max = 0.f;
+    const int col_lo = half * 128, col_hi = min(p.BN, col_lo + 128);
+    const uint32_t release_bar = map_to_cta(smem_u32(&tmem_empty[0]), 0);
+    for (int w = pair; w < num_work && ok; w += num_pairs) {
+      const Work x = decode_work_pair(p, w);
+      const int row = x.m0 + (int)rank * BM + q * 32 + lane;
+      float *crow = p.C + (size_t)x.split * p.split_stride + (size_t)row * p.ldc;
+      const float *bias = x.split == 0 ? p.bias : nullptr;
+      for (int c0 = x.kb0; c0 < x.kb1 && ok; c0 += p.kc, ++unit) {
+        const bool first = c0 == x.kb0;
+        ok = mbar_wait(&tmem_full[0], unit & 1, abort_flag, p.status);
+        ok = __all_sync(0xffffffffu, ok);
+        if (!ok) break;
+        tcgen05_fence_after();
+        const uint32_t t_row = tmem_base + ((uint32_t)(q * 32) << 16);
+        float v[4][32];
+#pragma unroll
+        for (int b = 0; b < 4; ++b) {
+          const int cc = col_lo + 32 * b;
+          if (cc < col_hi) {
+            uint32_t r[32];
+            tmem_ld32(t_row + cc, r);
+            if (P != 1) {
+              uint32_t r2[32];
+              tmem_ld32(t_row + kTmemBuf + cc, r2);
+              tmem_ld_wait();
+#pragma unroll
+              for (int j = 0; j < 32; ++j)
+                v[b][j] = (__uint_as_float(r[j]) + __uint_as_float(r2[j])) * out_scale;
+            } else {
+              tmem_ld_wait();
+#pragma unroll
+              for (int j = 0; j < 32; ++j) v[b][j] = __uint_as_float(r[j]) * out_scale;
+            }
+          }
+        }
+        tcgen05_fence_before();
+        __syncwarp();
+        if (lane == 0) mbar_arrive_cluster(release_bar);
+
+        if (row < p.M) {
+#pragma unroll
+          for (int b = 0; b < 4; ++b) {
+            const int cc = col_lo + 32 * b;
+            if (cc >= col_hi) continue;
+#pragma unroll
+            for (int j = 0; j < 32; j += 4) {
+              const int n = x.n0 + cc + j;
+              if (cc + j < p.BN && n + 3 < p.N) {
+                float4 o = make_float4(v[b][j], v[b][j + 1], v[b][j + 2], v[b][j + 3]);
+                if (first) {
+                  if (bias) {
+                    const float4 bv = *reinterpret_cast<const float4 *>(bias + n);
+                    o.x += bv.x; o.y += bv.y; o.z += bv.z; o.w += bv.w;
+                  }
+                } else {
+                  const float4 old = *reinterpret_cast<const float4 *>(crow + n);
+                  o.x += old.x; o.y += old.y; o.z += old.z; o.w += old.w;
+                }
+                *reinterpret_cast<float4 *>(crow + n) = o;
+                seen_max = fmaxf(seen_max, fmaxf(fmaxf(fabsf(o.x), fabsf(o.y)),
+                                                 fmaxf(fabsf(o.z), fabsf(o.w))));
+              } else if (cc + j < p.BN) {
+#pragma unroll
+                for (int u = 0; u < 4; ++u)
+                  if (n + u < p.N) {
+                    const float base = first ? (bias ? bias[n + u] : 0.f) : crow[n + u];
+                    const float o = v[b][j + u] + base;
+                    crow[n + u] = o;
+                    seen_max = fmaxf(seen_max, fabsf(o));
+                  }
+              }
+            }
+          }
+        }
+      }
+    }
+    if (p.absmax_out) {
+#pragma unroll
+      for (int o = 16; o > 0; o >>= 1) seen_max = fmaxf(seen_max, __shfl_xor_sync(0xffffffffu, seen_max, o));
+      if (lane == 0 && seen_max > 0.f) zp_atomic_absmax(p.absmax_out, seen_max);
+    }
+  }
+
+  tcgen05_fence_before();
+  __syncthreads();
+  cluster_sync_all();                   // neither CTA frees TMEM or exits while its peer still works
+  if (warp == 1) {
+    __syncwarp();
+    tcgen05_fence_after();
+    asm volatile("tcgen05.dealloc.cta_group::2.sync.aligned.b32 %0, %1;" ::"r"(tmem_base), "r"(512u)
+                 : "memory");
+  }
+}
+
 // ---- host side ---------------------------------------------------------------------------
 
 typedef CUresult (*EncodeTiledFn)(CUtensorMap *, CUtensorMapDataType, cuuint32_t, void *,
@@ -506,14 +834,60 @@ int make_map(CUtensorMap *map, const void *base, uint64_t inner, uint64_t outer,
   return ZP_OK;
 }
 
-int pick_bn(int64_t N, int cap) {
-  const int64_t tiles = zp_ceil_div(N, cap);
-  int64_t bn = zp_ceil_div(zp_ceil_div(N, tiles), 16) * 16;
-  if (bn < 16) bn = 16;
-  return (int)bn;
+// Tile width: the multiple of `step` in [cap/2, cap] that wastes the fewest padded columns
+// (ties: the widest); problems narrower than cap/2 get one tile.
+int pick_bn(int64_t N, int cap, int step = 16) {
+  if (N <= cap / 2) return (int)(zp_ceil_div(N, step) * step);
+  int best = cap;
+  int64_t best_pad = zp_ceil_div(N, cap) * cap;
+  for (int bn = cap - step; bn >= cap / 2; bn -= step) {
+    const int64_t pad = zp_ceil_div(N, bn) * bn;
+    if (pad < best_pad) { best_pad = pad; best = bn; }
+  }
+  return best;
+}
+
+// The CTA-pair kernel serves the two-plane (fp16) format unless the caller forces a kernel:
+// variant 2 = single-CTA kernel, variant 3 = pair kernel.
+bool pair_enabled() {
+  static int on = -1;
+  if (on < 0) {
+    const char *e = getenv("ZP_GEMM_PAIR");
+    on = (e && e[0] == '0') ? 0 : 1;
+  }
+  return on == 1;
+}
+int device_sms() {
+  int dev = 0, sms = 148;
+  cudaGetDevice(&dev);
+  cudaDeviceGetAttribute(&sms, cudaDevAttrMultiProcessorCount, dev);
+  return sms;
+}
+// Expected utilisation of the tensor pipes for one kernel choice and K split: padded-tile waste
+// times the evenness of the last wave, with the pair's lighter operand feed counted as a gain.
+double launch_score(const ZpGemmTc &g, bool pair, int splits) {
+  const int64_t units = pair ? device_sms() / 2 : device_sms();
+  const int tm = pair ? 256 : BM;
+  const int bn = pair ? pick_bn(g.N, 256, g.b_mn ? 128 : 16) : pick_bn(g.N, 256, g.b_mn ? 64 : 16);
+  const int64_t tiles_m = zp_ceil_div(g.M, tm), tiles_n = zp_ceil_div(g.N, bn);
+  const double pad = (double)(g.M * g.N) / (double)(tiles_m * tm * tiles_n * bn);
+  const int64_t items = tiles_m * tiles_n * splits;
+  const double wave = (double)items / (double)(zp_ceil_div(items, units) * units);
+  return pad * wave * (pair ? 1.12 : 1.0) - 0.004 * splits;
+}
+bool use_pair(const ZpGemmTc &g) {
+  if (g.planes != 2) return false;
+  if (g.variant == 2) return false;
+  if (g.variant == 3) return true;
+  if (!pair_enabled()) return false;
+  // short contractions leave the pair's cross-SM hand-offs exposed on every tile
+  if (g.K < 512) return false;
+  int s = g.ksplit < 1 ? 1 : g.ksplit;
+  return launch_score(g, true, s) >= launch_score(g, false, s);
 }
 
 int block_k(const ZpGemmTc &g) {
+  if (use_pair(g)) return 64;
   return ((g.planes == 3 && g.variant != 1) || g.planes == 2) ? 32 : 64;
 }
 
@@ -537,8 +911,7 @@ int launch(const ZpGemmTc &g, cudaStream_t st) {
   }
   GemmParams p;
   p.M = (int)g.M; p.N = (int)g.N; p.K = (int)g.K;
-  p.BN = pick_bn(g.N, BN_CAP);
-  if (g.b_mn) p.BN = (p.BN + 63) / 64 * 64;       // MN-major B tiles come in 64-wide blocks
+  p.BN = pick_bn(g.N, BN_CAP, g.b_mn ? 64 : 16);  // MN-major B tiles come in 64-wide blocks
   p.num_m = (int)zp_ceil_div(g.M, BM);
   p.num_n = (int)zp_ceil_div(g.N, p.BN);
   split_plan(g, BK, &p.ksplit, &p.kb_per_split, &p.num_k);
@@ -566,6 +939,55 @@ int launch(const ZpGemmTc &g, cudaStream_t st) {
   return ZP_OK;
 }
 
+template <int P, int BK, int STAGES>
+int launch_pair(const ZpGemmTc &g, cudaStream_t st) {
+  using L = SmemLayoutPair<P, BK, STAGES>;
+  static_assert(L::kTotal <= 232448, "shared memory budget of one CTA");
+  static int max_pairs = -1;            // co-resident CTA pairs of this kernel on the device
+  auto kernel = gemm_tc_pair_kernel<P, BK, STAGES>;
+  cudaLaunchAttribute attr[1];
+  attr[0].id = cudaLaunchAttributeClusterDimension;
+  attr[0].val.clusterDim.x = 2; attr[0].val.clusterDim.y = 1; attr[0].val.clusterDim.z = 1;
+  cudaLaunchConfig_t cfg = {};
+  cfg.blockDim = dim3(kThreads); cfg.dynamicSmemBytes = L::kTotal; cfg.stream = st;
+  cfg.attrs = attr; cfg.numAttrs = 1;
+  if (max_pairs < 0) {
+    ZP_CUDA(cudaFuncSetAttribute(kernel, cudaFuncAttributeMaxDynamicSharedMemorySize, L::kTotal));
+    int dev = 0, sms = 148, n = 0;
+    cudaGetDevice(&dev);
+    cudaDeviceGetAttribute(&sms, cudaDevAttrMultiProcessorCount, dev);
+    cfg.gridDim = dim3((unsigned)(sms / 2 * 2));
+    ZP_CUDA(cudaOccupancyMaxActiveClusters(&n, kernel, &cfg));
+    max_pairs = n < sms / 2 ? n : sms / 2;
+  }
+  if (max_pairs < 1) return ZP_ERR_UNSUPPORTED;
+  GemmParams p;
+  p.M = (int)g.M; p.N = (int)g.N; p.K = (int)g.K;
+  p.BN = pick_bn(g.N, 256, g.b_mn ? 128 : 16);    // each CTA's half of an MN-major tile: 64-wide blocks
+  p.num_m = (int)zp_ceil_div(g.M, BM2);
+  p.num_n = (int)zp_ceil_div(g.N, p.BN);
+  split_plan(g, BK, &p.ksplit, &p.kb_per_split, &p.num_k);
+  const int kc_elems = g.kc_elems > 0 ? g.kc_elems : 2048;
+  p.kc = kc_elems / BK < 1 ? 1 : kc_elems / BK;
+  p.a_mn = g.a_mn; p.b_mn = g.b_mn;
+  p.fp16 = g.fp16; p.scale_a = g.scale_a; p.scale_b = g.scale_b; p.absmax_out = g.absmax_out;
+  p.bias = g.bias; p.C = g.C; p.ldc = g.ldc; p.split_stride = g.split_stride; p.status = g.status;
+  const CUtensorMapSwizzle kswz = BK == 64 ? CU_TENSOR_MAP_SWIZZLE_128B : CU_TENSOR_MAP_SWIZZLE_64B;
+  CUtensorMap ma, mb;
+  int rc;
+  if (!g.a_mn) rc = make_map(&ma, g.A, g.K, g.M, P, g.lda, g.a_plane, BK, BM, kswz, g.fp16);
+  else rc = make_map(&ma, g.A, g.M, g.K, P, g.lda, g.a_plane, 64, BK, CU_TENSOR_MAP_SWIZZLE_128B, g.fp16);
+  if (rc) return rc;
+  if (!g.b_mn) rc = make_map(&mb, g.B, g.K, g.N, P, g.ldb, g.b_plane, BK, p.BN / 2, kswz, g.fp16);
+  else rc = make_map(&mb, g.B, g.N, g.K, P, g.ldb, g.b_plane, 64, BK, CU_TENSOR_MAP_SWIZZLE_128B, g.fp16);
+  if (rc) return rc;
+  const int work = p.num_m * p.num_n * p.ksplit;
+  cfg.gridDim = dim3((unsigned)(2 * (work < max_pairs ? work : max_pairs)));
+  ZP_CUDA(cudaLaunchKernelEx(&cfg, kernel, ma, mb, p));
+  ZP_LAUNCH_CHECK("gemm_tc_pair_kernel");
+  return ZP_OK;
+}
+
 }  // namespace
 
 int zp_gemm_tc_splits(const ZpGemmTc &g) {
@@ -573,6 +995,18 @@ int zp_gemm_tc_splits(const ZpGemmTc &g) {
   int ksplit, kbs, num_k;
   split_plan(g, block_k(g), &ksplit, &kbs, &num_k);
   return ksplit;
+}
+
+int zp_gemm_tc_pick_splits(const ZpGemmTc &g, int max_splits) {
+  ZpGemmTc t = g;
+  int best = 1;
+  double best_score = -1.0;
+  for (int s = 1; s <= max_splits; ++s) {
+    t.ksplit = s;
+    const double score = launch_score(t, use_pair(t), s);
+    if (score > best_score) { best_score = score; best = s; }
+  }
+  return best;
 }
 
 int zp_launch_gemm_tc(const ZpGemmTc &g, cudaStream_t st) {
@@ -585,6 +1019,7 @@ int zp_launch_gemm_tc(const ZpGemmTc &g, cudaStream_t st) {
   if ((reinterpret_cast<uintptr_t>(g.A) | reinterpret_cast<uintptr_t>(g.B) |
        reinterpret_cast<uintptr_t>(g.C)) & 15)
     return ZP_ERR_INVALID_ARG;
+  if (use_pair(g)) return launch_pair<2, 64, 3>(g, st);
   if (g.a_mn || g.b_mn) {
     // MN-major tiles are [BK][64] blocks under the 128-byte swizzle
     if (g.planes == 3)

@@ -126,7 +126,8 @@ int zp_linear_backward(const zp_plan *plan, int64_t M, int64_t K, int64_t N, con
   // dw[N, K] = dy^T x: contraction over the M rows, both operands MN-major, split over CTAs
   ZpGemmTc g{N, K, M, plan->planes, lw.dy.base, lw.dy.ld, lw.dy.plane_stride, 1,
              lw.x.base, lw.x.ld, lw.x.plane_stride, 1, nullptr, lw.partials, K, plan->status_dev,
-             0, kLinSplits, N * K, 0, plan->fp16, lw.dy.scale, lw.x.scale, nullptr};
+             0, 1, N * K, 0, plan->fp16, lw.dy.scale, lw.x.scale, nullptr};
+  g.ksplit = zp_gemm_tc_pick_splits(g, kLinSplits);
   const int splits = zp_gemm_tc_splits(g);
   if ((rc = zp_launch_gemm_tc(g, st))) return rc;
   sum_partials_kernel<<<(unsigned)zp_ceil_div(N * K, 256), 256, 0, st>>>(N * K, splits, lw.partials, dw);

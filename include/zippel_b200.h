@@ -216,6 +216,20 @@ int zp_linear_backward(const zp_plan *plan, int64_t M, int64_t K, int64_t N, con
                        const float *w, const float *dy, float *dx, float *dw, float *db,
                        void *work, size_t work_bytes, void *stream);
 
+/* LayerNorm followed by SiLU over rows of `width` floats (a multiple of 4, at most 1024), and the
+ * VJP: the hidden layers of the radial MLP (nn.LayerNorm + nn.SiLU, rad_func[1..2] and
+ * rad_func[4..5], blocks/eso2_ref.py:170-180) in one pass each way.  The forward saves mean[rows]
+ * and rstd[rows] for the backward.  dgamma/dbeta are summed in a fixed order (bit-reproducible).
+ * `work`: zp_layernorm_work_bytes(width) bytes of device scratch, caller-owned.                  */
+size_t zp_layernorm_work_bytes(int width);
+int zp_layernorm_silu_forward(int64_t rows, int width, const float *x, const float *gamma,
+                              const float *beta, float eps, float *y, float *mean, float *rstd,
+                              void *stream);
+int zp_layernorm_silu_backward(int64_t rows, int width, const float *x, const float *gamma,
+                               const float *beta, const float *mean, const float *rstd,
+                               const float *dy, float *dx, float *dgamma, float *dbeta,
+                               void *work, size_t work_bytes, void *stream);
+
 /* Reads (synchronously) and clears the plan's device status word: ZP_OK, or
  * ZP_ERR_DEVICE_TIMEOUT if a bounded device-side wait gave up since the last read.          */
 int zp_plan_device_status(zp_plan *plan, int *status_out);

@@ -366,6 +366,51 @@ class TensorCoreLinear(torch.autograd.Function):
         return None, dx.to(dt[0]), dw.to(dt[1]), db.to(dt[2])
 
 
+class LayerNormSiLU(torch.autograd.Function):
+    """silu(layer_norm(x) * gamma + beta) in one pass each way (``zp_layernorm_silu_forward`` /
+    ``_backward``): nn.LayerNorm + nn.SiLU of the radial MLP's hidden layers (reference
+    blocks/eso2_ref.py:170-180).  fp32, first order only."""
+
+    @staticmethod
+    def forward(ctx, x, gamma, beta, eps: float):
+        lib = _lib.load()
+        if not x.is_cuda:
+            raise RuntimeError("LayerNormSiLU needs CUDA tensors: there is no CPU path")
+        xf, gf, bf = _f32(x), _f32(gamma), _f32(beta)
+        rows, width = xf.shape
+        y = torch.empty_like(xf)
+        stats = torch.empty(2, rows, dtype=torch.float32, device=xf.device)
+        with torch.cuda.device(xf.device):
+            st = torch.cuda.current_stream().cuda_stream
+            _lib.check(lib.zp_layernorm_silu_forward(rows, width, xf.data_ptr(), gf.data_ptr(),
+                                                     bf.data_ptr(), float(eps), y.data_ptr(),
+                                                     stats[0].data_ptr(), stats[1].data_ptr(), st),
+                       "zp_layernorm_silu_forward")
+        ctx.dtypes = (x.dtype, gamma.dtype, beta.dtype)
+        ctx.save_for_backward(xf, gf, bf, stats)
+        return y.to(x.dtype)
+
+    @staticmethod
+    @torch.autograd.function.once_differentiable
+    def backward(ctx, grad_y):
+        lib = _lib.load()
+        xf, gf, bf, stats = ctx.saved_tensors
+        rows, width = xf.shape
+        dy = _f32(grad_y)
+        dx = torch.empty_like(xf)
+        dgb = torch.empty(2, width, dtype=torch.float32, device=xf.device)
+        nbytes = lib.zp_layernorm_work_bytes(width)
+        work = torch.empty(max(nbytes, 1), dtype=torch.uint8, device=xf.device)
+        with torch.cuda.device(xf.device):
+            st = torch.cuda.current_stream().cuda_stream
+            _lib.check(lib.zp_layernorm_silu_backward(
+                rows, width, xf.data_ptr(), gf.data_ptr(), bf.data_ptr(), stats[0].data_ptr(),
+                stats[1].data_ptr(), dy.data_ptr(), dx.data_ptr(), dgb[0].data_ptr(),
+                dgb[1].data_ptr(), work.data_ptr(), nbytes, st), "zp_layernorm_silu_backward")
+        dt = ctx.dtypes
+        return dx.to(dt[0]), dgb[0].to(dt[1]), dgb[1].to(dt[2]), None
+
+
 def edge_conv(plan: Plan, graph: EdgeGraph, x_node, edge_vec, cos_g, sin_g, radial, env,
               c1_m0: nn.Linear, c1_m, c2_m0: nn.Linear, c2_m) -> torch.Tensor:
     return EdgeConvFunction.apply(plan, graph, x_node, edge_vec, cos_g, sin_g, radial, env,
@@ -445,6 +490,31 @@ class ESO2Block(nn.Module):
         return Plan.get(c.lmax, c.mmax, c.sphere_channels, c.hidden_channels, device,
                         self.precision)
 
+    def radial_mlp(self, plan: Plan, x_edge: torch.Tensor) -> torch.Tensor:
+        """rad_func (Linear, LayerNorm, SiLU, ..., Linear; reference eso2_ref.py:164-182) with the
+        library's kernels: every Linear whose sizes are multiples of 8 runs on the contraction
+        engine in the plan's operand format, every LayerNorm + SiLU pair is one fused pass."""
+        h = x_edge
+        mods = list(self.rad_func)
+        i = 0
+        while i < len(mods):
+            m = mods[i]
+            if isinstance(m, nn.Linear):
+                if m.in_features % 8 == 0 and m.out_features % 8 == 0 and h.shape[0] > 0:
+                    h = TensorCoreLinear.apply(plan, h, m.weight, m.bias)
+                else:
+                    h = m(h)
+                i += 1
+            elif (isinstance(m, nn.LayerNorm) and i + 1 < len(mods) and isinstance(mods[i + 1], nn.SiLU)
+                  and m.normalized_shape[0] % 4 == 0 and m.normalized_shape[0] <= 1024
+                  and h.shape[0] > 0):
+                h = LayerNormSiLU.apply(h, m.weight, m.bias, m.eps)
+                i += 2
+            else:
+                h = m(h)
+                i += 1
+        return h
+
     # -- forward --------------------------------------------------------------------------
     def _edges_to_nodes(self, plan, graph, perm, pos, atomic_numbers, x_node, shifts, cos_gamma_k,
                         sin_gamma_k) -> torch.Tensor:
@@ -456,12 +526,7 @@ class ESO2Block(nn.Module):
         dist = edge_vec.pow(2).sum(-1).clamp_min(1e-24).sqrt()
         x_edge = torch.cat([self.gaussian_basis(dist), self.elem_emb(atomic_numbers[src]),
                             self.elem_emb(atomic_numbers[dst])], dim=-1)
-        hidden = self.rad_func[:-1](x_edge)
-        last = self.rad_func[-1]
-        if last.in_features % 8 == 0 and last.out_features % 8 == 0 and hidden.shape[0] > 0:
-            radial = TensorCoreLinear.apply(plan, hidden, last.weight, last.bias)
-        else:
-            radial = last(hidden)
+        radial = self.radial_mlp(plan, x_edge)
         env = self.envelope(dist / cfg.cutoff)
         return edge_conv(plan, graph, x_node, edge_vec, cos_gamma_k[perm], sin_gamma_k[perm],
                          radial, env, self.c1_m0, self.c1_m, self.c2_m0, self.c2_m)

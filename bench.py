@@ -375,16 +375,38 @@ def run_ours(args) -> dict | None:
                     "tensor-core passes per product, so mma_tflops = mma_passes x achieved is "
                     "what the tensor pipe executes"}
 
+    # whole-step bounds: streaming bytes (gathered node rows counted per edge, no reuse) against
+    # the copy bandwidth, algorithmic FLOPs against the tensor peak; the larger time binds
+    K = (CFG["lmax"] + 1) ** 2
+    n_weights = sum(p.numel() for p in so2_params)
+    bytes_fwd = (e * (2 * K * CFG["sphere_channels"] * 4 + 12 + 8 * (CFG["lmax"] + 1) + 8)
+                 + n * K * CFG["sphere_channels"] * 4 + n_weights * 4)
+    bytes_step = 2 * bytes_fwd + e * 12
+    t_hbm = bytes_step / (pk["hbm_gbs"] * 1e9) * 1e3
+    t_tensor = flops_step / (peak * 1e12) * 1e3
+    roof["whole_step"] = {
+        "streaming_bytes": bytes_step, "t_hbm_ms": t_hbm, "algorithmic_flops": flops_step,
+        "t_tensor_ms": t_tensor, "binds": "tensor" if t_tensor >= t_hbm else "hbm",
+        "frac_of_bound": max(t_hbm, t_tensor) / ms_per_step,
+        "hbm_frac_streaming": bytes_step / (ms_per_step * 1e-3) / (pk["hbm_gbs"] * 1e9),
+        "note": "t_tensor counts each product once at the bf16 peak; the fp32 operand format "
+                "needs mma_passes passes, so frac_of_bound <= 1/mma_passes for the GEMM part"}
+    q = statistics.quantiles(step_ms, n=4) if len(step_ms) >= 4 else [min(step_ms)] * 3
+
     line = None
     if rank == 0:
         line = {
             "metric": METRIC, "value": total_edges / (ms_per_step * 1e-3), "unit": "edges/s",
+            "ms_per_step_median": q[1], "ms_per_step_iqr": q[2] - q[0],
             "n_gpus": world, "steps": args.steps, "warmup": max(args.warmup, 3),
             "ms_per_step": ms_per_step, "higher_is_better": True, "scaling": "weak",
             "vs_baseline": None, "dtype": "bf16" if args.precision == "bf16" else "f32",
             "precision": args.precision, "data": "synthetic",
-            "config": workload_config(batch, "256 MiB L2 flush between steps, outside the "
-                                             "per-step events; per-step activations are >5 GB"),
+            "config": {**workload_config(batch, "256 MiB L2 flush between steps, outside the "
+                                                "per-step events; per-step activations are >5 GB"),
+                       "radial": "value: radial features and envelope are precomputed inputs of "
+                                 "the C-ABI step; e2e: computed inside the step (radial MLP on "
+                                 "the library's kernels)"},
             "fwd_only": {"value": e / (fwd_ms * 1e-3), "unit": "edges/s (this rank)",
                          "ms_per_step": fwd_ms},
             "wall_ms_per_step_incl_flush": t_wall * 1e3 / args.steps,

@@ -61,7 +61,7 @@ struct Workspace {
 
 // slots of the device-side scale array (fp16-plane precision): raw maxima, derived scales, and
 // per weight block {max |W|, scale} from kScWeights on
-enum { kScX = 0, kScRad, kScG, kScH1, kScDht, kScA1, kScHt, kScDy, kScDh1, kScWeights = 16,
+enum { kScX = 0, kScRad, kScG, kScH1, kScDht, kScA1, kScHt, kScDy, kScDh1, kScGate, kScWeights = 16,
        kScCount = kScWeights + 4 * (ZP_MAX_L + 1) };
 
 constexpr int kMaxWgradSplits = 8;
@@ -416,7 +416,8 @@ int zp_eso2_forward(const zp_plan *plan, int64_t N, int64_t E, const float *x_no
   if (plan->fp16)      // |gate(h1)| <= |h1|
     ZP_TIMED(ZP_K_GATE_FWD, zp_launch_scale(1.f, ws.scales + kScH1, nullptr, nullptr, 0.f,
                                             ws.scales + kScHt, st));
-  ZP_TIMED(ZP_K_GATE_FWD, zp_launch_gate_fwd(plan, E, ws.h1, ws.ht, st));
+  ZP_TIMED(ZP_K_GATE_FWD, zp_launch_gate_fwd(plan, E, ws.h1, ws.ht,
+                                             plan->fp16 ? ws.scales + kScGate : nullptr, st));
   for (int m = 0; m < plan->n_blocks && E > 0; ++m) {
     const int in = plan->c2_in[m], out = plan->c2_out[m];
     const ZpPlanes A = sub(ws.ht, (int64_t)t.m_row0[m] * t.H);
@@ -485,13 +486,12 @@ int zp_eso2_backward(const zp_plan *plan, int64_t N, int64_t E, const float *gra
     const int64_t ldx = conv ? ldh : lda;
     const int cin = conv ? t.H : 2 * t.C, cout = conv ? t.C : t.H;
     if (conv == 0) {
-      if (plan->fp16) {      // true max |dh1| from a store-free pass, then its scale
-        ZP_TIMED(ZP_K_GATE_BWD,
-                 zp_launch_gate_bwd(plan, E, ws.h1, ws.dht, ws.dh1, ws.scales + kScDht, st));
-        ZP_TIMED(ZP_K_GATE_BWD, zp_launch_scale(1.f, ws.scales + kScDht, nullptr, nullptr, 0.f,
-                                                ws.scales + kScDh1, st));
-      }
-      ZP_TIMED(ZP_K_GATE_BWD, zp_launch_gate_bwd(plan, E, ws.h1, ws.dht, ws.dh1, nullptr, st));
+      if (plan->fp16)        // |dh1| <= 1.1 max|dht| max(1, gate bound of the forward)
+        ZP_TIMED(ZP_K_GATE_BWD, zp_launch_scale(1.1f, ws.scales + kScDht, nullptr,
+                                                ws.scales + kScGate, 1.f, ws.scales + kScDh1, st));
+      ZP_TIMED(ZP_K_GATE_BWD, zp_launch_gate_bwd(plan, E, ws.h1, ws.dht, ws.dh1, st));
+    } else if (plan->fp16) {
+      ZP_CUDA(cudaMemsetAsync(ws.scales + kScDht, 0, sizeof(float), st));
     }
     for (int m = 0; m < plan->n_blocks; ++m) {
       const int in = conv ? plan->c2_in[m] : plan->c1_in[m];
@@ -512,7 +512,7 @@ int zp_eso2_backward(const zp_plan *plan, int64_t N, int64_t E, const float *gra
                         Wt, out, (int64_t)out * in, 0, nullptr, dX + xcol, ldx,
                         plan->status_dev, 0, 1, 0, 0, plan->fp16, dYm.scale,
                         wscale(plan, ws, conv, m),
-                        nullptr};
+                        (conv && plan->fp16) ? ws.scales + kScDht : nullptr};   // max |dht|
       ZP_TIMED(ZP_K_GEMM_DGRAD, zp_launch_gemm_tc(gd, st));
       ZpGemmTc gw_{out, in, E, P, dYm.base, dYm.ld, dYm.plane_stride, 1,
                    Xm.base, Xm.ld, Xm.plane_stride, 1, nullptr, G, in,

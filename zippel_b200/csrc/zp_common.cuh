@@ -117,10 +117,11 @@ int zp_launch_node_reduce(const zp_plan *p, int64_t N, const float *du_both,
                           const int32_t *row_ptr_src, float *grad_x, cudaStream_t st);
 
 int zp_launch_gate_fwd(const zp_plan *p, int64_t E, const float *h1, const ZpPlanes &ht,
-                       cudaStream_t st);
-// max_out != null: store nothing, only record max |dh1| in *max_out (device scalar)
+                       float *gate_max, cudaStream_t st);
+// gate_max (device scalar, may be null): bound of the backward's gate gradients per unit of
+// max |dht|, recorded by the forward
 int zp_launch_gate_bwd(const zp_plan *p, int64_t E, const float *h1, const float *dht,
-                       const ZpPlanes &dh1, float *max_out, cudaStream_t st);
+                       const ZpPlanes &dh1, cudaStream_t st);
 
 // Tensor-core product over bf16 planes: C[M,N] = sum_pairs A_pa * B_pb^T (+ bias), fp32 out.
 // K-major operand: X[p*plane + r*ld + k]; MN-major (x_mn = 1): X[p*plane + k*ld + r].

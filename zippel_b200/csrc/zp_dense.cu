@@ -64,41 +64,80 @@ __global__ void scale_kernel(float factor, const float *a, const float *b, const
 // ------------------------------------------------------------------------------------------
 __device__ __forceinline__ float sigmoidf(float x) { return 1.f / (1.f + __expf(-x)); }
 
+// One thread per (edge, hidden-channel quad) walks the Km rows.  With `gate_max` set it also
+// records  max over (edge, l, channel) of  sigmoid'(gate_l) * sum_{rows of l} |h1 row| : times
+// max |d ht| that bounds the gate part of the backward's dh1, which fixes the scale of its fp16
+// planes before they are written.
 __global__ void gate_fwd_kernel(const __grid_constant__ ZpTables t, int64_t E,
-                                const float *__restrict__ h1, const ZpPlanes ht) {
-  const int H4 = t.H / 4;
-  const int64_t idx = (int64_t)blockIdx.x * blockDim.x + threadIdx.x;
-  const int64_t total = E * t.Km * H4;
-  if (idx >= total) return;
-  const int h = (int)(idx % H4) * 4;
-  const int r = (int)((idx / H4) % t.Km);
-  const int64_t e = idx / ((int64_t)H4 * t.Km);
-  const float *row = h1 + (size_t)e * t.w1_cols;
-  const float4 x = *reinterpret_cast<const float4 *>(row + t.n_gate + r * t.H + h);
-  float o[4];
-  if (r == 0) {
-    o[0] = x.x * sigmoidf(x.x); o[1] = x.y * sigmoidf(x.y);
-    o[2] = x.z * sigmoidf(x.z); o[3] = x.w * sigmoidf(x.w);
-  } else {
-    const float4 g = *reinterpret_cast<const float4 *>(row + (t.row_l[r] - 1) * t.H + h);
-    o[0] = x.x * sigmoidf(g.x); o[1] = x.y * sigmoidf(g.y);
-    o[2] = x.z * sigmoidf(g.z); o[3] = x.w * sigmoidf(g.w);
-  }
-  zp_store_planes<4>(ht, e * ht.ld + (int64_t)r * t.H + h, o, zp_inv_scale(ht));
-}
-
-// one thread per (edge, hidden-channel quad): walks the Km rows, accumulates the lmax gate grads.
-// With `max_out` set nothing is stored: the kernel only records max |dh1| there (the scale of
-// the fp16 planes needs the true maximum; a product of bounds is far too loose once the gates
-// saturate).
-__global__ void gate_bwd_kernel(const __grid_constant__ ZpTables t, int64_t E,
-                                const float *__restrict__ h1, const float *__restrict__ dht,
-                                const ZpPlanes dh1, float *max_out) {
+                                const float *__restrict__ h1, const ZpPlanes ht,
+                                float *gate_max) {
   const int H4 = t.H / 4;
   const int64_t idx0 = (int64_t)blockIdx.x * blockDim.x + threadIdx.x;
   const bool in_range = idx0 < E * H4;
   const int64_t idx = in_range ? idx0 : 0;        // out-of-range threads recompute item 0
-  float seen = 0.f;
+  const int h = (int)(idx % H4) * 4;
+  const int64_t e = idx / H4;
+  const float *row = h1 + (size_t)e * t.w1_cols;
+  const float inv = zp_inv_scale(ht);
+  float sg[ZP_MAX_L][4], mag[ZP_MAX_L][4];
+#pragma unroll
+  for (int l = 0; l < ZP_MAX_L; ++l) {
+    if (l < t.lmax) {
+      const float4 g = *reinterpret_cast<const float4 *>(row + l * t.H + h);
+      sg[l][0] = sigmoidf(g.x); sg[l][1] = sigmoidf(g.y);
+      sg[l][2] = sigmoidf(g.z); sg[l][3] = sigmoidf(g.w);
+    }
+#pragma unroll
+    for (int v = 0; v < 4; ++v) mag[l][v] = 0.f;
+  }
+  for (int r = 0; r < t.Km; ++r) {
+    const float4 x4 = *reinterpret_cast<const float4 *>(row + t.n_gate + r * t.H + h);
+    const float x[4] = {x4.x, x4.y, x4.z, x4.w};
+    float o[4];
+    if (r == 0) {
+#pragma unroll
+      for (int v = 0; v < 4; ++v) o[v] = x[v] * sigmoidf(x[v]);
+    } else {
+      const int l = t.row_l[r] - 1;
+#pragma unroll
+      for (int ll = 0; ll < ZP_MAX_L; ++ll) {
+        if (ll == l) {
+#pragma unroll
+          for (int v = 0; v < 4; ++v) {
+            o[v] = x[v] * sg[ll][v];
+            mag[ll][v] += fabsf(x[v]);
+          }
+        }
+      }
+    }
+    if (in_range) zp_store_planes<4>(ht, e * ht.ld + (int64_t)r * t.H + h, o, inv);
+  }
+  if (gate_max) {
+    float seen = 0.f;
+#pragma unroll
+    for (int l = 0; l < ZP_MAX_L; ++l)
+      if (l < t.lmax) {
+#pragma unroll
+        for (int v = 0; v < 4; ++v)
+          seen = fmaxf(seen, sg[l][v] * (1.f - sg[l][v]) * mag[l][v]);
+      }
+#pragma unroll
+    for (int o = 16; o > 0; o >>= 1) seen = fmaxf(seen, __shfl_xor_sync(0xffffffffu, seen, o));
+    if ((threadIdx.x & 31) == 0 && seen > 0.f) zp_atomic_absmax(gate_max, seen);
+  }
+}
+
+// one thread per (edge, hidden-channel quad): walks the Km rows, accumulates the lmax gate grads.
+// The scale of the fp16 planes is fixed beforehand from max |dht| and the forward's gate bound:
+//   |dh1 row| <= 1.1 max|dht|  (sigmoid <= 1, silu' <= 1.1),
+//   |dh1 gate_l| = sigmoid'(g_l) |sum_rows dht h1| <= max|dht| * sigmoid'(g_l) sum_rows |h1|.
+__global__ void gate_bwd_kernel(const __grid_constant__ ZpTables t, int64_t E,
+                                const float *__restrict__ h1, const float *__restrict__ dht,
+                                const ZpPlanes dh1) {
+  const int H4 = t.H / 4;
+  const int64_t idx0 = (int64_t)blockIdx.x * blockDim.x + threadIdx.x;
+  const bool in_range = idx0 < E * H4;
+  const int64_t idx = in_range ? idx0 : 0;        // out-of-range threads recompute item 0
   const int h = (int)(idx % H4) * 4;
   const int64_t e = idx / H4;
   const float *row = h1 + (size_t)e * t.w1_cols;
@@ -140,12 +179,7 @@ __global__ void gate_bwd_kernel(const __grid_constant__ ZpTables t, int64_t E,
         }
       }
     }
-    if (max_out) {
-#pragma unroll
-      for (int v = 0; v < 4; ++v) seen = fmaxf(seen, fabsf(o[v]));
-    } else if (in_range) {
-      zp_store_planes<4>(dh1, drow + t.n_gate + r * t.H + h, o, inv);
-    }
+    if (in_range) zp_store_planes<4>(dh1, drow + t.n_gate + r * t.H + h, o, inv);
   }
 #pragma unroll
   for (int l = 0; l < ZP_MAX_L; ++l) {
@@ -153,18 +187,8 @@ __global__ void gate_bwd_kernel(const __grid_constant__ ZpTables t, int64_t E,
       float o[4];
 #pragma unroll
       for (int v = 0; v < 4; ++v) o[v] = dg[l][v] * sg[l][v] * (1.f - sg[l][v]);
-      if (max_out) {
-#pragma unroll
-        for (int v = 0; v < 4; ++v) seen = fmaxf(seen, fabsf(o[v]));
-      } else if (in_range) {
-        zp_store_planes<4>(dh1, drow + l * t.H + h, o, inv);
-      }
+      if (in_range) zp_store_planes<4>(dh1, drow + l * t.H + h, o, inv);
     }
-  }
-  if (max_out) {
-#pragma unroll
-    for (int o = 16; o > 0; o >>= 1) seen = fmaxf(seen, __shfl_xor_sync(0xffffffffu, seen, o));
-    if ((threadIdx.x & 31) == 0 && seen > 0.f) zp_atomic_absmax(max_out, seen);
   }
 }
 
@@ -333,21 +357,20 @@ int zp_launch_scale(float factor, const float *a, const float *b, const float *c
 }
 
 int zp_launch_gate_fwd(const zp_plan *p, int64_t E, const float *h1, const ZpPlanes &ht,
-                       cudaStream_t st) {
+                       float *gate_max, cudaStream_t st) {
+  if (gate_max) ZP_CUDA(cudaMemsetAsync(gate_max, 0, sizeof(float), st));
   if (E == 0) return ZP_OK;
-  const int64_t total = E * p->t.Km * (p->t.H / 4);
-  gate_fwd_kernel<<<(unsigned)zp_ceil_div(total, 256), 256, 0, st>>>(p->t, E, h1, ht);
+  const int64_t total = E * (p->t.H / 4);
+  gate_fwd_kernel<<<(unsigned)zp_ceil_div(total, 128), 128, 0, st>>>(p->t, E, h1, ht, gate_max);
   ZP_LAUNCH_CHECK("gate_fwd_kernel");
   return ZP_OK;
 }
 
 int zp_launch_gate_bwd(const zp_plan *p, int64_t E, const float *h1, const float *dht,
-                       const ZpPlanes &dh1, float *max_out, cudaStream_t st) {
-  if (max_out) ZP_CUDA(cudaMemsetAsync(max_out, 0, sizeof(float), st));
+                       const ZpPlanes &dh1, cudaStream_t st) {
   if (E == 0) return ZP_OK;
   const int64_t total = E * (p->t.H / 4);
-  gate_bwd_kernel<<<(unsigned)zp_ceil_div(total, 128), 128, 0, st>>>(p->t, E, h1, dht, dh1,
-                                                                      max_out);
+  gate_bwd_kernel<<<(unsigned)zp_ceil_div(total, 128), 128, 0, st>>>(p->t, E, h1, dht, dh1);
   ZP_LAUNCH_CHECK("gate_bwd_kernel");
   return ZP_OK;
 }

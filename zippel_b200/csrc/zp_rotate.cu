@@ -238,11 +238,44 @@ rotate_back_scatter_kernel(const __grid_constant__ ZpTables t, int64_t N,
 constexpr int kEdgeThreads = 256;
 
 template <int N>
-__device__ __forceinline__ void warp_sum_n(float (&p)[N]) {
+struct Pow2Ceil {
+  static constexpr int v = N <= 1 ? 1 : N <= 2 ? 2 : N <= 4 ? 4 : N <= 8 ? 8 : N <= 16 ? 16 : 32;
+};
+
+// Sums each of p[0..N) over the 32 lanes.  Halving exchange: at every step a lane hands half of
+// its values to the partner lane and adds the partner's other half to its own, so the step
+// costs half as many shuffles as the one before (about Pow2Ceil<N> shuffles in all, against
+// 5 N for one butterfly per value).  Afterwards the lane holds the total of element `idx`;
+// lanes that differ only in their low log2(32 / Pow2Ceil<N>) bits hold the same element.
+// The summation tree is fixed.
+template <int N>
+__device__ __forceinline__ float warp_sum_scatter(const float (&p)[N], int lane, int &idx) {
+  constexpr int NP = Pow2Ceil<N>::v;
+  static_assert(N <= 32, "at most one value per lane");
+  float q[NP];
 #pragma unroll
-  for (int o = 16; o > 0; o >>= 1)
+  for (int j = 0; j < NP; ++j) q[j] = j < N ? p[j] : 0.f;
+  idx = 0;
+  int mask = 16;
 #pragma unroll
-    for (int j = 0; j < N; ++j) p[j] += __shfl_xor_sync(0xffffffffu, p[j], o);
+  for (int h = NP / 2; h >= 1; h >>= 1) {
+    const bool up = (lane & mask) != 0;
+#pragma unroll
+    for (int j = 0; j < h; ++j) {
+      const float send = up ? q[j] : q[j + h];
+      const float keep = up ? q[j + h] : q[j];
+      q[j] = keep + __shfl_xor_sync(0xffffffffu, send, mask);
+    }
+    idx += up ? h : 0;
+    mask >>= 1;
+  }
+  for (; mask >= 1; mask >>= 1) q[0] += __shfl_xor_sync(0xffffffffu, q[0], mask);
+  return q[0];
+}
+// lanes that publish the result of warp_sum_scatter<N>: one per element
+template <int N>
+__device__ __forceinline__ bool warp_sum_owner(int lane, int idx) {
+  return (lane & (32 / Pow2Ceil<N>::v - 1)) == 0 && idx < N;
 }
 
 // ---- VJP of rotate_back_scatter, one edge per warp group ----------------------------------
@@ -286,11 +319,9 @@ struct GradOutE {
           }
           part[j] = s;
         }
-        warp_sum_n<n>(part);
-        if (lane == 0) {
-#pragma unroll
-          for (int j = 0; j < n; ++j) part_s[t.rot_off[r] + j] = part[j];
-        }
+        int idx;
+        const float tot = warp_sum_scatter<n>(part, lane, idx);
+        if (warp_sum_owner<n>(lane, idx)) part_s[t.rot_off[r] + idx] = tot;
 #pragma unroll
         for (int v = 0; v < 4; ++v) {
           genv = fmaf(yv[v], tv[v], genv);
@@ -412,11 +443,9 @@ struct RotInBwdE {
             }
             part[j] = s;
           }
-          warp_sum_n<n>(part);
-          if (lane == 0) {
-#pragma unroll
-            for (int j = 0; j < n; ++j) part_s[t.rot_off[r] + j] = part[j];
-          }
+          int idx;
+          const float tot = warp_sum_scatter<n>(part, lane, idx);
+          if (warp_sum_owner<n>(lane, idx)) part_s[t.rot_off[r] + idx] = tot;
         }
         if (active) vstore<4>(grad_e + col, gr);
       }
@@ -436,7 +465,7 @@ struct RotInBwdE<-1, LMAX> {
 
 // du_both [E][2][K][C]: half 0 = contribution to the source node, half 1 = to the destination
 template <int LMAX>
-__global__ void __launch_bounds__(kEdgeThreads)
+__global__ void __launch_bounds__(kEdgeThreads, (LMAX <= 4 ? 2 : 1))
 rotate_in_bwd_kernel(const __grid_constant__ ZpTables t, int64_t E, int W,
                      const float *__restrict__ da1, const float *__restrict__ radial,
                      const float *__restrict__ x, const int32_t *__restrict__ src,

@@ -230,6 +230,31 @@ int zp_layernorm_silu_backward(int64_t rows, int width, const float *x, const fl
                                const float *dy, float *dx, float *dgamma, float *dbeta,
                                void *work, size_t work_bytes, void *stream);
 
+/* Periodic neighbour list with the per-destination cap, on the device (the graph front end; the
+ * reference builds edge lists on the host with an external package and applies no cap,
+ * fixtures/make_fixtures.py:13-15, 78-100).  Cubic periodic box of edge `box`; positions fp64 [N,3],
+ * not necessarily inside [0, box) (shifts refer to the positions as given).
+ * Edges src -> dst with d2 = |pos[dst] - pos[src] + shift|^2 < cutoff^2 (shift = image * box,
+ * the zero-shift self pair excluded); per destination the max_neighbors smallest by
+ * (d2, src, shift_x, shift_y, shift_z) are kept (max_neighbors <= 0: all, at most
+ * ZP_NEIGHBORS_MAX_HITS per atom).  Output order is (dst, src, shift): destination-sorted, with
+ * row_ptr.  Two calls, because the edge count is only known after the first:
+ *   zp_neighbors_count  builds the cell list in `work`, writes row_ptr[N+1] (row_ptr[N] = E);
+ *   zp_neighbors_fill   (same pos/box/cutoff/max_neighbors/work) writes edge_index [2,E] int64
+ *                       (row 0 = src, row 1 = dst) and shifts [E,3] fp64.
+ * *flags_out (device int) is 0 on success; bit 0: a position that is not finite, bit 1: more than
+ * ZP_NEIGHBORS_MAX_HITS neighbours of one atom in an uncapped list, bit 2: the passes disagree.  */
+#define ZP_NEIGHBORS_MAX_HITS 512
+#define ZP_NEIGHBORS_MAX_CAP 256
+size_t zp_neighbors_work_bytes(int64_t n_atoms, double box, double cutoff);
+int zp_neighbors_count(const double *pos, int64_t n_atoms, double box, double cutoff,
+                       int max_neighbors, int32_t *row_ptr, int32_t *flags_out, void *work,
+                       size_t work_bytes, void *stream);
+int zp_neighbors_fill(const double *pos, int64_t n_atoms, double box, double cutoff,
+                      int max_neighbors, const int32_t *row_ptr, int64_t n_edges,
+                      int64_t *edge_index, double *shifts, int32_t *flags_out, void *work,
+                      size_t work_bytes, void *stream);
+
 /* Reads (synchronously) and clears the plan's device status word: ZP_OK, or
  * ZP_ERR_DEVICE_TIMEOUT if a bounded device-side wait gave up since the last read.          */
 int zp_plan_device_status(zp_plan *plan, int *status_out);

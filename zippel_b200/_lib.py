@@ -68,6 +68,10 @@ SIGNATURES = {
     "zp_layernorm_silu_forward": (C.c_int, [_I64, C.c_int, _P, _P, _P, C.c_float, _P, _P, _P, _P]),
     "zp_layernorm_silu_backward": (C.c_int, [_I64, C.c_int, _P, _P, _P, _P, _P, _P, _P, _P, _P, _P,
                                               _SZ, _P]),
+    "zp_neighbors_work_bytes": (_SZ, [_I64, C.c_double, C.c_double]),
+    "zp_neighbors_count": (C.c_int, [_P, _I64, C.c_double, C.c_double, C.c_int, _P, _P, _P, _SZ, _P]),
+    "zp_neighbors_fill": (C.c_int, [_P, _I64, C.c_double, C.c_double, C.c_int, _P, _I64, _P, _P, _P,
+                                    _P, _SZ, _P]),
     "zp_plan_device_status": (C.c_int, [_P, C.POINTER(C.c_int)]),
     "zp_kernel_class_name": (C.c_char_p, [C.c_int]),
     "zp_timing_enable": (C.c_int, [_P, C.c_int]),

@@ -165,6 +165,51 @@ def periodic_neighbors(pos: np.ndarray, box: float, cutoff: float,
     return np.stack([src, dst]), sh
 
 
+def neighbor_list(pos: torch.Tensor, box: float, cutoff: float,
+                  max_neighbors: int | None = 30) -> tuple[torch.Tensor, torch.Tensor, torch.Tensor]:
+    """The neighbour list on the device (``zp_neighbors_count`` / ``zp_neighbors_fill``): all edges
+    src -> dst with ``|pos[dst] - pos[src] + shift|^2 < cutoff^2`` in a cubic periodic box of edge
+    ``box`` (positions need not be wrapped into it), per destination the ``max_neighbors``
+    smallest by (d2, src, shift) kept.
+    ``pos``: CUDA tensor [N, 3] (computed in float64).  Returns (edge_index [2, E] int64,
+    shifts [E, 3] float64, row_ptr [N + 1] int32) in (dst, src, shift) order, which is already the
+    destination-sorted form the kernels consume.  One host read (the edge count) in between the
+    two passes."""
+    if not pos.is_cuda:
+        raise RuntimeError("neighbor_list needs a CUDA tensor: there is no CPU path")
+    lib = _lib.load()
+    p = pos.detach().to(torch.float64).contiguous()
+    n = p.shape[0]
+    cap = int(max_neighbors) if max_neighbors else 0
+    nbytes = lib.zp_neighbors_work_bytes(n, float(box), float(cutoff))
+    if nbytes == 0:
+        raise _lib.ZpError(1, "zp_neighbors_work_bytes")
+    dev = p.device
+    work = torch.empty(nbytes, dtype=torch.uint8, device=dev)
+    row_ptr = torch.empty(n + 1, dtype=torch.int32, device=dev)
+    flags = torch.zeros(1, dtype=torch.int32, device=dev)
+    with torch.cuda.device(dev):
+        st = torch.cuda.current_stream().cuda_stream
+        _lib.check(lib.zp_neighbors_count(p.data_ptr(), n, float(box), float(cutoff), cap,
+                                          row_ptr.data_ptr(), flags.data_ptr(), work.data_ptr(),
+                                          nbytes, st), "zp_neighbors_count")
+        e, fl = int(row_ptr[n].item()), int(flags.item())
+        if fl & 1:
+            raise ValueError("neighbor_list: positions must be finite")
+        if fl & 2:
+            raise _lib.ZpError(7, "zp_neighbors_count (more neighbours per atom than an uncapped "
+                                  "list can hold)")
+        edge_index = torch.empty(2, e, dtype=torch.int64, device=dev)
+        shifts = torch.empty(e, 3, dtype=torch.float64, device=dev)
+        _lib.check(lib.zp_neighbors_fill(p.data_ptr(), n, float(box), float(cutoff), cap,
+                                         row_ptr.data_ptr(), e, edge_index.data_ptr(),
+                                         shifts.data_ptr(), flags.data_ptr(), work.data_ptr(),
+                                         nbytes, st), "zp_neighbors_fill")
+        if int(flags.item()):
+            raise RuntimeError(f"zp_neighbors_fill: device flags {int(flags.item())}")
+    return edge_index, shifts, row_ptr
+
+
 def synthetic_batch(n_atoms: int, lmax: int, channels: int, cutoff: float, *,
                     density: float | None = 0.1, box: float | None = None,
                     max_neighbors: int | None = 30, n_structures: int = 1, seed: int = 0,

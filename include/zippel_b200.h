@@ -35,7 +35,7 @@ typedef enum zp_status {
   ZP_ERR_CUDA = 4,             /* a CUDA runtime call failed; see zp_last_cuda_error()     */
   ZP_ERR_DEVICE_TIMEOUT = 5,   /* a bounded device-side wait gave up (status word set)     */
   ZP_ERR_NO_DEVICE_CODE = 6,   /* the library holds no code for this GPU (needs sm_100a)   */
-  ZP_ERR_TOO_LARGE = 7         /* sizes exceed the fixed capacity of a non-allocating call  */
+  ZP_ERR_TOO_LARGE = 7         /* sizes exceed a fixed capacity of the entry point           */
 } zp_status;
 
 /* Mirrors the fields of the reference's BlockConfig (blocks/eso2_ref.py:51-76) that the
@@ -244,7 +244,7 @@ int zp_layernorm_silu_backward(int64_t rows, int width, const float *x, const fl
  *                       (row 0 = src, row 1 = dst) and shifts [E,3] fp64.
  * *flags_out (device int) is 0 on success; bit 0: a position that is not finite, bit 1: more than
  * ZP_NEIGHBORS_MAX_HITS neighbours of one atom in an uncapped list, bit 2: the passes disagree.  */
-#define ZP_NEIGHBORS_MAX_HITS 512
+#define ZP_NEIGHBORS_MAX_HITS 1024
 #define ZP_NEIGHBORS_MAX_CAP 256
 size_t zp_neighbors_work_bytes(int64_t n_atoms, double box, double cutoff);
 int zp_neighbors_count(const double *pos, int64_t n_atoms, double box, double cutoff,

@@ -149,7 +149,7 @@ const char *zp_status_string(int status) {
     case ZP_ERR_CUDA: return "CUDA runtime error";
     case ZP_ERR_DEVICE_TIMEOUT: return "device-side wait timed out";
     case ZP_ERR_NO_DEVICE_CODE: return "no device code for this GPU (library is built for sm_100a)";
-    case ZP_ERR_TOO_LARGE: return "problem exceeds the fixed capacity of this non-allocating entry point";
+    case ZP_ERR_TOO_LARGE: return "problem exceeds a fixed capacity of this entry point";
     default: return "unknown status";
   }
 }

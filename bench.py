@@ -539,6 +539,75 @@ def run_large(args) -> dict | None:
     return line
 
 
+# published by the reference on GH200 for its K4L2 configuration (lmax = mmax = 2, C = 128, fp32):
+# eager PyTorch forward of the block on these fixtures (other hardware: context, not a target)
+REFERENCE_PUBLISHED_FWD_MS = {"si_medium": 49.99, "si_small": 5.50}
+
+
+def run_fixture(args) -> dict:
+    """`--workload fixture --fixture NAME`: one of the reference's six benchmark structures
+    (perturbed bulk Si / Cu, 6 A cutoff, no neighbour cap), rebuilt on the device from the
+    recorded recipe, at the reference's K4L2 block configuration.  Times the module's forward to
+    the scalar energy and forward + first-order VJP of the node output, inputs resident."""
+    from zippel_b200 import fixtures as fx
+    from zippel_b200.blocks.eso2 import BlockConfig, ESO2Block
+    from zippel_b200.graph import EdgeGraph
+
+    dev = torch.device("cuda", 0)
+    torch.cuda.set_device(dev)
+    cfg = BlockConfig()                                   # lmax 2, mmax 2, C = H = EC = 128, 64 RBF
+    t0 = time.perf_counter()
+    arrays, meta = fx.build_fixture(args.fixture, device=dev)
+    build_s = time.perf_counter() - t0
+    batch = fx.load_batch((arrays, meta), dev, torch.float32, cfg, requires_grad=False)
+    block = ESO2Block(cfg, precision=args.precision)
+    xavier_(block, 0)
+    block = block.to(dev)
+    n, e = meta["n_atoms"], meta["n_edges"]
+    graph = EdgeGraph.build(batch["edge_index"], n)
+    up = torch.randn(batch["x_node"].shape, generator=torch.Generator("cpu").manual_seed(9)).to(dev)
+    a = (batch["atomic_numbers"], batch["edge_index"], batch["shifts"], batch["cos_gamma_k"],
+         batch["sin_gamma_k"])
+
+    def fwd():
+        with torch.no_grad():
+            return block(batch["pos"], a[0], batch["x_node"], *a[1:], graph=graph)
+
+    def fwd_vjp():
+        pos = batch["pos"].detach().requires_grad_(True)
+        x = batch["x_node"].detach().requires_grad_(True)
+        out = block.node_output(pos, a[0], x, *a[1:], graph=graph)
+        return torch.autograd.grad((out * up).sum(), [x, pos, *block.parameters()],
+                                   allow_unused=True)
+
+    def timed(fn):
+        for _ in range(max(args.warmup, 3)):
+            fn()
+        ms = []
+        for _ in range(args.steps):
+            ea, eb = torch.cuda.Event(True), torch.cuda.Event(True)
+            ea.record(); fn(); eb.record()
+            eb.synchronize()
+            ms.append(ea.elapsed_time(eb))
+        return statistics.median(ms)
+
+    f_ms, b_ms = timed(fwd), timed(fwd_vjp)
+    pub = REFERENCE_PUBLISHED_FWD_MS.get(args.fixture)
+    return {"metric": "edges/s, eSEN SO(2) block on a reference fixture (lmax2 mmax2 C128, fp32)",
+            "workload": f"fixture {args.fixture}", "value": e / (b_ms * 1e-3), "unit": "edges/s",
+            "n_gpus": 1, "steps": args.steps, "warmup": max(args.warmup, 3), "ms_per_step": b_ms,
+            "higher_is_better": True, "precision": args.precision, "data": "reference fixture rebuilt "
+            "from its recipe (content hash equal to the reference manifest's)",
+            "forward": {"ms": f_ms, "edges_per_s": e / (f_ms * 1e-3),
+                        "reference_published_eager_ms_gh200": pub,
+                        "ratio_to_published": (pub / f_ms) if pub else None},
+            "config": {"atoms": n, "edges": e, "avg_degree": meta["avg_degree"], "lmax": 2, "mmax": 2,
+                       "channels": 128, "sha256_content": meta["sha256_content"],
+                       "fixture_build_s": build_s},
+            "device_status": block.plan(dev).device_status(),
+            "peak_mem_gb": torch.cuda.max_memory_allocated(dev) / 1e9}
+
+
 def main() -> None:
     ap = argparse.ArgumentParser()
     ap.add_argument("--gpus", type=int, default=1)
@@ -550,7 +619,10 @@ def main() -> None:
     ap.add_argument("--no-cpu-baseline", action="store_true")
     ap.add_argument("--precision", default="fp32", choices=["fp32", "fp32_bf16x3", "bf16"],
                     help="operand format of the SO(2) contraction (see ESO2Block)")
-    ap.add_argument("--workload", default="cfg2", choices=["cfg2", "cfg3", "cfg4"],
+    ap.add_argument("--fixture", default="si_medium",
+                    choices=["si_small", "si_medium", "si_large", "cu_small", "cu_medium", "cu_large"],
+                    help="with --workload fixture: which of the reference's structures")
+    ap.add_argument("--workload", default="cfg2", choices=["cfg2", "cfg3", "cfg4", "fixture"],
                     help="cfg2 = the benchmark line; cfg3 / cfg4 = the larger BASELINE configurations")
     ap.add_argument("--structures", type=int, default=512, help="cfg3: number of 200-atom structures")
     ap.add_argument("--atoms", type=int, default=N_ATOMS,
@@ -572,7 +644,10 @@ def main() -> None:
         if int(os.environ.get("RANK", "0")) == 0:
             emit(run_reference(args))
         return
-    line = run_ours(args) if args.workload == "cfg2" else run_large(args)
+    if args.workload == "fixture":
+        line = run_fixture(args)
+    else:
+        line = run_ours(args) if args.workload == "cfg2" else run_large(args)
     if line is not None:
         emit(line)
 

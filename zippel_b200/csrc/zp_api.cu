@@ -486,9 +486,11 @@ int zp_eso2_backward(const zp_plan *plan, int64_t N, int64_t E, const float *gra
     const int64_t ldx = conv ? ldh : lda;
     const int cin = conv ? t.H : 2 * t.C, cout = conv ? t.C : t.H;
     if (conv == 0) {
-      if (plan->fp16)        // |dh1| <= 1.1 max|dht| max(1, gate bound of the forward)
-        ZP_TIMED(ZP_K_GATE_BWD, zp_launch_scale(1.1f, ws.scales + kScDht, nullptr,
-                                                ws.scales + kScGate, 1.f, ws.scales + kScDh1, st));
+      if (plan->fp16)        // |dh1| <= 1.1 max|dht| max(1, rows * max sigmoid' * max|h1|)
+        ZP_TIMED(ZP_K_GATE_BWD,
+                 zp_launch_scale(1.1f, ws.scales + kScDht, nullptr, ws.scales + kScGate, 1.f,
+                                 ws.scales + kScDh1, st, ws.scales + kScH1,
+                                 (float)(2 * t.mmax + 1)));
       ZP_TIMED(ZP_K_GATE_BWD, zp_launch_gate_bwd(plan, E, ws.h1, ws.dht, ws.dh1, st));
     } else if (plan->fp16) {
       ZP_CUDA(cudaMemsetAsync(ws.scales + kScDht, 0, sizeof(float), st));

@@ -118,8 +118,7 @@ int zp_launch_node_reduce(const zp_plan *p, int64_t N, const float *du_both,
 
 int zp_launch_gate_fwd(const zp_plan *p, int64_t E, const float *h1, const ZpPlanes &ht,
                        float *gate_max, cudaStream_t st);
-// gate_max (device scalar, may be null): bound of the backward's gate gradients per unit of
-// max |dht|, recorded by the forward
+// gate_max (device scalar, may be null): largest sigmoid'(gate) seen by the forward
 int zp_launch_gate_bwd(const zp_plan *p, int64_t E, const float *h1, const float *dht,
                        const ZpPlanes &dh1, cudaStream_t st);
 
@@ -149,11 +148,13 @@ int zp_gemm_tc_pick_splits(const ZpGemmTc &g, int max_splits);
 // fp32 [rows, cols] (row stride ld_in) -> planes [rows, out.ld], zero padded
 int zp_launch_split_planes(int64_t rows, int64_t cols, const float *in, int64_t ld_in,
                            const ZpPlanes &out, cudaStream_t st);
-// *out = max |in| (device scalar);  *scale = power of two mapping factor*a*b*max(offset_c, c) to 2^15
+// *out = max |in| (device scalar)
 int zp_launch_absmax(int64_t rows, int64_t cols, const float *in, int64_t ld, float *out,
                      cudaStream_t st);
+// *scale = power of two mapping factor*a*b*max(offset_c, c_factor*c*d) to 2^15 (device scalars;
+// null = 1; without c the max term is left out)
 int zp_launch_scale(float factor, const float *a, const float *b, const float *c, float offset_c,
-                    float *scale, cudaStream_t st);
+                    float *scale, cudaStream_t st, const float *d = nullptr, float c_factor = 1.f);
 
 // Folded SO(2) weights as bf16 planes: per block W_fold [P][out][in] followed by its transpose
 // [P][in][out], at element offset c{1,2}_woff[m] of `packed`.

@@ -51,11 +51,12 @@ __global__ void absmax_kernel(int64_t rows, int64_t cols, const float *__restric
   if ((threadIdx.x & 31) == 0 && m > 0.f) zp_atomic_absmax(out, m);
 }
 
-// scale[0] = power of two mapping  factor * a * b (* c)  to 2^15; null pointers count as 1
+// scale[0] = power of two mapping  factor * a * b * max(offset_c, c_factor * c * d)  to 2^15;
+// null pointers count as 1, the max term is left out when c is null
 __global__ void scale_kernel(float factor, const float *a, const float *b, const float *c,
-                             float offset_c, float *scale) {
+                             const float *d, float c_factor, float offset_c, float *scale) {
   float bound = factor * (a ? *a : 1.f) * (b ? *b : 1.f);
-  if (c) bound *= fmaxf(offset_c, *c);
+  if (c) bound *= fmaxf(offset_c, c_factor * *c * (d ? *d : 1.f));
   *scale = zp_scale_for_bound(bound);
 }
 
@@ -64,73 +65,50 @@ __global__ void scale_kernel(float factor, const float *a, const float *b, const
 // ------------------------------------------------------------------------------------------
 __device__ __forceinline__ float sigmoidf(float x) { return 1.f / (1.f + __expf(-x)); }
 
-// One thread per (edge, hidden-channel quad) walks the Km rows.  With `gate_max` set it also
-// records  max over (edge, l, channel) of  sigmoid'(gate_l) * sum_{rows of l} |h1 row| : times
-// max |d ht| that bounds the gate part of the backward's dh1, which fixes the scale of its fp16
-// planes before they are written.
+// One thread per (edge, row, hidden-channel quad).  With `gate_max` set it also records the largest
+// sigmoid'(gate) it sees: max|dht| * rows(l) * max|h1| * that value bounds the gate part of the
+// backward's dh1, which fixes the scale of its fp16 planes before they are written (the bound
+// follows the gates into saturation, where a constant 1/4 would be orders of magnitude loose).
 __global__ void gate_fwd_kernel(const __grid_constant__ ZpTables t, int64_t E,
                                 const float *__restrict__ h1, const ZpPlanes ht,
                                 float *gate_max) {
   const int H4 = t.H / 4;
   const int64_t idx0 = (int64_t)blockIdx.x * blockDim.x + threadIdx.x;
-  const bool in_range = idx0 < E * H4;
+  const int64_t total = E * t.Km * H4;
+  const bool in_range = idx0 < total;
   const int64_t idx = in_range ? idx0 : 0;        // out-of-range threads recompute item 0
   const int h = (int)(idx % H4) * 4;
-  const int64_t e = idx / H4;
+  const int r = (int)((idx / H4) % t.Km);
+  const int64_t e = idx / ((int64_t)H4 * t.Km);
   const float *row = h1 + (size_t)e * t.w1_cols;
-  const float inv = zp_inv_scale(ht);
-  float sg[ZP_MAX_L][4], mag[ZP_MAX_L][4];
-#pragma unroll
-  for (int l = 0; l < ZP_MAX_L; ++l) {
-    if (l < t.lmax) {
-      const float4 g = *reinterpret_cast<const float4 *>(row + l * t.H + h);
-      sg[l][0] = sigmoidf(g.x); sg[l][1] = sigmoidf(g.y);
-      sg[l][2] = sigmoidf(g.z); sg[l][3] = sigmoidf(g.w);
-    }
-#pragma unroll
-    for (int v = 0; v < 4; ++v) mag[l][v] = 0.f;
+  const float4 x = *reinterpret_cast<const float4 *>(row + t.n_gate + r * t.H + h);
+  float o[4], seen = 0.f;
+  // every gate l is used by the m = 0 row r = l: those rows alone probe sigmoid'
+  const bool probe = gate_max != nullptr && r >= 1 && r <= t.lmax;
+  if (r == 0) {
+    o[0] = x.x * sigmoidf(x.x); o[1] = x.y * sigmoidf(x.y);
+    o[2] = x.z * sigmoidf(x.z); o[3] = x.w * sigmoidf(x.w);
+  } else {
+    const float4 g = *reinterpret_cast<const float4 *>(row + (t.row_l[r] - 1) * t.H + h);
+    const float s0 = sigmoidf(g.x), s1 = sigmoidf(g.y), s2 = sigmoidf(g.z), s3 = sigmoidf(g.w);
+    o[0] = x.x * s0; o[1] = x.y * s1; o[2] = x.z * s2; o[3] = x.w * s3;
+    if (probe)
+      seen = fmaxf(fmaxf(s0 * (1.f - s0), s1 * (1.f - s1)), fmaxf(s2 * (1.f - s2), s3 * (1.f - s3)));
   }
-  for (int r = 0; r < t.Km; ++r) {
-    const float4 x4 = *reinterpret_cast<const float4 *>(row + t.n_gate + r * t.H + h);
-    const float x[4] = {x4.x, x4.y, x4.z, x4.w};
-    float o[4];
-    if (r == 0) {
+  if (in_range) zp_store_planes<4>(ht, e * ht.ld + (int64_t)r * t.H + h, o, zp_inv_scale(ht));
+  if (__any_sync(0xffffffffu, probe)) {
 #pragma unroll
-      for (int v = 0; v < 4; ++v) o[v] = x[v] * sigmoidf(x[v]);
-    } else {
-      const int l = t.row_l[r] - 1;
-#pragma unroll
-      for (int ll = 0; ll < ZP_MAX_L; ++ll) {
-        if (ll == l) {
-#pragma unroll
-          for (int v = 0; v < 4; ++v) {
-            o[v] = x[v] * sg[ll][v];
-            mag[ll][v] += fabsf(x[v]);
-          }
-        }
-      }
-    }
-    if (in_range) zp_store_planes<4>(ht, e * ht.ld + (int64_t)r * t.H + h, o, inv);
-  }
-  if (gate_max) {
-    float seen = 0.f;
-#pragma unroll
-    for (int l = 0; l < ZP_MAX_L; ++l)
-      if (l < t.lmax) {
-#pragma unroll
-        for (int v = 0; v < 4; ++v)
-          seen = fmaxf(seen, sg[l][v] * (1.f - sg[l][v]) * mag[l][v]);
-      }
-#pragma unroll
-    for (int o = 16; o > 0; o >>= 1) seen = fmaxf(seen, __shfl_xor_sync(0xffffffffu, seen, o));
-    if ((threadIdx.x & 31) == 0 && seen > 0.f) zp_atomic_absmax(gate_max, seen);
+    for (int k = 16; k > 0; k >>= 1) seen = fmaxf(seen, __shfl_xor_sync(0xffffffffu, seen, k));
+    // one address for the whole grid: only warps that would raise the maximum touch it atomically
+    if ((threadIdx.x & 31) == 0 && seen > *reinterpret_cast<volatile float *>(gate_max))
+      zp_atomic_absmax(gate_max, seen);
   }
 }
 
 // one thread per (edge, hidden-channel quad): walks the Km rows, accumulates the lmax gate grads.
 // The scale of the fp16 planes is fixed beforehand from max |dht| and the forward's gate bound:
 //   |dh1 row| <= 1.1 max|dht|  (sigmoid <= 1, silu' <= 1.1),
-//   |dh1 gate_l| = sigmoid'(g_l) |sum_rows dht h1| <= max|dht| * sigmoid'(g_l) sum_rows |h1|.
+//   |dh1 gate_l| = sigmoid'(g_l) |sum_rows dht h1| <= max|dht| * rows(l) * max|h1| * max sigmoid'.
 __global__ void gate_bwd_kernel(const __grid_constant__ ZpTables t, int64_t E,
                                 const float *__restrict__ h1, const float *__restrict__ dht,
                                 const ZpPlanes dh1) {
@@ -350,8 +328,8 @@ int zp_launch_absmax(int64_t rows, int64_t cols, const float *in, int64_t ld, fl
 }
 
 int zp_launch_scale(float factor, const float *a, const float *b, const float *c, float offset_c,
-                    float *scale, cudaStream_t st) {
-  scale_kernel<<<1, 1, 0, st>>>(factor, a, b, c, offset_c, scale);
+                    float *scale, cudaStream_t st, const float *d, float c_factor) {
+  scale_kernel<<<1, 1, 0, st>>>(factor, a, b, c, d, c_factor, offset_c, scale);
   ZP_LAUNCH_CHECK("scale_kernel");
   return ZP_OK;
 }
@@ -360,8 +338,8 @@ int zp_launch_gate_fwd(const zp_plan *p, int64_t E, const float *h1, const ZpPla
                        float *gate_max, cudaStream_t st) {
   if (gate_max) ZP_CUDA(cudaMemsetAsync(gate_max, 0, sizeof(float), st));
   if (E == 0) return ZP_OK;
-  const int64_t total = E * (p->t.H / 4);
-  gate_fwd_kernel<<<(unsigned)zp_ceil_div(total, 128), 128, 0, st>>>(p->t, E, h1, ht, gate_max);
+  const int64_t total = E * p->t.Km * (p->t.H / 4);
+  gate_fwd_kernel<<<(unsigned)zp_ceil_div(total, 256), 256, 0, st>>>(p->t, E, h1, ht, gate_max);
   ZP_LAUNCH_CHECK("gate_fwd_kernel");
   return ZP_OK;
 }

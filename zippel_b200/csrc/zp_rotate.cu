@@ -13,6 +13,8 @@
 // |m| <= mmax.  Channels are the fastest axis everywhere: a thread owns VEC consecutive
 // channels and moves them with one vector load/store.  No atomics: every output element is
 // produced by exactly one thread, in an order fixed by the CSR offsets.
+#include <algorithm>
+
 #include "zp_common.cuh"
 #include "zp_planes.cuh"
 
@@ -131,10 +133,11 @@ __device__ __forceinline__ void stage_rot(const ZpTables &t, const float *rot_e,
 
 template <int L, int LMAX, int VEC>
 struct RotBack {
-  static __device__ __forceinline__ void run(const ZpTables &t, const float *y_e,
+  // y_e: the edge's rows [Km][row_stride], this lane's channels start at c
+  static __device__ __forceinline__ void run(const ZpTables &t, const float *y_e, int row_stride,
                                              const float *rot_s, float env,
                                              float (&acc)[(LMAX + 1) * (LMAX + 1)][VEC], int c) {
-    RotBack<L - 1, LMAX, VEC>::run(t, y_e, rot_s, env, acc, c);
+    RotBack<L - 1, LMAX, VEC>::run(t, y_e, row_stride, rot_s, env, acc, c);
     constexpr int n = 2 * L + 1;
     const int mm = t.mmax < L ? t.mmax : L;
 #pragma unroll
@@ -144,7 +147,7 @@ struct RotBack {
         const int r = t.row_of[L][i];
         const float *rr = rot_s + t.rot_off[r];
         float yv[VEC];
-        vload<VEC>(yv, y_e + (size_t)r * t.C + c);
+        vload<VEC>(yv, y_e + (size_t)r * row_stride + c);
 #pragma unroll
         for (int v = 0; v < VEC; ++v) yv[v] *= env;
 #pragma unroll
@@ -159,16 +162,34 @@ struct RotBack {
 };
 template <int LMAX, int VEC>
 struct RotBack<-1, LMAX, VEC> {
-  static __device__ __forceinline__ void run(const ZpTables &, const float *, const float *,
+  static __device__ __forceinline__ void run(const ZpTables &, const float *, int, const float *,
                                              float, float (&)[(LMAX + 1) * (LMAX + 1)][VEC],
                                              int) {}
 };
 
 // One block (four warps) owns 32 x VEC channels of one destination node.  The node's edges are
 // dealt round-robin to the warps (warp w takes edges w, w + 4, ... of the CSR segment), which cuts
-// the serial load->rotate chain per node by four; the four partial sums are then added in warp
-// order through shared memory, so the result does not depend on timing.
+// the serial chain per node by four; the four partial sums are then added in warp order through
+// shared memory, so the result does not depend on timing.
+// Each warp keeps the rows of its NEXT edge in flight while it rotates the current one: every lane
+// copies its own channels of the Km rows into a two-stage shared buffer with cp.async (16 or 8
+// bytes per row), so the memory latency is paid once per edge, not once per row.
 constexpr int kBackWarps = 4;
+
+template <int BYTES>
+__device__ __forceinline__ void cp_async(float *smem_dst, const float *gmem_src) {
+  const uint32_t d = (uint32_t)__cvta_generic_to_shared(smem_dst);
+  if (BYTES == 16)
+    asm volatile("cp.async.cg.shared.global [%0], [%1], 16;" ::"r"(d), "l"(gmem_src) : "memory");
+  else
+    asm volatile("cp.async.ca.shared.global [%0], [%1], 8;" ::"r"(d), "l"(gmem_src) : "memory");
+}
+__device__ __forceinline__ void cp_async_commit() { asm volatile("cp.async.commit_group;" ::: "memory"); }
+template <int N>
+__device__ __forceinline__ void cp_async_wait() {
+  asm volatile("cp.async.wait_group %0;" ::"n"(N) : "memory");
+}
+
 template <int LMAX, int VEC>
 __global__ void __launch_bounds__(32 * kBackWarps)
 rotate_back_scatter_kernel(const __grid_constant__ ZpTables t, int64_t N,
@@ -176,12 +197,16 @@ rotate_back_scatter_kernel(const __grid_constant__ ZpTables t, int64_t N,
                            const float *__restrict__ rot, const int32_t *__restrict__ row_ptr,
                            float *__restrict__ node_out) {
   constexpr int K = (LMAX + 1) * (LMAX + 1);
-  extern __shared__ float smem[];          // rot [4][nnz_pad] | partial [4][K][32 * VEC]
+  constexpr int W = 32 * VEC;              // channels of this block
+  // rot [4][nnz_pad] | y stages [4 warps][2][Km][W], reused as partial [4][K][W] at the end
+  extern __shared__ __align__(16) float smem[];
   const int warp = threadIdx.x / 32, lane = threadIdx.x % 32;
   float *rot_s = smem + warp * t.nnz_pad;
-  float *part = smem + kBackWarps * t.nnz_pad;
+  float *region = smem + kBackWarps * t.nnz_pad;
+  float *ybuf = region + (size_t)warp * 2 * t.Km * W;
+  float *part = region;
   const int64_t n = blockIdx.x;
-  const int c0 = blockIdx.y * 32 * VEC;
+  const int c0 = blockIdx.y * W;
   const int c = c0 + lane * VEC;
   const bool active = c < t.C;
   float acc[K][VEC];
@@ -191,9 +216,7 @@ rotate_back_scatter_kernel(const __grid_constant__ ZpTables t, int64_t N,
     for (int v = 0; v < VEC; ++v) acc[k][v] = 0.f;
   const int e_beg = row_ptr[n], e_end = row_ptr[n + 1];
   // the next edge's packed rotation is fetched into registers while the current one is used
-  constexpr int kRotRegs = (ZP_MAX_KM * ZP_MAX_N + 31) / 32;     // generous upper bound, unrolled
   float nxt[8];
-  static_assert(kRotRegs >= 1, "");
   auto fetch = [&](int e) {
 #pragma unroll
     for (int i = 0; i < 8; ++i) {
@@ -201,19 +224,33 @@ rotate_back_scatter_kernel(const __grid_constant__ ZpTables t, int64_t N,
       nxt[i] = (e < e_end && k < t.nnz_pad) ? rot[(size_t)e * t.nnz_pad + k] : 0.f;
     }
   };
+  auto stage_rows = [&](int e, int stage) {          // this lane's channels of edge e's Km rows
+    if (e < e_end && active) {
+      const float *src = y + (size_t)e * t.Km * t.C + c;
+      float *dst = ybuf + (size_t)stage * t.Km * W + lane * VEC;
+      for (int r = 0; r < t.Km; ++r) cp_async<4 * VEC>(dst + r * W, src + (size_t)r * t.C);
+    }
+    cp_async_commit();
+  };
   fetch(e_beg + warp);
-  for (int e = e_beg + warp; e < e_end; e += kBackWarps) {
+  stage_rows(e_beg + warp, 0);
+  int stage = 0;
+  for (int e = e_beg + warp; e < e_end; e += kBackWarps, stage ^= 1) {
     __syncwarp();
 #pragma unroll
     for (int i = 0; i < 8; ++i)
       if (lane + 32 * i < t.nnz_pad) rot_s[lane + 32 * i] = nxt[i];
     const float env_e = env[e];
     fetch(e + kBackWarps);
+    stage_rows(e + kBackWarps, stage ^ 1);
+    cp_async_wait<1>();                  // everything but the group just committed has landed
     __syncwarp();
     if (active)
-      RotBack<LMAX, LMAX, VEC>::run(t, y + (size_t)e * t.Km * t.C, rot_s, env_e, acc, c);
+      RotBack<LMAX, LMAX, VEC>::run(t, ybuf + (size_t)stage * t.Km * W, W, rot_s, env_e, acc,
+                                    lane * VEC);
   }
-  constexpr int W = 32 * VEC;              // channels of this block
+  cp_async_wait<0>();
+  __syncthreads();                       // all warps are done with their stages: reuse as partials
 #pragma unroll
   for (int k = 0; k < K; ++k)
 #pragma unroll
@@ -231,9 +268,10 @@ rotate_back_scatter_kernel(const __grid_constant__ ZpTables t, int64_t N,
 }
 
 // ------------------------------------------------------------------------------------------
-// per-edge backward kernels: blockDim = 256; W warps cover one edge's channel groups, 8 / W
-// edges per block.  Channel reductions (the 2l+1 rotation-gradient entries of a row) are done
-// as batches of independent warp sums so the shuffles pipeline.
+// per-edge backward kernels: W warps cover one edge's channel groups.  rotate_grad_out runs eight
+// warps per block and loads rows as it goes; rotate_in_bwd runs four warps per block and first puts
+// every row it will read in flight with cp.async (one commit group per degree).  Channel
+// reductions (the 2l+1 rotation-gradient entries of a row) use a halving exchange.
 // ------------------------------------------------------------------------------------------
 constexpr int kEdgeThreads = 256;
 
@@ -395,14 +433,16 @@ rotate_grad_out_kernel(const __grid_constant__ ZpTables t, int64_t E, int W,
 //   grad_rot[e, r, j] += sum_c2 ga[r, c2] u[l^2 + j, c2]
 template <int L, int LMAX>
 struct RotInBwdE {
+  // stage: this warp's [Km + radial rows][128] buffer, filled by StageInBwd in level order
   static __device__ __forceinline__ void run(const ZpTables &t, const float *xrow,
-                                             const float *da_e, const float *rad_e,
-                                             float *grad_e, const float *rot_s, float *part_s,
-                                             float *du_row, int c2, bool active, int lane) {
-    RotInBwdE<L - 1, LMAX>::run(t, xrow, da_e, rad_e, grad_e, rot_s, part_s, du_row, c2, active, lane);
+                                             const float *stage, float *grad_e,
+                                             const float *rot_s, float *part_s, float *du_row,
+                                             int c2, bool active, int lane) {
+    RotInBwdE<L - 1, LMAX>::run(t, xrow, stage, grad_e, rot_s, part_s, du_row, c2, active, lane);
     constexpr int n = 2 * L + 1;
     const int C2 = 2 * t.C;
     const int mm = t.mmax < L ? t.mmax : L;
+    cp_async_wait<LMAX - L>();             // the rows of levels 0..L have landed
     float u[n][4], du[n][4];
 #pragma unroll
     for (int j = 0; j < n; ++j) {
@@ -415,7 +455,7 @@ struct RotInBwdE {
       if (am <= mm) {
         float gr[4] = {0.f, 0.f, 0.f, 0.f}, rad[4] = {0.f, 0.f, 0.f, 0.f};
         const int col = t.rad_off[am] + (L - am) * C2 + c2;
-        if (active) vload<4>(rad, rad_e + col);
+        if (active) vload<4>(rad, stage + (size_t)(t.Km + t.rad_off[am] / C2 + (L - am)) * 128 + lane * 4);
 #pragma unroll
         for (int sgn = 0; sgn < 2; ++sgn) {
           if (sgn == 1 && am == 0) continue;
@@ -423,7 +463,7 @@ struct RotInBwdE {
           const int r = t.row_of[L][i];
           const float *rr = rot_s + t.rot_off[r];
           float a[4] = {0.f, 0.f, 0.f, 0.f}, da[4] = {0.f, 0.f, 0.f, 0.f}, ga[4], part[n];
-          if (active) vload<4>(da, da_e + (size_t)r * C2 + c2);
+          if (active) vload<4>(da, stage + (size_t)r * 128 + lane * 4);
 #pragma unroll
           for (int j = 0; j < n; ++j)
 #pragma unroll
@@ -459,43 +499,87 @@ struct RotInBwdE {
 template <int LMAX>
 struct RotInBwdE<-1, LMAX> {
   static __device__ __forceinline__ void run(const ZpTables &, const float *, const float *,
-                                             const float *, float *, const float *, float *,
-                                             float *, int, bool, int) {}
+                                             float *, const float *, float *, float *, int, bool,
+                                             int) {}
 };
 
-// du_both [E][2][K][C]: half 0 = contribution to the source node, half 1 = to the destination
+// Puts every row the edge needs in flight at once: each lane copies its own four channels of the
+// Km gradient rows and of the radial rows into the warp's shared buffer with cp.async, one commit
+// group per degree, so RotInBwdE waits once per degree instead of once per row.
+template <int L, int LMAX>
+struct StageInBwd {
+  static __device__ __forceinline__ void run(const ZpTables &t, const float *da_e,
+                                             const float *rad_e, float *stage, int c2, int lane,
+                                             bool active) {
+    StageInBwd<L - 1, LMAX>::run(t, da_e, rad_e, stage, c2, lane, active);
+    constexpr int n = 2 * L + 1;
+    const int C2 = 2 * t.C;
+    const int mm = t.mmax < L ? t.mmax : L;
+    if (active) {
+#pragma unroll
+      for (int i = 0; i < n; ++i) {
+        const int am = i > L ? i - L : L - i;
+        if (am <= mm) {
+          const int r = t.row_of[L][i];
+          cp_async<16>(stage + (size_t)r * 128 + lane * 4, da_e + (size_t)r * C2 + c2);
+        }
+      }
+#pragma unroll
+      for (int am = 0; am <= L; ++am)
+        if (am <= mm)
+          cp_async<16>(stage + (size_t)(t.Km + t.rad_off[am] / C2 + (L - am)) * 128 + lane * 4,
+                       rad_e + t.rad_off[am] + (L - am) * C2 + c2);
+    }
+    cp_async_commit();
+  }
+};
 template <int LMAX>
-__global__ void __launch_bounds__(kEdgeThreads, (LMAX <= 4 ? 2 : 1))
+struct StageInBwd<-1, LMAX> {
+  static __device__ __forceinline__ void run(const ZpTables &, const float *, const float *, float *,
+                                             int, int, bool) {}
+};
+
+// du_both [E][2][K][C]: half 0 = contribution to the source node, half 1 = to the destination.
+// Blocks of `nw` warps, W warps per edge; shared memory: rot [nw / W][nnz_pad] |
+// partial [nw][nnz_pad] | stage [nw][Km + R / 2C][128].
+template <int LMAX>
+__global__ void __launch_bounds__(128, (LMAX <= 4 ? 3 : 2))
 rotate_in_bwd_kernel(const __grid_constant__ ZpTables t, int64_t E, int W,
                      const float *__restrict__ da1, const float *__restrict__ radial,
                      const float *__restrict__ x, const int32_t *__restrict__ src,
                      const int32_t *__restrict__ dst, const float *__restrict__ rot,
                      float *__restrict__ grad_radial, float *__restrict__ du_both,
                      float *__restrict__ grad_rot) {
-  extern __shared__ float smem[];
-  const int epb = 8 / W;
+  extern __shared__ __align__(16) float smem[];
+  const int nw = blockDim.x / 32;
+  const int epb = nw / W;
+  const int stage_rows = t.Km + t.R / (2 * t.C);
   float *rot_s = smem;
   float *part_all = smem + epb * t.nnz_pad;
   const int warp = threadIdx.x / 32, lane = threadIdx.x % 32;
+  float *stage = part_all + nw * t.nnz_pad + (size_t)warp * stage_rows * 128;
   const int slot = warp / W, wsub = warp % W;
   const int64_t e0 = (int64_t)blockIdx.x * epb;
   const int n_e = (int)min((int64_t)epb, E - e0);
-  for (int i = threadIdx.x; i < n_e * t.nnz_pad; i += blockDim.x) rot_s[i] = rot[e0 * t.nnz_pad + i];
-  __syncthreads();
   const bool edge_ok = slot < n_e;
   const int64_t e = e0 + (edge_ok ? slot : 0);
   const int c2 = (wsub * 32 + lane) * 4;
   const bool active = edge_ok && c2 < 2 * t.C;
+  StageInBwd<LMAX, LMAX>::run(t, da1 + (size_t)e * t.Km * 2 * t.C, radial + (size_t)e * t.R, stage,
+                              c2, lane, active);
+  for (int i = threadIdx.x; i < n_e * t.nnz_pad; i += blockDim.x) rot_s[i] = rot[e0 * t.nnz_pad + i];
+  __syncthreads();
   if (edge_ok) {
     const int half = c2 >= t.C ? 1 : 0;
     const int c = c2 - half * t.C;
     const int64_t node = half ? dst[e] : src[e];
     const float *xrow = x + (size_t)node * t.K * t.C + c;
     float *du_row = du_both + ((size_t)e * 2 + half) * t.K * t.C + c;
-    RotInBwdE<LMAX, LMAX>::run(t, xrow, da1 + (size_t)e * t.Km * 2 * t.C, radial + (size_t)e * t.R,
-                               grad_radial + (size_t)e * t.R, rot_s + slot * t.nnz_pad,
-                               part_all + warp * t.nnz_pad, du_row, c2, active, lane);
+    RotInBwdE<LMAX, LMAX>::run(t, xrow, stage, grad_radial + (size_t)e * t.R,
+                               rot_s + slot * t.nnz_pad, part_all + warp * t.nnz_pad, du_row, c2,
+                               active, lane);
   }
+  cp_async_wait<0>();
   __syncthreads();
   for (int i = threadIdx.x; i < n_e * t.nnz_pad; i += blockDim.x) {
     const int s = i / t.nnz_pad, k = i % t.nnz_pad;
@@ -558,7 +642,8 @@ int zp_launch_rotate_back_scatter(const zp_plan *p, int64_t N, const float *y, c
   const ZpTables &t = p->t;
   const int vec = t.lmax <= 4 ? 4 : 2;     // K x VEC accumulators must fit in registers
   const dim3 grid((unsigned)N, (unsigned)zp_ceil_div(t.C, 32 * vec));
-  const size_t smem = (size_t)kBackWarps * (t.nnz_pad + (size_t)t.K * 32 * vec) * sizeof(float);
+  const size_t rows = std::max<size_t>((size_t)t.K, 2 * (size_t)t.Km);   // partials | two y stages
+  const size_t smem = (size_t)kBackWarps * (t.nnz_pad + rows * 32 * vec) * sizeof(float);
 #define CALL(LM)                                                                               \
   {                                                                                            \
     auto kern = vec == 4 ? rotate_back_scatter_kernel<LM, 4> : rotate_back_scatter_kernel<LM, 2>; \
@@ -609,12 +694,22 @@ int zp_launch_rotate_in_bwd(const zp_plan *p, int64_t E, const float *da1, const
   const ZpTables &t = p->t;
   const int W = warps_per_edge(t.C / 2);
   if (!W) return ZP_ERR_UNSUPPORTED;
-  const int epb = 8 / W;
+  const int nw = 4;                          // warps per block
+  const int epb = nw / W;
   const dim3 grid((unsigned)zp_ceil_div(E, epb));
-  const size_t smem = (size_t)(epb + 8) * t.nnz_pad * sizeof(float);
+  const size_t stage_rows = (size_t)t.Km + (size_t)t.R / (2 * t.C);
+  const size_t smem = ((size_t)(epb + nw) * t.nnz_pad + (size_t)nw * stage_rows * 128) * sizeof(float);
 #define CALL(LM)                                                                               \
-  rotate_in_bwd_kernel<LM><<<grid, kEdgeThreads, smem, st>>>(t, E, W, da1, radial, x, src, dst, \
-                                                             rot, grad_radial, du_both, grad_rot)
+  {                                                                                            \
+    static size_t allowed = 48 * 1024;       /* per instantiation: raise the limit once */       \
+    if (smem > allowed) {                                                                      \
+      ZP_CUDA(cudaFuncSetAttribute(rotate_in_bwd_kernel<LM>,                                   \
+                                   cudaFuncAttributeMaxDynamicSharedMemorySize, (int)smem));   \
+      allowed = smem;                                                                          \
+    }                                                                                          \
+    rotate_in_bwd_kernel<LM><<<grid, 32 * nw, smem, st>>>(t, E, W, da1, radial, x, src, dst,   \
+                                                          rot, grad_radial, du_both, grad_rot); \
+  }
   ZP_DISPATCH_LMAX(t.lmax, CALL)
 #undef CALL
   ZP_LAUNCH_CHECK("rotate_in_bwd_kernel");

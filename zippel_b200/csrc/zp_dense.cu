@@ -201,41 +201,61 @@ __global__ void weight_scale_kernel(const FoldDesc d, float *scales) {
 
 // fold: writes W_fold [out, in] and its transpose [in, out] as 16-bit planes.
 //   m = 0 (folded == 0): W_fold = W.   m > 0: W = [Wa ; Wb] (rows), W_fold = [Wa -Wb ; Wb Wa].
-__global__ void fold_planes_kernel(const FoldDesc d, uint16_t *__restrict__ packed, int planes,
-                                   int fp16, const float *__restrict__ scales) {
+__global__ void __launch_bounds__(256)
+fold_planes_kernel(const FoldDesc d, uint16_t *__restrict__ packed, int planes, int fp16,
+                   const float *__restrict__ scales) {
+  // 32 x 32 tiles: the planes of W_fold go out row-major as they are formed; the transpose is
+  // written from a shared copy of the tile so that both stores run along the fastest axis.
+  __shared__ uint16_t tile[3][32][34];
   const int b = blockIdx.y;
   const int out = d.out[b], in = d.in[b];
   const int64_t total = (int64_t)out * in;
   uint16_t *wp = packed + d.woff[b], *wtp = wp + (size_t)planes * total;
   const float inv = fp16 ? 1.f / scales[2 * d.slot[b] + 1] : 1.f;
-  for (int64_t idx = (int64_t)blockIdx.x * blockDim.x + threadIdx.x; idx < total;
-       idx += (int64_t)gridDim.x * blockDim.x) {
-    const int col = (int)(idx % in), row = (int)(idx / in);
-    float v;
-    if (!d.folded[b]) {
-      v = d.w[b][idx];
-    } else {
-      const int half = out / 2, kin = in / 2;
-      const bool lower = row >= half, right = col >= kin;
-      const int o = lower ? row - half : row, c = right ? col - kin : col;
-      v = d.w[b][(size_t)((lower != right) ? half + o : o) * kin + c];
-      if (!lower && right) v = -v;
-    }
-    v *= inv;
-    for (int p = 0; p < planes; ++p) {
-      uint16_t h;
-      if (fp16) {
-        const __half q = __float2half_rn(v);
-        h = __half_as_ushort(q);
-        v -= __half2float(q);
-      } else {
-        const __nv_bfloat16 q = __float2bfloat16_rn(v);
-        h = __bfloat16_as_ushort(q);
-        v -= __bfloat162float(q);
+  const int tx = threadIdx.x & 31, ty = threadIdx.x >> 5;          // 32 x 8
+  const int tiles_c = (in + 31) / 32, tiles = ((out + 31) / 32) * tiles_c;
+  for (int tl = blockIdx.x; tl < tiles; tl += gridDim.x) {
+    const int r0 = (tl / tiles_c) * 32, c0 = (tl % tiles_c) * 32;
+#pragma unroll
+    for (int k = 0; k < 4; ++k) {
+      const int row = r0 + ty + 8 * k, col = c0 + tx;
+      if (row < out && col < in) {
+        float v;
+        if (!d.folded[b]) {
+          v = d.w[b][(size_t)row * in + col];
+        } else {
+          const int half = out / 2, kin = in / 2;
+          const bool lower = row >= half, right = col >= kin;
+          const int o = lower ? row - half : row, c = right ? col - kin : col;
+          v = d.w[b][(size_t)((lower != right) ? half + o : o) * kin + c];
+          if (!lower && right) v = -v;
+        }
+        v *= inv;
+        for (int p = 0; p < planes; ++p) {
+          uint16_t h;
+          if (fp16) {
+            const __half q = __float2half_rn(v);
+            h = __half_as_ushort(q);
+            v -= __half2float(q);
+          } else {
+            const __nv_bfloat16 q = __float2bfloat16_rn(v);
+            h = __bfloat16_as_ushort(q);
+            v -= __bfloat162float(q);
+          }
+          wp[(size_t)p * total + (size_t)row * in + col] = h;
+          tile[p][ty + 8 * k][tx] = h;
+        }
       }
-      wp[(size_t)p * total + idx] = h;
-      wtp[(size_t)p * total + (size_t)col * out + row] = h;
     }
+    __syncthreads();
+#pragma unroll
+    for (int k = 0; k < 4; ++k) {
+      const int col = c0 + ty + 8 * k, row = r0 + tx;
+      if (row < out && col < in)
+        for (int p = 0; p < planes; ++p)
+          wtp[(size_t)p * total + (size_t)col * out + row] = tile[p][tx][ty + 8 * k];
+    }
+    __syncthreads();
   }
 }
 
@@ -379,7 +399,7 @@ int zp_launch_fold_weights(const zp_plan *p, const zp_weights *w, void *packed, 
     weight_scale_kernel<<<1, 32, 0, st>>>(d, scales);
     ZP_LAUNCH_CHECK("weight_scale_kernel");
   }
-  fold_planes_kernel<<<dim3(148, d.n), 256, 0, st>>>(d, static_cast<uint16_t *>(packed), p->planes,
+  fold_planes_kernel<<<dim3(296, d.n), 256, 0, st>>>(d, static_cast<uint16_t *>(packed), p->planes,
                                                      p->fp16, scales);
   ZP_LAUNCH_CHECK("fold_planes_kernel");
   return ZP_OK;

@@ -362,8 +362,9 @@ def run_ours(args) -> dict | None:
     # DRAM bytes per launch: dram__bytes_read.sum + dram__bytes_write.sum of three forward launches
     # captured by ncu on an 18 000-edge case of this configuration (fp32 precision), averaged
     # and scaled by edges (operand and output bytes grow in proportion to the edge count)
-    traffic = 165.2e6 * (e / 18000.0) if args.precision == "fp32" and args.atoms == N_ATOMS else None
-    roof = {"bound": "tensor", "kernel": "gemm_tc_kernel (fwd + dgrad + wgrad launches)",
+    traffic = 172.9e6 * (e / 18000.0) if args.precision == "fp32" and args.atoms == N_ATOMS else None
+    roof = {"bound": "tensor",
+            "kernel": "gemm_tc_pair_kernel / gemm_tc_kernel (fwd + dgrad + wgrad launches)",
             "achieved": ach, "peak": peak, "unit": "TFLOP/s", "frac": ach / peak,
             "traffic": traffic, "share_of_step": gemm_share,
             "peak_source": f"{pk_src} bf16 dense sustained (no fp32/tf32 peak is measured)",

@@ -16,16 +16,26 @@
 
 namespace {
 
-// fp32 matrix -> planes (bf16, or fp16 with the tensor's scale), zero padding up to ld_out
+// fp32 matrix -> planes (bf16, or fp16 with the tensor's scale), zero padding up to ld_out.
+// threadIdx.x walks the quads of a row, threadIdx.y / blockIdx.x the rows (no division anywhere).
 __global__ void split_planes_kernel(int64_t rows, int64_t cols, const float *__restrict__ in,
                                     int64_t ld_in, const ZpPlanes out) {
-  const int64_t idx = (int64_t)blockIdx.x * blockDim.x + threadIdx.x;
-  if (idx >= rows * (out.ld / 2)) return;
-  const int64_t r = idx / (out.ld / 2), c = (idx % (out.ld / 2)) * 2;
-  float v[2];
-  v[0] = c < cols ? in[r * ld_in + c] : 0.f;
-  v[1] = c + 1 < cols ? in[r * ld_in + c + 1] : 0.f;
-  zp_store_planes<2>(out, r * out.ld + c, v, zp_inv_scale(out));
+  const int64_t c = 4 * ((int64_t)blockIdx.y * blockDim.x + threadIdx.x);
+  if (c >= out.ld) return;
+  const bool vec = (ld_in & 3) == 0 && (reinterpret_cast<uintptr_t>(in) & 15) == 0 && c + 3 < cols;
+  const float inv = zp_inv_scale(out);
+  for (int64_t r = (int64_t)blockIdx.x * blockDim.y + threadIdx.y; r < rows;
+       r += (int64_t)gridDim.x * blockDim.y) {
+    float v[4];
+    if (vec) {
+      const float4 q = *reinterpret_cast<const float4 *>(in + r * ld_in + c);
+      v[0] = q.x; v[1] = q.y; v[2] = q.z; v[3] = q.w;
+    } else {
+#pragma unroll
+      for (int k = 0; k < 4; ++k) v[k] = c + k < cols ? in[r * ld_in + c + k] : 0.f;
+    }
+    zp_store_planes<4>(out, r * out.ld + c, v, inv);
+  }
 }
 
 // max |x| over a strided matrix into *out (which the caller zeroed), and the scale derived from
@@ -69,17 +79,21 @@ __device__ __forceinline__ float sigmoidf(float x) { return 1.f / (1.f + __expf(
 // sigmoid'(gate) it sees: max|dht| * rows(l) * max|h1| * that value bounds the gate part of the
 // backward's dh1, which fixes the scale of its fp16 planes before they are written (the bound
 // follows the gates into saturation, where a constant 1/4 would be orders of magnitude loose).
+constexpr int kGateEdges = 8;
 __global__ void gate_fwd_kernel(const __grid_constant__ ZpTables t, int64_t E,
                                 const float *__restrict__ h1, const ZpPlanes ht,
                                 float *gate_max) {
+  // blockIdx.x counts groups of kGateEdges edges; the items of a group are indexed with 32-bit
+  // arithmetic (a 64-bit division per thread would cost more than the rest of the kernel)
   const int H4 = t.H / 4;
-  const int64_t idx0 = (int64_t)blockIdx.x * blockDim.x + threadIdx.x;
-  const int64_t total = E * t.Km * H4;
-  const bool in_range = idx0 < total;
-  const int64_t idx = in_range ? idx0 : 0;        // out-of-range threads recompute item 0
-  const int h = (int)(idx % H4) * 4;
-  const int r = (int)((idx / H4) % t.Km);
-  const int64_t e = idx / ((int64_t)H4 * t.Km);
+  const int per_edge = t.Km * H4;
+  const int item = blockIdx.y * blockDim.x + threadIdx.x;            // within the group
+  const int le = item / per_edge, rem = item - le * per_edge;
+  const int64_t e0 = (int64_t)blockIdx.x * kGateEdges + le;
+  const bool in_range = le < kGateEdges && e0 < E;
+  const int64_t e = in_range ? e0 : 0;            // out-of-range threads recompute edge 0
+  const int r = rem / H4;
+  const int h = (rem - r * H4) * 4;
   const float *row = h1 + (size_t)e * t.w1_cols;
   const float4 x = *reinterpret_cast<const float4 *>(row + t.n_gate + r * t.H + h);
   float o[4], seen = 0.f;
@@ -113,11 +127,12 @@ __global__ void gate_bwd_kernel(const __grid_constant__ ZpTables t, int64_t E,
                                 const float *__restrict__ h1, const float *__restrict__ dht,
                                 const ZpPlanes dh1) {
   const int H4 = t.H / 4;
-  const int64_t idx0 = (int64_t)blockIdx.x * blockDim.x + threadIdx.x;
-  const bool in_range = idx0 < E * H4;
-  const int64_t idx = in_range ? idx0 : 0;        // out-of-range threads recompute item 0
-  const int h = (int)(idx % H4) * 4;
-  const int64_t e = idx / H4;
+  const int item = blockIdx.y * blockDim.x + threadIdx.x;            // within a group of edges
+  const int le = item / H4;
+  const int64_t e0 = (int64_t)blockIdx.x * kGateEdges + le;
+  const bool in_range = le < kGateEdges && e0 < E;
+  const int64_t e = in_range ? e0 : 0;            // out-of-range threads recompute edge 0
+  const int h = (item - le * H4) * 4;
   const float *row = h1 + (size_t)e * t.w1_cols;
   const int64_t drow = e * dh1.ld;
   const float inv = zp_inv_scale(dh1);
@@ -133,6 +148,7 @@ __global__ void gate_bwd_kernel(const __grid_constant__ ZpTables t, int64_t E,
 #pragma unroll
     for (int v = 0; v < 4; ++v) dg[l][v] = 0.f;
   }
+#pragma unroll 4
   for (int r = 0; r < t.Km; ++r) {
     const float4 x4 = *reinterpret_cast<const float4 *>(row + t.n_gate + r * t.H + h);
     const float4 d4 = *reinterpret_cast<const float4 *>(dt + r * t.H + h);
@@ -330,8 +346,14 @@ __global__ void colsum_final_kernel(int64_t nparts, int64_t cols, const float *_
 int zp_launch_split_planes(int64_t rows, int64_t cols, const float *in, int64_t ld_in,
                            const ZpPlanes &out, cudaStream_t st) {
   if (rows == 0 || out.ld == 0) return ZP_OK;
-  split_planes_kernel<<<(unsigned)zp_ceil_div(rows * (out.ld / 2), 256), 256, 0, st>>>(
-      rows, cols, in, ld_in, out);
+  const int quads = (int)(out.ld / 4);
+  int bx = 32;
+  while (bx < quads && bx < 256) bx <<= 1;
+  const int by = 256 / bx;
+  int64_t gx = zp_ceil_div(rows, by);
+  if (gx > 148 * 32) gx = 148 * 32;
+  const dim3 grid((unsigned)gx, (unsigned)zp_ceil_div(quads, bx)), block(bx, by);
+  split_planes_kernel<<<grid, block, 0, st>>>(rows, cols, in, ld_in, out);
   ZP_LAUNCH_CHECK("split_planes_kernel");
   return ZP_OK;
 }
@@ -358,8 +380,9 @@ int zp_launch_gate_fwd(const zp_plan *p, int64_t E, const float *h1, const ZpPla
                        float *gate_max, cudaStream_t st) {
   if (gate_max) ZP_CUDA(cudaMemsetAsync(gate_max, 0, sizeof(float), st));
   if (E == 0) return ZP_OK;
-  const int64_t total = E * p->t.Km * (p->t.H / 4);
-  gate_fwd_kernel<<<(unsigned)zp_ceil_div(total, 256), 256, 0, st>>>(p->t, E, h1, ht, gate_max);
+  const int per_group = kGateEdges * p->t.Km * (p->t.H / 4);
+  const dim3 grid((unsigned)zp_ceil_div(E, kGateEdges), (unsigned)zp_ceil_div(per_group, 256));
+  gate_fwd_kernel<<<grid, 256, 0, st>>>(p->t, E, h1, ht, gate_max);
   ZP_LAUNCH_CHECK("gate_fwd_kernel");
   return ZP_OK;
 }
@@ -367,8 +390,9 @@ int zp_launch_gate_fwd(const zp_plan *p, int64_t E, const float *h1, const ZpPla
 int zp_launch_gate_bwd(const zp_plan *p, int64_t E, const float *h1, const float *dht,
                        const ZpPlanes &dh1, cudaStream_t st) {
   if (E == 0) return ZP_OK;
-  const int64_t total = E * (p->t.H / 4);
-  gate_bwd_kernel<<<(unsigned)zp_ceil_div(total, 128), 128, 0, st>>>(p->t, E, h1, dht, dh1);
+  const int per_group = kGateEdges * (p->t.H / 4);
+  const dim3 grid((unsigned)zp_ceil_div(E, kGateEdges), (unsigned)zp_ceil_div(per_group, 128));
+  gate_bwd_kernel<<<grid, 128, 0, st>>>(p->t, E, h1, dht, dh1);
   ZP_LAUNCH_CHECK("gate_bwd_kernel");
   return ZP_OK;
 }

@@ -437,7 +437,7 @@ def run_ours(args) -> dict | None:
 
 
 # ------------------------------------------------------------------------------------------
-# the larger BASELINE configurations (not the headline line): batched structures, single graph
+# the larger benchmark configurations (not the headline line): batched structures, single graph
 # ------------------------------------------------------------------------------------------
 
 def run_large(args) -> dict | None:
@@ -624,7 +624,7 @@ def main() -> None:
                     choices=["si_small", "si_medium", "si_large", "cu_small", "cu_medium", "cu_large"],
                     help="with --workload fixture: which of the reference's structures")
     ap.add_argument("--workload", default="cfg2", choices=["cfg2", "cfg3", "cfg4", "fixture"],
-                    help="cfg2 = the benchmark line; cfg3 / cfg4 = the larger BASELINE configurations")
+                    help="cfg2 = the benchmark line; cfg3 / cfg4 = the larger configurations")
     ap.add_argument("--structures", type=int, default=512, help="cfg3: number of 200-atom structures")
     ap.add_argument("--atoms", type=int, default=N_ATOMS,
                     help="atoms per GPU; anything but the default is a profiling-size run, "

@@ -230,6 +230,40 @@ int zp_layernorm_silu_backward(int64_t rows, int width, const float *x, const fl
                                const float *dy, float *dx, float *dgamma, float *dbeta,
                                void *work, size_t work_bytes, void *stream);
 
+/* Per-edge front end of the block in one pass, and its VJP: geometry (eso2_ref.py:320-321),
+ * Gaussian distance basis (:164-168, 323), element embeddings of both atoms (:324-326), envelope
+ * (:242-246, 343), and the copy of the roll-angle harmonics into the sorted edge order.  Inputs are
+ * in the caller's edge order; `perm`, `src`, `dst`, `row_ptr`, `perm_src`, `row_ptr_src` come from
+ * zp_csr_build; outputs are in the sorted order.  x_edge [E, num_basis + 2 edge_channels] is the
+ * input of the radial MLP.  The backward takes the gradients of edge_vec (from
+ * zp_eso2_backward), x_edge and env (any may be null = zero) and returns grad_pos [N,3] and
+ * grad_emb [n_elements, edge_channels] (may be null), both summed in a fixed order.
+ * edge_channels must be a multiple of 4.  `work`: zp_edge_features_work_bytes() bytes.          */
+typedef struct zp_front_config {
+  int32_t lmax;
+  int32_t num_basis;
+  int32_t edge_channels;
+  int32_t n_elements;          /* rows of the embedding table                                  */
+  int32_t envelope_exponent;   /* p of the polynomial envelope                                 */
+  float cutoff;
+  float gauss_coeff;           /* -0.5 / spacing^2 of the Gaussian basis                       */
+} zp_front_config;
+size_t zp_edge_features_work_bytes(const zp_front_config *cfg, int64_t n_nodes, int64_t n_edges);
+int zp_edge_features_forward(const zp_front_config *cfg, int64_t n_nodes, int64_t n_edges,
+                             const float *pos, const float *shifts, const int64_t *atomic_numbers,
+                             const float *emb, const float *gauss_offsets, const float *cos_g,
+                             const float *sin_g, const int32_t *perm, const int32_t *src,
+                             const int32_t *dst, float *edge_vec, float *dist, float *x_edge,
+                             float *env, float *cos_sorted, float *sin_sorted, void *stream);
+int zp_edge_features_backward(const zp_front_config *cfg, int64_t n_nodes, int64_t n_edges,
+                              const float *edge_vec, const float *dist, const float *x_edge,
+                              const float *gauss_offsets, const int64_t *atomic_numbers,
+                              const float *grad_edge_vec, const float *grad_x_edge,
+                              const float *grad_env, const int32_t *row_ptr,
+                              const int32_t *perm_src, const int32_t *row_ptr_src,
+                              float *grad_pos, float *grad_emb, void *work, size_t work_bytes,
+                              void *stream);
+
 /* Periodic neighbour list with the per-destination cap, on the device (the graph front end; the
  * reference builds edge lists on the host with an external package and applies no cap,
  * fixtures/make_fixtures.py:13-15, 78-100).  Cubic periodic box of edge `box`; positions fp64 [N,3],

@@ -32,6 +32,12 @@ class ZpSizes(C.Structure):
     _fields_ = [(n, C.c_int32) for n in ("K", "Km", "nnz", "nnz_pad", "R", "n_gate", "w1_cols")]
 
 
+class ZpFrontConfig(C.Structure):
+    _fields_ = [("lmax", C.c_int32), ("num_basis", C.c_int32), ("edge_channels", C.c_int32),
+                ("n_elements", C.c_int32), ("envelope_exponent", C.c_int32),
+                ("cutoff", C.c_float), ("gauss_coeff", C.c_float)]
+
+
 class ZpWeights(C.Structure):
     _fields_ = [("c1_w0", C.c_void_p), ("c1_b0", C.c_void_p), ("c1_wm", C.POINTER(C.c_void_p)),
                 ("c2_w0", C.c_void_p), ("c2_b0", C.c_void_p), ("c2_wm", C.POINTER(C.c_void_p))]
@@ -68,6 +74,10 @@ SIGNATURES = {
     "zp_layernorm_silu_forward": (C.c_int, [_I64, C.c_int, _P, _P, _P, C.c_float, _P, _P, _P, _P]),
     "zp_layernorm_silu_backward": (C.c_int, [_I64, C.c_int, _P, _P, _P, _P, _P, _P, _P, _P, _P, _P,
                                               _SZ, _P]),
+    "zp_edge_features_work_bytes": (_SZ, [C.POINTER(ZpFrontConfig), _I64, _I64]),
+    "zp_edge_features_forward": (C.c_int, [C.POINTER(ZpFrontConfig), _I64, _I64] + [_P] * 16 + [_P]),
+    "zp_edge_features_backward": (C.c_int, [C.POINTER(ZpFrontConfig), _I64, _I64] + [_P] * 14
+                                  + [_SZ, _P]),
     "zp_neighbors_work_bytes": (_SZ, [_I64, C.c_double, C.c_double]),
     "zp_neighbors_count": (C.c_int, [_P, _I64, C.c_double, C.c_double, C.c_int, _P, _P, _P, _SZ, _P]),
     "zp_neighbors_fill": (C.c_int, [_P, _I64, C.c_double, C.c_double, C.c_int, _P, _I64, _P, _P, _P,

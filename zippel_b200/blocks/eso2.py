@@ -411,6 +411,77 @@ class LayerNormSiLU(torch.autograd.Function):
         return dx.to(dt[0]), dgb[0].to(dt[1]), dgb[1].to(dt[2]), None
 
 
+class EdgeFeatures(torch.autograd.Function):
+    """Geometry, Gaussian basis, element embeddings, envelope and the re-ordering of the roll-angle
+    harmonics in one pass (``zp_edge_features_forward``), with the position / embedding gradients
+    summed per atom in a fixed order by ``zp_edge_features_backward``.  Takes over
+    blocks/eso2_ref.py:320-327 and :343 (the envelope value).  fp32, first order only.
+
+    Returns (edge_vec [E,3], x_edge [E, NB + 2 EC], env [E], cos_sorted, sin_sorted), all in the
+    graph's sorted edge order."""
+
+    @staticmethod
+    def forward(ctx, graph: EdgeGraph, perm32, front: "_lib.ZpFrontConfig", pos, shifts,
+                atomic_numbers, emb, gauss_offset, cos_g, sin_g):
+        """``perm32``: int32 positions of the graph's sorted edges in the caller's per-edge arrays
+        (``graph.perm`` for a whole graph, a slice of the parent's for a chunk)."""
+        lib = _lib.load()
+        if not pos.is_cuda:
+            raise RuntimeError("EdgeFeatures needs CUDA tensors: there is no CPU path")
+        dev = pos.device
+        n, e = graph.n_nodes, graph.n_edges
+        posf, shf, embf, off = _f32(pos), _f32(shifts), _f32(emb), _f32(gauss_offset)
+        cgf, sgf = _f32(cos_g), _f32(sin_g)
+        zi = atomic_numbers.to(torch.int64).contiguous()
+        f32 = dict(dtype=torch.float32, device=dev)
+        width = front.num_basis + 2 * front.edge_channels
+        edge_vec, dist = torch.empty(e, 3, **f32), torch.empty(e, **f32)
+        x_edge, env = torch.empty(e, width, **f32), torch.empty(e, **f32)
+        cs, ss = torch.empty(e, front.lmax + 1, **f32), torch.empty(e, front.lmax + 1, **f32)
+        with torch.cuda.device(dev):
+            st = torch.cuda.current_stream().cuda_stream
+            _lib.check(lib.zp_edge_features_forward(
+                ctypes.byref(front), n, e, posf.data_ptr(), shf.data_ptr(), zi.data_ptr(),
+                embf.data_ptr(), off.data_ptr(), cgf.data_ptr(), sgf.data_ptr(),
+                perm32.data_ptr(), graph.src.data_ptr(), graph.dst.data_ptr(),
+                edge_vec.data_ptr(), dist.data_ptr(), x_edge.data_ptr(), env.data_ptr(),
+                cs.data_ptr(), ss.data_ptr(), st), "zp_edge_features_forward")
+        ctx.graph, ctx.front = graph, front
+        ctx.dtypes = (pos.dtype, emb.dtype)
+        ctx.n_elem = emb.shape[0]
+        ctx.save_for_backward(edge_vec, dist, x_edge, off, zi)
+        ctx.mark_non_differentiable(cs, ss)
+        return edge_vec, x_edge, env, cs, ss
+
+    @staticmethod
+    @torch.autograd.function.once_differentiable
+    def backward(ctx, g_edge_vec, g_x_edge, g_env, _gc, _gs):
+        lib = _lib.load()
+        edge_vec, dist, x_edge, off, zi = ctx.saved_tensors
+        graph, front = ctx.graph, ctx.front
+        n, e = graph.n_nodes, graph.n_edges
+        dev = edge_vec.device
+        g_pos = torch.empty(n, 3, dtype=torch.float32, device=dev)
+        need_emb = ctx.needs_input_grad[6]
+        g_emb = torch.empty(ctx.n_elem, front.edge_channels, dtype=torch.float32,
+                            device=dev) if need_emb else None
+        ptr = lambda t: None if t is None else _f32(t)            # noqa: E731
+        gev, gxe, gen = ptr(g_edge_vec), ptr(g_x_edge), ptr(g_env)
+        nbytes = lib.zp_edge_features_work_bytes(ctypes.byref(front), n, e)
+        work = torch.empty(max(nbytes, 1), dtype=torch.uint8, device=dev)
+        dp = lambda t: None if t is None else t.data_ptr()        # noqa: E731
+        with torch.cuda.device(dev):
+            st = torch.cuda.current_stream().cuda_stream
+            _lib.check(lib.zp_edge_features_backward(
+                ctypes.byref(front), n, e, edge_vec.data_ptr(), dist.data_ptr(), x_edge.data_ptr(),
+                off.data_ptr(), zi.data_ptr(), dp(gev), dp(gxe), dp(gen), graph.row_ptr.data_ptr(),
+                graph.perm_src.data_ptr(), graph.row_ptr_src.data_ptr(), g_pos.data_ptr(),
+                dp(g_emb), work.data_ptr(), nbytes, st), "zp_edge_features_backward")
+        dt = ctx.dtypes
+        return (None, None, None, g_pos.to(dt[0]), None, None,
+                g_emb.to(dt[1]) if need_emb else None, None, None, None)
+
+
 def edge_conv(plan: Plan, graph: EdgeGraph, x_node, edge_vec, cos_g, sin_g, radial, env,
               c1_m0: nn.Linear, c1_m, c2_m0: nn.Linear, c2_m) -> torch.Tensor:
     return EdgeConvFunction.apply(plan, graph, x_node, edge_vec, cos_g, sin_g, radial, env,
@@ -485,6 +556,12 @@ class ESO2Block(nn.Module):
             feats.append(node_out[:, l * l:(l + 1) ** 2, :].pow(2).sum(dim=1))
         return torch.cat(feats, dim=-1)
 
+    def front_config(self) -> "_lib.ZpFrontConfig":
+        c = self.cfg
+        return _lib.ZpFrontConfig(c.lmax, c.num_distance_basis, c.edge_channels,
+                                  c.max_num_elements, c.envelope_exponent, float(c.cutoff),
+                                  float(self.gauss_coeff))
+
     def plan(self, device) -> Plan:
         c = self.cfg
         return Plan.get(c.lmax, c.mmax, c.sphere_channels, c.hidden_channels, device,
@@ -521,6 +598,14 @@ class ESO2Block(nn.Module):
         """Geometry, radial features, envelope and the edge convolution for the edges of `graph`
         (whose original positions in the caller's arrays are `perm`)."""
         cfg = self.cfg
+        if cfg.edge_channels % 4 == 0 and graph.n_edges > 0:
+            # geometry, distance basis, embeddings, envelope and the sorted copies in one pass
+            edge_vec, x_edge, env, cos_s, sin_s = EdgeFeatures.apply(
+                graph, perm.to(torch.int32).contiguous(), self.front_config(), pos, shifts,
+                atomic_numbers, self.elem_emb.weight, self.gauss_offset, cos_gamma_k, sin_gamma_k)
+            radial = self.radial_mlp(plan, x_edge)
+            return edge_conv(plan, graph, x_node, edge_vec, cos_s, sin_s, radial, env,
+                             self.c1_m0, self.c1_m, self.c2_m0, self.c2_m)
         src, dst = graph.src.long(), graph.dst.long()
         edge_vec = pos[dst] - pos[src] + shifts[perm]
         dist = edge_vec.pow(2).sum(-1).clamp_min(1e-24).sqrt()

@@ -161,16 +161,43 @@ edge_features_bwd_node_kernel(int64_t N, zp_front_config cfg, const float *__res
   }
 }
 
-// one block per element: rows of the atoms of that element, in index order
+// one block per element: rows of the atoms of that element, in index order.  Atoms are scanned
+// in chunks of blockDim.x: every thread tests one atom, then all threads walk the chunk's flags
+// in shared memory, so the serial part never waits on global memory for the element test.
 __global__ void __launch_bounds__(128)
 edge_features_bwd_elem_kernel(int64_t N, int EC, const int64_t *__restrict__ z,
                               const float *__restrict__ node_emb, float *__restrict__ g_emb) {
+  __shared__ unsigned char mine[128];
+  __shared__ int any;
   const int64_t elem = blockIdx.x;
-  for (int c = threadIdx.x; c < EC; c += blockDim.x) {
-    float acc = 0.f;
-    for (int64_t n = 0; n < N; ++n)
-      if (z[n] == elem) acc += node_emb[(size_t)n * EC + c];
-    g_emb[(size_t)elem * EC + c] = acc;
+  float acc[8];                                   // channels c = threadIdx.x + k * blockDim.x
+#pragma unroll
+  for (int k = 0; k < 8; ++k) acc[k] = 0.f;
+  for (int64_t n0 = 0; n0 < N; n0 += blockDim.x) {
+    if (threadIdx.x == 0) any = 0;
+    __syncthreads();
+    const int64_t n = n0 + threadIdx.x;
+    const bool hit = n < N && z[n] == elem;
+    mine[threadIdx.x] = hit;
+    if (hit) any = 1;
+    __syncthreads();
+    if (any) {
+      const int cnt = (int)min((int64_t)blockDim.x, N - n0);
+      for (int t = 0; t < cnt; ++t)
+        if (mine[t]) {
+#pragma unroll
+          for (int k = 0; k < 8; ++k) {
+            const int c = threadIdx.x + k * blockDim.x;
+            if (c < EC) acc[k] += node_emb[(size_t)(n0 + t) * EC + c];
+          }
+        }
+    }
+    __syncthreads();
+  }
+#pragma unroll
+  for (int k = 0; k < 8; ++k) {
+    const int c = threadIdx.x + k * blockDim.x;
+    if (c < EC) g_emb[(size_t)elem * EC + c] = acc[k];
   }
 }
 
@@ -178,7 +205,7 @@ int check_cfg(const zp_front_config *cfg) {
   if (!cfg) return ZP_ERR_INVALID_ARG;
   if (cfg->num_basis < 1 || cfg->edge_channels < 4 || (cfg->edge_channels % 4) ||
       cfg->n_elements < 1 || cfg->lmax < 0 || cfg->lmax > ZP_MAX_L || !(cfg->cutoff > 0.f) ||
-      cfg->envelope_exponent < 1 || cfg->envelope_exponent > 16)
+      cfg->edge_channels > 1024 || cfg->envelope_exponent < 1 || cfg->envelope_exponent > 16)
     return ZP_ERR_UNSUPPORTED;
   return ZP_OK;
 }

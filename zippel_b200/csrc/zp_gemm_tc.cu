@@ -98,15 +98,20 @@ __device__ __forceinline__ bool mbar_try_wait(uint64_t *bar, uint32_t parity) {
 }
 
 // Bounded wait.  Returns false when the CTA is aborting (this wait or another one timed out).
+// The clock is only looked at every 1024 failed polls (the first look starts the interval), so a
+// wait that is satisfied quickly never pays for reading the global timer.
 __device__ __forceinline__ bool mbar_wait(uint64_t *bar, uint32_t parity, volatile int *abort_flag,
                                           int *status) {
   if (mbar_try_wait(bar, parity)) return true;
-  const uint64_t t0 = globaltimer_ns();
+  uint64_t t0 = 0;
   uint32_t spins = 0;
   while (!mbar_try_wait(bar, parity)) {
     if ((++spins & 0x3ff) == 0) {
       if (*abort_flag) return false;
-      if (globaltimer_ns() - t0 > kWaitLimitNs) {
+      const uint64_t now = globaltimer_ns();
+      if (t0 == 0) {
+        t0 = now;
+      } else if (now - t0 > kWaitLimitNs) {
         *abort_flag = 1;
         atomicExch(status, (int)ZP_ERR_DEVICE_TIMEOUT);
         return false;
@@ -160,6 +165,15 @@ __device__ __forceinline__ void tmem_ld32(uint32_t taddr, uint32_t (&r)[32]) {
         "=r"(r[14]), "=r"(r[15]), "=r"(r[16]), "=r"(r[17]), "=r"(r[18]), "=r"(r[19]), "=r"(r[20]),
         "=r"(r[21]), "=r"(r[22]), "=r"(r[23]), "=r"(r[24]), "=r"(r[25]), "=r"(r[26]), "=r"(r[27]),
         "=r"(r[28]), "=r"(r[29]), "=r"(r[30]), "=r"(r[31])
+      : "r"(taddr));
+}
+__device__ __forceinline__ void tmem_ld16(uint32_t taddr, uint32_t (&r)[16]) {
+  asm volatile(
+      "tcgen05.ld.sync.aligned.32x32b.x16.b32 "
+      "{%0, %1, %2, %3, %4, %5, %6, %7, %8, %9, %10, %11, %12, %13, %14, %15}, [%16];"
+      : "=r"(r[0]), "=r"(r[1]), "=r"(r[2]), "=r"(r[3]), "=r"(r[4]), "=r"(r[5]), "=r"(r[6]),
+        "=r"(r[7]), "=r"(r[8]), "=r"(r[9]), "=r"(r[10]), "=r"(r[11]), "=r"(r[12]), "=r"(r[13]),
+        "=r"(r[14]), "=r"(r[15])
       : "r"(taddr));
 }
 __device__ __forceinline__ void tmem_ld_wait() {
@@ -395,19 +409,23 @@ gemm_tc_kernel(const __grid_constant__ CUtensorMap map_a, const __grid_constant_
         for (int b = 0; b < 4; ++b) {
           const int cc = col_lo + 32 * b;
           if (cc < col_hi) {                    // warp-uniform
-            uint32_t r[32];
-            tmem_ld32(t_row + cc, r);
-            if (P != 1) {
-              uint32_t r2[32];
-              tmem_ld32(t_row + kTmemBuf + cc, r2);
+            // 16 columns at a time, the small-product accumulator added in place: the slice
+            // itself (128 values per thread) leaves little room for staging registers
+#pragma unroll
+            for (int h = 0; h < 2; ++h) {
+              uint32_t r[16];
+              tmem_ld16(t_row + cc + 16 * h, r);
               tmem_ld_wait();
 #pragma unroll
-              for (int j = 0; j < 32; ++j)
-                v[b][j] = (__uint_as_float(r[j]) + __uint_as_float(r2[j])) * out_scale;
-            } else {
-              tmem_ld_wait();
+              for (int j = 0; j < 16; ++j) v[b][16 * h + j] = __uint_as_float(r[j]);
+              if (P != 1) {
+                tmem_ld16(t_row + kTmemBuf + cc + 16 * h, r);
+                tmem_ld_wait();
 #pragma unroll
-              for (int j = 0; j < 32; ++j) v[b][j] = __uint_as_float(r[j]) * out_scale;
+                for (int j = 0; j < 16; ++j) v[b][16 * h + j] += __uint_as_float(r[j]);
+              }
+#pragma unroll
+              for (int j = 0; j < 16; ++j) v[b][16 * h + j] *= out_scale;
             }
           }
         }
@@ -719,19 +737,23 @@ gemm_tc_pair_kernel(const __grid_constant__ CUtensorMap map_a,
         for (int b = 0; b < 4; ++b) {
           const int cc = col_lo + 32 * b;
           if (cc < col_hi) {
-            uint32_t r[32];
-            tmem_ld32(t_row + cc, r);
-            if (P != 1) {
-              uint32_t r2[32];
-              tmem_ld32(t_row + kTmemBuf + cc, r2);
+            // 16 columns at a time, the small-product accumulator added in place: the slice
+            // itself (128 values per thread) leaves little room for staging registers
+#pragma unroll
+            for (int h = 0; h < 2; ++h) {
+              uint32_t r[16];
+              tmem_ld16(t_row + cc + 16 * h, r);
               tmem_ld_wait();
 #pragma unroll
-              for (int j = 0; j < 32; ++j)
-                v[b][j] = (__uint_as_float(r[j]) + __uint_as_float(r2[j])) * out_scale;
-            } else {
-              tmem_ld_wait();
+              for (int j = 0; j < 16; ++j) v[b][16 * h + j] = __uint_as_float(r[j]);
+              if (P != 1) {
+                tmem_ld16(t_row + kTmemBuf + cc + 16 * h, r);
+                tmem_ld_wait();
 #pragma unroll
-              for (int j = 0; j < 32; ++j) v[b][j] = __uint_as_float(r[j]) * out_scale;
+                for (int j = 0; j < 16; ++j) v[b][16 * h + j] += __uint_as_float(r[j]);
+              }
+#pragma unroll
+              for (int j = 0; j < 16; ++j) v[b][16 * h + j] *= out_scale;
             }
           }
         }

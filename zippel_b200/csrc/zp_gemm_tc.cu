@@ -207,6 +207,7 @@ struct GemmParams {
   const float *bias;
   float *C;
   int64_t ldc, split_stride;
+  int tma_store;          // epilogue goes through TMA stores (map_c is valid)
   int *status;
 };
 
@@ -228,6 +229,91 @@ template <> struct Pairs<3> {
   __device__ static constexpr int b(int i) { return i == 0 ? 0 : i == 1 ? 0 : i == 2 ? 2 : i == 3 ? 1 : i == 4 ? 0 : 1; }
 };
 
+// ---- epilogue through TMA stores ------------------------------------------------------------
+// In TMEM a lane owns a row, so storing straight from the registers sends every lane of an
+// instruction to a different output row: 32 separate 16-byte pieces per instruction, and the
+// epilogue of a 128 x 256 tile costs ~8 000 store wavefronts.  Instead each epilogue warp writes
+// 32 x 32 blocks into its own 4 KB of shared memory (128-byte rows under the 128-byte swizzle, the
+// layout the tensor map names) and one lane hands the block to the TMA unit, which writes full
+// lines and clips rows / columns beyond the matrix.  Later K chunks of a tile use the reducing
+// store (add) after the previous store of that tile has completed.
+constexpr int kEpiBlockBytes = 32 * 32 * 4;
+constexpr int kEpiBytes = 8 * kEpiBlockBytes;                 // eight epilogue warps
+
+__device__ __forceinline__ void tma_store_3d(const CUtensorMap *map, const void *src, int c0, int c1,
+                                             int c2) {
+  asm volatile("cp.async.bulk.tensor.3d.global.shared::cta.bulk_group [%0, {%2, %3, %4}], [%1];"
+               :
+               : "l"(reinterpret_cast<uint64_t>(map)), "r"(smem_u32(src)), "r"(c0), "r"(c1), "r"(c2)
+               : "memory");
+}
+__device__ __forceinline__ void tma_reduce_add_3d(const CUtensorMap *map, const void *src, int c0,
+                                                  int c1, int c2) {
+  asm volatile(
+      "cp.reduce.async.bulk.tensor.3d.global.shared::cta.add.tile.bulk_group [%0, {%2, %3, %4}], [%1];"
+      :
+      : "l"(reinterpret_cast<uint64_t>(map)), "r"(smem_u32(src)), "r"(c0), "r"(c1), "r"(c2)
+      : "memory");
+}
+__device__ __forceinline__ void bulk_commit() { asm volatile("cp.async.bulk.commit_group;" ::: "memory"); }
+__device__ __forceinline__ void bulk_wait_read() {            // shared source may be overwritten
+  asm volatile("cp.async.bulk.wait_group.read 0;" ::: "memory");
+}
+__device__ __forceinline__ void bulk_wait_all() {             // the writes themselves are done
+  asm volatile("cp.async.bulk.wait_group 0;" ::: "memory");
+}
+
+// v[b][j]: value at row `row0 + lane`, column `n0 + col_lo + 32 b + j` (scaled, no bias yet).
+__device__ __forceinline__ void epilogue_store_tma(const GemmParams &p, const CUtensorMap *map_c,
+                                                   float (&v)[4][32], uint8_t *stage, int lane,
+                                                   int row0, int n0, int col_lo, int col_hi,
+                                                   int split, const float *bias, bool first,
+                                                   float &seen_max) {
+  if (row0 >= p.M) return;                        // warp-uniform: nothing of this slice exists
+  const bool row_ok = row0 + lane < p.M;
+  if (!first) {                                   // the tile's previous store must have landed
+    if (lane == 0) bulk_wait_all();
+    __syncwarp();
+  }
+#pragma unroll
+  for (int b = 0; b < 4; ++b) {
+    const int cc = col_lo + 32 * b;
+    if (cc >= col_hi) continue;                   // warp-uniform
+    const int n = n0 + cc;
+    if (n >= p.N) continue;
+    if (lane == 0) bulk_wait_read();              // the block buffer is free again
+    __syncwarp();
+#pragma unroll
+    for (int k = 0; k < 8; ++k) {
+      float4 o = make_float4(v[b][4 * k], v[b][4 * k + 1], v[b][4 * k + 2], v[b][4 * k + 3]);
+      if (first && bias) {
+        const int c = n + 4 * k;
+        o.x += c < p.N ? bias[c] : 0.f;
+        o.y += c + 1 < p.N ? bias[c + 1] : 0.f;
+        o.z += c + 2 < p.N ? bias[c + 2] : 0.f;
+        o.w += c + 3 < p.N ? bias[c + 3] : 0.f;
+      }
+      if (row_ok) {
+        const int c = n + 4 * k;
+        float m = c < p.N ? fabsf(o.x) : 0.f;
+        m = fmaxf(m, c + 1 < p.N ? fabsf(o.y) : 0.f);
+        m = fmaxf(m, c + 2 < p.N ? fabsf(o.z) : 0.f);
+        m = fmaxf(m, c + 3 < p.N ? fabsf(o.w) : 0.f);
+        seen_max = fmaxf(seen_max, m);
+      }
+      // 128-byte swizzle: 16-byte chunk k of row r sits at chunk k ^ (r & 7)
+      *reinterpret_cast<float4 *>(stage + lane * 128 + ((k ^ (lane & 7)) << 4)) = o;
+    }
+    asm volatile("fence.proxy.async.shared::cta;" ::: "memory");
+    __syncwarp();
+    if (lane == 0) {
+      if (first) tma_store_3d(map_c, stage, n, row0, split);
+      else tma_reduce_add_3d(map_c, stage, n, row0, split);
+      bulk_commit();
+    }
+  }
+}
+
 template <int P, int BK, int STAGES, int BN_CAP>
 struct SmemLayout {
   static constexpr int kATile = BM * BK * 2;
@@ -235,7 +321,12 @@ struct SmemLayout {
   static constexpr int kStage = P * (kATile + kBTile);
   static constexpr int kTiles = STAGES * kStage;
   static constexpr int kBars = 8 * (2 * STAGES + 4);
-  static constexpr int kTotal = kTiles + kBars + 16 + 1024;   // + tmem slot/abort + alignment slack
+  // barriers, TMEM slot and abort flag live in the first KB after the tiles; the epilogue's
+  // store blocks (when the CTA's budget allows them) follow, 1 KB aligned; + 1 KB alignment slack
+  static_assert(kBars + 16 <= 1024, "control words fit in one KB");
+  static constexpr bool kTmaEpilogue = kTiles + 1024 + kEpiBytes + 1024 <= 232448;
+  static constexpr int kEpiOffset = kTiles + 1024;
+  static constexpr int kTotal = kTiles + 1024 + (kTmaEpilogue ? kEpiBytes : 0) + 1024;
 };
 
 // One unit of work of a CTA: an output tile, a K split, and its k-block range.
@@ -256,7 +347,7 @@ __device__ __forceinline__ Work decode_work(const GemmParams &p, int w) {
 template <int P, int BK, int STAGES, int BN_CAP>
 __global__ void __launch_bounds__(kThreads, 1)
 gemm_tc_kernel(const __grid_constant__ CUtensorMap map_a, const __grid_constant__ CUtensorMap map_b,
-               const GemmParams p) {
+               const __grid_constant__ CUtensorMap map_c, const GemmParams p) {
   using L = SmemLayout<P, BK, STAGES, BN_CAP>;
   constexpr int kAccBufs = P == 1 ? 2 : 1;      // accumulation units in flight in TMEM
   extern __shared__ uint8_t smem_raw[];
@@ -385,6 +476,7 @@ gemm_tc_kernel(const __grid_constant__ CUtensorMap map_a, const __grid_constant_
     // registers and releases TMEM, so the next tile's MMAs start while it scales and stores.
     const int q = warp & 3;
     const int half = (warp - 2) >> 2;
+    uint8_t *epi_stage = smem + L::kEpiOffset + (warp - 2) * kEpiBlockBytes;
     uint32_t unit = 0;
     bool ok = true;
     const float out_scale = (p.scale_a ? *p.scale_a : 1.f) * (p.scale_b ? *p.scale_b : 1.f);
@@ -392,7 +484,8 @@ gemm_tc_kernel(const __grid_constant__ CUtensorMap map_a, const __grid_constant_
     const int col_lo = half * 128, col_hi = min(p.BN, col_lo + 128);
     for (int w = blockIdx.x; w < num_work && ok; w += gridDim.x) {
       const Work x = decode_work(p, w);
-      const int row = x.m0 + q * 32 + lane;
+      const int row0 = x.m0 + q * 32;
+      const int row = row0 + lane;
       float *crow = p.C + (size_t)x.split * p.split_stride + (size_t)row * p.ldc;
       const float *bias = x.split == 0 ? p.bias : nullptr;
       for (int c0 = x.kb0; c0 < x.kb1 && ok; c0 += p.kc, ++unit) {
@@ -433,7 +526,10 @@ gemm_tc_kernel(const __grid_constant__ CUtensorMap map_a, const __grid_constant_
         __syncwarp();
         if (lane == 0) mbar_arrive(&tmem_empty[buf]);      // TMEM slice is in registers now
 
-        if (row < p.M) {
+        if (L::kTmaEpilogue && p.tma_store) {
+          epilogue_store_tma(p, &map_c, v, epi_stage, lane, row0, x.n0, col_lo, col_hi, x.split,
+                             bias, first, seen_max);
+        } else if (row < p.M) {
 #pragma unroll
           for (int b = 0; b < 4; ++b) {
             const int cc = col_lo + 32 * b;
@@ -470,6 +566,7 @@ gemm_tc_kernel(const __grid_constant__ CUtensorMap map_a, const __grid_constant_
         }
       }
     }
+    if (L::kTmaEpilogue && p.tma_store && lane == 0) bulk_wait_all();   // this warp's stores are done
     if (p.absmax_out) {
 #pragma unroll
       for (int o = 16; o > 0; o >>= 1) seen_max = fmaxf(seen_max, __shfl_xor_sync(0xffffffffu, seen_max, o));
@@ -563,7 +660,10 @@ struct SmemLayoutPair {
   static constexpr int kStage = P * (kATile + kBTile);
   static constexpr int kTiles = STAGES * kStage;
   static constexpr int kBars = 8 * (2 * STAGES + 4);
-  static constexpr int kTotal = kTiles + kBars + 16 + 1024;
+  static_assert(kBars + 16 <= 1024, "control words fit in one KB");
+  static constexpr bool kTmaEpilogue = kTiles + 1024 + kEpiBytes + 1024 <= 232448;
+  static constexpr int kEpiOffset = kTiles + 1024;
+  static constexpr int kTotal = kTiles + 1024 + (kTmaEpilogue ? kEpiBytes : 0) + 1024;
 };
 
 __device__ __forceinline__ Work decode_work_pair(const GemmParams &p, int w) {
@@ -580,7 +680,8 @@ __device__ __forceinline__ Work decode_work_pair(const GemmParams &p, int w) {
 template <int P, int BK, int STAGES>
 __global__ void __launch_bounds__(kThreads, 1)
 gemm_tc_pair_kernel(const __grid_constant__ CUtensorMap map_a,
-                    const __grid_constant__ CUtensorMap map_b, const GemmParams p) {
+                    const __grid_constant__ CUtensorMap map_b,
+                    const __grid_constant__ CUtensorMap map_c, const GemmParams p) {
   using L = SmemLayoutPair<P, BK, STAGES>;
   extern __shared__ uint8_t smem_raw[];
   // the dynamic shared window starts at the same offset in both CTAs, so does everything below
@@ -714,6 +815,7 @@ gemm_tc_pair_kernel(const __grid_constant__ CUtensorMap map_a,
     // ---------------------------------------------------------------- epilogue (both CTAs)
     const int q = warp & 3;
     const int half = (warp - 2) >> 2;
+    uint8_t *epi_stage = smem + L::kEpiOffset + (warp - 2) * kEpiBlockBytes;
     uint32_t unit = 0;
     bool ok = true;
     const float out_scale = (p.scale_a ? *p.scale_a : 1.f) * (p.scale_b ? *p.scale_b : 1.f);
@@ -722,7 +824,8 @@ gemm_tc_pair_kernel(const __grid_constant__ CUtensorMap map_a,
     const uint32_t release_bar = map_to_cta(smem_u32(&tmem_empty[0]), 0);
     for (int w = pair; w < num_work && ok; w += num_pairs) {
       const Work x = decode_work_pair(p, w);
-      const int row = x.m0 + (int)rank * BM + q * 32 + lane;
+      const int row0 = x.m0 + (int)rank * BM + q * 32;
+      const int row = row0 + lane;
       float *crow = p.C + (size_t)x.split * p.split_stride + (size_t)row * p.ldc;
       const float *bias = x.split == 0 ? p.bias : nullptr;
       for (int c0 = x.kb0; c0 < x.kb1 && ok; c0 += p.kc, ++unit) {
@@ -761,7 +864,10 @@ gemm_tc_pair_kernel(const __grid_constant__ CUtensorMap map_a,
         __syncwarp();
         if (lane == 0) mbar_arrive_cluster(release_bar);
 
-        if (row < p.M) {
+        if (L::kTmaEpilogue && p.tma_store) {
+          epilogue_store_tma(p, &map_c, v, epi_stage, lane, row0, x.n0, col_lo, col_hi, x.split,
+                             bias, first, seen_max);
+        } else if (row < p.M) {
 #pragma unroll
           for (int b = 0; b < 4; ++b) {
             const int cc = col_lo + 32 * b;
@@ -798,6 +904,7 @@ gemm_tc_pair_kernel(const __grid_constant__ CUtensorMap map_a,
         }
       }
     }
+    if (L::kTmaEpilogue && p.tma_store && lane == 0) bulk_wait_all();   // this warp's stores are done
     if (p.absmax_out) {
 #pragma unroll
       for (int o = 16; o > 0; o >>= 1) seen_max = fmaxf(seen_max, __shfl_xor_sync(0xffffffffu, seen_max, o));
@@ -858,6 +965,25 @@ int make_map(CUtensorMap *map, const void *base, uint64_t inner, uint64_t outer,
 
 // Tile width: the multiple of `step` in [cap/2, cap] that wastes the fewest padded columns
 // (ties: the widest); problems narrower than cap/2 get one tile.
+// 3-d map over (column, row, split) of the fp32 output, 32 x 32 boxes under the 128-byte swizzle
+int make_map_c(CUtensorMap *map, float *C, uint64_t N, uint64_t M, uint64_t splits, uint64_t ldc,
+               uint64_t split_stride) {
+  EncodeTiledFn fn = encode_fn();
+  if (!fn) return ZP_ERR_CUDA;
+  const cuuint64_t dims[3] = {N, M, splits};
+  const cuuint64_t strides[2] = {ldc * 4, (splits > 1 ? split_stride : ldc * M) * 4};
+  const cuuint32_t box[3] = {32, 32, 1};
+  const cuuint32_t estr[3] = {1, 1, 1};
+  const CUresult r = fn(map, CU_TENSOR_MAP_DATA_TYPE_FLOAT32, 3, C, dims, strides, box, estr,
+                        CU_TENSOR_MAP_INTERLEAVE_NONE, CU_TENSOR_MAP_SWIZZLE_128B,
+                        CU_TENSOR_MAP_L2_PROMOTION_NONE, CU_TENSOR_MAP_FLOAT_OOB_FILL_NONE);
+  if (r != CUDA_SUCCESS) {
+    zp_set_cuda_error(cudaErrorInvalidValue, "cuTensorMapEncodeTiled (output)");
+    return ZP_ERR_CUDA;
+  }
+  return ZP_OK;
+}
+
 int pick_bn(int64_t N, int cap, int step = 16) {
   if (N <= cap / 2) return (int)(zp_ceil_div(N, step) * step);
   int best = cap;
@@ -890,7 +1016,7 @@ int device_sms() {
 double launch_score(const ZpGemmTc &g, bool pair, int splits) {
   const int64_t units = pair ? device_sms() / 2 : device_sms();
   const int tm = pair ? 256 : BM;
-  const int bn = pair ? pick_bn(g.N, 256, g.b_mn ? 128 : 16) : pick_bn(g.N, 256, g.b_mn ? 64 : 16);
+  const int bn = pair ? pick_bn(g.N, 256, g.b_mn ? 128 : 32) : pick_bn(g.N, 256, g.b_mn ? 64 : 32);
   const int64_t tiles_m = zp_ceil_div(g.M, tm), tiles_n = zp_ceil_div(g.N, bn);
   const double pad = (double)(g.M * g.N) / (double)(tiles_m * tm * tiles_n * bn);
   const int64_t items = tiles_m * tiles_n * splits;
@@ -933,7 +1059,8 @@ int launch(const ZpGemmTc &g, cudaStream_t st) {
   }
   GemmParams p;
   p.M = (int)g.M; p.N = (int)g.N; p.K = (int)g.K;
-  p.BN = pick_bn(g.N, BN_CAP, g.b_mn ? 64 : 16);  // MN-major B tiles come in 64-wide blocks
+  // whole 32-column store blocks; MN-major B tiles come in 64-wide blocks
+  p.BN = pick_bn(g.N, BN_CAP, g.b_mn ? 64 : 32);
   p.num_m = (int)zp_ceil_div(g.M, BM);
   p.num_n = (int)zp_ceil_div(g.N, p.BN);
   split_plan(g, BK, &p.ksplit, &p.kb_per_split, &p.num_k);
@@ -954,9 +1081,17 @@ int launch(const ZpGemmTc &g, cudaStream_t st) {
   int dev = 0, sms = 148;
   cudaGetDevice(&dev);
   cudaDeviceGetAttribute(&sms, cudaDevAttrMultiProcessorCount, dev);
+  CUtensorMap mc;
+  const int chunks = (int)zp_ceil_div(p.kb_per_split, p.kc);
+  p.tma_store = L::kTmaEpilogue && !(g.absmax_out && chunks > 1);
+  if (p.tma_store) {
+    if ((rc = make_map_c(&mc, g.C, g.N, g.M, p.ksplit, g.ldc, g.split_stride))) return rc;
+  } else {
+    mc = ma;                                      // never read
+  }
   const int work = p.num_m * p.num_n * p.ksplit;
   const int grid = work < sms ? work : sms;
-  gemm_tc_kernel<P, BK, STAGES, BN_CAP><<<grid, kThreads, L::kTotal, st>>>(ma, mb, p);
+  gemm_tc_kernel<P, BK, STAGES, BN_CAP><<<grid, kThreads, L::kTotal, st>>>(ma, mb, mc, p);
   ZP_LAUNCH_CHECK("gemm_tc_kernel");
   return ZP_OK;
 }
@@ -985,7 +1120,8 @@ int launch_pair(const ZpGemmTc &g, cudaStream_t st) {
   if (max_pairs < 1) return ZP_ERR_UNSUPPORTED;
   GemmParams p;
   p.M = (int)g.M; p.N = (int)g.N; p.K = (int)g.K;
-  p.BN = pick_bn(g.N, 256, g.b_mn ? 128 : 16);    // each CTA's half of an MN-major tile: 64-wide blocks
+  // whole 32-column store blocks; each CTA's half of an MN-major tile comes in 64-wide blocks
+  p.BN = pick_bn(g.N, 256, g.b_mn ? 128 : 32);
   p.num_m = (int)zp_ceil_div(g.M, BM2);
   p.num_n = (int)zp_ceil_div(g.N, p.BN);
   split_plan(g, BK, &p.ksplit, &p.kb_per_split, &p.num_k);
@@ -1003,9 +1139,17 @@ int launch_pair(const ZpGemmTc &g, cudaStream_t st) {
   if (!g.b_mn) rc = make_map(&mb, g.B, g.K, g.N, P, g.ldb, g.b_plane, BK, p.BN / 2, kswz, g.fp16);
   else rc = make_map(&mb, g.B, g.N, g.K, P, g.ldb, g.b_plane, 64, BK, CU_TENSOR_MAP_SWIZZLE_128B, g.fp16);
   if (rc) return rc;
+  CUtensorMap mc;
+  const int chunks = (int)zp_ceil_div(p.kb_per_split, p.kc);
+  p.tma_store = L::kTmaEpilogue && !(g.absmax_out && chunks > 1);
+  if (p.tma_store) {
+    if ((rc = make_map_c(&mc, g.C, g.N, g.M, p.ksplit, g.ldc, g.split_stride))) return rc;
+  } else {
+    mc = ma;                                      // never read
+  }
   const int work = p.num_m * p.num_n * p.ksplit;
   cfg.gridDim = dim3((unsigned)(2 * (work < max_pairs ? work : max_pairs)));
-  ZP_CUDA(cudaLaunchKernelEx(&cfg, kernel, ma, mb, p));
+  ZP_CUDA(cudaLaunchKernelEx(&cfg, kernel, ma, mb, mc, p));
   ZP_LAUNCH_CHECK("gemm_tc_pair_kernel");
   return ZP_OK;
 }

@@ -97,7 +97,7 @@ struct RotIn<-1, LMAX> {
 };
 
 template <int LMAX>
-__global__ void __launch_bounds__(kRotInThreads)
+__global__ void __launch_bounds__(kRotInThreads, (LMAX <= 4 ? 4 : 3))
 rotate_in_kernel(const __grid_constant__ ZpTables t, int64_t E, int epb,
                  const float *__restrict__ x, const int32_t *__restrict__ src,
                  const int32_t *__restrict__ dst, const float *__restrict__ rot,

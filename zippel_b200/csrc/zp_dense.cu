@@ -123,7 +123,8 @@ __global__ void gate_fwd_kernel(const __grid_constant__ ZpTables t, int64_t E,
 // The scale of the fp16 planes is fixed beforehand from max |dht| and the forward's gate bound:
 //   |dh1 row| <= 1.1 max|dht|  (sigmoid <= 1, silu' <= 1.1),
 //   |dh1 gate_l| = sigmoid'(g_l) |sum_rows dht h1| <= max|dht| * rows(l) * max|h1| * max sigmoid'.
-__global__ void gate_bwd_kernel(const __grid_constant__ ZpTables t, int64_t E,
+template <int LM>
+__global__ void __launch_bounds__(128, 6) gate_bwd_kernel(const __grid_constant__ ZpTables t, int64_t E,
                                 const float *__restrict__ h1, const float *__restrict__ dht,
                                 const ZpPlanes dh1) {
   const int H4 = t.H / 4;
@@ -137,10 +138,11 @@ __global__ void gate_bwd_kernel(const __grid_constant__ ZpTables t, int64_t E,
   const int64_t drow = e * dh1.ld;
   const float inv = zp_inv_scale(dh1);
   const float *dt = dht + (size_t)e * t.Km * t.H;
-  float sg[ZP_MAX_L][4], dg[ZP_MAX_L][4];
+  constexpr int NL = LM > 0 ? LM : 1;        // gates: one per degree 1..lmax
+  float sg[NL][4], dg[NL][4];
 #pragma unroll
-  for (int l = 0; l < ZP_MAX_L; ++l) {
-    if (l < t.lmax) {
+  for (int l = 0; l < NL; ++l) {
+    if (l < LM) {
       const float4 g = *reinterpret_cast<const float4 *>(row + l * t.H + h);
       sg[l][0] = sigmoidf(g.x); sg[l][1] = sigmoidf(g.y);
       sg[l][2] = sigmoidf(g.z); sg[l][3] = sigmoidf(g.w);
@@ -163,7 +165,7 @@ __global__ void gate_bwd_kernel(const __grid_constant__ ZpTables t, int64_t E,
     } else {
       const int l = t.row_l[r] - 1;
 #pragma unroll
-      for (int ll = 0; ll < ZP_MAX_L; ++ll) {
+      for (int ll = 0; ll < NL; ++ll) {
         if (ll == l) {
 #pragma unroll
           for (int v = 0; v < 4; ++v) {
@@ -176,8 +178,8 @@ __global__ void gate_bwd_kernel(const __grid_constant__ ZpTables t, int64_t E,
     if (in_range) zp_store_planes<4>(dh1, drow + t.n_gate + r * t.H + h, o, inv);
   }
 #pragma unroll
-  for (int l = 0; l < ZP_MAX_L; ++l) {
-    if (l < t.lmax) {
+  for (int l = 0; l < NL; ++l) {
+    if (l < LM) {
       float o[4];
 #pragma unroll
       for (int v = 0; v < 4; ++v) o[v] = dg[l][v] * sg[l][v] * (1.f - sg[l][v]);
@@ -392,7 +394,9 @@ int zp_launch_gate_bwd(const zp_plan *p, int64_t E, const float *h1, const float
   if (E == 0) return ZP_OK;
   const int per_group = kGateEdges * (p->t.H / 4);
   const dim3 grid((unsigned)zp_ceil_div(E, kGateEdges), (unsigned)zp_ceil_div(per_group, 128));
-  gate_bwd_kernel<<<grid, 128, 0, st>>>(p->t, E, h1, dht, dh1);
+#define CALL(LM) gate_bwd_kernel<LM><<<grid, 128, 0, st>>>(p->t, E, h1, dht, dh1)
+  ZP_DISPATCH_LMAX(p->t.lmax, CALL)
+#undef CALL
   ZP_LAUNCH_CHECK("gate_bwd_kernel");
   return ZP_OK;
 }

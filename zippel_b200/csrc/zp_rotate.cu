@@ -435,10 +435,11 @@ template <int L, int LMAX>
 struct RotInBwdE {
   // stage: this warp's [Km + radial rows][128] buffer, filled by StageInBwd in level order
   static __device__ __forceinline__ void run(const ZpTables &t, const float *xrow,
-                                             const float *stage, float *grad_e,
-                                             const float *rot_s, float *part_s, float *du_row,
-                                             int c2, bool active, int lane) {
-    RotInBwdE<L - 1, LMAX>::run(t, xrow, stage, grad_e, rot_s, part_s, du_row, c2, active, lane);
+                                             const float *stage, const float *rad_e,
+                                             float *grad_e, const float *rot_s, float *part_s,
+                                             float *du_row, int c2, bool active, int lane) {
+    RotInBwdE<L - 1, LMAX>::run(t, xrow, stage, rad_e, grad_e, rot_s, part_s, du_row, c2, active,
+                                lane);
     constexpr int n = 2 * L + 1;
     const int C2 = 2 * t.C;
     const int mm = t.mmax < L ? t.mmax : L;
@@ -455,7 +456,7 @@ struct RotInBwdE {
       if (am <= mm) {
         float gr[4] = {0.f, 0.f, 0.f, 0.f}, rad[4] = {0.f, 0.f, 0.f, 0.f};
         const int col = t.rad_off[am] + (L - am) * C2 + c2;
-        if (active) vload<4>(rad, stage + (size_t)(t.Km + t.rad_off[am] / C2 + (L - am)) * 128 + lane * 4);
+        if (active) vload<4>(rad, rad_e + col);
 #pragma unroll
         for (int sgn = 0; sgn < 2; ++sgn) {
           if (sgn == 1 && am == 0) continue;
@@ -499,13 +500,13 @@ struct RotInBwdE {
 template <int LMAX>
 struct RotInBwdE<-1, LMAX> {
   static __device__ __forceinline__ void run(const ZpTables &, const float *, const float *,
-                                             float *, const float *, float *, float *, int, bool,
-                                             int) {}
+                                             const float *, float *, const float *, float *,
+                                             float *, int, bool, int) {}
 };
 
-// Puts every row the edge needs in flight at once: each lane copies its own four channels of the
-// Km gradient rows and of the radial rows into the warp's shared buffer with cp.async, one commit
-// group per degree, so RotInBwdE waits once per degree instead of once per row.
+// Puts the gradient rows of the edge in flight at once: each lane copies its own four channels of
+// the Km rows into the warp's shared buffer with cp.async, one commit group per degree, so
+// RotInBwdE waits once per degree instead of once per row (the radial rows are loaded directly).
 template <int L, int LMAX>
 struct StageInBwd {
   static __device__ __forceinline__ void run(const ZpTables &t, const float *da_e,
@@ -524,11 +525,6 @@ struct StageInBwd {
           cp_async<16>(stage + (size_t)r * 128 + lane * 4, da_e + (size_t)r * C2 + c2);
         }
       }
-#pragma unroll
-      for (int am = 0; am <= L; ++am)
-        if (am <= mm)
-          cp_async<16>(stage + (size_t)(t.Km + t.rad_off[am] / C2 + (L - am)) * 128 + lane * 4,
-                       rad_e + t.rad_off[am] + (L - am) * C2 + c2);
     }
     cp_async_commit();
   }
@@ -541,9 +537,9 @@ struct StageInBwd<-1, LMAX> {
 
 // du_both [E][2][K][C]: half 0 = contribution to the source node, half 1 = to the destination.
 // Blocks of `nw` warps, W warps per edge; shared memory: rot [nw / W][nnz_pad] |
-// partial [nw][nnz_pad] | stage [nw][Km + R / 2C][128].
+// partial [nw][nnz_pad] | stage [nw][Km][128].
 template <int LMAX>
-__global__ void __launch_bounds__(128, (LMAX <= 4 ? 3 : 2))
+__global__ void __launch_bounds__(128, (LMAX <= 4 ? 4 : 2))
 rotate_in_bwd_kernel(const __grid_constant__ ZpTables t, int64_t E, int W,
                      const float *__restrict__ da1, const float *__restrict__ radial,
                      const float *__restrict__ x, const int32_t *__restrict__ src,
@@ -553,7 +549,7 @@ rotate_in_bwd_kernel(const __grid_constant__ ZpTables t, int64_t E, int W,
   extern __shared__ __align__(16) float smem[];
   const int nw = blockDim.x / 32;
   const int epb = nw / W;
-  const int stage_rows = t.Km + t.R / (2 * t.C);
+  const int stage_rows = t.Km;
   float *rot_s = smem;
   float *part_all = smem + epb * t.nnz_pad;
   const int warp = threadIdx.x / 32, lane = threadIdx.x % 32;
@@ -575,7 +571,8 @@ rotate_in_bwd_kernel(const __grid_constant__ ZpTables t, int64_t E, int W,
     const int64_t node = half ? dst[e] : src[e];
     const float *xrow = x + (size_t)node * t.K * t.C + c;
     float *du_row = du_both + ((size_t)e * 2 + half) * t.K * t.C + c;
-    RotInBwdE<LMAX, LMAX>::run(t, xrow, stage, grad_radial + (size_t)e * t.R,
+    RotInBwdE<LMAX, LMAX>::run(t, xrow, stage, radial + (size_t)e * t.R,
+                               grad_radial + (size_t)e * t.R,
                                rot_s + slot * t.nnz_pad, part_all + warp * t.nnz_pad, du_row, c2,
                                active, lane);
   }
@@ -697,7 +694,7 @@ int zp_launch_rotate_in_bwd(const zp_plan *p, int64_t E, const float *da1, const
   const int nw = 4;                          // warps per block
   const int epb = nw / W;
   const dim3 grid((unsigned)zp_ceil_div(E, epb));
-  const size_t stage_rows = (size_t)t.Km + (size_t)t.R / (2 * t.C);
+  const size_t stage_rows = (size_t)t.Km;
   const size_t smem = ((size_t)(epb + nw) * t.nnz_pad + (size_t)nw * stage_rows * 128) * sizeof(float);
 #define CALL(LM)                                                                               \
   {                                                                                            \

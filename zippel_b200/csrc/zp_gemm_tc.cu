@@ -702,8 +702,7 @@ gemm_tc_pair_kernel(const __grid_constant__ CUtensorMap map_a,
 
   if (threadIdx.x == 0) {
     for (int s = 0; s < STAGES; ++s) { mbar_init(&full[s], 1); mbar_init(&empty[s], 1); }
-    mbar_init(&tmem_full[0], 1);
-    mbar_init(&tmem_empty[0], 16);
+    for (int b = 0; b < 2; ++b) { mbar_init(&tmem_full[b], 1); mbar_init(&tmem_empty[b], 16); }
     *abort_flag = 0;
     asm volatile("fence.mbarrier_init.release.cluster;" ::: "memory");
     asm volatile("fence.proxy.async.shared::cta;" ::: "memory");
@@ -778,10 +777,14 @@ gemm_tc_pair_kernel(const __grid_constant__ CUtensorMap map_a,
         const Work x = decode_work_pair(p, w);
         for (int c0 = x.kb0; c0 < x.kb1 && ok; c0 += p.kc, ++unit) {
           const int c1 = min(x.kb1, c0 + p.kc);
-          ok = mbar_wait(&tmem_empty[0], (unit & 1) ^ 1, abort_flag, p.status);
+          // one plane: the two accumulator buffers alternate, so the next tile's MMAs run
+          // while the epilogue drains this one
+          const int buf = P == 1 ? (int)(unit & 1) : 0;
+          const uint32_t round = P == 1 ? (unit >> 1) : unit;
+          ok = mbar_wait(&tmem_empty[buf], (round & 1) ^ 1, abort_flag, p.status);
           if (!ok) break;
           tcgen05_fence_after();
-          const uint32_t d_main = tmem_base;
+          const uint32_t d_main = tmem_base + (uint32_t)buf * kTmemBuf;
           const uint32_t d_small = tmem_base + kTmemBuf;
           for (int kb = c0; kb < c1 && ok; ++kb, ++it) {
             const int s = it % STAGES;
@@ -807,7 +810,7 @@ gemm_tc_pair_kernel(const __grid_constant__ CUtensorMap map_a,
             }
             tcgen05_commit_pair(&empty[s]);
           }
-          if (ok) tcgen05_commit_pair(&tmem_full[0]);
+          if (ok) tcgen05_commit_pair(&tmem_full[buf]);
         }
       }
     }
@@ -821,7 +824,8 @@ gemm_tc_pair_kernel(const __grid_constant__ CUtensorMap map_a,
     const float out_scale = (p.scale_a ? *p.scale_a : 1.f) * (p.scale_b ? *p.scale_b : 1.f);
     float seen_max = 0.f;
     const int col_lo = half * 128, col_hi = min(p.BN, col_lo + 128);
-    const uint32_t release_bar = map_to_cta(smem_u32(&tmem_empty[0]), 0);
+    const uint32_t release_bar0 = map_to_cta(smem_u32(&tmem_empty[0]), 0);
+    const uint32_t release_bar1 = map_to_cta(smem_u32(&tmem_empty[1]), 0);
     for (int w = pair; w < num_work && ok; w += num_pairs) {
       const Work x = decode_work_pair(p, w);
       const int row0 = x.m0 + (int)rank * BM + q * 32;
@@ -830,11 +834,13 @@ gemm_tc_pair_kernel(const __grid_constant__ CUtensorMap map_a,
       const float *bias = x.split == 0 ? p.bias : nullptr;
       for (int c0 = x.kb0; c0 < x.kb1 && ok; c0 += p.kc, ++unit) {
         const bool first = c0 == x.kb0;
-        ok = mbar_wait(&tmem_full[0], unit & 1, abort_flag, p.status);
+        const int buf = P == 1 ? (int)(unit & 1) : 0;
+        const uint32_t round = P == 1 ? (unit >> 1) : unit;
+        ok = mbar_wait(&tmem_full[buf], round & 1, abort_flag, p.status);
         ok = __all_sync(0xffffffffu, ok);
         if (!ok) break;
         tcgen05_fence_after();
-        const uint32_t t_row = tmem_base + ((uint32_t)(q * 32) << 16);
+        const uint32_t t_row = tmem_base + ((uint32_t)(q * 32) << 16) + (uint32_t)buf * kTmemBuf;
         float v[4][32];
 #pragma unroll
         for (int b = 0; b < 4; ++b) {
@@ -862,7 +868,7 @@ gemm_tc_pair_kernel(const __grid_constant__ CUtensorMap map_a,
         }
         tcgen05_fence_before();
         __syncwarp();
-        if (lane == 0) mbar_arrive_cluster(release_bar);
+        if (lane == 0) mbar_arrive_cluster(buf ? release_bar1 : release_bar0);
 
         if (L::kTmaEpilogue && p.tma_store) {
           epilogue_store_tma(p, &map_c, v, epi_stage, lane, row0, x.n0, col_lo, col_hi, x.split,
@@ -995,7 +1001,8 @@ int pick_bn(int64_t N, int cap, int step = 16) {
   return best;
 }
 
-// The CTA-pair kernel serves the two-plane (fp16) format unless the caller forces a kernel:
+// The CTA-pair kernel serves the two-plane (fp16) and one-plane (bf16) formats unless the caller
+// forces a kernel:
 // variant 2 = single-CTA kernel, variant 3 = pair kernel.
 bool pair_enabled() {
   static int on = -1;
@@ -1021,10 +1028,12 @@ double launch_score(const ZpGemmTc &g, bool pair, int splits) {
   const double pad = (double)(g.M * g.N) / (double)(tiles_m * tm * tiles_n * bn);
   const int64_t items = tiles_m * tiles_n * splits;
   const double wave = (double)items / (double)(zp_ceil_div(items, units) * units);
-  return pad * wave * (pair ? 1.12 : 1.0) - 0.004 * splits;
+  // one plane (one MMA pass per k-block) leans on the operand feed harder than two planes do
+  const double feed = !pair ? 1.0 : g.planes == 1 ? 1.25 : 1.12;
+  return pad * wave * feed - 0.004 * splits;
 }
 bool use_pair(const ZpGemmTc &g) {
-  if (g.planes != 2) return false;
+  if (g.planes != 2 && g.planes != 1) return false;
   if (g.variant == 2) return false;
   if (g.variant == 3) return true;
   if (!pair_enabled()) return false;
@@ -1185,7 +1194,8 @@ int zp_launch_gemm_tc(const ZpGemmTc &g, cudaStream_t st) {
   if ((reinterpret_cast<uintptr_t>(g.A) | reinterpret_cast<uintptr_t>(g.B) |
        reinterpret_cast<uintptr_t>(g.C)) & 15)
     return ZP_ERR_INVALID_ARG;
-  if (use_pair(g)) return launch_pair<2, 64, 3>(g, st);
+  if (use_pair(g))
+    return g.planes == 2 ? launch_pair<2, 64, 3>(g, st) : launch_pair<1, 64, 6>(g, st);
   if (g.a_mn || g.b_mn) {
     // MN-major tiles are [BK][64] blocks under the 128-byte swizzle
     if (g.planes == 3)

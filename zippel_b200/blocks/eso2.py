@@ -594,18 +594,24 @@ class ESO2Block(nn.Module):
 
     # -- forward --------------------------------------------------------------------------
     def _edges_to_nodes(self, plan, graph, perm, pos, atomic_numbers, x_node, shifts, cos_gamma_k,
-                        sin_gamma_k) -> torch.Tensor:
+                        sin_gamma_k, x_ready=None) -> torch.Tensor:
         """Geometry, radial features, envelope and the edge convolution for the edges of `graph`
         (whose original positions in the caller's arrays are `perm`)."""
         cfg = self.cfg
+
+        def conv(*args):
+            if x_ready is not None:        # x_node is still arriving on another stream
+                torch.cuda.current_stream(pos.device).wait_event(x_ready)
+            return edge_conv(*args)
+
         if cfg.edge_channels % 4 == 0 and graph.n_edges > 0:
             # geometry, distance basis, embeddings, envelope and the sorted copies in one pass
             edge_vec, x_edge, env, cos_s, sin_s = EdgeFeatures.apply(
                 graph, perm.to(torch.int32).contiguous(), self.front_config(), pos, shifts,
                 atomic_numbers, self.elem_emb.weight, self.gauss_offset, cos_gamma_k, sin_gamma_k)
             radial = self.radial_mlp(plan, x_edge)
-            return edge_conv(plan, graph, x_node, edge_vec, cos_s, sin_s, radial, env,
-                             self.c1_m0, self.c1_m, self.c2_m0, self.c2_m)
+            return conv(plan, graph, x_node, edge_vec, cos_s, sin_s, radial, env,
+                        self.c1_m0, self.c1_m, self.c2_m0, self.c2_m)
         src, dst = graph.src.long(), graph.dst.long()
         edge_vec = pos[dst] - pos[src] + shifts[perm]
         dist = edge_vec.pow(2).sum(-1).clamp_min(1e-24).sqrt()
@@ -613,12 +619,17 @@ class ESO2Block(nn.Module):
                             self.elem_emb(atomic_numbers[dst])], dim=-1)
         radial = self.radial_mlp(plan, x_edge)
         env = self.envelope(dist / cfg.cutoff)
-        return edge_conv(plan, graph, x_node, edge_vec, cos_gamma_k[perm], sin_gamma_k[perm],
-                         radial, env, self.c1_m0, self.c1_m, self.c2_m0, self.c2_m)
+        return conv(plan, graph, x_node, edge_vec, cos_gamma_k[perm], sin_gamma_k[perm],
+                    radial, env, self.c1_m0, self.c1_m, self.c2_m0, self.c2_m)
 
     def node_output(self, pos, atomic_numbers, x_node, edge_index, shifts, cos_gamma_k,
-                    sin_gamma_k, graph: EdgeGraph | None = None) -> torch.Tensor:
+                    sin_gamma_k, graph: EdgeGraph | None = None,
+                    x_ready: "torch.cuda.Event | None" = None) -> torch.Tensor:
         """pos -> node_out [N, K, C] (what the reference scatters at eso2_ref.py:346-349).
+
+        ``x_ready``: an event after which ``x_node`` is valid (its host-to-device copy runs on
+        another stream); the current stream waits for it only where the embeddings are first
+        read, so the copy overlaps the edge sort, the front end and the radial MLP.
 
         Graphs whose per-edge activations (radial features included) exceed the memory budget
         are processed as destination-node chunks under activation checkpointing: each chunk's
@@ -633,7 +644,9 @@ class ESO2Block(nn.Module):
         perm = graph.perm64
         if len(chunks) == 1:
             return self._edges_to_nodes(plan, graph, perm, pos, atomic_numbers, x_node, shifts,
-                                        cos_gamma_k, sin_gamma_k)
+                                        cos_gamma_k, sin_gamma_k, x_ready)
+        if x_ready is not None:
+            torch.cuda.current_stream(pos.device).wait_event(x_ready)
         from torch.utils.checkpoint import checkpoint
         outs = []
         for c in chunks:

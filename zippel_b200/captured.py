@@ -54,6 +54,7 @@ class CapturedStep:
         self.node_out = None
         self.graph = torch.cuda.CUDAGraph()
         self.stream = torch.cuda.Stream(device)
+        self.copy_stream = torch.cuda.Stream(device)
 
         # chunk sizing reads the free memory of the device, which a recording must not do: the
         # whole edge list is one piece here (construction fails if its workspace does not fit)
@@ -74,11 +75,26 @@ class CapturedStep:
 
     def _enqueue(self) -> None:
         dev = self.device
-        t = {k: v.to(dev, non_blocking=True) for k, v in self.host.items()}
+        main, side = torch.cuda.current_stream(dev), self.copy_stream
+        # the small arrays first, on this stream; the two [N, K, C] arrays follow on a second
+        # stream, so their transfer runs beside the edge sort, the front end and the radial MLP
+        # (the embeddings) and beside the forward (the upstream gradient)
+        big = ("x_node", "upstream")
+        t = {k: v.to(dev, non_blocking=True) for k, v in self.host.items() if k not in big}
+        side.wait_stream(main)
+        ready = {}
+        with torch.cuda.stream(side):
+            for k in big:
+                t[k] = self.host[k].to(dev, non_blocking=True)
+                ready[k] = torch.cuda.Event()
+                ready[k].record(side)
         pos = t["pos"].requires_grad_(True)
         x = t["x_node"].requires_grad_(True)
         node_out = self.block.node_output(pos, t["atomic_numbers"], x, t["edge_index"],
-                                          t["shifts"], t["cos_gamma_k"], t["sin_gamma_k"])
+                                          t["shifts"], t["cos_gamma_k"], t["sin_gamma_k"],
+                                          x_ready=ready["x_node"])
+        main.wait_event(ready["upstream"])
+        main.wait_stream(side)
         loss = (node_out * t["upstream"]).sum()
         g = torch.autograd.grad(loss, [x, pos, *self.params], allow_unused=True)
         self.grad_pos_host.copy_(g[1], non_blocking=True)

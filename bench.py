@@ -336,7 +336,7 @@ def run_ours(args) -> dict | None:
         barrier()
         return (time.perf_counter() - t0) / args.steps
 
-    e2e_eager_s = time_e2e(e2e_step)
+    e2e_eager_s = time_e2e(e2e_step) if not args.no_e2e else float("nan")
 
     # the same step recorded once as a CUDA graph (zippel_b200.captured.CapturedStep): pinned
     # host inputs -> device, edge sort, front end, radial MLP, edge convolution, VJP, results
@@ -345,6 +345,8 @@ def run_ours(args) -> dict | None:
     e2e_path = ("zippel_b200.captured.CapturedStep.run: the module forward + VJP from pinned host "
                 "inputs to pinned host results, replayed as one CUDA graph")
     try:
+        if args.no_e2e:
+            raise RuntimeError("--no-e2e")
         cap = CapturedStep(block, batch, dev)
     except RuntimeError as err:                 # recording refused: report the eager path
         cap, e2e_path = None, f"eager module path (recording failed: {str(err)[:120]})"
@@ -654,6 +656,8 @@ def main() -> None:
     ap.add_argument("--cpu-sample-nodes", type=int, default=800,
                     help="CPU legs evaluate the edges into the first this-many atoms")
     ap.add_argument("--no-cpu-baseline", action="store_true")
+    ap.add_argument("--no-e2e", action="store_true",
+                    help="profiling runs: skip both end-to-end legs (the line then has no valid e2e)")
     ap.add_argument("--precision", default="fp32", choices=["fp32", "fp32_bf16x3", "bf16"],
                     help="operand format of the SO(2) contraction (see ESO2Block)")
     ap.add_argument("--fixture", default="si_medium",

@@ -68,10 +68,12 @@ struct RotIn {
 #pragma unroll
     for (int j = 0; j < n; ++j) vload<4>(u[j], xrow + (size_t)(L * L + j) * t.C);
     const int mm = t.mmax < L ? t.mmax : L;
-#pragma unroll
-    for (int i = 0; i < n; ++i) {
+    // a real loop over the rows |m| <= mmax of this degree: one copy of the body per degree keeps
+    // the kernel's code inside the instruction cache
+#pragma unroll 1
+    for (int i = L - mm; i <= L + mm; ++i) {
       const int am = i > L ? i - L : L - i;
-      if (am <= mm) {
+      {
         const int r = t.row_of[L][i];
         const float *rr = rot_s + t.rot_off[r];
         float acc[4] = {0.f, 0.f, 0.f, 0.f};
@@ -338,10 +340,11 @@ struct GradOutE {
       for (int v = 0; v < 4; ++v) g[j][v] = 0.f;
       if (active) vload<4>(g[j], g_row + (size_t)(L * L + j) * t.C);
     }
-#pragma unroll
-    for (int i = 0; i < n; ++i) {
-      const int am = i > L ? i - L : L - i;
-      if (am <= mm) {
+    // a real loop over the rows |m| <= mmax of this degree (one copy of the body per degree: the
+    // unrolled form spent more time waiting for instructions than for data)
+#pragma unroll 1
+    for (int i = L - mm; i <= L + mm; ++i) {
+      {
         const int r = t.row_of[L][i];
         const float *rr = rot_s + t.rot_off[r];
         float yv[4] = {0.f, 0.f, 0.f, 0.f}, tv[4] = {0.f, 0.f, 0.f, 0.f}, part[n];
@@ -451,9 +454,10 @@ struct RotInBwdE {
       for (int v = 0; v < 4; ++v) { u[j][v] = 0.f; du[j][v] = 0.f; }
       if (active) vload<4>(u[j], xrow + (size_t)(L * L + j) * t.C);
     }
-#pragma unroll
-    for (int am = 0; am <= L; ++am) {
-      if (am <= mm) {
+    // a real loop over |m| (one copy of the body per degree keeps the code in the instruction cache)
+#pragma unroll 1
+    for (int am = 0; am <= mm; ++am) {
+      {
         float gr[4] = {0.f, 0.f, 0.f, 0.f}, rad[4] = {0.f, 0.f, 0.f, 0.f};
         const int col = t.rad_off[am] + (L - am) * C2 + c2;
         if (active) vload<4>(rad, rad_e + col);

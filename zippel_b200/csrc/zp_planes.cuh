@@ -39,18 +39,17 @@ __device__ __forceinline__ float zp_scale_for_bound(float bound) {
 }
 
 // writes VEC (2 or 4) consecutive values at element offset `idx` of every plane;
-// `inv` = zp_inv_scale(p), read once per thread
-template <int VEC>
-__device__ __forceinline__ void zp_store_planes(const ZpPlanes &p, int64_t idx, const float (&v)[VEC],
-                                                float inv = 1.f) {
-  float x[VEC];
+// `inv` = zp_inv_scale(p), read once per thread.  The format is chosen by ONE warp-uniform branch
+// around the whole conversion (a per-element choice makes the compiler issue both conversions).
+template <int VEC, bool FP16>
+__device__ __forceinline__ void zp_store_planes_fmt(const ZpPlanes &p, int64_t idx, float (&x)[VEC]) {
 #pragma unroll
-  for (int i = 0; i < VEC; ++i) x[i] = v[i] * inv;
-  for (int pl = 0; pl < p.planes; ++pl) {
+  for (int pl = 0; pl < 3; ++pl) {
+    if (pl >= p.planes) break;
     uint16_t h[VEC];
 #pragma unroll
     for (int i = 0; i < VEC; ++i) {
-      if (p.fp16) {
+      if (FP16) {
         const __half q = __float2half_rn(x[i]);
         h[i] = __half_as_ushort(q);
         x[i] -= __half2float(q);
@@ -70,6 +69,16 @@ __device__ __forceinline__ void zp_store_planes(const ZpPlanes &p, int64_t idx, 
       *reinterpret_cast<uint32_t *>(dst) = (uint32_t)h[0] | ((uint32_t)h[VEC - 1] << 16);
     }
   }
+}
+
+template <int VEC>
+__device__ __forceinline__ void zp_store_planes(const ZpPlanes &p, int64_t idx, const float (&v)[VEC],
+                                                float inv = 1.f) {
+  float x[VEC];
+#pragma unroll
+  for (int i = 0; i < VEC; ++i) x[i] = v[i] * inv;
+  if (p.fp16) zp_store_planes_fmt<VEC, true>(p, idx, x);
+  else zp_store_planes_fmt<VEC, false>(p, idx, x);
 }
 
 __device__ __forceinline__ float zp_plane_value(const ZpPlanes &p, uint16_t bits) {

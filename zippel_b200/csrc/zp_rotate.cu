@@ -382,7 +382,7 @@ struct GradOutE<-1, LMAX> {
 
 // shared memory: rot [epb][nnz_pad] | partial [8 warps][nnz_pad] | genv [8]
 template <int LMAX>
-__global__ void __launch_bounds__(kEdgeThreads)
+__global__ void __launch_bounds__(kEdgeThreads, 3)
 rotate_grad_out_kernel(const __grid_constant__ ZpTables t, int64_t E, int W,
                        const float *__restrict__ g_out, const float *__restrict__ y,
                        const float *__restrict__ env, const float *__restrict__ rot,

@@ -446,7 +446,6 @@ struct RotInBwdE {
     constexpr int n = 2 * L + 1;
     const int C2 = 2 * t.C;
     const int mm = t.mmax < L ? t.mmax : L;
-    cp_async_wait<LMAX - L>();             // the rows of levels 0..L have landed
     float u[n][4], du[n][4];
 #pragma unroll
     for (int j = 0; j < n; ++j) {
@@ -454,13 +453,20 @@ struct RotInBwdE {
       for (int v = 0; v < 4; ++v) { u[j][v] = 0.f; du[j][v] = 0.f; }
       if (active) vload<4>(u[j], xrow + (size_t)(L * L + j) * t.C);
     }
+    cp_async_wait<LMAX - L>();             // the rows of levels 0..L have landed
     // a real loop over |m| (one copy of the body per degree keeps the code in the instruction cache)
+    // the radial gains of the NEXT |m| are requested before this |m|'s rows are worked on
+    float rad_next[4] = {0.f, 0.f, 0.f, 0.f};
+    if (active) vload<4>(rad_next, rad_e + t.rad_off[0] + L * C2 + c2);
 #pragma unroll 1
     for (int am = 0; am <= mm; ++am) {
       {
-        float gr[4] = {0.f, 0.f, 0.f, 0.f}, rad[4] = {0.f, 0.f, 0.f, 0.f};
+        float gr[4] = {0.f, 0.f, 0.f, 0.f}, rad[4];
+#pragma unroll
+        for (int v = 0; v < 4; ++v) rad[v] = rad_next[v];
         const int col = t.rad_off[am] + (L - am) * C2 + c2;
-        if (active) vload<4>(rad, rad_e + col);
+        if (active && am < mm)
+          vload<4>(rad_next, rad_e + t.rad_off[am + 1] + (L - am - 1) * C2 + c2);
 #pragma unroll
         for (int sgn = 0; sgn < 2; ++sgn) {
           if (sgn == 1 && am == 0) continue;

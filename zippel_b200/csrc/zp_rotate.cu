@@ -70,21 +70,27 @@ struct RotIn {
     const int mm = t.mmax < L ? t.mmax : L;
     // a real loop over the rows |m| <= mmax of this degree: one copy of the body per degree keeps
     // the kernel's code inside the instruction cache
+    // the radial gain of the NEXT row is requested before this row's sums are formed
+    float g_next[4];
+    vload<4>(g_next, rad_e + t.rad_off[mm] + (L - mm) * C2 + c2);
 #pragma unroll 1
     for (int i = L - mm; i <= L + mm; ++i) {
-      const int am = i > L ? i - L : L - i;
       {
         const int r = t.row_of[L][i];
         const float *rr = rot_s + t.rot_off[r];
-        float acc[4] = {0.f, 0.f, 0.f, 0.f};
+        float acc[4] = {0.f, 0.f, 0.f, 0.f}, g[4];
+#pragma unroll
+        for (int v = 0; v < 4; ++v) g[v] = g_next[v];
+        if (i < L + mm) {
+          const int an = i + 1 > L ? i + 1 - L : L - i - 1;
+          vload<4>(g_next, rad_e + t.rad_off[an] + (L - an) * C2 + c2);
+        }
 #pragma unroll
         for (int j = 0; j < n; ++j) {
           const float w = rr[j];
 #pragma unroll
           for (int v = 0; v < 4; ++v) acc[v] = fmaf(w, u[j][v], acc[v]);
         }
-        float g[4];
-        vload<4>(g, rad_e + t.rad_off[am] + (L - am) * C2 + c2);
 #pragma unroll
         for (int v = 0; v < 4; ++v) acc[v] *= g[v];
         zp_store_planes<4>(a1, a_row + (int64_t)r * C2 + c2, acc, inv);
@@ -342,13 +348,18 @@ struct GradOutE {
     }
     // a real loop over the rows |m| <= mmax of this degree (one copy of the body per degree: the
     // unrolled form spent more time waiting for instructions than for data)
+    // the NEXT row of y is requested before this row's sums and reductions
+    float y_next[4] = {0.f, 0.f, 0.f, 0.f};
+    if (active) vload<4>(y_next, y_e + (size_t)t.row_of[L][L - mm] * t.C + c);
 #pragma unroll 1
     for (int i = L - mm; i <= L + mm; ++i) {
       {
         const int r = t.row_of[L][i];
         const float *rr = rot_s + t.rot_off[r];
-        float yv[4] = {0.f, 0.f, 0.f, 0.f}, tv[4] = {0.f, 0.f, 0.f, 0.f}, part[n];
-        if (active) vload<4>(yv, y_e + (size_t)r * t.C + c);
+        float yv[4], tv[4] = {0.f, 0.f, 0.f, 0.f}, part[n];
+#pragma unroll
+        for (int v = 0; v < 4; ++v) yv[v] = y_next[v];
+        if (active && i < L + mm) vload<4>(y_next, y_e + (size_t)t.row_of[L][i + 1] * t.C + c);
 #pragma unroll
         for (int j = 0; j < n; ++j) {
           const float w = rr[j];

@@ -75,7 +75,8 @@ __global__ void scale_kernel(float factor, const float *a, const float *b, const
 // ------------------------------------------------------------------------------------------
 __device__ __forceinline__ float sigmoidf(float x) { return 1.f / (1.f + __expf(-x)); }
 
-// One thread per (edge, row, hidden-channel quad).  With `gate_max` set it also records the largest
+// One thread per (edge, pair of rows, hidden-channel quad): both rows' loads are issued before
+// either is used, which doubles the bytes a thread keeps in flight.  With `gate_max` set it also records the largest
 // sigmoid'(gate) it sees: max|dht| * rows(l) * max|h1| * that value bounds the gate part of the
 // backward's dh1, which fixes the scale of its fp16 planes before they are written (the bound
 // follows the gates into saturation, where a constant 1/4 would be orders of magnitude loose).
@@ -86,30 +87,42 @@ __global__ void gate_fwd_kernel(const __grid_constant__ ZpTables t, int64_t E,
   // blockIdx.x counts groups of kGateEdges edges; the items of a group are indexed with 32-bit
   // arithmetic (a 64-bit division per thread would cost more than the rest of the kernel)
   const int H4 = t.H / 4;
-  const int per_edge = t.Km * H4;
+  const int per_edge = ((t.Km + 1) / 2) * H4;
   const int item = blockIdx.y * blockDim.x + threadIdx.x;            // within the group
   const int le = item / per_edge, rem = item - le * per_edge;
   const int64_t e0 = (int64_t)blockIdx.x * kGateEdges + le;
   const bool in_range = le < kGateEdges && e0 < E;
   const int64_t e = in_range ? e0 : 0;            // out-of-range threads recompute edge 0
-  const int r = rem / H4;
-  const int h = (rem - r * H4) * 4;
+  const int rp = rem / H4;
+  const int h = (rem - rp * H4) * 4;
   const float *row = h1 + (size_t)e * t.w1_cols;
-  const float4 x = *reinterpret_cast<const float4 *>(row + t.n_gate + r * t.H + h);
-  float o[4], seen = 0.f;
-  // every gate l is used by the m = 0 row r = l: those rows alone probe sigmoid'
-  const bool probe = gate_max != nullptr && r >= 1 && r <= t.lmax;
-  if (r == 0) {
-    o[0] = x.x * sigmoidf(x.x); o[1] = x.y * sigmoidf(x.y);
-    o[2] = x.z * sigmoidf(x.z); o[3] = x.w * sigmoidf(x.w);
-  } else {
-    const float4 g = *reinterpret_cast<const float4 *>(row + (t.row_l[r] - 1) * t.H + h);
-    const float s0 = sigmoidf(g.x), s1 = sigmoidf(g.y), s2 = sigmoidf(g.z), s3 = sigmoidf(g.w);
-    o[0] = x.x * s0; o[1] = x.y * s1; o[2] = x.z * s2; o[3] = x.w * s3;
-    if (probe)
-      seen = fmaxf(fmaxf(s0 * (1.f - s0), s1 * (1.f - s1)), fmaxf(s2 * (1.f - s2), s3 * (1.f - s3)));
+  float4 x[2], g[2];
+  int rk[2];
+#pragma unroll
+  for (int k = 0; k < 2; ++k) {
+    const int r = 2 * rp + k;
+    rk[k] = r < t.Km ? r : -1;
+    const int rr = r < t.Km ? r : 0;               // a missing second row re-reads row 0
+    x[k] = *reinterpret_cast<const float4 *>(row + t.n_gate + rr * t.H + h);
+    g[k] = rr == 0 ? x[k] : *reinterpret_cast<const float4 *>(row + (t.row_l[rr] - 1) * t.H + h);
   }
-  if (in_range) zp_store_planes<4>(ht, e * ht.ld + (int64_t)r * t.H + h, o, zp_inv_scale(ht));
+  float seen = 0.f;
+  bool probe = false;
+  const float inv = zp_inv_scale(ht);
+#pragma unroll
+  for (int k = 0; k < 2; ++k) {
+    const int r = rk[k];
+    // row 0: x * sigmoid(x) (g holds x there); other rows: x * sigmoid(gate of the row's degree)
+    const float s0 = sigmoidf(g[k].x), s1 = sigmoidf(g[k].y), s2 = sigmoidf(g[k].z), s3 = sigmoidf(g[k].w);
+    const float o[4] = {x[k].x * s0, x[k].y * s1, x[k].z * s2, x[k].w * s3};
+    // every gate l is used by the m = 0 row r = l: those rows alone probe sigmoid'
+    if (gate_max != nullptr && r >= 1 && r <= t.lmax) {
+      probe = true;
+      seen = fmaxf(seen, fmaxf(fmaxf(s0 * (1.f - s0), s1 * (1.f - s1)),
+                               fmaxf(s2 * (1.f - s2), s3 * (1.f - s3))));
+    }
+    if (in_range && r >= 0) zp_store_planes<4>(ht, e * ht.ld + (int64_t)r * t.H + h, o, inv);
+  }
   if (__any_sync(0xffffffffu, probe)) {
 #pragma unroll
     for (int k = 16; k > 0; k >>= 1) seen = fmaxf(seen, __shfl_xor_sync(0xffffffffu, seen, k));
@@ -382,7 +395,7 @@ int zp_launch_gate_fwd(const zp_plan *p, int64_t E, const float *h1, const ZpPla
                        float *gate_max, cudaStream_t st) {
   if (gate_max) ZP_CUDA(cudaMemsetAsync(gate_max, 0, sizeof(float), st));
   if (E == 0) return ZP_OK;
-  const int per_group = kGateEdges * p->t.Km * (p->t.H / 4);
+  const int per_group = kGateEdges * ((p->t.Km + 1) / 2) * (p->t.H / 4);
   const dim3 grid((unsigned)zp_ceil_div(E, kGateEdges), (unsigned)zp_ceil_div(per_group, 256));
   gate_fwd_kernel<<<grid, 256, 0, st>>>(p->t, E, h1, ht, gate_max);
   ZP_LAUNCH_CHECK("gate_fwd_kernel");

@@ -81,6 +81,7 @@ __device__ __forceinline__ float sigmoidf(float x) { return 1.f / (1.f + __expf(
 // backward's dh1, which fixes the scale of its fp16 planes before they are written (the bound
 // follows the gates into saturation, where a constant 1/4 would be orders of magnitude loose).
 constexpr int kGateEdges = 8;
+constexpr int kGateSub = 4;            // groups of kGateEdges edges per block of gate_fwd
 __global__ void gate_fwd_kernel(const __grid_constant__ ZpTables t, int64_t E,
                                 const float *__restrict__ h1, const ZpPlanes ht,
                                 float *gate_max) {
@@ -90,38 +91,42 @@ __global__ void gate_fwd_kernel(const __grid_constant__ ZpTables t, int64_t E,
   const int per_edge = ((t.Km + 1) / 2) * H4;
   const int item = blockIdx.y * blockDim.x + threadIdx.x;            // within the group
   const int le = item / per_edge, rem = item - le * per_edge;
-  const int64_t e0 = (int64_t)blockIdx.x * kGateEdges + le;
-  const bool in_range = le < kGateEdges && e0 < E;
-  const int64_t e = in_range ? e0 : 0;            // out-of-range threads recompute edge 0
   const int rp = rem / H4;
   const int h = (rem - rp * H4) * 4;
-  const float *row = h1 + (size_t)e * t.w1_cols;
-  float4 x[2], g[2];
-  int rk[2];
-#pragma unroll
-  for (int k = 0; k < 2; ++k) {
-    const int r = 2 * rp + k;
-    rk[k] = r < t.Km ? r : -1;
-    const int rr = r < t.Km ? r : 0;               // a missing second row re-reads row 0
-    x[k] = *reinterpret_cast<const float4 *>(row + t.n_gate + rr * t.H + h);
-    g[k] = rr == 0 ? x[k] : *reinterpret_cast<const float4 *>(row + (t.row_l[rr] - 1) * t.H + h);
-  }
   float seen = 0.f;
   bool probe = false;
   const float inv = zp_inv_scale(ht);
+  // a block walks kGateSub groups of kGateEdges edges: fewer, longer-lived blocks
+#pragma unroll 2
+  for (int sub = 0; sub < kGateSub; ++sub) {
+    const int64_t e0 = ((int64_t)blockIdx.x * kGateSub + sub) * kGateEdges + le;
+    const bool in_range = le < kGateEdges && e0 < E;
+    const int64_t e = in_range ? e0 : 0;            // out-of-range threads recompute edge 0
+    const float *row = h1 + (size_t)e * t.w1_cols;
+    float4 x[2], g[2];
+    int rk[2];
 #pragma unroll
-  for (int k = 0; k < 2; ++k) {
-    const int r = rk[k];
-    // row 0: x * sigmoid(x) (g holds x there); other rows: x * sigmoid(gate of the row's degree)
-    const float s0 = sigmoidf(g[k].x), s1 = sigmoidf(g[k].y), s2 = sigmoidf(g[k].z), s3 = sigmoidf(g[k].w);
-    const float o[4] = {x[k].x * s0, x[k].y * s1, x[k].z * s2, x[k].w * s3};
-    // every gate l is used by the m = 0 row r = l: those rows alone probe sigmoid'
-    if (gate_max != nullptr && r >= 1 && r <= t.lmax) {
-      probe = true;
-      seen = fmaxf(seen, fmaxf(fmaxf(s0 * (1.f - s0), s1 * (1.f - s1)),
-                               fmaxf(s2 * (1.f - s2), s3 * (1.f - s3))));
+    for (int k = 0; k < 2; ++k) {
+      const int r = 2 * rp + k;
+      rk[k] = r < t.Km ? r : -1;
+      const int rr = r < t.Km ? r : 0;               // a missing second row re-reads row 0
+      x[k] = *reinterpret_cast<const float4 *>(row + t.n_gate + rr * t.H + h);
+      g[k] = rr == 0 ? x[k] : *reinterpret_cast<const float4 *>(row + (t.row_l[rr] - 1) * t.H + h);
     }
-    if (in_range && r >= 0) zp_store_planes<4>(ht, e * ht.ld + (int64_t)r * t.H + h, o, inv);
+#pragma unroll
+    for (int k = 0; k < 2; ++k) {
+      const int r = rk[k];
+      // row 0: x * sigmoid(x) (g holds x there); other rows: x * sigmoid(gate of the row's degree)
+      const float s0 = sigmoidf(g[k].x), s1 = sigmoidf(g[k].y), s2 = sigmoidf(g[k].z), s3 = sigmoidf(g[k].w);
+      const float o[4] = {x[k].x * s0, x[k].y * s1, x[k].z * s2, x[k].w * s3};
+      // every gate l is used by the m = 0 row r = l: those rows alone probe sigmoid'
+      if (gate_max != nullptr && r >= 1 && r <= t.lmax) {
+        probe = true;
+        seen = fmaxf(seen, fmaxf(fmaxf(s0 * (1.f - s0), s1 * (1.f - s1)),
+                                 fmaxf(s2 * (1.f - s2), s3 * (1.f - s3))));
+      }
+      if (in_range && r >= 0) zp_store_planes<4>(ht, e * ht.ld + (int64_t)r * t.H + h, o, inv);
+    }
   }
   if (__any_sync(0xffffffffu, probe)) {
 #pragma unroll
@@ -312,7 +317,7 @@ __global__ void unfold_kernel(int out, int in, int folded, int splits, int64_t s
 // column sums in two fixed-order stages.  Stage one: a block of 32 x 8 threads sums 128 rows of
 // 256 columns; a thread owns 8 consecutive columns (one 16-byte load per row and plane) and every
 // eighth row, the eight row groups are then added in order through shared memory.
-constexpr int kColRowsPerBlock = 128;
+constexpr int kColRowsPerBlock = 512;    // scratch is sized for 128 (more partials than are used)
 __global__ void __launch_bounds__(256)
 colsum_part_kernel(int64_t rows, int64_t cols, const ZpPlanes a, float *__restrict__ part) {
   __shared__ float red[8][32][9];
@@ -396,7 +401,8 @@ int zp_launch_gate_fwd(const zp_plan *p, int64_t E, const float *h1, const ZpPla
   if (gate_max) ZP_CUDA(cudaMemsetAsync(gate_max, 0, sizeof(float), st));
   if (E == 0) return ZP_OK;
   const int per_group = kGateEdges * ((p->t.Km + 1) / 2) * (p->t.H / 4);
-  const dim3 grid((unsigned)zp_ceil_div(E, kGateEdges), (unsigned)zp_ceil_div(per_group, 256));
+  const dim3 grid((unsigned)zp_ceil_div(E, kGateEdges * kGateSub),
+                  (unsigned)zp_ceil_div(per_group, 256));
   gate_fwd_kernel<<<grid, 256, 0, st>>>(p->t, E, h1, ht, gate_max);
   ZP_LAUNCH_CHECK("gate_fwd_kernel");
   return ZP_OK;
@@ -435,7 +441,7 @@ int zp_launch_fold_weights(const zp_plan *p, const zp_weights *w, void *packed, 
     }
   if (p->fp16) {       // one power-of-two scale per weight block from its largest magnitude
     ZP_CUDA(cudaMemsetAsync(scales, 0, sizeof(float) * 4 * (ZP_MAX_L + 1), st));
-    weight_absmax_kernel<<<dim3(32, d.n), 256, 0, st>>>(d, scales);
+    weight_absmax_kernel<<<dim3(148, d.n), 256, 0, st>>>(d, scales);
     ZP_LAUNCH_CHECK("weight_absmax_kernel");
     weight_scale_kernel<<<1, 32, 0, st>>>(d, scales);
     ZP_LAUNCH_CHECK("weight_scale_kernel");

@@ -43,30 +43,37 @@ __device__ __forceinline__ float zp_scale_for_bound(float bound) {
 // around the whole conversion (a per-element choice makes the compiler issue both conversions).
 template <int VEC, bool FP16>
 __device__ __forceinline__ void zp_store_planes_fmt(const ZpPlanes &p, int64_t idx, float (&x)[VEC]) {
+  static_assert(VEC == 2 || VEC == 4, "pairs of values");
 #pragma unroll
   for (int pl = 0; pl < 3; ++pl) {
     if (pl >= p.planes) break;
-    uint16_t h[VEC];
+    // two values per conversion instruction (the one-value conversions run on the quarter-rate
+    // special-function pipe and were a large share of the producer kernels' time there)
+    uint32_t w[VEC / 2];
 #pragma unroll
-    for (int i = 0; i < VEC; ++i) {
+    for (int i = 0; i < VEC / 2; ++i) {
       if (FP16) {
-        const __half q = __float2half_rn(x[i]);
-        h[i] = __half_as_ushort(q);
-        x[i] -= __half2float(q);
+        const __half2 q = __floats2half2_rn(x[2 * i], x[2 * i + 1]);       // low half = first value
+        const float2 f = __half22float2(q);
+        x[2 * i] -= f.x;
+        x[2 * i + 1] -= f.y;
+        w[i] = *reinterpret_cast<const uint32_t *>(&q);
       } else {
-        const __nv_bfloat16 q = __float2bfloat16_rn(x[i]);
-        h[i] = __bfloat16_as_ushort(q);
-        x[i] -= __bfloat162float(q);
+        const __nv_bfloat162 q = __floats2bfloat162_rn(x[2 * i], x[2 * i + 1]);
+        const float2 f = __bfloat1622float2(q);
+        x[2 * i] -= f.x;
+        x[2 * i + 1] -= f.y;
+        w[i] = *reinterpret_cast<const uint32_t *>(&q);
       }
     }
     uint16_t *dst = static_cast<uint16_t *>(p.base) + (size_t)pl * p.plane_stride + idx;
     if (VEC == 4) {
       uint2 u;
-      u.x = (uint32_t)h[0] | ((uint32_t)h[1] << 16);
-      u.y = (uint32_t)h[2] | ((uint32_t)h[VEC - 1] << 16);
+      u.x = w[0];
+      u.y = w[VEC / 2 - 1];
       *reinterpret_cast<uint2 *>(dst) = u;
     } else {
-      *reinterpret_cast<uint32_t *>(dst) = (uint32_t)h[0] | ((uint32_t)h[VEC - 1] << 16);
+      *reinterpret_cast<uint32_t *>(dst) = w[0];
     }
   }
 }

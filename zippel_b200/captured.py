@@ -12,6 +12,11 @@ It plays the part of the reference back end's ``allocate`` + ``run_program``
 (codegen/compose.py:146-239: buffers allocated once, every run only launches) for the whole
 module call (blocks/eso2_ref.py:317-349 and autograd through it).
 
+The recording keeps every buffer of one step alive in the graph's private memory pool — inputs,
+radial features, the block's workspace (about 125 KB per edge at lmax 4 / C 128 in the fp32
+operand format) and all gradients — so the edge list must fit one call; graphs that need the
+chunked path cannot be recorded.
+
 Sizes are fixed at construction: the number of atoms and the number of edges (the edge list
 itself, the positions and every other value may change from step to step).  The parameters are
 read where they live, so in-place optimiser updates are seen by the next replay.

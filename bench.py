@@ -19,6 +19,8 @@ The line printed by rank 0 carries
                recorded once as a CUDA graph (CapturedStep) and replayed per step; `e2e_eager`
                is the same step enqueued from Python every time
     roofline   the dominant kernel class, timed live with CUDA events inside the library
+    kernels    per kernel class: ms, launches and share of the step; the HBM-bound classes also
+               carry their algorithmic bytes, GB/s and fraction of the measured copy bandwidth
     cpu_baseline  the CPU oracle timed on this machine's host cores on a bounded sample
 `--impl reference` times the reference algorithm's CPU restatement (the oracle) instead.
 """
@@ -66,6 +68,28 @@ def gemm_macs_per_edge(cfg) -> int:
         km = L + 1 - m
         total += (2 * km * 2 * C) * (2 * km * H) + (2 * km * H) * (2 * km * C)
     return total
+
+
+def hbm_bytes_per_step(block, n: int, e: int) -> dict:
+    """Algorithmic bytes one step moves in each HBM-bound kernel class (timing class names of the
+    library): fp32 arrays 4 bytes per value, 16-bit operand planes 2 bytes per value and plane."""
+    c = block.cfg
+    lay = block.layout
+    K, Km = (c.lmax + 1) ** 2, lay.m_size[0] + 2 * sum(lay.m_size[1:])
+    C, H, R = c.sphere_channels, c.hidden_channels, block.num_channels_rad
+    w1 = c.lmax * H + Km * H                     # gate head + rows of conv1's output
+    P = {2: 2, 0: 3, 1: 1}[block.precision]      # planes per operand
+    per_edge = {
+        "rotate_in": R * 4 + Km * 2 * C * 2 * P,
+        "gate_fwd": w1 * 4 + Km * H * 2 * P,
+        "rotate_back_scatter": Km * C * 4,
+        "rotate_grad_out": Km * C * 4 + Km * C * 2 * P,
+        "gate_bwd": w1 * 4 + Km * H * 4 + w1 * 2 * P,
+        "rotate_in_bwd": Km * 2 * C * 4 + 2 * R * 4 + 2 * K * C * 4,
+        "src_reduce": 2 * K * C * 4,
+    }
+    per_node = {"rotate_back_scatter": K * C * 4, "src_reduce": K * C * 4}
+    return {k: e * v + n * per_node.get(k, 0) for k, v in per_edge.items()}
 
 
 def xavier_(block, seed: int) -> None:
@@ -383,6 +407,13 @@ def run_ours(args) -> dict | None:
                    "share": v[0] / total_kernel_ms if total_kernel_ms else 0.0}
                for k, v in timing.items() if v[1]}
     launches = sum(v[1] for v in timing.values()) / args.steps
+    # HBM-side kernel classes: algorithmic bytes per step (each operand once; gathered node rows
+    # come from L2 and are not counted) against the measured copy bandwidth
+    for k, nbytes in hbm_bytes_per_step(block, n, e).items():
+        if k in kernels and kernels[k]["ms_per_step"] > 0:
+            gbs = nbytes / (kernels[k]["ms_per_step"] * 1e-3) / 1e9
+            kernels[k]["hbm"] = {"algorithmic_bytes": nbytes, "gbs": gbs,
+                                 "frac_of_measured_copy": gbs / peaks()[0]["hbm_gbs"]}
     # The dominant kernel is the tensor-core contraction: one kernel (gemm_tc_kernel) serving the
     # forward, input-gradient and weight-gradient products, 18 launches per step.
     gemm = [k for k in kernels if k.startswith("gemm")]

@@ -514,8 +514,9 @@ def run_large(args) -> dict | None:
     --precision is given), sharded over the ranks with no data-path exchange.  `--workload cfg4`:
     one graph of `--atoms` atoms at lmax 6, partitioned by destination-node range over the ranks
     (all-gather of embedding shards forward, reduce-scatter backward).  Inputs are resident on the
-    device; the step is the module API's forward + VJP, chunked over destination ranges when the
-    activations exceed memory (the backward then recomputes each chunk's forward)."""
+    device; the step is `ESO2Block.node_output_vjp` (per destination chunk the forward and at once
+    the backward), or with --recompute and for the partitioned graph `node_output` + autograd,
+    whose backward recomputes each chunk's forward."""
     import torch.distributed as dist
 
     from zippel_b200 import partition as part
@@ -561,7 +562,16 @@ def run_large(args) -> dict | None:
     graph = EdgeGraph.build(ei, n)
     e_local = ei.shape[1]
 
+    streamed = not args.recompute and not (args.workload == "cfg4" and world > 1)
+
     def step():
+        if streamed:
+            # chunk forward, then at once chunk backward: no forward is computed twice
+            _out, gx, gpos, gp = block.node_output_vjp(d["pos"], d["atomic_numbers"], x_in, ei, sh,
+                                                       cg, sg, up, graph=graph)
+            if world > 1:
+                part.all_reduce_grads([gpos, *[g_ for g_ in gp if g_ is not None]])
+            return gx, gpos, gp
         pos = d["pos"].detach().requires_grad_(True)
         x = x_in.detach().requires_grad_(True)
         if args.workload == "cfg4" and world > 1:
@@ -600,8 +610,11 @@ def run_large(args) -> dict | None:
                 "config": {"atoms_total": n if args.workload == "cfg4" else 200 * args.structures,
                            "edges_total": edges.item(), "lmax": cfg["lmax"], "mmax": cfg["mmax"],
                            "channels": cfg["sphere_channels"], "chunks_per_rank": chunks,
-                           "note": "module API forward+VJP, inputs resident; chunked runs "
-                                   "recompute the forward in the backward"},
+                           "note": ("ESO2Block.node_output_vjp, inputs resident: per destination "
+                                    "chunk the forward and at once the backward, no recompute"
+                                    if streamed else
+                                    "module API forward + autograd VJP, inputs resident; chunked "
+                                    "runs recompute the forward in the backward")},
                 "device_status": status, "peak_mem_gb": torch.cuda.max_memory_allocated(dev) / 1e9}
     if world > 1:
         dist.barrier()
@@ -696,6 +709,9 @@ def main() -> None:
                     help="with --workload fixture: which of the reference's structures")
     ap.add_argument("--workload", default="cfg2", choices=["cfg2", "cfg3", "cfg4", "fixture"],
                     help="cfg2 = the benchmark line; cfg3 / cfg4 = the larger configurations")
+    ap.add_argument("--recompute", action="store_true",
+                    help="cfg3 / cfg4: node_output + autograd (chunks recompute their forward) "
+                         "instead of the streamed node_output_vjp")
     ap.add_argument("--structures", type=int, default=512, help="cfg3: number of 200-atom structures")
     ap.add_argument("--atoms", type=int, default=N_ATOMS,
                     help="atoms per GPU; anything but the default is a profiling-size run, "

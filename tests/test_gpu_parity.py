@@ -251,3 +251,44 @@ def test_ir_program_dispatch(jd64):
     other.scale(meta["energy"], 2.0)
     with pytest.raises(UnsupportedProgram):
         compile_program(other, sizes)
+
+
+def test_streamed_vjp_without_recompute(monkeypatch):
+    """`node_output_vjp` (chunk forward, then at once chunk backward) against `node_output` +
+    autograd, for a fixed upstream tensor and for a per-row callable (loss = sum node_out^2)."""
+    from zippel_b200.blocks import eso2
+    from zippel_b200.graph import EdgeGraph
+    cfg = dict(lmax=3, mmax=2, sphere_channels=16, hidden_channels=8, edge_channels=8,
+               num_distance_basis=6, cutoff=5.0)
+    params = orc.init_params(cfg, seed=41)
+    case = random_case(cfg, 60, 3000, seed=42)
+    block = make_block(cfg, params)
+    dev = "cuda"
+    args = [case["pos"].to(dev, torch.float32), case["atomic_numbers"].to(dev),
+            case["x_node"].to(dev, torch.float32), case["edge_index"].to(dev),
+            case["shifts"].to(dev, torch.float32), case["cos_gamma_k"].to(dev, torch.float32),
+            case["sin_gamma_k"].to(dev, torch.float32)]
+    up = case["upstream"].to(dev, torch.float32)
+
+    def reference(loss_fn):
+        pos, x = args[0].clone().requires_grad_(True), args[2].clone().requires_grad_(True)
+        out = block.node_output(pos, args[1], x, *args[3:])
+        grads = torch.autograd.grad(loss_fn(out), [x, pos, *block.parameters()], allow_unused=True)
+        return out.detach(), grads
+
+    want_t, grads_t = reference(lambda o: (o * up).sum())
+    want_c, grads_c = reference(lambda o: (o * o).sum())
+
+    monkeypatch.setattr(eso2, "MAX_EDGES_PER_CALL", 2048)      # module-level pieces of <= 1024 edges
+    graph = EdgeGraph.build(args[3], 60)
+    assert len(graph.chunks(1024)) >= 3
+    for upstream, want, grads in ((up, want_t, grads_t),
+                                  (lambda rows, n0, n1: 2.0 * rows, want_c, grads_c)):
+        out, gx, gpos, gp = block.node_output_vjp(*args, upstream, graph=graph)
+        assert rel_l2(out, want) < 1e-5
+        assert rel_l2(gx, grads[0]) < 1e-5 and rel_l2(gpos, grads[1]) < 1e-5
+        for got_p, want_p, (name, _) in zip(gp, grads[2:], block.named_parameters()):
+            if want_p is None:
+                assert got_p is None, name
+            else:
+                assert rel_l2(got_p, want_p) < 1e-5, name

@@ -663,6 +663,59 @@ class ESO2Block(nn.Module):
                 outs.append(run(pos, x_node))
         return torch.cat(outs, dim=0)
 
+    def node_output_vjp(self, pos, atomic_numbers, x_node, edge_index, shifts, cos_gamma_k,
+                        sin_gamma_k, upstream, graph: EdgeGraph | None = None):
+        """node_out and the vector-Jacobian product of <node_out, upstream> in one sweep over
+        destination-node chunks, WITHOUT recomputing any forward.
+
+        A chunk's rows of node_out are final as soon as the chunk's forward has run (a chunk holds
+        every edge into its nodes), so when the upstream gradient of a row depends on that row
+        alone the chunk's backward can follow at once and its activations be dropped.  ``upstream``
+        is either the gradient tensor [N, K, C] or a callable ``(rows, n0, n1) -> gradient of
+        rows`` (e.g. the derivative of a per-atom readout, reference eso2_ref.py:351-362, evaluated
+        on rows ``n0:n1``).  ``node_output`` + autograd has to keep or recompute every chunk
+        (one extra forward per chunk); this entry point does three passes' worth of work instead
+        of four on graphs that do not fit one call.
+
+        Returns ``(node_out, grad_x_node, grad_pos, param_grads)`` with ``param_grads`` in the
+        order of ``self.parameters()`` (``None`` for parameters the node output does not use).
+        """
+        n = pos.shape[0]
+        if graph is None:
+            graph = EdgeGraph.build(edge_index, n)
+        plan = self.plan(pos.device)
+        budget = max(1024, _edge_budget(plan, n, graph.n_edges) // 2)
+        chunks = graph.chunks(budget)
+        perm = graph.perm64
+        params = list(self.parameters())
+        gx = torch.zeros_like(x_node)
+        gpos = torch.zeros_like(pos)
+        gparams: list = [None] * len(params)
+        outs = []
+        for c in chunks:
+            if len(chunks) > 1:
+                c.sub.node_range = (c.n0, c.n1)
+                sub_graph, sub_perm = c.sub, perm[c.e0:c.e1]
+            else:
+                sub_graph, sub_perm = graph, perm
+            pos_ = pos.detach().requires_grad_(True)
+            x_ = x_node.detach().requires_grad_(True)
+            with torch.enable_grad():
+                rows = self._edges_to_nodes(plan, sub_graph, sub_perm, pos_, atomic_numbers, x_,
+                                            shifts, cos_gamma_k, sin_gamma_k)
+            g_rows = (upstream(rows.detach(), c.n0, c.n1) if callable(upstream)
+                      else upstream[c.n0:c.n1])
+            grads = torch.autograd.grad(rows, [x_, pos_, *params], g_rows, allow_unused=True)
+            gx += grads[0]
+            gpos += grads[1]
+            for i, g in enumerate(grads[2:]):
+                if g is not None:
+                    gparams[i] = g if gparams[i] is None else gparams[i].add_(g)
+            outs.append(rows.detach())
+            del rows, grads, g_rows
+        node_out = outs[0] if len(outs) == 1 else torch.cat(outs, dim=0)
+        return node_out, gx, gpos, gparams
+
     def forward(self, pos, atomic_numbers, x_node, edge_index, shifts, cos_gamma_k, sin_gamma_k,
                 jd=None, graph: EdgeGraph | None = None) -> torch.Tensor:
         """Scalar E.  ``jd`` is accepted for signature compatibility; the kernels use the J

@@ -562,9 +562,14 @@ def run_large(args) -> dict | None:
     graph = EdgeGraph.build(ei, n)
     e_local = ei.shape[1]
 
-    streamed = not args.recompute and not (args.workload == "cfg4" and world > 1)
+    streamed = not args.recompute
 
     def step():
+        if streamed and args.workload == "cfg4" and world > 1:
+            _out, gx, gpos, gp = part.partitioned_node_output_vjp(
+                block, d["pos"], d["atomic_numbers"], x_in, ei, sh, cg, sg, up, nranges, rank,
+                graph=graph)
+            return gx, gpos, gp
         if streamed:
             # chunk forward, then at once chunk backward: no forward is computed twice
             _out, gx, gpos, gp = block.node_output_vjp(d["pos"], d["atomic_numbers"], x_in, ei, sh,

@@ -51,8 +51,15 @@ def _worker(rank: int, port: int, out_dir: str):
                                 [x_shard, pos, *block.parameters()], allow_unused=True)
     shared = [g.clone() if g is not None else None for g in grads[1:]]
     part.all_reduce_grads(shared)
+    # the same partition through the streamed sweep (no autograd graph across the collectives)
+    out2, gx2, gpos2, gp2 = part.partitioned_node_output_vjp(
+        block, pos.detach(), case["atomic_numbers"].to(dev), x_shard.detach(),
+        case["edge_index"][:, keep].to(dev), f(case["shifts"][keep]), f(case["cos_gamma_k"][keep]),
+        f(case["sin_gamma_k"][keep]), f(case["upstream"][a:b]), ranges, rank)
     torch.cuda.synchronize()
-    torch.save({"out": out.detach().cpu(), "gx": grads[0].cpu(), "gpos": shared[0].cpu(),
+    streamed = {"out": out2.cpu(), "gx": gx2.cpu(), "gpos": gpos2.cpu(),
+                "gw": {k: (g.cpu() if g is not None else None) for k, g in zip(names, gp2)}}
+    torch.save({"streamed": streamed, "out": out.detach().cpu(), "gx": grads[0].cpu(), "gpos": shared[0].cpu(),
                 "gw": {k: (g.cpu() if g is not None else None) for k, g in zip(names, shared[1:])},
                 "range": (a, b), "status": block.plan(dev).device_status()},
                os.path.join(out_dir, f"rank{rank}.pt"))
@@ -77,3 +84,9 @@ def test_two_gpu_destination_partition(tmp_path, jd64):
         assert rel_l2(got["gpos"], want_gpos) < 1e-5
         for k in ("c1_m0.weight", "c1_m.0.weight", "c2_m.1.weight", "c2_m0.bias", "rad_func.0.weight"):
             assert rel_l2(got["gw"][k], want_pg[k]) < 1e-5, k
+        st = got["streamed"]
+        assert rel_l2(st["out"], want_out[a:b]) < 1e-5
+        assert rel_l2(st["gx"], want_gx[a:b]) < 1e-5
+        assert rel_l2(st["gpos"], want_gpos) < 1e-5
+        for k in ("c1_m0.weight", "c1_m.0.weight", "c2_m.1.weight", "c2_m0.bias", "rad_func.0.weight"):
+            assert rel_l2(st["gw"][k], want_pg[k]) < 1e-5, k

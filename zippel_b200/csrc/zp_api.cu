@@ -61,7 +61,8 @@ struct Workspace {
 
 // slots of the device-side scale array (fp16-plane precision): raw maxima, derived scales, and
 // per weight block {max |W|, scale} from kScWeights on
-enum { kScX = 0, kScRad, kScG, kScH1, kScDht, kScA1, kScHt, kScDy, kScDh1, kScGate, kScWeights = 16,
+enum { kScX = 0, kScRad, kScG, kScH1, kScDht, kScA1, kScHt, kScDy, kScDh1, kScGate,
+       kScMaxNode /* an int */, kScWeights = 16,
        kScCount = kScWeights + 4 * (ZP_MAX_L + 1) };
 
 constexpr int kMaxWgradSplits = 8;
@@ -389,8 +390,12 @@ int zp_eso2_forward(const zp_plan *plan, int64_t N, int64_t E, const float *x_no
 
   if (plan->fp16) {
     // magnitude bounds -> power-of-two scales, all on the device:  |rot row . x| <= sqrt(2l+1) max|x|
-    ZP_TIMED(ZP_K_FOLD, zp_launch_absmax(N, (int64_t)t.K * t.C, x_node, (int64_t)t.K * t.C,
-                                         ws.scales + kScX, st));
+    // over every row the edges can name: a caller that asks for the rows of a node range passes
+    // that range's row count as N while its edges gather from the whole array
+    int *max_node = reinterpret_cast<int *>(ws.scales + kScMaxNode);
+    ZP_TIMED(ZP_K_FOLD, zp_launch_max_index(E, src, dst, max_node, st));
+    ZP_TIMED(ZP_K_FOLD, zp_launch_absmax_row_range(x_node, (int64_t)t.K * t.C, nullptr, max_node, N,
+                                                   ws.scales + kScX, st));
     ZP_TIMED(ZP_K_FOLD, zp_launch_absmax(E, t.R, radial, t.R, ws.scales + kScRad, st));
     ZP_TIMED(ZP_K_FOLD, zp_launch_scale(3.7f, ws.scales + kScX, ws.scales + kScRad, nullptr, 0.f,
                                         ws.scales + kScA1, st));
@@ -468,8 +473,14 @@ int zp_eso2_backward(const zp_plan *plan, int64_t N, int64_t E, const float *gra
   cudaDeviceGetAttribute(&sms, cudaDevAttrMultiProcessorCount, plan->device);
 
   if (plan->fp16) {
-    ZP_TIMED(ZP_K_ROTATE_GRAD_OUT, zp_launch_absmax(N, (int64_t)t.K * t.C, grad_node_out,
-                                                    (int64_t)t.K * t.C, ws.scales + kScG, st));
+    // only rows dst[0] .. dst[E-1] (the edges are destination-sorted): the rows the kernels read,
+    // and the only ones a caller that holds a node range's rows alone has
+    if (E > 0)
+      ZP_TIMED(ZP_K_ROTATE_GRAD_OUT,
+               zp_launch_absmax_row_range(grad_node_out, (int64_t)t.K * t.C, dst, dst + (E - 1), 0,
+                                          ws.scales + kScG, st));
+    else
+      ZP_CUDA(cudaMemsetAsync(ws.scales + kScG, 0, sizeof(float), st));
     ZP_TIMED(ZP_K_ROTATE_GRAD_OUT, zp_launch_scale(3.7f, ws.scales + kScG, nullptr, nullptr, 0.f,
                                                    ws.scales + kScDy, st));
   }

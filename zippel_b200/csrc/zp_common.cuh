@@ -151,6 +151,14 @@ int zp_launch_split_planes(int64_t rows, int64_t cols, const float *in, int64_t 
 // *out = max |in| (device scalar)
 int zp_launch_absmax(int64_t rows, int64_t cols, const float *in, int64_t ld, float *out,
                      cudaStream_t st);
+// *out = largest node index in src / dst (device scalar)
+int zp_launch_max_index(int64_t E, const int32_t *src, const int32_t *dst, int *out,
+                        cudaStream_t st);
+// *out = max |in| over rows [first ? *first : 0, max(min_rows, last ? *last + 1 : 0)) of a
+// contiguous [*, cols] matrix; first / last are device pointers to row numbers
+int zp_launch_absmax_row_range(const float *in, int64_t cols, const int32_t *first,
+                               const int32_t *last, int64_t min_rows, float *out,
+                               cudaStream_t st);
 // *scale = power of two mapping factor*a*b*max(offset_c, c_factor*c*d) to 2^15 (device scalars;
 // null = 1; without c the max term is left out)
 int zp_launch_scale(float factor, const float *a, const float *b, const float *c, float offset_c,

@@ -61,6 +61,40 @@ __global__ void absmax_kernel(int64_t rows, int64_t cols, const float *__restric
   if ((threadIdx.x & 31) == 0 && m > 0.f) zp_atomic_absmax(out, m);
 }
 
+// largest node index the edge list names (the caller zeroed *out)
+__global__ void max_index_kernel(int64_t E, const int32_t *__restrict__ src,
+                                 const int32_t *__restrict__ dst, int *out) {
+  int m = 0;
+  for (int64_t i = (int64_t)blockIdx.x * blockDim.x + threadIdx.x; i < E;
+       i += (int64_t)gridDim.x * blockDim.x)
+    m = max(m, max(src[i], dst[i]));
+#pragma unroll
+  for (int o = 16; o > 0; o >>= 1) m = max(m, __shfl_xor_sync(0xffffffffu, m, o));
+  if ((threadIdx.x & 31) == 0 && m > 0) atomicMax(out, m);
+}
+
+// max |x| over rows [r0, r1) of a contiguous [*, cols] matrix (cols a multiple of 4, 16-byte
+// aligned rows), the row numbers read from device memory:
+//   r0 = first ? *first : 0,   r1 = max(min_rows, last ? *last + 1 : 0)
+__global__ void absmax_row_range_kernel(const float *__restrict__ in, int64_t cols,
+                                        const int32_t *first, const int32_t *last,
+                                        int64_t min_rows, float *out) {
+  const int64_t r0 = first ? *first : 0;
+  int64_t r1 = last ? (int64_t)*last + 1 : 0;
+  if (r1 < min_rows) r1 = min_rows;
+  float m = 0.f;
+  const float4 *in4 = reinterpret_cast<const float4 *>(in + r0 * cols);
+  const int64_t n4 = (r1 > r0 ? r1 - r0 : 0) * cols / 4;
+  for (int64_t i = (int64_t)blockIdx.x * blockDim.x + threadIdx.x; i < n4;
+       i += (int64_t)gridDim.x * blockDim.x) {
+    const float4 v = in4[i];
+    m = fmaxf(fmaxf(m, fmaxf(fabsf(v.x), fabsf(v.y))), fmaxf(fabsf(v.z), fabsf(v.w)));
+  }
+#pragma unroll
+  for (int o = 16; o > 0; o >>= 1) m = fmaxf(m, __shfl_xor_sync(0xffffffffu, m, o));
+  if ((threadIdx.x & 31) == 0 && m > 0.f) zp_atomic_absmax(out, m);
+}
+
 // scale[0] = power of two mapping  factor * a * b * max(offset_c, c_factor * c * d)  to 2^15;
 // null pointers count as 1, the max term is left out when c is null
 __global__ void scale_kernel(float factor, const float *a, const float *b, const float *c,
@@ -386,6 +420,27 @@ int zp_launch_absmax(int64_t rows, int64_t cols, const float *in, int64_t ld, fl
   if (blocks > 1184) blocks = 1184;
   absmax_kernel<<<(unsigned)blocks, 256, 0, st>>>(rows, cols, in, ld, out);
   ZP_LAUNCH_CHECK("absmax_kernel");
+  return ZP_OK;
+}
+
+int zp_launch_max_index(int64_t E, const int32_t *src, const int32_t *dst, int *out,
+                        cudaStream_t st) {
+  ZP_CUDA(cudaMemsetAsync(out, 0, sizeof(int), st));
+  if (E == 0) return ZP_OK;
+  int64_t blocks = zp_ceil_div(E, 256 * 4);
+  if (blocks > 592) blocks = 592;
+  max_index_kernel<<<(unsigned)blocks, 256, 0, st>>>(E, src, dst, out);
+  ZP_LAUNCH_CHECK("max_index_kernel");
+  return ZP_OK;
+}
+
+int zp_launch_absmax_row_range(const float *in, int64_t cols, const int32_t *first,
+                               const int32_t *last, int64_t min_rows, float *out,
+                               cudaStream_t st) {
+  ZP_CUDA(cudaMemsetAsync(out, 0, sizeof(float), st));
+  if (cols == 0 || (cols & 3)) return cols ? ZP_ERR_INVALID_ARG : ZP_OK;
+  absmax_row_range_kernel<<<1184, 256, 0, st>>>(in, cols, first, last, min_rows, out);
+  ZP_LAUNCH_CHECK("absmax_row_range_kernel");
   return ZP_OK;
 }
 

@@ -47,35 +47,44 @@ def local_edges(edge_index: torch.Tensor, node_range: tuple[int, int]) -> torch.
     return torch.nonzero((dst >= node_range[0]) & (dst < node_range[1]), as_tuple=False).flatten()
 
 
+def gather_rows(shard: torch.Tensor, ranges, rank: int, group=None) -> torch.Tensor:
+    """All-gather of row shards ``[n_r, ...]`` into the full ``[N, ...]`` array (local memory)."""
+    n_max = max(b - a for a, b in ranges)
+    padded = shard.new_zeros((n_max, *shard.shape[1:]))
+    padded[: shard.shape[0]] = shard
+    parts = [torch.empty_like(padded) for _ in ranges]
+    dist.all_gather(parts, padded.contiguous(), group=group)
+    return torch.cat([p[: b - a] for p, (a, b) in zip(parts, ranges)], dim=0)
+
+
+def scatter_sum_rows(grad_full: torch.Tensor, ranges, rank: int, group=None) -> torch.Tensor:
+    """Sum of the ranks' full ``[N, ...]`` arrays, each rank keeping its own rows."""
+    a, b = ranges[rank]
+    if dist.get_backend(group) == "nccl":
+        n_max = max(y - x for x, y in ranges)
+        padded = grad_full.new_zeros((len(ranges), n_max, *grad_full.shape[1:]))
+        for i, (x, y) in enumerate(ranges):
+            padded[i, : y - x] = grad_full[x:y]
+        out = torch.empty_like(padded[0])
+        dist.reduce_scatter_tensor(out, padded, op=dist.ReduceOp.SUM, group=group)
+        return out[: b - a]
+    total = grad_full.contiguous().clone()
+    dist.all_reduce(total, op=dist.ReduceOp.SUM, group=group)
+    return total[a:b]
+
+
 class GatherRows(torch.autograd.Function):
-    """All-gather of row shards ``[n_r, ...]`` into the full ``[N, ...]`` array; its VJP is the
-    reduce-scatter (sum) of the full gradient back to the shards."""
+    """``gather_rows`` with its VJP, the reduce-scatter (sum) of the full gradient back to the
+    shards."""
 
     @staticmethod
     def forward(ctx, shard: torch.Tensor, ranges, rank: int, group):
         ctx.ranges, ctx.rank, ctx.group = ranges, rank, group
-        n_max = max(b - a for a, b in ranges)
-        padded = shard.new_zeros((n_max, *shard.shape[1:]))
-        padded[: shard.shape[0]] = shard
-        parts = [torch.empty_like(padded) for _ in ranges]
-        dist.all_gather(parts, padded.contiguous(), group=group)
-        return torch.cat([p[: b - a] for p, (a, b) in zip(parts, ranges)], dim=0)
+        return gather_rows(shard, ranges, rank, group)
 
     @staticmethod
     def backward(ctx, grad_full: torch.Tensor):
-        ranges, rank, group = ctx.ranges, ctx.rank, ctx.group
-        a, b = ranges[rank]
-        if dist.get_backend(group) == "nccl":
-            n_max = max(y - x for x, y in ranges)
-            padded = grad_full.new_zeros((len(ranges), n_max, *grad_full.shape[1:]))
-            for i, (x, y) in enumerate(ranges):
-                padded[i, : y - x] = grad_full[x:y]
-            out = torch.empty_like(padded[0])
-            dist.reduce_scatter_tensor(out, padded, op=dist.ReduceOp.SUM, group=group)
-            return out[: b - a], None, None, None
-        total = grad_full.contiguous().clone()
-        dist.all_reduce(total, op=dist.ReduceOp.SUM, group=group)
-        return total[a:b], None, None, None
+        return scatter_sum_rows(grad_full, ctx.ranges, ctx.rank, ctx.group), None, None, None
 
 
 def partitioned_node_output(node_output_fn, pos, atomic_numbers, x_shard, edge_index, shifts,
@@ -92,6 +101,34 @@ def partitioned_node_output(node_output_fn, pos, atomic_numbers, x_shard, edge_i
     out = node_output_fn(pos, atomic_numbers, x_full, edge_index, shifts, cos_gamma_k, sin_gamma_k)
     a, b = ranges[rank]
     return out[a:b]
+
+
+def partitioned_node_output_vjp(block, pos, atomic_numbers, x_shard, edge_index, shifts,
+                                cos_gamma_k, sin_gamma_k, upstream_shard, ranges, rank: int,
+                                graph=None, group=None):
+    """Destination-range partition through ``ESO2Block.node_output_vjp``: per destination chunk
+    the forward and at once the backward, nothing recomputed.
+
+    Arguments as ``partitioned_node_output``; ``upstream_shard`` is the gradient with respect to
+    this rank's rows of ``node_out``.  Returns ``(node_out rows, grad of x_shard, grad_pos,
+    param_grads)``; ``grad_pos`` and ``param_grads`` are already summed over the ranks.
+    """
+    a, b = ranges[rank]
+    x_full = gather_rows(x_shard.detach(), ranges, rank, group)
+
+    def upstream(rows, n0, n1):                   # rows outside this rank's range carry no gradient
+        g = torch.zeros_like(rows)
+        lo, hi = max(n0, a), min(n1, b)
+        if hi > lo:
+            g[lo - n0:hi - n0] = upstream_shard[lo - a:hi - a]
+        return g
+
+    out, gx_full, gpos, gparams = block.node_output_vjp(
+        pos, atomic_numbers, x_full, edge_index, shifts, cos_gamma_k, sin_gamma_k, upstream,
+        graph=graph)
+    gx = scatter_sum_rows(gx_full, ranges, rank, group)
+    all_reduce_grads([gpos, *gparams], group)
+    return out[a:b], gx, gpos, gparams
 
 
 def all_reduce_grads(tensors, group=None) -> None:

@@ -162,7 +162,10 @@ size_t zp_workspace_bytes(const zp_plan *plan, int64_t n_nodes, int64_t n_edges,
  * (rot_e [x_src ; x_dst])))).  Replaces blocks/eso2_ref.py:334-349 and the 55-kernel program
  * run by codegen/compose.py:218-239.  x_node, node_out [N, K, C]; edge_vec [E,3];
  * cos_g, sin_g [E, lmax+1]; radial [E, R]; env [E]; src, dst [E]; row_ptr [N+1].
- * node_out is overwritten (rows without incoming edges become zero).                       */
+ * node_out is overwritten (rows without incoming edges become zero).
+ * Node ranges: to get rows n0..n1 only, pass n_nodes = n1 - n0, row_ptr + n0 and a node_out of
+ * n1 - n0 rows with the edges into those nodes; src / dst keep the numbering of x_node, which
+ * then has more than n_nodes rows (every row an edge names is read, no other).             */
 int zp_eso2_forward(const zp_plan *plan, int64_t n_nodes, int64_t n_edges,
                     const float *x_node, const float *edge_vec, const float *cos_g,
                     const float *sin_g, const float *radial, const float *env,
@@ -174,7 +177,10 @@ int zp_eso2_forward(const zp_plan *plan, int64_t n_nodes, int64_t n_edges,
  * blocks/eso2_ref.py:334-349; IR rule zippel/vjp.py:88-153).  Needs the workspace of the
  * matching forward call.  Outputs (all overwritten): grad_x_node [N,K,C]; grad_edge_vec
  * [E,3] (through the rotation only); grad_radial [E,R]; grad_env [E]; weight gradients in
- * the reference layout.  perm_src / row_ptr_src: the source-sorted view from zp_csr_build.  */
+ * the reference layout.  perm_src / row_ptr_src: the source-sorted view from zp_csr_build.
+ * grad_node_out is indexed by dst and read at rows dst[0] .. dst[E-1] only (the edges are
+ * destination-sorted), so a caller holding the gradient of rows n0..n1 alone passes that
+ * array's address minus n0 rows.                                                            */
 int zp_eso2_backward(const zp_plan *plan, int64_t n_nodes, int64_t n_edges,
                      const float *grad_node_out, const float *x_node, const float *edge_vec,
                      const float *cos_g, const float *sin_g, const float *radial,

@@ -79,17 +79,23 @@ def hbm_bytes_per_step(block, n: int, e: int) -> dict:
     C, H, R = c.sphere_channels, c.hidden_channels, block.num_channels_rad
     w1 = c.lmax * H + Km * H                     # gate head + rows of conv1's output
     P = {2: 2, 0: 3, 1: 1}[block.precision]      # planes per operand
+    # with the fused epilogues (one- and two-plane formats) the gate activation and the rotation
+    # back run inside the contractions; what is left of the scatter is the sum of the per-row
+    # partial sums (one slab of nnz x C values per node and one per 32-edge block)
+    fused = P != 3 and os.environ.get("ZP_FUSED_EPILOGUE", "1") != "0"
+    nnz = sum((2 * min(l, c.mmax) + 1) * (2 * l + 1) for l in range(c.lmax + 1))
     per_edge = {
         "rotate_in": R * 4 + Km * 2 * C * 2 * P,
-        "gate_fwd": w1 * 4 + Km * H * 2 * P,
-        "rotate_back_scatter": Km * C * 4,
+        **({} if fused else {"gate_fwd": w1 * 4 + Km * H * 2 * P}),
+        "rotate_back_scatter": nnz * C * 4 / 32 if fused else Km * C * 4,
         "rotate_grad_out": Km * C * 4 + Km * C * 2 * P,
         "gate_bwd": w1 * 4 + Km * H * 4 + w1 * 2 * P,
         "rotate_in_bwd": Km * 2 * C * 4 + 2 * R * 4 + 2 * K * C * 4,
         "src_reduce": 2 * K * C * 4,
     }
-    per_node = {"rotate_back_scatter": K * C * 4, "src_reduce": K * C * 4}
-    return {k: e * v + n * per_node.get(k, 0) for k, v in per_edge.items()}
+    per_node = {"rotate_back_scatter": K * C * 4 + (nnz * C * 4 if fused else 0),
+                "src_reduce": K * C * 4}
+    return {k: int(e * v + n * per_node.get(k, 0)) for k, v in per_edge.items()}
 
 
 def xavier_(block, seed: int) -> None:

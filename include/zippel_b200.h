@@ -153,8 +153,13 @@ typedef struct zp_weight_grads {
   float *const *c2_wm;
 } zp_weight_grads;
 
-/* Bytes of scratch + saved activations for E edges / N nodes.  The same workspace must be
- * passed to zp_eso2_forward and to the zp_eso2_backward that follows it.                   */
+/* Bytes of scratch + saved activations for E edges / N nodes (N = the n_nodes given to the
+ * forward call it serves; the backward's share does not depend on it).  with_backward = ZP_WS_FORWARD: zp_eso2_forward alone; ZP_WS_BACKWARD:
+ * zp_eso2_forward and the zp_eso2_backward that follows it, which must get the same workspace;
+ * ZP_WS_INFERENCE: zp_eso2_forward_inference.                                                */
+#define ZP_WS_FORWARD 0
+#define ZP_WS_BACKWARD 1
+#define ZP_WS_INFERENCE 2
 size_t zp_workspace_bytes(const zp_plan *plan, int64_t n_nodes, int64_t n_edges,
                           int with_backward);
 
@@ -172,6 +177,19 @@ int zp_eso2_forward(const zp_plan *plan, int64_t n_nodes, int64_t n_edges,
                     const int32_t *src, const int32_t *dst, const int32_t *row_ptr,
                     const zp_weights *w, float *node_out, void *workspace,
                     size_t workspace_bytes, void *stream);
+
+/* zp_eso2_forward for callers that will not ask for gradients (the reference under
+ * torch.no_grad(): blocks/eso2_ref.py:334-349 with nothing saved for autograd).  Same arguments
+ * and result; the workspace (ZP_WS_INFERENCE) is smaller because conv1's pre-activation rows and
+ * conv2's output are consumed on chip by the epilogues of the contractions (gate activation;
+ * envelope, rotation back and the per-node sums) and never written.  zp_eso2_backward cannot
+ * follow this call.                                                                          */
+int zp_eso2_forward_inference(const zp_plan *plan, int64_t n_nodes, int64_t n_edges,
+                              const float *x_node, const float *edge_vec, const float *cos_g,
+                              const float *sin_g, const float *radial, const float *env,
+                              const int32_t *src, const int32_t *dst, const int32_t *row_ptr,
+                              const zp_weights *w, float *node_out, void *workspace,
+                              size_t workspace_bytes, void *stream);
 
 /* First-order VJP of zp_eso2_forward (what torch.autograd.grad computes through
  * blocks/eso2_ref.py:334-349; IR rule zippel/vjp.py:88-153).  Needs the workspace of the

@@ -61,6 +61,8 @@ SIGNATURES = {
     "zp_workspace_bytes": (_SZ, [_P, _I64, _I64, C.c_int]),
     "zp_eso2_forward": (C.c_int, [_P, _I64, _I64] + [_P] * 9 + [C.POINTER(ZpWeights), _P, _P,
                                                                 _SZ, _P]),
+    "zp_eso2_forward_inference": (C.c_int, [_P, _I64, _I64] + [_P] * 9 + [C.POINTER(ZpWeights), _P,
+                                                                          _P, _SZ, _P]),
     "zp_eso2_backward": (C.c_int, [_P, _I64, _I64] + [_P] * 12 + [C.POINTER(ZpWeights)]
                          + [_P] * 4 + [C.POINTER(ZpWeights), _P, _SZ, _P]),
     "zp_split_planes": (C.c_int, [_I64, _I64, _P, _I64, _P, _I64, _I64, C.c_int, _P]),

@@ -151,8 +151,11 @@ class Plan:
                    "zp_plan_device_status")
         return st.value
 
-    def workspace(self, n: int, e: int, with_backward: bool) -> torch.Tensor:
-        nbytes = _lib.load().zp_workspace_bytes(self.handle, n, e, int(with_backward))
+    def workspace(self, n: int, e: int, with_backward: bool, inference: bool = False) -> torch.Tensor:
+        """Workspace of one forward (+ backward) call over ``e`` edges and ``n`` node rows;
+        ``inference``: for ``zp_eso2_forward_inference`` (nothing kept for a backward)."""
+        mode = 1 if with_backward else (2 if inference else 0)
+        nbytes = _lib.load().zp_workspace_bytes(self.handle, n, e, mode)
         return torch.empty(max(nbytes, 16), dtype=torch.uint8, device=self.device)
 
 
@@ -188,12 +191,18 @@ def _edge_budget(plan: Plan, n: int, e: int) -> int:
     return max(1024, int(0.5 * free / max(per_edge, 1.0)))
 
 
-def _abi_forward(plan, n_rows, e, x, ev, cg, sg, rad, en, src, dst, row_ptr, wstruct, out, ws):
+def _abi_forward(plan, n_rows, e, x, ev, cg, sg, rad, en, src, dst, row_ptr, wstruct, out, ws,
+                 inference: bool = False):
+    """``inference``: nothing is kept for a backward (``zp_eso2_forward_inference``; ``ws`` sized
+    for it)."""
     st = torch.cuda.current_stream().cuda_stream
-    _lib.check(_lib.load().zp_eso2_forward(
+    lib = _lib.load()
+    fn = lib.zp_eso2_forward_inference if inference else lib.zp_eso2_forward
+    _lib.check(fn(
         plan.handle, n_rows, e, x.data_ptr(), ev.data_ptr(), cg.data_ptr(), sg.data_ptr(),
         rad.data_ptr(), en.data_ptr(), src.data_ptr(), dst.data_ptr(), row_ptr.data_ptr(),
-        ctypes.byref(wstruct), out.data_ptr(), ws.data_ptr(), ws.numel(), st), "zp_eso2_forward")
+        ctypes.byref(wstruct), out.data_ptr(), ws.data_ptr(), ws.numel(), st),
+        "zp_eso2_forward_inference" if inference else "zp_eso2_forward")
 
 
 def _abi_backward(plan, n, e, g_ptr: int, x, ev, cg, sg, rad, en, sub: EdgeGraph, wstruct, gx, gev,
@@ -241,16 +250,18 @@ class EdgeConvFunction(torch.autograd.Function):
             chunks = ([EdgeChunk(0, e, 0, n, graph)] if rng is not None
                       else graph.chunks(_edge_budget(plan, n, e)))
             if len(chunks) == 1:
-                ws = plan.workspace(n, e, needs_bwd)
+                ws = plan.workspace(n1 - n0, e, needs_bwd, inference=not needs_bwd)
                 _abi_forward(plan, n1 - n0, e, x, ev, cg, sg, rad, en, graph.src, graph.dst,
-                             graph.row_ptr[n0:], wstruct, out, ws)
+                             graph.row_ptr[n0:], wstruct, out, ws, inference=not needs_bwd)
             else:
-                ws = plan.workspace(n, max(c.n_edges for c in chunks), False)
+                # the backward recomputes each chunk, so no chunk keeps anything here
+                ws = plan.workspace(max(c.n1 - c.n0 for c in chunks),
+                                    max(c.n_edges for c in chunks), False, inference=True)
                 for c in chunks:
                     sl = slice(c.e0, c.e1)
                     _abi_forward(plan, c.n1 - c.n0, c.n_edges, x, ev[sl], cg[sl], sg[sl], rad[sl],
                                  en[sl], c.sub.src, c.sub.dst, c.sub.row_ptr[c.n0:],
-                                 wstruct, out[c.n0:c.n1], ws)
+                                 wstruct, out[c.n0:c.n1], ws, inference=True)
                 ws = None
         del keep
         if needs_bwd:
@@ -289,7 +300,8 @@ class EdgeConvFunction(torch.autograd.Function):
             else:
                 # per chunk: recompute its forward into the shared workspace, then its backward;
                 # node and weight gradients add up over chunks, per-edge gradients are slices
-                ws = plan.workspace(n, max(c.n_edges for c in chunks), True)
+                ws = plan.workspace(max(c.n1 - c.n0 for c in chunks),
+                                    max(c.n_edges for c in chunks), True)
                 gx_c = torch.empty_like(gx)
                 gws_c = [torch.empty_like(t) for t in gws]
                 cstruct, keep3 = _weights_struct(mmax, gws_c[0], gws_c[1], gws_c[4:4 + mmax],

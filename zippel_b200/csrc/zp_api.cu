@@ -1,6 +1,7 @@
 // C ABI of zippel_b200: plan/tables, workspace carving, and the forward / backward drivers
 // that sequence the kernels on the caller's stream.
 #include <cstdio>
+#include <cstdlib>
 #include <cstring>
 #include <new>
 #include <vector>
@@ -50,10 +51,13 @@ thread_local int64_t g_launches = 0;
 bool aligned16(const void *p) { return (reinterpret_cast<uintptr_t>(p) & 15u) == 0; }
 
 // Workspace carving; every region starts 256-byte aligned.
-//   forward:  rot | a1 planes | h1 | ht planes | y | folded weight planes
+//   forward:  rot | a1 planes | h1 | ht planes | y | folded weight planes | head, cont partials
 //   backward: dy planes | dht | dh1 planes | da1 | du_src | grot | wgrad partials | scratch
+// mode 0 / 1: forward that keeps what a backward reads (1: plus the backward's own regions);
+// mode 2: forward alone with fused epilogues -- of h1 only the gate scalars exist, y does not.
 struct Workspace {
-  float *rot, *h1, *y, *dht, *da1, *du_src, *grot, *wgrad, *scratch, *scales;
+  float *rot, *h1, *y, *dht, *da1, *du_src, *grot, *wgrad, *scratch, *scales, *head, *cont;
+  int64_t ld_h1;
   ZpPlanes a1, ht, dy, dh1;
   uint16_t *wfold;
   size_t bytes;
@@ -66,11 +70,30 @@ enum { kScX = 0, kScRad, kScG, kScH1, kScDht, kScA1, kScHt, kScDy, kScDh1, kScGa
        kScCount = kScWeights + 4 * (ZP_MAX_L + 1) };
 
 constexpr int kMaxWgradSplits = 8;
+constexpr int kChunkK = 2048;          // contraction length of one TMEM accumulation chunk
 
 int64_t round8(int64_t x) { return (x + 7) / 8 * 8; }
 
-Workspace carve(const zp_plan *p, int64_t N, int64_t E, int with_backward, void *base) {
-  (void)N;
+// The fused epilogues (gate activation in conv1, rotation back + segmented sums in conv2) need
+// one- or two-plane operands and contractions that fit one accumulation chunk.  ZP_FUSED_EPILOGUE=0
+// in the environment turns them off (for A/B measurements).
+bool fused_enabled() {
+  static int on = -1;
+  if (on < 0) {
+    const char *e = getenv("ZP_FUSED_EPILOGUE");
+    on = (e && e[0] == '0') ? 0 : 1;
+  }
+  return on == 1;
+}
+bool can_fuse(const zp_plan *p, int conv) {
+  if (!fused_enabled() || p->planes == 3) return false;
+  if ((conv ? p->t.C : p->t.H) % 4) return false;
+  for (int m = 0; m < p->n_blocks; ++m)
+    if ((conv ? p->c2_in[m] : p->c1_in[m]) > kChunkK) return false;
+  return true;
+}
+
+Workspace carve(const zp_plan *p, int64_t N, int64_t E, int mode, void *base) {
   const ZpTables &t = p->t;
   Workspace w;
   std::memset(&w, 0, sizeof(w));
@@ -92,14 +115,25 @@ Workspace carve(const zp_plan *p, int64_t N, int64_t E, int with_backward, void 
     return pl;
   };
   const size_t e = (size_t)E;
+  const bool lean = mode == 2 && can_fuse(p, 0) && can_fuse(p, 1);
   w.rot = takef(e * t.nnz_pad);
   w.a1 = takep((int64_t)t.Km * 2 * t.C);
-  w.h1 = takef(e * t.w1_cols);
+  w.ld_h1 = lean ? t.n_gate : t.w1_cols;
+  w.h1 = takef(e * w.ld_h1);
   w.ht = takep((int64_t)t.Km * t.H);
-  w.y = takef(e * t.Km * t.C);
+  if (!lean) w.y = takef(e * t.Km * t.C);
   w.wfold = reinterpret_cast<uint16_t *>(take((size_t)p->w_elems * 2));
   w.scales = takef(kScCount);
-  if (with_backward) {
+  // the partial sums of the rotate-back epilogue live only inside the forward: the backward's own
+  // regions start at the same offset and reuse the space
+  const size_t off_fwd = off;
+  if (can_fuse(p, 1)) {
+    w.head = takef((size_t)N * t.nnz * t.C);
+    w.cont = takef((size_t)zp_ceil_div(E, 32) * t.nnz * t.C);
+  }
+  const size_t end_fwd = off;
+  if (mode == 1) {
+    off = off_fwd;
     w.dy = takep((int64_t)t.Km * t.C);
     w.dht = takef(e * t.Km * t.H);
     w.dh1 = takep(t.w1_cols);
@@ -115,7 +149,7 @@ Workspace carve(const zp_plan *p, int64_t N, int64_t E, int with_backward, void 
     w.dy.scale = w.scales + kScDy;
     w.dh1.scale = w.scales + kScDh1;
   }
-  w.bytes = off;
+  w.bytes = off > end_fwd ? off : end_fwd;
   return w;
 }
 
@@ -357,7 +391,7 @@ int zp_wigner_backward(const zp_plan *plan, int64_t n_edges, const float *edge_v
 
 size_t zp_workspace_bytes(const zp_plan *plan, int64_t n_nodes, int64_t n_edges,
                           int with_backward) {
-  if (!plan || n_nodes < 0 || n_edges < 0) return 0;
+  if (!plan || n_nodes < 0 || n_edges < 0 || with_backward < 0 || with_backward > 2) return 0;
   return carve(plan, n_nodes, n_edges, with_backward, nullptr).bytes;
 }
 
@@ -369,11 +403,13 @@ static int check_weights(const zp_plan *p, const zp_weights *w) {
   return ZP_OK;
 }
 
-int zp_eso2_forward(const zp_plan *plan, int64_t N, int64_t E, const float *x_node,
-                    const float *edge_vec, const float *cos_g, const float *sin_g,
-                    const float *radial, const float *env, const int32_t *src,
-                    const int32_t *dst, const int32_t *row_ptr, const zp_weights *w,
-                    float *node_out, void *workspace, size_t workspace_bytes, void *stream) {
+// keep != 0: everything a following zp_eso2_backward reads is left in the workspace
+static int eso2_forward(const zp_plan *plan, int64_t N, int64_t E, const float *x_node,
+                        const float *edge_vec, const float *cos_g, const float *sin_g,
+                        const float *radial, const float *env, const int32_t *src,
+                        const int32_t *dst, const int32_t *row_ptr, const zp_weights *w,
+                        float *node_out, void *workspace, size_t workspace_bytes, void *stream,
+                        int keep) {
   if (!plan || N < 0 || E < 0) return ZP_ERR_INVALID_ARG;
   if (N == 0) return E == 0 ? ZP_OK : ZP_ERR_INVALID_ARG;
   if (!x_node || !row_ptr || !node_out || !workspace) return ZP_ERR_INVALID_ARG;
@@ -383,10 +419,12 @@ int zp_eso2_forward(const zp_plan *plan, int64_t N, int64_t E, const float *x_no
     return ZP_ERR_INVALID_ARG;
   int rc = check_weights(plan, w);
   if (rc) return rc;
-  const Workspace ws = carve(plan, N, E, 0, workspace);
+  const Workspace ws = carve(plan, N, E, keep ? 0 : 2, workspace);
   if (workspace_bytes < ws.bytes) return ZP_ERR_WORKSPACE;
   cudaStream_t st = (cudaStream_t)stream;
   const ZpTables &t = plan->t;
+  const bool fuse1 = can_fuse(plan, 0), fuse2 = can_fuse(plan, 1);
+  const bool lean = !keep && fuse1 && fuse2;          // h1 rows and y are never written
 
   if (plan->fp16) {
     // magnitude bounds -> power-of-two scales, all on the device:  |rot row . x| <= sqrt(2l+1) max|x|
@@ -407,35 +445,125 @@ int zp_eso2_forward(const zp_plan *plan, int64_t N, int64_t E, const float *x_no
            zp_launch_rotate_in(plan, E, x_node, src, dst, ws.rot, radial, ws.a1, st));
   const int P = plan->planes;
   const int64_t ldy = (int64_t)t.Km * t.C;
-  for (int m = 0; m < plan->n_blocks && E > 0; ++m) {
-    const int in = plan->c1_in[m], out = plan->c1_out[m];
-    const ZpPlanes A = sub(ws.a1, (int64_t)t.m_row0[m] * 2 * t.C);
-    float *Cc = ws.h1 + (m == 0 ? 0 : t.n_gate + (size_t)t.m_row0[m] * t.H);
-    const ZpGemmTc g{E, out, in, P, A.base, A.ld, A.plane_stride, 0,
-                     ws.wfold + plan->c1_woff[m], in, (int64_t)out * in, 0,
-                     m == 0 ? w->c1_b0 : nullptr, Cc, t.w1_cols, plan->status_dev, 0, 1, 0, 0,
-                     plan->fp16, A.scale, wscale(plan, ws, 0, m),
-                     plan->fp16 ? ws.scales + kScH1 : nullptr};
-    ZP_TIMED(ZP_K_GEMM_FWD, zp_launch_gemm_tc(g, st));
+
+  // tables of the fused epilogues
+  ZpEpilogue epi;
+  std::memset(&epi, 0, sizeof(epi));
+  std::memcpy(epi.row_l, t.row_l, sizeof(epi.row_l));
+  std::memcpy(epi.rot_off, t.rot_off, sizeof(epi.rot_off));
+
+  // ---- conv1 (+ gate) ----
+  if (fuse1 && E > 0) {
+    // The gate activation runs in the epilogue of conv1.  Its fp16 planes need their scale before
+    // the values exist, so the scale comes from a bound: |gate_act(h1)| <= |h1| <= in * max|a1| *
+    // max|W| + max|b| (two planes keep 22 bits of everything within 2^19 of the bound).  The gate
+    // scalars (the first n_gate columns of the m = 0 block) are formed first, by a launch of
+    // their own; the other launches read them back from h1.
+    if (plan->fp16)
+      ZP_TIMED(ZP_K_GATE_FWD, zp_launch_conv1_bound(plan, ws.scales + kScA1, ws.scales + kScWeights,
+                                                    w->c1_b0, ws.scales + kScHt, st));
+    float *slope = plan->fp16 ? ws.scales + kScGate : nullptr;
+    if (slope) ZP_CUDA(cudaMemsetAsync(slope, 0, sizeof(float), st));
+    epi.mode = ZP_EPI_GATE;
+    epi.store_c = lean ? 0 : 1;
+    epi.width = t.H;
+    epi.gate = ws.h1;
+    epi.ld_gate = ws.ld_h1;
+    epi.slope_max = slope;
+    for (int m = 0; m < plan->n_blocks; ++m) {
+      const int in = plan->c1_in[m], out = plan->c1_out[m];
+      const ZpPlanes A = sub(ws.a1, (int64_t)t.m_row0[m] * 2 * t.C);
+      const int gate_cols = m == 0 ? t.n_gate : 0;
+      if (gate_cols) {
+        const ZpGemmTc g{E, gate_cols, in, P, A.base, A.ld, A.plane_stride, 0,
+                         ws.wfold + plan->c1_woff[m], in, (int64_t)out * in, 0,
+                         w->c1_b0, ws.h1, ws.ld_h1, plan->status_dev, 0, 1, 0, 0,
+                         plan->fp16, A.scale, wscale(plan, ws, 0, m),
+                         plan->fp16 ? ws.scales + kScH1 : nullptr, nullptr};
+        ZP_TIMED(ZP_K_GEMM_FWD, zp_launch_gemm_tc(g, st));
+      }
+      epi.row_first = t.m_row0[m];
+      epi.out = sub(ws.ht, (int64_t)t.m_row0[m] * t.H);
+      // lean: the fp32 rows are never stored (C is not dereferenced)
+      float *Cc = ws.h1 + (lean ? 0 : t.n_gate + (size_t)t.m_row0[m] * t.H);
+      const ZpGemmTc g{E, out - gate_cols, in, P, A.base, A.ld, A.plane_stride, 0,
+                       ws.wfold + plan->c1_woff[m] + (int64_t)gate_cols * in, in,
+                       (int64_t)out * in, 0, m == 0 ? w->c1_b0 + gate_cols : nullptr, Cc,
+                       ws.ld_h1, plan->status_dev, 0, 1, 0, 0, plan->fp16, A.scale,
+                       wscale(plan, ws, 0, m), plan->fp16 ? ws.scales + kScH1 : nullptr, &epi};
+      ZP_TIMED(ZP_K_GEMM_FWD, zp_launch_gemm_tc(g, st));
+    }
+  } else {
+    for (int m = 0; m < plan->n_blocks && E > 0; ++m) {
+      const int in = plan->c1_in[m], out = plan->c1_out[m];
+      const ZpPlanes A = sub(ws.a1, (int64_t)t.m_row0[m] * 2 * t.C);
+      float *Cc = ws.h1 + (m == 0 ? 0 : t.n_gate + (size_t)t.m_row0[m] * t.H);
+      const ZpGemmTc g{E, out, in, P, A.base, A.ld, A.plane_stride, 0,
+                       ws.wfold + plan->c1_woff[m], in, (int64_t)out * in, 0,
+                       m == 0 ? w->c1_b0 : nullptr, Cc, t.w1_cols, plan->status_dev, 0, 1, 0, 0,
+                       plan->fp16, A.scale, wscale(plan, ws, 0, m),
+                       plan->fp16 ? ws.scales + kScH1 : nullptr, nullptr};
+      ZP_TIMED(ZP_K_GEMM_FWD, zp_launch_gemm_tc(g, st));
+    }
+    if (plan->fp16)      // |gate(h1)| <= |h1|
+      ZP_TIMED(ZP_K_GATE_FWD, zp_launch_scale(1.f, ws.scales + kScH1, nullptr, nullptr, 0.f,
+                                              ws.scales + kScHt, st));
+    ZP_TIMED(ZP_K_GATE_FWD, zp_launch_gate_fwd(plan, E, ws.h1, ws.ht,
+                                               plan->fp16 ? ws.scales + kScGate : nullptr, st));
   }
-  if (plan->fp16)      // |gate(h1)| <= |h1|
-    ZP_TIMED(ZP_K_GATE_FWD, zp_launch_scale(1.f, ws.scales + kScH1, nullptr, nullptr, 0.f,
-                                            ws.scales + kScHt, st));
-  ZP_TIMED(ZP_K_GATE_FWD, zp_launch_gate_fwd(plan, E, ws.h1, ws.ht,
-                                             plan->fp16 ? ws.scales + kScGate : nullptr, st));
+
+  // ---- conv2 (+ envelope, rotation back, segmented sums) ----
+  if (fuse2) {
+    epi.mode = ZP_EPI_ROTATE_BACK;
+    epi.store_c = lean ? 0 : 1;
+    epi.width = t.C;
+    epi.rot = ws.rot;
+    epi.env = env;
+    epi.row_ptr = row_ptr;
+    epi.n_nodes = (int)N;
+    epi.nnz = t.nnz;
+    epi.nnz_pad = t.nnz_pad;
+    epi.head = ws.head;
+    epi.cont = ws.cont;
+  }
   for (int m = 0; m < plan->n_blocks && E > 0; ++m) {
     const int in = plan->c2_in[m], out = plan->c2_out[m];
     const ZpPlanes A = sub(ws.ht, (int64_t)t.m_row0[m] * t.H);
-    float *Cc = ws.y + (size_t)t.m_row0[m] * t.C;
+    float *Cc = lean ? ws.h1 : ws.y + (size_t)t.m_row0[m] * t.C;     // lean: never dereferenced
+    epi.row_first = t.m_row0[m];
     const ZpGemmTc g{E, out, in, P, A.base, A.ld, A.plane_stride, 0,
                      ws.wfold + plan->c2_woff[m], in, (int64_t)out * in, 0,
                      m == 0 ? w->c2_b0 : nullptr, Cc, ldy, plan->status_dev, 0, 1, 0, 0,
-                     plan->fp16, A.scale, wscale(plan, ws, 1, m), nullptr};
+                     plan->fp16, A.scale, wscale(plan, ws, 1, m), nullptr,
+                     fuse2 ? &epi : nullptr};
     ZP_TIMED(ZP_K_GEMM_FWD, zp_launch_gemm_tc(g, st));
   }
-  ZP_TIMED(ZP_K_ROTATE_BACK,
-           zp_launch_rotate_back_scatter(plan, N, ws.y, env, ws.rot, row_ptr, node_out, st));
+  if (fuse2)
+    ZP_TIMED(ZP_K_ROTATE_BACK,
+             zp_launch_node_sum(plan, N, ws.head, ws.cont, row_ptr, node_out, st));
+  else
+    ZP_TIMED(ZP_K_ROTATE_BACK,
+             zp_launch_rotate_back_scatter(plan, N, ws.y, env, ws.rot, row_ptr, node_out, st));
   return ZP_OK;
+}
+
+int zp_eso2_forward(const zp_plan *plan, int64_t N, int64_t E, const float *x_node,
+                    const float *edge_vec, const float *cos_g, const float *sin_g,
+                    const float *radial, const float *env, const int32_t *src,
+                    const int32_t *dst, const int32_t *row_ptr, const zp_weights *w,
+                    float *node_out, void *workspace, size_t workspace_bytes, void *stream) {
+  return eso2_forward(plan, N, E, x_node, edge_vec, cos_g, sin_g, radial, env, src, dst, row_ptr,
+                      w, node_out, workspace, workspace_bytes, stream, 1);
+}
+
+int zp_eso2_forward_inference(const zp_plan *plan, int64_t N, int64_t E, const float *x_node,
+                              const float *edge_vec, const float *cos_g, const float *sin_g,
+                              const float *radial, const float *env, const int32_t *src,
+                              const int32_t *dst, const int32_t *row_ptr, const zp_weights *w,
+                              float *node_out, void *workspace, size_t workspace_bytes,
+                              void *stream) {
+  return eso2_forward(plan, N, E, x_node, edge_vec, cos_g, sin_g, radial, env, src, dst, row_ptr,
+                      w, node_out, workspace, workspace_bytes, stream, 0);
 }
 
 int zp_eso2_backward(const zp_plan *plan, int64_t N, int64_t E, const float *grad_node_out,
@@ -462,7 +590,8 @@ int zp_eso2_backward(const zp_plan *plan, int64_t N, int64_t E, const float *gra
     return ZP_ERR_INVALID_ARG;
   int rc = check_weights(plan, w);
   if (rc) return rc;
-  const Workspace ws = carve(plan, N, E, 1, workspace);
+  // (the node count only sizes regions that live inside the forward)
+  const Workspace ws = carve(plan, 0, E, 1, workspace);
   if (workspace_bytes < ws.bytes) return ZP_ERR_WORKSPACE;
   cudaStream_t st = (cudaStream_t)stream;
   const ZpTables &t = plan->t;

@@ -112,6 +112,10 @@ int zp_launch_rotate_in_bwd(const zp_plan *p, int64_t E, const float *da1, const
                             const float *x, const int32_t *src, const int32_t *dst,
                             const float *rot, float *grad_radial, float *du_both, float *grad_rot,
                             cudaStream_t st);
+// node_out[n, l^2 + j, c] = sum over the m' rows r of degree l, in table order, of
+//   head[n][rot_off[r] + j][c] + the continuation partials of the 32-edge blocks n's edges reach
+int zp_launch_node_sum(const zp_plan *p, int64_t N, const float *head, const float *cont,
+                       const int32_t *row_ptr, float *node_out, cudaStream_t st);
 int zp_launch_node_reduce(const zp_plan *p, int64_t N, const float *du_both,
                           const int32_t *row_ptr, const int32_t *perm_src,
                           const int32_t *row_ptr_src, float *grad_x, cudaStream_t st);
@@ -121,6 +125,41 @@ int zp_launch_gate_fwd(const zp_plan *p, int64_t E, const float *h1, const ZpPla
 // gate_max (device scalar, may be null): largest sigmoid'(gate) seen by the forward
 int zp_launch_gate_bwd(const zp_plan *p, int64_t E, const float *h1, const float *dht,
                        const ZpPlanes &dh1, cudaStream_t st);
+
+// Work the contraction's epilogue does on a finished 32-row x 32-column block of the result
+// while it is still on chip (staged in shared memory), besides or instead of storing it.
+//   ZP_EPI_GATE         conv1 of the SO(2) block: column n is hidden channel (n % width) of m' row
+//                       row_first + n / width; the block goes through the gate activation
+//                       (blocks/eso2_ref.py:295-301: SiLU for row 0, x * sigmoid(gate[l-1]) for the
+//                       others, the raw gate scalars read from `gate`) and is written as 16-bit
+//                       operand planes for conv2.
+//   ZP_EPI_ROTATE_BACK  conv2: column n is channel (n % width) of m' row row_first + n / width;
+//                       every edge's value is scaled by its envelope, expanded by the edge's
+//                       packed rotation row into the 2l+1 outputs of its degree and summed over
+//                       the consecutive edges of a destination node (the edges are destination
+//                       sorted).  A node's first run of edges inside a 32-row block goes to
+//                       head[node], a run that continues from the previous block to cont[block];
+//                       zp_launch_node_sum adds them up in a fixed order.
+// Requires K-major operands, one accumulation chunk and no K split.
+enum { ZP_EPI_NONE = 0, ZP_EPI_GATE = 1, ZP_EPI_ROTATE_BACK = 2 };
+struct ZpEpilogue {
+  int mode;
+  int store_c;                                  // also store the fp32 result to C
+  int width;                                    // channels per m' row (H or C)
+  int row_first;                                // m' row of column 0
+  int8_t row_l[ZP_MAX_KM];                      // degree of each m' row
+  int16_t rot_off[ZP_MAX_KM];                   // offset of the row's entries in a packed rotation
+  // gate
+  const float *gate;                            // [M, ld_gate] raw gate scalars, block l-1 at column (l-1)*width
+  int64_t ld_gate;
+  ZpPlanes out;                                 // activated rows: element (e, n) at e*out.ld + n
+  float *slope_max;                             // running max of sigmoid'(gate), or null
+  // rotate back
+  const float *rot, *env;                       // [M, nnz_pad], [M]
+  const int32_t *row_ptr;                       // [n_nodes + 1] offsets of the nodes' edges
+  int n_nodes, nnz, nnz_pad;
+  float *head, *cont;                           // [n_nodes][nnz][width], [ceil(M/32)][nnz][width]
+};
 
 // Tensor-core product over bf16 planes: C[M,N] = sum_pairs A_pa * B_pb^T (+ bias), fp32 out.
 // K-major operand: X[p*plane + r*ld + k]; MN-major (x_mn = 1): X[p*plane + k*ld + r].
@@ -139,8 +178,11 @@ struct ZpGemmTc {
   int fp16;                                     // planes are fp16 (planes must be 2), else bf16
   const float *scale_a, *scale_b;               // device scalars multiplied into the result
   float *absmax_out;                            // device scalar updated with max |C| (or null)
+  const ZpEpilogue *epi;                        // fused epilogue (null = store C)
 };
 int zp_launch_gemm_tc(const ZpGemmTc &g, cudaStream_t st);
+// whether zp_launch_gemm_tc accepts a fused epilogue for this problem
+bool zp_gemm_tc_fusable(const ZpGemmTc &g);
 // number of partial outputs the launch above will write for this problem (<= g.ksplit)
 int zp_gemm_tc_splits(const ZpGemmTc &g);
 // K split (<= max_splits) that fills the device's CTAs (or CTA pairs) most evenly for this problem
@@ -173,5 +215,10 @@ int zp_launch_fold_weights(const zp_plan *p, const zp_weights *w, void *packed, 
 int zp_launch_unfold_wgrad(const zp_plan *p, const float *partials, int64_t split_stride,
                            const int *splits_c1, const int *splits_c2, const zp_weight_grads *gw,
                            cudaStream_t st);
+// *ht_scale = fp16-plane scale of conv1's activated output from an a-priori bound:
+//   |h1| <= max_m(in_m * max|a1| * max|W1_m|) + max|b1|,  |gate_act(h1)| <= |h1|
+// (a1_scale maps the bound of a1 to 2^15; wscales: {max, scale} pairs per weight block)
+int zp_launch_conv1_bound(const zp_plan *p, const float *a1_scale, const float *wscales,
+                          const float *bias, float *ht_scale, cudaStream_t st);
 int zp_launch_colsum(int64_t rows, int64_t cols, const ZpPlanes &a, float *out, float *scratch,
                      cudaStream_t st);

@@ -395,7 +395,45 @@ __global__ void colsum_final_kernel(int64_t nparts, int64_t cols, const float *_
   out[c] = s;
 }
 
+// scale of conv1's activated output from an a-priori bound (one block):
+//   |h1| <= max_m(in_m * A * max|W_m|) + max|b|,  A = 2^15 * a1_scale >= max|a1|
+struct BoundDesc {
+  int n;
+  int in[ZP_MAX_L + 1];
+  int n_bias;
+};
+__global__ void __launch_bounds__(256)
+conv1_bound_kernel(const BoundDesc d, const float *a1_scale, const float *wscales,
+                   const float *__restrict__ bias, float *ht_scale) {
+  __shared__ float red[8];
+  float m = 0.f;
+  for (int i = threadIdx.x; i < d.n_bias; i += blockDim.x) m = fmaxf(m, fabsf(bias[i]));
+#pragma unroll
+  for (int o = 16; o > 0; o >>= 1) m = fmaxf(m, __shfl_xor_sync(0xffffffffu, m, o));
+  if ((threadIdx.x & 31) == 0) red[threadIdx.x >> 5] = m;
+  __syncthreads();
+  if (threadIdx.x == 0) {
+    float bmax = 0.f;
+    for (int i = 0; i < 8; ++i) bmax = fmaxf(bmax, red[i]);
+    const float a = 32768.f * *a1_scale;
+    float bound = 0.f;
+    for (int b = 0; b < d.n; ++b) bound = fmaxf(bound, (float)d.in[b] * a * wscales[2 * b]);
+    *ht_scale = zp_scale_for_bound(1.001f * (bound + bmax));
+  }
+}
+
 }  // namespace
+
+int zp_launch_conv1_bound(const zp_plan *p, const float *a1_scale, const float *wscales,
+                          const float *bias, float *ht_scale, cudaStream_t st) {
+  BoundDesc d;
+  d.n = p->n_blocks;
+  for (int m = 0; m < p->n_blocks; ++m) d.in[m] = p->c1_in[m];
+  d.n_bias = p->c1_out[0];
+  conv1_bound_kernel<<<1, 256, 0, st>>>(d, a1_scale, wscales, bias, ht_scale);
+  ZP_LAUNCH_CHECK("conv1_bound_kernel");
+  return ZP_OK;
+}
 
 int zp_launch_split_planes(int64_t rows, int64_t cols, const float *in, int64_t ld_in,
                            const ZpPlanes &out, cudaStream_t st) {

@@ -39,6 +39,7 @@
 // and the matrix descriptors name.  Every mbarrier wait is bounded: after ~2 s it records
 // ZP_ERR_DEVICE_TIMEOUT in the status word, raises the CTA's abort flag and the CTA drains.
 #include <cstdlib>
+#include <mutex>
 
 #include <cuda.h>
 #include <cuda_bf16.h>
@@ -209,6 +210,7 @@ struct GemmParams {
   int64_t ldc, split_stride;
   int tma_store;          // epilogue goes through TMA stores (map_c is valid)
   int *status;
+  ZpEpilogue epi;         // work of the fused epilogues (mode 0: none)
 };
 
 // plane pairs; for three planes pair 0 is the leading product, pairs 1..5 the small ones
@@ -314,6 +316,149 @@ __device__ __forceinline__ void epilogue_store_tma(const GemmParams &p, const CU
   }
 }
 
+
+// ---- fused epilogues ------------------------------------------------------------------------
+// A finished 32 x 32 block of the result sits in the warp's shared-memory stage in the layout
+// above (row = edge, 16-byte chunk k of row r at chunk k ^ (r & 7)).  The fused epilogues read
+// it back in a second assignment of lanes and consume it there, so the values never have to come
+// back from HBM: the gate activation walks it row-wise (eight lanes share a row, coalesced
+// loads of the gate scalars and 8-byte plane stores), the rotation back walks it column-wise
+// (a lane owns one channel and runs over the block's edges in order).
+__device__ __forceinline__ float fast_sigmoid(float x) { return 1.f / (1.f + __expf(-x)); }
+
+__device__ __forceinline__ void gate_block(const ZpEpilogue &f, const uint8_t *stage, int lane,
+                                           int row0, int n, int M, int N, float inv,
+                                           float &slope_max) {
+#pragma unroll 2
+  for (int it = 0; it < 8; ++it) {
+    const int rr = it * 4 + (lane >> 3), k = lane & 7;
+    const int row = row0 + rr, col = n + 4 * k;
+    if (row < M && col < N) {
+      const float4 x = *reinterpret_cast<const float4 *>(stage + rr * 128 + ((k ^ (rr & 7)) << 4));
+      const int rq = col / f.width;
+      const int r = f.row_first + rq, h = col - rq * f.width;
+      float4 g = x;                              // row 0 (l = 0): x * sigmoid(x)
+      if (r != 0)
+        g = *reinterpret_cast<const float4 *>(f.gate + (size_t)row * f.ld_gate +
+                                              (f.row_l[r] - 1) * f.width + h);
+      const float s0 = fast_sigmoid(g.x), s1 = fast_sigmoid(g.y), s2 = fast_sigmoid(g.z),
+                  s3 = fast_sigmoid(g.w);
+      const float o[4] = {x.x * s0, x.y * s1, x.z * s2, x.w * s3};
+      if (r != 0)
+        slope_max = fmaxf(slope_max, fmaxf(fmaxf(s0 * (1.f - s0), s1 * (1.f - s1)),
+                                           fmaxf(s2 * (1.f - s2), s3 * (1.f - s3))));
+      zp_store_planes<4>(f.out, (int64_t)row * f.out.ld + col, o, inv);
+    }
+  }
+}
+
+// the last node n with row_ptr[n] <= e  (row_ptr[0] <= e < row_ptr[n_nodes])
+__device__ __forceinline__ int find_node(const int32_t *__restrict__ row_ptr, int n_nodes, int e) {
+  int lo = 0, hi = n_nodes;
+  while (hi - lo > 1) {
+    const int mid = (lo + hi) >> 1;
+    if (row_ptr[mid] <= e) lo = mid; else hi = mid;
+  }
+  return lo;
+}
+
+constexpr int kMaxNj = 2 * ZP_MAX_L + 1;
+
+// node: the node of edge row0 (from find_node)
+__device__ __forceinline__ void rotate_back_block(const ZpEpilogue &f, const uint8_t *stage, int lane,
+                                                  int row0, int n, int M, int N, int node) {
+  const int col = n + lane;
+  const bool col_ok = col < N;
+  const int cq = col_ok ? col : n;               // lanes beyond the matrix shadow column n
+  const int rq = cq / f.width;
+  const int r = f.row_first + rq, c = cq - rq * f.width;
+  const int off = f.rot_off[r];
+  const int nj = 2 * f.row_l[r] + 1;
+  const int njmax = __reduce_max_sync(0xffffffffu, nj);
+  const int row_end = min(row0 + 32, M);
+  const size_t slab = (size_t)f.nnz * f.width;
+  int e = row0;
+  while (e < row_end) {
+    while (node + 1 < f.n_nodes && f.row_ptr[node + 1] <= e) ++node;    // nodes without edges
+    const bool is_head = f.row_ptr[node] == e;
+    int stop = min(f.row_ptr[node + 1], row_end);
+    if (stop <= e) stop = row_end;               // offsets that do not cover the edges: never spin
+    float acc[kMaxNj];
+#pragma unroll
+    for (int j = 0; j < kMaxNj; ++j) acc[j] = 0.f;
+#pragma unroll 2
+    for (; e < stop; ++e) {
+      const int i = e - row0;
+      const float yv = f.env[e] * *reinterpret_cast<const float *>(
+                                      stage + i * 128 + (((lane >> 2) ^ (i & 7)) << 4) + ((lane & 3) << 2));
+      const float *re = f.rot + (size_t)e * f.nnz_pad + off;
+#pragma unroll
+      for (int j = 0; j < kMaxNj; ++j) {
+        if (j >= njmax) break;                   // warp-uniform
+        if (j < nj) acc[j] = fmaf(re[j], yv, acc[j]);
+      }
+    }
+    float *out = (is_head ? f.head + (size_t)node * slab : f.cont + (size_t)(row0 >> 5) * slab) +
+                 (size_t)off * f.width + c;
+    if (col_ok) {
+#pragma unroll
+      for (int j = 0; j < kMaxNj; ++j)
+        if (j < nj) out[(size_t)j * f.width] = acc[j];
+    }
+  }
+}
+
+// v[b][j]: value at row `row0 + lane`, column `n0 + col_lo + 32 b + j` (scaled, no bias yet).
+template <int EPI>
+__device__ __forceinline__ void epilogue_fused(const GemmParams &p, const CUtensorMap *map_c,
+                                               float (&v)[4][32], uint8_t *stage, int lane, int row0,
+                                               int n0, int col_lo, int col_hi, const float *bias,
+                                               float &seen_max, float &slope_max, int node) {
+  if (row0 >= p.M) return;
+  const bool row_ok = row0 + lane < p.M;
+  const float inv = EPI == ZP_EPI_GATE ? zp_inv_scale(p.epi.out) : 1.f;
+#pragma unroll
+  for (int b = 0; b < 4; ++b) {
+    const int cc = col_lo + 32 * b;
+    if (cc >= col_hi) continue;                   // warp-uniform
+    const int n = n0 + cc;
+    if (n >= p.N) continue;
+    if (p.epi.store_c && lane == 0) bulk_wait_read();   // the TMA store of the previous block
+    __syncwarp();                                 // ... and every lane's reads of it are done
+#pragma unroll
+    for (int k = 0; k < 8; ++k) {
+      float4 o = make_float4(v[b][4 * k], v[b][4 * k + 1], v[b][4 * k + 2], v[b][4 * k + 3]);
+      const int c = n + 4 * k;
+      if (bias) {
+        o.x += c < p.N ? bias[c] : 0.f;
+        o.y += c + 1 < p.N ? bias[c + 1] : 0.f;
+        o.z += c + 2 < p.N ? bias[c + 2] : 0.f;
+        o.w += c + 3 < p.N ? bias[c + 3] : 0.f;
+      }
+      if (row_ok) {
+        float m = c < p.N ? fabsf(o.x) : 0.f;
+        m = fmaxf(m, c + 1 < p.N ? fabsf(o.y) : 0.f);
+        m = fmaxf(m, c + 2 < p.N ? fabsf(o.z) : 0.f);
+        m = fmaxf(m, c + 3 < p.N ? fabsf(o.w) : 0.f);
+        seen_max = fmaxf(seen_max, m);
+      }
+      *reinterpret_cast<float4 *>(stage + lane * 128 + ((k ^ (lane & 7)) << 4)) = o;
+    }
+    if (p.epi.store_c) {
+      asm volatile("fence.proxy.async.shared::cta;" ::: "memory");
+      __syncwarp();
+      if (lane == 0) {
+        tma_store_3d(map_c, stage, n, row0, 0);
+        bulk_commit();
+      }
+    } else {
+      __syncwarp();
+    }
+    if (EPI == ZP_EPI_GATE) gate_block(p.epi, stage, lane, row0, n, p.M, p.N, inv, slope_max);
+    else rotate_back_block(p.epi, stage, lane, row0, n, p.M, p.N, node);
+  }
+}
+
 template <int P, int BK, int STAGES, int BN_CAP>
 struct SmemLayout {
   static constexpr int kATile = BM * BK * 2;
@@ -344,10 +489,9 @@ __device__ __forceinline__ Work decode_work(const GemmParams &p, int w) {
   return x;
 }
 
-template <int P, int BK, int STAGES, int BN_CAP>
-__global__ void __launch_bounds__(kThreads, 1)
-gemm_tc_kernel(const __grid_constant__ CUtensorMap map_a, const __grid_constant__ CUtensorMap map_b,
-               const __grid_constant__ CUtensorMap map_c, const GemmParams p) {
+template <int P, int BK, int STAGES, int BN_CAP, int EPI>
+__device__ __forceinline__ void gemm_tc_body(const CUtensorMap &map_a, const CUtensorMap &map_b,
+                                             const CUtensorMap &map_c, const GemmParams &p) {
   using L = SmemLayout<P, BK, STAGES, BN_CAP>;
   constexpr int kAccBufs = P == 1 ? 2 : 1;      // accumulation units in flight in TMEM
   extern __shared__ uint8_t smem_raw[];
@@ -480,7 +624,7 @@ gemm_tc_kernel(const __grid_constant__ CUtensorMap map_a, const __grid_constant_
     uint32_t unit = 0;
     bool ok = true;
     const float out_scale = (p.scale_a ? *p.scale_a : 1.f) * (p.scale_b ? *p.scale_b : 1.f);
-    float seen_max = 0.f;
+    float seen_max = 0.f, slope_max = 0.f;
     const int col_lo = half * 128, col_hi = min(p.BN, col_lo + 128);
     for (int w = blockIdx.x; w < num_work && ok; w += gridDim.x) {
       const Work x = decode_work(p, w);
@@ -491,6 +635,9 @@ gemm_tc_kernel(const __grid_constant__ CUtensorMap map_a, const __grid_constant_
       for (int c0 = x.kb0; c0 < x.kb1 && ok; c0 += p.kc, ++unit) {
         const int buf = unit % kAccBufs;
         const bool first = c0 == x.kb0;         // first chunk stores, later chunks add
+        int node = 0;                           // looked up while the tile is still being formed
+        if (EPI == ZP_EPI_ROTATE_BACK && row0 < p.M)
+          node = find_node(p.epi.row_ptr, p.epi.n_nodes, row0);
         ok = mbar_wait(&tmem_full[buf], (unit / kAccBufs) & 1, abort_flag, p.status);
         ok = __all_sync(0xffffffffu, ok);
         if (!ok) break;
@@ -526,7 +673,11 @@ gemm_tc_kernel(const __grid_constant__ CUtensorMap map_a, const __grid_constant_
         __syncwarp();
         if (lane == 0) mbar_arrive(&tmem_empty[buf]);      // TMEM slice is in registers now
 
-        if (L::kTmaEpilogue && p.tma_store) {
+        if (EPI != ZP_EPI_NONE) {
+          if (L::kTmaEpilogue)
+            epilogue_fused<EPI>(p, &map_c, v, epi_stage, lane, row0, x.n0, col_lo, col_hi, bias,
+                                seen_max, slope_max, node);
+        } else if (L::kTmaEpilogue && p.tma_store) {
           epilogue_store_tma(p, &map_c, v, epi_stage, lane, row0, x.n0, col_lo, col_hi, x.split,
                              bias, first, seen_max);
         } else if (row < p.M) {
@@ -572,6 +723,11 @@ gemm_tc_kernel(const __grid_constant__ CUtensorMap map_a, const __grid_constant_
       for (int o = 16; o > 0; o >>= 1) seen_max = fmaxf(seen_max, __shfl_xor_sync(0xffffffffu, seen_max, o));
       if (lane == 0 && seen_max > 0.f) zp_atomic_absmax(p.absmax_out, seen_max);
     }
+    if (EPI == ZP_EPI_GATE && p.epi.slope_max) {
+#pragma unroll
+      for (int o = 16; o > 0; o >>= 1) slope_max = fmaxf(slope_max, __shfl_xor_sync(0xffffffffu, slope_max, o));
+      if (lane == 0 && slope_max > 0.f) zp_atomic_absmax(p.epi.slope_max, slope_max);
+    }
   }
 
   tcgen05_fence_before();
@@ -581,6 +737,22 @@ gemm_tc_kernel(const __grid_constant__ CUtensorMap map_a, const __grid_constant_
     asm volatile("tcgen05.dealloc.cta_group::1.sync.aligned.b32 %0, %1;" ::"r"(tmem_base), "r"(512u)
                  : "memory");
   }
+}
+
+template <int P, int BK, int STAGES, int BN_CAP>
+__global__ void __launch_bounds__(kThreads, 1)
+gemm_tc_kernel(const __grid_constant__ CUtensorMap map_a, const __grid_constant__ CUtensorMap map_b,
+               const __grid_constant__ CUtensorMap map_c, const __grid_constant__ GemmParams p) {
+  gemm_tc_body<P, BK, STAGES, BN_CAP, ZP_EPI_NONE>(map_a, map_b, map_c, p);
+}
+// the same contraction with a fused epilogue (the epilogue warps hold more live values)
+template <int P, int BK, int STAGES, int BN_CAP, int EPI>
+__global__ void __maxnreg__(200)
+gemm_tc_fused_kernel(const __grid_constant__ CUtensorMap map_a,
+                     const __grid_constant__ CUtensorMap map_b,
+                     const __grid_constant__ CUtensorMap map_c,
+                     const __grid_constant__ GemmParams p) {
+  gemm_tc_body<P, BK, STAGES, BN_CAP, EPI>(map_a, map_b, map_c, p);
 }
 
 // ---- CTA-pair variant ---------------------------------------------------------------------
@@ -677,11 +849,9 @@ __device__ __forceinline__ Work decode_work_pair(const GemmParams &p, int w) {
   return x;
 }
 
-template <int P, int BK, int STAGES>
-__global__ void __launch_bounds__(kThreads, 1)
-gemm_tc_pair_kernel(const __grid_constant__ CUtensorMap map_a,
-                    const __grid_constant__ CUtensorMap map_b,
-                    const __grid_constant__ CUtensorMap map_c, const GemmParams p) {
+template <int P, int BK, int STAGES, int EPI>
+__device__ __forceinline__ void gemm_tc_pair_body(const CUtensorMap &map_a, const CUtensorMap &map_b,
+                                                  const CUtensorMap &map_c, const GemmParams &p) {
   using L = SmemLayoutPair<P, BK, STAGES>;
   extern __shared__ uint8_t smem_raw[];
   // the dynamic shared window starts at the same offset in both CTAs, so does everything below
@@ -822,7 +992,7 @@ gemm_tc_pair_kernel(const __grid_constant__ CUtensorMap map_a,
     uint32_t unit = 0;
     bool ok = true;
     const float out_scale = (p.scale_a ? *p.scale_a : 1.f) * (p.scale_b ? *p.scale_b : 1.f);
-    float seen_max = 0.f;
+    float seen_max = 0.f, slope_max = 0.f;
     const int col_lo = half * 128, col_hi = min(p.BN, col_lo + 128);
     const uint32_t release_bar0 = map_to_cta(smem_u32(&tmem_empty[0]), 0);
     const uint32_t release_bar1 = map_to_cta(smem_u32(&tmem_empty[1]), 0);
@@ -836,6 +1006,9 @@ gemm_tc_pair_kernel(const __grid_constant__ CUtensorMap map_a,
         const bool first = c0 == x.kb0;
         const int buf = P == 1 ? (int)(unit & 1) : 0;
         const uint32_t round = P == 1 ? (unit >> 1) : unit;
+        int node = 0;                           // looked up while the tile is still being formed
+        if (EPI == ZP_EPI_ROTATE_BACK && row0 < p.M)
+          node = find_node(p.epi.row_ptr, p.epi.n_nodes, row0);
         ok = mbar_wait(&tmem_full[buf], round & 1, abort_flag, p.status);
         ok = __all_sync(0xffffffffu, ok);
         if (!ok) break;
@@ -870,7 +1043,11 @@ gemm_tc_pair_kernel(const __grid_constant__ CUtensorMap map_a,
         __syncwarp();
         if (lane == 0) mbar_arrive_cluster(buf ? release_bar1 : release_bar0);
 
-        if (L::kTmaEpilogue && p.tma_store) {
+        if (EPI != ZP_EPI_NONE) {
+          if (L::kTmaEpilogue)
+            epilogue_fused<EPI>(p, &map_c, v, epi_stage, lane, row0, x.n0, col_lo, col_hi, bias,
+                                seen_max, slope_max, node);
+        } else if (L::kTmaEpilogue && p.tma_store) {
           epilogue_store_tma(p, &map_c, v, epi_stage, lane, row0, x.n0, col_lo, col_hi, x.split,
                              bias, first, seen_max);
         } else if (row < p.M) {
@@ -916,6 +1093,11 @@ gemm_tc_pair_kernel(const __grid_constant__ CUtensorMap map_a,
       for (int o = 16; o > 0; o >>= 1) seen_max = fmaxf(seen_max, __shfl_xor_sync(0xffffffffu, seen_max, o));
       if (lane == 0 && seen_max > 0.f) zp_atomic_absmax(p.absmax_out, seen_max);
     }
+    if (EPI == ZP_EPI_GATE && p.epi.slope_max) {
+#pragma unroll
+      for (int o = 16; o > 0; o >>= 1) slope_max = fmaxf(slope_max, __shfl_xor_sync(0xffffffffu, slope_max, o));
+      if (lane == 0 && slope_max > 0.f) zp_atomic_absmax(p.epi.slope_max, slope_max);
+    }
   }
 
   tcgen05_fence_before();
@@ -927,6 +1109,23 @@ gemm_tc_pair_kernel(const __grid_constant__ CUtensorMap map_a,
     asm volatile("tcgen05.dealloc.cta_group::2.sync.aligned.b32 %0, %1;" ::"r"(tmem_base), "r"(512u)
                  : "memory");
   }
+}
+
+template <int P, int BK, int STAGES>
+__global__ void __launch_bounds__(kThreads, 1)
+gemm_tc_pair_kernel(const __grid_constant__ CUtensorMap map_a,
+                    const __grid_constant__ CUtensorMap map_b,
+                    const __grid_constant__ CUtensorMap map_c,
+                    const __grid_constant__ GemmParams p) {
+  gemm_tc_pair_body<P, BK, STAGES, ZP_EPI_NONE>(map_a, map_b, map_c, p);
+}
+template <int P, int BK, int STAGES, int EPI>
+__global__ void __maxnreg__(200)
+gemm_tc_pair_fused_kernel(const __grid_constant__ CUtensorMap map_a,
+                          const __grid_constant__ CUtensorMap map_b,
+                          const __grid_constant__ CUtensorMap map_c,
+                          const __grid_constant__ GemmParams p) {
+  gemm_tc_pair_body<P, BK, STAGES, EPI>(map_a, map_b, map_c, p);
 }
 
 // ---- host side ---------------------------------------------------------------------------
@@ -1056,28 +1255,65 @@ void split_plan(const ZpGemmTc &g, int bk, int *ksplit, int *kbs, int *num_k) {
   *ksplit = (int)zp_ceil_div(*num_k, *kbs);
 }
 
-template <int P, int BK, int STAGES, int BN_CAP>
-int launch(const ZpGemmTc &g, cudaStream_t st) {
+// One-time set-up of a kernel is per device (the raised dynamic shared-memory limit is an
+// attribute of the function ON a device): remembered per device ordinal under a lock, since a
+// plan may be used from several host threads.
+constexpr int kMaxDevices = 64;
+struct PerDevice {
+  std::mutex lock;
+  int value[kMaxDevices];
+  bool done[kMaxDevices];
+  PerDevice() { for (int i = 0; i < kMaxDevices; ++i) { value[i] = 0; done[i] = false; } }
+};
+
+bool fused_mode_ok(const ZpGemmTc &g, int bk) {
+  if (!g.epi || g.epi->mode == ZP_EPI_NONE) return true;
+  if (g.a_mn || g.b_mn || (g.planes != 1 && g.planes != 2)) return false;
+  int ksplit, kbs, num_k;
+  split_plan(g, bk, &ksplit, &kbs, &num_k);
+  const int kc_elems = g.kc_elems > 0 ? g.kc_elems : 2048;
+  const int kc = kc_elems / bk < 1 ? 1 : kc_elems / bk;
+  return ksplit == 1 && kbs <= kc && (g.epi->width % 4) == 0;
+}
+
+void fill_params(GemmParams &p, const ZpGemmTc &g, int bk) {
+  p.M = (int)g.M; p.N = (int)g.N; p.K = (int)g.K;
+  split_plan(g, bk, &p.ksplit, &p.kb_per_split, &p.num_k);
+  const int kc_elems = g.kc_elems > 0 ? g.kc_elems : 2048;
+  p.kc = kc_elems / bk < 1 ? 1 : kc_elems / bk;
+  p.a_mn = g.a_mn; p.b_mn = g.b_mn;
+  p.fp16 = g.fp16; p.scale_a = g.scale_a; p.scale_b = g.scale_b; p.absmax_out = g.absmax_out;
+  p.bias = g.bias; p.C = g.C; p.ldc = g.ldc; p.split_stride = g.split_stride; p.status = g.status;
+  if (g.epi) p.epi = *g.epi;
+  else p.epi.mode = ZP_EPI_NONE;
+}
+
+template <int P, int BK, int STAGES, int BN_CAP, int EPI>
+int launch_e(const ZpGemmTc &g, cudaStream_t st) {
   using L = SmemLayout<P, BK, STAGES, BN_CAP>;
   static_assert(L::kTotal <= 232448, "shared memory budget of one CTA");
-  static bool configured = false;
-  if (!configured) {
-    ZP_CUDA(cudaFuncSetAttribute(gemm_tc_kernel<P, BK, STAGES, BN_CAP>,
-                                 cudaFuncAttributeMaxDynamicSharedMemorySize, L::kTotal));
-    configured = true;
+  static_assert(EPI == ZP_EPI_NONE || L::kTmaEpilogue, "fused epilogues need the store stage");
+  auto kernel = [] {
+    if constexpr (EPI == ZP_EPI_NONE) return gemm_tc_kernel<P, BK, STAGES, BN_CAP>;
+    else return gemm_tc_fused_kernel<P, BK, STAGES, BN_CAP, EPI>;
+  }();
+  int dev = 0, sms = 148;
+  ZP_CUDA(cudaGetDevice(&dev));
+  if (dev < 0 || dev >= kMaxDevices) return ZP_ERR_UNSUPPORTED;
+  static PerDevice configured;
+  {
+    std::lock_guard<std::mutex> hold(configured.lock);
+    if (!configured.done[dev]) {
+      ZP_CUDA(cudaFuncSetAttribute(kernel, cudaFuncAttributeMaxDynamicSharedMemorySize, L::kTotal));
+      configured.done[dev] = true;
+    }
   }
   GemmParams p;
-  p.M = (int)g.M; p.N = (int)g.N; p.K = (int)g.K;
+  fill_params(p, g, BK);
   // whole 32-column store blocks; MN-major B tiles come in 64-wide blocks
   p.BN = pick_bn(g.N, BN_CAP, g.b_mn ? 64 : 32);
   p.num_m = (int)zp_ceil_div(g.M, BM);
   p.num_n = (int)zp_ceil_div(g.N, p.BN);
-  split_plan(g, BK, &p.ksplit, &p.kb_per_split, &p.num_k);
-  const int kc_elems = g.kc_elems > 0 ? g.kc_elems : 2048;
-  p.kc = kc_elems / BK < 1 ? 1 : kc_elems / BK;
-  p.a_mn = g.a_mn; p.b_mn = g.b_mn;
-  p.fp16 = g.fp16; p.scale_a = g.scale_a; p.scale_b = g.scale_b; p.absmax_out = g.absmax_out;
-  p.bias = g.bias; p.C = g.C; p.ldc = g.ldc; p.split_stride = g.split_stride; p.status = g.status;
   const CUtensorMapSwizzle kswz = BK == 64 ? CU_TENSOR_MAP_SWIZZLE_128B : CU_TENSOR_MAP_SWIZZLE_64B;
   CUtensorMap ma, mb;
   int rc;
@@ -1087,12 +1323,11 @@ int launch(const ZpGemmTc &g, cudaStream_t st) {
   if (!g.b_mn) rc = make_map(&mb, g.B, g.K, g.N, P, g.ldb, g.b_plane, BK, p.BN, kswz, g.fp16);
   else rc = make_map(&mb, g.B, g.N, g.K, P, g.ldb, g.b_plane, 64, BK, CU_TENSOR_MAP_SWIZZLE_128B, g.fp16);
   if (rc) return rc;
-  int dev = 0, sms = 148;
-  cudaGetDevice(&dev);
   cudaDeviceGetAttribute(&sms, cudaDevAttrMultiProcessorCount, dev);
   CUtensorMap mc;
   const int chunks = (int)zp_ceil_div(p.kb_per_split, p.kc);
-  p.tma_store = L::kTmaEpilogue && !(g.absmax_out && chunks > 1);
+  p.tma_store = EPI == ZP_EPI_NONE ? (L::kTmaEpilogue && !(g.absmax_out && chunks > 1))
+                                   : p.epi.store_c;
   if (p.tma_store) {
     if ((rc = make_map_c(&mc, g.C, g.N, g.M, p.ksplit, g.ldc, g.split_stride))) return rc;
   } else {
@@ -1100,45 +1335,62 @@ int launch(const ZpGemmTc &g, cudaStream_t st) {
   }
   const int work = p.num_m * p.num_n * p.ksplit;
   const int grid = work < sms ? work : sms;
-  gemm_tc_kernel<P, BK, STAGES, BN_CAP><<<grid, kThreads, L::kTotal, st>>>(ma, mb, mc, p);
+  kernel<<<grid, kThreads, L::kTotal, st>>>(ma, mb, mc, p);
   ZP_LAUNCH_CHECK("gemm_tc_kernel");
   return ZP_OK;
 }
 
-template <int P, int BK, int STAGES>
-int launch_pair(const ZpGemmTc &g, cudaStream_t st) {
+template <int P, int BK, int STAGES, int BN_CAP>
+int launch(const ZpGemmTc &g, cudaStream_t st) {
+  const int mode = g.epi ? g.epi->mode : ZP_EPI_NONE;
+  if constexpr (SmemLayout<P, BK, STAGES, BN_CAP>::kTmaEpilogue && (P == 1 || P == 2)) {
+    if (mode == ZP_EPI_GATE) return launch_e<P, BK, STAGES, BN_CAP, ZP_EPI_GATE>(g, st);
+    if (mode == ZP_EPI_ROTATE_BACK) return launch_e<P, BK, STAGES, BN_CAP, ZP_EPI_ROTATE_BACK>(g, st);
+  }
+  if (mode != ZP_EPI_NONE) return ZP_ERR_UNSUPPORTED;
+  return launch_e<P, BK, STAGES, BN_CAP, ZP_EPI_NONE>(g, st);
+}
+
+template <int P, int BK, int STAGES, int EPI>
+int launch_pair_e(const ZpGemmTc &g, cudaStream_t st) {
   using L = SmemLayoutPair<P, BK, STAGES>;
   static_assert(L::kTotal <= 232448, "shared memory budget of one CTA");
-  static int max_pairs = -1;            // co-resident CTA pairs of this kernel on the device
-  auto kernel = gemm_tc_pair_kernel<P, BK, STAGES>;
+  static_assert(EPI == ZP_EPI_NONE || L::kTmaEpilogue, "fused epilogues need the store stage");
+  auto kernel = [] {
+    if constexpr (EPI == ZP_EPI_NONE) return gemm_tc_pair_kernel<P, BK, STAGES>;
+    else return gemm_tc_pair_fused_kernel<P, BK, STAGES, EPI>;
+  }();
   cudaLaunchAttribute attr[1];
   attr[0].id = cudaLaunchAttributeClusterDimension;
   attr[0].val.clusterDim.x = 2; attr[0].val.clusterDim.y = 1; attr[0].val.clusterDim.z = 1;
   cudaLaunchConfig_t cfg = {};
   cfg.blockDim = dim3(kThreads); cfg.dynamicSmemBytes = L::kTotal; cfg.stream = st;
   cfg.attrs = attr; cfg.numAttrs = 1;
-  if (max_pairs < 0) {
-    ZP_CUDA(cudaFuncSetAttribute(kernel, cudaFuncAttributeMaxDynamicSharedMemorySize, L::kTotal));
-    int dev = 0, sms = 148, n = 0;
-    cudaGetDevice(&dev);
-    cudaDeviceGetAttribute(&sms, cudaDevAttrMultiProcessorCount, dev);
-    cfg.gridDim = dim3((unsigned)(sms / 2 * 2));
-    ZP_CUDA(cudaOccupancyMaxActiveClusters(&n, kernel, &cfg));
-    max_pairs = n < sms / 2 ? n : sms / 2;
+  int dev = 0;
+  ZP_CUDA(cudaGetDevice(&dev));
+  if (dev < 0 || dev >= kMaxDevices) return ZP_ERR_UNSUPPORTED;
+  static PerDevice pairs;               // co-resident CTA pairs of this kernel, per device
+  int max_pairs;
+  {
+    std::lock_guard<std::mutex> hold(pairs.lock);
+    if (!pairs.done[dev]) {
+      ZP_CUDA(cudaFuncSetAttribute(kernel, cudaFuncAttributeMaxDynamicSharedMemorySize, L::kTotal));
+      int sms = 148, n = 0;
+      cudaDeviceGetAttribute(&sms, cudaDevAttrMultiProcessorCount, dev);
+      cfg.gridDim = dim3((unsigned)(sms / 2 * 2));
+      ZP_CUDA(cudaOccupancyMaxActiveClusters(&n, kernel, &cfg));
+      pairs.value[dev] = n < sms / 2 ? n : sms / 2;
+      pairs.done[dev] = true;
+    }
+    max_pairs = pairs.value[dev];
   }
   if (max_pairs < 1) return ZP_ERR_UNSUPPORTED;
   GemmParams p;
-  p.M = (int)g.M; p.N = (int)g.N; p.K = (int)g.K;
+  fill_params(p, g, BK);
   // whole 32-column store blocks; each CTA's half of an MN-major tile comes in 64-wide blocks
   p.BN = pick_bn(g.N, 256, g.b_mn ? 128 : 32);
   p.num_m = (int)zp_ceil_div(g.M, BM2);
   p.num_n = (int)zp_ceil_div(g.N, p.BN);
-  split_plan(g, BK, &p.ksplit, &p.kb_per_split, &p.num_k);
-  const int kc_elems = g.kc_elems > 0 ? g.kc_elems : 2048;
-  p.kc = kc_elems / BK < 1 ? 1 : kc_elems / BK;
-  p.a_mn = g.a_mn; p.b_mn = g.b_mn;
-  p.fp16 = g.fp16; p.scale_a = g.scale_a; p.scale_b = g.scale_b; p.absmax_out = g.absmax_out;
-  p.bias = g.bias; p.C = g.C; p.ldc = g.ldc; p.split_stride = g.split_stride; p.status = g.status;
   const CUtensorMapSwizzle kswz = BK == 64 ? CU_TENSOR_MAP_SWIZZLE_128B : CU_TENSOR_MAP_SWIZZLE_64B;
   CUtensorMap ma, mb;
   int rc;
@@ -1150,7 +1402,8 @@ int launch_pair(const ZpGemmTc &g, cudaStream_t st) {
   if (rc) return rc;
   CUtensorMap mc;
   const int chunks = (int)zp_ceil_div(p.kb_per_split, p.kc);
-  p.tma_store = L::kTmaEpilogue && !(g.absmax_out && chunks > 1);
+  p.tma_store = EPI == ZP_EPI_NONE ? (L::kTmaEpilogue && !(g.absmax_out && chunks > 1))
+                                   : p.epi.store_c;
   if (p.tma_store) {
     if ((rc = make_map_c(&mc, g.C, g.N, g.M, p.ksplit, g.ldc, g.split_stride))) return rc;
   } else {
@@ -1161,6 +1414,14 @@ int launch_pair(const ZpGemmTc &g, cudaStream_t st) {
   ZP_CUDA(cudaLaunchKernelEx(&cfg, kernel, ma, mb, mc, p));
   ZP_LAUNCH_CHECK("gemm_tc_pair_kernel");
   return ZP_OK;
+}
+
+template <int P, int BK, int STAGES>
+int launch_pair(const ZpGemmTc &g, cudaStream_t st) {
+  const int mode = g.epi ? g.epi->mode : ZP_EPI_NONE;
+  if (mode == ZP_EPI_GATE) return launch_pair_e<P, BK, STAGES, ZP_EPI_GATE>(g, st);
+  if (mode == ZP_EPI_ROTATE_BACK) return launch_pair_e<P, BK, STAGES, ZP_EPI_ROTATE_BACK>(g, st);
+  return launch_pair_e<P, BK, STAGES, ZP_EPI_NONE>(g, st);
 }
 
 }  // namespace
@@ -1184,10 +1445,16 @@ int zp_gemm_tc_pick_splits(const ZpGemmTc &g, int max_splits) {
   return best;
 }
 
+bool zp_gemm_tc_fusable(const ZpGemmTc &g) {
+  if (g.M <= 0 || g.N <= 0 || g.K <= 0) return false;
+  return fused_mode_ok(g, block_k(g));
+}
+
 int zp_launch_gemm_tc(const ZpGemmTc &g, cudaStream_t st) {
   if (g.M <= 0 || g.N <= 0) return ZP_OK;
   if (g.K <= 0) return ZP_ERR_INVALID_ARG;
   if (g.fp16 != (g.planes == 2)) return ZP_ERR_UNSUPPORTED;   // fp16 planes come in pairs
+  if (!fused_mode_ok(g, block_k(g))) return ZP_ERR_UNSUPPORTED;
   if ((g.lda % 8) || (g.ldb % 8) || (g.a_plane % 8) || (g.b_plane % 8) || (g.ldc % 4) ||
       (g.split_stride % 4))
     return ZP_ERR_INVALID_ARG;

@@ -632,7 +632,52 @@ node_reduce_kernel(int64_t N, int KC4, const float4 *__restrict__ du_both,
   }
 }
 
+// Final sums after the rotate-back epilogue of conv2.  The epilogue leaves, per m' row r, the
+// partial sums of a node's edges: head[n] for the run that starts at the node's first edge and
+// cont[b] for the run that enters 32-edge block b from the block before.  One block per node adds,
+// per output row (l, j), the rows r of that degree in table order and, within a row, head first and
+// then the continuation blocks in ascending order: a fixed order, so results repeat bit for bit.
+__global__ void __launch_bounds__(128)
+node_sum_kernel(const __grid_constant__ ZpTables t, int64_t N, const float *__restrict__ head,
+                const float *__restrict__ cont, const int32_t *__restrict__ row_ptr,
+                float *__restrict__ node_out) {
+  const int64_t n = blockIdx.x;
+  const int C4 = t.C / 4;
+  const int beg = row_ptr[n], end = row_ptr[n + 1];
+  const int b_first = beg >> 5, b_last = end > beg ? (end - 1) >> 5 : b_first;
+  const size_t slab = (size_t)t.nnz * t.C;
+  const float *hn = head + (size_t)n * slab;
+  for (int i = threadIdx.x; i < t.K * C4; i += blockDim.x) {
+    const int k = i / C4, c = (i - k * C4) * 4;
+    int l = 0;
+    while ((l + 1) * (l + 1) <= k) ++l;
+    const int j = k - l * l;
+    float4 acc = make_float4(0.f, 0.f, 0.f, 0.f);
+    if (end > beg) {
+      const int mm = t.mmax < l ? t.mmax : l;
+      for (int q = l - mm; q <= l + mm; ++q) {
+        const size_t o = (size_t)(t.rot_off[t.row_of[l][q]] + j) * t.C + c;
+        float4 v = *reinterpret_cast<const float4 *>(hn + o);
+        for (int b = b_first + 1; b <= b_last; ++b) {
+          const float4 w = *reinterpret_cast<const float4 *>(cont + (size_t)b * slab + o);
+          v.x += w.x; v.y += w.y; v.z += w.z; v.w += w.w;
+        }
+        acc.x += v.x; acc.y += v.y; acc.z += v.z; acc.w += v.w;
+      }
+    }
+    *reinterpret_cast<float4 *>(node_out + ((size_t)n * t.K + k) * t.C + c) = acc;
+  }
+}
+
 }  // namespace
+
+int zp_launch_node_sum(const zp_plan *p, int64_t N, const float *head, const float *cont,
+                       const int32_t *row_ptr, float *node_out, cudaStream_t st) {
+  if (N == 0) return ZP_OK;
+  node_sum_kernel<<<(unsigned)N, 128, 0, st>>>(p->t, N, head, cont, row_ptr, node_out);
+  ZP_LAUNCH_CHECK("node_sum_kernel");
+  return ZP_OK;
+}
 
 int zp_launch_rotate_in(const zp_plan *p, int64_t E, const float *x, const int32_t *src,
                         const int32_t *dst, const float *rot, const float *radial,

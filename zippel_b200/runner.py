@@ -23,7 +23,7 @@ class EdgeConvRunner:
         self.lib = _lib.load()
         n, e, s, dev = graph.n_nodes, graph.n_edges, plan.sizes, plan.device
         f32 = dict(dtype=torch.float32, device=dev)
-        self.ws = plan.workspace(n, e, with_backward)
+        self.ws = plan.workspace(n, e, with_backward, inference=not with_backward)
         self.node_out = torch.empty(n, s.K, plan.c, **f32)
         if with_backward:
             self.grad_x = torch.empty(n, s.K, plan.c, **f32)
@@ -57,7 +57,9 @@ class EdgeConvRunner:
         x, ev, cg, sg, rad, en = self.inputs
         g = self.graph
         st = torch.cuda.current_stream().cuda_stream
-        _lib.check(self.lib.zp_eso2_forward(
+        # without a backward nothing is kept: the leaner entry point
+        fn = self.lib.zp_eso2_forward if self.with_backward else self.lib.zp_eso2_forward_inference
+        _lib.check(fn(
             self.plan.handle, g.n_nodes, g.n_edges, x.data_ptr(), ev.data_ptr(), cg.data_ptr(),
             sg.data_ptr(), rad.data_ptr(), en.data_ptr(), g.src.data_ptr(), g.dst.data_ptr(),
             g.row_ptr.data_ptr(), ctypes.byref(self._w), self.node_out.data_ptr(),

@@ -90,3 +90,18 @@ def test_two_gpu_destination_partition(tmp_path, jd64):
         assert rel_l2(st["gpos"], want_gpos) < 1e-5
         for k in ("c1_m0.weight", "c1_m.0.weight", "c2_m.1.weight", "c2_m0.bias", "rad_func.0.weight"):
             assert rel_l2(st["gw"][k], want_pg[k]) < 1e-5, k
+
+
+def test_one_process_two_devices(jd64):
+    """A small forward + VJP on cuda:0 and then on cuda:1 from the same process: every kernel's
+    one-time set-up (raised shared-memory limit, resident cluster count) is kept per device."""
+    if torch.cuda.device_count() < 2:
+        pytest.skip("needs two GPUs")
+    from tests.helpers import (check_against, gpu_node_out_and_vjp, make_block,
+                               oracle_node_out_and_vjp)
+    cfg, params, case = _case()
+    want = oracle_node_out_and_vjp(cfg, params, case, case["upstream"], jd64)
+    for dev in ("cuda:0", "cuda:1", "cuda:0"):
+        got = gpu_node_out_and_vjp(make_block(cfg, params, device=dev), case, case["upstream"],
+                                   device=dev)
+        check_against(*got, *want)

@@ -204,6 +204,31 @@ def test_csr_build_bit_exact(n, e, seed):
         assert np.array_equal(getattr(got, key).cpu().numpy(), want[key]), key
 
 
+def test_csr_build_rejects_node_indices_out_of_range():
+    """What torch indexing does for the reference (IndexError), without any out-of-range access."""
+    from zippel_b200.graph import EdgeGraph
+    ei = torch.tensor([[0, 1, 2, 5], [1, 2, 0, 1]], dtype=torch.int64, device="cuda")
+    with pytest.raises(IndexError):
+        EdgeGraph.build(ei, 5)                       # src 5 >= N
+    ei[0, 3] = -1
+    with pytest.raises(IndexError):
+        EdgeGraph.build(ei, 5)
+    ei[0, 3] = 4
+    assert EdgeGraph.build(ei, 5).row_ptr.cpu().tolist() == [0, 1, 3, 4, 4, 4]
+
+
+def test_chunks_keep_leading_nodes_without_edges():
+    """Edge-less nodes at the start, followed by a node above the budget: every row must be covered."""
+    from zippel_b200.graph import EdgeGraph
+    dst = torch.cat([torch.full((100,), 2), torch.full((20,), 3)])
+    src = torch.arange(120) % 2
+    graph = EdgeGraph.build(torch.stack([src, dst]).cuda(), 5)
+    pieces = graph.chunks(10)
+    assert pieces[0].n0 == 0 and pieces[-1].n1 == 5
+    assert all(a.n1 == b.n0 and a.e1 == b.e0 for a, b in zip(pieces, pieces[1:]))
+    assert sum(p.n_edges for p in pieces) == 120
+
+
 def test_abi_rejects_bad_arguments():
     from zippel_b200 import _lib
     from zippel_b200.blocks.eso2 import Plan

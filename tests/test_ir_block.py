@@ -78,3 +78,60 @@ def test_bind_accepts_reference_shaped_layouts(jd64):
     assert inputs["c1_w1a"].shape == (1, 4, 4, 4, 16) and inputs["rad_wm2"].shape == (1, 3, 16, 4)
     prog, _ = build_forward(BlockConfig(**cfg))
     assert set(prog.inputs) <= set(inputs)
+
+
+def _training_step_oracle(params, cfg, batch, jd, pos, x_node, e_ref, f_ref, w_e=1.0, w_f=1.0):
+    """E, F = -dE/dpos kept differentiable, L = w_e (E - e_ref)^2 + w_f mean((F - f_ref)^2): the
+    reference's conservative_training_step (blocks/eso2_ref.py:365-385) on the oracle."""
+    e = orc.block_energy(params, cfg, pos, batch["atomic_numbers"], x_node, batch["edge_index"],
+                         batch["shifts"], batch["cos_gamma_k"], batch["sin_gamma_k"], jd)
+    (de,) = torch.autograd.grad(e, pos, create_graph=True)
+    f = -de
+    return e, f, w_e * (e - e_ref).pow(2).mean() + w_f * (f - f_ref).pow(2).mean()
+
+
+@pytest.mark.parametrize("lmax,mmax", [(2, 2), (3, 1)])
+def test_double_backward_program_three_ways(lmax, mmax, jd64):
+    """build_dbwd evaluated by the interpreter == double autograd through the oracle == central
+    differences of the loss (after the reference's tests/test_ir_block.py:106-137)."""
+    from zippel_b200.blocks.eso2_ir import build_dbwd
+    cfg, params, block, batch = setup(lmax, mmax, seed=5)
+    n = batch["pos"].shape[0]
+    g = torch.Generator("cpu").manual_seed(9)
+    e_ref = torch.randn(1, generator=g, dtype=DT)
+    f_ref = torch.randn(n, 3, generator=g, dtype=DT)
+    prog, meta = build_dbwd(BlockConfig(**cfg), block.gauss_coeff, w_e=0.7, w_f=1.3)
+    inputs, sizes = bind(block, batch, jd64)
+    inputs |= {"seed_E": torch.ones(1, dtype=DT), "seed_L": torch.ones(1, dtype=DT), "e_ref": e_ref,
+               "f_ref": f_ref, "inv_nf": torch.full((1,), 1.0 / (3 * n), dtype=DT)}
+    env = interp.run(prog, inputs, sizes)
+
+    p = {k: v.clone().requires_grad_(True) for k, v in params.items()}
+    pos = batch["pos"].clone().requires_grad_(True)
+    x = batch["x_node"].clone().requires_grad_(True)
+    e, f, loss = _training_step_oracle(p, cfg, batch, jd64, pos, x, e_ref[0], f_ref, 0.7, 1.3)
+    names = ["c1_m0.weight", "c2_m0.bias", "rad_func.0.weight", "readout.2.weight", "rad_func.4.bias"]
+    grads = torch.autograd.grad(loss, [pos, x, *[p[k] for k in names]])
+
+    rel = lambda a, b: ((a - b).norm() / b.norm().clamp_min(1e-300)).item()      # noqa: E731
+    assert abs(env[meta["loss"]].item() - loss.item()) < 1e-11 * max(1.0, abs(loss.item()))
+    assert rel(env[meta["force"]], f.detach()) < 1e-10
+    assert rel(env[meta["grads"]["pos"]], grads[0]) < 1e-9
+    assert rel(env[meta["grads"]["x_node"]], grads[1]) < 1e-9
+    ir_names = {"c1_m0.weight": "c1_w0", "c2_m0.bias": "c2_b0", "rad_func.0.weight": "rad_w0",
+                "readout.2.weight": "ro_w1", "rad_func.4.bias": "rad_be1"}
+    for k, want in zip(names, grads[2:]):
+        got = env[meta["grads"][ir_names[k]]].reshape(want.shape)
+        assert rel(got, want) < 1e-9, k
+
+    # third leg: central differences of L along a random direction in position space
+    def loss_at(q):
+        q = q.clone().requires_grad_(True)
+        return _training_step_oracle(params, cfg, batch, jd64, q, batch["x_node"], e_ref[0], f_ref,
+                                     0.7, 1.3)[2].item()
+
+    d = torch.randn(n, 3, generator=g, dtype=DT)
+    h = 1e-6
+    fd = (loss_at(batch["pos"] + h * d) - loss_at(batch["pos"] - h * d)) / (2 * h)
+    got = (env[meta["grads"]["pos"]] * d).sum().item()
+    assert abs(got - fd) < 1e-6 * max(abs(fd), 1e-9)

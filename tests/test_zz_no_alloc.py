@@ -52,3 +52,38 @@ def test_static_scratch_refuses_sizes_beyond_its_capacity():
     assert lib.zp_csr_build_static(ei.data_ptr(), 262145, 10, *args) == 7
     assert lib.zp_csr_build_static(ei.data_ptr(), 8, 65537, *args) == 7
     assert b"capacity" in lib.zp_status_string(7)
+
+
+@pytest.mark.parametrize("n,e", [(65536, 262144), (65536, 0), (1, 262144), (17, 0)])
+def test_static_scratch_at_its_limits(n, e):
+    """Exactly at the two maxima the sort's scratch fills the fixed array to the byte; an empty edge
+    list is legal.  Results equal zp_csr_build's bit for bit."""
+    from zippel_b200 import _lib
+    from zippel_b200.graph import EdgeGraph
+    lib = _lib.load()
+    assert lib.zp_csr_work_bytes(262144, 65536) == 1574144            # ZP_CSR_STATIC_BYTES
+    g = torch.Generator("cpu").manual_seed(n + e)
+    ei = torch.randint(0, n, (2, e), generator=g).cuda()
+    rc, got = _static_build(lib, ei, n)
+    assert rc == 0, lib.zp_status_string(rc)
+    want = EdgeGraph.build(ei, n)
+    torch.cuda.synchronize()
+    for key, val in got.items():
+        assert np.array_equal(val.cpu().numpy(), getattr(want, key).cpu().numpy()), key
+
+
+def test_static_scratch_flags_node_indices_out_of_range():
+    """An index outside [0, N) must not be used as an address into the fixed array: the edge is
+    left out and the status call reports it; the next, valid call is clean again."""
+    import ctypes
+    from zippel_b200 import _lib
+    lib = _lib.load()
+    ei = torch.tensor([[0, 1, 2, 3], [1, 2, 99, 0]], dtype=torch.int64, device="cuda")
+    rc, got = _static_build(lib, ei, 4)
+    assert rc == 0
+    flag = ctypes.c_int(0)
+    assert lib.zp_csr_static_status(ctypes.byref(flag)) == 0 and flag.value == 1
+    assert got["row_ptr"].cpu().tolist() == [0, 1, 2, 3, 4]           # three edges counted
+    ei[1, 2] = 3
+    rc, _ = _static_build(lib, ei, 4)
+    assert rc == 0 and lib.zp_csr_static_status(ctypes.byref(flag)) == 0 and flag.value == 0

@@ -328,4 +328,42 @@ def build_force(cfg: BlockConfig = BlockConfig(), gauss_coeff=None):
     return p, meta
 
 
-__all__ = ["build_wigner", "build_forward", "build_force", "linear", "layernorm"]
+def build_dbwd(cfg: BlockConfig = BlockConfig(), gauss_coeff=None, w_e: float = 1.0,
+               w_f: float = 1.0):
+    """The conservative training step as one program (reference ``blocks/eso2_ir.py:593-636`` for
+    ``conservative_training_step``, ``blocks/eso2_ref.py:365-385``): energy, force F = -dE/dpos,
+    loss L = w_e (E - e_ref)^2 + w_f mean((F - f_ref)^2), and dL/d(parameters, pos, x_node).
+
+    The second ``vjp`` runs over a program that already contains the force ops, so it
+    differentiates through them: a genuine double backward, not two first-order passes.
+    Extra inputs: ``e_ref`` [graph], ``f_ref`` [node, 3], ``inv_nf`` = 1 / (3 N) as a rank-0
+    constant (N is a run-time size and cannot sit in a path coefficient), ``seed_L`` [graph].
+    """
+    from ..zippel.vjp import vjp
+
+    p, meta = build_force(cfg, gauss_coeff)
+    graph_t, vec_t = BufferType("graph", ()), BufferType("node", (("x", 3),))
+    p.add_input("e_ref", graph_t)
+    p.add_input("f_ref", vec_t)
+    p.add_input("inv_nf", BufferType("none", ()))
+    b = _Builder(p)
+
+    err_e = b.lin([(1.0, meta["energy"]), (-1.0, "e_ref")], hint="dE")
+    term_e = b.prod(err_e, err_e, coeff=w_e, hint="Eterm")         # one graph: the mean is the square
+    err_f = p.contract([meta["force"], "f_ref"], vec_t,
+                       [P(1.0, "x->x", (0,), ((S,),), (S,)), P(-1.0, "x->x", (1,), ((S,),), (S,))],
+                       hint="dF")
+    term_f = p.contract([err_f, err_f, "inv_nf"], graph_t,
+                        [P(w_f, "x,x,->", (0, 1, 2), ((S,), (S,), ()), ())], out_index_map="zn",
+                        hint="Fterm")
+    loss = b.lin([(1.0, term_e), (1.0, term_f)], hint="loss")
+
+    seed = p.add_input("seed_L", graph_t)
+    wrt = [*meta["params"], "pos", "x_node"]
+    grads = vjp(p, loss, wrt, seed=seed, zero_index={"node": "zn", "edge": "ze"})
+    p.outputs = (loss, *grads.values())
+    meta |= {"loss": loss, "seed_L": seed, "grads": grads, "kind": "dbwd"}
+    return p, meta
+
+
+__all__ = ["build_wigner", "build_forward", "build_force", "build_dbwd", "linear", "layernorm"]

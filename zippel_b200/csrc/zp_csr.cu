@@ -17,13 +17,24 @@ namespace {
 
 constexpr int kScanBlock = 1024;
 
-__global__ void count_kernel(int64_t E, const int64_t *__restrict__ key, int32_t *counts) {
+// Node indices come from the caller.  One outside [0, N) is never used as an address: the edge
+// is left out, the flag word is raised, and zp_csr_status reports it (the arrays of such a call
+// are not a valid sort).
+__global__ void count_kernel(int64_t E, int64_t N, const int64_t *__restrict__ key,
+                             const int64_t *__restrict__ other, int32_t *counts, int32_t *flag) {
   const int64_t i = (int64_t)blockIdx.x * blockDim.x + threadIdx.x;
-  if (i < E) atomicAdd(&counts[key[i]], 1);
+  if (i >= E) return;
+  const int64_t k = key[i];
+  if ((uint64_t)k >= (uint64_t)N || (uint64_t)other[i] >= (uint64_t)N) {
+    *flag = 1;
+    return;
+  }
+  atomicAdd(&counts[k], 1);
 }
+// keys written by rank_dst_kernel: in range by construction, -1 in slots an invalid edge left empty
 __global__ void count32_kernel(int64_t E, const int32_t *__restrict__ key, int32_t *counts) {
   const int64_t i = (int64_t)blockIdx.x * blockDim.x + threadIdx.x;
-  if (i < E) atomicAdd(&counts[key[i]], 1);
+  if (i < E && key[i] >= 0) atomicAdd(&counts[key[i]], 1);
 }
 
 // exclusive scan of n ints in three steps: per-block scan, scan of block totals, add back
@@ -59,12 +70,14 @@ __global__ void scan_add_kernel(int64_t n, int32_t *out, const int32_t *__restri
   if (i == n) out[n] = total_slot_value_is_E;
 }
 
-__global__ void bucket_kernel(int64_t E, const int64_t *__restrict__ key,
+__global__ void bucket_kernel(int64_t E, int64_t N, const int64_t *__restrict__ key,
+                              const int64_t *__restrict__ other,
                               const int32_t *__restrict__ row_ptr, int32_t *cursor,
                               int32_t *tmp) {
   const int64_t i = (int64_t)blockIdx.x * blockDim.x + threadIdx.x;
   if (i >= E) return;
   const int64_t k = key[i];
+  if ((uint64_t)k >= (uint64_t)N || (uint64_t)other[i] >= (uint64_t)N) return;   // flagged above
   tmp[row_ptr[k] + atomicAdd(&cursor[k], 1)] = (int32_t)i;
 }
 __global__ void bucket32_kernel(int64_t E, const int32_t *__restrict__ key,
@@ -73,6 +86,7 @@ __global__ void bucket32_kernel(int64_t E, const int32_t *__restrict__ key,
   const int64_t i = (int64_t)blockIdx.x * blockDim.x + threadIdx.x;
   if (i >= E) return;
   const int32_t k = key[i];
+  if (k < 0) return;
   tmp[row_ptr[k] + atomicAdd(&cursor[k], 1)] = (int32_t)i;
 }
 
@@ -116,7 +130,7 @@ __global__ void rank_src_kernel(int64_t N, const int32_t *__restrict__ row_ptr_s
 }
 
 struct CsrWork {
-  int32_t *counts, *cursor, *tmp, *block_sums;
+  int32_t *flag, *counts, *cursor, *tmp, *block_sums;
   size_t bytes;
 };
 
@@ -128,6 +142,7 @@ CsrWork carve_csr(int64_t E, int64_t N, void *base) {
     off += zp_align_up(n * sizeof(int32_t), 256);
     return p;
   };
+  w.flag = take(1);
   w.counts = take((size_t)N + 1);
   w.cursor = take((size_t)N + 1);
   w.tmp = take((size_t)(E > 0 ? E : 1));
@@ -173,15 +188,22 @@ int zp_csr_build(const int64_t *edge_index, int64_t E, int64_t N, int32_t *perm,
   int rc;
 
   // destination view
+  ZP_CUDA(cudaMemsetAsync(w.flag, 0, sizeof(int32_t), st));
+  if (E) {      // slots an invalid edge leaves empty read as "no edge"
+    ZP_CUDA(cudaMemsetAsync(src_sorted, 0xff, sizeof(int32_t) * E, st));
+    ZP_CUDA(cudaMemsetAsync(dst_sorted, 0xff, sizeof(int32_t) * E, st));
+    ZP_CUDA(cudaMemsetAsync(perm, 0, sizeof(int32_t) * E, st));
+    ZP_CUDA(cudaMemsetAsync(perm_src, 0, sizeof(int32_t) * E, st));
+  }
   ZP_CUDA(cudaMemsetAsync(w.counts, 0, sizeof(int32_t) * (N + 1), st));
   ZP_CUDA(cudaMemsetAsync(w.cursor, 0, sizeof(int32_t) * (N + 1), st));
   if (E) {
-    count_kernel<<<eb, 256, 0, st>>>(E, dst64, w.counts);
+    count_kernel<<<eb, 256, 0, st>>>(E, N, dst64, src64, w.counts, w.flag);
     ZP_LAUNCH_CHECK("count_kernel");
   }
   if ((rc = exclusive_scan(N, w.counts, row_ptr, w.block_sums, E, st))) return rc;
   if (E) {
-    bucket_kernel<<<eb, 256, 0, st>>>(E, dst64, row_ptr, w.cursor, w.tmp);
+    bucket_kernel<<<eb, 256, 0, st>>>(E, N, dst64, src64, row_ptr, w.cursor, w.tmp);
     ZP_LAUNCH_CHECK("bucket_kernel");
     rank_dst_kernel<<<nbw, 256, 0, st>>>(N, src64, row_ptr, w.tmp, perm, src_sorted, dst_sorted);
     ZP_LAUNCH_CHECK("rank_dst_kernel");
@@ -204,10 +226,36 @@ int zp_csr_build(const int64_t *edge_index, int64_t E, int64_t N, int32_t *perm,
   return ZP_OK;
 }
 
+int zp_csr_status(const void *work, int *status_out) {
+  if (!work || !status_out) return ZP_ERR_INVALID_ARG;
+  int32_t flag = 0;
+  ZP_CUDA(cudaMemcpy(&flag, carve_csr(0, 0, const_cast<void *>(work)).flag, sizeof(flag),
+                     cudaMemcpyDeviceToHost));
+  *status_out = flag ? ZP_ERR_INVALID_ARG : ZP_OK;
+  return ZP_OK;
+}
+
 // The sort without a caller-provided work buffer and without any allocation: the scratch is the
 // file-scope device array above.  Its device address is looked up once per device (first call on
 // that device, with that device current) and cached; the sort itself is zp_csr_build unchanged,
 // which clears the counters it needs at the start of every call.
+static int static_scratch(void **out) {
+  constexpr int kMaxDevices = 64;
+  static std::mutex mu;
+  static void *scratch_of_device[kMaxDevices] = {nullptr};
+  int dev = -1;
+  ZP_CUDA(cudaGetDevice(&dev));
+  if (dev < 0 || dev >= kMaxDevices) return ZP_ERR_UNSUPPORTED;
+  std::lock_guard<std::mutex> lock(mu);
+  if (!scratch_of_device[dev]) {
+    void *ptr = nullptr;
+    ZP_CUDA(cudaGetSymbolAddress(&ptr, g_csr_static_scratch));
+    scratch_of_device[dev] = ptr;
+  }
+  *out = scratch_of_device[dev];
+  return ZP_OK;
+}
+
 int zp_csr_build_static(const int64_t *edge_index, int64_t E, int64_t N, int32_t *perm,
                         int32_t *src_sorted, int32_t *dst_sorted, int32_t *row_ptr,
                         int32_t *perm_src, int32_t *row_ptr_src, void *stream) {
@@ -215,24 +263,18 @@ int zp_csr_build_static(const int64_t *edge_index, int64_t E, int64_t N, int32_t
   if (E > ZP_CSR_STATIC_MAX_EDGES || N > ZP_CSR_STATIC_MAX_NODES ||
       carve_csr(E, N, nullptr).bytes > (size_t)ZP_CSR_STATIC_BYTES)
     return ZP_ERR_TOO_LARGE;
-  constexpr int kMaxDevices = 64;
-  static std::mutex mu;
-  static void *scratch_of_device[kMaxDevices] = {nullptr};
-  int dev = -1;
-  ZP_CUDA(cudaGetDevice(&dev));
-  if (dev < 0 || dev >= kMaxDevices) return ZP_ERR_UNSUPPORTED;
   void *scratch = nullptr;
-  {
-    std::lock_guard<std::mutex> lock(mu);
-    if (!scratch_of_device[dev]) {
-      void *ptr = nullptr;
-      ZP_CUDA(cudaGetSymbolAddress(&ptr, g_csr_static_scratch));
-      scratch_of_device[dev] = ptr;
-    }
-    scratch = scratch_of_device[dev];
-  }
+  const int rc = static_scratch(&scratch);
+  if (rc) return rc;
   return zp_csr_build(edge_index, E, N, perm, src_sorted, dst_sorted, row_ptr, perm_src,
                       row_ptr_src, scratch, (size_t)ZP_CSR_STATIC_BYTES, stream);
+}
+
+int zp_csr_static_status(int *status_out) {
+  void *scratch = nullptr;
+  const int rc = static_scratch(&scratch);
+  if (rc) return rc;
+  return zp_csr_status(scratch, status_out);
 }
 
 }  // extern "C"

@@ -747,7 +747,7 @@ gemm_tc_kernel(const __grid_constant__ CUtensorMap map_a, const __grid_constant_
 }
 // the same contraction with a fused epilogue (the epilogue warps hold more live values)
 template <int P, int BK, int STAGES, int BN_CAP, int EPI>
-__global__ void __maxnreg__(200)
+__global__ void __launch_bounds__(kThreads, 1)
 gemm_tc_fused_kernel(const __grid_constant__ CUtensorMap map_a,
                      const __grid_constant__ CUtensorMap map_b,
                      const __grid_constant__ CUtensorMap map_c,
@@ -1120,7 +1120,7 @@ gemm_tc_pair_kernel(const __grid_constant__ CUtensorMap map_a,
   gemm_tc_pair_body<P, BK, STAGES, ZP_EPI_NONE>(map_a, map_b, map_c, p);
 }
 template <int P, int BK, int STAGES, int EPI>
-__global__ void __maxnreg__(200)
+__global__ void __launch_bounds__(kThreads, 1)
 gemm_tc_pair_fused_kernel(const __grid_constant__ CUtensorMap map_a,
                           const __grid_constant__ CUtensorMap map_b,
                           const __grid_constant__ CUtensorMap map_c,

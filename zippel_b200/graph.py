@@ -65,16 +65,20 @@ class EdgeGraph:
             out = [EdgeChunk(0, self.n_edges, 0, self.n_nodes, self)]
         else:
             rp = self.row_ptr.cpu().numpy().astype(np.int64)
-            out, n0 = [], 0
+            out, n0, start = [], 0, 0
             while n0 < self.n_nodes:
                 # furthest node boundary n1 > n0 with rp[n1] - rp[n0] <= max_edges
                 n1 = int(np.searchsorted(rp, rp[n0] + max_edges, side="right")) - 1
                 n1 = min(max(n1, n0 + 1), self.n_nodes)
                 if n1 == self.n_nodes or rp[n1] > rp[n0]:
-                    out.append((n0, n1))
+                    out.append((start, n1))          # `start` < n0: edge-less nodes carried along
+                    start = n1
                 elif out:
                     out[-1] = (out[-1][0], n1)
+                    start = n1
                 n0 = n1
+            assert out[0][0] == 0 and out[-1][1] == self.n_nodes
+            assert all(a[1] == b[0] for a, b in zip(out, out[1:]))
             pieces = []
             for n0, n1 in out:
                 e0, e1 = int(rp[n0]), int(rp[n1])
@@ -85,8 +89,13 @@ class EdgeGraph:
         return out
 
     @staticmethod
-    def build(edge_index: torch.Tensor, n_nodes: int) -> "EdgeGraph":
-        """Runs ``zp_csr_build`` on ``edge_index`` ([2, E] int64, CUDA)."""
+    def build(edge_index: torch.Tensor, n_nodes: int, validate: bool = True) -> "EdgeGraph":
+        """Runs ``zp_csr_build`` on ``edge_index`` ([2, E] int64, CUDA).
+
+        ``validate``: read back the kernel's range flag (one device synchronisation) and raise
+        ``IndexError`` if a node index lies outside ``[0, n_nodes)``, as indexing with it raises in
+        the reference.  Skipped while the stream is being captured into a CUDA graph (no
+        synchronisation is possible there; the kernels leave such edges out either way)."""
         if not edge_index.is_cuda:
             raise RuntimeError("EdgeGraph.build needs a CUDA edge_index; there is no CPU path")
         lib = _lib.load()
@@ -103,6 +112,12 @@ class EdgeGraph:
                                         dst.data_ptr(), row_ptr.data_ptr(), perm_src.data_ptr(),
                                         row_ptr_src.data_ptr(), work.data_ptr(), nbytes, st),
                        "zp_csr_build")
+            if validate and e and not torch.cuda.is_current_stream_capturing():
+                import ctypes
+                flag = ctypes.c_int(0)
+                _lib.check(lib.zp_csr_status(work.data_ptr(), ctypes.byref(flag)), "zp_csr_status")
+                if flag.value:
+                    raise IndexError(f"edge_index names a node outside [0, {n_nodes})")
         return EdgeGraph(n_nodes, e, perm[:e], src[:e], dst[:e], row_ptr, perm_src[:e], row_ptr_src)
 
 

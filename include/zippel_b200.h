@@ -91,10 +91,10 @@ int zp_plan_tables(const zp_plan *plan, int32_t *row_l, int32_t *row_m, int32_t 
  * `work` needs zp_csr_work_bytes(E, N) bytes.                                              */
 size_t zp_csr_work_bytes(int64_t n_edges, int64_t n_nodes);
 /* Node indices outside [0, n_nodes) are never used as addresses: such an edge is left out and a
- * flag in `work` is raised (the reference's torch indexing raises on the same input).  After the
- * call has run, zp_csr_status reads the flag (synchronously): *status_out = ZP_OK, or
- * ZP_ERR_INVALID_ARG when the arrays of that call are not a valid sort.                       */
-int zp_csr_status(const void *work, int *status_out);
+ * flag in `work` is raised (the reference's torch indexing raises on the same input).
+ * zp_csr_status waits for `stream` (the one the build was given) and reads the flag:
+ * *status_out = ZP_OK, or ZP_ERR_INVALID_ARG when the arrays of that call are not a valid sort. */
+int zp_csr_status(const void *work, void *stream, int *status_out);
 int zp_csr_build(const int64_t *edge_index /* [2,E] int64: row 0 src, row 1 dst */,
                  int64_t n_edges, int64_t n_nodes,
                  int32_t *perm, int32_t *src_sorted, int32_t *dst_sorted, int32_t *row_ptr,
@@ -125,7 +125,7 @@ int zp_csr_build_static(const int64_t *edge_index, int64_t n_edges, int64_t n_no
                         int32_t *perm, int32_t *src_sorted, int32_t *dst_sorted,
                         int32_t *row_ptr, int32_t *perm_src, int32_t *row_ptr_src, void *stream);
 /* zp_csr_status for the last zp_csr_build_static on the current device. */
-int zp_csr_static_status(int *status_out);
+int zp_csr_static_status(void *stream, int *status_out);
 
 /* Packed rotation rot[e, rot_off[r] + j] = D_l(e)[row of (l, m_r), j], the nonzeros of
  * to_m @ wigner (replaces wigner_from_edge_vec, blocks/wigner.py:115-160, and the einsum at

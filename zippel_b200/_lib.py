@@ -56,8 +56,8 @@ SIGNATURES = {
     "zp_csr_work_bytes": (_SZ, [_I64, _I64]),
     "zp_csr_build": (C.c_int, [_P, _I64, _I64, _P, _P, _P, _P, _P, _P, _P, _SZ, _P]),
     "zp_csr_build_static": (C.c_int, [_P, _I64, _I64, _P, _P, _P, _P, _P, _P, _P]),
-    "zp_csr_status": (C.c_int, [_P, C.POINTER(C.c_int)]),
-    "zp_csr_static_status": (C.c_int, [C.POINTER(C.c_int)]),
+    "zp_csr_status": (C.c_int, [_P, _P, C.POINTER(C.c_int)]),
+    "zp_csr_static_status": (C.c_int, [_P, C.POINTER(C.c_int)]),
     "zp_wigner_forward": (C.c_int, [_P, _I64, _P, _P, _P, _P, _P]),
     "zp_wigner_backward": (C.c_int, [_P, _I64, _P, _P, _P, _P, _P, _P]),
     "zp_workspace_bytes": (_SZ, [_P, _I64, _I64, C.c_int]),

@@ -56,7 +56,7 @@ bool aligned16(const void *p) { return (reinterpret_cast<uintptr_t>(p) & 15u) ==
 // mode 0 / 1: forward that keeps what a backward reads (1: plus the backward's own regions);
 // mode 2: forward alone with fused epilogues -- of h1 only the gate scalars exist, y does not.
 struct Workspace {
-  float *rot, *h1, *y, *dht, *da1, *du_src, *grot, *wgrad, *scratch, *scales, *head, *cont;
+  float *rot, *h1, *y, *dht, *da1, *du_src, *dcont, *grot, *wgrad, *scratch, *scales, *head, *cont;
   int64_t ld_h1;
   ZpPlanes a1, ht, dy, dh1;
   uint16_t *wfold;
@@ -138,7 +138,14 @@ Workspace carve(const zp_plan *p, int64_t N, int64_t E, int mode, void *base) {
     w.dht = takef(e * t.Km * t.H);
     w.dh1 = takep(t.w1_cols);
     w.da1 = takef(e * t.Km * 2 * t.C);
-    w.du_src = takef(e * 2 * t.K * t.C);
+    // per-edge contributions to grad_x: both halves, or (pipelined kernel) the source half alone
+    // plus one continuation slab per 32-edge block for the destination half
+    if (zp_rotate_in_bwd_pipelined(p)) {
+      w.du_src = takef(e * t.K * t.C);
+      w.dcont = takef((size_t)zp_ceil_div(E, 32) * t.K * t.C);
+    } else {
+      w.du_src = takef(e * 2 * t.K * t.C);
+    }
     w.grot = takef(e * t.nnz_pad);
     w.wgrad = takef((size_t)kMaxWgradSplits * p->g_elems);
     w.scratch = takef((size_t)zp_ceil_div(E > 0 ? E : 1, 128) * (size_t)t.w1_cols);   // column-sum partials
@@ -668,12 +675,24 @@ int zp_eso2_backward(const zp_plan *plan, int64_t N, int64_t E, const float *gra
              zp_launch_colsum(E, conv ? plan->c2_out[0] : plan->c1_out[0], dYp,
                               conv ? gw->c2_b0 : gw->c1_b0, ws.scratch, st));
   }
-  ZP_TIMED(ZP_K_ROTATE_IN_BWD,
-           zp_launch_rotate_in_bwd(plan, E, ws.da1, radial, x_node, src, dst, ws.rot,
-                                   grad_radial, ws.du_src, ws.grot, st));
-  ZP_TIMED(ZP_K_SRC_REDUCE,
-           zp_launch_node_reduce(plan, N, ws.du_src, row_ptr, perm_src, row_ptr_src,
-                                 grad_x_node, st));
+  if (zp_rotate_in_bwd_pipelined(plan)) {
+    // the destination half's per-node sums land in grad_x_node itself (rows of nodes with
+    // incoming edges), node_reduce then adds the continuation slabs and the source half in place
+    ZP_TIMED(ZP_K_ROTATE_IN_BWD,
+             zp_launch_rotate_in_bwd_pipe(plan, E, ws.da1, radial, x_node, src, dst, row_ptr, ws.rot,
+                                          grad_radial, ws.du_src, grad_x_node, ws.dcont, ws.grot,
+                                          st));
+    ZP_TIMED(ZP_K_SRC_REDUCE,
+             zp_launch_node_reduce_pipe(plan, N, ws.du_src, grad_x_node, ws.dcont, row_ptr, perm_src,
+                                        row_ptr_src, grad_x_node, st));
+  } else {
+    ZP_TIMED(ZP_K_ROTATE_IN_BWD,
+             zp_launch_rotate_in_bwd(plan, E, ws.da1, radial, x_node, src, dst, ws.rot,
+                                     grad_radial, ws.du_src, ws.grot, st));
+    ZP_TIMED(ZP_K_SRC_REDUCE,
+             zp_launch_node_reduce(plan, N, ws.du_src, row_ptr, perm_src, row_ptr_src,
+                                   grad_x_node, st));
+  }
   ZP_TIMED(ZP_K_WIGNER_BWD,
            zp_launch_wigner_bwd(plan, E, edge_vec, cos_g, sin_g, ws.grot, grad_edge_vec, st));
   ZP_TIMED(ZP_K_FOLD, zp_launch_unfold_wgrad(plan, ws.wgrad, plan->g_elems, splits_c1, splits_c2,

@@ -226,11 +226,13 @@ int zp_csr_build(const int64_t *edge_index, int64_t E, int64_t N, int32_t *perm,
   return ZP_OK;
 }
 
-int zp_csr_status(const void *work, int *status_out) {
+int zp_csr_status(const void *work, void *stream, int *status_out) {
   if (!work || !status_out) return ZP_ERR_INVALID_ARG;
   int32_t flag = 0;
-  ZP_CUDA(cudaMemcpy(&flag, carve_csr(0, 0, const_cast<void *>(work)).flag, sizeof(flag),
-                     cudaMemcpyDeviceToHost));
+  cudaStream_t st = (cudaStream_t)stream;
+  ZP_CUDA(cudaMemcpyAsync(&flag, carve_csr(0, 0, const_cast<void *>(work)).flag, sizeof(flag),
+                          cudaMemcpyDeviceToHost, st));
+  ZP_CUDA(cudaStreamSynchronize(st));
   *status_out = flag ? ZP_ERR_INVALID_ARG : ZP_OK;
   return ZP_OK;
 }
@@ -270,11 +272,11 @@ int zp_csr_build_static(const int64_t *edge_index, int64_t E, int64_t N, int32_t
                       row_ptr_src, scratch, (size_t)ZP_CSR_STATIC_BYTES, stream);
 }
 
-int zp_csr_static_status(int *status_out) {
+int zp_csr_static_status(void *stream, int *status_out) {
   void *scratch = nullptr;
   const int rc = static_scratch(&scratch);
   if (rc) return rc;
-  return zp_csr_status(scratch, status_out);
+  return zp_csr_status(scratch, stream, status_out);
 }
 
 }  // extern "C"

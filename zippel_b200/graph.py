@@ -115,7 +115,7 @@ class EdgeGraph:
             if validate and e and not torch.cuda.is_current_stream_capturing():
                 import ctypes
                 flag = ctypes.c_int(0)
-                _lib.check(lib.zp_csr_status(work.data_ptr(), ctypes.byref(flag)), "zp_csr_status")
+                _lib.check(lib.zp_csr_status(work.data_ptr(), st, ctypes.byref(flag)), "zp_csr_status")
                 if flag.value:
                     raise IndexError(f"edge_index names a node outside [0, {n_nodes})")
         return EdgeGraph(n_nodes, e, perm[:e], src[:e], dst[:e], row_ptr, perm_src[:e], row_ptr_src)

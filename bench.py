@@ -83,7 +83,6 @@ def hbm_bytes_per_step(block, n: int, e: int) -> dict:
     # back run inside the contractions; what is left of the scatter is the sum of the per-row
     # partial sums (one slab of nnz x C values per node and one per 32-edge block)
     fused = P != 3 and os.environ.get("ZP_FUSED_EPILOGUE", "1") != "0"
-    piped = C <= 128 and os.environ.get("ZP_ROTATE_IN_BWD_PIPE", "1") != "0"
     nnz = sum((2 * min(l, c.mmax) + 1) * (2 * l + 1) for l in range(c.lmax + 1))
     per_edge = {
         "rotate_in": R * 4 + Km * 2 * C * 2 * P,
@@ -91,13 +90,11 @@ def hbm_bytes_per_step(block, n: int, e: int) -> dict:
         "rotate_back_scatter": nnz * C * 4 / 32 if fused else Km * C * 4,
         "rotate_grad_out": Km * C * 4 + Km * C * 2 * P,
         "gate_bwd": w1 * 4 + Km * H * 4 + w1 * 2 * P,
-        # pipelined form (C <= 128): only the source half is written per edge; the destination
-        # half is summed on chip (one slab of K x C per node and one per 32-edge block)
-        "rotate_in_bwd": Km * 2 * C * 4 + 2 * R * 4 + (1 if piped else 2) * K * C * 4,
-        "src_reduce": (K * C * 4 + K * C * 4 / 32) if piped else 2 * K * C * 4,
+        "rotate_in_bwd": Km * 2 * C * 4 + 2 * R * 4 + 2 * K * C * 4,
+        "src_reduce": 2 * K * C * 4,
     }
     per_node = {"rotate_back_scatter": K * C * 4 + (nnz * C * 4 if fused else 0),
-                "src_reduce": (2 if piped else 1) * K * C * 4}
+                "src_reduce": K * C * 4}
     return {k: int(e * v + n * per_node.get(k, 0)) for k, v in per_edge.items()}
 
 

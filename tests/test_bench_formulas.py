@@ -35,9 +35,8 @@ def test_hbm_bytes_per_step(bench):
     assert "gate_fwd" not in got                # runs inside conv1's epilogue
     assert got["rotate_grad_out"] == e * (km * c * 4 + km * c * 2 * 2)
     assert got["gate_bwd"] == e * (w1 * 4 + km * h * 4 + w1 * 2 * 2)
-    # pipelined backward of the rotation: source half per edge, destination half per node / block
-    assert got["rotate_in_bwd"] == e * (km * 2 * c * 4 + 2 * r * 4 + k * c * 4)
-    assert got["src_reduce"] == e * k * c * 4 + e * k * c * 4 // 32 + 2 * n * k * c * 4
+    assert got["rotate_in_bwd"] == e * (km * 2 * c * 4 + 2 * r * 4 + 2 * k * c * 4)
+    assert got["src_reduce"] == e * 2 * k * c * 4 + n * k * c * 4
     # what is left of the scatter: the per-row partial sums (115 x C per node and per 32 edges)
     assert got["rotate_back_scatter"] == e * 115 * c * 4 // 32 + n * (k + 115) * c * 4
     unfused = ESO2Block(BlockConfig(**bench.CFG), precision="fp32_bf16x3")

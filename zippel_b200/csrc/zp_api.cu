@@ -56,8 +56,9 @@ bool aligned16(const void *p) { return (reinterpret_cast<uintptr_t>(p) & 15u) ==
 // mode 0 / 1: forward that keeps what a backward reads (1: plus the backward's own regions);
 // mode 2: forward alone with fused epilogues -- of h1 only the gate scalars exist, y does not.
 struct Workspace {
-  float *rot, *h1, *y, *dht, *da1, *du_src, *dcont, *grot, *wgrad, *scratch, *scales, *head, *cont;
+  float *rot, *h1, *y, *dht, *da1, *du_src, *grot, *wgrad, *scratch, *scales, *head, *cont;
   int64_t ld_h1;
+  int32_t *block_node;
   ZpPlanes a1, ht, dy, dh1;
   uint16_t *wfold;
   size_t bytes;
@@ -130,6 +131,7 @@ Workspace carve(const zp_plan *p, int64_t N, int64_t E, int mode, void *base) {
   if (can_fuse(p, 1)) {
     w.head = takef((size_t)N * t.nnz * t.C);
     w.cont = takef((size_t)zp_ceil_div(E, 32) * t.nnz * t.C);
+    w.block_node = reinterpret_cast<int32_t *>(take((size_t)zp_ceil_div(E, 32) * sizeof(int32_t)));
   }
   const size_t end_fwd = off;
   if (mode == 1) {
@@ -138,14 +140,7 @@ Workspace carve(const zp_plan *p, int64_t N, int64_t E, int mode, void *base) {
     w.dht = takef(e * t.Km * t.H);
     w.dh1 = takep(t.w1_cols);
     w.da1 = takef(e * t.Km * 2 * t.C);
-    // per-edge contributions to grad_x: both halves, or (pipelined kernel) the source half alone
-    // plus one continuation slab per 32-edge block for the destination half
-    if (zp_rotate_in_bwd_pipelined(p)) {
-      w.du_src = takef(e * t.K * t.C);
-      w.dcont = takef((size_t)zp_ceil_div(E, 32) * t.K * t.C);
-    } else {
-      w.du_src = takef(e * 2 * t.K * t.C);
-    }
+    w.du_src = takef(e * 2 * t.K * t.C);
     w.grot = takef(e * t.nnz_pad);
     w.wgrad = takef((size_t)kMaxWgradSplits * p->g_elems);
     w.scratch = takef((size_t)zp_ceil_div(E > 0 ? E : 1, 128) * (size_t)t.w1_cols);   // column-sum partials
@@ -532,6 +527,8 @@ static int eso2_forward(const zp_plan *plan, int64_t N, int64_t E, const float *
     epi.nnz_pad = t.nnz_pad;
     epi.head = ws.head;
     epi.cont = ws.cont;
+    epi.block_node = ws.block_node;
+    ZP_TIMED(ZP_K_ROTATE_BACK, zp_launch_block_nodes(E, N, row_ptr, ws.block_node, st));
   }
   for (int m = 0; m < plan->n_blocks && E > 0; ++m) {
     const int in = plan->c2_in[m], out = plan->c2_out[m];
@@ -675,24 +672,12 @@ int zp_eso2_backward(const zp_plan *plan, int64_t N, int64_t E, const float *gra
              zp_launch_colsum(E, conv ? plan->c2_out[0] : plan->c1_out[0], dYp,
                               conv ? gw->c2_b0 : gw->c1_b0, ws.scratch, st));
   }
-  if (zp_rotate_in_bwd_pipelined(plan)) {
-    // the destination half's per-node sums land in grad_x_node itself (rows of nodes with
-    // incoming edges), node_reduce then adds the continuation slabs and the source half in place
-    ZP_TIMED(ZP_K_ROTATE_IN_BWD,
-             zp_launch_rotate_in_bwd_pipe(plan, E, ws.da1, radial, x_node, src, dst, row_ptr, ws.rot,
-                                          grad_radial, ws.du_src, grad_x_node, ws.dcont, ws.grot,
-                                          st));
-    ZP_TIMED(ZP_K_SRC_REDUCE,
-             zp_launch_node_reduce_pipe(plan, N, ws.du_src, grad_x_node, ws.dcont, row_ptr, perm_src,
-                                        row_ptr_src, grad_x_node, st));
-  } else {
-    ZP_TIMED(ZP_K_ROTATE_IN_BWD,
-             zp_launch_rotate_in_bwd(plan, E, ws.da1, radial, x_node, src, dst, ws.rot,
-                                     grad_radial, ws.du_src, ws.grot, st));
-    ZP_TIMED(ZP_K_SRC_REDUCE,
-             zp_launch_node_reduce(plan, N, ws.du_src, row_ptr, perm_src, row_ptr_src,
-                                   grad_x_node, st));
-  }
+  ZP_TIMED(ZP_K_ROTATE_IN_BWD,
+           zp_launch_rotate_in_bwd(plan, E, ws.da1, radial, x_node, src, dst, ws.rot,
+                                   grad_radial, ws.du_src, ws.grot, st));
+  ZP_TIMED(ZP_K_SRC_REDUCE,
+           zp_launch_node_reduce(plan, N, ws.du_src, row_ptr, perm_src, row_ptr_src,
+                                 grad_x_node, st));
   ZP_TIMED(ZP_K_WIGNER_BWD,
            zp_launch_wigner_bwd(plan, E, edge_vec, cos_g, sin_g, ws.grot, grad_edge_vec, st));
   ZP_TIMED(ZP_K_FOLD, zp_launch_unfold_wgrad(plan, ws.wgrad, plan->g_elems, splits_c1, splits_c2,

@@ -116,18 +116,6 @@ int zp_launch_rotate_in_bwd(const zp_plan *p, int64_t E, const float *da1, const
 //   head[n][rot_off[r] + j][c] + the continuation partials of the 32-edge blocks n's edges reach
 int zp_launch_node_sum(const zp_plan *p, int64_t N, const float *head, const float *cont,
                        const int32_t *row_ptr, float *node_out, cudaStream_t st);
-// The pipelined form of the two kernels above (channel counts up to 128): blocks of 32 edges, the
-// destination half summed on chip into dhead [N][K][C] / dcont [ceil(E/32)][K][C], only the
-// source half written per edge (du_src [E][K][C]).
-bool zp_rotate_in_bwd_pipelined(const zp_plan *p);
-int zp_launch_rotate_in_bwd_pipe(const zp_plan *p, int64_t E, const float *da1, const float *radial,
-                                 const float *x, const int32_t *src, const int32_t *dst,
-                                 const int32_t *row_ptr, const float *rot, float *grad_radial,
-                                 float *du_src, float *dhead, float *dcont, float *grad_rot,
-                                 cudaStream_t st);
-int zp_launch_node_reduce_pipe(const zp_plan *p, int64_t N, const float *du_src, const float *dhead,
-                               const float *dcont, const int32_t *row_ptr, const int32_t *perm_src,
-                               const int32_t *row_ptr_src, float *grad_x, cudaStream_t st);
 int zp_launch_node_reduce(const zp_plan *p, int64_t N, const float *du_both,
                           const int32_t *row_ptr, const int32_t *perm_src,
                           const int32_t *row_ptr_src, float *grad_x, cudaStream_t st);
@@ -169,6 +157,7 @@ struct ZpEpilogue {
   // rotate back
   const float *rot, *env;                       // [M, nnz_pad], [M]
   const int32_t *row_ptr;                       // [n_nodes + 1] offsets of the nodes' edges
+  const int32_t *block_node;                    // [ceil(M/32)] node of edge 32 b (zp_launch_block_nodes)
   int n_nodes, nnz, nnz_pad;
   float *head, *cont;                           // [n_nodes][nnz][width], [ceil(M/32)][nnz][width]
 };
@@ -193,6 +182,9 @@ struct ZpGemmTc {
   const ZpEpilogue *epi;                        // fused epilogue (null = store C)
 };
 int zp_launch_gemm_tc(const ZpGemmTc &g, cudaStream_t st);
+// block_node[b] = node of the first edge of 32-edge block b, for ZpEpilogue::block_node
+int zp_launch_block_nodes(int64_t E, int64_t N, const int32_t *row_ptr, int32_t *block_node,
+                          cudaStream_t st);
 // whether zp_launch_gemm_tc accepts a fused epilogue for this problem
 bool zp_gemm_tc_fusable(const ZpGemmTc &g);
 // number of partial outputs the launch above will write for this problem (<= g.ksplit)

@@ -329,22 +329,33 @@ __device__ __forceinline__ float fast_sigmoid(float x) { return 1.f / (1.f + __e
 __device__ __forceinline__ void gate_block(const ZpEpilogue &f, const uint8_t *stage, int lane,
                                            int row0, int n, int M, int N, float inv,
                                            float &slope_max) {
-#pragma unroll 2
+  // Pass 1: request the gate scalars of all eight row groups (independent loads, one memory round
+  // trip for the block).  Pass 2: activate and store.
+  const int k = lane & 7, col = n + 4 * k;
+  const int rq = col / f.width;
+  const int r = f.row_first + rq, h = col - rq * f.width;
+  const bool col_ok = col < N;
+  const bool gated = r != 0;                      // row 0 (l = 0): x * sigmoid(x)
+  const float *gcol = f.gate + (gated ? (f.row_l[r] - 1) * f.width + h : 0);
+  float4 g[8];
+#pragma unroll
   for (int it = 0; it < 8; ++it) {
-    const int rr = it * 4 + (lane >> 3), k = lane & 7;
-    const int row = row0 + rr, col = n + 4 * k;
-    if (row < M && col < N) {
+    const int row = row0 + it * 4 + (lane >> 3);
+    g[it] = make_float4(0.f, 0.f, 0.f, 0.f);
+    if (gated && col_ok && row < M)
+      g[it] = *reinterpret_cast<const float4 *>(gcol + (size_t)row * f.ld_gate);
+  }
+#pragma unroll
+  for (int it = 0; it < 8; ++it) {
+    const int rr = it * 4 + (lane >> 3);
+    const int row = row0 + rr;
+    if (row < M && col_ok) {
       const float4 x = *reinterpret_cast<const float4 *>(stage + rr * 128 + ((k ^ (rr & 7)) << 4));
-      const int rq = col / f.width;
-      const int r = f.row_first + rq, h = col - rq * f.width;
-      float4 g = x;                              // row 0 (l = 0): x * sigmoid(x)
-      if (r != 0)
-        g = *reinterpret_cast<const float4 *>(f.gate + (size_t)row * f.ld_gate +
-                                              (f.row_l[r] - 1) * f.width + h);
-      const float s0 = fast_sigmoid(g.x), s1 = fast_sigmoid(g.y), s2 = fast_sigmoid(g.z),
-                  s3 = fast_sigmoid(g.w);
+      const float4 q = gated ? g[it] : x;
+      const float s0 = fast_sigmoid(q.x), s1 = fast_sigmoid(q.y), s2 = fast_sigmoid(q.z),
+                  s3 = fast_sigmoid(q.w);
       const float o[4] = {x.x * s0, x.y * s1, x.z * s2, x.w * s3};
-      if (r != 0)
+      if (gated)
         slope_max = fmaxf(slope_max, fmaxf(fmaxf(s0 * (1.f - s0), s1 * (1.f - s1)),
                                            fmaxf(s2 * (1.f - s2), s3 * (1.f - s3))));
       zp_store_planes<4>(f.out, (int64_t)row * f.out.ld + col, o, inv);
@@ -352,21 +363,19 @@ __device__ __forceinline__ void gate_block(const ZpEpilogue &f, const uint8_t *s
   }
 }
 
-// the last node n with row_ptr[n] <= e  (row_ptr[0] <= e < row_ptr[n_nodes])
-__device__ __forceinline__ int find_node(const int32_t *__restrict__ row_ptr, int n_nodes, int e) {
-  int lo = 0, hi = n_nodes;
-  while (hi - lo > 1) {
-    const int mid = (lo + hi) >> 1;
-    if (row_ptr[mid] <= e) lo = mid; else hi = mid;
-  }
-  return lo;
+// row_ptr[idx] for the rotate-back epilogue: lane d of the warp holds row_ptr[node0 + d] (fetched
+// once per tile), anything further away comes from memory.  idx is warp-uniform.
+__device__ __forceinline__ int row_ptr_at(const ZpEpilogue &f, int idx, int node0, int rp_l) {
+  const int d = idx - node0;
+  return (d >= 0 && d < 32) ? __shfl_sync(0xffffffffu, rp_l, d) : f.row_ptr[idx];
 }
 
 constexpr int kMaxNj = 2 * ZP_MAX_L + 1;
 
 // node: the node of edge row0 (from find_node)
 __device__ __forceinline__ void rotate_back_block(const ZpEpilogue &f, const uint8_t *stage, int lane,
-                                                  int row0, int n, int M, int N, int node) {
+                                                  int row0, int n, int M, int N, int node,
+                                                  const int node0, const int rp_l) {
   const int col = n + lane;
   const bool col_ok = col < N;
   const int cq = col_ok ? col : n;               // lanes beyond the matrix shadow column n
@@ -377,25 +386,60 @@ __device__ __forceinline__ void rotate_back_block(const ZpEpilogue &f, const uin
   const int njmax = __reduce_max_sync(0xffffffffu, nj);
   const int row_end = min(row0 + 32, M);
   const size_t slab = (size_t)f.nnz * f.width;
+  // Usual case: the block's 32 columns lie in one m' row, so every lane needs the same rotation
+  // entries.  Lane i then fetches the envelope and the row's 2l+1 entries of EDGE row0 + i (all
+  // requests in flight together: one memory round trip per block) and the edge loop broadcasts
+  // them with shuffles.  Otherwise every lane reads its own row's entries edge by edge.
+  const bool one_row = __all_sync(0xffffffffu, r == __shfl_sync(0xffffffffu, r, 0));
+  float env_l = 0.f, rot_l[kMaxNj];
+#pragma unroll
+  for (int j = 0; j < kMaxNj; ++j) rot_l[j] = 0.f;
+  if (one_row && row0 + lane < row_end) {
+    const int ei = row0 + lane;
+    env_l = f.env[ei];
+    const float *re = f.rot + (size_t)ei * f.nnz_pad + off;
+#pragma unroll
+    for (int j = 0; j < kMaxNj; ++j)
+      if (j < nj) rot_l[j] = re[j];
+  }
   int e = row0;
   while (e < row_end) {
-    while (node + 1 < f.n_nodes && f.row_ptr[node + 1] <= e) ++node;    // nodes without edges
-    const bool is_head = f.row_ptr[node] == e;
-    int stop = min(f.row_ptr[node + 1], row_end);
+    int next = row_ptr_at(f, node + 1, node0, rp_l);
+    while (node + 1 < f.n_nodes && next <= e) {  // nodes without edges
+      ++node;
+      next = row_ptr_at(f, node + 1, node0, rp_l);
+    }
+    const bool is_head = row_ptr_at(f, node, node0, rp_l) == e;
+    int stop = min(next, row_end);
     if (stop <= e) stop = row_end;               // offsets that do not cover the edges: never spin
     float acc[kMaxNj];
 #pragma unroll
     for (int j = 0; j < kMaxNj; ++j) acc[j] = 0.f;
-#pragma unroll 2
-    for (; e < stop; ++e) {
-      const int i = e - row0;
-      const float yv = f.env[e] * *reinterpret_cast<const float *>(
-                                      stage + i * 128 + (((lane >> 2) ^ (i & 7)) << 4) + ((lane & 3) << 2));
-      const float *re = f.rot + (size_t)e * f.nnz_pad + off;
+    if (one_row) {
+#pragma unroll 4
+      for (; e < stop; ++e) {
+        const int i = e - row0;
+        const float yv = __shfl_sync(0xffffffffu, env_l, i) *
+                         *reinterpret_cast<const float *>(stage + i * 128 + (((lane >> 2) ^ (i & 7)) << 4) +
+                                                          ((lane & 3) << 2));
 #pragma unroll
-      for (int j = 0; j < kMaxNj; ++j) {
-        if (j >= njmax) break;                   // warp-uniform
-        if (j < nj) acc[j] = fmaf(re[j], yv, acc[j]);
+        for (int j = 0; j < kMaxNj; ++j) {
+          if (j >= njmax) break;                 // warp-uniform
+          acc[j] = fmaf(__shfl_sync(0xffffffffu, rot_l[j], i), yv, acc[j]);
+        }
+      }
+    } else {
+#pragma unroll 2
+      for (; e < stop; ++e) {
+        const int i = e - row0;
+        const float yv = f.env[e] * *reinterpret_cast<const float *>(
+                                        stage + i * 128 + (((lane >> 2) ^ (i & 7)) << 4) + ((lane & 3) << 2));
+        const float *re = f.rot + (size_t)e * f.nnz_pad + off;
+#pragma unroll
+        for (int j = 0; j < kMaxNj; ++j) {
+          if (j >= njmax) break;                 // warp-uniform
+          if (j < nj) acc[j] = fmaf(re[j], yv, acc[j]);
+        }
       }
     }
     float *out = (is_head ? f.head + (size_t)node * slab : f.cont + (size_t)(row0 >> 5) * slab) +
@@ -413,7 +457,8 @@ template <int EPI>
 __device__ __forceinline__ void epilogue_fused(const GemmParams &p, const CUtensorMap *map_c,
                                                float (&v)[4][32], uint8_t *stage, int lane, int row0,
                                                int n0, int col_lo, int col_hi, const float *bias,
-                                               float &seen_max, float &slope_max, int node) {
+                                               float &seen_max, float &slope_max, int node,
+                                               int rp_l) {
   if (row0 >= p.M) return;
   const bool row_ok = row0 + lane < p.M;
   const float inv = EPI == ZP_EPI_GATE ? zp_inv_scale(p.epi.out) : 1.f;
@@ -455,7 +500,7 @@ __device__ __forceinline__ void epilogue_fused(const GemmParams &p, const CUtens
       __syncwarp();
     }
     if (EPI == ZP_EPI_GATE) gate_block(p.epi, stage, lane, row0, n, p.M, p.N, inv, slope_max);
-    else rotate_back_block(p.epi, stage, lane, row0, n, p.M, p.N, node);
+    else rotate_back_block(p.epi, stage, lane, row0, n, p.M, p.N, node, node, rp_l);
   }
 }
 
@@ -635,9 +680,13 @@ __device__ __forceinline__ void gemm_tc_body(const CUtensorMap &map_a, const CUt
       for (int c0 = x.kb0; c0 < x.kb1 && ok; c0 += p.kc, ++unit) {
         const int buf = unit % kAccBufs;
         const bool first = c0 == x.kb0;         // first chunk stores, later chunks add
-        int node = 0;                           // looked up while the tile is still being formed
-        if (EPI == ZP_EPI_ROTATE_BACK && row0 < p.M)
-          node = find_node(p.epi.row_ptr, p.epi.n_nodes, row0);
+        // the node of the warp's first edge and the offsets of the 32 nodes from there on,
+        // fetched while the tile is still being formed
+        int node = 0, rp_l = 0;
+        if (EPI == ZP_EPI_ROTATE_BACK && row0 < p.M) {
+          node = p.epi.block_node[row0 >> 5];
+          rp_l = p.epi.row_ptr[min(node + lane, p.epi.n_nodes)];
+        }
         ok = mbar_wait(&tmem_full[buf], (unit / kAccBufs) & 1, abort_flag, p.status);
         ok = __all_sync(0xffffffffu, ok);
         if (!ok) break;
@@ -676,7 +725,7 @@ __device__ __forceinline__ void gemm_tc_body(const CUtensorMap &map_a, const CUt
         if (EPI != ZP_EPI_NONE) {
           if (L::kTmaEpilogue)
             epilogue_fused<EPI>(p, &map_c, v, epi_stage, lane, row0, x.n0, col_lo, col_hi, bias,
-                                seen_max, slope_max, node);
+                                seen_max, slope_max, node, rp_l);
         } else if (L::kTmaEpilogue && p.tma_store) {
           epilogue_store_tma(p, &map_c, v, epi_stage, lane, row0, x.n0, col_lo, col_hi, x.split,
                              bias, first, seen_max);
@@ -1006,9 +1055,13 @@ __device__ __forceinline__ void gemm_tc_pair_body(const CUtensorMap &map_a, cons
         const bool first = c0 == x.kb0;
         const int buf = P == 1 ? (int)(unit & 1) : 0;
         const uint32_t round = P == 1 ? (unit >> 1) : unit;
-        int node = 0;                           // looked up while the tile is still being formed
-        if (EPI == ZP_EPI_ROTATE_BACK && row0 < p.M)
-          node = find_node(p.epi.row_ptr, p.epi.n_nodes, row0);
+        // the node of the warp's first edge and the offsets of the 32 nodes from there on,
+        // fetched while the tile is still being formed
+        int node = 0, rp_l = 0;
+        if (EPI == ZP_EPI_ROTATE_BACK && row0 < p.M) {
+          node = p.epi.block_node[row0 >> 5];
+          rp_l = p.epi.row_ptr[min(node + lane, p.epi.n_nodes)];
+        }
         ok = mbar_wait(&tmem_full[buf], round & 1, abort_flag, p.status);
         ok = __all_sync(0xffffffffu, ok);
         if (!ok) break;
@@ -1046,7 +1099,7 @@ __device__ __forceinline__ void gemm_tc_pair_body(const CUtensorMap &map_a, cons
         if (EPI != ZP_EPI_NONE) {
           if (L::kTmaEpilogue)
             epilogue_fused<EPI>(p, &map_c, v, epi_stage, lane, row0, x.n0, col_lo, col_hi, bias,
-                                seen_max, slope_max, node);
+                                seen_max, slope_max, node, rp_l);
         } else if (L::kTmaEpilogue && p.tma_store) {
           epilogue_store_tma(p, &map_c, v, epi_stage, lane, row0, x.n0, col_lo, col_hi, x.split,
                              bias, first, seen_max);
@@ -1126,6 +1179,21 @@ gemm_tc_pair_fused_kernel(const __grid_constant__ CUtensorMap map_a,
                           const __grid_constant__ CUtensorMap map_c,
                           const __grid_constant__ GemmParams p) {
   gemm_tc_pair_body<P, BK, STAGES, EPI>(map_a, map_b, map_c, p);
+}
+
+// block_node[b] = the last node n with row_ptr[n] <= 32 b: the node of the first edge of 32-edge
+// block b (row_ptr[0] = 0 and row_ptr[n_nodes] = E > 32 b)
+__global__ void block_node_kernel(int64_t n_blocks, int n_nodes, const int32_t *__restrict__ row_ptr,
+                                  int32_t *__restrict__ block_node) {
+  const int64_t b = (int64_t)blockIdx.x * blockDim.x + threadIdx.x;
+  if (b >= n_blocks) return;
+  const int e = (int)(b * 32);
+  int lo = 0, hi = n_nodes;
+  while (hi - lo > 1) {
+    const int mid = (lo + hi) >> 1;
+    if (row_ptr[mid] <= e) lo = mid; else hi = mid;
+  }
+  block_node[b] = lo;
 }
 
 // ---- host side ---------------------------------------------------------------------------
@@ -1443,6 +1511,15 @@ int zp_gemm_tc_pick_splits(const ZpGemmTc &g, int max_splits) {
     if (score > best_score) { best_score = score; best = s; }
   }
   return best;
+}
+
+int zp_launch_block_nodes(int64_t E, int64_t N, const int32_t *row_ptr, int32_t *block_node,
+                          cudaStream_t st) {
+  const int64_t nb = zp_ceil_div(E, 32);
+  if (nb == 0 || N == 0) return ZP_OK;
+  block_node_kernel<<<(unsigned)zp_ceil_div(nb, 256), 256, 0, st>>>(nb, (int)N, row_ptr, block_node);
+  ZP_LAUNCH_CHECK("block_node_kernel");
+  return ZP_OK;
 }
 
 bool zp_gemm_tc_fusable(const ZpGemmTc &g) {

@@ -14,8 +14,6 @@
 // channels and moves them with one vector load/store.  No atomics: every output element is
 // produced by exactly one thread, in an order fixed by the CSR offsets.
 #include <algorithm>
-#include <cstdlib>
-#include <mutex>
 
 #include "zp_common.cuh"
 #include "zp_planes.cuh"
@@ -634,227 +632,6 @@ node_reduce_kernel(int64_t N, int KC4, const float4 *__restrict__ du_both,
   }
 }
 
-// ---- VJP of rotate_in, pipelined form ---------------------------------------------------------
-// A block walks 32 consecutive edges (block b owns edges [32 b, 32 b + 32)).  Its first W warps
-// work on the source half of the 2C message channels, the other W on the destination half; a
-// lane owns ONE channel, so a node's K rows and the K gradient rows fit in registers.
-//   * Every warp copies the rows of the NEXT edge it will need (its 32 channels of the Km rows
-//     of da1, of the radial gains, the packed rotation, and for the source half the K rows of
-//     x[src]) into a two-stage shared buffer with cp.async while it works on the current edge:
-//     memory time and arithmetic overlap instead of adding up.
-//   * The destination half never writes per-edge contributions: consecutive edges share their
-//     destination (the list is destination sorted), so the K rows are accumulated in registers
-//     and flushed when the node changes -- to dhead[node] if the run began at the node's first
-//     edge, to dcont[block] if it continues a run of the previous block.  node_reduce adds
-//     head, continuations and the per-edge source contributions in a fixed order.
-//   * grad_rot needs sums over all 2C channels: each warp reduces its 32 channels (halving
-//     exchange) into its row of a shared table; after the block's barrier of the edge, one thread
-//     per entry adds the 2W rows in order and accumulates into grad_rot.
-constexpr int kRibEdges = 32;
-
-template <int N>
-__device__ __forceinline__ void cp_async4(float *smem_dst, const float *gmem_src) {
-  const uint32_t d = (uint32_t)__cvta_generic_to_shared(smem_dst);
-  asm volatile("cp.async.ca.shared.global [%0], [%1], 4;" ::"r"(d), "l"(gmem_src) : "memory");
-}
-
-template <int L, int LMAX>
-struct RibDeg {
-  static constexpr int K = (LMAX + 1) * (LMAX + 1);
-  // st_da [Km][32], st_rad [rows][32]: this lane's channel of the staged rows
-  static __device__ __forceinline__ void run(const ZpTables &t, const float (&u)[K], float (&du)[K],
-                                             const float *st_da, const float *st_rad,
-                                             const float *rot_s, float *part_s, float *grad_e,
-                                             bool active, int lane, int C2) {
-    RibDeg<L - 1, LMAX>::run(t, u, du, st_da, st_rad, rot_s, part_s, grad_e, active, lane, C2);
-    constexpr int n = 2 * L + 1;
-    const int mm = t.mmax < L ? t.mmax : L;
-#pragma unroll 1
-    for (int am = 0; am <= mm; ++am) {
-      // radial column block of (|m|, l): rad_off[am] / 2C + (l - am)
-      const int rrow = t.rad_off[am] / C2 + (L - am);
-      const float rad = st_rad[rrow * 32 + lane];
-      float gr = 0.f;
-#pragma unroll
-      for (int sgn = 0; sgn < 2; ++sgn) {
-        if (sgn == 1 && am == 0) continue;
-        const int r = t.row_of[L][sgn == 0 ? L + am : L - am];
-        const float *rr = rot_s + t.rot_off[r];
-        const float da = st_da[r * 32 + lane];
-        float a = 0.f, w[n];
-#pragma unroll
-        for (int j = 0; j < n; ++j) {
-          w[j] = rr[j];
-          a = fmaf(w[j], u[L * L + j], a);
-        }
-        gr = fmaf(da, a, gr);
-        const float ga = da * rad;
-        float part[n];
-#pragma unroll
-        for (int j = 0; j < n; ++j) {
-          du[L * L + j] = fmaf(w[j], ga, du[L * L + j]);
-          part[j] = ga * u[L * L + j];
-        }
-        int idx;
-        const float tot = warp_sum_scatter<n>(part, lane, idx);
-        if (warp_sum_owner<n>(lane, idx)) part_s[t.rot_off[r] + idx] = tot;
-      }
-      if (active) grad_e[t.rad_off[am] + (L - am) * C2] = gr;
-    }
-  }
-};
-template <int LMAX>
-struct RibDeg<-1, LMAX> {
-  static constexpr int K = (LMAX + 1) * (LMAX + 1);
-  static __device__ __forceinline__ void run(const ZpTables &, const float (&)[K], float (&)[K],
-                                             const float *, const float *, const float *, float *,
-                                             float *, bool, int, int) {}
-};
-
-// shared memory per warp and stage: da [Km][32] | rad [rad_rows][32] | rot [nnz_pad] | u [K][32]
-// (u only in the source half's stages); then part [2][2W][nnz_pad]
-template <int LMAX>
-__global__ void __launch_bounds__(256, (LMAX <= 4 ? 2 : 1))
-rotate_in_bwd_pipe_kernel(const __grid_constant__ ZpTables t, int64_t E, int W, int rad_rows,
-                          const float *__restrict__ da1, const float *__restrict__ radial,
-                          const float *__restrict__ x, const int32_t *__restrict__ src,
-                          const int32_t *__restrict__ dst, const int32_t *__restrict__ row_ptr,
-                          const float *__restrict__ rot, float *__restrict__ grad_radial,
-                          float *__restrict__ du_src, float *__restrict__ dhead,
-                          float *__restrict__ dcont, float *__restrict__ grad_rot) {
-  constexpr int K = (LMAX + 1) * (LMAX + 1);
-  extern __shared__ __align__(16) float smem[];
-  const int warp = threadIdx.x / 32, lane = threadIdx.x % 32, nw = 2 * W;
-  const int half = warp / W, slice = warp % W;
-  const int c = slice * 32 + lane;
-  const bool active = c < t.C;
-  const int C2 = 2 * t.C, c2 = half * t.C + c;
-  // source-half warps also stage the K rows of x[src]; the destination half keeps its node's rows
-  const int sf_dst = (t.Km + rad_rows) * 32 + t.nnz_pad, sf_src = sf_dst + K * 32;
-  const int stage_floats = half == 0 ? sf_src : sf_dst;
-  float *my = smem + (half == 0 ? (size_t)warp * 2 * sf_src
-                                : (size_t)W * 2 * sf_src + (size_t)(warp - W) * 2 * sf_dst);
-  float *part_all = smem + (size_t)W * 2 * (sf_src + sf_dst);      // [2][nw][nnz_pad]
-  const int64_t e0 = (int64_t)blockIdx.x * kRibEdges;
-  const int64_t e1 = min(E, e0 + kRibEdges);
-  const size_t KC = (size_t)t.K * t.C;
-
-  // lanes beyond the channel count never copy: their slots stay zero
-  for (int i = lane; i < 2 * stage_floats; i += 32) my[i] = 0.f;
-  __syncwarp();
-
-  auto stage = [&](int64_t e, int s) {
-    float *b = my + (size_t)s * stage_floats;
-    float *b_da = b, *b_rad = b + t.Km * 32, *b_rot = b_rad + rad_rows * 32;
-    float *b_u = b_rot + t.nnz_pad;
-    if (active) {
-      const float *da_e = da1 + (size_t)e * t.Km * C2 + c2;
-      for (int r = 0; r < t.Km; ++r) cp_async4<0>(b_da + r * 32 + lane, da_e + (size_t)r * C2);
-      const float *rad_e = radial + (size_t)e * t.R + c2;
-      for (int r = 0; r < rad_rows; ++r) cp_async4<0>(b_rad + r * 32 + lane, rad_e + (size_t)r * C2);
-      if (half == 0) {
-        const float *xr = x + (size_t)src[e] * KC + c;
-        for (int k = 0; k < K; ++k) cp_async4<0>(b_u + k * 32 + lane, xr + (size_t)k * t.C);
-      }
-    }
-    for (int i = lane; i < t.nnz_pad / 4; i += 32)
-      cp_async<16>(b_rot + 4 * i, rot + (size_t)e * t.nnz_pad + 4 * i);
-    cp_async_commit();
-  };
-
-  float u[K], du[K];
-#pragma unroll
-  for (int k = 0; k < K; ++k) { u[k] = 0.f; du[k] = 0.f; }
-  int cur = -1;                  // destination half: node whose rows are in u / du
-  int64_t seg_start = e0;
-
-  auto flush = [&]() {           // destination half: the run [seg_start, ...) of node `cur` ends
-    if (cur < 0) return;
-    float *o = (row_ptr[cur] == (int32_t)seg_start ? dhead + (size_t)cur * KC
-                                                   : dcont + (size_t)blockIdx.x * KC) + c;
-    if (active) {
-#pragma unroll
-      for (int k = 0; k < K; ++k) o[(size_t)k * t.C] = du[k];
-    }
-#pragma unroll
-    for (int k = 0; k < K; ++k) du[k] = 0.f;
-  };
-
-  if (e0 < e1) stage(e0, 0);
-  int s = 0;
-  for (int64_t e = e0; e < e1; ++e, s ^= 1) {
-    if (e + 1 < e1) stage(e + 1, s ^ 1);
-    else cp_async_commit();
-    cp_async_wait<1>();
-    __syncwarp();
-    const float *b = my + (size_t)s * stage_floats;
-    const float *b_da = b, *b_rad = b + t.Km * 32, *b_rot = b_rad + rad_rows * 32;
-    const float *b_u = b_rot + t.nnz_pad;
-    if (half == 0) {
-#pragma unroll
-      for (int k = 0; k < K; ++k) { u[k] = b_u[k * 32 + lane]; du[k] = 0.f; }
-    } else {
-      const int node = dst[e];
-      if (node != cur) {
-        flush();
-        cur = node;
-        seg_start = e;
-        const float *xr = x + (size_t)node * KC + c;
-#pragma unroll
-        for (int k = 0; k < K; ++k) u[k] = active ? xr[(size_t)k * t.C] : 0.f;
-      }
-    }
-    float *part_s = part_all + ((size_t)((e - e0) & 1) * nw + warp) * t.nnz_pad;
-    RibDeg<LMAX, LMAX>::run(t, u, du, b_da, b_rad, b_rot, part_s,
-                            grad_radial + (size_t)e * t.R + c2, active, lane, C2);
-    if (half == 0 && active) {
-      float *o = du_src + (size_t)e * KC + c;
-#pragma unroll
-      for (int k = 0; k < K; ++k) o[(size_t)k * t.C] = du[k];
-    }
-    __syncthreads();             // every warp's partial sums of edge e are in the table
-    const float *pe = part_all + (size_t)((e - e0) & 1) * nw * t.nnz_pad;
-    for (int i = threadIdx.x; i < t.nnz; i += blockDim.x) {
-      float acc = 0.f;
-      for (int w = 0; w < nw; ++w) acc += pe[w * t.nnz_pad + i];
-      grad_rot[e * t.nnz_pad + i] += acc;
-    }
-  }
-  cp_async_wait<0>();
-  if (half == 1) flush();
-}
-
-// grad_x[n] = head[n] + continuation partials of the blocks n's incoming edges reach (both from
-// the destination half above) + the per-edge source contributions of the edges leaving n, all in
-// a fixed order.
-__global__ void __launch_bounds__(128)
-node_reduce_pipe_kernel(int64_t N, int KC4, const float4 *__restrict__ du_src,
-                        const float4 *dhead /* may be grad_x itself */,
-                        const float4 *__restrict__ dcont,
-                        const int32_t *__restrict__ row_ptr, const int32_t *__restrict__ perm_src,
-                        const int32_t *__restrict__ row_ptr_src, float4 *grad_x) {
-  const int64_t n = blockIdx.x;
-  if (n >= N) return;
-  const int beg = row_ptr[n], end = row_ptr[n + 1];
-  const int sbeg = row_ptr_src[n], send = row_ptr_src[n + 1];
-  const int b_first = beg / kRibEdges, b_last = end > beg ? (end - 1) / kRibEdges : b_first;
-  for (int i = threadIdx.x; i < KC4; i += blockDim.x) {
-    float4 acc = make_float4(0.f, 0.f, 0.f, 0.f);
-    if (end > beg) {
-      acc = dhead[(size_t)n * KC4 + i];
-      for (int b = b_first + 1; b <= b_last; ++b) {
-        const float4 v = dcont[(size_t)b * KC4 + i];
-        acc.x += v.x; acc.y += v.y; acc.z += v.z; acc.w += v.w;
-      }
-    }
-    for (int k = sbeg; k < send; ++k) {
-      const float4 v = du_src[(size_t)perm_src[k] * KC4 + i];
-      acc.x += v.x; acc.y += v.y; acc.z += v.z; acc.w += v.w;
-    }
-    grad_x[(size_t)n * KC4 + i] = acc;
-  }
-}
-
 // Final sums after the rotate-back epilogue of conv2.  The epilogue leaves, per m' row r, the
 // partial sums of a node's edges: head[n] for the run that starts at the node's first edge and
 // cont[b] for the run that enters 32-edge block b from the block before.  One block per node adds,
@@ -999,65 +776,6 @@ int zp_launch_rotate_in_bwd(const zp_plan *p, int64_t E, const float *da1, const
   ZP_DISPATCH_LMAX(t.lmax, CALL)
 #undef CALL
   ZP_LAUNCH_CHECK("rotate_in_bwd_kernel");
-  return ZP_OK;
-}
-
-bool zp_rotate_in_bwd_pipelined(const zp_plan *p) {
-  static int on = -1;
-  if (on < 0) {
-    const char *e = getenv("ZP_ROTATE_IN_BWD_PIPE");
-    on = (e && e[0] == '0') ? 0 : 1;
-  }
-  return on == 1 && p->t.C <= 128;
-}
-
-int zp_launch_rotate_in_bwd_pipe(const zp_plan *p, int64_t E, const float *da1, const float *radial,
-                                 const float *x, const int32_t *src, const int32_t *dst,
-                                 const int32_t *row_ptr, const float *rot, float *grad_radial,
-                                 float *du_src, float *dhead, float *dcont, float *grad_rot,
-                                 cudaStream_t st) {
-  if (E == 0) return ZP_OK;
-  const ZpTables &t = p->t;
-  const int W = (t.C + 31) / 32;
-  if (W > 4) return ZP_ERR_UNSUPPORTED;
-  const int rad_rows = t.R / (2 * t.C);
-  const size_t sf_dst = (size_t)(t.Km + rad_rows) * 32 + t.nnz_pad, sf_src = sf_dst + (size_t)t.K * 32;
-  const size_t smem = ((size_t)W * 2 * (sf_src + sf_dst) + (size_t)2 * 2 * W * t.nnz_pad) * sizeof(float);
-  if (smem > 227 * 1024) return ZP_ERR_UNSUPPORTED;
-  const dim3 grid((unsigned)zp_ceil_div(E, kRibEdges));
-  int dev = 0;
-  ZP_CUDA(cudaGetDevice(&dev));
-#define CALL(LM)                                                                                \
-  {                                                                                             \
-    static std::mutex lock;                                                                     \
-    static size_t allowed[64] = {0};     /* per device: raise the limit when it grows */         \
-    {                                                                                           \
-      std::lock_guard<std::mutex> hold(lock);                                                   \
-      if (dev >= 0 && dev < 64 && smem > 48 * 1024 && smem > allowed[dev]) {                    \
-        ZP_CUDA(cudaFuncSetAttribute(rotate_in_bwd_pipe_kernel<LM>,                             \
-                                     cudaFuncAttributeMaxDynamicSharedMemorySize, (int)smem));  \
-        allowed[dev] = smem;                                                                    \
-      }                                                                                         \
-    }                                                                                           \
-    rotate_in_bwd_pipe_kernel<LM><<<grid, 64 * W, smem, st>>>(                                  \
-        t, E, W, rad_rows, da1, radial, x, src, dst, row_ptr, rot, grad_radial, du_src, dhead,  \
-        dcont, grad_rot);                                                                       \
-  }
-  ZP_DISPATCH_LMAX(t.lmax, CALL)
-#undef CALL
-  ZP_LAUNCH_CHECK("rotate_in_bwd_pipe_kernel");
-  return ZP_OK;
-}
-
-int zp_launch_node_reduce_pipe(const zp_plan *p, int64_t N, const float *du_src, const float *dhead,
-                               const float *dcont, const int32_t *row_ptr, const int32_t *perm_src,
-                               const int32_t *row_ptr_src, float *grad_x, cudaStream_t st) {
-  if (N == 0) return ZP_OK;
-  const int KC4 = p->t.K * p->t.C / 4;
-  node_reduce_pipe_kernel<<<(unsigned)N, 128, 0, st>>>(
-      N, KC4, (const float4 *)du_src, (const float4 *)dhead, (const float4 *)dcont, row_ptr,
-      perm_src, row_ptr_src, (float4 *)grad_x);
-  ZP_LAUNCH_CHECK("node_reduce_pipe_kernel");
   return ZP_OK;
 }
 

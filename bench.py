@@ -79,10 +79,10 @@ def hbm_bytes_per_step(block, n: int, e: int) -> dict:
     C, H, R = c.sphere_channels, c.hidden_channels, block.num_channels_rad
     w1 = c.lmax * H + Km * H                     # gate head + rows of conv1's output
     P = {2: 2, 0: 3, 1: 1}[block.precision]      # planes per operand
-    # with the fused epilogues (one- and two-plane formats) the gate activation and the rotation
-    # back run inside the contractions; what is left of the scatter is the sum of the per-row
-    # partial sums (one slab of nnz x C values per node and one per 32-edge block)
-    fused = P != 3 and os.environ.get("ZP_FUSED_EPILOGUE", "1") != "0"
+    # with the opt-in fused epilogues (ZP_FUSED_EPILOGUE=1, one- and two-plane formats) the gate
+    # activation and the rotation back run inside the contractions; what is left of the scatter is
+    # the sum of the per-row partial sums (one slab of nnz x C values per node and per 32-edge block)
+    fused = P != 3 and os.environ.get("ZP_FUSED_EPILOGUE", "0") == "1"
     nnz = sum((2 * min(l, c.mmax) + 1) * (2 * l + 1) for l in range(c.lmax + 1))
     per_edge = {
         "rotate_in": R * 4 + Km * 2 * C * 2 * P,

@@ -25,23 +25,25 @@ def test_contraction_macs_per_edge(bench):
     assert bench.gemm_macs_per_edge(bench.CFG) == want == 6_799_360
 
 
-def test_hbm_bytes_per_step(bench):
+def test_hbm_bytes_per_step(bench, monkeypatch):
     block = ESO2Block(BlockConfig(**bench.CFG))             # fp32 precision: two fp16 planes
     n, e = 2000, 60000
     got = bench.hbm_bytes_per_step(block, n, e)
     km, k, c, h, r = 19, 25, 128, 128, 3072
     w1 = 4 * h + km * h
     assert got["rotate_in"] == e * (r * 4 + km * 2 * c * 2 * 2)
-    assert "gate_fwd" not in got                # runs inside conv1's epilogue
+    assert got["gate_fwd"] == e * (w1 * 4 + km * h * 2 * 2)
     assert got["rotate_grad_out"] == e * (km * c * 4 + km * c * 2 * 2)
     assert got["gate_bwd"] == e * (w1 * 4 + km * h * 4 + w1 * 2 * 2)
     assert got["rotate_in_bwd"] == e * (km * 2 * c * 4 + 2 * r * 4 + 2 * k * c * 4)
     assert got["src_reduce"] == e * 2 * k * c * 4 + n * k * c * 4
-    # what is left of the scatter: the per-row partial sums (115 x C per node and per 32 edges)
-    assert got["rotate_back_scatter"] == e * 115 * c * 4 // 32 + n * (k + 115) * c * 4
-    unfused = ESO2Block(BlockConfig(**bench.CFG), precision="fp32_bf16x3")
-    got3 = bench.hbm_bytes_per_step(unfused, n, e)
-    assert got3["gate_fwd"] == e * (w1 * 4 + km * h * 2 * 3)
-    assert got3["rotate_back_scatter"] == e * km * c * 4 + n * k * c * 4
+    assert got["rotate_back_scatter"] == e * km * c * 4 + n * k * c * 4
+    # opt-in fused epilogues: the gate runs inside conv1, and what is left of the scatter is the
+    # sum of the per-row partial sums (115 x C per node and per 32 edges)
+    monkeypatch.setenv("ZP_FUSED_EPILOGUE", "1")
+    fused = bench.hbm_bytes_per_step(block, n, e)
+    assert "gate_fwd" not in fused
+    assert fused["rotate_back_scatter"] == e * 115 * c * 4 // 32 + n * (k + 115) * c * 4
+    monkeypatch.delenv("ZP_FUSED_EPILOGUE")
     one_plane = ESO2Block(BlockConfig(**bench.CFG), precision="bf16")
     assert bench.hbm_bytes_per_step(one_plane, n, e)["rotate_in"] == e * (r * 4 + km * 2 * c * 2)

@@ -197,6 +197,37 @@ def cpu_step_factory(batch, sample_nodes: int, threads: int):
     return step, int(keep.sum())
 
 
+def interp_baseline(threads: int) -> dict:
+    """The second CPU comparator: the FP64 IR interpreter (the reference's zippel/interp.py:135 run,
+    restated under oracle/) evaluating the force program -- energy and F = -dE/dpos -- on the
+    CPU-runnable configuration: 64 atoms in a 10 A cube, 5 A cutoff, lmax 2, C 32."""
+    from oracle import eso2_oracle as orc
+    from oracle import ir_interp as interp
+    from zippel_b200.blocks.eso2 import BlockConfig, ESO2Block
+    from zippel_b200.blocks.eso2_ir import build_force
+    from zippel_b200.blocks.ir_bind import bind
+    from zippel_b200.graph import synthetic_batch
+    torch.set_num_threads(threads)
+    cfg = dict(lmax=2, mmax=2, sphere_channels=32, hidden_channels=32, edge_channels=32,
+               num_distance_basis=32, cutoff=5.0)
+    batch = synthetic_batch(64, 2, 32, 5.0, box=10.0, max_neighbors=None, seed=0, dtype=torch.float64)
+    block = ESO2Block(BlockConfig(**cfg)).double()
+    jd = orc.load_jd(ROOT / "zippel_b200" / "data" / "jd.npz", 2)
+    prog, _meta = build_force(BlockConfig(**cfg), block.gauss_coeff)
+    inputs, sizes = bind(block, batch, jd)
+    inputs["seed_E"] = torch.ones(1, dtype=torch.float64)
+    interp.run(prog, inputs, sizes)
+    times = []
+    for _ in range(3):
+        t0 = time.perf_counter()
+        interp.run(prog, inputs, sizes)
+        times.append(time.perf_counter() - t0)
+    dt, e = statistics.median(times), batch["meta"]["n_edges"]
+    return {"value": e / dt, "unit": "edges/s", "cores": threads, "kind": "port",
+            "sample": f"IR interpreter, force program (E and dE/dpos), FP64, {e} edges, median of 3 "
+                      "runs after 1 warm-up"}
+
+
 def run_reference(args) -> dict:
     threads = os.cpu_count() or 1
     batch = make_workload(0, args.atoms)
@@ -215,7 +246,8 @@ def run_reference(args) -> dict:
         "n_gpus": args.gpus, "steps": args.steps, "warmup": args.warmup,
         "ms_per_step": dt * 1e3, "higher_is_better": True, "scaling": "weak",
         "vs_baseline": None, "dtype": "f32", "data": "synthetic",
-        "config": workload_config(batch, "host cores only"),
+        "config": workload_config(batch),
+        "notes": {"l2": "host cores only"},
         "cpu_baseline": {"value": val, "unit": "edges/s", "cores": threads, "kind": "port",
                          "sample": sample},
         "e2e": {"value": val, "unit": "edges/s", "h2d_bytes_per_step": 0,
@@ -224,12 +256,13 @@ def run_reference(args) -> dict:
     }
 
 
-def workload_config(batch, l2: str) -> dict:
+def workload_config(batch) -> dict:
+    """The same dict in both arms (what differs between them is said under `notes`)."""
     m = batch["meta"]
     return {"workload": f"eSEN SO(2) block fwd+VJP, {m['n_atoms']} atoms periodic cube 0.1/A^3, 6 A cutoff, "
                         "30 neighbours, lmax4 mmax2 C128 H128 EC128 64 RBF, fp32",
             "atoms_per_gpu": m["n_atoms"], "edges_per_gpu": m["n_edges"], "lmax": CFG["lmax"],
-            "mmax": CFG["mmax"], "channels": CFG["sphere_channels"], "l2": l2}
+            "mmax": CFG["mmax"], "channels": CFG["sphere_channels"]}
 
 
 # ------------------------------------------------------------------------------------------
@@ -286,9 +319,9 @@ def run_ours(args) -> dict | None:
 
     def kernel_step():
         runner.forward()
-        gw = runner.backward(upstream)[4]
-        if world > 1:
-            all_reduce_grads([gw[0], gw[1], *gw[2], gw[3], gw[4], *gw[5]])
+        runner.backward(upstream)
+        if world > 1:          # every weight gradient is a view of this one buffer
+            dist.all_reduce(runner.grad_w_flat, op=dist.ReduceOp.SUM)
 
     def barrier():
         if world > 1:
@@ -474,11 +507,12 @@ def run_ours(args) -> dict | None:
             "ms_per_step": ms_per_step, "higher_is_better": True, "scaling": "weak",
             "vs_baseline": None, "dtype": "bf16" if args.precision == "bf16" else "f32",
             "precision": args.precision, "data": "synthetic",
-            "config": {**workload_config(batch, "256 MiB L2 flush between steps, outside the "
-                                                "per-step events; per-step activations are >5 GB"),
-                       "radial": "value: radial features and envelope are precomputed inputs of "
-                                 "the C-ABI step; e2e: computed inside the step (radial MLP on "
-                                 "the library's kernels)"},
+            "config": workload_config(batch),
+            "notes": {"l2": "256 MiB L2 flush between steps, outside the per-step events; "
+                            "per-step activations are >5 GB",
+                      "radial": "value: radial features and envelope are precomputed inputs of "
+                                "the C-ABI step; e2e: computed inside the step (radial MLP on "
+                                "the library's kernels)"},
             "fwd_only": {"value": e / (fwd_ms * 1e-3), "unit": "edges/s (this rank)",
                          "ms_per_step": fwd_ms},
             "wall_ms_per_step_incl_flush": t_wall * 1e3 / args.steps,
@@ -496,96 +530,169 @@ def run_ours(args) -> dict | None:
             threads = os.cpu_count() or 1
             step, n_s = cpu_step_factory(batch, args.cpu_sample_nodes, threads)
             step()
-            t0 = time.perf_counter()
-            reps = 2
+            reps, times = 3, []
             for _ in range(reps):
+                t0 = time.perf_counter()
                 step()
-            dt = (time.perf_counter() - t0) / reps
+                times.append(time.perf_counter() - t0)
+            dt = statistics.median(times)
             line["cpu_baseline"] = {
                 "value": n_s / dt, "unit": "edges/s", "cores": threads, "kind": "port",
                 "sample": f"oracle fwd+VJP on the {n_s} edges into the first "
-                          f"{args.cpu_sample_nodes} atoms, {reps} repetitions after 1 warm-up"}
+                          f"{args.cpu_sample_nodes} atoms, median of {reps} repetitions after 1 "
+                          "warm-up",
+                "interp_cfg0": interp_baseline(threads)}
+    # ---- the two larger configurations, each in child processes of their own ----------------
+    if not args.no_large and args.atoms == N_ATOMS:
+        del runner, flush
+        cap = cap_grads = None
+        torch.cuda.empty_cache()
+        legs = large_legs(args, world, rank)
+        if line is not None:
+            line.update(legs)
     if world > 1:
         dist.barrier()
         dist.destroy_process_group()
     return line
 
 
+def large_legs(args, world: int, rank: int) -> dict:
+    """Runs `--workload cfg3` (512 structures of 200 atoms, bf16, strong scaling over the ranks) and
+    `--workload cfg4` (one 200 000-atom graph at lmax 6, destination-range partition) for a few
+    steps each.  Every rank starts one child process per leg; the children form a process group of
+    their own on another port, so a failure or a timeout there costs the leg, never the headline
+    line.  Returns {"cfg3": ..., "cfg4": ...} (the child's result line, or {"error": ...})."""
+    out = {}
+    here = str(pathlib.Path(__file__).resolve())
+    base_port = int(os.environ.get("MASTER_PORT", "29500"))
+    for i, (name, extra) in enumerate((
+            ("cfg3", ["--structures", str(args.structures), "--steps", "2", "--warmup", "1"]),
+            ("cfg4", ["--atoms", str(args.large_atoms), "--steps", "1", "--warmup", "1"]))):
+        env = dict(os.environ, MASTER_PORT=str(base_port + 101 * (i + 1)))
+        cmd = [sys.executable, here, "--workload", name, "--gpus", str(world), "--parity-nodes",
+               str(args.parity_nodes), *extra]
+        try:
+            res = subprocess.run(cmd, env=env, capture_output=True, text=True, timeout=args.large_timeout)
+            lines = [ln for ln in res.stdout.splitlines() if ln.startswith("{")]
+            if res.returncode == 0 and (lines or rank != 0):
+                out[name] = json.loads(lines[-1]) if lines else None
+            else:
+                out[name] = {"error": f"exit {res.returncode}: {res.stderr.strip()[-300:]}"}
+        except subprocess.TimeoutExpired:
+            out[name] = {"error": f"no result within {args.large_timeout} s"}
+    return out
+
+
 # ------------------------------------------------------------------------------------------
 # the larger benchmark configurations (not the headline line): batched structures, single graph
 # ------------------------------------------------------------------------------------------
 
-def run_large(args) -> dict | None:
-    """`--workload cfg3`: `--structures` independent 200-atom structures (bf16 precision unless
-    --precision is given), sharded over the ranks with no data-path exchange.  `--workload cfg4`:
-    one graph of `--atoms` atoms at lmax 6, partitioned by destination-node range over the ranks
-    (all-gather of embedding shards forward, reduce-scatter backward).  Inputs are resident on the
-    device; the step is `ESO2Block.node_output_vjp` (per destination chunk the forward and at once
-    the backward), or with --recompute and for the partitioned graph `node_output` + autograd,
-    whose backward recomputes each chunk's forward."""
+def make_large_inputs(workload: str, world: int, rank: int, dev, structures: int, atoms: int):
+    """Seeded inputs of the two larger configurations, on the device.
+
+    cfg3: `structures` independent 200-atom periodic cubes (block-diagonal batch), this rank's
+    contiguous share.  cfg4: one periodic cube of `atoms` atoms, lmax 6; every rank draws the same
+    positions and builds the neighbour list on its own device (zp_neighbors), then keeps the edges
+    into its destination-node range."""
+    from zippel_b200 import partition as part
+    from zippel_b200.blocks.wigner import gamma_harmonics
+    from zippel_b200.graph import neighbor_list, synthetic_batch
+
+    cfg = dict(CFG)
+    if workload == "cfg3":
+        a, b = part.structure_ranges(structures, world)[rank]
+        batch = synthetic_batch(200, cfg["lmax"], cfg["sphere_channels"], cfg["cutoff"],
+                                density=DENSITY, max_neighbors=MAX_NEIGHBORS, n_structures=b - a,
+                                seed=100 + rank)
+        d = {k: v.to(dev) for k, v in batch.items() if torch.is_tensor(v)}
+        g = torch.Generator("cpu").manual_seed(9 + rank)
+        d["upstream"] = torch.randn(batch["x_node"].shape, generator=g).to(dev)
+        return cfg, d, None
+    cfg["lmax"] = 6
+    k = (cfg["lmax"] + 1) ** 2
+    box = float((atoms / DENSITY) ** (1.0 / 3.0))
+    g = torch.Generator("cpu").manual_seed(5)
+    pos = (torch.rand(atoms, 3, generator=g, dtype=torch.float64) * box).to(dev)
+    edge_index, shifts, _ = neighbor_list(pos, box, cfg["cutoff"], MAX_NEIGHBORS)
+    e = edge_index.shape[1]
+    gd = torch.Generator(dev).manual_seed(6)          # the big arrays are drawn on the device
+    gamma = torch.rand(e, generator=gd, device=dev, dtype=torch.float64) * 2 * torch.pi
+    cos_g, sin_g = gamma_harmonics(gamma, cfg["lmax"])
+    d = {"pos": pos.float(), "edge_index": edge_index, "shifts": shifts.float(),
+         "cos_gamma_k": cos_g.float(), "sin_gamma_k": sin_g.float(),
+         "atomic_numbers": torch.randint(1, 30, (atoms,), generator=gd, device=dev),
+         "x_node": torch.randn(atoms, k, cfg["sphere_channels"], generator=gd, device=dev),
+         "upstream": torch.randn(atoms, k, cfg["sphere_channels"], generator=gd, device=dev)}
+    return cfg, d, part.node_ranges(atoms, world)
+
+
+def sampled_parity(block, cfg: dict, pos, z, x_full, ei, sh, cg, sg, rows, row0: int, row1: int,
+                   n_sample: int, seed: int) -> float:
+    """Relative L2 of `n_sample` rows of node_out (`rows` = rows row0:row1) against the CPU oracle.
+    A row depends on its node's incoming edges only, so the oracle runs on the small graph made of
+    the sampled destinations, their incoming edges and those edges' sources (nodes renumbered)."""
+    from oracle import eso2_oracle as orc
+    g = torch.Generator("cpu").manual_seed(seed)
+    nodes = (torch.randperm(row1 - row0, generator=g)[:n_sample] + row0).to(ei.device)
+    keep = torch.isin(ei[1], nodes)
+    e_sub = ei[:, keep]
+    used, inverse = torch.unique(torch.cat([nodes, e_sub.reshape(-1)]), return_inverse=True)
+    where, e_new = inverse[:nodes.numel()], inverse[nodes.numel():].reshape(2, -1)
+    f64 = lambda t: t.detach().cpu().double()                 # noqa: E731
+    params = {k: f64(v) for k, v in block.state_dict().items()}
+    jd = orc.load_jd(ROOT / "zippel_b200" / "data" / "jd.npz", cfg["lmax"])
+    want = orc.block_node_out(params, cfg, f64(pos[used]), z[used].cpu(), f64(x_full[used]),
+                              e_new.cpu(), f64(sh[keep]), f64(cg[keep]), f64(sg[keep]), jd)[where.cpu()]
+    got = f64(rows[nodes - row0])
+    return ((got - want).norm() / want.norm().clamp_min(1e-300)).item()
+
+
+def measure_large(workload: str, world: int, rank: int, dev, *, precision: str, structures: int,
+                  atoms: int, steps: int, warmup: int, recompute: bool = False,
+                  parity_nodes: int = 0) -> dict | None:
+    """One of the two larger configurations inside an initialised process group (or alone).
+    Returns the result dict on rank 0, None elsewhere."""
     import torch.distributed as dist
 
     from zippel_b200 import partition as part
     from zippel_b200.blocks.eso2 import BlockConfig, ESO2Block
-    from zippel_b200.graph import EdgeGraph, synthetic_batch
+    from zippel_b200.graph import EdgeGraph
 
-    world = int(os.environ.get("WORLD_SIZE", "1"))
-    rank = int(os.environ.get("RANK", "0"))
-    local = int(os.environ.get("LOCAL_RANK", "0"))
-    torch.cuda.set_device(local)
-    dev = torch.device("cuda", local)
-    if world > 1:
-        dist.init_process_group("nccl", device_id=dev)
-    cfg = dict(CFG)
-    if args.workload == "cfg3":
-        ranges = part.structure_ranges(args.structures, world)
-        n_struct = ranges[rank][1] - ranges[rank][0]
-        batch = synthetic_batch(200, cfg["lmax"], cfg["sphere_channels"], cfg["cutoff"],
-                                density=DENSITY, max_neighbors=MAX_NEIGHBORS,
-                                n_structures=n_struct, seed=100 + rank)
-        precision = args.precision if args.precision_given else "bf16"
-    else:
-        cfg["lmax"] = 6
-        batch = synthetic_batch(args.atoms, 6, cfg["sphere_channels"], cfg["cutoff"],
-                                density=DENSITY, max_neighbors=MAX_NEIGHBORS, seed=5)
-        precision = args.precision
+    t_setup = time.perf_counter()
+    cfg, d, nranges = make_large_inputs(workload, world, rank, dev, structures, atoms)
     block = ESO2Block(BlockConfig(**cfg), precision=precision)
     xavier_(block, 0)
     block = block.to(dev)
-    n = batch["pos"].shape[0]
-    g = torch.Generator("cpu").manual_seed(9)
-    up_full = torch.randn(batch["x_node"].shape, generator=g)
-    d = {k: v.to(dev) for k, v in batch.items() if torch.is_tensor(v)}
-    if args.workload == "cfg4" and world > 1:
-        nranges = part.node_ranges(n, world)
+    n = d["pos"].shape[0]
+    ei, sh, cg, sg = d["edge_index"], d["shifts"], d["cos_gamma_k"], d["sin_gamma_k"]
+    x_in, up = d["x_node"], d["upstream"]
+    partitioned = workload == "cfg4" and world > 1
+    if partitioned:
         a, b = nranges[rank]
-        keep = part.local_edges(d["edge_index"], nranges[rank])
-        ei, sh, cg, sg = d["edge_index"][:, keep], d["shifts"][keep], d["cos_gamma_k"][keep], d["sin_gamma_k"][keep]
-        x_in, up = d["x_node"][a:b].clone(), up_full[a:b].to(dev)
-    else:
-        ei, sh, cg, sg = d["edge_index"], d["shifts"], d["cos_gamma_k"], d["sin_gamma_k"]
-        x_in, up = d["x_node"], up_full.to(dev)
+        keep = part.local_edges(ei, nranges[rank])
+        ei, sh, cg, sg = ei[:, keep], sh[keep], cg[keep], sg[keep]
+        x_in, up = x_in[a:b].clone(), up[a:b].clone()
     graph = EdgeGraph.build(ei, n)
     e_local = ei.shape[1]
-
-    streamed = not args.recompute
+    t_setup = time.perf_counter() - t_setup
+    streamed = not recompute
 
     def step():
-        if streamed and args.workload == "cfg4" and world > 1:
-            _out, gx, gpos, gp = part.partitioned_node_output_vjp(
+        if streamed and partitioned:
+            out, gx, gpos, gp = part.partitioned_node_output_vjp(
                 block, d["pos"], d["atomic_numbers"], x_in, ei, sh, cg, sg, up, nranges, rank,
                 graph=graph)
-            return gx, gpos, gp
+            return out, gx, gpos, gp
         if streamed:
             # chunk forward, then at once chunk backward: no forward is computed twice
-            _out, gx, gpos, gp = block.node_output_vjp(d["pos"], d["atomic_numbers"], x_in, ei, sh,
-                                                       cg, sg, up, graph=graph)
+            out, gx, gpos, gp = block.node_output_vjp(d["pos"], d["atomic_numbers"], x_in, ei, sh,
+                                                      cg, sg, up, graph=graph)
             if world > 1:
                 part.all_reduce_grads([gpos, *[g_ for g_ in gp if g_ is not None]])
-            return gx, gpos, gp
+            return out, gx, gpos, gp
         pos = d["pos"].detach().requires_grad_(True)
         x = x_in.detach().requires_grad_(True)
-        if args.workload == "cfg4" and world > 1:
+        if partitioned:
             fn = lambda p_, z_, xf, e_, s_, c_, g_: block.node_output(p_, z_, xf, e_, s_, c_, g_, graph=graph)  # noqa: E731
             out = part.partitioned_node_output(fn, pos, d["atomic_numbers"], x, ei, sh, cg, sg, nranges, rank)
         else:
@@ -593,20 +700,22 @@ def run_large(args) -> dict | None:
         grads = torch.autograd.grad((out * up).sum(), [x, pos, *block.parameters()], allow_unused=True)
         if world > 1:
             part.all_reduce_grads([grads[1], *[g_ for g_ in grads[2:] if g_ is not None]])
-        return grads
+        return out.detach(), grads[0], grads[1], grads[2:]
 
-    for _ in range(max(args.warmup, 1)):
-        step()
+    torch.cuda.reset_peak_memory_stats(dev)
+    res = None
+    for _ in range(max(warmup, 1)):
+        res = step()
     torch.cuda.synchronize()
     if world > 1:
         dist.barrier()
     a_ev, b_ev = torch.cuda.Event(True), torch.cuda.Event(True)
     a_ev.record()
-    for _ in range(args.steps):
-        step()
+    for _ in range(steps):
+        res = step()
     b_ev.record()
     torch.cuda.synchronize()
-    ms = torch.tensor([a_ev.elapsed_time(b_ev) / args.steps], dtype=torch.float64, device=dev)
+    ms = torch.tensor([a_ev.elapsed_time(b_ev) / steps], dtype=torch.float64, device=dev)
     edges = torch.tensor([float(e_local)], dtype=torch.float64, device=dev)
     if world > 1:
         dist.all_reduce(ms, op=dist.ReduceOp.MAX)
@@ -615,18 +724,52 @@ def run_large(args) -> dict | None:
     status = block.plan(dev).device_status()
     line = None
     if rank == 0:
-        line = {"metric": METRIC, "workload": args.workload, "value": edges.item() / (ms.item() * 1e-3),
-                "unit": "edges/s", "n_gpus": world, "steps": args.steps, "ms_per_step": ms.item(),
-                "precision": precision, "data": "synthetic", "scaling": "strong",
-                "config": {"atoms_total": n if args.workload == "cfg4" else 200 * args.structures,
+        parity = None
+        if parity_nodes:
+            r0, r1 = nranges[0] if partitioned else (0, n)   # rank 0's rows; its edges hold all into them
+            parity = sampled_parity(block, cfg, d["pos"], d["atomic_numbers"], d["x_node"], ei, sh, cg,
+                                    sg, res[0], r0, r1, parity_nodes, seed=11)
+        line = {"workload": workload, "value": edges.item() / (ms.item() * 1e-3), "unit": "edges/s",
+                "n_gpus": world, "steps": steps, "ms_per_step": ms.item(), "precision": precision,
+                "scaling": "strong",
+                "config": {"atoms_total": n if workload == "cfg4" else 200 * structures,
                            "edges_total": edges.item(), "lmax": cfg["lmax"], "mmax": cfg["mmax"],
                            "channels": cfg["sphere_channels"], "chunks_per_rank": chunks,
-                           "note": ("ESO2Block.node_output_vjp, inputs resident: per destination "
+                           "path": ("ESO2Block.node_output_vjp, inputs resident: per destination "
                                     "chunk the forward and at once the backward, no recompute"
                                     if streamed else
                                     "module API forward + autograd VJP, inputs resident; chunked "
                                     "runs recompute the forward in the backward")},
-                "device_status": status, "peak_mem_gb": torch.cuda.max_memory_allocated(dev) / 1e9}
+                "device_status": status, "peak_mem_gb": torch.cuda.max_memory_allocated(dev) / 1e9,
+                "setup_s": t_setup, "parity_rel_l2_sampled_rows": parity}
+    del res
+    return line
+
+
+def run_large(args) -> dict | None:
+    """`--workload cfg3`: `--structures` independent 200-atom structures (bf16 precision unless
+    --precision is given), sharded over the ranks with no data-path exchange.  `--workload cfg4`:
+    one graph of `--atoms` atoms at lmax 6, partitioned by destination-node range over the ranks
+    (all-gather of embedding shards forward, reduce-scatter backward).  Inputs are resident on the
+    device; the step is `ESO2Block.node_output_vjp` (per destination chunk the forward and at once
+    the backward), or with --recompute `node_output` + autograd, whose backward recomputes each
+    chunk's forward."""
+    import torch.distributed as dist
+
+    world = int(os.environ.get("WORLD_SIZE", "1"))
+    rank = int(os.environ.get("RANK", "0"))
+    local = int(os.environ.get("LOCAL_RANK", "0"))
+    torch.cuda.set_device(local)
+    dev = torch.device("cuda", local)
+    if world > 1:
+        dist.init_process_group("nccl", device_id=dev)
+    precision = args.precision if (args.workload == "cfg4" or args.precision_given) else "bf16"
+    line = measure_large(args.workload, world, rank, dev, precision=precision,
+                         structures=args.structures,
+                         atoms=args.atoms if args.workload == "cfg4" else 200, steps=args.steps,
+                         warmup=args.warmup, recompute=args.recompute, parity_nodes=args.parity_nodes)
+    if line is not None:
+        line = {"metric": METRIC, "data": "synthetic", **line}
     if world > 1:
         dist.barrier()
         dist.destroy_process_group()
@@ -724,6 +867,12 @@ def main() -> None:
                     help="cfg3 / cfg4: node_output + autograd (chunks recompute their forward) "
                          "instead of the streamed node_output_vjp")
     ap.add_argument("--structures", type=int, default=512, help="cfg3: number of 200-atom structures")
+    ap.add_argument("--parity-nodes", type=int, default=6,
+                    help="cfg3 / cfg4 legs: destination rows checked against the CPU oracle (0 = none)")
+    ap.add_argument("--no-large", action="store_true",
+                    help="skip the cfg3 / cfg4 legs that follow the headline measurement")
+    ap.add_argument("--large-atoms", type=int, default=200000, help="atoms of the cfg4 leg")
+    ap.add_argument("--large-timeout", type=int, default=300, help="seconds allowed per cfg3 / cfg4 leg")
     ap.add_argument("--atoms", type=int, default=N_ATOMS,
                     help="atoms per GPU; anything but the default is a profiling-size run, "
                          "not the benchmark workload")

@@ -47,9 +47,18 @@ class EdgeConvRunner:
         self._w, k1 = _weights_struct(self.plan.mmax, *self.weights)
         self._keep = [k1]
         if self.with_backward:
-            g = [torch.empty_like(t) for t in (c1_w0, c1_b0, c2_w0, c2_b0)]
-            g1, g2 = [torch.empty_like(t) for t in c1_wm], [torch.empty_like(t) for t in c2_wm]
-            self.grad_w = (g[0], g[1], g1, g[2], g[3], g2)
+            # all weight gradients are views of ONE buffer, so that a data-parallel caller can
+            # all-reduce them in place with a single collective (no gather / copy-back)
+            order = [c1_w0, c1_b0, *c1_wm, c2_w0, c2_b0, *c2_wm]
+            starts, total = [], 0
+            for t in order:
+                starts.append(total)
+                total += (t.numel() + 63) // 64 * 64          # 256-byte aligned views
+            self.grad_w_flat = torch.zeros(total, dtype=torch.float32, device=c1_w0.device)
+            views = [self.grad_w_flat[a:a + t.numel()].view_as(t) for a, t in zip(starts, order)]
+            m = len(c1_wm)
+            self.grad_w = (views[0], views[1], views[2:2 + m], views[2 + m], views[3 + m],
+                           views[4 + m:])
             self._gw, k2 = _weights_struct(self.plan.mmax, *self.grad_w)
             self._keep.append(k2)
 

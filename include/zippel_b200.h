@@ -324,6 +324,16 @@ int zp_neighbors_fill(const double *pos, int64_t n_atoms, double box, double cut
  * ZP_ERR_DEVICE_TIMEOUT if a bounded device-side wait gave up since the last read.          */
 int zp_plan_device_status(zp_plan *plan, int *status_out);
 
+/* Self-test of the bounded device-side waits (no reference counterpart).  Every wait inside the
+ * contraction kernels gives up after a time limit, records ZP_ERR_DEVICE_TIMEOUT in the plan's
+ * status word and lets all warps of the CTA return, so a lost signal can never hang the GPU.
+ * This call launches one tiny product on one SM whose operand loads are deliberately never
+ * issued, with the limit set to `limit_ns`: the kernel returns after about that long,
+ * zp_plan_device_status then reports (and clears) ZP_ERR_DEVICE_TIMEOUT, and the library keeps
+ * working.  `scratch`: at least 32 KiB of device memory, 256-byte aligned.                     */
+int zp_selftest_bounded_wait(zp_plan *plan, void *scratch, size_t scratch_bytes, int64_t limit_ns,
+                             void *stream);
+
 /* Per-kernel-class device timing for benchmarks (the reference times whole steps with CUDA
  * events, bench/harness.py:88-149; there is no per-kernel counterpart).  While enabled, the
  * forward/backward drivers bracket each kernel class with CUDA events on the caller's stream.

@@ -135,3 +135,42 @@ def test_tensor_core_linear_and_vjp(M, K, N, precision):
     else:
         assert got.shape == (0, N) and hw.abs().max().item() == 0.0
     assert plan.device_status() == 0
+
+
+def test_bounded_wait_runs_out_and_the_library_keeps_working():
+    """A wait that nothing will ever satisfy: the kernel must give up after its time limit, record
+    ZP_ERR_DEVICE_TIMEOUT in the plan's status word and return with every warp (no trap, no hang);
+    the status reads once and clears, and the next product is correct."""
+    import ctypes
+    import time
+    from zippel_b200 import _lib
+    from zippel_b200.blocks.eso2 import Plan
+    lib = _lib.load()
+    plan = Plan.get(2, 2, 8, 8, "cuda", precision=1)
+    torch.cuda.synchronize()
+    assert plan.device_status() == 0
+    scratch = torch.empty(64 << 10, dtype=torch.uint8, device="cuda")
+    st = torch.cuda.current_stream().cuda_stream
+    t0 = time.perf_counter()
+    _lib.check(lib.zp_selftest_bounded_wait(plan.handle, scratch.data_ptr(), scratch.numel(),
+                                            3_000_000, st), "zp_selftest_bounded_wait")   # 3 ms
+    torch.cuda.synchronize()
+    assert time.perf_counter() - t0 < 1.0                     # it returned, and soon
+    assert plan.device_status() == 5                          # ZP_ERR_DEVICE_TIMEOUT
+    assert plan.device_status() == 0                          # read once, then clear
+    # a normal product afterwards
+    g = torch.Generator("cpu").manual_seed(0)
+    a = torch.randn(200, 96, generator=g).cuda()
+    b = torch.randn(72, 96, generator=g).cuda()
+    ap, bp = torch.empty(200, 96, dtype=torch.bfloat16, device="cuda"), torch.empty(72, 96, dtype=torch.bfloat16, device="cuda")
+    for src, dst in ((a, ap), (b, bp)):
+        _lib.check(lib.zp_split_planes(src.shape[0], 96, src.data_ptr(), 96, dst.data_ptr(), 96,
+                                       src.shape[0] * 96, 1, st), "zp_split_planes")
+    c = torch.empty(200, 72, device="cuda")
+    _lib.check(lib.zp_gemm_planes(plan.handle, 200, 72, 96, 1, ap.data_ptr(), 96, 200 * 96, 0,
+                                  bp.data_ptr(), 96, 72 * 96, 0, None, c.data_ptr(), 72, 0, 1, 0, 0,
+                                  None, st), "zp_gemm_planes")
+    want = ap.float() @ bp.float().T
+    assert (c - want).abs().max().item() < 1e-3 * want.abs().max().item()
+    assert plan.device_status() == 0
+    assert lib.zp_selftest_bounded_wait(plan.handle, scratch.data_ptr(), 16, 1000, st) == 3   # workspace

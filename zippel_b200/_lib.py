@@ -87,6 +87,7 @@ SIGNATURES = {
     "zp_neighbors_fill": (C.c_int, [_P, _I64, C.c_double, C.c_double, C.c_int, _P, _I64, _P, _P, _P,
                                     _P, _SZ, _P]),
     "zp_plan_device_status": (C.c_int, [_P, C.POINTER(C.c_int)]),
+    "zp_selftest_bounded_wait": (C.c_int, [_P, _P, _SZ, _I64, _P]),
     "zp_kernel_class_name": (C.c_char_p, [C.c_int]),
     "zp_timing_enable": (C.c_int, [_P, C.c_int]),
     "zp_timing_read": (C.c_int, [_P, C.POINTER(C.c_float), C.POINTER(C.c_int64)]),

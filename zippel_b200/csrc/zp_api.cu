@@ -377,6 +377,23 @@ int zp_gemm_planes(zp_plan *plan, int64_t M, int64_t N, int64_t K, int planes, c
   return zp_launch_gemm_tc(g, (cudaStream_t)stream);
 }
 
+int zp_selftest_bounded_wait(zp_plan *plan, void *scratch, size_t scratch_bytes, int64_t limit_ns,
+                             void *stream) {
+  // a 128 x 32 x 64 one-plane product whose producer never loads: the MMA warp's first wait
+  // runs out, raises the CTA's abort flag and the status word, and every warp leaves normally
+  constexpr int64_t M = 128, N = 32, K = 64;
+  const size_t need = (size_t)(M * K + N * K) * 2 + (size_t)M * N * 4;
+  if (!plan || !scratch || limit_ns <= 0 || (reinterpret_cast<uintptr_t>(scratch) & 255))
+    return ZP_ERR_INVALID_ARG;
+  if (scratch_bytes < need) return ZP_ERR_WORKSPACE;
+  char *base = static_cast<char *>(scratch);
+  ZP_CUDA(cudaMemsetAsync(base, 0, need, (cudaStream_t)stream));
+  ZpGemmTc g{M, N, K, 1, base, K, M * K, 0, base + M * K * 2, K, N * K, 0, nullptr,
+             reinterpret_cast<float *>(base + (M * K + N * K) * 2), N, plan->status_dev,
+             2 /* one-SM kernel */, 1, 0, 0, 0, nullptr, nullptr, nullptr, nullptr, limit_ns, 1};
+  return zp_launch_gemm_tc(g, (cudaStream_t)stream);
+}
+
 int zp_wigner_forward(const zp_plan *plan, int64_t n_edges, const float *edge_vec,
                       const float *cos_g, const float *sin_g, float *rot, void *stream) {
   if (!plan || n_edges < 0) return ZP_ERR_INVALID_ARG;

@@ -180,6 +180,8 @@ struct ZpGemmTc {
   const float *scale_a, *scale_b;               // device scalars multiplied into the result
   float *absmax_out;                            // device scalar updated with max |C| (or null)
   const ZpEpilogue *epi;                        // fused epilogue (null = store C)
+  int64_t wait_limit_ns;                        // bound of the device-side waits (0 = 2 s)
+  int unarmed;                                  // self-test: no operand is ever loaded
 };
 int zp_launch_gemm_tc(const ZpGemmTc &g, cudaStream_t st);
 // block_node[b] = node of the first edge of 32-edge block b, for ZpEpilogue::block_node

@@ -51,7 +51,7 @@ namespace {
 constexpr int BM = 128;
 constexpr int kTmemBuf = 256;          // TMEM columns per accumulator buffer
 constexpr int kThreads = 320;            // producer warp, MMA warp, eight epilogue warps
-constexpr uint64_t kWaitLimitNs = 2000000000ull;
+constexpr uint64_t kWaitLimitNs = 2000000000ull;   // default bound of every device-side wait
 
 __device__ __forceinline__ uint32_t smem_u32(const void *p) {
   return (uint32_t)__cvta_generic_to_shared(p);
@@ -102,7 +102,7 @@ __device__ __forceinline__ bool mbar_try_wait(uint64_t *bar, uint32_t parity) {
 // The clock is only looked at every 1024 failed polls (the first look starts the interval), so a
 // wait that is satisfied quickly never pays for reading the global timer.
 __device__ __forceinline__ bool mbar_wait(uint64_t *bar, uint32_t parity, volatile int *abort_flag,
-                                          int *status) {
+                                          int *status, uint64_t limit_ns = kWaitLimitNs) {
   if (mbar_try_wait(bar, parity)) return true;
   uint64_t t0 = 0;
   uint32_t spins = 0;
@@ -112,7 +112,7 @@ __device__ __forceinline__ bool mbar_wait(uint64_t *bar, uint32_t parity, volati
       const uint64_t now = globaltimer_ns();
       if (t0 == 0) {
         t0 = now;
-      } else if (now - t0 > kWaitLimitNs) {
+      } else if (now - t0 > limit_ns) {
         *abort_flag = 1;
         atomicExch(status, (int)ZP_ERR_DEVICE_TIMEOUT);
         return false;
@@ -210,6 +210,8 @@ struct GemmParams {
   int64_t ldc, split_stride;
   int tma_store;          // epilogue goes through TMA stores (map_c is valid)
   int *status;
+  uint64_t wait_limit_ns; // bound of every mbarrier wait
+  int unarmed;            // self-test: the producers load nothing, so the first wait runs out
   ZpEpilogue epi;         // work of the fused epilogues (mode 0: none)
 };
 
@@ -576,14 +578,14 @@ __device__ __forceinline__ void gemm_tc_body(const CUtensorMap &map_a, const CUt
 
   if (warp == 0) {
     // ---------------------------------------------------------------- TMA producer
-    if (elect_one()) {
+    if (!p.unarmed && elect_one()) {
       uint32_t it = 0;
       bool ok = true;
       for (int w = blockIdx.x; w < num_work && ok; w += gridDim.x) {
         const Work x = decode_work(p, w);
         for (int kb = x.kb0; kb < x.kb1 && ok; ++kb, ++it) {
           const int s = it % STAGES;
-          ok = mbar_wait(&empty[s], ((it / STAGES) & 1) ^ 1, abort_flag, p.status);
+          ok = mbar_wait(&empty[s], ((it / STAGES) & 1) ^ 1, abort_flag, p.status, p.wait_limit_ns);
           if (!ok) break;
           uint8_t *st = smem + (size_t)s * L::kStage;
           mbar_expect_tx(&full[s], P * (a_bytes + b_bytes));
@@ -622,7 +624,7 @@ __device__ __forceinline__ void gemm_tc_body(const CUtensorMap &map_a, const CUt
         for (int c0 = x.kb0; c0 < x.kb1 && ok; c0 += p.kc, ++unit) {
           const int c1 = min(x.kb1, c0 + p.kc);
           const int buf = unit % kAccBufs;
-          ok = mbar_wait(&tmem_empty[buf], ((unit / kAccBufs) & 1) ^ 1, abort_flag, p.status);
+          ok = mbar_wait(&tmem_empty[buf], ((unit / kAccBufs) & 1) ^ 1, abort_flag, p.status, p.wait_limit_ns);
           if (!ok) break;
           tcgen05_fence_after();
           // one plane: accumulator `buf`; three planes: leading product at column 0, small at 256
@@ -630,7 +632,7 @@ __device__ __forceinline__ void gemm_tc_body(const CUtensorMap &map_a, const CUt
           const uint32_t d_small = tmem_base + kTmemBuf;
           for (int kb = c0; kb < c1 && ok; ++kb, ++it) {
             const int s = it % STAGES;
-            ok = mbar_wait(&full[s], (it / STAGES) & 1, abort_flag, p.status);
+            ok = mbar_wait(&full[s], (it / STAGES) & 1, abort_flag, p.status, p.wait_limit_ns);
             if (!ok) break;
             tcgen05_fence_after();
             const uint32_t sa = smem_u32(smem + (size_t)s * L::kStage);
@@ -687,7 +689,7 @@ __device__ __forceinline__ void gemm_tc_body(const CUtensorMap &map_a, const CUt
           node = p.epi.block_node[row0 >> 5];
           rp_l = p.epi.row_ptr[min(node + lane, p.epi.n_nodes)];
         }
-        ok = mbar_wait(&tmem_full[buf], (unit / kAccBufs) & 1, abort_flag, p.status);
+        ok = mbar_wait(&tmem_full[buf], (unit / kAccBufs) & 1, abort_flag, p.status, p.wait_limit_ns);
         ok = __all_sync(0xffffffffu, ok);
         if (!ok) break;
         tcgen05_fence_after();
@@ -946,7 +948,7 @@ __device__ __forceinline__ void gemm_tc_pair_body(const CUtensorMap &map_a, cons
 
   if (warp == 0) {
     // ---------------------------------------------------------------- TMA producer (both CTAs)
-    if (elect_one()) {
+    if (!p.unarmed && elect_one()) {
       uint32_t it = 0;
       bool ok = true;
       for (int w = pair; w < num_work && ok; w += num_pairs) {
@@ -954,7 +956,7 @@ __device__ __forceinline__ void gemm_tc_pair_body(const CUtensorMap &map_a, cons
         const int m0 = x.m0 + (int)rank * BM, n0 = x.n0 + (int)rank * half_n;
         for (int kb = x.kb0; kb < x.kb1 && ok; ++kb, ++it) {
           const int s = it % STAGES;
-          ok = mbar_wait(&empty[s], ((it / STAGES) & 1) ^ 1, abort_flag, p.status);
+          ok = mbar_wait(&empty[s], ((it / STAGES) & 1) ^ 1, abort_flag, p.status, p.wait_limit_ns);
           if (!ok) break;
           uint8_t *st = smem + (size_t)s * L::kStage;
           if (rank == 0) mbar_expect_tx(&full[s], 2 * P * (a_bytes + b_bytes));
@@ -980,7 +982,7 @@ __device__ __forceinline__ void gemm_tc_pair_body(const CUtensorMap &map_a, cons
       }
       // the leader's last stage releases must have landed here before this CTA may exit
       for (int j = 0; j < STAGES && ok; ++j, ++it)
-        ok = mbar_wait(&empty[it % STAGES], ((it / STAGES) & 1) ^ 1, abort_flag, p.status);
+        ok = mbar_wait(&empty[it % STAGES], ((it / STAGES) & 1) ^ 1, abort_flag, p.status, p.wait_limit_ns);
     }
   } else if (warp == 1) {
     // ---------------------------------------------------------------- MMA issuer (leader only)
@@ -1000,14 +1002,14 @@ __device__ __forceinline__ void gemm_tc_pair_body(const CUtensorMap &map_a, cons
           // while the epilogue drains this one
           const int buf = P == 1 ? (int)(unit & 1) : 0;
           const uint32_t round = P == 1 ? (unit >> 1) : unit;
-          ok = mbar_wait(&tmem_empty[buf], (round & 1) ^ 1, abort_flag, p.status);
+          ok = mbar_wait(&tmem_empty[buf], (round & 1) ^ 1, abort_flag, p.status, p.wait_limit_ns);
           if (!ok) break;
           tcgen05_fence_after();
           const uint32_t d_main = tmem_base + (uint32_t)buf * kTmemBuf;
           const uint32_t d_small = tmem_base + kTmemBuf;
           for (int kb = c0; kb < c1 && ok; ++kb, ++it) {
             const int s = it % STAGES;
-            ok = mbar_wait(&full[s], (it / STAGES) & 1, abort_flag, p.status);
+            ok = mbar_wait(&full[s], (it / STAGES) & 1, abort_flag, p.status, p.wait_limit_ns);
             if (!ok) break;
             tcgen05_fence_after();
             const uint32_t sa = smem_u32(smem + (size_t)s * L::kStage);
@@ -1062,7 +1064,7 @@ __device__ __forceinline__ void gemm_tc_pair_body(const CUtensorMap &map_a, cons
           node = p.epi.block_node[row0 >> 5];
           rp_l = p.epi.row_ptr[min(node + lane, p.epi.n_nodes)];
         }
-        ok = mbar_wait(&tmem_full[buf], round & 1, abort_flag, p.status);
+        ok = mbar_wait(&tmem_full[buf], round & 1, abort_flag, p.status, p.wait_limit_ns);
         ok = __all_sync(0xffffffffu, ok);
         if (!ok) break;
         tcgen05_fence_after();
@@ -1352,6 +1354,8 @@ void fill_params(GemmParams &p, const ZpGemmTc &g, int bk) {
   p.a_mn = g.a_mn; p.b_mn = g.b_mn;
   p.fp16 = g.fp16; p.scale_a = g.scale_a; p.scale_b = g.scale_b; p.absmax_out = g.absmax_out;
   p.bias = g.bias; p.C = g.C; p.ldc = g.ldc; p.split_stride = g.split_stride; p.status = g.status;
+  p.wait_limit_ns = g.wait_limit_ns > 0 ? (uint64_t)g.wait_limit_ns : kWaitLimitNs;
+  p.unarmed = g.unarmed;
   if (g.epi) p.epi = *g.epi;
   else p.epi.mode = ZP_EPI_NONE;
 }

@@ -3,6 +3,7 @@
 #include <cstdio>
 #include <cstdlib>
 #include <cstring>
+#include <mutex>
 #include <new>
 #include <vector>
 
@@ -158,6 +159,45 @@ Workspace carve(const zp_plan *p, int64_t N, int64_t E, int mode, void *base) {
   return w;
 }
 
+// ZP_STREAMS=0 in the environment keeps every launch on the caller's stream.
+bool lanes_enabled() {
+  static int on = -1;
+  if (on < 0) {
+    const char *e = getenv("ZP_STREAMS");
+    on = (e && e[0] == '0') ? 0 : 1;
+  }
+  return on == 1;
+}
+
+// The caller's stream plus the plan's two side streams for one forward / backward call.
+struct Lanes {
+  const zp_plan *p;
+  cudaStream_t main;
+  bool on;
+  std::unique_lock<std::mutex> hold;
+  Lanes(const zp_plan *plan, cudaStream_t st)
+      : p(plan), main(st), on(lanes_enabled() && !plan->timer && plan->aux_stream[0]) {
+    if (on) hold = std::unique_lock<std::mutex>(*static_cast<std::mutex *>(plan->lane_lock));
+  }
+  cudaStream_t pick(int i) const { return (!on || i % 3 == 0) ? main : p->aux_stream[i % 3 - 1]; }
+  // side streams continue from what the caller's stream has been given so far
+  int fork() {
+    if (!on) return ZP_OK;
+    ZP_CUDA(cudaEventRecord(p->ev_fork, main));
+    for (int i = 0; i < 2; ++i) ZP_CUDA(cudaStreamWaitEvent(p->aux_stream[i], p->ev_fork, 0));
+    return ZP_OK;
+  }
+  // the caller's stream continues after everything the side streams have been given
+  int join() {
+    if (!on) return ZP_OK;
+    for (int i = 0; i < 2; ++i) {
+      ZP_CUDA(cudaEventRecord(p->ev_join[i], p->aux_stream[i]));
+      ZP_CUDA(cudaStreamWaitEvent(main, p->ev_join[i], 0));
+    }
+    return ZP_OK;
+  }
+};
+
 const float *wscale(const zp_plan *p, const Workspace &w, int conv, int m) {
   return p->fp16 ? w.scales + kScWeights + (conv * (ZP_MAX_L + 1) + m) * 2 + 1 : nullptr;
 }
@@ -270,6 +310,17 @@ int zp_plan_create(const zp_config *cfg, const double *jd_host, zp_plan **plan_o
   p->w_elems = woff;
   p->g_elems = goff;
 
+  p->lane_lock = new (std::nothrow) std::mutex;
+  if (!p->lane_lock ||
+      cudaStreamCreateWithFlags(&p->aux_stream[0], cudaStreamNonBlocking) != cudaSuccess ||
+      cudaStreamCreateWithFlags(&p->aux_stream[1], cudaStreamNonBlocking) != cudaSuccess ||
+      cudaEventCreateWithFlags(&p->ev_fork, cudaEventDisableTiming) != cudaSuccess ||
+      cudaEventCreateWithFlags(&p->ev_join[0], cudaEventDisableTiming) != cudaSuccess ||
+      cudaEventCreateWithFlags(&p->ev_join[1], cudaEventDisableTiming) != cudaSuccess) {
+    zp_set_cuda_error(cudaGetLastError(), "zp_plan_create (streams)");
+    zp_plan_destroy(p);
+    return ZP_ERR_CUDA;
+  }
   if (cudaGetDevice(&p->device) != cudaSuccess ||
       cudaMalloc(&p->status_dev, sizeof(int)) != cudaSuccess ||
       cudaMemset(p->status_dev, 0, sizeof(int)) != cudaSuccess ||
@@ -277,7 +328,7 @@ int zp_plan_create(const zp_config *cfg, const double *jd_host, zp_plan **plan_o
       cudaMemcpy(p->jd_dev, jd_host, sizeof(double) * jo, cudaMemcpyHostToDevice) !=
           cudaSuccess) {
     zp_set_cuda_error(cudaGetLastError(), "zp_plan_create");
-    delete p;
+    zp_plan_destroy(p);
     return ZP_ERR_CUDA;
   }
   *plan_out = p;
@@ -323,6 +374,12 @@ int zp_plan_destroy(zp_plan *plan) {
   zp_timing_enable(plan, 0);
   if (plan->jd_dev) cudaFree(plan->jd_dev);
   if (plan->status_dev) cudaFree(plan->status_dev);
+  for (int i = 0; i < 2; ++i) {
+    if (plan->aux_stream[i]) cudaStreamDestroy(plan->aux_stream[i]);
+    if (plan->ev_join[i]) cudaEventDestroy(plan->ev_join[i]);
+  }
+  if (plan->ev_fork) cudaEventDestroy(plan->ev_fork);
+  delete static_cast<std::mutex *>(plan->lane_lock);
   delete plan;
   return ZP_OK;
 }
@@ -444,6 +501,7 @@ static int eso2_forward(const zp_plan *plan, int64_t N, int64_t E, const float *
   const Workspace ws = carve(plan, N, E, keep ? 0 : 2, workspace);
   if (workspace_bytes < ws.bytes) return ZP_ERR_WORKSPACE;
   cudaStream_t st = (cudaStream_t)stream;
+  Lanes lanes(plan, st);
   const ZpTables &t = plan->t;
   const bool fuse1 = can_fuse(plan, 0), fuse2 = can_fuse(plan, 1);
   const bool lean = !keep && fuse1 && fuse2;          // h1 rows and y are never written
@@ -504,6 +562,7 @@ static int eso2_forward(const zp_plan *plan, int64_t N, int64_t E, const float *
                          plan->fp16 ? ws.scales + kScH1 : nullptr, nullptr};
         ZP_TIMED(ZP_K_GEMM_FWD, zp_launch_gemm_tc(g, st));
       }
+      if (m == 0 && (rc = lanes.fork())) return rc;      // the other launches read the gates
       epi.row_first = t.m_row0[m];
       epi.out = sub(ws.ht, (int64_t)t.m_row0[m] * t.H);
       // lean: the fp32 rows are never stored (C is not dereferenced)
@@ -513,9 +572,12 @@ static int eso2_forward(const zp_plan *plan, int64_t N, int64_t E, const float *
                        (int64_t)out * in, 0, m == 0 ? w->c1_b0 + gate_cols : nullptr, Cc,
                        ws.ld_h1, plan->status_dev, 0, 1, 0, 0, plan->fp16, A.scale,
                        wscale(plan, ws, 0, m), plan->fp16 ? ws.scales + kScH1 : nullptr, &epi};
-      ZP_TIMED(ZP_K_GEMM_FWD, zp_launch_gemm_tc(g, st));
+      ZP_TIMED(ZP_K_GEMM_FWD, zp_launch_gemm_tc(g, lanes.pick(m)));
     }
+    if ((rc = lanes.join())) return rc;
   } else {
+    // the per-m products are independent: side by side on the plan's streams
+    if ((rc = lanes.fork())) return rc;
     for (int m = 0; m < plan->n_blocks && E > 0; ++m) {
       const int in = plan->c1_in[m], out = plan->c1_out[m];
       const ZpPlanes A = sub(ws.a1, (int64_t)t.m_row0[m] * 2 * t.C);
@@ -525,8 +587,9 @@ static int eso2_forward(const zp_plan *plan, int64_t N, int64_t E, const float *
                        m == 0 ? w->c1_b0 : nullptr, Cc, t.w1_cols, plan->status_dev, 0, 1, 0, 0,
                        plan->fp16, A.scale, wscale(plan, ws, 0, m),
                        plan->fp16 ? ws.scales + kScH1 : nullptr, nullptr};
-      ZP_TIMED(ZP_K_GEMM_FWD, zp_launch_gemm_tc(g, st));
+      ZP_TIMED(ZP_K_GEMM_FWD, zp_launch_gemm_tc(g, lanes.pick(m)));
     }
+    if ((rc = lanes.join())) return rc;
     if (plan->fp16)      // |gate(h1)| <= |h1|
       ZP_TIMED(ZP_K_GATE_FWD, zp_launch_scale(1.f, ws.scales + kScH1, nullptr, nullptr, 0.f,
                                               ws.scales + kScHt, st));
@@ -550,6 +613,7 @@ static int eso2_forward(const zp_plan *plan, int64_t N, int64_t E, const float *
     epi.block_node = ws.block_node;
     ZP_TIMED(ZP_K_ROTATE_BACK, zp_launch_block_nodes(E, N, row_ptr, ws.block_node, st));
   }
+  if ((rc = lanes.fork())) return rc;
   for (int m = 0; m < plan->n_blocks && E > 0; ++m) {
     const int in = plan->c2_in[m], out = plan->c2_out[m];
     const ZpPlanes A = sub(ws.ht, (int64_t)t.m_row0[m] * t.H);
@@ -560,8 +624,9 @@ static int eso2_forward(const zp_plan *plan, int64_t N, int64_t E, const float *
                      m == 0 ? w->c2_b0 : nullptr, Cc, ldy, plan->status_dev, 0, 1, 0, 0,
                      plan->fp16, A.scale, wscale(plan, ws, 1, m), nullptr,
                      fuse2 ? &epi : nullptr};
-    ZP_TIMED(ZP_K_GEMM_FWD, zp_launch_gemm_tc(g, st));
+    ZP_TIMED(ZP_K_GEMM_FWD, zp_launch_gemm_tc(g, lanes.pick(m)));
   }
+  if ((rc = lanes.join())) return rc;
   if (fuse2)
     ZP_TIMED(ZP_K_ROTATE_BACK,
              zp_launch_node_sum(plan, N, ws.head, ws.cont, row_ptr, node_out, st));
@@ -618,6 +683,7 @@ int zp_eso2_backward(const zp_plan *plan, int64_t N, int64_t E, const float *gra
   const Workspace ws = carve(plan, 0, E, 1, workspace);
   if (workspace_bytes < ws.bytes) return ZP_ERR_WORKSPACE;
   cudaStream_t st = (cudaStream_t)stream;
+  Lanes lanes(plan, st);
   const ZpTables &t = plan->t;
   const int P = plan->planes;
   const int64_t lda = (int64_t)t.Km * 2 * t.C, ldh = (int64_t)t.Km * t.H;
@@ -659,6 +725,9 @@ int zp_eso2_backward(const zp_plan *plan, int64_t N, int64_t E, const float *gra
     } else if (plan->fp16) {
       ZP_CUDA(cudaMemsetAsync(ws.scales + kScDht, 0, sizeof(float), st));
     }
+    // the input- and weight-gradient products of the blocks and the bias column sums only read
+    // dY, X and the weights: side by side on the plan's streams
+    if ((rc = lanes.fork())) return rc;
     for (int m = 0; m < plan->n_blocks; ++m) {
       const int in = conv ? plan->c2_in[m] : plan->c1_in[m];
       const int out = conv ? plan->c2_out[m] : plan->c1_out[m];
@@ -671,7 +740,7 @@ int zp_eso2_backward(const zp_plan *plan, int64_t N, int64_t E, const float *gra
       int &nsplit = (conv ? splits_c2 : splits_c1)[m];
       nsplit = 1;
       if (E == 0) {
-        ZP_CUDA(cudaMemsetAsync(G, 0, sizeof(float) * (size_t)out * in, st));
+        ZP_CUDA(cudaMemsetAsync(G, 0, sizeof(float) * (size_t)out * in, lanes.pick(2 * m + 1)));
         continue;
       }
       const ZpGemmTc gd{E, in, out, P, dYm.base, dYm.ld, dYm.plane_stride, 0,
@@ -679,18 +748,19 @@ int zp_eso2_backward(const zp_plan *plan, int64_t N, int64_t E, const float *gra
                         plan->status_dev, 0, 1, 0, 0, plan->fp16, dYm.scale,
                         wscale(plan, ws, conv, m),
                         (conv && plan->fp16) ? ws.scales + kScDht : nullptr};   // max |dht|
-      ZP_TIMED(ZP_K_GEMM_DGRAD, zp_launch_gemm_tc(gd, st));
+      ZP_TIMED(ZP_K_GEMM_DGRAD, zp_launch_gemm_tc(gd, lanes.pick(2 * m)));
       ZpGemmTc gw_{out, in, E, P, dYm.base, dYm.ld, dYm.plane_stride, 1,
                    Xm.base, Xm.ld, Xm.plane_stride, 1, nullptr, G, in,
                    plan->status_dev, 0, 1, plan->g_elems, 0, plan->fp16, dYm.scale, Xm.scale,
                    nullptr};
       gw_.ksplit = zp_gemm_tc_pick_splits(gw_, kMaxWgradSplits);
       nsplit = zp_gemm_tc_splits(gw_);
-      ZP_TIMED(ZP_K_GEMM_WGRAD, zp_launch_gemm_tc(gw_, st));
+      ZP_TIMED(ZP_K_GEMM_WGRAD, zp_launch_gemm_tc(gw_, lanes.pick(2 * m + 1)));
     }
     ZP_TIMED(ZP_K_BIAS_GRAD,
              zp_launch_colsum(E, conv ? plan->c2_out[0] : plan->c1_out[0], dYp,
-                              conv ? gw->c2_b0 : gw->c1_b0, ws.scratch, st));
+                              conv ? gw->c2_b0 : gw->c1_b0, ws.scratch, lanes.pick(2)));
+    if ((rc = lanes.join())) return rc;
   }
   ZP_TIMED(ZP_K_ROTATE_IN_BWD,
            zp_launch_rotate_in_bwd(plan, E, ws.da1, radial, x_node, src, dst, ws.rot,

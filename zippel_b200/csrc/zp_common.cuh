@@ -49,6 +49,14 @@ struct zp_plan {
   int64_t w_elems;                              // bf16 elements of all folded planes
   int64_t c1_goff[ZP_MAX_L + 1], c2_goff[ZP_MAX_L + 1];   // fp32 offsets of the folded gradients
   int64_t g_elems;                              // fp32 elements of one set of folded gradients
+  // Two more streams for launches that do not depend on each other (the per-m products of one
+  // convolution, input- and weight-gradient products): run side by side, the last partial wave
+  // of one persistent kernel is filled by the next kernel's CTAs.  Forked from and joined back
+  // into the caller's stream inside every call; `lane_lock` serialises the enqueueing of calls
+  // that share the plan.
+  cudaStream_t aux_stream[2];
+  cudaEvent_t ev_fork, ev_join[2];
+  void *lane_lock;                              // std::mutex
 };
 
 // thread-local text of the last CUDA error

@@ -8,13 +8,17 @@ do not provide).  Unlike the reference, ``mmax < lmax`` works: the l-major -> m'
 is the rectangular ``[Km, K]`` matrix.
 
 What runs where
-    * edge geometry, Gaussian basis, element embedding, the radial MLP, the envelope and the
-      readout head are small torch ops on the GPU;
+    * the per-edge front end (geometry, Gaussian basis, element embeddings, envelope) is one
+      kernel each way (``EdgeFeatures``); the radial MLP runs on the contraction engine
+      (``TensorCoreLinear``) with fused LayerNorm + SiLU passes (``LayerNormSiLU``);
     * everything per edge and per (l, m, channel) -- gather, Wigner-D rotation, both SO(2)
       convolutions, the gate, rotation back and the scatter onto destination nodes, forward and
       VJP -- is one call into the C ABI (``zp_eso2_forward`` / ``zp_eso2_backward``) through
-      ``EdgeConvFunction``.
-There is no fallback: without the built library and a supported GPU every call raises.
+      ``EdgeConvFunction``;
+    * only the readout head after the node output (invariants, two small dense layers) is torch.
+There is no fallback: without the built library and a supported GPU every call raises, and
+sizes the kernels do not take (``edge_channels`` not a multiple of 4 or above 1024) are refused
+when the block is built.
 """
 
 from __future__ import annotations
@@ -172,7 +176,7 @@ def _f32(t: torch.Tensor) -> torch.Tensor:
 
 
 #: Upper bound on the edges handed to one forward/backward call of the C ABI.  ``None`` sizes it
-#: from the device's free memory (the per-call workspace is ~140 KB per edge at lmax 4 / C 128).
+#: from the device's free memory (the per-call workspace is ~123 KB per edge at lmax 4 / C 128).
 #: Larger graphs are processed as destination-node chunks; the backward then recomputes each
 #: chunk's forward instead of keeping every chunk's activations.
 MAX_EDGES_PER_CALL: int | None = None
@@ -183,12 +187,15 @@ def _edge_budget(plan: Plan, n: int, e: int) -> int:
         return max(1, MAX_EDGES_PER_CALL)
     lib = _lib.load()
     probe = 4096
-    per_edge = (lib.zp_workspace_bytes(plan.handle, n, probe, 1)
-                - lib.zp_workspace_bytes(plan.handle, n, 0, 1)) / probe
+    per_edge = (lib.zp_workspace_bytes(plan.handle, 0, probe, 1)
+                - lib.zp_workspace_bytes(plan.handle, 0, 0, 1)) / probe
     free, _total = torch.cuda.mem_get_info(plan.device)
     # memory the caching allocator holds but is not using can be re-used for the workspace
     free += torch.cuda.memory_reserved(plan.device) - torch.cuda.memory_allocated(plan.device)
-    return max(1024, int(0.5 * free / max(per_edge, 1.0)))
+    budget = max(1024, int(0.5 * free / max(per_edge, 1.0)))
+    # rounded down to a power of two: free memory drifts from call to call, and the chunking of a
+    # graph that is reused (cached per budget) should not be redone for every small change
+    return 1 << (budget.bit_length() - 1)
 
 
 def _abi_forward(plan, n_rows, e, x, ev, cg, sg, rad, en, src, dst, row_ptr, wstruct, out, ws,
@@ -494,6 +501,43 @@ class EdgeFeatures(torch.autograd.Function):
                 g_emb.to(dt[1]) if need_emb else None, None, None, None)
 
 
+def tensor_core_linear(plan: Plan, x: torch.Tensor, weight: torch.Tensor, bias) -> torch.Tensor:
+    """``x @ weight.T + bias`` through ``TensorCoreLinear`` for any sizes: the engine wants inner
+    and outer widths in multiples of 8, so odd ones are zero-padded (and the result sliced)."""
+    n_out, n_in = weight.shape
+    pad_in, pad_out = (-n_in) % 8, (-n_out) % 8
+    if bias is None:
+        bias = weight.new_zeros(n_out)
+    if pad_in or pad_out:
+        x = torch.nn.functional.pad(x, (0, pad_in))
+        weight = torch.nn.functional.pad(weight, (0, pad_in, 0, pad_out))
+        bias = torch.nn.functional.pad(bias, (0, pad_out))
+    y = TensorCoreLinear.apply(plan, x, weight, bias)
+    return y[:, :n_out] if pad_out else y
+
+
+def radial_mlp(plan: Plan, x_edge: torch.Tensor, layers: list) -> torch.Tensor:
+    """A ``Linear / LayerNorm / SiLU`` stack (the reference's ``rad_func``) on the library's
+    kernels.  ``layers``: modules, or for a functional caller tuples ``("linear", w, b)`` /
+    ``("ln_silu", gamma, beta, eps)``."""
+    h, i = x_edge, 0
+    while i < len(layers):
+        m = layers[i]
+        if isinstance(m, tuple):
+            h = (tensor_core_linear(plan, h, m[1], m[2]) if m[0] == "linear"
+                 else LayerNormSiLU.apply(h, m[1], m[2], m[3]))
+            i += 1
+        elif isinstance(m, nn.Linear):
+            h = tensor_core_linear(plan, h, m.weight, m.bias) if h.shape[0] else h.new_zeros(0, m.out_features)
+            i += 1
+        elif isinstance(m, nn.LayerNorm) and i + 1 < len(layers) and isinstance(layers[i + 1], nn.SiLU):
+            h = LayerNormSiLU.apply(h, m.weight, m.bias, m.eps) if h.shape[0] else h
+            i += 2
+        else:
+            raise _lib.ZpError(2, f"radial MLP layer {type(m).__name__} (no kernel for it)")
+    return h
+
+
 def edge_conv(plan: Plan, graph: EdgeGraph, x_node, edge_vec, cos_g, sin_g, radial, env,
               c1_m0: nn.Linear, c1_m, c2_m0: nn.Linear, c2_m) -> torch.Tensor:
     return EdgeConvFunction.apply(plan, graph, x_node, edge_vec, cos_g, sin_g, radial, env,
@@ -517,6 +561,9 @@ class ESO2Block(nn.Module):
         tensor-core passes); "fp32_bf16x3" as three bf16 terms (24 bits, six passes, no scales);
         "bf16" rounds operands to bf16.  Accumulation is fp32 in all three."""
         super().__init__()
+        if cfg.edge_channels % 4 or not 0 < cfg.edge_channels <= 1024:
+            raise ValueError("edge_channels must be a multiple of 4 in [4, 1024]: the front-end and "
+                             "LayerNorm kernels take no other width, and there is no other path")
         self.cfg = cfg
         self.precision = self.PRECISIONS[precision]
         self.layout = Layout.make(cfg.lmax, cfg.mmax)
@@ -549,6 +596,7 @@ class ESO2Block(nn.Module):
             for lin in (*self.c1_m, *self.c2_m):
                 lin.weight.mul_(1.0 / math.sqrt(2.0))
         self.readout = nn.Sequential(nn.Linear(C * (L + 1), C), nn.SiLU(), nn.Linear(C, 1))
+        self._jd_seen: set = set()
         p = float(cfg.envelope_exponent)
         self.env_p, self.env_a = p, -(p + 1) * (p + 2) / 2
         self.env_b, self.env_c = p * (p + 2), -p * (p + 1) / 2
@@ -580,29 +628,11 @@ class ESO2Block(nn.Module):
                         self.precision)
 
     def radial_mlp(self, plan: Plan, x_edge: torch.Tensor) -> torch.Tensor:
-        """rad_func (Linear, LayerNorm, SiLU, ..., Linear; reference eso2_ref.py:164-182) with the
-        library's kernels: every Linear whose sizes are multiples of 8 runs on the contraction
-        engine in the plan's operand format, every LayerNorm + SiLU pair is one fused pass."""
-        h = x_edge
-        mods = list(self.rad_func)
-        i = 0
-        while i < len(mods):
-            m = mods[i]
-            if isinstance(m, nn.Linear):
-                if m.in_features % 8 == 0 and m.out_features % 8 == 0 and h.shape[0] > 0:
-                    h = TensorCoreLinear.apply(plan, h, m.weight, m.bias)
-                else:
-                    h = m(h)
-                i += 1
-            elif (isinstance(m, nn.LayerNorm) and i + 1 < len(mods) and isinstance(mods[i + 1], nn.SiLU)
-                  and m.normalized_shape[0] % 4 == 0 and m.normalized_shape[0] <= 1024
-                  and h.shape[0] > 0):
-                h = LayerNormSiLU.apply(h, m.weight, m.bias, m.eps)
-                i += 2
-            else:
-                h = m(h)
-                i += 1
-        return h
+        """rad_func (Linear, LayerNorm, SiLU, ..., Linear; reference eso2_ref.py:164-182) on the
+        library's kernels: every Linear on the contraction engine in the plan's operand format
+        (widths that are not multiples of 8 are zero-padded to the next one, which changes no
+        value), every LayerNorm + SiLU pair as one fused pass."""
+        return radial_mlp(plan, x_edge, list(self.rad_func))
 
     # -- forward --------------------------------------------------------------------------
     def _edges_to_nodes(self, plan, graph, perm, pos, atomic_numbers, x_node, shifts, cos_gamma_k,
@@ -616,23 +646,13 @@ class ESO2Block(nn.Module):
                 torch.cuda.current_stream(pos.device).wait_event(x_ready)
             return edge_conv(*args)
 
-        if cfg.edge_channels % 4 == 0 and graph.n_edges > 0:
-            # geometry, distance basis, embeddings, envelope and the sorted copies in one pass
-            edge_vec, x_edge, env, cos_s, sin_s = EdgeFeatures.apply(
-                graph, perm.to(torch.int32).contiguous(), self.front_config(), pos, shifts,
-                atomic_numbers, self.elem_emb.weight, self.gauss_offset, cos_gamma_k, sin_gamma_k)
-            radial = self.radial_mlp(plan, x_edge)
-            return conv(plan, graph, x_node, edge_vec, cos_s, sin_s, radial, env,
-                        self.c1_m0, self.c1_m, self.c2_m0, self.c2_m)
-        src, dst = graph.src.long(), graph.dst.long()
-        edge_vec = pos[dst] - pos[src] + shifts[perm]
-        dist = edge_vec.pow(2).sum(-1).clamp_min(1e-24).sqrt()
-        x_edge = torch.cat([self.gaussian_basis(dist), self.elem_emb(atomic_numbers[src]),
-                            self.elem_emb(atomic_numbers[dst])], dim=-1)
+        # geometry, distance basis, embeddings, envelope and the sorted copies in one pass
+        edge_vec, x_edge, env, cos_s, sin_s = EdgeFeatures.apply(
+            graph, perm.to(torch.int32).contiguous(), self.front_config(), pos, shifts,
+            atomic_numbers, self.elem_emb.weight, self.gauss_offset, cos_gamma_k, sin_gamma_k)
         radial = self.radial_mlp(plan, x_edge)
-        env = self.envelope(dist / cfg.cutoff)
-        return conv(plan, graph, x_node, edge_vec, cos_gamma_k[perm], sin_gamma_k[perm],
-                    radial, env, self.c1_m0, self.c1_m, self.c2_m0, self.c2_m)
+        return conv(plan, graph, x_node, edge_vec, cos_s, sin_s, radial, env,
+                    self.c1_m0, self.c1_m, self.c2_m0, self.c2_m)
 
     def node_output(self, pos, atomic_numbers, x_node, edge_index, shifts, cos_gamma_k,
                     sin_gamma_k, graph: EdgeGraph | None = None,
@@ -648,7 +668,13 @@ class ESO2Block(nn.Module):
         forward is recomputed in the backward, so memory stays bounded by one chunk."""
         n = pos.shape[0]
         if graph is None:
+            # new input: node indices are range-checked by the sort, element numbers here (a
+            # caller that passes a prebuilt graph has had both checked when it was built)
             graph = EdgeGraph.build(edge_index, n)
+            if (atomic_numbers.numel() and not torch.cuda.is_current_stream_capturing()
+                    and not bool(((atomic_numbers >= 0)
+                                  & (atomic_numbers < self.cfg.max_num_elements)).all())):
+                raise IndexError(f"atomic_numbers outside [0, {self.cfg.max_num_elements})")
         plan = self.plan(pos.device)
         # radial features and their gradients roughly double the per-edge footprint
         budget = max(1024, _edge_budget(plan, n, graph.n_edges) // 2)
@@ -662,7 +688,6 @@ class ESO2Block(nn.Module):
         from torch.utils.checkpoint import checkpoint
         outs = []
         for c in chunks:
-            c.sub.node_range = (c.n0, c.n1)
             sub_perm = perm[c.e0:c.e1]
 
             def run(pos_, x_, c=c, sub_perm=sub_perm):
@@ -706,7 +731,6 @@ class ESO2Block(nn.Module):
         outs = []
         for c in chunks:
             if len(chunks) > 1:
-                c.sub.node_range = (c.n0, c.n1)
                 sub_graph, sub_perm = c.sub, perm[c.e0:c.e1]
             else:
                 sub_graph, sub_perm = graph, perm
@@ -728,10 +752,26 @@ class ESO2Block(nn.Module):
         node_out = outs[0] if len(outs) == 1 else torch.cat(outs, dim=0)
         return node_out, gx, gpos, gparams
 
+    def _check_jd(self, jd) -> None:
+        """The kernels hold the J matrices shipped with the package; a caller's ``jd`` (the
+        reference passes ``blocks/Jd.pt``) must be those same matrices.  Checked once per list."""
+        if jd is None or id(jd) in self._jd_seen:
+            return
+        want = load_jd(self.cfg.lmax)
+        if len(jd) <= self.cfg.lmax:
+            raise ValueError(f"jd has {len(jd)} matrices, lmax = {self.cfg.lmax} needs {self.cfg.lmax + 1}")
+        for l, w in enumerate(want):
+            got = torch.as_tensor(jd[l]).detach().to("cpu", torch.float64)
+            if got.shape != w.shape or not torch.allclose(got, w, rtol=0.0, atol=1e-6):
+                raise ValueError(f"jd[{l}] differs from the J matrix the kernels were built with "
+                                 "(zippel_b200/data/jd.npz = the reference's blocks/Jd.pt)")
+        self._jd_seen.add(id(jd))
+
     def forward(self, pos, atomic_numbers, x_node, edge_index, shifts, cos_gamma_k, sin_gamma_k,
                 jd=None, graph: EdgeGraph | None = None) -> torch.Tensor:
-        """Scalar E.  ``jd`` is accepted for signature compatibility; the kernels use the J
-        matrices shipped with the package."""
+        """Scalar E.  ``jd`` (the reference's argument) is verified against the J matrices the
+        kernels use; anything else raises ``ValueError``."""
+        self._check_jd(jd)
         node_out = self.node_output(pos, atomic_numbers, x_node, edge_index, shifts,
                                     cos_gamma_k, sin_gamma_k, graph)
         return self.readout(self.node_invariants(node_out)).sum()

@@ -18,7 +18,7 @@ import dataclasses
 import torch
 import torch.nn.functional as F
 
-from ..blocks.eso2 import BlockConfig, EdgeConvFunction, Plan
+from ..blocks.eso2 import BlockConfig, EdgeConvFunction, Plan, radial_mlp
 from ..blocks.eso2_ir import build_force, build_forward
 from ..graph import EdgeGraph
 from ..zippel.ir import BufferType, Program
@@ -112,20 +112,21 @@ def _block_energy(cp: CompiledProgram, env: dict, pos: torch.Tensor):
                        and op.paths[0].operands == (0, 0) and op.paths[0].subscripts == "g,g->g")
     d = dist[:, None] - env["gauss_offset"][0][None, :]
     x_edge = torch.cat([torch.exp(gauss_coeff * d * d), env["emb_src"][perm], env["emb_dst"][perm]], -1)
-    h = x_edge
-    for tag in ("0", "1"):
-        h = F.linear(h, env[f"rad_w{tag}"][0], env[f"rad_b{tag}"][0])
-        h = F.silu(F.layer_norm(h, h.shape[-1:], env[f"rad_g{tag}"][0], env[f"rad_be{tag}"][0], 1e-5))
+    # the radial MLP on the library's kernels, as the module path runs it
     w6 = torch.cat([env[f"rad_wm{m}"][0].reshape(-1, EC) for m in range(mmax + 1)])
     b6 = torch.cat([env[f"rad_bm{m}"][0].reshape(-1) for m in range(mmax + 1)])
-    radial = F.linear(h, w6, b6)
+    plan = Plan.get(L, mmax, C, H, pos.device)
+    layers = []
+    for tag in ("0", "1"):
+        layers += [("linear", env[f"rad_w{tag}"][0], env[f"rad_b{tag}"][0]),
+                   ("ln_silu", env[f"rad_g{tag}"][0], env[f"rad_be{tag}"][0], 1e-5)]
+    radial = radial_mlp(plan, x_edge, [*layers, ("linear", w6, b6)])
     ds = dist / cfg.cutoff
     p = float(cfg.envelope_exponent)
     env_e = 1 + ds ** p * (-(p + 1) * (p + 2) / 2 + ds * (p * (p + 2) - p * (p + 1) / 2 * ds))
     env_e = torch.where(ds < 1, env_e, torch.zeros_like(env_e))
     fold = lambda tag, m: torch.cat([env[f"{tag}_w{m}a"][0].flatten(0, 1).flatten(1),      # noqa: E731
                                      env[f"{tag}_w{m}b"][0].flatten(0, 1).flatten(1)])
-    plan = Plan.get(L, mmax, C, H, pos.device)
     node_out = EdgeConvFunction.apply(
         plan, graph, env["x_node"], edge_vec, env["cos_g"][perm], env["sin_g"][perm], radial, env_e,
         env["c1_w0"][0].flatten(1), env["c1_b0"][0], env["c2_w0"][0].flatten(1), env["c2_b0"][0],

@@ -72,8 +72,13 @@ edge_features_fwd_kernel(int64_t E, zp_front_config cfg, const float *__restrict
     const float t = d - offsets[b];
     row[b] = expf(cfg.gauss_coeff * t * t);
   }
-  const float4 *es = reinterpret_cast<const float4 *>(emb + (size_t)z[i] * EC);
-  const float4 *ed = reinterpret_cast<const float4 *>(emb + (size_t)z[j] * EC);
+  // element numbers come from the caller: one outside the table never becomes an address (it is
+  // clamped to the nearest row; the Python layer rejects such input before it gets here, as
+  // nn.Embedding does in the reference)
+  const int64_t zi = min(max(z[i], (int64_t)0), (int64_t)cfg.n_elements - 1);
+  const int64_t zj = min(max(z[j], (int64_t)0), (int64_t)cfg.n_elements - 1);
+  const float4 *es = reinterpret_cast<const float4 *>(emb + (size_t)zi * EC);
+  const float4 *ed = reinterpret_cast<const float4 *>(emb + (size_t)zj * EC);
   for (int c = lane; c < EC / 4; c += 32) {
     const float4 a = es[c], b = ed[c];
     float *ps = row + NB + 4 * c, *pd = row + NB + EC + 4 * c;

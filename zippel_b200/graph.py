@@ -61,6 +61,7 @@ class EdgeGraph:
         cache = self.__dict__.setdefault("_chunk_cache", {})
         if max_edges in cache:
             return cache[max_edges]
+        cache.clear()                     # one entry: the chunking for the latest budget
         if self.n_edges <= max_edges:
             out = [EdgeChunk(0, self.n_edges, 0, self.n_nodes, self)]
         else:
@@ -83,7 +84,9 @@ class EdgeGraph:
             for n0, n1 in out:
                 e0, e1 = int(rp[n0]), int(rp[n1])
                 ei = torch.stack([self.src[e0:e1].long(), self.dst[e0:e1].long()])
-                pieces.append(EdgeChunk(e0, e1, n0, n1, EdgeGraph.build(ei, self.n_nodes)))
+                sub = EdgeGraph.build(ei, self.n_nodes, validate=False)
+                sub.node_range = (n0, n1)            # all of its edges end in these rows
+                pieces.append(EdgeChunk(e0, e1, n0, n1, sub))
             out = pieces
         cache[max_edges] = out
         return out

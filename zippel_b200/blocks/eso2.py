@@ -509,6 +509,9 @@ def tensor_core_linear(plan: Plan, x: torch.Tensor, weight: torch.Tensor, bias) 
     if bias is None:
         bias = weight.new_zeros(n_out)
     if pad_in or pad_out:
+        # narrow, odd-sized layers keep fp32 accuracy whatever the plan's operand format is
+        # (they cost next to nothing; the bf16 format is meant for the wide products)
+        plan = Plan.get(plan.lmax, plan.mmax, plan.c, plan.h, plan.device, precision=2)
         x = torch.nn.functional.pad(x, (0, pad_in))
         weight = torch.nn.functional.pad(weight, (0, pad_in, 0, pad_out))
         bias = torch.nn.functional.pad(bias, (0, pad_out))

@@ -575,7 +575,10 @@ def large_legs(args, world: int, rank: int) -> dict:
     for i, (name, extra) in enumerate((
             ("cfg3", ["--structures", str(args.structures), "--steps", "2", "--warmup", "1"]),
             ("cfg4", ["--atoms", str(args.large_atoms), "--steps", "1", "--warmup", "1"]))):
-        env = dict(os.environ, MASTER_PORT=str(base_port + 101 * (i + 1)))
+        # a rendezvous of the children's own: rank 0 of them opens the store on another port
+        # (the launcher's "use the agent's store" switch must not reach them)
+        env = {k: v for k, v in os.environ.items() if not k.startswith("TORCHELASTIC")}
+        env["MASTER_PORT"] = str(base_port + 101 * (i + 1))
         cmd = [sys.executable, here, "--workload", name, "--gpus", str(world), "--parity-nodes",
                str(args.parity_nodes), *extra]
         try:
@@ -879,7 +882,7 @@ def main() -> None:
     ap.add_argument("--no-large", action="store_true",
                     help="skip the cfg3 / cfg4 legs that follow the headline measurement")
     ap.add_argument("--large-atoms", type=int, default=200000, help="atoms of the cfg4 leg")
-    ap.add_argument("--large-timeout", type=int, default=300, help="seconds allowed per cfg3 / cfg4 leg")
+    ap.add_argument("--large-timeout", type=int, default=200, help="seconds allowed per cfg3 / cfg4 leg")
     ap.add_argument("--atoms", type=int, default=N_ATOMS,
                     help="atoms per GPU; anything but the default is a profiling-size run, "
                          "not the benchmark workload")

@@ -4,6 +4,8 @@
 #include <cuda_runtime.h>
 #include <stdint.h>
 
+#include <mutex>
+
 #include "zippel_b200.h"
 #include "zp_planes.cuh"
 
@@ -83,6 +85,27 @@ int64_t &zp_launch_counter();
       return ZP_ERR_CUDA;                               \
     }                                                   \
   } while (0)
+
+// A kernel's raised dynamic shared-memory limit is an attribute of the function ON a device, so
+// "already raised" is remembered per device ordinal (one ZpSmemOptIn per call site, under a lock:
+// plans on several devices and several host threads may share the process).
+struct ZpSmemOptIn {
+  std::mutex lock;
+  size_t allowed[64];
+  ZpSmemOptIn() { for (size_t &a : allowed) a = 48 * 1024; }
+};
+template <typename Kernel>
+int zp_ensure_smem(Kernel kernel, size_t bytes, ZpSmemOptIn &state) {
+  int dev = 0;
+  ZP_CUDA(cudaGetDevice(&dev));
+  if (dev < 0 || dev >= 64) return ZP_ERR_UNSUPPORTED;
+  std::lock_guard<std::mutex> hold(state.lock);
+  if (bytes > state.allowed[dev]) {
+    ZP_CUDA(cudaFuncSetAttribute(kernel, cudaFuncAttributeMaxDynamicSharedMemorySize, (int)bytes));
+    state.allowed[dev] = bytes;
+  }
+  return ZP_OK;
+}
 
 static inline int64_t zp_ceil_div(int64_t a, int64_t b) { return (a + b - 1) / b; }
 static inline size_t zp_align_up(size_t x, size_t a) { return (x + a - 1) / a * a; }

@@ -411,12 +411,8 @@ int zp_neighbors_fill(const double *pos, int64_t N, double box, double cutoff, i
   cudaStream_t st = (cudaStream_t)stream;
   if (N > 0) {
     const size_t smem = sizeof(Hit) * kHitCap * kWarpsPerBlock;
-    static bool configured = false;
-    if (!configured) {
-      ZP_CUDA(cudaFuncSetAttribute(fill_kernel, cudaFuncAttributeMaxDynamicSharedMemorySize,
-                                   (int)smem));
-      configured = true;
-    }
+    static ZpSmemOptIn opt_in;
+    if (int rc_ = zp_ensure_smem(fill_kernel, smem, opt_in)) return rc_;
     fill_kernel<<<(unsigned)zp_ceil_div(N, kWarpsPerBlock), 32 * kWarpsPerBlock, smem, st>>>(
         N, pos, g, w.cell_start, w.cell_atoms, max_neighbors, row_ptr, E, edge_index, shifts,
         w.flags);

@@ -239,12 +239,8 @@ int zp_layernorm_silu_backward(int64_t rows, int width, const float *x, const fl
   float *partial = static_cast<float *>(work);
 #define CALL(G)                                                                                 \
   do {                                                                                          \
-    static bool configured = false;                                                             \
-    if (!configured) {                                                                          \
-      ZP_CUDA(cudaFuncSetAttribute(ln_silu_bwd_kernel<G>,                                       \
-                                   cudaFuncAttributeMaxDynamicSharedMemorySize, 65536));        \
-      configured = true;                                                                        \
-    }                                                                                           \
+    static ZpSmemOptIn opt_in;                                                                  \
+    if (int rc_ = zp_ensure_smem(ln_silu_bwd_kernel<G>, 65536, opt_in)) return rc_;             \
     ln_silu_bwd_kernel<G><<<blocks, 32 * kWarps, smem, st>>>(rows, width, x, gamma, beta, mean, \
                                                              rstd, dy, dx, partial);           \
   } while (0)

@@ -710,11 +710,8 @@ int zp_launch_rotate_back_scatter(const zp_plan *p, int64_t N, const float *y, c
 #define CALL(LM)                                                                               \
   {                                                                                            \
     auto kern = vec == 4 ? rotate_back_scatter_kernel<LM, 4> : rotate_back_scatter_kernel<LM, 2>; \
-    static size_t allowed = 48 * 1024;     /* per instantiation: raise the limit once */         \
-    if (smem > allowed) {                                                                      \
-      ZP_CUDA(cudaFuncSetAttribute(kern, cudaFuncAttributeMaxDynamicSharedMemorySize, (int)smem)); \
-      allowed = smem;                                                                          \
-    }                                                                                          \
+    static ZpSmemOptIn opt_in;             /* per instantiation and device */                    \
+    if (int rc_ = zp_ensure_smem(kern, smem, opt_in)) return rc_;                              \
     kern<<<grid, 32 * kBackWarps, smem, st>>>(t, N, y, env, rot, row_ptr, node_out);           \
   }
   ZP_DISPATCH_LMAX(t.lmax, CALL)
@@ -764,12 +761,8 @@ int zp_launch_rotate_in_bwd(const zp_plan *p, int64_t E, const float *da1, const
   const size_t smem = ((size_t)(epb + nw) * t.nnz_pad + (size_t)nw * stage_rows * 128) * sizeof(float);
 #define CALL(LM)                                                                               \
   {                                                                                            \
-    static size_t allowed = 48 * 1024;       /* per instantiation: raise the limit once */       \
-    if (smem > allowed) {                                                                      \
-      ZP_CUDA(cudaFuncSetAttribute(rotate_in_bwd_kernel<LM>,                                   \
-                                   cudaFuncAttributeMaxDynamicSharedMemorySize, (int)smem));   \
-      allowed = smem;                                                                          \
-    }                                                                                          \
+    static ZpSmemOptIn opt_in;               /* per instantiation and device */                  \
+    if (int rc_ = zp_ensure_smem(rotate_in_bwd_kernel<LM>, smem, opt_in)) return rc_;          \
     rotate_in_bwd_kernel<LM><<<grid, 32 * nw, smem, st>>>(t, E, W, da1, radial, x, src, dst,   \
                                                           rot, grad_radial, du_both, grad_rot); \
   }

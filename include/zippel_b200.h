@@ -216,6 +216,36 @@ int zp_eso2_backward(const zp_plan *plan, int64_t n_nodes, int64_t n_edges,
                      const zp_weight_grads *gw, void *workspace, size_t workspace_bytes,
                      void *stream);
 
+/* The edge convolution with the LAST dense layer of the radial MLP inside the call
+ * (rad_func[6] of blocks/eso2_ref.py:169-182, the layer blocks/eso2_ir.py:353-358, 423-429 split per
+ * m): instead of radial [E, R] the caller passes the layer's input h_rad [E, edge_channels], its
+ * weight rad_w [R, edge_channels] and bias rad_b [R].  The call forms radial in its workspace, takes
+ * its largest magnitude from the product's epilogue instead of scanning it, and in the backward
+ * hands the gradient of radial to the layer's VJP as operand planes, so neither radial nor its
+ * gradient is read back for a magnitude scan or a format change; the backward returns
+ * grad_h_rad [E, edge_channels], grad_rad_w and grad_rad_b instead of grad_radial.
+ * edge_channels: a multiple of 8.  Workspace: zp_workspace_bytes_radial (modes as
+ * zp_workspace_bytes).  keep_for_backward = 0 behaves like zp_eso2_forward_inference.            */
+size_t zp_workspace_bytes_radial(const zp_plan *plan, int64_t n_nodes, int64_t n_edges,
+                                 int edge_channels, int with_backward);
+int zp_eso2_forward_radial(const zp_plan *plan, int64_t n_nodes, int64_t n_edges,
+                           const float *x_node, const float *edge_vec, const float *cos_g,
+                           const float *sin_g, const float *h_rad, const float *rad_w,
+                           const float *rad_b, int edge_channels, const float *env,
+                           const int32_t *src, const int32_t *dst, const int32_t *row_ptr,
+                           const zp_weights *w, float *node_out, void *workspace,
+                           size_t workspace_bytes, int keep_for_backward, void *stream);
+int zp_eso2_backward_radial(const zp_plan *plan, int64_t n_nodes, int64_t n_edges,
+                            const float *grad_node_out, const float *x_node,
+                            const float *edge_vec, const float *cos_g, const float *sin_g,
+                            const float *h_rad, const float *rad_w, const float *rad_b,
+                            int edge_channels, const float *env, const int32_t *src,
+                            const int32_t *dst, const int32_t *row_ptr, const int32_t *perm_src,
+                            const int32_t *row_ptr_src, const zp_weights *w, float *grad_x_node,
+                            float *grad_edge_vec, float *grad_h_rad, float *grad_rad_w,
+                            float *grad_rad_b, float *grad_env, const zp_weight_grads *gw,
+                            void *workspace, size_t workspace_bytes, void *stream);
+
 /* The contraction engine on its own (no reference counterpart: the reference calls
  * torch.nn.functional.linear, blocks/eso2_ref.py:272,286).  Exposed for tests and benchmarks.
  * zp_split_planes writes an fp32 matrix [rows, cols] (row stride ld_in) as `planes` 16-bit

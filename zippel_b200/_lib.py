@@ -67,6 +67,12 @@ SIGNATURES = {
                                                                           _P, _SZ, _P]),
     "zp_eso2_backward": (C.c_int, [_P, _I64, _I64] + [_P] * 12 + [C.POINTER(ZpWeights)]
                          + [_P] * 4 + [C.POINTER(ZpWeights), _P, _SZ, _P]),
+    "zp_workspace_bytes_radial": (_SZ, [_P, _I64, _I64, C.c_int, C.c_int]),
+    "zp_eso2_forward_radial": (C.c_int, [_P, _I64, _I64] + [_P] * 7 + [C.c_int] + [_P] * 4
+                               + [C.POINTER(ZpWeights), _P, _P, _SZ, C.c_int, _P]),
+    "zp_eso2_backward_radial": (C.c_int, [_P, _I64, _I64] + [_P] * 8 + [C.c_int] + [_P] * 6
+                                + [C.POINTER(ZpWeights)] + [_P] * 6
+                                + [C.POINTER(ZpWeights), _P, _SZ, _P]),
     "zp_split_planes": (C.c_int, [_I64, _I64, _P, _I64, _P, _I64, _I64, C.c_int, _P]),
     "zp_gemm_planes": (C.c_int, [_P, _I64, _I64, _I64, C.c_int, _P, _I64, _I64, C.c_int, _P, _I64,
                                  _I64, C.c_int, _P, _P, _I64, C.c_int, C.c_int, _I64, C.c_int,

@@ -155,11 +155,17 @@ class Plan:
                    "zp_plan_device_status")
         return st.value
 
-    def workspace(self, n: int, e: int, with_backward: bool, inference: bool = False) -> torch.Tensor:
+    def workspace(self, n: int, e: int, with_backward: bool, inference: bool = False,
+                  edge_channels: int = 0) -> torch.Tensor:
         """Workspace of one forward (+ backward) call over ``e`` edges and ``n`` node rows;
-        ``inference``: for ``zp_eso2_forward_inference`` (nothing kept for a backward)."""
+        ``inference``: for ``zp_eso2_forward_inference`` (nothing kept for a backward);
+        ``edge_channels`` > 0: for the entry points that run the last radial layer themselves."""
         mode = 1 if with_backward else (2 if inference else 0)
-        nbytes = _lib.load().zp_workspace_bytes(self.handle, n, e, mode)
+        lib = _lib.load()
+        nbytes = (lib.zp_workspace_bytes_radial(self.handle, n, e, edge_channels, mode)
+                  if edge_channels else lib.zp_workspace_bytes(self.handle, n, e, mode))
+        if nbytes == 0 and edge_channels:
+            raise _lib.ZpError(2, "zp_workspace_bytes_radial")
         return torch.empty(max(nbytes, 16), dtype=torch.uint8, device=self.device)
 
 
@@ -199,11 +205,21 @@ def _edge_budget(plan: Plan, n: int, e: int) -> int:
 
 
 def _abi_forward(plan, n_rows, e, x, ev, cg, sg, rad, en, src, dst, row_ptr, wstruct, out, ws,
-                 inference: bool = False):
-    """``inference``: nothing is kept for a backward (``zp_eso2_forward_inference``; ``ws`` sized
-    for it)."""
+                 inference: bool = False, layer=None):
+    """``inference``: nothing is kept for a backward (``ws`` sized for that).  ``layer`` =
+    ``(rad_w, rad_b)``: ``rad`` is then the INPUT of the last radial layer, which the call runs
+    itself (``zp_eso2_forward_radial``)."""
     st = torch.cuda.current_stream().cuda_stream
     lib = _lib.load()
+    if layer is not None:
+        rw, rb = layer
+        _lib.check(lib.zp_eso2_forward_radial(
+            plan.handle, n_rows, e, x.data_ptr(), ev.data_ptr(), cg.data_ptr(), sg.data_ptr(),
+            rad.data_ptr(), rw.data_ptr(), rb.data_ptr(), rw.shape[1], en.data_ptr(),
+            src.data_ptr(), dst.data_ptr(), row_ptr.data_ptr(), ctypes.byref(wstruct),
+            out.data_ptr(), ws.data_ptr(), ws.numel(), 0 if inference else 1, st),
+            "zp_eso2_forward_radial")
+        return
     fn = lib.zp_eso2_forward_inference if inference else lib.zp_eso2_forward
     _lib.check(fn(
         plan.handle, n_rows, e, x.data_ptr(), ev.data_ptr(), cg.data_ptr(), sg.data_ptr(),
@@ -213,11 +229,25 @@ def _abi_forward(plan, n_rows, e, x, ev, cg, sg, rad, en, src, dst, row_ptr, wst
 
 
 def _abi_backward(plan, n, e, g_ptr: int, x, ev, cg, sg, rad, en, sub: EdgeGraph, wstruct, gx, gev,
-                  grad, gen, gstruct, ws):
+                  grad, gen, gstruct, ws, layer=None):
     """``g_ptr``: address of row 0 of grad_node_out.  The kernels read it only at the rows of the
-    edges' destinations, so a caller holding rows n0:n1 alone passes its base minus n0 rows."""
+    edges' destinations, so a caller holding rows n0:n1 alone passes its base minus n0 rows.
+    ``layer`` = ``(rad_w, rad_b, grad_rad_w, grad_rad_b)``: ``rad`` / ``grad`` are the input of
+    the last radial layer and its gradient (``zp_eso2_backward_radial``)."""
     st = torch.cuda.current_stream().cuda_stream
-    _lib.check(_lib.load().zp_eso2_backward(
+    lib = _lib.load()
+    if layer is not None:
+        rw, rb, grw, grb = layer
+        _lib.check(lib.zp_eso2_backward_radial(
+            plan.handle, n, e, g_ptr, x.data_ptr(), ev.data_ptr(), cg.data_ptr(), sg.data_ptr(),
+            rad.data_ptr(), rw.data_ptr(), rb.data_ptr(), rw.shape[1], en.data_ptr(),
+            sub.src.data_ptr(), sub.dst.data_ptr(), sub.row_ptr.data_ptr(),
+            sub.perm_src.data_ptr(), sub.row_ptr_src.data_ptr(), ctypes.byref(wstruct),
+            gx.data_ptr(), gev.data_ptr(), grad.data_ptr(), grw.data_ptr(), grb.data_ptr(),
+            gen.data_ptr(), ctypes.byref(gstruct), ws.data_ptr(), ws.numel(), st),
+            "zp_eso2_backward_radial")
+        return
+    _lib.check(lib.zp_eso2_backward(
         plan.handle, n, e, g_ptr, x.data_ptr(), ev.data_ptr(), cg.data_ptr(),
         sg.data_ptr(), rad.data_ptr(), en.data_ptr(), sub.src.data_ptr(), sub.dst.data_ptr(),
         sub.row_ptr.data_ptr(), sub.perm_src.data_ptr(), sub.row_ptr_src.data_ptr(),
@@ -230,21 +260,31 @@ class EdgeConvFunction(torch.autograd.Function):
 
     Per-edge inputs are in the graph's destination-sorted order.  Differentiable w.r.t. x_node,
     edge_vec (through the rotation), radial, env and the SO(2) weights; first order only.
+    With ``rad_w`` / ``rad_b`` given (weight [R, EC] and bias [R] of the radial MLP's last layer),
+    ``radial`` is that layer's INPUT [E, EC] and the layer runs inside the kernel path, forward
+    and VJP (the gradients then go to the input, the weight and the bias).
     """
 
     @staticmethod
     def forward(ctx, plan: Plan, graph: EdgeGraph, x_node, edge_vec, cos_g, sin_g, radial, env,
-                c1_w0, c1_b0, c2_w0, c2_b0, *wm):
+                rad_w, rad_b, c1_w0, c1_b0, c2_w0, c2_b0, *wm):
         mmax = plan.mmax
         n, e = graph.n_nodes, graph.n_edges
-        ins = (x_node, edge_vec, cos_g, sin_g, radial, env, c1_w0, c1_b0, c2_w0, c2_b0, *wm)
-        tens = [_f32(t) for t in ins]
-        x, ev, cg, sg, rad, en, w10, b10, w20, b20 = tens[:10]
-        wms = tens[10:]
+        has_layer = rad_w is not None
         s = plan.sizes
+        if not has_layer:        # placeholders keep the argument positions (no gradient flows)
+            rad_w, rad_b = radial.new_zeros(0), radial.new_zeros(0)
+        ins = (x_node, edge_vec, cos_g, sin_g, radial, env, rad_w, rad_b, c1_w0, c1_b0, c2_w0,
+               c2_b0, *wm)
+        tens = [_f32(t) for t in ins]
+        x, ev, cg, sg, rad, en, rw, rb, w10, b10, w20, b20 = tens[:12]
+        wms = tens[12:]
+        layer = (rw, rb) if has_layer else None
+        ec = rw.shape[1] if has_layer else 0
         assert x.shape == (n, s.K, plan.c), (x.shape, (n, s.K, plan.c))
-        assert rad.shape == (e, s.R) and ev.shape == (e, 3) and en.shape == (e,)
-        assert cg.shape == (e, plan.lmax + 1) and sg.shape == cg.shape
+        assert rad.shape == ((e, ec) if has_layer else (e, s.R)) and ev.shape == (e, 3)
+        assert not has_layer or (rw.shape == (s.R, ec) and rb.shape == (s.R,))
+        assert en.shape == (e,) and cg.shape == (e, plan.lmax + 1) and sg.shape == cg.shape
         needs_bwd = any(ctx.needs_input_grad)
         # a graph may carry `node_range = (n0, n1)`: all its edges end in those nodes and only
         # those rows of node_out are wanted (used by the chunked module path)
@@ -257,24 +297,27 @@ class EdgeConvFunction(torch.autograd.Function):
             chunks = ([EdgeChunk(0, e, 0, n, graph)] if rng is not None
                       else graph.chunks(_edge_budget(plan, n, e)))
             if len(chunks) == 1:
-                ws = plan.workspace(n1 - n0, e, needs_bwd, inference=not needs_bwd)
+                ws = plan.workspace(n1 - n0, e, needs_bwd, inference=not needs_bwd, edge_channels=ec)
                 _abi_forward(plan, n1 - n0, e, x, ev, cg, sg, rad, en, graph.src, graph.dst,
-                             graph.row_ptr[n0:], wstruct, out, ws, inference=not needs_bwd)
+                             graph.row_ptr[n0:], wstruct, out, ws, inference=not needs_bwd,
+                             layer=layer)
             else:
                 # the backward recomputes each chunk, so no chunk keeps anything here
                 ws = plan.workspace(max(c.n1 - c.n0 for c in chunks),
-                                    max(c.n_edges for c in chunks), False, inference=True)
+                                    max(c.n_edges for c in chunks), False, inference=True,
+                                    edge_channels=ec)
                 for c in chunks:
                     sl = slice(c.e0, c.e1)
                     _abi_forward(plan, c.n1 - c.n0, c.n_edges, x, ev[sl], cg[sl], sg[sl], rad[sl],
                                  en[sl], c.sub.src, c.sub.dst, c.sub.row_ptr[c.n0:],
-                                 wstruct, out[c.n0:c.n1], ws, inference=True)
+                                 wstruct, out[c.n0:c.n1], ws, inference=True, layer=layer)
                 ws = None
         del keep
         if needs_bwd:
             # the workspace goes through save_for_backward like any activation, so that
             # activation checkpointing can drop it and recompute
             ctx.plan, ctx.graph, ctx.chunks, ctx.has_ws = plan, graph, chunks, ws is not None
+            ctx.has_layer = has_layer
             ctx.save_for_backward(*tens, *([ws] if ws is not None else []))
             ctx.in_dtypes = [t.dtype for t in ins]
         return out.to(x_node.dtype)
@@ -287,12 +330,15 @@ class EdgeConvFunction(torch.autograd.Function):
         ws = tens[-1] if ctx.has_ws else None
         if ctx.has_ws:
             tens = tens[:-1]
-        x, ev, cg, sg, rad, en, w10, b10, w20, b20 = tens[:10]
-        wms = tens[10:]
+        x, ev, cg, sg, rad, en, rw, rb, w10, b10, w20, b20 = tens[:12]
+        wms = tens[12:]
         mmax = plan.mmax
         n, e = graph.n_nodes, graph.n_edges
         g = _f32(grad_out)
         gx, gev, grad, gen = (torch.empty_like(t) for t in (x, ev, rad, en))
+        grw, grb = torch.empty_like(rw), torch.empty_like(rb)
+        layer = (rw, rb, grw, grb) if ctx.has_layer else None
+        ec = rw.shape[1] if ctx.has_layer else 0
         gws = [torch.empty_like(t) for t in (w10, b10, w20, b20, *wms)]
         wstruct, keep = _weights_struct(mmax, w10, b10, wms[:mmax], w20, b20, wms[mmax:])
         gstruct, keep2 = _weights_struct(mmax, gws[0], gws[1], gws[4:4 + mmax], gws[2], gws[3],
@@ -303,13 +349,14 @@ class EdgeConvFunction(torch.autograd.Function):
         with torch.cuda.device(x.device):
             if len(chunks) == 1:
                 _abi_backward(plan, n, e, g_ptr, x, ev, cg, sg, rad, en, graph, wstruct, gx, gev,
-                              grad, gen, gstruct, ws)
+                              grad, gen, gstruct, ws, layer=layer)
             else:
                 # per chunk: recompute its forward into the shared workspace, then its backward;
                 # node and weight gradients add up over chunks, per-edge gradients are slices
                 ws = plan.workspace(max(c.n1 - c.n0 for c in chunks),
-                                    max(c.n_edges for c in chunks), True)
+                                    max(c.n_edges for c in chunks), True, edge_channels=ec)
                 gx_c = torch.empty_like(gx)
+                grw_c, grb_c = torch.empty_like(rw), torch.empty_like(rb)
                 gws_c = [torch.empty_like(t) for t in gws]
                 cstruct, keep3 = _weights_struct(mmax, gws_c[0], gws_c[1], gws_c[4:4 + mmax],
                                                  gws_c[2], gws_c[3], gws_c[4 + mmax:])
@@ -319,18 +366,20 @@ class EdgeConvFunction(torch.autograd.Function):
                     sl = slice(c.e0, c.e1)
                     _abi_forward(plan, c.n1 - c.n0, c.n_edges, x, ev[sl], cg[sl], sg[sl], rad[sl],
                                  en[sl], c.sub.src, c.sub.dst, c.sub.row_ptr[c.n0:], wstruct,
-                                 scratch_out, ws)
+                                 scratch_out, ws, layer=layer[:2] if layer else None)
                     first = i == 0
+                    lay = None if layer is None else (rw, rb, *((grw, grb) if first else (grw_c, grb_c)))
                     _abi_backward(plan, n, c.n_edges, g_ptr, x, ev[sl], cg[sl], sg[sl], rad[sl], en[sl],
                                   c.sub, wstruct, gx if first else gx_c, gev[sl], grad[sl], gen[sl],
-                                  gstruct if first else cstruct, ws)
+                                  gstruct if first else cstruct, ws, layer=lay)
                     if not first:
                         gx.add_(gx_c)
-                        for a_, b_ in zip(gws, gws_c):
+                        for a_, b_ in zip([*gws, grw, grb], [*gws_c, grw_c, grb_c]):
                             a_.add_(b_)
                 del keep3
         del keep, keep2
-        grads = [gx, gev, None, None, grad, gen, *gws]
+        grads = [gx, gev, None, None, grad, gen, grw if ctx.has_layer else None,
+                 grb if ctx.has_layer else None, *gws]
         dts = ctx.in_dtypes
         outs = []
         for i, gr in enumerate(grads):
@@ -542,9 +591,11 @@ def radial_mlp(plan: Plan, x_edge: torch.Tensor, layers: list) -> torch.Tensor:
 
 
 def edge_conv(plan: Plan, graph: EdgeGraph, x_node, edge_vec, cos_g, sin_g, radial, env,
-              c1_m0: nn.Linear, c1_m, c2_m0: nn.Linear, c2_m) -> torch.Tensor:
+              c1_m0: nn.Linear, c1_m, c2_m0: nn.Linear, c2_m, rad_w=None, rad_b=None) -> torch.Tensor:
+    """``rad_w`` / ``rad_b``: see ``EdgeConvFunction`` (``radial`` is then the last radial
+    layer's input)."""
     return EdgeConvFunction.apply(plan, graph, x_node, edge_vec, cos_g, sin_g, radial, env,
-                                  c1_m0.weight, c1_m0.bias, c2_m0.weight, c2_m0.bias,
+                                  rad_w, rad_b, c1_m0.weight, c1_m0.bias, c2_m0.weight, c2_m0.bias,
                                   *[l.weight for l in c1_m], *[l.weight for l in c2_m])
 
 
@@ -653,6 +704,13 @@ class ESO2Block(nn.Module):
         edge_vec, x_edge, env, cos_s, sin_s = EdgeFeatures.apply(
             graph, perm.to(torch.int32).contiguous(), self.front_config(), pos, shifts,
             atomic_numbers, self.elem_emb.weight, self.gauss_offset, cos_gamma_k, sin_gamma_k)
+        last = self.rad_func[-1]
+        if isinstance(last, nn.Linear) and last.in_features % 8 == 0 and graph.n_edges > 0:
+            # the last (widest) radial layer runs inside the edge-convolution call: its output
+            # and that output's gradient never leave the kernel path
+            h_rad = radial_mlp(plan, x_edge, list(self.rad_func)[:-1])
+            return conv(plan, graph, x_node, edge_vec, cos_s, sin_s, h_rad, env,
+                        self.c1_m0, self.c1_m, self.c2_m0, self.c2_m, last.weight, last.bias)
         radial = self.radial_mlp(plan, x_edge)
         return conv(plan, graph, x_node, edge_vec, cos_s, sin_s, radial, env,
                     self.c1_m0, self.c1_m, self.c2_m0, self.c2_m)

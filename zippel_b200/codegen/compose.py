@@ -129,7 +129,7 @@ def _block_energy(cp: CompiledProgram, env: dict, pos: torch.Tensor):
                                      env[f"{tag}_w{m}b"][0].flatten(0, 1).flatten(1)])
     node_out = EdgeConvFunction.apply(
         plan, graph, env["x_node"], edge_vec, env["cos_g"][perm], env["sin_g"][perm], radial, env_e,
-        env["c1_w0"][0].flatten(1), env["c1_b0"][0], env["c2_w0"][0].flatten(1), env["c2_b0"][0],
+        None, None, env["c1_w0"][0].flatten(1), env["c1_b0"][0], env["c2_w0"][0].flatten(1), env["c2_b0"][0],
         *[fold("c1", m) for m in range(1, mmax + 1)], *[fold("c2", m) for m in range(1, mmax + 1)])
     feats = [node_out[:, 0, :]] + [node_out[:, l * l:(l + 1) ** 2, :].pow(2).sum(1)
                                    for l in range(1, L + 1)]

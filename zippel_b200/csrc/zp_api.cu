@@ -58,9 +58,11 @@ bool aligned16(const void *p) { return (reinterpret_cast<uintptr_t>(p) & 15u) ==
 // mode 2: forward alone with fused epilogues -- of h1 only the gate scalars exist, y does not.
 struct Workspace {
   float *rot, *h1, *y, *dht, *da1, *du_src, *grot, *wgrad, *scratch, *scales, *head, *cont;
+  float *radial, *rad_partials;          // radial layer inside the call: its output, dW partials
   int64_t ld_h1;
   int32_t *block_node;
   ZpPlanes a1, ht, dy, dh1;
+  ZpPlanes hr, rw, gr;                   // planes of the layer's input, weight, output gradient
   uint16_t *wfold;
   size_t bytes;
 };
@@ -68,7 +70,11 @@ struct Workspace {
 // slots of the device-side scale array (fp16-plane precision): raw maxima, derived scales, and
 // per weight block {max |W|, scale} from kScWeights on
 enum { kScX = 0, kScRad, kScG, kScH1, kScDht, kScA1, kScHt, kScDy, kScDh1, kScGate,
-       kScMaxNode /* an int */, kScWeights = 16,
+       kScMaxNode /* an int */,
+       // the radial layer run inside the call: {max, scale} of its input and of its weight, max
+       // of conv1's input gradient, scale of the planes of grad_radial
+       kScHr, kScHrScale, kScRw, kScRwScale, kScDa1, kScGrScale,
+       kScWeights = 24,
        kScCount = kScWeights + 4 * (ZP_MAX_L + 1) };
 
 constexpr int kMaxWgradSplits = 8;
@@ -98,7 +104,10 @@ bool can_fuse(const zp_plan *p, int conv) {
   return true;
 }
 
-Workspace carve(const zp_plan *p, int64_t N, int64_t E, int mode, void *base) {
+constexpr int kRadialSplits = 8;         // K splits of the radial layer's weight gradient
+
+// ec > 0: the last layer of the radial MLP (ec -> R) runs inside the call
+Workspace carve(const zp_plan *p, int64_t N, int64_t E, int mode, void *base, int ec = 0) {
   const ZpTables &t = p->t;
   Workspace w;
   std::memset(&w, 0, sizeof(w));
@@ -109,16 +118,17 @@ Workspace carve(const zp_plan *p, int64_t N, int64_t E, int mode, void *base) {
     return ptr;
   };
   auto takef = [&](size_t elems) { return reinterpret_cast<float *>(take(elems * sizeof(float))); };
-  auto takep = [&](int64_t cols) {
+  auto takep_rows = [&](int64_t rows, int64_t cols) {
     ZpPlanes pl;
     pl.ld = round8(cols);
     pl.planes = p->planes;
     pl.fp16 = p->fp16;
     pl.scale = nullptr;
-    pl.plane_stride = (int64_t)zp_align_up((size_t)E * pl.ld, 128);
+    pl.plane_stride = (int64_t)zp_align_up((size_t)rows * pl.ld, 128);
     pl.base = take((size_t)pl.planes * pl.plane_stride * 2);
     return pl;
   };
+  auto takep = [&](int64_t cols) { return takep_rows(E, cols); };
   const size_t e = (size_t)E;
   const bool lean = mode == 2 && can_fuse(p, 0) && can_fuse(p, 1);
   w.rot = takef(e * t.nnz_pad);
@@ -129,6 +139,11 @@ Workspace carve(const zp_plan *p, int64_t N, int64_t E, int mode, void *base) {
   if (!lean) w.y = takef(e * t.Km * t.C);
   w.wfold = reinterpret_cast<uint16_t *>(take((size_t)p->w_elems * 2));
   w.scales = takef(kScCount);
+  if (ec > 0) {
+    w.radial = takef(e * t.R);
+    w.hr = takep(ec);
+    w.rw = takep_rows(t.R, ec);
+  }
   // the partial sums of the rotate-back epilogue live only inside the forward: the backward's own
   // regions start at the same offset and reuse the space
   const size_t off_fwd = off;
@@ -147,13 +162,22 @@ Workspace carve(const zp_plan *p, int64_t N, int64_t E, int mode, void *base) {
     w.du_src = takef(e * 2 * t.K * t.C);
     w.grot = takef(e * t.nnz_pad);
     w.wgrad = takef((size_t)kMaxWgradSplits * p->g_elems);
-    w.scratch = takef((size_t)zp_ceil_div(E > 0 ? E : 1, 128) * (size_t)t.w1_cols);   // column-sum partials
+    // column-sum partials (bias gradients; the widest user is the radial layer's R columns)
+    w.scratch = takef((size_t)zp_ceil_div(E > 0 ? E : 1, 128) *
+                      (size_t)(ec > 0 && t.R > t.w1_cols ? t.R : t.w1_cols));
+    if (ec > 0) {
+      w.gr = takep(t.R);
+      w.rad_partials = takef((size_t)kRadialSplits * t.R * ec);
+    }
   }
   if (p->fp16 && base) {
     w.a1.scale = w.scales + kScA1;
     w.ht.scale = w.scales + kScHt;
     w.dy.scale = w.scales + kScDy;
     w.dh1.scale = w.scales + kScDh1;
+    w.hr.scale = w.scales + kScHrScale;
+    w.rw.scale = w.scales + kScRwScale;
+    w.gr.scale = w.scales + kScGrScale;
   }
   w.bytes = off > end_fwd ? off : end_fwd;
   return w;
@@ -482,23 +506,40 @@ static int check_weights(const zp_plan *p, const zp_weights *w) {
   return ZP_OK;
 }
 
+// The last dense layer of the radial MLP (blocks/eso2_ref.py:169-182, rad_func[6]), when the call
+// runs it itself: radial[E, R] = h[E, ec] w[R, ec]^T + b.
+struct RadialLayer {
+  const float *h, *w, *b;
+  int ec;
+  float *grad_h, *grad_w, *grad_b;       // backward only
+};
+
+static int check_radial_layer(const zp_plan *plan, const RadialLayer *rl, int64_t E, bool backward) {
+  if (!rl->w || !rl->b || (E && !rl->h)) return ZP_ERR_INVALID_ARG;
+  if (rl->ec <= 0 || rl->ec % 8 || plan->t.R % 8) return ZP_ERR_UNSUPPORTED;
+  if (!aligned16(rl->h) || !aligned16(rl->w)) return ZP_ERR_INVALID_ARG;
+  if (backward && (!rl->grad_w || !rl->grad_b || (E && !rl->grad_h))) return ZP_ERR_INVALID_ARG;
+  return ZP_OK;
+}
+
 // keep != 0: everything a following zp_eso2_backward reads is left in the workspace
 static int eso2_forward(const zp_plan *plan, int64_t N, int64_t E, const float *x_node,
                         const float *edge_vec, const float *cos_g, const float *sin_g,
                         const float *radial, const float *env, const int32_t *src,
                         const int32_t *dst, const int32_t *row_ptr, const zp_weights *w,
                         float *node_out, void *workspace, size_t workspace_bytes, void *stream,
-                        int keep) {
+                        int keep, const RadialLayer *rl = nullptr) {
   if (!plan || N < 0 || E < 0) return ZP_ERR_INVALID_ARG;
   if (N == 0) return E == 0 ? ZP_OK : ZP_ERR_INVALID_ARG;
   if (!x_node || !row_ptr || !node_out || !workspace) return ZP_ERR_INVALID_ARG;
-  if (E && (!edge_vec || !cos_g || !sin_g || !radial || !env || !src || !dst))
+  if (E && (!edge_vec || !cos_g || !sin_g || (!radial && !rl) || !env || !src || !dst))
     return ZP_ERR_INVALID_ARG;
   if (!aligned16(x_node) || !aligned16(node_out) || !aligned16(radial) || !aligned16(workspace))
     return ZP_ERR_INVALID_ARG;
   int rc = check_weights(plan, w);
   if (rc) return rc;
-  const Workspace ws = carve(plan, N, E, keep ? 0 : 2, workspace);
+  if (rl && (rc = check_radial_layer(plan, rl, E, false))) return rc;
+  const Workspace ws = carve(plan, N, E, keep ? 0 : 2, workspace, rl ? rl->ec : 0);
   if (workspace_bytes < ws.bytes) return ZP_ERR_WORKSPACE;
   cudaStream_t st = (cudaStream_t)stream;
   Lanes lanes(plan, st);
@@ -506,6 +547,28 @@ static int eso2_forward(const zp_plan *plan, int64_t N, int64_t E, const float *
   const bool fuse1 = can_fuse(plan, 0), fuse2 = can_fuse(plan, 1);
   const bool lean = !keep && fuse1 && fuse2;          // h1 rows and y are never written
 
+  if (rl && E > 0) {
+    // the radial layer: its input and weight as planes, its output into the workspace; the
+    // largest output magnitude (which scales the rotated message) falls out of the epilogue
+    const int ec = rl->ec;
+    if (plan->fp16) {
+      ZP_TIMED(ZP_K_FOLD, zp_launch_absmax(E, ec, rl->h, ec, ws.scales + kScHr, st));
+      ZP_TIMED(ZP_K_FOLD, zp_launch_scale(1.f, ws.scales + kScHr, nullptr, nullptr, 0.f,
+                                          ws.scales + kScHrScale, st));
+      ZP_TIMED(ZP_K_FOLD, zp_launch_absmax(t.R, ec, rl->w, ec, ws.scales + kScRw, st));
+      ZP_TIMED(ZP_K_FOLD, zp_launch_scale(1.f, ws.scales + kScRw, nullptr, nullptr, 0.f,
+                                          ws.scales + kScRwScale, st));
+      ZP_CUDA(cudaMemsetAsync(ws.scales + kScRad, 0, sizeof(float), st));
+    }
+    ZP_TIMED(ZP_K_FOLD, zp_launch_split_planes(E, ec, rl->h, ec, ws.hr, st));
+    ZP_TIMED(ZP_K_FOLD, zp_launch_split_planes(t.R, ec, rl->w, ec, ws.rw, st));
+    const ZpGemmTc g{E, t.R, ec, plan->planes, ws.hr.base, ws.hr.ld, ws.hr.plane_stride, 0,
+                     ws.rw.base, ws.rw.ld, ws.rw.plane_stride, 0, rl->b, ws.radial, t.R,
+                     plan->status_dev, 0, 1, 0, 0, plan->fp16, ws.hr.scale, ws.rw.scale,
+                     plan->fp16 ? ws.scales + kScRad : nullptr};
+    ZP_TIMED(ZP_K_GEMM_FWD, zp_launch_gemm_tc(g, st));
+    radial = ws.radial;
+  }
   if (plan->fp16) {
     // magnitude bounds -> power-of-two scales, all on the device:  |rot row . x| <= sqrt(2l+1) max|x|
     // over every row the edges can name: a caller that asks for the rows of a node range passes
@@ -514,7 +577,8 @@ static int eso2_forward(const zp_plan *plan, int64_t N, int64_t E, const float *
     ZP_TIMED(ZP_K_FOLD, zp_launch_max_index(E, src, dst, max_node, st));
     ZP_TIMED(ZP_K_FOLD, zp_launch_absmax_row_range(x_node, (int64_t)t.K * t.C, nullptr, max_node, N,
                                                    ws.scales + kScX, st));
-    ZP_TIMED(ZP_K_FOLD, zp_launch_absmax(E, t.R, radial, t.R, ws.scales + kScRad, st));
+    if (!rl || E == 0)
+      ZP_TIMED(ZP_K_FOLD, zp_launch_absmax(E, t.R, radial, t.R, ws.scales + kScRad, st));
     ZP_TIMED(ZP_K_FOLD, zp_launch_scale(3.7f, ws.scales + kScX, ws.scales + kScRad, nullptr, 0.f,
                                         ws.scales + kScA1, st));
     ZP_CUDA(cudaMemsetAsync(ws.scales + kScH1, 0, sizeof(float), st));
@@ -655,33 +719,35 @@ int zp_eso2_forward_inference(const zp_plan *plan, int64_t N, int64_t E, const f
                       w, node_out, workspace, workspace_bytes, stream, 0);
 }
 
-int zp_eso2_backward(const zp_plan *plan, int64_t N, int64_t E, const float *grad_node_out,
-                     const float *x_node, const float *edge_vec, const float *cos_g,
-                     const float *sin_g, const float *radial, const float *env,
-                     const int32_t *src, const int32_t *dst, const int32_t *row_ptr,
-                     const int32_t *perm_src, const int32_t *row_ptr_src, const zp_weights *w,
-                     float *grad_x_node, float *grad_edge_vec, float *grad_radial,
-                     float *grad_env, const zp_weight_grads *gw, void *workspace,
-                     size_t workspace_bytes, void *stream) {
+static int eso2_backward(const zp_plan *plan, int64_t N, int64_t E, const float *grad_node_out,
+                         const float *x_node, const float *edge_vec, const float *cos_g,
+                         const float *sin_g, const float *radial, const float *env,
+                         const int32_t *src, const int32_t *dst, const int32_t *row_ptr,
+                         const int32_t *perm_src, const int32_t *row_ptr_src, const zp_weights *w,
+                         float *grad_x_node, float *grad_edge_vec, float *grad_radial,
+                         float *grad_env, const zp_weight_grads *gw, void *workspace,
+                         size_t workspace_bytes, void *stream, const RadialLayer *rl) {
   if (!plan || N < 0 || E < 0) return ZP_ERR_INVALID_ARG;
   if (N == 0) return E == 0 ? ZP_OK : ZP_ERR_INVALID_ARG;
   if (!grad_node_out || !x_node || !row_ptr || !row_ptr_src || !grad_x_node || !workspace || !gw)
     return ZP_ERR_INVALID_ARG;
-  if (E && (!edge_vec || !cos_g || !sin_g || !radial || !env || !src || !dst || !perm_src ||
-            !grad_edge_vec || !grad_radial || !grad_env))
+  if (E && (!edge_vec || !cos_g || !sin_g || (!radial && !rl) || !env || !src || !dst || !perm_src ||
+            !grad_edge_vec || (!grad_radial && !rl) || !grad_env))
     return ZP_ERR_INVALID_ARG;
   if (!gw->c1_w0 || !gw->c1_b0 || !gw->c2_w0 || !gw->c2_b0) return ZP_ERR_INVALID_ARG;
   for (int m = 1; m < plan->n_blocks; ++m)
     if (!gw->c1_wm || !gw->c2_wm || !gw->c1_wm[m - 1] || !gw->c2_wm[m - 1])
       return ZP_ERR_INVALID_ARG;
   if (!aligned16(grad_node_out) || !aligned16(grad_x_node) || !aligned16(grad_radial) ||
-      !aligned16(workspace))
+      !aligned16(workspace))   /* a null grad_radial (radial layer inside the call) is aligned */
     return ZP_ERR_INVALID_ARG;
   int rc = check_weights(plan, w);
   if (rc) return rc;
+  if (rl && (rc = check_radial_layer(plan, rl, E, true))) return rc;
   // (the node count only sizes regions that live inside the forward)
-  const Workspace ws = carve(plan, 0, E, 1, workspace);
+  const Workspace ws = carve(plan, 0, E, 1, workspace, rl ? rl->ec : 0);
   if (workspace_bytes < ws.bytes) return ZP_ERR_WORKSPACE;
+  if (rl) radial = ws.radial;            // left there by the forward
   cudaStream_t st = (cudaStream_t)stream;
   Lanes lanes(plan, st);
   const ZpTables &t = plan->t;
@@ -716,6 +782,7 @@ int zp_eso2_backward(const zp_plan *plan, int64_t N, int64_t E, const float *gra
     const int64_t ldx = conv ? ldh : lda;
     const int cin = conv ? t.H : 2 * t.C, cout = conv ? t.C : t.H;
     if (conv == 0) {
+      if (plan->fp16 && rl) ZP_CUDA(cudaMemsetAsync(ws.scales + kScDa1, 0, sizeof(float), st));
       if (plan->fp16)        // |dh1| <= 1.1 max|dht| max(1, rows * max sigmoid' * max|h1|)
         ZP_TIMED(ZP_K_GATE_BWD,
                  zp_launch_scale(1.1f, ws.scales + kScDht, nullptr, ws.scales + kScGate, 1.f,
@@ -747,7 +814,9 @@ int zp_eso2_backward(const zp_plan *plan, int64_t N, int64_t E, const float *gra
                         Wt, out, (int64_t)out * in, 0, nullptr, dX + xcol, ldx,
                         plan->status_dev, 0, 1, 0, 0, plan->fp16, dYm.scale,
                         wscale(plan, ws, conv, m),
-                        (conv && plan->fp16) ? ws.scales + kScDht : nullptr};   // max |dht|
+                        // max |dht|; max |da1| when the radial layer's gradient needs it
+                        !plan->fp16 ? nullptr : conv ? ws.scales + kScDht
+                                                     : rl ? ws.scales + kScDa1 : nullptr};
       ZP_TIMED(ZP_K_GEMM_DGRAD, zp_launch_gemm_tc(gd, lanes.pick(2 * m)));
       ZpGemmTc gw_{out, in, E, P, dYm.base, dYm.ld, dYm.plane_stride, 1,
                    Xm.base, Xm.ld, Xm.plane_stride, 1, nullptr, G, in,
@@ -762,9 +831,29 @@ int zp_eso2_backward(const zp_plan *plan, int64_t N, int64_t E, const float *gra
                               conv ? gw->c2_b0 : gw->c1_b0, ws.scratch, lanes.pick(2)));
     if ((rc = lanes.join())) return rc;
   }
-  ZP_TIMED(ZP_K_ROTATE_IN_BWD,
-           zp_launch_rotate_in_bwd(plan, E, ws.da1, radial, x_node, src, dst, ws.rot,
-                                   grad_radial, ws.du_src, ws.grot, st));
+  if (rl) {
+    // grad_radial leaves the kernel as operand planes for the layer's VJP; their scale comes from
+    // |grad_radial| <= 2 max|da1| max|rot . x| <= 2 * 3.7 max|da1| max|x|
+    if (plan->fp16)
+      ZP_TIMED(ZP_K_ROTATE_IN_BWD, zp_launch_scale(7.4f, ws.scales + kScDa1, ws.scales + kScX, nullptr,
+                                                   0.f, ws.scales + kScGrScale, st));
+    ZP_TIMED(ZP_K_ROTATE_IN_BWD,
+             zp_launch_rotate_in_bwd(plan, E, ws.da1, radial, x_node, src, dst, ws.rot,
+                                     nullptr, ws.du_src, ws.grot, st, &ws.gr));
+    if (E > 0) {
+      ZP_TIMED(ZP_K_GEMM_WGRAD,
+               zp_linear_backward_planes(plan, E, rl->ec, t.R, ws.hr, ws.rw, ws.gr, rl->grad_h,
+                                         rl->grad_w, rl->grad_b, ws.rad_partials, kRadialSplits,
+                                         ws.scratch, st));
+    } else {
+      ZP_CUDA(cudaMemsetAsync(rl->grad_w, 0, sizeof(float) * (size_t)t.R * rl->ec, st));
+      ZP_CUDA(cudaMemsetAsync(rl->grad_b, 0, sizeof(float) * (size_t)t.R, st));
+    }
+  } else {
+    ZP_TIMED(ZP_K_ROTATE_IN_BWD,
+             zp_launch_rotate_in_bwd(plan, E, ws.da1, radial, x_node, src, dst, ws.rot,
+                                     grad_radial, ws.du_src, ws.grot, st));
+  }
   ZP_TIMED(ZP_K_SRC_REDUCE,
            zp_launch_node_reduce(plan, N, ws.du_src, row_ptr, perm_src, row_ptr_src,
                                  grad_x_node, st));
@@ -773,6 +862,55 @@ int zp_eso2_backward(const zp_plan *plan, int64_t N, int64_t E, const float *gra
   ZP_TIMED(ZP_K_FOLD, zp_launch_unfold_wgrad(plan, ws.wgrad, plan->g_elems, splits_c1, splits_c2,
                                              gw, st));
   return ZP_OK;
+}
+
+int zp_eso2_backward(const zp_plan *plan, int64_t N, int64_t E, const float *grad_node_out,
+                     const float *x_node, const float *edge_vec, const float *cos_g,
+                     const float *sin_g, const float *radial, const float *env,
+                     const int32_t *src, const int32_t *dst, const int32_t *row_ptr,
+                     const int32_t *perm_src, const int32_t *row_ptr_src, const zp_weights *w,
+                     float *grad_x_node, float *grad_edge_vec, float *grad_radial,
+                     float *grad_env, const zp_weight_grads *gw, void *workspace,
+                     size_t workspace_bytes, void *stream) {
+  return eso2_backward(plan, N, E, grad_node_out, x_node, edge_vec, cos_g, sin_g, radial, env, src,
+                       dst, row_ptr, perm_src, row_ptr_src, w, grad_x_node, grad_edge_vec,
+                       grad_radial, grad_env, gw, workspace, workspace_bytes, stream, nullptr);
+}
+
+size_t zp_workspace_bytes_radial(const zp_plan *plan, int64_t n_nodes, int64_t n_edges,
+                                 int edge_channels, int with_backward) {
+  if (!plan || n_nodes < 0 || n_edges < 0 || with_backward < 0 || with_backward > 2 ||
+      edge_channels <= 0 || edge_channels % 8)
+    return 0;
+  return carve(plan, n_nodes, n_edges, with_backward, nullptr, edge_channels).bytes;
+}
+
+int zp_eso2_forward_radial(const zp_plan *plan, int64_t N, int64_t E, const float *x_node,
+                           const float *edge_vec, const float *cos_g, const float *sin_g,
+                           const float *h_rad, const float *rad_w, const float *rad_b,
+                           int edge_channels, const float *env, const int32_t *src,
+                           const int32_t *dst, const int32_t *row_ptr, const zp_weights *w,
+                           float *node_out, void *workspace, size_t workspace_bytes,
+                           int keep_for_backward, void *stream) {
+  const RadialLayer rl{h_rad, rad_w, rad_b, edge_channels, nullptr, nullptr, nullptr};
+  return eso2_forward(plan, N, E, x_node, edge_vec, cos_g, sin_g, nullptr, env, src, dst, row_ptr,
+                      w, node_out, workspace, workspace_bytes, stream, keep_for_backward, &rl);
+}
+
+int zp_eso2_backward_radial(const zp_plan *plan, int64_t N, int64_t E, const float *grad_node_out,
+                            const float *x_node, const float *edge_vec, const float *cos_g,
+                            const float *sin_g, const float *h_rad, const float *rad_w,
+                            const float *rad_b, int edge_channels, const float *env,
+                            const int32_t *src, const int32_t *dst, const int32_t *row_ptr,
+                            const int32_t *perm_src, const int32_t *row_ptr_src,
+                            const zp_weights *w, float *grad_x_node, float *grad_edge_vec,
+                            float *grad_h_rad, float *grad_rad_w, float *grad_rad_b,
+                            float *grad_env, const zp_weight_grads *gw, void *workspace,
+                            size_t workspace_bytes, void *stream) {
+  const RadialLayer rl{h_rad, rad_w, rad_b, edge_channels, grad_h_rad, grad_rad_w, grad_rad_b};
+  return eso2_backward(plan, N, E, grad_node_out, x_node, edge_vec, cos_g, sin_g, nullptr, env, src,
+                       dst, row_ptr, perm_src, row_ptr_src, w, grad_x_node, grad_edge_vec, nullptr,
+                       grad_env, gw, workspace, workspace_bytes, stream, &rl);
 }
 
 }  // extern "C"

@@ -139,10 +139,11 @@ int zp_launch_rotate_grad_out(const zp_plan *p, int64_t E, const float *g, const
                               const ZpPlanes &dy, float *grad_env, float *grad_rot,
                               cudaStream_t st);
 // du_both [E][2][K][C]: per-edge contributions to grad_x of the source (0) and destination (1)
+// grad_radial goes out as fp32 rows [E, R], or (grad_radial_planes given) as operand planes
 int zp_launch_rotate_in_bwd(const zp_plan *p, int64_t E, const float *da1, const float *radial,
                             const float *x, const int32_t *src, const int32_t *dst,
                             const float *rot, float *grad_radial, float *du_both, float *grad_rot,
-                            cudaStream_t st);
+                            cudaStream_t st, const ZpPlanes *grad_radial_planes = nullptr);
 // node_out[n, l^2 + j, c] = sum over the m' rows r of degree l, in table order, of
 //   head[n][rot_off[r] + j][c] + the continuation partials of the 32-edge blocks n's edges reach
 int zp_launch_node_sum(const zp_plan *p, int64_t N, const float *head, const float *cont,
@@ -257,5 +258,11 @@ int zp_launch_unfold_wgrad(const zp_plan *p, const float *partials, int64_t spli
 // (a1_scale maps the bound of a1 to 2^15; wscales: {max, scale} pairs per weight block)
 int zp_launch_conv1_bound(const zp_plan *p, const float *a1_scale, const float *wscales,
                           const float *bias, float *ht_scale, cudaStream_t st);
+// VJP of y = x W^T + b with all operands as planes; `partials`: max_splits * N * K floats,
+// `colsum_scratch`: ceil(M / 128) * N floats (only when db is wanted)
+int zp_linear_backward_planes(const zp_plan *plan, int64_t M, int64_t K, int64_t N,
+                              const ZpPlanes &x, const ZpPlanes &w, const ZpPlanes &dy, float *dx,
+                              float *dw, float *db, float *partials, int max_splits,
+                              float *colsum_scratch, cudaStream_t st);
 int zp_launch_colsum(int64_t rows, int64_t cols, const ZpPlanes &a, float *out, float *scratch,
                      cudaStream_t st);

@@ -67,6 +67,38 @@ int split_scaled(const zp_plan *p, int64_t rows, int64_t cols, const float *in, 
   return zp_launch_split_planes(rows, cols, in, cols, pl, st);
 }
 
+}  // namespace
+
+// The three products of a dense layer's VJP with every operand already in plane form.
+//   dx[M, K] = dy[M, N] W[N, K]        (contraction over N: W as stored is the MN-major operand)
+//   dw[N, K] = dy^T x                  (contraction over the M rows, both operands MN-major,
+//                                       split over CTAs into `partials`, summed in order)
+//   db[N]    = column sums of dy
+int zp_linear_backward_planes(const zp_plan *plan, int64_t M, int64_t K, int64_t N,
+                              const ZpPlanes &x, const ZpPlanes &w, const ZpPlanes &dy, float *dx,
+                              float *dw, float *db, float *partials, int max_splits,
+                              float *colsum_scratch, cudaStream_t st) {
+  int rc;
+  if (dx) {
+    const ZpGemmTc g{M, K, N, plan->planes, dy.base, dy.ld, dy.plane_stride, 0,
+                     w.base, w.ld, w.plane_stride, 1, nullptr, dx, K, plan->status_dev,
+                     0, 1, 0, 0, plan->fp16, dy.scale, w.scale, nullptr};
+    if ((rc = zp_launch_gemm_tc(g, st))) return rc;
+  }
+  ZpGemmTc g{N, K, M, plan->planes, dy.base, dy.ld, dy.plane_stride, 1,
+             x.base, x.ld, x.plane_stride, 1, nullptr, partials, K, plan->status_dev,
+             0, 1, N * K, 0, plan->fp16, dy.scale, x.scale, nullptr};
+  g.ksplit = zp_gemm_tc_pick_splits(g, max_splits);
+  const int splits = zp_gemm_tc_splits(g);
+  if ((rc = zp_launch_gemm_tc(g, st))) return rc;
+  sum_partials_kernel<<<(unsigned)zp_ceil_div(N * K, 256), 256, 0, st>>>(N * K, splits, partials, dw);
+  ZP_LAUNCH_CHECK("sum_partials_kernel");
+  if (db) return zp_launch_colsum(M, N, dy, db, colsum_scratch, st);
+  return ZP_OK;
+}
+
+namespace {
+
 int check(const zp_plan *p, int64_t M, int64_t K, int64_t N) {
   if (!p || M < 0 || K <= 0 || N <= 0) return ZP_ERR_INVALID_ARG;
   if (K % 8 || N % 8) return ZP_ERR_UNSUPPORTED;
@@ -117,23 +149,8 @@ int zp_linear_backward(const zp_plan *plan, int64_t M, int64_t K, int64_t N, con
   if ((rc = split_scaled(plan, M, K, x, lw.x, lw.scales + 0, st))) return rc;
   if ((rc = split_scaled(plan, N, K, w, lw.w, lw.scales + 2, st))) return rc;
   if ((rc = split_scaled(plan, M, N, dy, lw.dy, lw.scales + 4, st))) return rc;
-  if (dx) {      // dx[M, K] = dy[M, N] W[N, K]: contraction over N, W is the MN-major operand
-    const ZpGemmTc g{M, K, N, plan->planes, lw.dy.base, lw.dy.ld, lw.dy.plane_stride, 0,
-                     lw.w.base, lw.w.ld, lw.w.plane_stride, 1, nullptr, dx, K, plan->status_dev,
-                     0, 1, 0, 0, plan->fp16, lw.dy.scale, lw.w.scale, nullptr};
-    if ((rc = zp_launch_gemm_tc(g, st))) return rc;
-  }
-  // dw[N, K] = dy^T x: contraction over the M rows, both operands MN-major, split over CTAs
-  ZpGemmTc g{N, K, M, plan->planes, lw.dy.base, lw.dy.ld, lw.dy.plane_stride, 1,
-             lw.x.base, lw.x.ld, lw.x.plane_stride, 1, nullptr, lw.partials, K, plan->status_dev,
-             0, 1, N * K, 0, plan->fp16, lw.dy.scale, lw.x.scale, nullptr};
-  g.ksplit = zp_gemm_tc_pick_splits(g, kLinSplits);
-  const int splits = zp_gemm_tc_splits(g);
-  if ((rc = zp_launch_gemm_tc(g, st))) return rc;
-  sum_partials_kernel<<<(unsigned)zp_ceil_div(N * K, 256), 256, 0, st>>>(N * K, splits, lw.partials, dw);
-  ZP_LAUNCH_CHECK("sum_partials_kernel");
-  if (db) return zp_launch_colsum(M, N, lw.dy, db, lw.colsum, st);
-  return ZP_OK;
+  return zp_linear_backward_planes(plan, M, K, N, lw.x, lw.w, lw.dy, dx, dw, db, lw.partials,
+                                   kLinSplits, lw.colsum, st);
 }
 
 }  // extern "C"

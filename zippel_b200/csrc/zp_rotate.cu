@@ -450,10 +450,11 @@ struct RotInBwdE {
   // stage: this warp's [Km + radial rows][128] buffer, filled by StageInBwd in level order
   static __device__ __forceinline__ void run(const ZpTables &t, const float *xrow,
                                              const float *stage, const float *rad_e,
-                                             float *grad_e, const float *rot_s, float *part_s,
+                                             float *grad_e, const ZpPlanes &gp, int64_t gp_row,
+                                             float gp_inv, const float *rot_s, float *part_s,
                                              float *du_row, int c2, bool active, int lane) {
-    RotInBwdE<L - 1, LMAX>::run(t, xrow, stage, rad_e, grad_e, rot_s, part_s, du_row, c2, active,
-                                lane);
+    RotInBwdE<L - 1, LMAX>::run(t, xrow, stage, rad_e, grad_e, gp, gp_row, gp_inv, rot_s, part_s,
+                                du_row, c2, active, lane);
     constexpr int n = 2 * L + 1;
     const int C2 = 2 * t.C;
     const int mm = t.mmax < L ? t.mmax : L;
@@ -509,7 +510,10 @@ struct RotInBwdE {
           const float tot = warp_sum_scatter<n>(part, lane, idx);
           if (warp_sum_owner<n>(lane, idx)) part_s[t.rot_off[r] + idx] = tot;
         }
-        if (active) vstore<4>(grad_e + col, gr);
+        if (active) {              // fp32 rows, or operand planes for the radial layer's VJP
+          if (gp.planes) zp_store_planes<4>(gp, gp_row + col, gr, gp_inv);
+          else vstore<4>(grad_e + col, gr);
+        }
       }
     }
     if (active) {
@@ -521,8 +525,9 @@ struct RotInBwdE {
 template <int LMAX>
 struct RotInBwdE<-1, LMAX> {
   static __device__ __forceinline__ void run(const ZpTables &, const float *, const float *,
-                                             const float *, float *, const float *, float *,
-                                             float *, int, bool, int) {}
+                                             const float *, float *, const ZpPlanes &, int64_t,
+                                             float, const float *, float *, float *, int, bool,
+                                             int) {}
 };
 
 // Puts the gradient rows of the edge in flight at once: each lane copies its own four channels of
@@ -565,8 +570,8 @@ rotate_in_bwd_kernel(const __grid_constant__ ZpTables t, int64_t E, int W,
                      const float *__restrict__ da1, const float *__restrict__ radial,
                      const float *__restrict__ x, const int32_t *__restrict__ src,
                      const int32_t *__restrict__ dst, const float *__restrict__ rot,
-                     float *__restrict__ grad_radial, float *__restrict__ du_both,
-                     float *__restrict__ grad_rot) {
+                     float *__restrict__ grad_radial, const ZpPlanes grad_radial_planes,
+                     float *__restrict__ du_both, float *__restrict__ grad_rot) {
   extern __shared__ __align__(16) float smem[];
   const int nw = blockDim.x / 32;
   const int epb = nw / W;
@@ -593,7 +598,8 @@ rotate_in_bwd_kernel(const __grid_constant__ ZpTables t, int64_t E, int W,
     const float *xrow = x + (size_t)node * t.K * t.C + c;
     float *du_row = du_both + ((size_t)e * 2 + half) * t.K * t.C + c;
     RotInBwdE<LMAX, LMAX>::run(t, xrow, stage, radial + (size_t)e * t.R,
-                               grad_radial + (size_t)e * t.R,
+                               grad_radial + (size_t)e * t.R, grad_radial_planes,
+                               e * grad_radial_planes.ld, zp_inv_scale(grad_radial_planes),
                                rot_s + slot * t.nnz_pad, part_all + warp * t.nnz_pad, du_row, c2,
                                active, lane);
   }
@@ -749,7 +755,9 @@ int zp_launch_rotate_grad_out(const zp_plan *p, int64_t E, const float *g, const
 int zp_launch_rotate_in_bwd(const zp_plan *p, int64_t E, const float *da1, const float *radial,
                             const float *x, const int32_t *src, const int32_t *dst,
                             const float *rot, float *grad_radial, float *du_both, float *grad_rot,
-                            cudaStream_t st) {
+                            cudaStream_t st, const ZpPlanes *grad_radial_planes) {
+  ZpPlanes gp{nullptr, 0, 0, 0, 0, nullptr};
+  if (grad_radial_planes) gp = *grad_radial_planes;
   if (E == 0) return ZP_OK;
   const ZpTables &t = p->t;
   const int W = warps_per_edge(t.C / 2);
@@ -764,7 +772,8 @@ int zp_launch_rotate_in_bwd(const zp_plan *p, int64_t E, const float *da1, const
     static ZpSmemOptIn opt_in;               /* per instantiation and device */                  \
     if (int rc_ = zp_ensure_smem(rotate_in_bwd_kernel<LM>, smem, opt_in)) return rc_;          \
     rotate_in_bwd_kernel<LM><<<grid, 32 * nw, smem, st>>>(t, E, W, da1, radial, x, src, dst,   \
-                                                          rot, grad_radial, du_both, grad_rot); \
+                                                          rot, grad_radial, gp, du_both,       \
+                                                          grad_rot);                           \
   }
   ZP_DISPATCH_LMAX(t.lmax, CALL)
 #undef CALL

@@ -291,6 +291,25 @@ int zp_layernorm_silu_backward(int64_t rows, int width, const float *x, const fl
                                const float *dy, float *dx, float *dgamma, float *dbeta,
                                void *work, size_t work_bytes, void *stream);
 
+/* The energy head after the node output and its VJP (readout, blocks/eso2_ref.py:351-362 and
+ * :236-238): rotation invariants of node_out [N, K, C] (the l = 0 row, and per degree l >= 1 the
+ * squared norm over m), Linear((lmax+1)C -> C) with weight w0 [C, (lmax+1)C] and bias b0 [C], SiLU,
+ * Linear(C -> 1) with w1 [C] and b1 [1], summed over the nodes into *energy (device).  The
+ * backward takes dE (*grad_energy, device) and returns the parameter gradients and
+ * grad_node_out [N, K, C], which is the upstream gradient zp_eso2_backward wants in a force
+ * pass.  The hidden layer runs on the contraction engine in the plan's operand format; all sums
+ * over nodes have a fixed order.  `work`: zp_readout_work_bytes() bytes; the backward reads what
+ * the forward left there, so both get the same buffer.                                          */
+size_t zp_readout_work_bytes(const zp_plan *plan, int64_t n_nodes);
+int zp_readout_forward(const zp_plan *plan, int64_t n_nodes, const float *node_out, const float *w0,
+                       const float *b0, const float *w1, const float *b1, float *energy, void *work,
+                       size_t work_bytes, void *stream);
+int zp_readout_backward(const zp_plan *plan, int64_t n_nodes, const float *node_out,
+                        const float *w0, const float *b0, const float *w1, const float *b1,
+                        const float *grad_energy, float *grad_node_out, float *grad_w0,
+                        float *grad_b0, float *grad_w1, float *grad_b1, void *work,
+                        size_t work_bytes, void *stream);
+
 /* Per-edge front end of the block in one pass, and its VJP: geometry (eso2_ref.py:320-321),
  * Gaussian distance basis (:164-168, 323), element embeddings of both atoms (:324-326), envelope
  * (:242-246, 343), and the copy of the roll-angle harmonics into the sorted edge order.  Inputs are

@@ -84,6 +84,9 @@ SIGNATURES = {
     "zp_layernorm_silu_forward": (C.c_int, [_I64, C.c_int, _P, _P, _P, C.c_float, _P, _P, _P, _P]),
     "zp_layernorm_silu_backward": (C.c_int, [_I64, C.c_int, _P, _P, _P, _P, _P, _P, _P, _P, _P, _P,
                                               _SZ, _P]),
+    "zp_readout_work_bytes": (_SZ, [_P, _I64]),
+    "zp_readout_forward": (C.c_int, [_P, _I64] + [_P] * 7 + [_SZ, _P]),
+    "zp_readout_backward": (C.c_int, [_P, _I64] + [_P] * 12 + [_SZ, _P]),
     "zp_edge_features_work_bytes": (_SZ, [C.POINTER(ZpFrontConfig), _I64, _I64]),
     "zp_edge_features_forward": (C.c_int, [C.POINTER(ZpFrontConfig), _I64, _I64] + [_P] * 16 + [_P]),
     "zp_edge_features_backward": (C.c_int, [C.POINTER(ZpFrontConfig), _I64, _I64] + [_P] * 14

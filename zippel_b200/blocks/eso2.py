@@ -15,7 +15,8 @@ What runs where
       convolutions, the gate, rotation back and the scatter onto destination nodes, forward and
       VJP -- is one call into the C ABI (``zp_eso2_forward`` / ``zp_eso2_backward``) through
       ``EdgeConvFunction``;
-    * only the readout head after the node output (invariants, two small dense layers) is torch.
+    * the readout head after the node output (invariants, two dense layers, sum over atoms) is
+      ``Readout`` (``zp_readout_forward`` / ``zp_readout_backward``).
 There is no fallback: without the built library and a supported GPU every call raises, and
 sizes the kernels do not take (``edge_channels`` not a multiple of 4 or above 1024) are refused
 when the block is built.
@@ -550,6 +551,53 @@ class EdgeFeatures(torch.autograd.Function):
                 g_emb.to(dt[1]) if need_emb else None, None, None, None)
 
 
+class Readout(torch.autograd.Function):
+    """E = sum_n Linear(C -> 1)(SiLU(Linear((lmax+1)C -> C)(invariants(node_out[n])))) and its VJP
+    (``zp_readout_forward`` / ``zp_readout_backward``; reference blocks/eso2_ref.py:351-362).
+    The gradient it returns for ``node_out`` is the upstream gradient of the edge convolution's
+    backward in a force evaluation.  First order only."""
+
+    @staticmethod
+    def forward(ctx, plan: Plan, node_out, w0, b0, w1, b1):
+        lib = _lib.load()
+        if not node_out.is_cuda:
+            raise RuntimeError("Readout needs CUDA tensors: there is no CPU path")
+        x, w0f, b0f, w1f, b1f = (_f32(t) for t in (node_out, w0, b0, w1.reshape(-1), b1))
+        n = x.shape[0]
+        nbytes = lib.zp_readout_work_bytes(plan.handle, n)
+        work = torch.empty(max(nbytes, 16), dtype=torch.uint8, device=x.device)
+        energy = torch.empty(1, dtype=torch.float32, device=x.device)
+        with torch.cuda.device(x.device):
+            st = torch.cuda.current_stream().cuda_stream
+            _lib.check(lib.zp_readout_forward(plan.handle, n, x.data_ptr(), w0f.data_ptr(),
+                                              b0f.data_ptr(), w1f.data_ptr(), b1f.data_ptr(),
+                                              energy.data_ptr(), work.data_ptr(), work.numel(), st),
+                       "zp_readout_forward")
+        ctx.plan = plan
+        ctx.shapes = (w1.shape, [t.dtype for t in (node_out, w0, b0, w1, b1)])
+        ctx.save_for_backward(x, w0f, b0f, w1f, b1f, work)
+        return energy.reshape(()).to(node_out.dtype)
+
+    @staticmethod
+    @torch.autograd.function.once_differentiable
+    def backward(ctx, grad_e):
+        lib = _lib.load()
+        x, w0f, b0f, w1f, b1f, work = ctx.saved_tensors
+        n = x.shape[0]
+        ge = _f32(grad_e).reshape(1)
+        gx, gw0, gb0, gw1, gb1 = (torch.empty_like(t) for t in (x, w0f, b0f, w1f, b1f))
+        with torch.cuda.device(x.device):
+            st = torch.cuda.current_stream().cuda_stream
+            _lib.check(lib.zp_readout_backward(
+                ctx.plan.handle, n, x.data_ptr(), w0f.data_ptr(), b0f.data_ptr(), w1f.data_ptr(),
+                b1f.data_ptr(), ge.data_ptr(), gx.data_ptr(), gw0.data_ptr(), gb0.data_ptr(),
+                gw1.data_ptr(), gb1.data_ptr(), work.data_ptr(), work.numel(), st),
+                "zp_readout_backward")
+        w1_shape, dts = ctx.shapes
+        return (None, gx.to(dts[0]), gw0.to(dts[1]), gb0.to(dts[2]),
+                gw1.reshape(w1_shape).to(dts[3]), gb1.to(dts[4]))
+
+
 def tensor_core_linear(plan: Plan, x: torch.Tensor, weight: torch.Tensor, bias) -> torch.Tensor:
     """``x @ weight.T + bias`` through ``TensorCoreLinear`` for any sizes: the engine wants inner
     and outer widths in multiples of 8, so odd ones are zero-padded (and the result sliced)."""
@@ -835,4 +883,11 @@ class ESO2Block(nn.Module):
         self._check_jd(jd)
         node_out = self.node_output(pos, atomic_numbers, x_node, edge_index, shifts,
                                     cos_gamma_k, sin_gamma_k, graph)
-        return self.readout(self.node_invariants(node_out)).sum()
+        return self.energy(node_out)
+
+    def energy(self, node_out: torch.Tensor) -> torch.Tensor:
+        """The readout head on the library's kernels (``Readout``): invariants, two dense layers,
+        sum over atoms."""
+        lin0, lin1 = self.readout[0], self.readout[2]
+        return Readout.apply(self.plan(node_out.device), node_out, lin0.weight, lin0.bias,
+                             lin1.weight, lin1.bias)

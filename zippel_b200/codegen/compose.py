@@ -16,9 +16,8 @@ from __future__ import annotations
 import dataclasses
 
 import torch
-import torch.nn.functional as F
 
-from ..blocks.eso2 import BlockConfig, EdgeConvFunction, Plan, radial_mlp
+from ..blocks.eso2 import BlockConfig, EdgeConvFunction, Plan, Readout, radial_mlp
 from ..blocks.eso2_ir import build_force, build_forward
 from ..graph import EdgeGraph
 from ..zippel.ir import BufferType, Program
@@ -131,10 +130,8 @@ def _block_energy(cp: CompiledProgram, env: dict, pos: torch.Tensor):
         plan, graph, env["x_node"], edge_vec, env["cos_g"][perm], env["sin_g"][perm], radial, env_e,
         None, None, env["c1_w0"][0].flatten(1), env["c1_b0"][0], env["c2_w0"][0].flatten(1), env["c2_b0"][0],
         *[fold("c1", m) for m in range(1, mmax + 1)], *[fold("c2", m) for m in range(1, mmax + 1)])
-    feats = [node_out[:, 0, :]] + [node_out[:, l * l:(l + 1) ** 2, :].pow(2).sum(1)
-                                   for l in range(1, L + 1)]
-    hid = F.silu(F.linear(torch.cat(feats, -1), env["ro_w0"][0], env["ro_b0"][0]))
-    energy = F.linear(hid, env["ro_w1"][0], env["ro_b1"][0]).sum()
+    energy = Readout.apply(plan, node_out, env["ro_w0"][0], env["ro_b0"][0], env["ro_w1"][0],
+                           env["ro_b1"][0])
     return energy, node_out
 
 

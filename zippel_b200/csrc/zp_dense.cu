@@ -330,22 +330,32 @@ fold_planes_kernel(const FoldDesc d, uint16_t *__restrict__ packed, int planes, 
 }
 
 // Sums the `splits` partial folded gradients in order and maps them back to the reference
-// layout: m = 0 copies; m > 0: dWa = F[0,0] + F[1,1], dWb = F[1,0] - F[0,1].
-__global__ void unfold_kernel(int out, int in, int folded, int splits, int64_t split_stride,
-                              const float *__restrict__ f, float *__restrict__ gw) {
-  const int64_t idx = (int64_t)blockIdx.x * blockDim.x + threadIdx.x;
+// layout: m = 0 copies; m > 0: dWa = F[0,0] + F[1,1], dWb = F[1,0] - F[0,1].  All weight blocks
+// of both convolutions in one launch (blockIdx.y = block).
+struct UnfoldDesc {
+  int n;
+  int out[2 * (ZP_MAX_L + 1)], in[2 * (ZP_MAX_L + 1)], folded[2 * (ZP_MAX_L + 1)];
+  int splits[2 * (ZP_MAX_L + 1)];
+  int64_t foff[2 * (ZP_MAX_L + 1)];             // offset of the block's folded gradient
+  float *gw[2 * (ZP_MAX_L + 1)];
+};
+__global__ void unfold_kernel(const UnfoldDesc d, int64_t split_stride, const float *__restrict__ f) {
+  const int b = blockIdx.y;
+  const int out = d.out[b], in = d.in[b], folded = d.folded[b];
   const int kin = folded ? in / 2 : in, half = out / 2;
   const int64_t total = (int64_t)out * kin;
-  if (idx >= total) return;
-  const int c = (int)(idx % kin), row = (int)(idx / kin);
-  float acc = 0.f;
-  for (int s = 0; s < splits; ++s) {
-    const float *fs = f + (size_t)s * split_stride;
-    if (!folded) acc += fs[idx];
-    else if (row < half) acc += fs[(size_t)row * in + c] + fs[(size_t)(half + row) * in + kin + c];
-    else acc += fs[(size_t)row * in + c] - fs[(size_t)(row - half) * in + kin + c];
+  for (int64_t idx = (int64_t)blockIdx.x * blockDim.x + threadIdx.x; idx < total;
+       idx += (int64_t)gridDim.x * blockDim.x) {
+    const int c = (int)(idx % kin), row = (int)(idx / kin);
+    float acc = 0.f;
+    for (int s = 0; s < d.splits[b]; ++s) {
+      const float *fs = f + d.foff[b] + (size_t)s * split_stride;
+      if (!folded) acc += fs[idx];
+      else if (row < half) acc += fs[(size_t)row * in + c] + fs[(size_t)(half + row) * in + kin + c];
+      else acc += fs[(size_t)row * in + c] - fs[(size_t)(row - half) * in + kin + c];
+    }
+    d.gw[b][idx] = acc;
   }
-  gw[idx] = acc;
 }
 
 // column sums in two fixed-order stages.  Stage one: a block of 32 x 8 threads sums 128 rows of
@@ -548,18 +558,22 @@ int zp_launch_fold_weights(const zp_plan *p, const zp_weights *w, void *packed, 
 int zp_launch_unfold_wgrad(const zp_plan *p, const float *partials, int64_t split_stride,
                            const int *splits_c1, const int *splits_c2, const zp_weight_grads *gw,
                            cudaStream_t st) {
+  UnfoldDesc d;
+  d.n = 0;
   for (int conv = 0; conv < 2; ++conv) {
     for (int m = 0; m < p->n_blocks; ++m) {
-      const int out = conv ? p->c2_out[m] : p->c1_out[m], in = conv ? p->c2_in[m] : p->c1_in[m];
-      const float *f = partials + (conv ? p->c2_goff[m] : p->c1_goff[m]);
-      float *g = m == 0 ? (conv ? gw->c2_w0 : gw->c1_w0)
-                        : (conv ? gw->c2_wm[m - 1] : gw->c1_wm[m - 1]);
-      const int64_t total = (int64_t)out * (m > 0 ? in / 2 : in);
-      unfold_kernel<<<(unsigned)zp_ceil_div(total, 256), 256, 0, st>>>(
-          out, in, m > 0, (conv ? splits_c2 : splits_c1)[m], split_stride, f, g);
-      ZP_LAUNCH_CHECK("unfold_kernel");
+      const int b = d.n++;
+      d.out[b] = conv ? p->c2_out[m] : p->c1_out[m];
+      d.in[b] = conv ? p->c2_in[m] : p->c1_in[m];
+      d.folded[b] = m > 0;
+      d.splits[b] = (conv ? splits_c2 : splits_c1)[m];
+      d.foff[b] = conv ? p->c2_goff[m] : p->c1_goff[m];
+      d.gw[b] = m == 0 ? (conv ? gw->c2_w0 : gw->c1_w0)
+                       : (conv ? gw->c2_wm[m - 1] : gw->c1_wm[m - 1]);
     }
   }
+  unfold_kernel<<<dim3(148, d.n), 256, 0, st>>>(d, split_stride, partials);
+  ZP_LAUNCH_CHECK("unfold_kernel");
   return ZP_OK;
 }
 

@@ -166,28 +166,33 @@ edge_features_bwd_node_kernel(int64_t N, zp_front_config cfg, const float *__res
   }
 }
 
-// one block per element: rows of the atoms of that element, in index order.  Atoms are scanned
-// in chunks of blockDim.x: every thread tests one atom, then all threads walk the chunk's flags
-// in shared memory, so the serial part never waits on global memory for the element test.
+// one block per (element, slice of the atoms): rows of the slice's atoms of that element, in
+// index order, into partial[slice][element]; the slices are then added in slice order.  Atoms are
+// scanned in chunks of blockDim.x: every thread tests one atom, then all threads walk the chunk's
+// flags in shared memory, so the serial part never waits on global memory for the element test.
+constexpr int kElemSlices = 8;           // the rows of one element are a serial chain of loads
 __global__ void __launch_bounds__(128)
 edge_features_bwd_elem_kernel(int64_t N, int EC, const int64_t *__restrict__ z,
-                              const float *__restrict__ node_emb, float *__restrict__ g_emb) {
+                              const float *__restrict__ node_emb, float *__restrict__ partial) {
   __shared__ unsigned char mine[128];
   __shared__ int any;
   const int64_t elem = blockIdx.x;
+  const int64_t per = (N + kElemSlices - 1) / kElemSlices;
+  const int64_t lo = blockIdx.y * per, hi = min(N, lo + per);
+  float *g_emb = partial + (size_t)blockIdx.y * gridDim.x * EC;
   float acc[8];                                   // channels c = threadIdx.x + k * blockDim.x
 #pragma unroll
   for (int k = 0; k < 8; ++k) acc[k] = 0.f;
-  for (int64_t n0 = 0; n0 < N; n0 += blockDim.x) {
+  for (int64_t n0 = lo; n0 < hi; n0 += blockDim.x) {
     if (threadIdx.x == 0) any = 0;
     __syncthreads();
     const int64_t n = n0 + threadIdx.x;
-    const bool hit = n < N && z[n] == elem;
+    const bool hit = n < hi && z[n] == elem;
     mine[threadIdx.x] = hit;
     if (hit) any = 1;
     __syncthreads();
     if (any) {
-      const int cnt = (int)min((int64_t)blockDim.x, N - n0);
+      const int cnt = (int)min((int64_t)blockDim.x, hi - n0);
       for (int t = 0; t < cnt; ++t)
         if (mine[t]) {
 #pragma unroll
@@ -206,6 +211,15 @@ edge_features_bwd_elem_kernel(int64_t N, int EC, const int64_t *__restrict__ z,
   }
 }
 
+__global__ void edge_features_elem_sum_kernel(int64_t total, const float *__restrict__ partial,
+                                             float *__restrict__ g_emb) {
+  const int64_t i = (int64_t)blockIdx.x * blockDim.x + threadIdx.x;
+  if (i >= total) return;
+  float s = 0.f;
+  for (int k = 0; k < kElemSlices; ++k) s += partial[(size_t)k * total + i];
+  g_emb[i] = s;
+}
+
 int check_cfg(const zp_front_config *cfg) {
   if (!cfg) return ZP_ERR_INVALID_ARG;
   if (cfg->num_basis < 1 || cfg->edge_channels < 4 || (cfg->edge_channels % 4) ||
@@ -222,7 +236,9 @@ extern "C" {
 size_t zp_edge_features_work_bytes(const zp_front_config *cfg, int64_t n_nodes, int64_t n_edges) {
   if (check_cfg(cfg) || n_nodes < 0 || n_edges < 0) return 0;
   return zp_align_up(sizeof(float) * 3 * (size_t)n_edges, 256) +
-         zp_align_up(sizeof(float) * (size_t)n_nodes * cfg->edge_channels, 256) + 256;
+         zp_align_up(sizeof(float) * (size_t)n_nodes * cfg->edge_channels, 256) +
+         zp_align_up(sizeof(float) * (size_t)kElemSlices * cfg->n_elements * cfg->edge_channels, 256) +
+         256;
 }
 
 int zp_edge_features_forward(const zp_front_config *cfg, int64_t N, int64_t E, const float *pos,
@@ -276,9 +292,16 @@ int zp_edge_features_backward(const zp_front_config *cfg, int64_t N, int64_t E,
       grad_emb ? node_emb : nullptr);
   ZP_LAUNCH_CHECK("edge_features_bwd_node_kernel");
   if (grad_emb) {
-    edge_features_bwd_elem_kernel<<<(unsigned)cfg->n_elements, 128, 0, st>>>(
-        N, cfg->edge_channels, atomic_numbers, node_emb, grad_emb);
+    float *partial = reinterpret_cast<float *>(
+        reinterpret_cast<unsigned char *>(node_emb) +
+        zp_align_up(sizeof(float) * (size_t)N * cfg->edge_channels, 256));
+    const int64_t total = (int64_t)cfg->n_elements * cfg->edge_channels;
+    edge_features_bwd_elem_kernel<<<dim3((unsigned)cfg->n_elements, kElemSlices), 128, 0, st>>>(
+        N, cfg->edge_channels, atomic_numbers, node_emb, partial);
     ZP_LAUNCH_CHECK("edge_features_bwd_elem_kernel");
+    edge_features_elem_sum_kernel<<<(unsigned)zp_ceil_div(total, 256), 256, 0, st>>>(total, partial,
+                                                                                  grad_emb);
+    ZP_LAUNCH_CHECK("edge_features_elem_sum_kernel");
   }
   return ZP_OK;
 }

@@ -263,16 +263,23 @@ __device__ __forceinline__ void bulk_commit() { asm volatile("cp.async.bulk.comm
 __device__ __forceinline__ void bulk_wait_read() {            // shared source may be overwritten
   asm volatile("cp.async.bulk.wait_group.read 0;" ::: "memory");
 }
+__device__ __forceinline__ void bulk_wait_read_but_one() {    // all but the newest group were read
+  asm volatile("cp.async.bulk.wait_group.read 1;" ::: "memory");
+}
 __device__ __forceinline__ void bulk_wait_all() {             // the writes themselves are done
   asm volatile("cp.async.bulk.wait_group 0;" ::: "memory");
 }
 
 // v[b][j]: value at row `row0 + lane`, column `n0 + col_lo + 32 b + j` (scaled, no bias yet).
+// EB = 2: the warp alternates between two block buffers, so one block's store is still being read
+// out of shared memory while the next block is staged (products with a short contraction are
+// bound by their output stores, and one 4 KB block per warp in flight does not cover the latency).
+template <int EB>
 __device__ __forceinline__ void epilogue_store_tma(const GemmParams &p, const CUtensorMap *map_c,
-                                                   float (&v)[4][32], uint8_t *stage, int lane,
+                                                   float (&v)[4][32], uint8_t *stage0, int lane,
                                                    int row0, int n0, int col_lo, int col_hi,
                                                    int split, const float *bias, bool first,
-                                                   float &seen_max) {
+                                                   float &seen_max, uint32_t &blocks_done) {
   if (row0 >= p.M) return;                        // warp-uniform: nothing of this slice exists
   const bool row_ok = row0 + lane < p.M;
   if (!first) {                                   // the tile's previous store must have landed
@@ -285,7 +292,12 @@ __device__ __forceinline__ void epilogue_store_tma(const GemmParams &p, const CU
     if (cc >= col_hi) continue;                   // warp-uniform
     const int n = n0 + cc;
     if (n >= p.N) continue;
-    if (lane == 0) bulk_wait_read();              // the block buffer is free again
+    uint8_t *stage = stage0 + (EB == 2 ? (blocks_done & 1) * kEpiBlockBytes : 0);
+    ++blocks_done;
+    if (lane == 0) {                              // the block buffer is free again
+      if (EB == 2) bulk_wait_read_but_one();
+      else bulk_wait_read();
+    }
     __syncwarp();
 #pragma unroll
     for (int k = 0; k < 8; ++k) {
@@ -506,8 +518,9 @@ __device__ __forceinline__ void epilogue_fused(const GemmParams &p, const CUtens
   }
 }
 
-template <int P, int BK, int STAGES, int BN_CAP>
+template <int P, int BK, int STAGES, int BN_CAP, int EB = 1>
 struct SmemLayout {
+  static constexpr int kEpiBytes = EB * ::kEpiBytes;
   static constexpr int kATile = BM * BK * 2;
   static constexpr int kBTile = BN_CAP * BK * 2;
   static constexpr int kStage = P * (kATile + kBTile);
@@ -536,10 +549,10 @@ __device__ __forceinline__ Work decode_work(const GemmParams &p, int w) {
   return x;
 }
 
-template <int P, int BK, int STAGES, int BN_CAP, int EPI>
+template <int P, int BK, int STAGES, int BN_CAP, int EPI, int EB = 1>
 __device__ __forceinline__ void gemm_tc_body(const CUtensorMap &map_a, const CUtensorMap &map_b,
                                              const CUtensorMap &map_c, const GemmParams &p) {
-  using L = SmemLayout<P, BK, STAGES, BN_CAP>;
+  using L = SmemLayout<P, BK, STAGES, BN_CAP, EB>;
   constexpr int kAccBufs = P == 1 ? 2 : 1;      // accumulation units in flight in TMEM
   extern __shared__ uint8_t smem_raw[];
   uint8_t *smem = reinterpret_cast<uint8_t *>((reinterpret_cast<uintptr_t>(smem_raw) + 1023) &
@@ -667,8 +680,8 @@ __device__ __forceinline__ void gemm_tc_body(const CUtensorMap &map_a, const CUt
     // registers and releases TMEM, so the next tile's MMAs start while it scales and stores.
     const int q = warp & 3;
     const int half = (warp - 2) >> 2;
-    uint8_t *epi_stage = smem + L::kEpiOffset + (warp - 2) * kEpiBlockBytes;
-    uint32_t unit = 0;
+    uint8_t *epi_stage = smem + L::kEpiOffset + (warp - 2) * kEpiBlockBytes * EB;
+    uint32_t unit = 0, blocks_done = 0;
     bool ok = true;
     const float out_scale = (p.scale_a ? *p.scale_a : 1.f) * (p.scale_b ? *p.scale_b : 1.f);
     float seen_max = 0.f, slope_max = 0.f;
@@ -729,8 +742,8 @@ __device__ __forceinline__ void gemm_tc_body(const CUtensorMap &map_a, const CUt
             epilogue_fused<EPI>(p, &map_c, v, epi_stage, lane, row0, x.n0, col_lo, col_hi, bias,
                                 seen_max, slope_max, node, rp_l);
         } else if (L::kTmaEpilogue && p.tma_store) {
-          epilogue_store_tma(p, &map_c, v, epi_stage, lane, row0, x.n0, col_lo, col_hi, x.split,
-                             bias, first, seen_max);
+          epilogue_store_tma<EB>(p, &map_c, v, epi_stage, lane, row0, x.n0, col_lo, col_hi, x.split,
+                                 bias, first, seen_max, blocks_done);
         } else if (row < p.M) {
 #pragma unroll
           for (int b = 0; b < 4; ++b) {
@@ -790,11 +803,11 @@ __device__ __forceinline__ void gemm_tc_body(const CUtensorMap &map_a, const CUt
   }
 }
 
-template <int P, int BK, int STAGES, int BN_CAP>
+template <int P, int BK, int STAGES, int BN_CAP, int EB = 1>
 __global__ void __launch_bounds__(kThreads, 1)
 gemm_tc_kernel(const __grid_constant__ CUtensorMap map_a, const __grid_constant__ CUtensorMap map_b,
                const __grid_constant__ CUtensorMap map_c, const __grid_constant__ GemmParams p) {
-  gemm_tc_body<P, BK, STAGES, BN_CAP, ZP_EPI_NONE>(map_a, map_b, map_c, p);
+  gemm_tc_body<P, BK, STAGES, BN_CAP, ZP_EPI_NONE, EB>(map_a, map_b, map_c, p);
 }
 // the same contraction with a fused epilogue (the epilogue warps hold more live values)
 template <int P, int BK, int STAGES, int BN_CAP, int EPI>
@@ -1040,7 +1053,7 @@ __device__ __forceinline__ void gemm_tc_pair_body(const CUtensorMap &map_a, cons
     const int q = warp & 3;
     const int half = (warp - 2) >> 2;
     uint8_t *epi_stage = smem + L::kEpiOffset + (warp - 2) * kEpiBlockBytes;
-    uint32_t unit = 0;
+    uint32_t unit = 0, blocks_done = 0;
     bool ok = true;
     const float out_scale = (p.scale_a ? *p.scale_a : 1.f) * (p.scale_b ? *p.scale_b : 1.f);
     float seen_max = 0.f, slope_max = 0.f;
@@ -1103,8 +1116,8 @@ __device__ __forceinline__ void gemm_tc_pair_body(const CUtensorMap &map_a, cons
             epilogue_fused<EPI>(p, &map_c, v, epi_stage, lane, row0, x.n0, col_lo, col_hi, bias,
                                 seen_max, slope_max, node, rp_l);
         } else if (L::kTmaEpilogue && p.tma_store) {
-          epilogue_store_tma(p, &map_c, v, epi_stage, lane, row0, x.n0, col_lo, col_hi, x.split,
-                             bias, first, seen_max);
+          epilogue_store_tma<1>(p, &map_c, v, epi_stage, lane, row0, x.n0, col_lo, col_hi, x.split,
+                                bias, first, seen_max, blocks_done);
         } else if (row < p.M) {
 #pragma unroll
           for (int b = 0; b < 4; ++b) {
@@ -1360,13 +1373,14 @@ void fill_params(GemmParams &p, const ZpGemmTc &g, int bk) {
   else p.epi.mode = ZP_EPI_NONE;
 }
 
-template <int P, int BK, int STAGES, int BN_CAP, int EPI>
+template <int P, int BK, int STAGES, int BN_CAP, int EPI, int EB = 1>
 int launch_e(const ZpGemmTc &g, cudaStream_t st) {
-  using L = SmemLayout<P, BK, STAGES, BN_CAP>;
+  using L = SmemLayout<P, BK, STAGES, BN_CAP, EB>;
+  static_assert(EB == 1 || EPI == ZP_EPI_NONE, "two store buffers only in the plain epilogue");
   static_assert(L::kTotal <= 232448, "shared memory budget of one CTA");
   static_assert(EPI == ZP_EPI_NONE || L::kTmaEpilogue, "fused epilogues need the store stage");
   auto kernel = [] {
-    if constexpr (EPI == ZP_EPI_NONE) return gemm_tc_kernel<P, BK, STAGES, BN_CAP>;
+    if constexpr (EPI == ZP_EPI_NONE) return gemm_tc_kernel<P, BK, STAGES, BN_CAP, EB>;
     else return gemm_tc_fused_kernel<P, BK, STAGES, BN_CAP, EPI>;
   }();
   int dev = 0, sms = 148;
@@ -1552,9 +1566,18 @@ int zp_launch_gemm_tc(const ZpGemmTc &g, cudaStream_t st) {
     if (g.planes == 1) return launch<1, 64, 4, 256>(g, st);
     return ZP_ERR_UNSUPPORTED;
   }
-  if (g.planes == 2) return launch<2, 32, 4, 256>(g, st);
+  // a contraction of at most four k-blocks is bound by its output stores: fewer operand stages,
+  // two store buffers per epilogue warp
+  const bool store_bound = !(g.epi && g.epi->mode) && g.ksplit <= 1;
+  if (g.planes == 2) {
+    if (store_bound && g.K <= 128) return launch_e<2, 32, 2, 256, ZP_EPI_NONE, 2>(g, st);
+    return launch<2, 32, 4, 256>(g, st);
+  }
   if (g.planes == 3)
     return g.variant == 1 ? launch<3, 64, 2, 128>(g, st) : launch<3, 32, 3, 256>(g, st);
-  if (g.planes == 1) return launch<1, 64, 4, 256>(g, st);
+  if (g.planes == 1) {
+    if (store_bound && g.K <= 256) return launch_e<1, 64, 2, 256, ZP_EPI_NONE, 2>(g, st);
+    return launch<1, 64, 4, 256>(g, st);
+  }
   return ZP_ERR_UNSUPPORTED;
 }

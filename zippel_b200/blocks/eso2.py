@@ -200,9 +200,11 @@ def _edge_budget(plan: Plan, n: int, e: int) -> int:
     # memory the caching allocator holds but is not using can be re-used for the workspace
     free += torch.cuda.memory_reserved(plan.device) - torch.cuda.memory_allocated(plan.device)
     budget = max(1024, int(0.5 * free / max(per_edge, 1.0)))
-    # rounded down to a power of two: free memory drifts from call to call, and the chunking of a
-    # graph that is reused (cached per budget) should not be redone for every small change
-    return 1 << (budget.bit_length() - 1)
+    # rounded down to four significant bits: free memory drifts from call to call, and the
+    # chunking of a graph that is reused (cached per budget) should not be redone for every
+    # small change
+    step = 1 << max(budget.bit_length() - 4, 0)
+    return budget // step * step
 
 
 def _abi_forward(plan, n_rows, e, x, ev, cg, sg, rad, en, src, dst, row_ptr, wstruct, out, ws,

@@ -573,7 +573,7 @@ def large_legs(args, world: int, rank: int) -> dict:
     here = str(pathlib.Path(__file__).resolve())
     base_port = int(os.environ.get("MASTER_PORT", "29500"))
     for i, (name, extra) in enumerate((
-            ("cfg3", ["--structures", str(args.structures), "--steps", "2", "--warmup", "1"]),
+            ("cfg3", ["--structures", str(args.structures), "--steps", "2", "--warmup", "2"]),
             ("cfg4", ["--atoms", str(args.large_atoms), "--steps", "1", "--warmup", "1"]))):
         # a rendezvous of the children's own: rank 0 of them opens the store on another port
         # (the launcher's "use the agent's store" switch must not reach them)
@@ -719,13 +719,14 @@ def measure_large(workload: str, world: int, rank: int, dev, *, precision: str, 
     torch.cuda.synchronize()
     if world > 1:
         dist.barrier()
-    a_ev, b_ev = torch.cuda.Event(True), torch.cuda.Event(True)
-    a_ev.record()
-    for _ in range(steps):
+    marks = [torch.cuda.Event(True) for _ in range(steps + 1)]
+    marks[0].record()
+    for i in range(steps):
         res = step()
-    b_ev.record()
+        marks[i + 1].record()
     torch.cuda.synchronize()
-    ms = torch.tensor([a_ev.elapsed_time(b_ev) / steps], dtype=torch.float64, device=dev)
+    each = [marks[i].elapsed_time(marks[i + 1]) for i in range(steps)]    # this rank's steps
+    ms = torch.tensor([marks[0].elapsed_time(marks[-1]) / steps], dtype=torch.float64, device=dev)
     edges = torch.tensor([float(e_local)], dtype=torch.float64, device=dev)
     if world > 1:
         dist.all_reduce(ms, op=dist.ReduceOp.MAX)
@@ -740,7 +741,8 @@ def measure_large(workload: str, world: int, rank: int, dev, *, precision: str, 
             parity = sampled_parity(block, cfg, d["pos"], d["atomic_numbers"], d["x_node"], ei, sh, cg,
                                     sg, res[0], r0, r1, parity_nodes, seed=11)
         line = {"workload": workload, "value": edges.item() / (ms.item() * 1e-3), "unit": "edges/s",
-                "n_gpus": world, "steps": steps, "ms_per_step": ms.item(), "precision": precision,
+                "n_gpus": world, "steps": steps, "ms_per_step": ms.item(), "ms_each_step_rank0": each,
+                "precision": precision,
                 "scaling": "strong",
                 "config": {"atoms_total": n if workload == "cfg4" else 200 * structures,
                            "edges_total": edges.item(), "lmax": cfg["lmax"], "mmax": cfg["mmax"],

@@ -717,19 +717,17 @@ __device__ __forceinline__ void gemm_tc_body(const CUtensorMap &map_a, const CUt
             // itself (128 values per thread) leaves little room for staging registers
 #pragma unroll
             for (int h = 0; h < 2; ++h) {
-              uint32_t r[16];
+              // both accumulators' loads are in flight together: one wait per 16 columns
+              uint32_t r[16], r2[16];
               tmem_ld16(t_row + cc + 16 * h, r);
+              if (P != 1) tmem_ld16(t_row + kTmemBuf + cc + 16 * h, r2);
               tmem_ld_wait();
 #pragma unroll
-              for (int j = 0; j < 16; ++j) v[b][16 * h + j] = __uint_as_float(r[j]);
-              if (P != 1) {
-                tmem_ld16(t_row + kTmemBuf + cc + 16 * h, r);
-                tmem_ld_wait();
-#pragma unroll
-                for (int j = 0; j < 16; ++j) v[b][16 * h + j] += __uint_as_float(r[j]);
+              for (int j = 0; j < 16; ++j) {
+                float a = __uint_as_float(r[j]);
+                if (P != 1) a += __uint_as_float(r2[j]);
+                v[b][16 * h + j] = a * out_scale;
               }
-#pragma unroll
-              for (int j = 0; j < 16; ++j) v[b][16 * h + j] *= out_scale;
             }
           }
         }
@@ -1091,19 +1089,17 @@ __device__ __forceinline__ void gemm_tc_pair_body(const CUtensorMap &map_a, cons
             // itself (128 values per thread) leaves little room for staging registers
 #pragma unroll
             for (int h = 0; h < 2; ++h) {
-              uint32_t r[16];
+              // both accumulators' loads are in flight together: one wait per 16 columns
+              uint32_t r[16], r2[16];
               tmem_ld16(t_row + cc + 16 * h, r);
+              if (P != 1) tmem_ld16(t_row + kTmemBuf + cc + 16 * h, r2);
               tmem_ld_wait();
 #pragma unroll
-              for (int j = 0; j < 16; ++j) v[b][16 * h + j] = __uint_as_float(r[j]);
-              if (P != 1) {
-                tmem_ld16(t_row + kTmemBuf + cc + 16 * h, r);
-                tmem_ld_wait();
-#pragma unroll
-                for (int j = 0; j < 16; ++j) v[b][16 * h + j] += __uint_as_float(r[j]);
+              for (int j = 0; j < 16; ++j) {
+                float a = __uint_as_float(r[j]);
+                if (P != 1) a += __uint_as_float(r2[j]);
+                v[b][16 * h + j] = a * out_scale;
               }
-#pragma unroll
-              for (int j = 0; j < 16; ++j) v[b][16 * h + j] *= out_scale;
             }
           }
         }

@@ -381,12 +381,29 @@ def run_ours(args) -> dict | None:
     loss_host = torch.empty((), pin_memory=True)
     d2h = out_host.numel() * 4 + 4
 
+    copy_stream = torch.cuda.Stream(dev)
+
     def e2e_step():
-        t = {k: v.to(dev, non_blocking=True) for k, v in host.items()}
+        # the two [N, K, C] arrays travel on a second stream beside the edge sort, the front end
+        # and the radial MLP (x_node) and beside the forward (the upstream gradient); their
+        # device buffers are allocated on the compute stream, which also outlives their use
+        main = torch.cuda.current_stream(dev)
+        big = ("x_node", "upstream")
+        t = {k: v.to(dev, non_blocking=True) for k, v in host.items() if k not in big}
+        ready = {}
+        for k in big:
+            t[k] = torch.empty(host[k].shape, dtype=host[k].dtype, device=dev)
+        copy_stream.wait_stream(main)
+        with torch.cuda.stream(copy_stream):
+            for k in big:
+                t[k].copy_(host[k], non_blocking=True)
+                ready[k] = torch.cuda.Event()
+                ready[k].record(copy_stream)
         pos = t["pos"].requires_grad_(True)
         x = t["x_node"].requires_grad_(True)
         node_out = block.node_output(pos, t["atomic_numbers"], x, t["edge_index"], t["shifts"],
-                                     t["cos_gamma_k"], t["sin_gamma_k"])
+                                     t["cos_gamma_k"], t["sin_gamma_k"], x_ready=ready["x_node"])
+        main.wait_event(ready["upstream"])
         loss = (node_out * t["upstream"]).sum()
         grads = torch.autograd.grad(loss, [x, pos, *block.parameters()], allow_unused=True)
         if world > 1:

@@ -47,3 +47,16 @@ def test_hbm_bytes_per_step(bench, monkeypatch):
     monkeypatch.delenv("ZP_FUSED_EPILOGUE")
     one_plane = ESO2Block(BlockConfig(**bench.CFG), precision="bf16")
     assert bench.hbm_bytes_per_step(one_plane, n, e)["rotate_in"] == e * (r * 4 + km * 2 * c * 2)
+
+
+def test_chunk_budget_quantisation():
+    """The per-call edge budget keeps four significant bits: stable under small drifts of the
+    free memory, never above the raw budget, never less than 7/8 of it."""
+    from zippel_b200.blocks.eso2 import _quantise_budget
+
+    for raw in (1024, 1025, 60000, 383_999, 384_000, 1_000_003, 6_000_000):
+        q = _quantise_budget(raw)
+        assert q <= raw and q * 8 >= raw * 7
+        assert _quantise_budget(q) == q
+    assert _quantise_budget(700_000) == _quantise_budget(710_000)     # same bucket
+    assert _quantise_budget(15) == 15 and _quantise_budget(1) == 1

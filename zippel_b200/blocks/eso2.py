@@ -199,10 +199,13 @@ def _edge_budget(plan: Plan, n: int, e: int) -> int:
     free, _total = torch.cuda.mem_get_info(plan.device)
     # memory the caching allocator holds but is not using can be re-used for the workspace
     free += torch.cuda.memory_reserved(plan.device) - torch.cuda.memory_allocated(plan.device)
-    budget = max(1024, int(0.5 * free / max(per_edge, 1.0)))
-    # rounded down to four significant bits: free memory drifts from call to call, and the
-    # chunking of a graph that is reused (cached per budget) should not be redone for every
-    # small change
+    return _quantise_budget(max(1024, int(0.5 * free / max(per_edge, 1.0))))
+
+
+def _quantise_budget(budget: int) -> int:
+    """``budget`` rounded down to four significant bits: free memory drifts from call to call,
+    and the chunking of a graph that is reused (cached per budget) should not be redone for
+    every small change.  At most 1/8 of the budget is given up."""
     step = 1 << max(budget.bit_length() - 4, 0)
     return budget // step * step
 

@@ -595,7 +595,7 @@ def large_legs(args, world: int, rank: int) -> dict:
         # a rendezvous of the children's own: rank 0 of them opens the store on another port
         # (the launcher's "use the agent's store" switch must not reach them)
         env = {k: v for k, v in os.environ.items() if not k.startswith("TORCHELASTIC")}
-        env["MASTER_PORT"] = str(base_port + 101 * (i + 1))
+        env["MASTER_PORT"] = str(1024 + (base_port + 101 * (i + 1) - 1024) % 64000)
         cmd = [sys.executable, here, "--workload", name, "--gpus", str(world), "--parity-nodes",
                str(args.parity_nodes), *extra]
         try:

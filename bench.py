@@ -18,6 +18,7 @@ The line printed by rank 0 carries
                copies, CSR build, radial MLP, forward, autograd backward, device->host read,
                recorded once as a CUDA graph (CapturedStep) and replayed per step; `e2e_eager`
                is the same step enqueued from Python every time
+    radial_in_call  the resident step again with the last radial layer (EC -> R) inside the call
     roofline   the dominant kernel class, timed live with CUDA events inside the library
     kernels    per kernel class: ms, launches and share of the step; the HBM-bound classes also
                carry their algorithmic bytes, GB/s and fraction of the measured copy bandwidth
@@ -372,6 +373,31 @@ def run_ours(args) -> dict | None:
         fwd_ms += fa.elapsed_time(fb)
     fwd_ms /= args.steps
 
+    # the same resident step with the LAST radial layer (EC -> R) inside the call: the op takes the
+    # 128-wide hidden activations and that layer's parameters instead of `radial` [E, R]
+    with torch.no_grad():
+        h_rad = block.rad_func[:-1](x_edge).contiguous()
+    last = block.rad_func[-1]
+    runner_r = EdgeConvRunner(block.plan(dev), graph, with_backward=True,
+                              edge_channels=CFG["edge_channels"])
+    runner_r.bind(d["x_node"].contiguous(), edge_vec, cg, sg, h_rad, env,
+                  block.c1_m0.weight.detach(), block.c1_m0.bias.detach(),
+                  [l.weight.detach() for l in block.c1_m], block.c2_m0.weight.detach(),
+                  block.c2_m0.bias.detach(), [l.weight.detach() for l in block.c2_m],
+                  rad_layer=(last.weight.detach().contiguous(), last.bias.detach().contiguous()))
+    for _ in range(3):
+        runner_r.forward(); runner_r.backward(upstream)
+    ra, rb = torch.cuda.Event(True), torch.cuda.Event(True)
+    barrier()
+    rad_ms = 0.0
+    for _ in range(args.steps):
+        flush.zero_()
+        ra.record(); runner_r.forward(); runner_r.backward(upstream); rb.record()
+        rb.synchronize()
+        rad_ms += ra.elapsed_time(rb)
+    rad_ms /= args.steps
+    del runner_r, h_rad
+
     # ---- end to end through the module API from pinned host memory -------------------------
     host = {k: batch[k].pin_memory() for k in ("pos", "x_node", "edge_index", "shifts",
                                                "cos_gamma_k", "sin_gamma_k", "atomic_numbers",
@@ -539,6 +565,11 @@ def run_ours(args) -> dict | None:
                                 "the library's kernels)"},
             "fwd_only": {"value": e / (fwd_ms * 1e-3), "unit": "edges/s (this rank)",
                          "ms_per_step": fwd_ms},
+            "radial_in_call": {"value": e / (rad_ms * 1e-3), "unit": "edges/s (this rank)",
+                               "ms_per_step": rad_ms,
+                               "what": "the resident step with the last radial layer (EC -> R) and "
+                                       "its VJP inside the call (zp_eso2_forward_radial / "
+                                       "zp_eso2_backward_radial); `value` has `radial` precomputed"},
             "wall_ms_per_step_incl_flush": t_wall * 1e3 / args.steps,
             "roofline": roof, "kernels": kernels, "gpu_launches": launches,
             "e2e": {"value": total_edges / e2e_s.item(), "unit": "edges/s",

@@ -321,3 +321,49 @@ def test_streamed_vjp_without_recompute(monkeypatch):
                 assert got_p is None, name
             else:
                 assert rel_l2(got_p, want_p) < 1e-5, name
+
+
+def test_runner_with_the_last_radial_layer_inside_the_call():
+    """`EdgeConvRunner` with `edge_channels` set takes the hidden activations of the radial MLP and
+    the last layer's parameters; results equal the runner fed with `radial` = that layer applied
+    by torch, and the extra gradients equal the layer's VJP of `grad_radial`."""
+    from zippel_b200.graph import EdgeGraph
+    from zippel_b200.runner import EdgeConvRunner
+    cfg = dict(lmax=4, mmax=2, sphere_channels=32, hidden_channels=32, edge_channels=32,
+               num_distance_basis=16, cutoff=5.0)
+    params = orc.init_params(cfg, seed=51)
+    case = random_case(cfg, 40, 900, seed=52)
+    block = make_block(cfg, params)
+    dev = torch.device("cuda")
+    graph = EdgeGraph.build(case["edge_index"].to(dev), 40)
+    e, r = 900, block.plan(dev).sizes.R
+    g = torch.Generator().manual_seed(53)
+    f32 = lambda t: t.to(dev, torch.float32).contiguous()                      # noqa: E731
+    perm = graph.perm64
+    pos = f32(case["pos"])
+    ev = (pos[graph.dst.long()] - pos[graph.src.long()] + f32(case["shifts"])[perm]).contiguous()
+    cg, sg = f32(case["cos_gamma_k"])[perm].contiguous(), f32(case["sin_gamma_k"])[perm].contiguous()
+    h_rad = f32(torch.randn(e, 32, generator=g))
+    rw, rb = f32(torch.randn(r, 32, generator=g) * 0.2), f32(torch.randn(r, generator=g) * 0.1)
+    env = f32(torch.rand(e, generator=g))
+    radial = (h_rad @ rw.T + rb).contiguous()
+    up = f32(case["upstream"])
+    w = (block.c1_m0.weight.detach(), block.c1_m0.bias.detach(),
+         [l.weight.detach() for l in block.c1_m], block.c2_m0.weight.detach(),
+         block.c2_m0.bias.detach(), [l.weight.detach() for l in block.c2_m])
+    a = EdgeConvRunner(block.plan(dev), graph)
+    a.bind(f32(case["x_node"]), ev, cg, sg, radial, env, *w)
+    out_a = a.forward().clone()
+    gx_a, gev_a, grad_a, genv_a, gw_a = a.backward(up)
+    b = EdgeConvRunner(block.plan(dev), graph, edge_channels=32)
+    b.bind(f32(case["x_node"]), ev, cg, sg, h_rad, env, *w, rad_layer=(rw, rb))
+    out_b = b.forward().clone()
+    gx_b, gev_b, gh_b, genv_b, gw_b = b.backward(up)
+    assert rel_l2(out_b, out_a) < 1e-5
+    assert rel_l2(gx_b, gx_a) < 1e-5 and rel_l2(gev_b, gev_a) < 1e-5 and rel_l2(genv_b, genv_a) < 1e-5
+    assert rel_l2(gw_b[0], gw_a[0]) < 1e-5 and rel_l2(gw_b[2][1], gw_a[2][1]) < 1e-5
+    assert rel_l2(gh_b, grad_a @ rw) < 1e-5
+    assert rel_l2(b.grad_rad_w, grad_a.T @ h_rad) < 1e-5
+    assert rel_l2(b.grad_rad_b, grad_a.sum(0)) < 1e-5
+    with pytest.raises(ValueError):
+        a.bind(f32(case["x_node"]), ev, cg, sg, radial, env, *w, rad_layer=(rw, rb))

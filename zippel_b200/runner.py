@@ -18,27 +18,43 @@ from .graph import EdgeGraph
 
 
 class EdgeConvRunner:
-    def __init__(self, plan: Plan, graph: EdgeGraph, with_backward: bool = True):
+    """``edge_channels`` > 0: the last radial layer (edge_channels -> R) runs inside the call
+    (``zp_eso2_forward_radial`` / ``zp_eso2_backward_radial``): ``bind`` then takes that layer's
+    input ``h_rad [E, edge_channels]`` in place of ``radial`` and its weight and bias as
+    ``rad_layer``; the backward returns ``grad_h_rad`` where it otherwise returns ``grad_radial``
+    and fills ``grad_rad_w`` / ``grad_rad_b``."""
+
+    def __init__(self, plan: Plan, graph: EdgeGraph, with_backward: bool = True,
+                 edge_channels: int = 0):
         self.plan, self.graph, self.with_backward = plan, graph, with_backward
+        self.edge_channels = int(edge_channels)
         self.lib = _lib.load()
         n, e, s, dev = graph.n_nodes, graph.n_edges, plan.sizes, plan.device
         f32 = dict(dtype=torch.float32, device=dev)
-        self.ws = plan.workspace(n, e, with_backward, inference=not with_backward)
+        self.ws = plan.workspace(n, e, with_backward, inference=not with_backward,
+                                 edge_channels=self.edge_channels)
         self.node_out = torch.empty(n, s.K, plan.c, **f32)
         if with_backward:
             self.grad_x = torch.empty(n, s.K, plan.c, **f32)
             self.grad_edge_vec = torch.empty(e, 3, **f32)
-            self.grad_radial = torch.empty(e, s.R, **f32)
+            self.grad_radial = torch.empty(e, self.edge_channels or s.R, **f32)
             self.grad_env = torch.empty(e, **f32)
             self.grad_w = None
+            if self.edge_channels:
+                self.grad_rad_w = torch.empty(s.R, self.edge_channels, **f32)
+                self.grad_rad_b = torch.empty(s.R, **f32)
         self._w = self._gw = None
         self._keep = []
+        self.rad_layer = None
 
     def bind(self, x_node, edge_vec, cos_g, sin_g, radial, env, c1_w0, c1_b0, c1_wm, c2_w0,
-             c2_b0, c2_wm):
+             c2_b0, c2_wm, rad_layer=None):
         """Fixes the input tensors (fp32, contiguous, sorted-edge order); no copies are made."""
+        if bool(self.edge_channels) != (rad_layer is not None):
+            raise ValueError("rad_layer=(weight, bias) goes with edge_channels > 0, and only then")
         tens = [x_node, edge_vec, cos_g, sin_g, radial, env, c1_w0, c1_b0, c2_w0, c2_b0,
-                *c1_wm, *c2_wm]
+                *c1_wm, *c2_wm, *(rad_layer or ())]
+        self.rad_layer = tuple(rad_layer) if rad_layer is not None else None
         for t in tens:
             if t.dtype != torch.float32 or not t.is_contiguous() or not t.is_cuda:
                 raise ValueError("EdgeConvRunner.bind needs contiguous fp32 CUDA tensors")
@@ -66,6 +82,15 @@ class EdgeConvRunner:
         x, ev, cg, sg, rad, en = self.inputs
         g = self.graph
         st = torch.cuda.current_stream().cuda_stream
+        if self.rad_layer is not None:
+            rw, rb = self.rad_layer
+            _lib.check(self.lib.zp_eso2_forward_radial(
+                self.plan.handle, g.n_nodes, g.n_edges, x.data_ptr(), ev.data_ptr(), cg.data_ptr(),
+                sg.data_ptr(), rad.data_ptr(), rw.data_ptr(), rb.data_ptr(), self.edge_channels,
+                en.data_ptr(), g.src.data_ptr(), g.dst.data_ptr(), g.row_ptr.data_ptr(),
+                ctypes.byref(self._w), self.node_out.data_ptr(), self.ws.data_ptr(),
+                self.ws.numel(), 1 if self.with_backward else 0, st), "zp_eso2_forward_radial")
+            return self.node_out
         # without a backward nothing is kept: the leaner entry point
         fn = self.lib.zp_eso2_forward if self.with_backward else self.lib.zp_eso2_forward_inference
         _lib.check(fn(
@@ -79,6 +104,19 @@ class EdgeConvRunner:
         x, ev, cg, sg, rad, en = self.inputs
         g = self.graph
         st = torch.cuda.current_stream().cuda_stream
+        if self.rad_layer is not None:
+            rw, rb = self.rad_layer
+            _lib.check(self.lib.zp_eso2_backward_radial(
+                self.plan.handle, g.n_nodes, g.n_edges, grad_node_out.data_ptr(), x.data_ptr(),
+                ev.data_ptr(), cg.data_ptr(), sg.data_ptr(), rad.data_ptr(), rw.data_ptr(),
+                rb.data_ptr(), self.edge_channels, en.data_ptr(), g.src.data_ptr(),
+                g.dst.data_ptr(), g.row_ptr.data_ptr(), g.perm_src.data_ptr(),
+                g.row_ptr_src.data_ptr(), ctypes.byref(self._w), self.grad_x.data_ptr(),
+                self.grad_edge_vec.data_ptr(), self.grad_radial.data_ptr(),
+                self.grad_rad_w.data_ptr(), self.grad_rad_b.data_ptr(), self.grad_env.data_ptr(),
+                ctypes.byref(self._gw), self.ws.data_ptr(), self.ws.numel(), st),
+                "zp_eso2_backward_radial")
+            return self.grad_x, self.grad_edge_vec, self.grad_radial, self.grad_env, self.grad_w
         _lib.check(self.lib.zp_eso2_backward(
             self.plan.handle, g.n_nodes, g.n_edges, grad_node_out.data_ptr(), x.data_ptr(),
             ev.data_ptr(), cg.data_ptr(), sg.data_ptr(), rad.data_ptr(), en.data_ptr(),

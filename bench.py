@@ -397,6 +397,16 @@ def run_ours(args) -> dict | None:
         rad_ms += ra.elapsed_time(rb)
     rad_ms /= args.steps
     del runner_r, h_rad
+    # ... and with frozen parameters (a force evaluation: gradients w.r.t. x_node and positions only)
+    barrier()
+    frozen_ms = 0.0
+    for i in range(3 + args.steps):
+        flush.zero_()
+        ra.record(); runner.forward(); runner.backward(upstream, weight_grads=False); rb.record()
+        rb.synchronize()
+        if i >= 3:
+            frozen_ms += ra.elapsed_time(rb)
+    frozen_ms /= args.steps
 
     # ---- end to end through the module API from pinned host memory -------------------------
     host = {k: batch[k].pin_memory() for k in ("pos", "x_node", "edge_index", "shifts",
@@ -570,6 +580,12 @@ def run_ours(args) -> dict | None:
                                "what": "the resident step with the last radial layer (EC -> R) and "
                                        "its VJP inside the call (zp_eso2_forward_radial / "
                                        "zp_eso2_backward_radial); `value` has `radial` precomputed"},
+            "frozen_parameters": {"value": e / (frozen_ms * 1e-3), "unit": "edges/s (this rank)",
+                                  "ms_per_step": frozen_ms,
+                                  "what": "forward + VJP w.r.t. x_node, edge vectors, radial "
+                                          "features and envelope only (gw = NULL: no "
+                                          "weight-gradient products), the force evaluation of an "
+                                          "MD loop; not the headline workload"},
             "wall_ms_per_step_incl_flush": t_wall * 1e3 / args.steps,
             "roofline": roof, "kernels": kernels, "gpu_launches": launches,
             "e2e": {"value": total_edges / e2e_s.item(), "unit": "edges/s",

@@ -205,7 +205,10 @@ int zp_eso2_forward_inference(const zp_plan *plan, int64_t n_nodes, int64_t n_ed
  * the reference layout.  perm_src / row_ptr_src: the source-sorted view from zp_csr_build.
  * grad_node_out is indexed by dst and read at rows dst[0] .. dst[E-1] only (the edges are
  * destination-sorted), so a caller holding the gradient of rows n0..n1 alone passes that
- * array's address minus n0 rows.                                                            */
+ * array's address minus n0 rows.
+ * gw == NULL: the parameters are frozen (a force evaluation in an MD loop, autograd with
+ * requires_grad = False on the weights): the weight-gradient products, the bias column sums and
+ * the unfolding are not run, everything else is unchanged.                                     */
 int zp_eso2_backward(const zp_plan *plan, int64_t n_nodes, int64_t n_edges,
                      const float *grad_node_out, const float *x_node, const float *edge_vec,
                      const float *cos_g, const float *sin_g, const float *radial,
@@ -225,7 +228,9 @@ int zp_eso2_backward(const zp_plan *plan, int64_t n_nodes, int64_t n_edges,
  * gradient is read back for a magnitude scan or a format change; the backward returns
  * grad_h_rad [E, edge_channels], grad_rad_w and grad_rad_b instead of grad_radial.
  * edge_channels: a multiple of 8.  Workspace: zp_workspace_bytes_radial (modes as
- * zp_workspace_bytes).  keep_for_backward = 0 behaves like zp_eso2_forward_inference.            */
+ * zp_workspace_bytes).  keep_for_backward = 0 behaves like zp_eso2_forward_inference.
+ * In the backward gw may be NULL as in zp_eso2_backward, and grad_rad_w / grad_rad_b may be NULL
+ * together (frozen layer): only grad_h_rad is then formed from the gradient of radial.          */
 size_t zp_workspace_bytes_radial(const zp_plan *plan, int64_t n_nodes, int64_t n_edges,
                                  int edge_channels, int with_backward);
 int zp_eso2_forward_radial(const zp_plan *plan, int64_t n_nodes, int64_t n_edges,
@@ -266,7 +271,7 @@ int zp_gemm_planes(zp_plan *plan, int64_t M, int64_t N, int64_t K, int planes, c
                    int variant, int ksplit, int64_t split_stride, int kc_elems, int *splits_out,
                    void *stream);
 /* A dense layer on the same engine, in the plan's operand format: y[M,N] = x[M,K] w[N,K]^T + bias,
- * and its VJP (dx may be null; db may be null).  Takes over the fp32 library GEMMs of the widest
+ * and its VJP (dx may be null; db may be null; dw may be null if dx is not: frozen layer).  Takes over the fp32 library GEMMs of the widest
  * radial-MLP layer (rad_func[6], blocks/eso2_ref.py:169-182, 327).  K and N multiples of 8.
  * `work`: zp_linear_work_bytes(plan, M, K, N) bytes of device scratch, caller-owned.           */
 size_t zp_linear_work_bytes(const zp_plan *plan, int64_t M, int64_t K, int64_t N);

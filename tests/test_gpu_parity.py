@@ -367,3 +367,40 @@ def test_runner_with_the_last_radial_layer_inside_the_call():
     assert rel_l2(b.grad_rad_b, grad_a.sum(0)) < 1e-5
     with pytest.raises(ValueError):
         a.bind(f32(case["x_node"]), ev, cg, sg, radial, env, *w, rad_layer=(rw, rb))
+    # frozen parameters (gw = NULL): the other gradients are the same numbers, the weight-gradient
+    # buffers are not touched
+    for run, ref in ((a, (gx_a, gev_a, grad_a, genv_a)), (b, (gx_b, gev_b, gh_b, genv_b))):
+        ref = [t.clone() for t in ref]
+        run.grad_w_flat.fill_(7.0)
+        run.forward()
+        got = run.backward(up, weight_grads=False)
+        for g_, r_ in zip(got[:4], ref):
+            assert torch.equal(g_, r_)
+        assert bool((run.grad_w_flat == 7.0).all())
+
+
+def test_frozen_parameters_give_the_same_forces(jd64):
+    """With `requires_grad_(False)` on the block the backward skips every parameter-gradient
+    product (SO(2) weights, radial MLP, readout); E and dE/dpos do not change."""
+    cfg = dict(lmax=3, mmax=2, sphere_channels=16, hidden_channels=16, edge_channels=16,
+               num_distance_basis=8, cutoff=5.0)
+    params = orc.init_params(cfg, seed=61)
+    case = random_case(cfg, 30, 500, seed=62)
+    block = make_block(cfg, params)
+    dev = "cuda"
+    args = [case["atomic_numbers"].to(dev), case["x_node"].to(dev, torch.float32),
+            case["edge_index"].to(dev), case["shifts"].to(dev, torch.float32),
+            case["cos_gamma_k"].to(dev, torch.float32), case["sin_gamma_k"].to(dev, torch.float32)]
+
+    def energy_and_forces():
+        pos = case["pos"].to(dev, torch.float32).requires_grad_(True)
+        e = block(pos, *args)
+        (de,) = torch.autograd.grad(e, pos)
+        return e.detach(), de
+
+    e0, f0 = energy_and_forces()
+    block.requires_grad_(False)
+    e1, f1 = energy_and_forces()
+    block.requires_grad_(True)
+    assert torch.equal(e0, e1)
+    assert rel_l2(f1, f0) < 1e-6

@@ -239,18 +239,22 @@ def _abi_backward(plan, n, e, g_ptr: int, x, ev, cg, sg, rad, en, sub: EdgeGraph
     """``g_ptr``: address of row 0 of grad_node_out.  The kernels read it only at the rows of the
     edges' destinations, so a caller holding rows n0:n1 alone passes its base minus n0 rows.
     ``layer`` = ``(rad_w, rad_b, grad_rad_w, grad_rad_b)``: ``rad`` / ``grad`` are the input of
-    the last radial layer and its gradient (``zp_eso2_backward_radial``)."""
+    the last radial layer and its gradient (``zp_eso2_backward_radial``).  ``gstruct`` None, or
+    the layer's two gradient tensors None: those parameters are frozen, their gradients are not
+    computed."""
     st = torch.cuda.current_stream().cuda_stream
     lib = _lib.load()
+    g_ref = ctypes.byref(gstruct) if gstruct is not None else None
     if layer is not None:
         rw, rb, grw, grb = layer
+        grw_ptr, grb_ptr = (grw.data_ptr(), grb.data_ptr()) if grw is not None else (None, None)
         _lib.check(lib.zp_eso2_backward_radial(
             plan.handle, n, e, g_ptr, x.data_ptr(), ev.data_ptr(), cg.data_ptr(), sg.data_ptr(),
             rad.data_ptr(), rw.data_ptr(), rb.data_ptr(), rw.shape[1], en.data_ptr(),
             sub.src.data_ptr(), sub.dst.data_ptr(), sub.row_ptr.data_ptr(),
             sub.perm_src.data_ptr(), sub.row_ptr_src.data_ptr(), ctypes.byref(wstruct),
-            gx.data_ptr(), gev.data_ptr(), grad.data_ptr(), grw.data_ptr(), grb.data_ptr(),
-            gen.data_ptr(), ctypes.byref(gstruct), ws.data_ptr(), ws.numel(), st),
+            gx.data_ptr(), gev.data_ptr(), grad.data_ptr(), grw_ptr, grb_ptr,
+            gen.data_ptr(), g_ref, ws.data_ptr(), ws.numel(), st),
             "zp_eso2_backward_radial")
         return
     _lib.check(lib.zp_eso2_backward(
@@ -258,7 +262,7 @@ def _abi_backward(plan, n, e, g_ptr: int, x, ev, cg, sg, rad, en, sub: EdgeGraph
         sg.data_ptr(), rad.data_ptr(), en.data_ptr(), sub.src.data_ptr(), sub.dst.data_ptr(),
         sub.row_ptr.data_ptr(), sub.perm_src.data_ptr(), sub.row_ptr_src.data_ptr(),
         ctypes.byref(wstruct), gx.data_ptr(), gev.data_ptr(), grad.data_ptr(), gen.data_ptr(),
-        ctypes.byref(gstruct), ws.data_ptr(), ws.numel(), st), "zp_eso2_backward")
+        g_ref, ws.data_ptr(), ws.numel(), st), "zp_eso2_backward")
 
 
 class EdgeConvFunction(torch.autograd.Function):
@@ -342,13 +346,16 @@ class EdgeConvFunction(torch.autograd.Function):
         n, e = graph.n_nodes, graph.n_edges
         g = _f32(grad_out)
         gx, gev, grad, gen = (torch.empty_like(t) for t in (x, ev, rad, en))
-        grw, grb = torch.empty_like(rw), torch.empty_like(rb)
+        # frozen parameters (an MD force evaluation): their gradient products are not run
+        want_w = any(ctx.needs_input_grad[10:])
+        want_lw = ctx.has_layer and (ctx.needs_input_grad[8] or ctx.needs_input_grad[9])
+        grw, grb = (torch.empty_like(rw), torch.empty_like(rb)) if want_lw else (None, None)
         layer = (rw, rb, grw, grb) if ctx.has_layer else None
         ec = rw.shape[1] if ctx.has_layer else 0
-        gws = [torch.empty_like(t) for t in (w10, b10, w20, b20, *wms)]
+        gws = [torch.empty_like(t) for t in (w10, b10, w20, b20, *wms)] if want_w else []
         wstruct, keep = _weights_struct(mmax, w10, b10, wms[:mmax], w20, b20, wms[mmax:])
-        gstruct, keep2 = _weights_struct(mmax, gws[0], gws[1], gws[4:4 + mmax], gws[2], gws[3],
-                                         gws[4 + mmax:])
+        gstruct, keep2 = (_weights_struct(mmax, gws[0], gws[1], gws[4:4 + mmax], gws[2], gws[3],
+                                          gws[4 + mmax:]) if want_w else (None, None))
         rng = getattr(graph, "node_range", None)
         row_bytes = plan.sizes.K * plan.c * 4
         g_ptr = g.data_ptr() - (rng[0] * row_bytes if rng is not None else 0)
@@ -362,10 +369,12 @@ class EdgeConvFunction(torch.autograd.Function):
                 ws = plan.workspace(max(c.n1 - c.n0 for c in chunks),
                                     max(c.n_edges for c in chunks), True, edge_channels=ec)
                 gx_c = torch.empty_like(gx)
-                grw_c, grb_c = torch.empty_like(rw), torch.empty_like(rb)
+                grw_c, grb_c = ((torch.empty_like(rw), torch.empty_like(rb)) if want_lw
+                                else (None, None))
                 gws_c = [torch.empty_like(t) for t in gws]
-                cstruct, keep3 = _weights_struct(mmax, gws_c[0], gws_c[1], gws_c[4:4 + mmax],
-                                                 gws_c[2], gws_c[3], gws_c[4 + mmax:])
+                cstruct, keep3 = (_weights_struct(mmax, gws_c[0], gws_c[1], gws_c[4:4 + mmax],
+                                                  gws_c[2], gws_c[3], gws_c[4 + mmax:])
+                                  if want_w else (None, None))
                 scratch_out = torch.empty(max(c.n1 - c.n0 for c in chunks), plan.sizes.K, plan.c,
                                           dtype=torch.float32, device=x.device)
                 for i, c in enumerate(chunks):
@@ -381,11 +390,12 @@ class EdgeConvFunction(torch.autograd.Function):
                     if not first:
                         gx.add_(gx_c)
                         for a_, b_ in zip([*gws, grw, grb], [*gws_c, grw_c, grb_c]):
-                            a_.add_(b_)
+                            if a_ is not None:
+                                a_.add_(b_)
                 del keep3
         del keep, keep2
-        grads = [gx, gev, None, None, grad, gen, grw if ctx.has_layer else None,
-                 grb if ctx.has_layer else None, *gws]
+        grads = [gx, gev, None, None, grad, gen, grw, grb,
+                 *(gws if want_w else [None] * (4 + len(wms)))]
         dts = ctx.in_dtypes
         outs = []
         for i, gr in enumerate(grads):
@@ -426,18 +436,25 @@ class TensorCoreLinear(torch.autograd.Function):
         m, k = xf.shape
         n = wf.shape[0]
         dy = _f32(grad_y)
-        dx, dw = torch.empty_like(xf), torch.empty_like(wf)
-        db = torch.empty(n, dtype=torch.float32, device=xf.device)
+        # a frozen layer forms the input gradient only; a layer whose input needs none, the
+        # parameter gradients only
+        want_x = ctx.needs_input_grad[1]
+        want_w = ctx.needs_input_grad[2] or ctx.needs_input_grad[3] or not want_x
+        dx = torch.empty_like(xf) if want_x else None
+        dw = torch.empty_like(wf) if want_w else None
+        db = torch.empty(n, dtype=torch.float32, device=xf.device) if want_w else None
         nbytes = lib.zp_linear_work_bytes(plan.handle, m, k, n)
         work = torch.empty(nbytes, dtype=torch.uint8, device=xf.device)
+        ptr = lambda t: t.data_ptr() if t is not None else None                  # noqa: E731
         with torch.cuda.device(xf.device):
             st = torch.cuda.current_stream().cuda_stream
             _lib.check(lib.zp_linear_backward(plan.handle, m, k, n, xf.data_ptr(), wf.data_ptr(),
-                                              dy.data_ptr(), dx.data_ptr(), dw.data_ptr(),
-                                              db.data_ptr(), work.data_ptr(), nbytes, st),
+                                              dy.data_ptr(), ptr(dx), ptr(dw), ptr(db),
+                                              work.data_ptr(), nbytes, st),
                        "zp_linear_backward")
         dt = ctx.dtypes
-        return None, dx.to(dt[0]), dw.to(dt[1]), db.to(dt[2])
+        to = lambda t, d: t.to(d) if t is not None else None                       # noqa: E731
+        return None, to(dx, dt[0]), to(dw, dt[1]), to(db, dt[2])
 
 
 class LayerNormSiLU(torch.autograd.Function):

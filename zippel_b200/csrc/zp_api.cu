@@ -518,7 +518,8 @@ static int check_radial_layer(const zp_plan *plan, const RadialLayer *rl, int64_
   if (!rl->w || !rl->b || (E && !rl->h)) return ZP_ERR_INVALID_ARG;
   if (rl->ec <= 0 || rl->ec % 8 || plan->t.R % 8) return ZP_ERR_UNSUPPORTED;
   if (!aligned16(rl->h) || !aligned16(rl->w)) return ZP_ERR_INVALID_ARG;
-  if (backward && (!rl->grad_w || !rl->grad_b || (E && !rl->grad_h))) return ZP_ERR_INVALID_ARG;
+  // the layer's parameter gradients are wanted together or not at all (frozen parameters)
+  if (backward && ((!rl->grad_w != !rl->grad_b) || (E && !rl->grad_h))) return ZP_ERR_INVALID_ARG;
   return ZP_OK;
 }
 
@@ -729,15 +730,20 @@ static int eso2_backward(const zp_plan *plan, int64_t N, int64_t E, const float 
                          size_t workspace_bytes, void *stream, const RadialLayer *rl) {
   if (!plan || N < 0 || E < 0) return ZP_ERR_INVALID_ARG;
   if (N == 0) return E == 0 ? ZP_OK : ZP_ERR_INVALID_ARG;
-  if (!grad_node_out || !x_node || !row_ptr || !row_ptr_src || !grad_x_node || !workspace || !gw)
+  if (!grad_node_out || !x_node || !row_ptr || !row_ptr_src || !grad_x_node || !workspace)
     return ZP_ERR_INVALID_ARG;
+  // gw == NULL: the parameters are frozen (an MD / inference force evaluation): no weight-gradient
+  // product, no bias column sum, no unfolding
+  const bool want_w = gw != nullptr;
   if (E && (!edge_vec || !cos_g || !sin_g || (!radial && !rl) || !env || !src || !dst || !perm_src ||
             !grad_edge_vec || (!grad_radial && !rl) || !grad_env))
     return ZP_ERR_INVALID_ARG;
-  if (!gw->c1_w0 || !gw->c1_b0 || !gw->c2_w0 || !gw->c2_b0) return ZP_ERR_INVALID_ARG;
-  for (int m = 1; m < plan->n_blocks; ++m)
-    if (!gw->c1_wm || !gw->c2_wm || !gw->c1_wm[m - 1] || !gw->c2_wm[m - 1])
-      return ZP_ERR_INVALID_ARG;
+  if (want_w) {
+    if (!gw->c1_w0 || !gw->c1_b0 || !gw->c2_w0 || !gw->c2_b0) return ZP_ERR_INVALID_ARG;
+    for (int m = 1; m < plan->n_blocks; ++m)
+      if (!gw->c1_wm || !gw->c2_wm || !gw->c1_wm[m - 1] || !gw->c2_wm[m - 1])
+        return ZP_ERR_INVALID_ARG;
+  }
   if (!aligned16(grad_node_out) || !aligned16(grad_x_node) || !aligned16(grad_radial) ||
       !aligned16(workspace))   /* a null grad_radial (radial layer inside the call) is aligned */
     return ZP_ERR_INVALID_ARG;
@@ -807,7 +813,8 @@ static int eso2_backward(const zp_plan *plan, int64_t N, int64_t E, const float 
       int &nsplit = (conv ? splits_c2 : splits_c1)[m];
       nsplit = 1;
       if (E == 0) {
-        ZP_CUDA(cudaMemsetAsync(G, 0, sizeof(float) * (size_t)out * in, lanes.pick(2 * m + 1)));
+        if (want_w)
+          ZP_CUDA(cudaMemsetAsync(G, 0, sizeof(float) * (size_t)out * in, lanes.pick(2 * m + 1)));
         continue;
       }
       const ZpGemmTc gd{E, in, out, P, dYm.base, dYm.ld, dYm.plane_stride, 0,
@@ -817,7 +824,8 @@ static int eso2_backward(const zp_plan *plan, int64_t N, int64_t E, const float 
                         // max |dht|; max |da1| when the radial layer's gradient needs it
                         !plan->fp16 ? nullptr : conv ? ws.scales + kScDht
                                                      : rl ? ws.scales + kScDa1 : nullptr};
-      ZP_TIMED(ZP_K_GEMM_DGRAD, zp_launch_gemm_tc(gd, lanes.pick(2 * m)));
+      ZP_TIMED(ZP_K_GEMM_DGRAD, zp_launch_gemm_tc(gd, lanes.pick(want_w ? 2 * m : m)));
+      if (!want_w) continue;
       ZpGemmTc gw_{out, in, E, P, dYm.base, dYm.ld, dYm.plane_stride, 1,
                    Xm.base, Xm.ld, Xm.plane_stride, 1, nullptr, G, in,
                    plan->status_dev, 0, 1, plan->g_elems, 0, plan->fp16, dYm.scale, Xm.scale,
@@ -826,9 +834,10 @@ static int eso2_backward(const zp_plan *plan, int64_t N, int64_t E, const float 
       nsplit = zp_gemm_tc_splits(gw_);
       ZP_TIMED(ZP_K_GEMM_WGRAD, zp_launch_gemm_tc(gw_, lanes.pick(2 * m + 1)));
     }
-    ZP_TIMED(ZP_K_BIAS_GRAD,
-             zp_launch_colsum(E, conv ? plan->c2_out[0] : plan->c1_out[0], dYp,
-                              conv ? gw->c2_b0 : gw->c1_b0, ws.scratch, lanes.pick(2)));
+    if (want_w)
+      ZP_TIMED(ZP_K_BIAS_GRAD,
+               zp_launch_colsum(E, conv ? plan->c2_out[0] : plan->c1_out[0], dYp,
+                                conv ? gw->c2_b0 : gw->c1_b0, ws.scratch, lanes.pick(2)));
     if ((rc = lanes.join())) return rc;
   }
   if (rl) {
@@ -845,7 +854,7 @@ static int eso2_backward(const zp_plan *plan, int64_t N, int64_t E, const float 
                zp_linear_backward_planes(plan, E, rl->ec, t.R, ws.hr, ws.rw, ws.gr, rl->grad_h,
                                          rl->grad_w, rl->grad_b, ws.rad_partials, kRadialSplits,
                                          ws.scratch, st));
-    } else {
+    } else if (rl->grad_w) {
       ZP_CUDA(cudaMemsetAsync(rl->grad_w, 0, sizeof(float) * (size_t)t.R * rl->ec, st));
       ZP_CUDA(cudaMemsetAsync(rl->grad_b, 0, sizeof(float) * (size_t)t.R, st));
     }
@@ -859,8 +868,9 @@ static int eso2_backward(const zp_plan *plan, int64_t N, int64_t E, const float 
                                  grad_x_node, st));
   ZP_TIMED(ZP_K_WIGNER_BWD,
            zp_launch_wigner_bwd(plan, E, edge_vec, cos_g, sin_g, ws.grot, grad_edge_vec, st));
-  ZP_TIMED(ZP_K_FOLD, zp_launch_unfold_wgrad(plan, ws.wgrad, plan->g_elems, splits_c1, splits_c2,
-                                             gw, st));
+  if (want_w)
+    ZP_TIMED(ZP_K_FOLD, zp_launch_unfold_wgrad(plan, ws.wgrad, plan->g_elems, splits_c1, splits_c2,
+                                               gw, st));
   return ZP_OK;
 }
 

@@ -85,6 +85,7 @@ int zp_linear_backward_planes(const zp_plan *plan, int64_t M, int64_t K, int64_t
                      0, 1, 0, 0, plan->fp16, dy.scale, w.scale, nullptr};
     if ((rc = zp_launch_gemm_tc(g, st))) return rc;
   }
+  if (!dw) return db ? zp_launch_colsum(M, N, dy, db, colsum_scratch, st) : ZP_OK;
   ZpGemmTc g{N, K, M, plan->planes, dy.base, dy.ld, dy.plane_stride, 1,
              x.base, x.ld, x.plane_stride, 1, nullptr, partials, K, plan->status_dev,
              0, 1, N * K, 0, plan->fp16, dy.scale, x.scale, nullptr};
@@ -137,17 +138,18 @@ int zp_linear_backward(const zp_plan *plan, int64_t M, int64_t K, int64_t N, con
                        void *work, size_t work_bytes, void *stream) {
   int rc = check(plan, M, K, N);
   if (rc) return rc;
-  if (!w || !dw || !work || (M && (!x || !dy))) return ZP_ERR_INVALID_ARG;
+  if (!w || !work || (!dw && !dx) || (M && (!x || !dy))) return ZP_ERR_INVALID_ARG;
   const LinWork lw = carve_lin(plan, M, K, N, work);
   if (work_bytes < lw.bytes) return ZP_ERR_WORKSPACE;
   cudaStream_t st = (cudaStream_t)stream;
   if (M == 0) {
-    ZP_CUDA(cudaMemsetAsync(dw, 0, sizeof(float) * N * K, st));
+    if (dw) ZP_CUDA(cudaMemsetAsync(dw, 0, sizeof(float) * N * K, st));
     if (db) ZP_CUDA(cudaMemsetAsync(db, 0, sizeof(float) * N, st));
     return ZP_OK;
   }
-  if ((rc = split_scaled(plan, M, K, x, lw.x, lw.scales + 0, st))) return rc;
-  if ((rc = split_scaled(plan, N, K, w, lw.w, lw.scales + 2, st))) return rc;
+  // dw == NULL: frozen parameters, only the input gradient (and db if given) is formed
+  if (dw && (rc = split_scaled(plan, M, K, x, lw.x, lw.scales + 0, st))) return rc;
+  if (dx && (rc = split_scaled(plan, N, K, w, lw.w, lw.scales + 2, st))) return rc;
   if ((rc = split_scaled(plan, M, N, dy, lw.dy, lw.scales + 4, st))) return rc;
   return zp_linear_backward_planes(plan, M, K, N, lw.x, lw.w, lw.dy, dx, dw, db, lw.partials,
                                    kLinSplits, lw.colsum, st);

@@ -100,10 +100,13 @@ class EdgeConvRunner:
             self.ws.data_ptr(), self.ws.numel(), st), "zp_eso2_forward")
         return self.node_out
 
-    def backward(self, grad_node_out: torch.Tensor):
+    def backward(self, grad_node_out: torch.Tensor, weight_grads: bool = True):
+        """``weight_grads=False``: the parameters are frozen (a force evaluation): their gradient
+        products are not run and ``grad_w`` / ``grad_rad_w`` / ``grad_rad_b`` keep old contents."""
         x, ev, cg, sg, rad, en = self.inputs
         g = self.graph
         st = torch.cuda.current_stream().cuda_stream
+        gw_ref = ctypes.byref(self._gw) if weight_grads else None
         if self.rad_layer is not None:
             rw, rb = self.rad_layer
             _lib.check(self.lib.zp_eso2_backward_radial(
@@ -113,8 +116,9 @@ class EdgeConvRunner:
                 g.dst.data_ptr(), g.row_ptr.data_ptr(), g.perm_src.data_ptr(),
                 g.row_ptr_src.data_ptr(), ctypes.byref(self._w), self.grad_x.data_ptr(),
                 self.grad_edge_vec.data_ptr(), self.grad_radial.data_ptr(),
-                self.grad_rad_w.data_ptr(), self.grad_rad_b.data_ptr(), self.grad_env.data_ptr(),
-                ctypes.byref(self._gw), self.ws.data_ptr(), self.ws.numel(), st),
+                self.grad_rad_w.data_ptr() if weight_grads else None,
+                self.grad_rad_b.data_ptr() if weight_grads else None, self.grad_env.data_ptr(),
+                gw_ref, self.ws.data_ptr(), self.ws.numel(), st),
                 "zp_eso2_backward_radial")
             return self.grad_x, self.grad_edge_vec, self.grad_radial, self.grad_env, self.grad_w
         _lib.check(self.lib.zp_eso2_backward(
@@ -123,7 +127,7 @@ class EdgeConvRunner:
             g.src.data_ptr(), g.dst.data_ptr(), g.row_ptr.data_ptr(), g.perm_src.data_ptr(),
             g.row_ptr_src.data_ptr(), ctypes.byref(self._w), self.grad_x.data_ptr(),
             self.grad_edge_vec.data_ptr(), self.grad_radial.data_ptr(), self.grad_env.data_ptr(),
-            ctypes.byref(self._gw), self.ws.data_ptr(), self.ws.numel(), st), "zp_eso2_backward")
+            gw_ref, self.ws.data_ptr(), self.ws.numel(), st), "zp_eso2_backward")
         return self.grad_x, self.grad_edge_vec, self.grad_radial, self.grad_env, self.grad_w
 
     # -- per-kernel-class timing ---------------------------------------------------------

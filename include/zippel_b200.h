@@ -208,7 +208,9 @@ int zp_eso2_forward_inference(const zp_plan *plan, int64_t n_nodes, int64_t n_ed
  * array's address minus n0 rows.
  * gw == NULL: the parameters are frozen (a force evaluation in an MD loop, autograd with
  * requires_grad = False on the weights): the weight-gradient products, the bias column sums and
- * the unfolding are not run, everything else is unchanged.                                     */
+ * the unfolding are not run, everything else is unchanged.  grad_x_node == NULL: the embeddings
+ * are an input without a gradient (E and dE/dpos of one block, the reference's build_force,
+ * blocks/eso2_ir.py:579-590): the per-edge contributions are neither written nor summed.       */
 int zp_eso2_backward(const zp_plan *plan, int64_t n_nodes, int64_t n_edges,
                      const float *grad_node_out, const float *x_node, const float *edge_vec,
                      const float *cos_g, const float *sin_g, const float *radial,

@@ -377,6 +377,11 @@ def test_runner_with_the_last_radial_layer_inside_the_call():
         for g_, r_ in zip(got[:4], ref):
             assert torch.equal(g_, r_)
         assert bool((run.grad_w_flat == 7.0).all())
+        run.grad_x.fill_(7.0)                  # no gradient of x_node either
+        got = run.backward(up, weight_grads=False, x_grad=False)
+        for g_, r_ in zip(got[1:4], ref[1:]):
+            assert torch.equal(g_, r_)
+        assert bool((run.grad_x == 7.0).all())
 
 
 def test_frozen_parameters_give_the_same_forces(jd64):
@@ -392,15 +397,17 @@ def test_frozen_parameters_give_the_same_forces(jd64):
             case["edge_index"].to(dev), case["shifts"].to(dev, torch.float32),
             case["cos_gamma_k"].to(dev, torch.float32), case["sin_gamma_k"].to(dev, torch.float32)]
 
-    def energy_and_forces():
+    def energy_and_forces(x_grad: bool):
         pos = case["pos"].to(dev, torch.float32).requires_grad_(True)
-        e = block(pos, *args)
-        (de,) = torch.autograd.grad(e, pos)
+        x = args[1].clone().requires_grad_(x_grad)
+        e = block(pos, args[0], x, *args[2:])
+        de = torch.autograd.grad(e, [pos, x] if x_grad else [pos])[0]
         return e.detach(), de
 
-    e0, f0 = energy_and_forces()
+    e0, f0 = energy_and_forces(True)           # every gradient formed
     block.requires_grad_(False)
-    e1, f1 = energy_and_forces()
+    e1, f1 = energy_and_forces(True)           # frozen parameters
+    e2, f2 = energy_and_forces(False)          # ... and embeddings without a gradient
     block.requires_grad_(True)
-    assert torch.equal(e0, e1)
-    assert rel_l2(f1, f0) < 1e-6
+    assert torch.equal(e0, e1) and torch.equal(e0, e2)
+    assert rel_l2(f1, f0) < 1e-6 and rel_l2(f2, f0) < 1e-6

@@ -245,6 +245,7 @@ def _abi_backward(plan, n, e, g_ptr: int, x, ev, cg, sg, rad, en, sub: EdgeGraph
     st = torch.cuda.current_stream().cuda_stream
     lib = _lib.load()
     g_ref = ctypes.byref(gstruct) if gstruct is not None else None
+    gx_ptr = gx.data_ptr() if gx is not None else None          # None: no gradient of x_node
     if layer is not None:
         rw, rb, grw, grb = layer
         grw_ptr, grb_ptr = (grw.data_ptr(), grb.data_ptr()) if grw is not None else (None, None)
@@ -253,7 +254,7 @@ def _abi_backward(plan, n, e, g_ptr: int, x, ev, cg, sg, rad, en, sub: EdgeGraph
             rad.data_ptr(), rw.data_ptr(), rb.data_ptr(), rw.shape[1], en.data_ptr(),
             sub.src.data_ptr(), sub.dst.data_ptr(), sub.row_ptr.data_ptr(),
             sub.perm_src.data_ptr(), sub.row_ptr_src.data_ptr(), ctypes.byref(wstruct),
-            gx.data_ptr(), gev.data_ptr(), grad.data_ptr(), grw_ptr, grb_ptr,
+            gx_ptr, gev.data_ptr(), grad.data_ptr(), grw_ptr, grb_ptr,
             gen.data_ptr(), g_ref, ws.data_ptr(), ws.numel(), st),
             "zp_eso2_backward_radial")
         return
@@ -261,7 +262,7 @@ def _abi_backward(plan, n, e, g_ptr: int, x, ev, cg, sg, rad, en, sub: EdgeGraph
         plan.handle, n, e, g_ptr, x.data_ptr(), ev.data_ptr(), cg.data_ptr(),
         sg.data_ptr(), rad.data_ptr(), en.data_ptr(), sub.src.data_ptr(), sub.dst.data_ptr(),
         sub.row_ptr.data_ptr(), sub.perm_src.data_ptr(), sub.row_ptr_src.data_ptr(),
-        ctypes.byref(wstruct), gx.data_ptr(), gev.data_ptr(), grad.data_ptr(), gen.data_ptr(),
+        ctypes.byref(wstruct), gx_ptr, gev.data_ptr(), grad.data_ptr(), gen.data_ptr(),
         g_ref, ws.data_ptr(), ws.numel(), st), "zp_eso2_backward")
 
 
@@ -345,7 +346,9 @@ class EdgeConvFunction(torch.autograd.Function):
         mmax = plan.mmax
         n, e = graph.n_nodes, graph.n_edges
         g = _f32(grad_out)
-        gx, gev, grad, gen = (torch.empty_like(t) for t in (x, ev, rad, en))
+        gev, grad, gen = (torch.empty_like(t) for t in (ev, rad, en))
+        # embeddings that need no gradient (E and dE/dpos of one block): nothing is summed per node
+        gx = torch.empty_like(x) if ctx.needs_input_grad[2] else None
         # frozen parameters (an MD force evaluation): their gradient products are not run
         want_w = any(ctx.needs_input_grad[10:])
         want_lw = ctx.has_layer and (ctx.needs_input_grad[8] or ctx.needs_input_grad[9])
@@ -368,7 +371,7 @@ class EdgeConvFunction(torch.autograd.Function):
                 # node and weight gradients add up over chunks, per-edge gradients are slices
                 ws = plan.workspace(max(c.n1 - c.n0 for c in chunks),
                                     max(c.n_edges for c in chunks), True, edge_channels=ec)
-                gx_c = torch.empty_like(gx)
+                gx_c = torch.empty_like(gx) if gx is not None else None
                 grw_c, grb_c = ((torch.empty_like(rw), torch.empty_like(rb)) if want_lw
                                 else (None, None))
                 gws_c = [torch.empty_like(t) for t in gws]
@@ -388,8 +391,7 @@ class EdgeConvFunction(torch.autograd.Function):
                                   c.sub, wstruct, gx if first else gx_c, gev[sl], grad[sl], gen[sl],
                                   gstruct if first else cstruct, ws, layer=lay)
                     if not first:
-                        gx.add_(gx_c)
-                        for a_, b_ in zip([*gws, grw, grb], [*gws_c, grw_c, grb_c]):
+                        for a_, b_ in zip([gx, *gws, grw, grb], [gx_c, *gws_c, grw_c, grb_c]):
                             if a_ is not None:
                                 a_.add_(b_)
                 del keep3

@@ -730,7 +730,7 @@ static int eso2_backward(const zp_plan *plan, int64_t N, int64_t E, const float 
                          size_t workspace_bytes, void *stream, const RadialLayer *rl) {
   if (!plan || N < 0 || E < 0) return ZP_ERR_INVALID_ARG;
   if (N == 0) return E == 0 ? ZP_OK : ZP_ERR_INVALID_ARG;
-  if (!grad_node_out || !x_node || !row_ptr || !row_ptr_src || !grad_x_node || !workspace)
+  if (!grad_node_out || !x_node || !row_ptr || !row_ptr_src || !workspace)
     return ZP_ERR_INVALID_ARG;
   // gw == NULL: the parameters are frozen (an MD / inference force evaluation): no weight-gradient
   // product, no bias column sum, no unfolding
@@ -754,6 +754,9 @@ static int eso2_backward(const zp_plan *plan, int64_t N, int64_t E, const float 
   const Workspace ws = carve(plan, 0, E, 1, workspace, rl ? rl->ec : 0);
   if (workspace_bytes < ws.bytes) return ZP_ERR_WORKSPACE;
   if (rl) radial = ws.radial;            // left there by the forward
+  // grad_x_node == NULL: the embeddings are an input without a gradient (E and dE/dpos of one
+  // block): the per-edge contributions are neither written nor summed
+  float *du_out = grad_x_node ? ws.du_src : nullptr;
   cudaStream_t st = (cudaStream_t)stream;
   Lanes lanes(plan, st);
   const ZpTables &t = plan->t;
@@ -848,7 +851,7 @@ static int eso2_backward(const zp_plan *plan, int64_t N, int64_t E, const float 
                                                    0.f, ws.scales + kScGrScale, st));
     ZP_TIMED(ZP_K_ROTATE_IN_BWD,
              zp_launch_rotate_in_bwd(plan, E, ws.da1, radial, x_node, src, dst, ws.rot,
-                                     nullptr, ws.du_src, ws.grot, st, &ws.gr));
+                                     nullptr, du_out, ws.grot, st, &ws.gr));
     if (E > 0) {
       ZP_TIMED(ZP_K_GEMM_WGRAD,
                zp_linear_backward_planes(plan, E, rl->ec, t.R, ws.hr, ws.rw, ws.gr, rl->grad_h,
@@ -861,11 +864,12 @@ static int eso2_backward(const zp_plan *plan, int64_t N, int64_t E, const float 
   } else {
     ZP_TIMED(ZP_K_ROTATE_IN_BWD,
              zp_launch_rotate_in_bwd(plan, E, ws.da1, radial, x_node, src, dst, ws.rot,
-                                     grad_radial, ws.du_src, ws.grot, st));
+                                     grad_radial, du_out, ws.grot, st));
   }
-  ZP_TIMED(ZP_K_SRC_REDUCE,
-           zp_launch_node_reduce(plan, N, ws.du_src, row_ptr, perm_src, row_ptr_src,
-                                 grad_x_node, st));
+  if (grad_x_node)
+    ZP_TIMED(ZP_K_SRC_REDUCE,
+             zp_launch_node_reduce(plan, N, ws.du_src, row_ptr, perm_src, row_ptr_src,
+                                   grad_x_node, st));
   ZP_TIMED(ZP_K_WIGNER_BWD,
            zp_launch_wigner_bwd(plan, E, edge_vec, cos_g, sin_g, ws.grot, grad_edge_vec, st));
   if (want_w)

@@ -516,7 +516,7 @@ struct RotInBwdE {
         }
       }
     }
-    if (active) {
+    if (active && du_row) {              // no du_both: the caller wants no gradient of x_node
 #pragma unroll
       for (int j = 0; j < n; ++j) vstore<4>(du_row + (size_t)(L * L + j) * t.C, du[j]);
     }
@@ -596,7 +596,7 @@ rotate_in_bwd_kernel(const __grid_constant__ ZpTables t, int64_t E, int W,
     const int c = c2 - half * t.C;
     const int64_t node = half ? dst[e] : src[e];
     const float *xrow = x + (size_t)node * t.K * t.C + c;
-    float *du_row = du_both + ((size_t)e * 2 + half) * t.K * t.C + c;
+    float *du_row = du_both ? du_both + ((size_t)e * 2 + half) * t.K * t.C + c : nullptr;
     RotInBwdE<LMAX, LMAX>::run(t, xrow, stage, radial + (size_t)e * t.R,
                                grad_radial + (size_t)e * t.R, grad_radial_planes,
                                e * grad_radial_planes.ld, zp_inv_scale(grad_radial_planes),

@@ -100,13 +100,16 @@ class EdgeConvRunner:
             self.ws.data_ptr(), self.ws.numel(), st), "zp_eso2_forward")
         return self.node_out
 
-    def backward(self, grad_node_out: torch.Tensor, weight_grads: bool = True):
+    def backward(self, grad_node_out: torch.Tensor, weight_grads: bool = True,
+                 x_grad: bool = True):
         """``weight_grads=False``: the parameters are frozen (a force evaluation): their gradient
-        products are not run and ``grad_w`` / ``grad_rad_w`` / ``grad_rad_b`` keep old contents."""
+        products are not run and ``grad_w`` / ``grad_rad_w`` / ``grad_rad_b`` keep old contents.
+        ``x_grad=False``: no gradient of ``x_node`` (``grad_x`` keeps its old contents)."""
         x, ev, cg, sg, rad, en = self.inputs
         g = self.graph
         st = torch.cuda.current_stream().cuda_stream
         gw_ref = ctypes.byref(self._gw) if weight_grads else None
+        gx_ptr = self.grad_x.data_ptr() if x_grad else None
         if self.rad_layer is not None:
             rw, rb = self.rad_layer
             _lib.check(self.lib.zp_eso2_backward_radial(
@@ -114,7 +117,7 @@ class EdgeConvRunner:
                 ev.data_ptr(), cg.data_ptr(), sg.data_ptr(), rad.data_ptr(), rw.data_ptr(),
                 rb.data_ptr(), self.edge_channels, en.data_ptr(), g.src.data_ptr(),
                 g.dst.data_ptr(), g.row_ptr.data_ptr(), g.perm_src.data_ptr(),
-                g.row_ptr_src.data_ptr(), ctypes.byref(self._w), self.grad_x.data_ptr(),
+                g.row_ptr_src.data_ptr(), ctypes.byref(self._w), gx_ptr,
                 self.grad_edge_vec.data_ptr(), self.grad_radial.data_ptr(),
                 self.grad_rad_w.data_ptr() if weight_grads else None,
                 self.grad_rad_b.data_ptr() if weight_grads else None, self.grad_env.data_ptr(),
@@ -125,7 +128,7 @@ class EdgeConvRunner:
             self.plan.handle, g.n_nodes, g.n_edges, grad_node_out.data_ptr(), x.data_ptr(),
             ev.data_ptr(), cg.data_ptr(), sg.data_ptr(), rad.data_ptr(), en.data_ptr(),
             g.src.data_ptr(), g.dst.data_ptr(), g.row_ptr.data_ptr(), g.perm_src.data_ptr(),
-            g.row_ptr_src.data_ptr(), ctypes.byref(self._w), self.grad_x.data_ptr(),
+            g.row_ptr_src.data_ptr(), ctypes.byref(self._w), gx_ptr,
             self.grad_edge_vec.data_ptr(), self.grad_radial.data_ptr(), self.grad_env.data_ptr(),
             gw_ref, self.ws.data_ptr(), self.ws.numel(), st), "zp_eso2_backward")
         return self.grad_x, self.grad_edge_vec, self.grad_radial, self.grad_env, self.grad_w

@@ -893,6 +893,13 @@ def run_fixture(args) -> dict:
         return torch.autograd.grad((out * up).sum(), [x, pos, *block.parameters()],
                                    allow_unused=True)
 
+    def energy_forces():
+        # E and dE/dpos with frozen parameters and embeddings (the reference's force program,
+        # blocks/eso2_ir.py:579-590): no parameter or embedding gradient is formed
+        pos = batch["pos"].detach().requires_grad_(True)
+        e_ = block(pos, a[0], batch["x_node"], *a[1:], graph=graph)
+        return torch.autograd.grad(e_, pos)
+
     def timed(fn):
         for _ in range(max(args.warmup, 3)):
             fn()
@@ -905,6 +912,9 @@ def run_fixture(args) -> dict:
         return statistics.median(ms)
 
     f_ms, b_ms = timed(fwd), timed(fwd_vjp)
+    block.requires_grad_(False)
+    ef_ms = timed(energy_forces)
+    block.requires_grad_(True)
     pub = REFERENCE_PUBLISHED_FWD_MS.get(args.fixture)
     return {"metric": "edges/s, eSEN SO(2) block on a reference fixture (lmax2 mmax2 C128, fp32)",
             "workload": f"fixture {args.fixture}", "value": e / (b_ms * 1e-3), "unit": "edges/s",
@@ -914,6 +924,8 @@ def run_fixture(args) -> dict:
             "forward": {"ms": f_ms, "edges_per_s": e / (f_ms * 1e-3),
                         "reference_published_eager_ms_gh200": pub,
                         "ratio_to_published": (pub / f_ms) if pub else None},
+            "energy_and_forces": {"ms": ef_ms, "edges_per_s": e / (ef_ms * 1e-3),
+                                  "what": "E and dE/dpos, parameters and embeddings frozen"},
             "config": {"atoms": n, "edges": e, "avg_degree": meta["avg_degree"], "lmax": 2, "mmax": 2,
                        "channels": 128, "sha256_content": meta["sha256_content"],
                        "fixture_build_s": build_s},

@@ -384,7 +384,7 @@ def test_runner_with_the_last_radial_layer_inside_the_call():
         assert bool((run.grad_x == 7.0).all())
 
 
-def test_frozen_parameters_give_the_same_forces(jd64):
+def test_frozen_parameters_give_the_same_forces(jd64, monkeypatch):
     """With `requires_grad_(False)` on the block the backward skips every parameter-gradient
     product (SO(2) weights, radial MLP, readout); E and dE/dpos do not change."""
     cfg = dict(lmax=3, mmax=2, sphere_channels=16, hidden_channels=16, edge_channels=16,
@@ -408,6 +408,11 @@ def test_frozen_parameters_give_the_same_forces(jd64):
     block.requires_grad_(False)
     e1, f1 = energy_and_forces(True)           # frozen parameters
     e2, f2 = energy_and_forces(False)          # ... and embeddings without a gradient
+    from zippel_b200.blocks import eso2
+    monkeypatch.setattr(eso2, "MAX_EDGES_PER_CALL", 256)       # the same in destination chunks
+    e3, f3 = energy_and_forces(False)
+    e4, f4 = energy_and_forces(True)
     block.requires_grad_(True)
     assert torch.equal(e0, e1) and torch.equal(e0, e2)
     assert rel_l2(f1, f0) < 1e-6 and rel_l2(f2, f0) < 1e-6
+    assert rel_l2(e3, e0) < 1e-6 and rel_l2(f3, f0) < 1e-5 and rel_l2(f4, f0) < 1e-5

@@ -46,6 +46,25 @@ def test_replay_equals_module_path(precision):
     assert block.plan("cuda").device_status() == 0
 
 
+def test_frozen_block_records_a_force_evaluation():
+    """With every parameter frozen the recorded step forms the gradients of x_node and pos only;
+    they equal those of the step recorded with trainable parameters."""
+    torch.manual_seed(2)
+    block = ESO2Block(BlockConfig(**CFG)).to("cuda")
+    case = _f32(random_case(CFG, 40, 500, 4))
+    full = CapturedStep(block, case, "cuda")
+    full.run()
+    block.requires_grad_(False)
+    frozen = CapturedStep(block, case, "cuda")
+    block.requires_grad_(True)
+    frozen.run()
+    assert frozen.grads["params"] == {} and len(full.grads["params"]) > 0
+    assert torch.equal(frozen.node_out, full.node_out)
+    assert torch.equal(frozen.grads["pos"], full.grads["pos"])
+    assert torch.equal(frozen.grads["x_node"], full.grads["x_node"])
+    assert torch.equal(frozen.grad_pos_host, full.grad_pos_host)
+
+
 def test_parameter_updates_are_seen():
     torch.manual_seed(1)
     block = ESO2Block(BlockConfig(**CFG)).to("cuda")

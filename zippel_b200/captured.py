@@ -53,7 +53,10 @@ class CapturedStep:
         self.grad_pos_host = torch.empty(self.n_atoms, 3, pin_memory=True)
         self.loss_host = torch.empty((), pin_memory=True)
         self.d2h_bytes = self.grad_pos_host.numel() * 4 + 4
-        self.params = [p for p in block.parameters()]
+        # frozen parameters (requires_grad False) get no gradient: the recorded backward then
+        # runs no weight-gradient products (a force evaluation in an MD loop)
+        self.param_names = [n for n, p in block.named_parameters() if p.requires_grad]
+        self.params = [p for p in block.parameters() if p.requires_grad]
         self.dev: dict = {}
         self.grads: dict = {}
         self.node_out = None
@@ -106,7 +109,7 @@ class CapturedStep:
         self.loss_host.copy_(loss.detach(), non_blocking=True)
         self.dev, self.node_out = t, node_out.detach()
         self.grads = {"x_node": g[0], "pos": g[1],
-                      "params": {n: gr for (n, _), gr in zip(self.block.named_parameters(), g[2:])}}
+                      "params": dict(zip(self.param_names, g[2:]))}
 
     def run(self, sync: bool = True) -> None:
         """Replays the recorded step on the current stream with the current contents of

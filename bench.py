@@ -638,7 +638,8 @@ def large_legs(args, world: int, rank: int) -> dict:
     base_port = int(os.environ.get("MASTER_PORT", "29500"))
     for i, (name, extra) in enumerate((
             ("cfg3", ["--structures", str(args.structures), "--steps", "2", "--warmup", "2"]),
-            ("cfg4", ["--atoms", str(args.large_atoms), "--steps", "1", "--warmup", "1"]))):
+            ("cfg4", ["--atoms", str(args.large_atoms), "--steps", "1" if world == 1 else "2",
+                      "--warmup", "2"]))):
         # a rendezvous of the children's own: rank 0 of them opens the store on another port
         # (the launcher's "use the agent's store" switch must not reach them)
         env = {k: v for k, v in os.environ.items() if not k.startswith("TORCHELASTIC")}

@@ -283,6 +283,12 @@ int zp_linear_forward(const zp_plan *plan, int64_t M, int64_t K, int64_t N, cons
 int zp_linear_backward(const zp_plan *plan, int64_t M, int64_t K, int64_t N, const float *x,
                        const float *w, const float *dy, float *dx, float *dw, float *db,
                        void *work, size_t work_bytes, void *stream);
+/* zp_linear_backward for a caller that kept the `work` buffer of the matching zp_linear_forward
+ * untouched: the 16-bit planes of x and w and their scales are still there, so neither is scanned
+ * or re-formatted again (x and w themselves are not read).                                     */
+int zp_linear_backward_saved(const zp_plan *plan, int64_t M, int64_t K, int64_t N, const float *dy,
+                             float *dx, float *dw, float *db, void *work, size_t work_bytes,
+                             void *stream);
 
 /* LayerNorm followed by SiLU over rows of `width` floats (a multiple of 4, at most 1024), and the
  * VJP: the hidden layers of the radial MLP (nn.LayerNorm + nn.SiLU, rad_func[1..2] and

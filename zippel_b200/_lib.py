@@ -80,6 +80,7 @@ SIGNATURES = {
     "zp_linear_work_bytes": (_SZ, [_P, _I64, _I64, _I64]),
     "zp_linear_forward": (C.c_int, [_P, _I64, _I64, _I64, _P, _P, _P, _P, _P, _SZ, _P]),
     "zp_linear_backward": (C.c_int, [_P, _I64, _I64, _I64, _P, _P, _P, _P, _P, _P, _P, _SZ, _P]),
+    "zp_linear_backward_saved": (C.c_int, [_P, _I64, _I64, _I64, _P, _P, _P, _P, _P, _SZ, _P]),
     "zp_layernorm_work_bytes": (_SZ, [C.c_int]),
     "zp_layernorm_silu_forward": (C.c_int, [_I64, C.c_int, _P, _P, _P, C.c_float, _P, _P, _P, _P]),
     "zp_layernorm_silu_backward": (C.c_int, [_I64, C.c_int, _P, _P, _P, _P, _P, _P, _P, _P, _P, _P,

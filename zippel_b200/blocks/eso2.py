@@ -426,34 +426,36 @@ class TensorCoreLinear(torch.autograd.Function):
                                              bf.data_ptr(), y.data_ptr(), work.data_ptr(), nbytes,
                                              st), "zp_linear_forward")
         ctx.plan, ctx.dtypes = plan, (x.dtype, weight.dtype, bias.dtype)
-        ctx.save_for_backward(xf, wf)
+        # what the backward reads of x and W are their 16-bit planes, which the forward has just
+        # written into `work`: the buffer is kept instead of the two fp32 arrays, and the backward
+        # neither scans nor re-formats them again
+        ctx.shape = (m, k, n)
+        ctx.work = work if any(ctx.needs_input_grad) else None
         return y.to(x.dtype)
 
     @staticmethod
     @torch.autograd.function.once_differentiable
     def backward(ctx, grad_y):
         lib = _lib.load()
-        xf, wf = ctx.saved_tensors
-        plan = ctx.plan
-        m, k = xf.shape
-        n = wf.shape[0]
+        plan, work = ctx.plan, ctx.work
+        m, k, n = ctx.shape
         dy = _f32(grad_y)
+        dev = dy.device
         # a frozen layer forms the input gradient only; a layer whose input needs none, the
         # parameter gradients only
         want_x = ctx.needs_input_grad[1]
         want_w = ctx.needs_input_grad[2] or ctx.needs_input_grad[3] or not want_x
-        dx = torch.empty_like(xf) if want_x else None
-        dw = torch.empty_like(wf) if want_w else None
-        db = torch.empty(n, dtype=torch.float32, device=xf.device) if want_w else None
-        nbytes = lib.zp_linear_work_bytes(plan.handle, m, k, n)
-        work = torch.empty(nbytes, dtype=torch.uint8, device=xf.device)
+        f32 = dict(dtype=torch.float32, device=dev)
+        dx = torch.empty(m, k, **f32) if want_x else None
+        dw = torch.empty(n, k, **f32) if want_w else None
+        db = torch.empty(n, **f32) if want_w else None
         ptr = lambda t: t.data_ptr() if t is not None else None                  # noqa: E731
-        with torch.cuda.device(xf.device):
+        with torch.cuda.device(dev):
             st = torch.cuda.current_stream().cuda_stream
-            _lib.check(lib.zp_linear_backward(plan.handle, m, k, n, xf.data_ptr(), wf.data_ptr(),
-                                              dy.data_ptr(), ptr(dx), ptr(dw), ptr(db),
-                                              work.data_ptr(), nbytes, st),
-                       "zp_linear_backward")
+            _lib.check(lib.zp_linear_backward_saved(plan.handle, m, k, n, dy.data_ptr(), ptr(dx),
+                                                    ptr(dw), ptr(db), work.data_ptr(),
+                                                    work.numel(), st),
+                       "zp_linear_backward_saved")
         dt = ctx.dtypes
         to = lambda t, d: t.to(d) if t is not None else None                       # noqa: E731
         return None, to(dx, dt[0]), to(dw, dt[1]), to(db, dt[2])

@@ -155,4 +155,24 @@ int zp_linear_backward(const zp_plan *plan, int64_t M, int64_t K, int64_t N, con
                                    kLinSplits, lw.colsum, st);
 }
 
+int zp_linear_backward_saved(const zp_plan *plan, int64_t M, int64_t K, int64_t N, const float *dy,
+                             float *dx, float *dw, float *db, void *work, size_t work_bytes,
+                             void *stream) {
+  int rc = check(plan, M, K, N);
+  if (rc) return rc;
+  if (!work || (!dw && !dx) || (M && !dy)) return ZP_ERR_INVALID_ARG;
+  const LinWork lw = carve_lin(plan, M, K, N, work);
+  if (work_bytes < lw.bytes) return ZP_ERR_WORKSPACE;
+  cudaStream_t st = (cudaStream_t)stream;
+  if (M == 0) {
+    if (dw) ZP_CUDA(cudaMemsetAsync(dw, 0, sizeof(float) * N * K, st));
+    if (db) ZP_CUDA(cudaMemsetAsync(db, 0, sizeof(float) * N, st));
+    return ZP_OK;
+  }
+  // the planes of x and w and their scales are where zp_linear_forward left them
+  if ((rc = split_scaled(plan, M, N, dy, lw.dy, lw.scales + 4, st))) return rc;
+  return zp_linear_backward_planes(plan, M, K, N, lw.x, lw.w, lw.dy, dx, dw, db, lw.partials,
+                                   kLinSplits, lw.colsum, st);
+}
+
 }  // extern "C"

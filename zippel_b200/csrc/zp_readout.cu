@@ -209,8 +209,9 @@ int zp_readout_backward(const zp_plan *plan, int64_t N, const float *node_out, c
   head_param_grad_kernel<<<(unsigned)zp_ceil_div(t.C, 128), 128, 0, st>>>(N, t.C, rw.partial,
                                                                           grad_energy, grad_w1, grad_b1);
   ZP_LAUNCH_CHECK("head_param_grad_kernel");
-  int rc = zp_linear_backward(plan, N, W, t.C, rw.inv, w0, rw.g_hid, rw.g_inv, grad_w0, grad_b0,
-                              rw.linear, rw.linear_bytes, stream);
+  // the hidden layer's operand planes are still in the work buffer the forward used
+  int rc = zp_linear_backward_saved(plan, N, W, t.C, rw.g_hid, rw.g_inv, grad_w0, grad_b0,
+                                    rw.linear, rw.linear_bytes, stream);
   if (rc) return rc;
   node_invariants_bwd_kernel<<<(unsigned)N, 128, 0, st>>>(t, N, node_out, rw.g_inv, grad_node_out);
   ZP_LAUNCH_CHECK("node_invariants_bwd_kernel");

@@ -93,7 +93,11 @@ size_t zp_csr_work_bytes(int64_t n_edges, int64_t n_nodes);
 /* Node indices outside [0, n_nodes) are never used as addresses: such an edge is left out and a
  * flag in `work` is raised (the reference's torch indexing raises on the same input).
  * zp_csr_status waits for `stream` (the one the build was given) and reads the flag:
- * *status_out = ZP_OK, or ZP_ERR_INVALID_ARG when the arrays of that call are not a valid sort. */
+ * *status_out = ZP_OK, or ZP_ERR_INVALID_ARG when the arrays of that call are not a valid sort.
+ * Even then every entry stays inside its range: row_ptr[n_nodes] is the number of edges that were
+ * kept, and the slots past it hold an edge 0 -> 0 at original position 0, so a caller that
+ * launches per-edge work over all E slots without reading the flag (a recorded graph replay)
+ * never indexes outside its arrays.                                                           */
 int zp_csr_status(const void *work, void *stream, int *status_out);
 int zp_csr_build(const int64_t *edge_index /* [2,E] int64: row 0 src, row 1 dst */,
                  int64_t n_edges, int64_t n_nodes,

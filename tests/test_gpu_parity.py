@@ -208,11 +208,22 @@ def test_csr_build_rejects_node_indices_out_of_range():
     """What torch indexing does for the reference (IndexError), without any out-of-range access."""
     from zippel_b200.graph import EdgeGraph
     ei = torch.tensor([[0, 1, 2, 5], [1, 2, 0, 1]], dtype=torch.int64, device="cuda")
+    # free blocks of the caching allocator hold large values from here on: the sort's scratch and
+    # outputs start from them, so a slot that an omitted edge leaves unwritten would show
+    junk = torch.full((8 << 20,), 0x7F7F7F7F, dtype=torch.int32, device="cuda")
+    del junk
     with pytest.raises(IndexError):
         EdgeGraph.build(ei, 5)                       # src 5 >= N
     ei[0, 3] = -1
     with pytest.raises(IndexError):
         EdgeGraph.build(ei, 5)
+    # the arrays of a flagged sort still index inside [0, N) and [0, E) everywhere (a caller that
+    # replays a recorded step never reads the flag): the omitted edge's slot is an edge 0 -> 0
+    g = EdgeGraph.build(ei, 5, validate=False)
+    assert g.row_ptr.cpu().tolist() == [0, 1, 2, 3, 3, 3]
+    assert g.row_ptr_src.cpu().tolist() == [0, 2, 3, 4, 4, 4]
+    assert g.src.cpu().tolist() == [2, 0, 1, 0] and g.dst.cpu().tolist() == [0, 1, 2, 0]
+    assert g.perm.cpu().tolist() == [2, 0, 1, 0] and g.perm_src.cpu().tolist() == [1, 3, 2, 0]
     ei[0, 3] = 4
     assert EdgeGraph.build(ei, 5).row_ptr.cpu().tolist() == [0, 1, 3, 4, 4, 4]
 

@@ -31,10 +31,12 @@ __global__ void count_kernel(int64_t E, int64_t N, const int64_t *__restrict__ k
   }
   atomicAdd(&counts[k], 1);
 }
-// keys written by rank_dst_kernel: in range by construction, -1 in slots an invalid edge left empty
-__global__ void count32_kernel(int64_t E, const int32_t *__restrict__ key, int32_t *counts) {
+// keys written by rank_dst_kernel, or the 0 a slot without a valid edge was cleared to: in range
+// by construction (the test keeps a broken invariant from becoming a wild access)
+__global__ void count32_kernel(int64_t E, int64_t N, const int32_t *__restrict__ key,
+                               int32_t *counts) {
   const int64_t i = (int64_t)blockIdx.x * blockDim.x + threadIdx.x;
-  if (i < E && key[i] >= 0) atomicAdd(&counts[key[i]], 1);
+  if (i < E && (uint32_t)key[i] < (uint64_t)N) atomicAdd(&counts[key[i]], 1);
 }
 
 // exclusive scan of n ints in three steps: per-block scan, scan of block totals, add back
@@ -53,6 +55,7 @@ __global__ void scan_block_kernel(int64_t n, const int32_t *__restrict__ in, int
   if (i < n) out[i] = s[threadIdx.x] - in[i];          // exclusive
   if (threadIdx.x == kScanBlock - 1) block_sums[blockIdx.x] = s[threadIdx.x];
 }
+// block_sums [nb + 1]: exclusive prefix of the block totals, the grand total in slot nb
 __global__ void scan_sums_kernel(int64_t nb, int32_t *block_sums) {
   if (threadIdx.x == 0 && blockIdx.x == 0) {
     int32_t run = 0;
@@ -61,13 +64,16 @@ __global__ void scan_sums_kernel(int64_t nb, int32_t *block_sums) {
       block_sums[b] = run;
       run += v;
     }
+    block_sums[nb] = run;
   }
 }
-__global__ void scan_add_kernel(int64_t n, int32_t *out, const int32_t *__restrict__ block_sums,
-                                int32_t total_slot_value_is_E) {
+// out[n] = the number of elements COUNTED (edges that were left out for an invalid node index are
+// not among them), so that no offset range ever covers a slot nothing was written to
+__global__ void scan_add_kernel(int64_t n, int64_t nb, int32_t *out,
+                                const int32_t *__restrict__ block_sums) {
   const int64_t i = (int64_t)blockIdx.x * kScanBlock + threadIdx.x;
   if (i < n) out[i] += block_sums[blockIdx.x];
-  if (i == n) out[n] = total_slot_value_is_E;
+  if (i == n) out[n] = block_sums[nb];
 }
 
 __global__ void bucket_kernel(int64_t E, int64_t N, const int64_t *__restrict__ key,
@@ -80,18 +86,18 @@ __global__ void bucket_kernel(int64_t E, int64_t N, const int64_t *__restrict__ 
   if ((uint64_t)k >= (uint64_t)N || (uint64_t)other[i] >= (uint64_t)N) return;   // flagged above
   tmp[row_ptr[k] + atomicAdd(&cursor[k], 1)] = (int32_t)i;
 }
-__global__ void bucket32_kernel(int64_t E, const int32_t *__restrict__ key,
+__global__ void bucket32_kernel(int64_t E, int64_t N, const int32_t *__restrict__ key,
                                 const int32_t *__restrict__ row_ptr, int32_t *cursor,
                                 int32_t *tmp) {
   const int64_t i = (int64_t)blockIdx.x * blockDim.x + threadIdx.x;
   if (i >= E) return;
   const int32_t k = key[i];
-  if (k < 0) return;
+  if ((uint32_t)k >= (uint64_t)N) return;
   tmp[row_ptr[k] + atomicAdd(&cursor[k], 1)] = (int32_t)i;
 }
 
 // One warp per destination node: order its edges by (src, original position).
-__global__ void rank_dst_kernel(int64_t N, const int64_t *__restrict__ src64,
+__global__ void rank_dst_kernel(int64_t N, int64_t E, const int64_t *__restrict__ src64,
                                 const int32_t *__restrict__ row_ptr,
                                 const int32_t *__restrict__ tmp, int32_t *perm,
                                 int32_t *src_sorted, int32_t *dst_sorted) {
@@ -100,11 +106,15 @@ __global__ void rank_dst_kernel(int64_t N, const int64_t *__restrict__ src64,
   if (n >= N) return;
   const int beg = row_ptr[n], end = row_ptr[n + 1];
   for (int i = beg + lane; i < end; i += 32) {
+    // every slot of a bucket was filled by bucket_kernel with an edge id; the range test only
+    // keeps a broken invariant from turning into a wild read
     const int32_t id = tmp[i];
+    if ((uint32_t)id >= (uint64_t)E) continue;
     const int64_t s = src64[id];
     int rank = 0;
     for (int j = beg; j < end; ++j) {
       const int32_t jd = tmp[j];
+      if ((uint32_t)jd >= (uint64_t)E) continue;
       const int64_t sj = src64[jd];
       rank += (sj < s) || (sj == s && jd < id);
     }
@@ -125,7 +135,7 @@ __global__ void rank_src_kernel(int64_t N, const int32_t *__restrict__ row_ptr_s
     const int32_t id = tmp[i];
     int rank = 0;
     for (int j = beg; j < end; ++j) rank += tmp[j] < id;
-    perm_src[beg + rank] = id;
+    perm_src[beg + rank] = id;          // ids are positions 0 .. E-1 written by bucket32_kernel
   }
 }
 
@@ -151,14 +161,14 @@ CsrWork carve_csr(int64_t E, int64_t N, void *base) {
   return w;
 }
 
-int exclusive_scan(int64_t n, const int32_t *in, int32_t *out, int32_t *block_sums, int64_t E,
+int exclusive_scan(int64_t n, const int32_t *in, int32_t *out, int32_t *block_sums,
                    cudaStream_t st) {
   const int64_t nb = zp_ceil_div(n + 1, kScanBlock);
   scan_block_kernel<<<(unsigned)nb, kScanBlock, 0, st>>>(n, in, out, block_sums);
   ZP_LAUNCH_CHECK("scan_block_kernel");
   scan_sums_kernel<<<1, 32, 0, st>>>(nb, block_sums);
   ZP_LAUNCH_CHECK("scan_sums_kernel");
-  scan_add_kernel<<<(unsigned)nb, kScanBlock, 0, st>>>(n, out, block_sums, (int32_t)E);
+  scan_add_kernel<<<(unsigned)nb, kScanBlock, 0, st>>>(n, nb, out, block_sums);
   ZP_LAUNCH_CHECK("scan_add_kernel");
   return ZP_OK;
 }
@@ -189,9 +199,12 @@ int zp_csr_build(const int64_t *edge_index, int64_t E, int64_t N, int32_t *perm,
 
   // destination view
   ZP_CUDA(cudaMemsetAsync(w.flag, 0, sizeof(int32_t), st));
-  if (E) {      // slots an invalid edge leaves empty read as "no edge"
-    ZP_CUDA(cudaMemsetAsync(src_sorted, 0xff, sizeof(int32_t) * E, st));
-    ZP_CUDA(cudaMemsetAsync(dst_sorted, 0xff, sizeof(int32_t) * E, st));
+  if (E) {
+    // The slots an invalid edge leaves empty (the last ones, past row_ptr[N]) read as edges
+    // 0 -> 0 at position 0: a caller that launches per-edge kernels over all E slots without
+    // looking at the flag (a recorded graph replay) still indexes inside its arrays.
+    ZP_CUDA(cudaMemsetAsync(src_sorted, 0, sizeof(int32_t) * E, st));
+    ZP_CUDA(cudaMemsetAsync(dst_sorted, 0, sizeof(int32_t) * E, st));
     ZP_CUDA(cudaMemsetAsync(perm, 0, sizeof(int32_t) * E, st));
     ZP_CUDA(cudaMemsetAsync(perm_src, 0, sizeof(int32_t) * E, st));
   }
@@ -201,11 +214,11 @@ int zp_csr_build(const int64_t *edge_index, int64_t E, int64_t N, int32_t *perm,
     count_kernel<<<eb, 256, 0, st>>>(E, N, dst64, src64, w.counts, w.flag);
     ZP_LAUNCH_CHECK("count_kernel");
   }
-  if ((rc = exclusive_scan(N, w.counts, row_ptr, w.block_sums, E, st))) return rc;
+  if ((rc = exclusive_scan(N, w.counts, row_ptr, w.block_sums, st))) return rc;
   if (E) {
     bucket_kernel<<<eb, 256, 0, st>>>(E, N, dst64, src64, row_ptr, w.cursor, w.tmp);
     ZP_LAUNCH_CHECK("bucket_kernel");
-    rank_dst_kernel<<<nbw, 256, 0, st>>>(N, src64, row_ptr, w.tmp, perm, src_sorted, dst_sorted);
+    rank_dst_kernel<<<nbw, 256, 0, st>>>(N, E, src64, row_ptr, w.tmp, perm, src_sorted, dst_sorted);
     ZP_LAUNCH_CHECK("rank_dst_kernel");
   }
 
@@ -213,12 +226,12 @@ int zp_csr_build(const int64_t *edge_index, int64_t E, int64_t N, int32_t *perm,
   ZP_CUDA(cudaMemsetAsync(w.counts, 0, sizeof(int32_t) * (N + 1), st));
   ZP_CUDA(cudaMemsetAsync(w.cursor, 0, sizeof(int32_t) * (N + 1), st));
   if (E) {
-    count32_kernel<<<eb, 256, 0, st>>>(E, src_sorted, w.counts);
+    count32_kernel<<<eb, 256, 0, st>>>(E, N, src_sorted, w.counts);
     ZP_LAUNCH_CHECK("count32_kernel");
   }
-  if ((rc = exclusive_scan(N, w.counts, row_ptr_src, w.block_sums, E, st))) return rc;
+  if ((rc = exclusive_scan(N, w.counts, row_ptr_src, w.block_sums, st))) return rc;
   if (E) {
-    bucket32_kernel<<<eb, 256, 0, st>>>(E, src_sorted, row_ptr_src, w.cursor, w.tmp);
+    bucket32_kernel<<<eb, 256, 0, st>>>(E, N, src_sorted, row_ptr_src, w.cursor, w.tmp);
     ZP_LAUNCH_CHECK("bucket32_kernel");
     rank_src_kernel<<<nbw, 256, 0, st>>>(N, row_ptr_src, w.tmp, perm_src);
     ZP_LAUNCH_CHECK("rank_src_kernel");

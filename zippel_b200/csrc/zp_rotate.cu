@@ -199,7 +199,7 @@ __device__ __forceinline__ void cp_async_wait() {
 }
 
 template <int LMAX, int VEC>
-__global__ void __launch_bounds__(32 * kBackWarps)
+__global__ void __launch_bounds__(32 * kBackWarps, (LMAX >= 5 && VEC == 2 ? 3 : 1))
 rotate_back_scatter_kernel(const __grid_constant__ ZpTables t, int64_t N,
                            const float *__restrict__ y, const float *__restrict__ env,
                            const float *__restrict__ rot, const int32_t *__restrict__ row_ptr,
@@ -565,7 +565,7 @@ struct StageInBwd<-1, LMAX> {
 // Blocks of `nw` warps, W warps per edge; shared memory: rot [nw / W][nnz_pad] |
 // partial [nw][nnz_pad] | stage [nw][Km][128].
 template <int LMAX>
-__global__ void __launch_bounds__(128, (LMAX <= 4 ? 4 : 2))
+__global__ void __launch_bounds__(128, (LMAX <= 4 ? 4 : 3))
 rotate_in_bwd_kernel(const __grid_constant__ ZpTables t, int64_t E, int W,
                      const float *__restrict__ da1, const float *__restrict__ radial,
                      const float *__restrict__ x, const int32_t *__restrict__ src,
